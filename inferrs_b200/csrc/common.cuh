@@ -1,0 +1,69 @@
+// Shared helpers of the sm_100a kernels: element types, conversions, reductions, launch checks.
+//
+// Every library is built twice from the same sources: with -DIB_ACT_BF16=0 the
+// activation and cache element `act_t` is float (the true 32-bit path), with
+// -DIB_ACT_BF16=1 it is __nv_bfloat16.  Arithmetic inside the kernels is float in
+// both builds; only what is stored between kernels changes.
+#pragma once
+
+#include <cuda_bf16.h>
+#include <cuda_runtime.h>
+#include <stdint.h>
+
+#ifndef IB_ACT_BF16
+#error "build with -DIB_ACT_BF16=0 or -DIB_ACT_BF16=1"
+#endif
+
+#if IB_ACT_BF16
+typedef __nv_bfloat16 act_t;
+#else
+typedef float act_t;
+#endif
+
+#define IB_EXPORT extern "C" __attribute__((visibility("default")))
+
+// Error codes returned by the exported functions.  0 is success; positive values are
+// cudaError_t of the launch; negative values are refusals of the arguments.
+#define IB_OK 0
+#define IB_ERR_UNSUPPORTED (-1)
+#define IB_ERR_ARGUMENT (-2)
+
+__device__ __forceinline__ float ib_to_float(float v) { return v; }
+__device__ __forceinline__ float ib_to_float(__nv_bfloat16 v) { return __bfloat162float(v); }
+
+template <typename T> __device__ __forceinline__ T ib_from_float(float v);
+template <> __device__ __forceinline__ float ib_from_float<float>(float v) { return v; }
+template <> __device__ __forceinline__ __nv_bfloat16 ib_from_float<__nv_bfloat16>(float v) {
+    return __float2bfloat16_rn(v);
+}
+
+__device__ __forceinline__ float ib_warp_sum(float v) {
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) v += __shfl_xor_sync(0xffffffffu, v, o);
+    return v;
+}
+
+__device__ __forceinline__ float ib_warp_max(float v) {
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) v = fmaxf(v, __shfl_xor_sync(0xffffffffu, v, o));
+    return v;
+}
+
+// Sum over a block of up to 1024 threads; every thread gets the result.  The order of
+// the additions depends only on blockDim, so a row's result does not depend on the batch.
+__device__ __forceinline__ float ib_block_sum(float v, float* smem32) {
+    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+    const int nwarps = (blockDim.x + 31) >> 5;
+    v = ib_warp_sum(v);
+    __syncthreads();  // smem32 may still be read from an earlier call
+    if (lane == 0) smem32[warp] = v;
+    __syncthreads();
+    float r = (lane < nwarps) ? smem32[lane] : 0.0f;
+    r = ib_warp_sum(r);
+    return r;
+}
+
+static inline int ib_launch_status() {
+    cudaError_t e = cudaPeekAtLastError();
+    return e == cudaSuccess ? IB_OK : (int)e;
+}

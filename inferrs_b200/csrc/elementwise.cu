@@ -1,0 +1,122 @@
+// Embedding gather, fused residual-add + RMSNorm, SiLU-gate product.
+//
+// The residual stream is float in both builds: the sum x + delta is formed and
+// kept in 32-bit, and only the normalised copy that feeds the next matrix
+// product is stored as act_t.
+#include "common.cuh"
+
+// ---------------------------------------------------------------------------
+// Embedding: out[row, :] = table[ids[row], :]   (no scale)
+// ---------------------------------------------------------------------------
+template <typename WT>
+__global__ void embedding_gather_kernel(const WT* __restrict__ table, const int* __restrict__ ids,
+                                        float* __restrict__ out, int width, int vocab) {
+    const int row = blockIdx.x;
+    const int id = ids[row];
+    const bool ok = id >= 0 && id < vocab;  // the host refuses such ids before the launch
+    const WT* src = table + (size_t)(ok ? id : 0) * width;
+    float* dst = out + (size_t)row * width;
+    for (int j = threadIdx.x; j < width; j += blockDim.x) dst[j] = ok ? ib_to_float(src[j]) : 0.0f;
+}
+
+IB_EXPORT int ib_embedding_gather(const void* table, int table_is_f32, const int* ids, float* out, int n_rows,
+                                  int width, int vocab, cudaStream_t stream) {
+    if (n_rows <= 0) return IB_OK;
+    if (width <= 0 || vocab <= 0) return IB_ERR_ARGUMENT;
+    const int threads = width >= 1024 ? 256 : 128;
+    if (table_is_f32)
+        embedding_gather_kernel<float><<<n_rows, threads, 0, stream>>>((const float*)table, ids, out, width, vocab);
+    else
+        embedding_gather_kernel<__nv_bfloat16>
+            <<<n_rows, threads, 0, stream>>>((const __nv_bfloat16*)table, ids, out, width, vocab);
+    return ib_launch_status();
+}
+
+// ---------------------------------------------------------------------------
+// x += delta (kept in the float residual), out = x / sqrt(mean(x^2) + eps) * w
+//
+// rows == nullptr : row r of residual/delta -> row r of out; the sum is written back.
+// rows != nullptr : row rows[r] of residual/delta -> row r of out; nothing is written
+//                   back (used for the last norm, which only the wanted rows need).
+// ---------------------------------------------------------------------------
+template <typename WT>
+__global__ void add_rms_norm_kernel(float* __restrict__ residual, const act_t* __restrict__ delta,
+                                    const WT* __restrict__ weight, act_t* __restrict__ out,
+                                    const int* __restrict__ rows, int width, float eps) {
+    __shared__ float red[32];
+    const int r = blockIdx.x;
+    const int src = rows ? rows[r] : r;
+    float* res = residual + (size_t)src * width;
+    const act_t* del = delta ? delta + (size_t)src * width : nullptr;
+    const bool write_back = (rows == nullptr) && (del != nullptr);
+    float ss = 0.0f;
+    for (int j = threadIdx.x; j < width; j += blockDim.x) {
+        float v = res[j];
+        if (del) v += ib_to_float(del[j]);
+        if (write_back) res[j] = v;
+        ss += v * v;
+    }
+    ss = ib_block_sum(ss, red);
+    const float inv = 1.0f / sqrtf(ss / (float)width + eps);
+    act_t* dst = out + (size_t)r * width;
+    for (int j = threadIdx.x; j < width; j += blockDim.x) {
+        float v = res[j];  // this thread's own write, if there was one
+        if (del && !write_back) v += ib_to_float(del[j]);
+        dst[j] = ib_from_float<act_t>(v * inv * ib_to_float(weight[j]));
+    }
+}
+
+IB_EXPORT int ib_add_rms_norm(float* residual, const void* delta, const void* weight, int weight_is_f32, void* out,
+                              const int* rows, int n_rows, int width, float eps, cudaStream_t stream) {
+    if (n_rows <= 0) return IB_OK;
+    if (width <= 0) return IB_ERR_ARGUMENT;
+    int threads = 128;
+    if (width >= 2048) threads = 512;
+    else if (width >= 512) threads = 256;
+    if (weight_is_f32)
+        add_rms_norm_kernel<float><<<n_rows, threads, 0, stream>>>(residual, (const act_t*)delta, (const float*)weight,
+                                                                  (act_t*)out, rows, width, eps);
+    else
+        add_rms_norm_kernel<__nv_bfloat16><<<n_rows, threads, 0, stream>>>(
+            residual, (const act_t*)delta, (const __nv_bfloat16*)weight, (act_t*)out, rows, width, eps);
+    return ib_launch_status();
+}
+
+// ---------------------------------------------------------------------------
+// out[r, j] = silu(gate_up[r, j]) * gate_up[r, inner + j],  silu(z) = z / (1 + exp(-z))
+// ---------------------------------------------------------------------------
+__global__ void silu_gate_kernel(const act_t* __restrict__ gate_up, act_t* __restrict__ out, int inner, long total) {
+    for (long i = (long)blockIdx.x * blockDim.x + threadIdx.x; i < total; i += (long)gridDim.x * blockDim.x) {
+        const long r = i / inner;
+        const int j = (int)(i - r * inner);
+        const float g = ib_to_float(gate_up[r * 2 * inner + j]);
+        const float u = ib_to_float(gate_up[r * 2 * inner + inner + j]);
+        out[i] = ib_from_float<act_t>(g / (1.0f + expf(-g)) * u);
+    }
+}
+
+IB_EXPORT int ib_silu_gate(const void* gate_up, void* out, int n_rows, int inner, cudaStream_t stream) {
+    if (n_rows <= 0) return IB_OK;
+    if (inner <= 0) return IB_ERR_ARGUMENT;
+    const long total = (long)n_rows * inner;
+    long blocks = (total + 255) / 256;
+    if (blocks > 148L * 16) blocks = 148L * 16;
+    silu_gate_kernel<<<(int)blocks, 256, 0, stream>>>((const act_t*)gate_up, (act_t*)out, inner, total);
+    return ib_launch_status();
+}
+
+// ---------------------------------------------------------------------------
+// Casts between float and act_t (used where a 32-bit weight meets bfloat16 activations).
+// ---------------------------------------------------------------------------
+__global__ void act_to_float_kernel(const act_t* __restrict__ in, float* __restrict__ out, long total) {
+    for (long i = (long)blockIdx.x * blockDim.x + threadIdx.x; i < total; i += (long)gridDim.x * blockDim.x)
+        out[i] = ib_to_float(in[i]);
+}
+
+IB_EXPORT int ib_act_to_float(const void* in, float* out, long total, cudaStream_t stream) {
+    if (total <= 0) return IB_OK;
+    long blocks = (total + 255) / 256;
+    if (blocks > 148L * 16) blocks = 148L * 16;
+    act_to_float_kernel<<<(int)blocks, 256, 0, stream>>>((const act_t*)in, out, total);
+    return ib_launch_status();
+}

@@ -1,0 +1,104 @@
+// Per-head RMSNorm of queries and keys, rotation by position, and the write of
+// keys and values into their cache pages: one kernel, one pass over the fused
+// projection output.
+//
+// Input row layout: [ n_heads*d queries | n_kv_heads*d keys | n_kv_heads*d values ]
+// (or queries only, when the layer reads another entry's cache).
+// Norm, rotation angle tables (float) and the products are all 32-bit; only the
+// stores are act_t.
+#include "common.cuh"
+
+#define QRS_WARPS 4
+
+template <typename WT>
+__global__ void qk_norm_rope_store_kernel(
+    const act_t* __restrict__ qkv, int row_stride, int n_heads, int n_kv_heads, int head_dim, int store_kv,
+    const WT* __restrict__ q_weight, const WT* __restrict__ k_weight, float eps,
+    const float* __restrict__ cos_table, const float* __restrict__ sin_table, int rot_dim,
+    const int* __restrict__ positions, const int* __restrict__ row_request,
+    const int* __restrict__ block_table, int max_pages, int page_size, int n_pages,
+    act_t* __restrict__ k_pages, act_t* __restrict__ v_pages, act_t* __restrict__ q_out) {
+    extern __shared__ float smem[];
+    const int row = blockIdx.x;
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const int d = head_dim;
+    const int half = rot_dim / 2;
+    float* sh = smem + warp * d;
+    const int pos = positions[row];
+    const int heads_total = n_heads + (store_kv ? 2 * n_kv_heads : 0);
+
+    // Where this row's key and value go: page and place within the page.
+    long kv_base = -1;  // element offset of (page, kv head 0, slot, 0)
+    if (store_kv) {
+        const int req = row_request[row];
+        const int page = block_table[(long)req * max_pages + pos / page_size];
+        if (page >= 0 && page < n_pages)
+            kv_base = ((long)page * n_kv_heads * page_size + (pos % page_size)) * d;
+    }
+
+    for (int head = warp; head < heads_total; head += QRS_WARPS) {
+        const act_t* src = qkv + (long)row * row_stride + (long)head * d;
+        const int kind = head < n_heads ? 0 : (head < n_heads + n_kv_heads ? 1 : 2);  // 0 q, 1 k, 2 v
+        float ss = 0.0f;
+        for (int j = lane; j < d; j += 32) {
+            const float v = ib_to_float(src[j]);
+            sh[j] = v;
+            ss += v * v;
+        }
+        act_t* dst;
+        if (kind == 0) {
+            dst = q_out + ((long)row * n_heads + head) * d;
+        } else {
+            if (kv_base < 0) { __syncwarp(); continue; }
+            const int kvh = head - n_heads - (kind == 2 ? n_kv_heads : 0);
+            dst = (kind == 1 ? k_pages : v_pages) + kv_base + (long)kvh * page_size * d;
+        }
+        if (kind == 2) {
+            for (int j = lane; j < d; j += 32) dst[j] = ib_from_float<act_t>(sh[j]);
+            __syncwarp();
+            continue;
+        }
+        const WT* w = kind == 0 ? q_weight : k_weight;
+        if (w != nullptr) {
+            ss = ib_warp_sum(ss);
+            const float inv = 1.0f / sqrtf(ss / (float)d + eps);
+            for (int j = lane; j < d; j += 32) sh[j] = sh[j] * inv * ib_to_float(w[j]);
+        }
+        __syncwarp();
+        const float* c = cos_table + (long)pos * half;
+        const float* s = sin_table + (long)pos * half;
+        for (int j = lane; j < d; j += 32) {
+            float o;
+            if (j < half) o = sh[j] * c[j] - sh[j + half] * s[j];
+            else if (j < rot_dim) o = sh[j - half] * s[j - half] + sh[j] * c[j - half];
+            else o = sh[j];
+            dst[j] = ib_from_float<act_t>(o);
+        }
+        __syncwarp();  // sh is overwritten by this warp's next head
+    }
+}
+
+IB_EXPORT int ib_qk_norm_rope_store(const void* qkv, int row_stride, int n_rows, int n_heads, int n_kv_heads,
+                                    int head_dim, int store_kv, const void* q_weight, const void* k_weight,
+                                    int weight_is_f32, float eps, const float* cos_table, const float* sin_table,
+                                    int rot_dim, int table_rows, const int* positions, const int* row_request,
+                                    const int* block_table, int max_pages, int page_size, int n_pages,
+                                    void* k_pages, void* v_pages, void* q_out, cudaStream_t stream) {
+    if (n_rows <= 0) return IB_OK;
+    if (head_dim <= 0 || head_dim > 1024 || n_heads <= 0 || rot_dim < 0 || rot_dim > head_dim || (rot_dim & 1))
+        return IB_ERR_ARGUMENT;
+    if (store_kv && (n_kv_heads <= 0 || page_size <= 0 || max_pages <= 0)) return IB_ERR_ARGUMENT;
+    if (rot_dim > 0 && (cos_table == nullptr || sin_table == nullptr || table_rows <= 0)) return IB_ERR_ARGUMENT;
+    const size_t smem = (size_t)QRS_WARPS * head_dim * sizeof(float);
+    if (weight_is_f32)
+        qk_norm_rope_store_kernel<float><<<n_rows, 32 * QRS_WARPS, smem, stream>>>(
+            (const act_t*)qkv, row_stride, n_heads, n_kv_heads, head_dim, store_kv, (const float*)q_weight,
+            (const float*)k_weight, eps, cos_table, sin_table, rot_dim, positions, row_request, block_table,
+            max_pages, page_size, n_pages, (act_t*)k_pages, (act_t*)v_pages, (act_t*)q_out);
+    else
+        qk_norm_rope_store_kernel<__nv_bfloat16><<<n_rows, 32 * QRS_WARPS, smem, stream>>>(
+            (const act_t*)qkv, row_stride, n_heads, n_kv_heads, head_dim, store_kv, (const __nv_bfloat16*)q_weight,
+            (const __nv_bfloat16*)k_weight, eps, cos_table, sin_table, rot_dim, positions, row_request, block_table,
+            max_pages, page_size, n_pages, (act_t*)k_pages, (act_t*)v_pages, (act_t*)q_out);
+    return ib_launch_status();
+}

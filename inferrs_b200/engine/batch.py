@@ -1,0 +1,147 @@
+"""One step's batch: which tokens of which requests run, and what the kernels need to know of them.
+
+The reference runs one sequence per forward pass, either its whole prompt or
+one decoded token (inferrs/src/engine.rs:2074-2147), and resolves cache slots
+on the host per pass (inferrs-models/src/models/attention_utils.rs:252-283).
+Here a step is a flat list of rows: every request contributes its next tokens,
+a portion of a prompt or a single decoded token, and the rows of one request
+stand together in order.
+"""
+from __future__ import annotations
+
+from dataclasses import dataclass, field
+from typing import Hashable, List, Optional, Sequence
+
+import numpy as np
+import torch
+
+from ..cache.manager import CacheManager
+from ..cache.storage import CacheStorage
+
+
+@dataclass
+class StepEntry:
+    """The next tokens of one request and the places among them whose logits are wanted."""
+
+    rid: Hashable
+    tokens: Sequence[int]
+    want: Sequence[int] = ()
+
+
+@dataclass
+class StepContext:
+    """Device tensors (int32) and host numbers that describe a step to the parts.
+
+    token_ids [N]      the rows' token ids
+    positions [N]      each row's position within its request
+    row_request [N]    each row's index into this step's requests
+    q_start [R+1]      rows q_start[r] .. q_start[r+1]-1 belong to request r
+    kv_len [R]         tokens of request r in the cache once this step's keys are written
+    slots [R]          state slot of request r
+    logit_rows [W]     rows whose logits are returned, in the order of entries and of ``want``
+    block_tables[g]    [R, max_pages_g] page ids of request r in cache group g (-1: given back)
+    """
+
+    token_ids: torch.Tensor
+    positions: torch.Tensor
+    row_request: torch.Tensor
+    q_start: torch.Tensor
+    kv_len: torch.Tensor
+    slots: torch.Tensor
+    logit_rows: torch.Tensor
+    block_tables: List[torch.Tensor]
+    storage: CacheStorage
+    n_rows: int
+    n_requests: int
+    q_lens: List[int]
+    kv_lens: List[int]
+    slot_list: List[int]
+    max_q_len: int
+    max_kv_len: int
+    extra: dict = field(default_factory=dict)
+
+    @property
+    def decode_only(self) -> bool:
+        return self.max_q_len == 1
+
+
+class BatchError(ValueError):
+    pass
+
+
+def build_context(entries: Sequence[StepEntry], manager: CacheManager, storage: CacheStorage, vocab_size: int,
+                  max_positions: int, device: torch.device, fixed_pages: Optional[Sequence[int]] = None
+                  ) -> StepContext:
+    """Check the entries and lay their rows out.  Pages must already be reserved in ``manager``.
+
+    ``fixed_pages[g]`` pads group g's block table to that many columns (for replayed launches
+    whose shapes must not change); otherwise each table is as wide as its longest row.
+    """
+    if not entries:
+        raise BatchError("a step needs at least one entry")
+    seen = set()
+    ids: List[int] = []
+    positions: List[int] = []
+    row_request: List[int] = []
+    q_start = [0]
+    kv_lens, slots, logit_rows, q_lens = [], [], [], []
+    for r, e in enumerate(entries):
+        if e.rid in seen:
+            raise BatchError(f"request {e.rid!r} appears twice in one step")
+        seen.add(e.rid)
+        toks = list(e.tokens)
+        if not toks:
+            raise BatchError(f"request {e.rid!r}: a step must bring at least one token")
+        held = manager.n_tokens(e.rid)
+        if held + len(toks) > max_positions:
+            raise BatchError(f"request {e.rid!r}: {held} + {len(toks)} tokens exceed the model's "
+                             f"{max_positions} positions")
+        for t in toks:
+            if not (isinstance(t, (int, np.integer)) and 0 <= int(t) < vocab_size):
+                raise BatchError(f"request {e.rid!r}: token id {t!r} is outside the vocabulary of {vocab_size}")
+        for w in e.want:
+            if not 0 <= int(w) < len(toks):
+                raise BatchError(f"request {e.rid!r}: wanted place {w} is outside its {len(toks)} tokens")
+            logit_rows.append(q_start[-1] + int(w))
+        ids.extend(int(t) for t in toks)
+        positions.extend(range(held, held + len(toks)))
+        row_request.extend([r] * len(toks))
+        q_start.append(q_start[-1] + len(toks))
+        q_lens.append(len(toks))
+        kv_lens.append(held + len(toks))
+        slots.append(manager.slot(e.rid))
+    n, nreq = len(ids), len(entries)
+    tables = []
+    for g in range(len(manager.groups)):
+        rows = [manager.block_table(e.rid, g) for e in entries]
+        width = max(1, max(len(t) for t in rows))
+        if fixed_pages is not None:
+            if width > fixed_pages[g]:
+                raise BatchError(f"group {g}: a block table of {width} pages exceeds the fixed {fixed_pages[g]}")
+            width = fixed_pages[g]
+        arr = np.full((nreq, width), -1, dtype=np.int32)
+        for r, t in enumerate(rows):
+            arr[r, :len(t)] = t
+        tables.append(arr)
+    # one host buffer, one copy
+    parts = [np.asarray(ids, dtype=np.int32), np.asarray(positions, dtype=np.int32),
+             np.asarray(row_request, dtype=np.int32), np.asarray(q_start, dtype=np.int32),
+             np.asarray(kv_lens, dtype=np.int32), np.asarray(slots, dtype=np.int32),
+             np.asarray(logit_rows, dtype=np.int32)] + [t.reshape(-1) for t in tables]
+    sizes = [p.size for p in parts]
+    # every part starts on a 16-byte boundary, which vector loads and bulk copies need
+    offsets, total = [], 0
+    for s in sizes:
+        offsets.append(total)
+        total += (s + 3) // 4 * 4
+    host = np.zeros(max(total, 4), dtype=np.int32)
+    for p, o in zip(parts, offsets):
+        host[o:o + p.size] = p
+    dev = torch.from_numpy(host).to(device)
+    views = [dev[o:o + s] for o, s in zip(offsets, sizes)]
+    return StepContext(
+        token_ids=views[0], positions=views[1], row_request=views[2], q_start=views[3], kv_len=views[4],
+        slots=views[5], logit_rows=views[6],
+        block_tables=[views[7 + g].view(nreq, tables[g].shape[1]) for g in range(len(tables))],
+        storage=storage, n_rows=n, n_requests=nreq, q_lens=q_lens, kv_lens=kv_lens, slot_list=slots,
+        max_q_len=max(q_lens), max_kv_len=max(kv_lens))

@@ -1,0 +1,128 @@
+"""A model assembled from a :class:`ModelSpec`: embedding, scheduled layers, last norm, head.
+
+Nothing here is specific to an architecture.  The reference's counterpart is
+``Qwen3Model::forward`` (inferrs-models/src/models/qwen3.rs:398-407): embed,
+run the layers, norm, and logits for the rows that are wanted (the reference
+wants only the last, inferrs-models/src/models/attention_utils.rs:382-395).
+"""
+from __future__ import annotations
+
+from typing import Dict, List, Optional
+
+import torch
+
+from .. import kernels
+from ..cache.storage import KVNeed, StateNeed
+from ..parts.basic import Linear
+from ..parts.registry import part_class
+from ..parts.spec import ModelSpec, TensorDecl
+from ..runtime import Runtime
+
+
+class ModelError(ValueError):
+    pass
+
+
+def declared_tensors(spec: ModelSpec) -> List[TensorDecl]:
+    """Every tensor the model's parts expect, in a fixed order, each name once."""
+    decls: List[TensorDecl] = [TensorDecl(spec.embedding, (spec.vocab_size, spec.width))]
+    for layer in spec.layers:
+        decls += part_class("norm", layer.mixer_norm).declare(layer.mixer_norm)
+        decls += part_class("mixer", layer.mixer).declare(layer.mixer)
+        decls += part_class("norm", layer.ffn_norm).declare(layer.ffn_norm)
+        decls += part_class("feed_forward", layer.ffn).declare(layer.ffn)
+    decls += part_class("norm", spec.final_norm).declare(spec.final_norm)
+    decls.append(TensorDecl(spec.lm_head, (spec.vocab_size, spec.width), optional=spec.lm_head_optional))
+    seen, out = {}, []
+    for d in decls:
+        if d.name in seen:
+            if seen[d.name].shape != d.shape:
+                raise ModelError(f"tensor '{d.name}' is declared with shapes {seen[d.name].shape} and {d.shape}")
+            continue
+        seen[d.name] = d
+        out.append(d)
+    return out
+
+
+def check_schedule(spec: ModelSpec):
+    """The schedule names existing layers; every cache has exactly one writer, which runs before its readers."""
+    if not spec.schedule:
+        raise ModelError("the schedule is empty")
+    writers: Dict[int, int] = {}
+    for i, e in enumerate(spec.schedule):
+        if not 0 <= e.layer < len(spec.layers):
+            raise ModelError(f"schedule entry {i} names layer {e.layer}; the model has {len(spec.layers)}")
+        mixer = spec.layers[e.layer].mixer
+        cls = part_class("mixer", mixer)
+        writes = cls.writes_cache(mixer) if hasattr(cls, "writes_cache") else True
+        if writes:
+            if e.cache in writers:
+                raise ModelError(f"cache {e.cache} is written by schedule entries {writers[e.cache]} and {i}")
+            writers[e.cache] = i
+        elif e.cache not in writers:
+            raise ModelError(f"schedule entry {i} reads cache {e.cache} before any entry has written it")
+
+
+def cache_needs(spec: ModelSpec):
+    """(paged needs, fixed-size state needs) per cache id, asked of the mixers in the schedule."""
+    check_schedule(spec)
+    kv: Dict[int, KVNeed] = {}
+    states: Dict[int, StateNeed] = {}
+    for e in spec.schedule:
+        mixer = spec.layers[e.layer].mixer
+        cls = part_class("mixer", mixer)
+        need = cls.cache_need(mixer)
+        if need is not None:
+            if e.cache in kv and kv[e.cache] != need:
+                raise ModelError(f"cache {e.cache} is used with different needs: {kv[e.cache]} and {need}")
+            kv[e.cache] = need
+        st = cls.state_need(mixer)
+        if st is not None:
+            if e.cache in states and states[e.cache] != st:
+                raise ModelError(f"state {e.cache} is used with different needs")
+            states[e.cache] = st
+    return kv, states
+
+
+class Model:
+    def __init__(self, spec: ModelSpec, weights: Dict[str, torch.Tensor], rt: Runtime):
+        check_schedule(spec)
+        self.spec = spec
+        self.rt = rt
+        self.embedding = weights[spec.embedding]
+        self.blocks = []
+        for layer in spec.layers:
+            mixer_norm = part_class("norm", layer.mixer_norm)(layer.mixer_norm, weights, rt)
+            mixer = part_class("mixer", layer.mixer)(layer.mixer, weights, rt)
+            ffn_norm = part_class("norm", layer.ffn_norm)(layer.ffn_norm, weights, rt)
+            ffn = part_class("feed_forward", layer.ffn)(layer.ffn, weights, rt)
+            self.blocks.append(part_class("arrangement", _Arrangement(layer.arrangement))(
+                layer, mixer_norm, mixer, ffn_norm, ffn))
+        self.final_norm = part_class("norm", spec.final_norm)(spec.final_norm, weights, rt)
+        head = weights.get(spec.lm_head)
+        if head is None:
+            if not spec.lm_head_optional:
+                raise ModelError(f"tensor '{spec.lm_head}' is missing and the model does not tie its head")
+            head = self.embedding  # the table stands in (qwen3.rs:366-373)
+        self.tied = head is self.embedding
+        self.head = Linear(head, rt)
+
+    def forward(self, ctx) -> torch.Tensor:
+        """Run the step's rows through all scheduled layers; float32 logits [wanted rows, vocab]."""
+        n = ctx.token_ids.shape[0]
+        residual = torch.empty((n, self.spec.width), dtype=torch.float32, device=self.rt.device)
+        kernels.embedding_gather(self.embedding, ctx.token_ids, residual, self.rt.dtype)
+        pending: Optional[torch.Tensor] = None
+        for entry in self.spec.schedule:
+            pending = self.blocks[entry.layer].forward(ctx, entry.cache, residual, pending)
+        if ctx.logit_rows.shape[0] == 0:
+            return torch.empty((0, self.spec.vocab_size), dtype=torch.float32, device=self.rt.device)
+        h = self.final_norm.add_norm(residual, pending, rows=ctx.logit_rows)
+        return self.head(h, out_dtype=torch.float32)
+
+
+class _Arrangement:
+    """The arrangement's name as a description with a ``kind``."""
+
+    def __init__(self, kind: str):
+        self.kind = kind

@@ -1,0 +1,77 @@
+"""The step function: run the tokens it is given, as one batch, from the cache.
+
+``ModelRunner`` owns the model, the cache's device memory and its book-keeping.
+``step`` takes a list of (request, its next tokens, wanted places), reserves the
+pages, runs only those tokens through every scheduled layer, and returns the
+logits at the wanted places.  Portions of prompts and single decoded tokens may
+stand side by side; a prompt may be cut anywhere.
+
+The reference's nearest counterparts are ``CausalLM::forward_paged``
+(inferrs-models/src/models/mod.rs:169-339) driven per sequence by
+``cb_prefill`` / ``cb_decode_step`` (inferrs/src/engine.rs:2074-2147).
+"""
+from __future__ import annotations
+
+from typing import Dict, Hashable, List, Optional, Sequence
+
+import torch
+
+from ..cache.manager import CacheManager, OutOfPages
+from ..cache.storage import CacheStorage
+from ..parts.spec import ModelSpec
+from ..runtime import Runtime
+from .batch import StepContext, StepEntry, build_context
+from .model import Model, cache_needs
+
+
+class ModelRunner:
+    def __init__(self, spec: ModelSpec, weights: Dict[str, torch.Tensor], rt: Runtime, page_size: int,
+                 n_pages: int, max_requests: int):
+        self.spec = spec
+        self.rt = rt
+        self.model = Model(spec, weights, rt)
+        kv_needs, state_needs = cache_needs(spec)
+        self.storage = CacheStorage(kv_needs, state_needs, page_size, n_pages, max_requests, rt.dtype, rt.device)
+        self.manager = CacheManager(self.storage.layouts, page_size, self.storage.n_pages, max_requests)
+        self.page_size = page_size
+        self.steps_run = 0
+
+    # ---- requests -----------------------------------------------------------
+    def admit(self, rid: Hashable) -> int:
+        slot = self.manager.admit(rid)
+        self.storage.clear_slot(slot)
+        return slot
+
+    def release(self, rid: Hashable):
+        self.manager.release(rid)
+
+    def has(self, rid: Hashable) -> bool:
+        return self.manager.has(rid)
+
+    def n_tokens(self, rid: Hashable) -> int:
+        return self.manager.n_tokens(rid)
+
+    # ---- the step -----------------------------------------------------------
+    def prepare(self, entries: Sequence[StepEntry], fixed_pages: Optional[Sequence[int]] = None) -> StepContext:
+        """Reserve pages for all entries (all or nothing: OutOfPages leaves the cache untouched) and
+        build the step's description."""
+        wants = {}
+        for e in entries:
+            if e.rid in wants:
+                raise ValueError(f"request {e.rid!r} appears twice in one step")
+            wants[e.rid] = len(e.tokens)
+        self.manager.reserve(wants)
+        return build_context(entries, self.manager, self.storage, self.spec.vocab_size, self.spec.max_positions,
+                             self.rt.device, fixed_pages)
+
+    def commit(self, entries: Sequence[StepEntry]):
+        for e in entries:
+            self.manager.commit(e.rid, len(e.tokens))
+        self.steps_run += 1
+
+    def step(self, entries: Sequence[StepEntry]) -> torch.Tensor:
+        """float32 logits [number of wanted places, vocab], in the order of entries and of ``want``."""
+        ctx = self.prepare(entries)
+        logits = self.model.forward(ctx)
+        self.commit(entries)
+        return logits

@@ -1,0 +1,294 @@
+"""Python face of the CUDA kernels in ``csrc/``.
+
+Every function checks what it is given (device, dtype, shape, contiguity),
+refuses what the kernel does not take with a clear message, and launches on
+torch's current CUDA stream.  There is no other implementation behind these
+functions: without a CUDA device, ``nvcc`` or a successful build they raise.
+"""
+from __future__ import annotations
+
+import ctypes
+from typing import Optional
+
+import torch
+
+from .csrc.build import load_library
+
+c_int, c_long, c_float, c_void_p = ctypes.c_int, ctypes.c_long, ctypes.c_float, ctypes.c_void_p
+
+
+class KernelError(RuntimeError):
+    pass
+
+
+_SIGNATURES = {
+    "ib_embedding_gather": [c_void_p, c_int, c_void_p, c_void_p, c_int, c_int, c_int, c_void_p],
+    "ib_add_rms_norm": [c_void_p, c_void_p, c_void_p, c_int, c_void_p, c_void_p, c_int, c_int, c_float, c_void_p],
+    "ib_silu_gate": [c_void_p, c_void_p, c_int, c_int, c_void_p],
+    "ib_act_to_float": [c_void_p, c_void_p, c_long, c_void_p],
+    "ib_qk_norm_rope_store": [c_void_p, c_int, c_int, c_int, c_int, c_int, c_int, c_void_p, c_void_p, c_int, c_float,
+                              c_void_p, c_void_p, c_int, c_int, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int,
+                              c_void_p, c_void_p, c_void_p, c_void_p],
+    "ib_paged_attention_generic": [c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_void_p, c_void_p,
+                                   c_int, c_int, c_int, c_int, c_float, c_int, c_void_p, c_void_p],
+    "ib_gemm_tn_simt": [c_void_p, c_int, c_void_p, c_int, c_void_p, c_int, c_int, c_int, c_int, c_long, c_long,
+                        c_long, c_void_p],
+    "ib_argmax": [c_void_p, c_void_p, c_int, c_int, c_long, c_void_p],
+}
+
+_LIBS = {}
+
+
+def _core(act_dtype: torch.dtype):
+    """The core library built for this activation dtype, with argument types set."""
+    if act_dtype == torch.float32:
+        name = "core_f32"
+    elif act_dtype == torch.bfloat16:
+        name = "core_bf16"
+    else:
+        raise KernelError(f"activations must be float32 or bfloat16, got {act_dtype}")
+    lib = _LIBS.get(name)
+    if lib is None:
+        lib = load_library(name)
+        for fn, args in _SIGNATURES.items():
+            f = getattr(lib, fn)
+            f.argtypes = args
+            f.restype = c_int
+        _LIBS[name] = lib
+    return lib
+
+
+def _stream() -> int:
+    return torch.cuda.current_stream().cuda_stream
+
+
+def _check(code: int, what: str):
+    if code == 0:
+        return
+    if code == -1:
+        raise KernelError(f"{what}: these sizes are not supported by the kernel")
+    if code == -2:
+        raise KernelError(f"{what}: invalid argument")
+    raise KernelError(f"{what}: CUDA launch failed with error {code}")
+
+
+def _need(t: Optional[torch.Tensor], name: str, dtypes, ndim: Optional[int] = None, optional: bool = False):
+    if t is None:
+        if optional:
+            return
+        raise KernelError(f"{name} is required")
+    if not t.is_cuda:
+        raise KernelError(f"{name} must be a CUDA tensor (the kernels have no CPU implementation), got {t.device}")
+    if t.dtype not in dtypes:
+        raise KernelError(f"{name} must have dtype in {dtypes}, got {t.dtype}")
+    if ndim is not None and t.dim() != ndim:
+        raise KernelError(f"{name} must have {ndim} dimensions, got shape {tuple(t.shape)}")
+    if not t.is_contiguous():
+        raise KernelError(f"{name} must be contiguous, got strides {t.stride()} for shape {tuple(t.shape)}")
+
+
+def _p(t: Optional[torch.Tensor]) -> Optional[int]:
+    return None if t is None else t.data_ptr()
+
+
+_W = (torch.float32, torch.bfloat16)
+_I = (torch.int32,)
+
+
+def embedding_gather(table: torch.Tensor, ids: torch.Tensor, out: torch.Tensor, act_dtype: torch.dtype):
+    """out[r, :] = table[ids[r], :] as float32."""
+    _need(table, "table", _W, 2)
+    _need(ids, "ids", _I, 1)
+    _need(out, "out", (torch.float32,), 2)
+    n, width = out.shape
+    if ids.shape[0] != n or table.shape[1] != width:
+        raise KernelError(f"embedding_gather: ids {tuple(ids.shape)}, table {tuple(table.shape)}, out {tuple(out.shape)}")
+    _check(_core(act_dtype).ib_embedding_gather(_p(table), int(table.dtype == torch.float32), _p(ids), _p(out), n,
+                                                width, table.shape[0], _stream()), "embedding_gather")
+
+
+def add_rms_norm(residual: torch.Tensor, delta: Optional[torch.Tensor], weight: torch.Tensor, eps: float,
+                 out: torch.Tensor, rows: Optional[torch.Tensor] = None):
+    """residual += delta (float32, in place when ``rows`` is None); out = rms_norm(residual) * weight.
+
+    With ``rows`` (int32 [W]) only those rows are read and out has W rows; nothing is written back.
+    """
+    act = out.dtype
+    _need(residual, "residual", (torch.float32,), 2)
+    _need(delta, "delta", (act,), 2, optional=True)
+    _need(weight, "weight", _W, 1)
+    _need(out, "out", _W, 2)
+    _need(rows, "rows", _I, 1, optional=True)
+    n, width = residual.shape
+    n_out = n if rows is None else rows.shape[0]
+    if weight.shape[0] != width or out.shape != (n_out, width) or (delta is not None and delta.shape != residual.shape):
+        raise KernelError(f"add_rms_norm: residual {tuple(residual.shape)}, weight {tuple(weight.shape)}, "
+                          f"out {tuple(out.shape)}, delta {None if delta is None else tuple(delta.shape)}")
+    _check(_core(act).ib_add_rms_norm(_p(residual), _p(delta), _p(weight), int(weight.dtype == torch.float32),
+                                      _p(out), _p(rows), n_out, width, float(eps), _stream()), "add_rms_norm")
+
+
+def silu_gate(gate_up: torch.Tensor, out: torch.Tensor):
+    """out[r, j] = silu(gate_up[r, j]) * gate_up[r, inner + j]."""
+    act = out.dtype
+    _need(gate_up, "gate_up", (act,), 2)
+    _need(out, "out", _W, 2)
+    n, inner = out.shape
+    if gate_up.shape != (n, 2 * inner):
+        raise KernelError(f"silu_gate: gate_up {tuple(gate_up.shape)} does not match out {tuple(out.shape)}")
+    _check(_core(act).ib_silu_gate(_p(gate_up), _p(out), n, inner, _stream()), "silu_gate")
+
+
+def qk_norm_rope_store(qkv: torch.Tensor, n_heads: int, n_kv_heads: int, head_dim: int, store_kv: bool,
+                       q_weight: Optional[torch.Tensor], k_weight: Optional[torch.Tensor], eps: float,
+                       cos: Optional[torch.Tensor], sin: Optional[torch.Tensor], rot_dim: int,
+                       positions: torch.Tensor, row_request: torch.Tensor, block_table: Optional[torch.Tensor],
+                       k_pages: Optional[torch.Tensor], v_pages: Optional[torch.Tensor], q_out: torch.Tensor):
+    """Per-head norm of q and k, rotation by position, q to ``q_out``, k and v into their pages.
+
+    qkv [N, (n_heads + 2 n_kv_heads) * d] (queries only when ``store_kv`` is False);
+    pages [n_pages, n_kv_heads, page_size, d]; block_table int32 [R, max_pages].
+    """
+    act = q_out.dtype
+    _need(qkv, "qkv", (act,), 2)
+    _need(q_out, "q_out", _W, 3)
+    _need(positions, "positions", _I, 1)
+    _need(row_request, "row_request", _I, 1)
+    n = qkv.shape[0]
+    cols = (n_heads + (2 * n_kv_heads if store_kv else 0)) * head_dim
+    if qkv.shape[1] != cols or q_out.shape != (n, n_heads, head_dim) or positions.shape[0] != n \
+            or row_request.shape[0] != n:
+        raise KernelError(f"qk_norm_rope_store: qkv {tuple(qkv.shape)} (want {cols} columns), q_out "
+                          f"{tuple(q_out.shape)}, positions {tuple(positions.shape)}")
+    wdt = None
+    for name, w in (("q_weight", q_weight), ("k_weight", k_weight)):
+        _need(w, name, _W, 1, optional=True)
+        if w is not None:
+            if w.shape[0] != head_dim:
+                raise KernelError(f"{name} has {w.shape[0]} elements, head_dim is {head_dim}")
+            if wdt is not None and w.dtype != wdt:
+                raise KernelError("q_weight and k_weight must have the same dtype")
+            wdt = w.dtype
+    table_rows = 0
+    if rot_dim:
+        _need(cos, "cos", (torch.float32,), 2)
+        _need(sin, "sin", (torch.float32,), 2)
+        if cos.shape[1] != rot_dim // 2 or sin.shape != cos.shape:
+            raise KernelError(f"rotation tables {tuple(cos.shape)} do not match rot_dim {rot_dim}")
+        table_rows = cos.shape[0]
+    max_pages = page_size = n_pages = 0
+    if store_kv:
+        _need(block_table, "block_table", _I, 2)
+        _need(k_pages, "k_pages", (act,), 4)
+        _need(v_pages, "v_pages", (act,), 4)
+        n_pages, nkv, page_size, d = k_pages.shape
+        if (nkv, d) != (n_kv_heads, head_dim) or v_pages.shape != k_pages.shape:
+            raise KernelError(f"cache pages {tuple(k_pages.shape)} do not match {n_kv_heads} heads of {head_dim}")
+        max_pages = block_table.shape[1]
+    _check(_core(act).ib_qk_norm_rope_store(
+        _p(qkv), cols, n, n_heads, n_kv_heads, head_dim, int(store_kv), _p(q_weight), _p(k_weight),
+        int(wdt == torch.float32), float(eps), _p(cos) if rot_dim else None, _p(sin) if rot_dim else None, rot_dim,
+        table_rows, _p(positions), _p(row_request), _p(block_table) if store_kv else None, max_pages, page_size,
+        n_pages, _p(k_pages) if store_kv else None, _p(v_pages) if store_kv else None, _p(q_out), _stream()),
+        "qk_norm_rope_store")
+
+
+def paged_attention_generic(q: torch.Tensor, k_pages: torch.Tensor, v_pages: torch.Tensor, block_table: torch.Tensor,
+                            row_request: torch.Tensor, positions: torch.Tensor, scale: float, window: Optional[int],
+                            out: torch.Tensor):
+    """out[r, h*d:(h+1)*d] = attention of token r's head h over its request's cached keys lo..pos."""
+    act = out.dtype
+    _need(q, "q", (act,), 3)
+    _need(k_pages, "k_pages", (act,), 4)
+    _need(v_pages, "v_pages", (act,), 4)
+    _need(block_table, "block_table", _I, 2)
+    _need(row_request, "row_request", _I, 1)
+    _need(positions, "positions", _I, 1)
+    _need(out, "out", _W, 2)
+    n, nh, d = q.shape
+    n_pages, nkv, page_size, dk = k_pages.shape
+    if dk != d or v_pages.shape != k_pages.shape or out.shape != (n, nh * d) or nh % nkv:
+        raise KernelError(f"paged_attention: q {tuple(q.shape)}, pages {tuple(k_pages.shape)}, out {tuple(out.shape)}")
+    if d > 512:
+        raise KernelError(f"paged_attention: head_dim {d} is larger than 512, the largest the kernel takes")
+    _check(_core(act).ib_paged_attention_generic(
+        _p(q), _p(k_pages), _p(v_pages), _p(block_table), block_table.shape[1], page_size, n_pages, _p(row_request),
+        _p(positions), n, nh, nkv, d, float(scale), int(window) if window else 0, _p(out), _stream()),
+        "paged_attention_generic")
+
+
+def gemm_tn_simt(x: torch.Tensor, w: torch.Tensor, out: torch.Tensor, act_dtype: torch.dtype):
+    """out = x @ w.T with 32-bit fused multiply-adds in ascending k (no tensor cores)."""
+    _need(x, "x", _W, 2)
+    _need(w, "w", _W, 2)
+    _need(out, "out", _W, 2)
+    n, k = x.shape
+    m = w.shape[0]
+    if w.shape[1] != k or out.shape != (n, m):
+        raise KernelError(f"gemm: x {tuple(x.shape)}, w {tuple(w.shape)}, out {tuple(out.shape)}")
+    code = _core(act_dtype).ib_gemm_tn_simt(_p(x), int(x.dtype == torch.float32), _p(w),
+                                            int(w.dtype == torch.float32), _p(out), int(out.dtype == torch.float32),
+                                            n, m, k, k, k, m, _stream())
+    if code == -1:
+        raise KernelError(f"gemm: no kernel for x {x.dtype}, w {w.dtype}, out {out.dtype} with activations {act_dtype}")
+    _check(code, "gemm_tn_simt")
+
+
+def argmax(logits: torch.Tensor, out: torch.Tensor, act_dtype: torch.dtype = torch.float32):
+    """out[r] = index of the largest logit of row r (lowest index among equals).  ``act_dtype`` only
+    selects which of the two builds of the kernel library serves the call."""
+    _need(logits, "logits", (torch.float32,), 2)
+    _need(out, "out", _I, 1)
+    if out.shape[0] != logits.shape[0]:
+        raise KernelError(f"argmax: logits {tuple(logits.shape)}, out {tuple(out.shape)}")
+    _check(_core(act_dtype).ib_argmax(_p(logits), _p(out), logits.shape[0], logits.shape[1], logits.shape[1],
+                                          _stream()), "argmax")
+
+
+_MM_F32_OUT = None  # does this torch give float32 results from a bfloat16 product?
+
+
+def gemm_tn_bf16(x: torch.Tensor, w: torch.Tensor, out: torch.Tensor):
+    """out = x @ w.T for bfloat16 x and w on the tensor cores with float32 accumulation.
+
+    The product itself is the vendor library's (cuBLASLt through ``torch.mm``), as the reference
+    calls cuBLAS for every matrix product (candle-core/src/cuda_backend/mod.rs:2260-2310).
+    ``out`` may be bfloat16 or float32.
+    """
+    global _MM_F32_OUT
+    _need(x, "x", (torch.bfloat16,), 2)
+    _need(w, "w", (torch.bfloat16,), 2)
+    _need(out, "out", _W, 2)
+    if w.shape[1] != x.shape[1] or out.shape != (x.shape[0], w.shape[0]):
+        raise KernelError(f"gemm: x {tuple(x.shape)}, w {tuple(w.shape)}, out {tuple(out.shape)}")
+    if out.dtype == torch.bfloat16:
+        torch.mm(x, w.t(), out=out)
+        return
+    if _MM_F32_OUT is None:
+        try:
+            torch.mm(x[:1], w[:8].t(), out_dtype=torch.float32)
+            _MM_F32_OUT = True
+        except (TypeError, RuntimeError):
+            _MM_F32_OUT = False
+    if _MM_F32_OUT:
+        torch.mm(x, w.t(), out_dtype=torch.float32, out=out)
+    else:
+        gemm_tn_simt(x, w, out, torch.bfloat16)
+
+
+def linear(x: torch.Tensor, w: torch.Tensor, out: torch.Tensor, act_dtype: torch.dtype):
+    """out = x @ w.T in the precision that ``act_dtype`` and the weight's own dtype ask for."""
+    if act_dtype == torch.float32 or w.dtype == torch.float32:
+        gemm_tn_simt(x, w, out, act_dtype)
+    else:
+        gemm_tn_bf16(x, w, out)
+
+
+def paged_attention(q: torch.Tensor, k_pages: torch.Tensor, v_pages: torch.Tensor, block_table: torch.Tensor,
+                    ctx, scale: float, window: Optional[int], out: torch.Tensor):
+    """Attention of every row of the step over its request's pages; picks the kernel for the sizes.
+
+    ``ctx`` is the step's :class:`~inferrs_b200.engine.batch.StepContext` (row_request, positions
+    and what the faster kernels need to cut the work).
+    """
+    paged_attention_generic(q, k_pages, v_pages, block_table, ctx.row_request, ctx.positions, scale, window, out)

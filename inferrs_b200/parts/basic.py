@@ -1,0 +1,108 @@
+"""Norm, position encoding and the matrix product that the other parts are made of."""
+from __future__ import annotations
+
+from typing import Dict, List, Optional, Sequence
+
+import torch
+
+from .. import kernels
+from ..runtime import Runtime
+from .registry import register_norm, register_position
+from .spec import NormSpec, PositionSpec, TensorDecl
+
+
+class RMSNorm:
+    """x / sqrt(mean(x^2) + eps) * w, in float32 (inferrs-kernels/candle-kernels/src/reduce.cu:188-228),
+    fused with the residual addition that precedes it in a block."""
+
+    @staticmethod
+    def declare(spec: NormSpec) -> List[TensorDecl]:
+        return [TensorDecl(spec.weight, (spec.size,), init="norm")]
+
+    def __init__(self, spec: NormSpec, weights: Dict[str, torch.Tensor], rt: Runtime):
+        self.spec = spec
+        self.rt = rt
+        self.weight = weights[spec.weight]
+
+    def add_norm(self, residual: torch.Tensor, delta: Optional[torch.Tensor],
+                 rows: Optional[torch.Tensor] = None) -> torch.Tensor:
+        n = residual.shape[0] if rows is None else rows.shape[0]
+        out = torch.empty((n, self.spec.size), dtype=self.rt.dtype, device=residual.device)
+        kernels.add_rms_norm(residual, delta, self.weight, self.spec.eps, out, rows)
+        return out
+
+
+register_norm("rms", RMSNorm)
+
+
+class RotarySplitHalf:
+    """cos/sin of position * theta^(-2i/rot_dim), i < rot_dim/2, all in float32
+    (inferrs-models/src/models/attention_utils.rs:186-216); element i is rotated with
+    element i + rot_dim/2 (attention_utils.rs:137-151).  The reference casts the tables to the
+    run dtype; here they stay float32."""
+
+    def __init__(self, spec: PositionSpec, rt: Runtime):
+        if spec.rot_dim <= 0 or spec.rot_dim % 2:
+            raise ValueError(f"rot_dim must be positive and even, got {spec.rot_dim}")
+        if spec.max_positions <= 0:
+            raise ValueError(f"max_positions must be positive, got {spec.max_positions}")
+        self.spec = spec
+        half = spec.rot_dim // 2
+        exponent = torch.arange(half, dtype=torch.float32) * 2.0 / float(spec.rot_dim)
+        inv_freq = 1.0 / torch.pow(torch.tensor(float(spec.theta), dtype=torch.float32), exponent)
+        angle = torch.arange(spec.max_positions, dtype=torch.float32)[:, None] * inv_freq[None, :]
+        self.cos = torch.cos(angle).contiguous().to(rt.device)
+        self.sin = torch.sin(angle).contiguous().to(rt.device)
+
+    def tables(self):
+        return self.cos, self.sin, self.spec.rot_dim
+
+
+class NoPosition:
+    def __init__(self, spec: PositionSpec, rt: Runtime):
+        self.spec = spec
+
+    def tables(self):
+        return None, None, 0
+
+
+register_position("rotary_split_half", RotarySplitHalf)
+register_position("none", NoPosition)
+
+
+def build_position(spec: PositionSpec, rt: Runtime):
+    """One table per distinct description, shared by all layers that name it."""
+    from .registry import part_class
+
+    key = ("position", spec)
+    if key not in rt.shared:
+        rt.shared[key] = part_class("position", spec)(spec, rt)
+    return rt.shared[key]
+
+
+def fuse_rows(tensors: Sequence[torch.Tensor]) -> torch.Tensor:
+    """Stack weight matrices [out_i, in] along ``out``.  Mixed precisions become float32."""
+    if len({t.dtype for t in tensors}) > 1:
+        tensors = [t.to(torch.float32) for t in tensors]
+    return torch.cat(list(tensors), dim=0).contiguous()
+
+
+class Linear:
+    """y = x W^T, W stored [out, in], no bias (candle-nn/src/linear.rs:41-82).
+
+    float32 runs: FFMA kernel.  bfloat16 runs: tensor-core product with float32 accumulation for a
+    bfloat16 weight; a weight that is stored in float32 keeps its precision and goes through the
+    FFMA kernel with the bfloat16 activations widened on the fly.
+    """
+
+    def __init__(self, weight: torch.Tensor, rt: Runtime):
+        if weight.dim() != 2:
+            raise ValueError(f"a linear weight must be a matrix, got shape {tuple(weight.shape)}")
+        self.weight = weight.contiguous()
+        self.rt = rt
+        self.n_out, self.n_in = weight.shape
+
+    def __call__(self, x: torch.Tensor, out_dtype: Optional[torch.dtype] = None) -> torch.Tensor:
+        out = torch.empty((x.shape[0], self.n_out), dtype=out_dtype or self.rt.dtype, device=x.device)
+        kernels.linear(x, self.weight, out, self.rt.dtype)
+        return out

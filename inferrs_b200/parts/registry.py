@@ -1,0 +1,78 @@
+"""From a part description's ``kind`` to the class that runs it.
+
+Five kinds of part can be registered: mixers, feed-forwards, norms, position
+encodings and block arrangements.  A model is built by looking up the class of
+every description in its :class:`~inferrs_b200.parts.spec.ModelSpec`; a test or
+a user adds a part with one ``register_*`` call and a description dataclass of
+their own, without touching this package.
+
+Interfaces (``rt`` is a :class:`~inferrs_b200.runtime.Runtime`, ``weights`` a
+dict from tensor name to tensor on the device):
+
+mixer
+    ``declare(spec) -> [TensorDecl]`` (static), ``cache_need(spec) -> KVNeed | None`` (static),
+    ``state_need(spec) -> StateNeed | None`` (static), ``__init__(spec, weights, rt)``,
+    ``forward(ctx, cache_id, h) -> y`` with h, y ``[rows, width]`` in the activation dtype.
+feed-forward
+    ``declare(spec)``, ``__init__(spec, weights, rt)``, ``forward(ctx, h) -> y``.
+norm
+    ``declare(spec)``, ``__init__(spec, weights, rt)``,
+    ``add_norm(residual, delta, rows=None) -> h``: adds ``delta`` (or nothing) into the float32
+    residual in place and returns the normalised rows in the activation dtype; with ``rows``
+    it reads only those rows and writes nothing back.
+position encoding
+    ``__init__(spec, rt)``, ``tables() -> (cos, sin, rot_dim)``: float32 ``[max_positions, rot_dim/2]``
+    tables that the attention kernels index by position (``rot_dim`` 0: no rotation).
+arrangement
+    ``__init__(spec, mixer_norm, mixer, ffn_norm, ffn)``,
+    ``forward(ctx, cache_id, residual, pending) -> pending``.
+"""
+from __future__ import annotations
+
+from typing import Any, Dict
+
+_CATEGORIES = ("mixer", "feed_forward", "norm", "position", "arrangement")
+_REGISTRY: Dict[str, Dict[str, type]] = {c: {} for c in _CATEGORIES}
+
+
+class PartError(ValueError):
+    pass
+
+
+def register_part(category: str, kind: str, cls: type, replace: bool = False) -> type:
+    if category not in _REGISTRY:
+        raise PartError(f"unknown part category '{category}'; one of {_CATEGORIES}")
+    if kind in _REGISTRY[category] and not replace and _REGISTRY[category][kind] is not cls:
+        raise PartError(f"{category} '{kind}' is already registered")
+    _REGISTRY[category][kind] = cls
+    return cls
+
+
+def register_mixer(kind: str, cls: type, replace: bool = False) -> type:
+    return register_part("mixer", kind, cls, replace)
+
+
+def register_feed_forward(kind: str, cls: type, replace: bool = False) -> type:
+    return register_part("feed_forward", kind, cls, replace)
+
+
+def register_norm(kind: str, cls: type, replace: bool = False) -> type:
+    return register_part("norm", kind, cls, replace)
+
+
+def register_position(kind: str, cls: type, replace: bool = False) -> type:
+    return register_part("position", kind, cls, replace)
+
+
+def register_arrangement(kind: str, cls: type, replace: bool = False) -> type:
+    return register_part("arrangement", kind, cls, replace)
+
+
+def part_class(category: str, spec: Any) -> type:
+    kind = getattr(spec, "kind", None)
+    if kind is None:
+        raise PartError(f"a {category} description needs a 'kind', got {spec!r}")
+    try:
+        return _REGISTRY[category][kind]
+    except KeyError:
+        raise PartError(f"no {category} of kind '{kind}' is registered; known: {sorted(_REGISTRY[category])}") from None

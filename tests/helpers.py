@@ -1,0 +1,43 @@
+"""Tiny configurations and the ways of cutting a request into steps that the tests share."""
+from __future__ import annotations
+
+import random
+from typing import Dict, List, Sequence
+
+import torch
+
+# Two configurations of the architecture that differ in every size and option.
+CONFIG_A = {
+    "architectures": ["Qwen3ForCausalLM"], "model_type": "qwen3",
+    "num_hidden_layers": 2, "hidden_size": 64, "num_attention_heads": 4, "num_key_value_heads": 2,
+    "head_dim": 16, "intermediate_size": 128, "vocab_size": 256, "rope_theta": 10000.0, "rms_norm_eps": 1e-6,
+    "max_position_embeddings": 512, "tie_word_embeddings": True, "hidden_act": "silu",
+}
+CONFIG_B = {
+    "architectures": ["Qwen3ForCausalLM"], "model_type": "qwen3",
+    "num_hidden_layers": 3, "hidden_size": 96, "num_attention_heads": 8, "num_key_value_heads": 2,
+    "head_dim": 32, "intermediate_size": 272, "vocab_size": 517, "rope_theta": 1000000.0, "rms_norm_eps": 1e-5,
+    "max_position_embeddings": 640, "tie_word_embeddings": False, "hidden_act": "silu",
+}
+PAGE_SIZE = {"A": 4, "B": 16}
+
+
+def random_tokens(n: int, vocab: int, seed: int) -> List[int]:
+    g = torch.Generator().manual_seed(seed)
+    return torch.randint(0, vocab, (n,), generator=g).tolist()
+
+
+def cut(n: int, sizes: Sequence[int]) -> List[int]:
+    """Cut n tokens into portions, cycling through ``sizes``; the last portion takes what is left."""
+    out, i = [], 0
+    while n > 0:
+        s = min(sizes[i % len(sizes)], n)
+        out.append(s)
+        n -= s
+        i += 1
+    return out
+
+
+def rel_err(a: torch.Tensor, b: torch.Tensor) -> float:
+    """Largest absolute difference over the largest absolute value of the reference ``b``."""
+    return float((a.double() - b.double()).abs().max() / b.double().abs().max().clamp_min(1e-30))
