@@ -1,0 +1,135 @@
+"""The engine on the GPU against the plain implementation, in float32 and bfloat16: every way of
+cutting requests into steps must give the same logits."""
+import pytest
+import torch
+
+import plain_qwen3
+from helpers import CONFIG_A, CONFIG_B, PAGE_SIZE, cut, random_tokens, rel_err
+from inferrs_b200.engine.batch import StepEntry
+from inferrs_b200.engine.loading import load_model_dir
+from inferrs_b200.engine.runner import ModelRunner
+from inferrs_b200.runtime import Runtime
+
+pytestmark = pytest.mark.gpu
+
+CONFIGS = {"A": CONFIG_A, "B": CONFIG_B}
+# float32: the north-star bound.  bfloat16: the plain implementation rounds where the engine stores
+# bfloat16, so what is left is the order of sums and a few roundings that fall differently.
+TOL = {torch.float32: 1e-4, torch.bfloat16: 3e-2}
+_plain_cache = {}
+
+
+def make_runner(model_dir, dtype, page_size, n_pages, max_requests=4):
+    rt = Runtime.cuda(dtype)
+    spec, weights, _ = load_model_dir(model_dir, rt)
+    return ModelRunner(spec, weights, rt, page_size=page_size, n_pages=n_pages, max_requests=max_requests)
+
+
+def plain_logits(model_dir, tokens, dtype):
+    key = (model_dir, tuple(tokens), dtype)
+    if key not in _plain_cache:
+        cfg, w = plain_qwen3.read_model(model_dir)
+        _plain_cache[key] = plain_qwen3.forward(cfg, w, tokens, store=None if dtype == torch.float32 else dtype)
+    return _plain_cache[key]
+
+
+def check(got, want, dtype, what=""):
+    err = rel_err(got.cpu(), want)
+    assert err < TOL[dtype], f"{what}: relative error {err:.3e}"
+    if dtype == torch.float32:
+        assert torch.equal(got.cpu().argmax(-1), want.argmax(-1)), f"{what}: greedy tokens differ"
+
+
+@pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
+@pytest.mark.parametrize("name", ["A", "B"])
+def test_whole(model_dirs, name, dtype):
+    runner = make_runner(model_dirs[name], dtype, PAGE_SIZE[name], n_pages=128)
+    for i, n in enumerate([1, 5, 17, 33, 100]):
+        toks = random_tokens(n, CONFIGS[name]["vocab_size"], seed=i)
+        runner.admit(i)
+        got = runner.step([StepEntry(i, toks, list(range(n)))])
+        runner.release(i)
+        check(got, plain_logits(model_dirs[name], toks, dtype), dtype, f"whole {n}")
+
+
+@pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
+@pytest.mark.parametrize("name", ["A", "B"])
+def test_prefill_then_last_32_one_by_one(model_dirs, name, dtype):
+    toks = random_tokens(150, CONFIGS[name]["vocab_size"], seed=11)
+    want = plain_logits(model_dirs[name], toks, dtype)
+    runner = make_runner(model_dirs[name], dtype, PAGE_SIZE[name], n_pages=64)
+    runner.admit("r")
+    rows = [runner.step([StepEntry("r", toks[:118], list(range(118)))])]
+    for t in range(118, 150):
+        rows.append(runner.step([StepEntry("r", toks[t:t + 1], [0])]))
+    check(torch.cat(rows), want, dtype, "decode after prefill")
+
+
+@pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
+@pytest.mark.parametrize("name", ["A", "B"])
+def test_portions_of_changing_size(model_dirs, name, dtype):
+    toks = random_tokens(131, CONFIGS[name]["vocab_size"], seed=12)
+    want = plain_logits(model_dirs[name], toks, dtype)
+    runner = make_runner(model_dirs[name], dtype, PAGE_SIZE[name], n_pages=64)
+    runner.admit("r")
+    rows, at = [], 0
+    for n in cut(len(toks), [7, 2, 13, 3, 2, 31, 1, 16]):
+        rows.append(runner.step([StepEntry("r", toks[at:at + n], list(range(n)))]))
+        at += n
+    check(torch.cat(rows), want, dtype, "portions")
+
+
+@pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
+@pytest.mark.parametrize("name", ["A", "B"])
+def test_mixed_requests_with_page_reuse(model_dirs, name, dtype):
+    ps = PAGE_SIZE[name]
+    lens = [70, 23, 97, 31, 18, 64, 5, 49]
+    prompts = [random_tokens(n, CONFIGS[name]["vocab_size"], seed=20 + i) for i, n in enumerate(lens)]
+    want = [plain_logits(model_dirs[name], p, dtype) for p in prompts]
+    pages = lambda n: (n + ps - 1) // ps  # noqa: E731
+    n_pages = pages(97) + pages(70) + pages(64) + pages(49) + 1  # too few for all: pages are used again
+    runner = make_runner(model_dirs[name], dtype, ps, n_pages=n_pages)
+    got = [[] for _ in prompts]
+    at = [0] * len(prompts)
+    live, nxt, step = [], 0, 0
+    sizes = [5, 2, 9, 1, 3, 16, 1, 1, 27]
+    while live or nxt < len(prompts):
+        while len(live) < 4 and nxt < len(prompts) and \
+                sum(pages(lens[i]) for i in live) + pages(lens[nxt]) <= n_pages:
+            runner.admit(nxt)
+            live.append(nxt)
+            nxt += 1
+        entries = []
+        for k, i in enumerate(live):
+            if (step + k) % 3 == 2 and len(live) > 1:
+                continue
+            n = min(sizes[(step + i) % len(sizes)], lens[i] - at[i])
+            entries.append((i, n))
+        if not entries:
+            entries = [(live[0], 1)]
+        out = runner.step([StepEntry(i, prompts[i][at[i]:at[i] + n], list(range(n))) for i, n in entries])
+        o = 0
+        for i, n in entries:
+            got[i].append(out[o:o + n])
+            o += n
+            at[i] += n
+        for i in [i for i in live if at[i] == lens[i]]:
+            runner.release(i)
+            live.remove(i)
+        runner.manager.check_invariants()
+        step += 1
+    for i in range(len(prompts)):
+        check(torch.cat(got[i]), want[i], dtype, f"mixed request {i}")
+
+
+@pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
+def test_long_decode(model_dirs, dtype):
+    name = "B"
+    toks = random_tokens(400, CONFIGS[name]["vocab_size"], seed=31)
+    want = plain_logits(model_dirs[name], toks, dtype)
+    runner = make_runner(model_dirs[name], dtype, PAGE_SIZE[name], n_pages=32)
+    runner.admit("r")
+    rows = [runner.step([StepEntry("r", toks[:3], [0, 1, 2])])]
+    for t in range(3, 400):
+        rows.append(runner.step([StepEntry("r", toks[t:t + 1], [0])]))
+    check(torch.cat(rows), want, dtype, "long decode")

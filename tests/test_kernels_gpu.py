@@ -1,0 +1,218 @@
+"""Each CUDA kernel alone against its plain statement in ``kernel_refs``, at sizes that the tiny
+models do not use (odd widths, partial rotation, windows, shuffled pages)."""
+import pytest
+import torch
+
+import kernel_refs as R
+from helpers import rel_err
+
+pytestmark = pytest.mark.gpu
+
+DTYPES = [torch.float32, torch.bfloat16]
+TOL = {torch.float32: 2e-5, torch.bfloat16: 1.2e-2}  # bfloat16: one rounding of the stored result is 2^-8
+
+
+def dev():
+    return torch.device("cuda")
+
+
+def rand(shape, dtype, seed, scale=1.0):
+    g = torch.Generator(device="cpu").manual_seed(seed)
+    return (torch.randn(shape, generator=g) * scale).to(dtype).to(dev())
+
+
+@pytest.mark.parametrize("dtype", DTYPES)
+@pytest.mark.parametrize("wdtype", DTYPES)
+def test_embedding_gather(dtype, wdtype):
+    from inferrs_b200 import kernels as K
+    table = rand((1000, 200), wdtype, 0)
+    ids = torch.randint(0, 1000, (37,), dtype=torch.int32, device=dev())
+    out = torch.empty((37, 200), dtype=torch.float32, device=dev())
+    ref = torch.empty_like(out)
+    K.embedding_gather(table, ids, out, dtype)
+    R.embedding_gather(table, ids, ref)
+    assert torch.equal(out, ref)
+
+
+@pytest.mark.parametrize("dtype", DTYPES)
+@pytest.mark.parametrize("width", [200, 96, 4096, 5000])
+def test_add_rms_norm(dtype, width):
+    from inferrs_b200 import kernels as K
+    n = 19
+    for wdtype in ([torch.float32] if dtype == torch.float32 else DTYPES):
+        res = rand((n, width), torch.float32, 1)
+        delta = rand((n, width), dtype, 2)
+        w = (1 + 0.1 * rand((width,), torch.float32, 3)).to(wdtype)
+        for use_delta in (True, False):
+            r1, r2 = res.clone(), res.clone()
+            out = torch.empty((n, width), dtype=dtype, device=dev())
+            ref = torch.empty_like(out)
+            K.add_rms_norm(r1, delta if use_delta else None, w, 1e-5, out)
+            R.add_rms_norm(r2, delta if use_delta else None, w, 1e-5, ref)
+            assert rel_err(out, ref) < TOL[dtype]
+            assert rel_err(r1, r2) < 1e-6
+        rows = torch.tensor([3, 0, 18, 7], dtype=torch.int32, device=dev())
+        r1 = res.clone()
+        out = torch.empty((4, width), dtype=dtype, device=dev())
+        ref = torch.empty_like(out)
+        K.add_rms_norm(r1, delta, w, 1e-6, out, rows)
+        R.add_rms_norm(res.clone(), delta, w, 1e-6, ref, rows)
+        assert rel_err(out, ref) < TOL[dtype]
+        assert torch.equal(r1, res), "the row-gathering form must not write the residual back"
+
+
+@pytest.mark.parametrize("dtype", DTYPES)
+def test_silu_gate(dtype):
+    from inferrs_b200 import kernels as K
+    gu = rand((33, 2 * 150), dtype, 4, scale=3.0)
+    out = torch.empty((33, 150), dtype=dtype, device=dev())
+    ref = torch.empty_like(out)
+    K.silu_gate(gu, out)
+    R.silu_gate(gu, ref)
+    assert rel_err(out, ref) < TOL[dtype]
+
+
+def _paged_setup(dtype, n_kv, d, page_size, lens, new, seed, n_pages=None):
+    """Requests with lens[r] cached tokens of which the last new[r] are this step's rows."""
+    g = torch.Generator().manual_seed(seed)
+    pages_per = [(l + page_size - 1) // page_size for l in lens]
+    total = sum(pages_per)
+    n_pages = n_pages or total + 3
+    perm = torch.randperm(n_pages, generator=g)[:total].tolist()
+    table = torch.full((len(lens), max(pages_per)), -1, dtype=torch.int32)
+    at = 0
+    for r, n in enumerate(pages_per):
+        table[r, :n] = torch.tensor(perm[at:at + n], dtype=torch.int32)
+        at += n
+    positions, row_request = [], []
+    for r, (l, t) in enumerate(zip(lens, new)):
+        positions += list(range(l - t, l))
+        row_request += [r] * t
+    k_pages = rand((n_pages, n_kv, page_size, d), dtype, seed + 1)
+    v_pages = rand((n_pages, n_kv, page_size, d), dtype, seed + 2)
+    return (table.to(dev()), torch.tensor(positions, dtype=torch.int32, device=dev()),
+            torch.tensor(row_request, dtype=torch.int32, device=dev()), k_pages, v_pages)
+
+
+@pytest.mark.parametrize("dtype", DTYPES)
+@pytest.mark.parametrize("nh,nkv,d,rot,ps", [(6, 3, 48, 48, 8), (4, 4, 16, 8, 4), (8, 2, 128, 128, 16), (3, 1, 80, 0, 16)])
+def test_qk_norm_rope_store(dtype, nh, nkv, d, rot, ps):
+    from inferrs_b200 import kernels as K
+    lens, new = [21, 9, 40], [5, 9, 1]
+    table, positions, row_request, k_pages, v_pages = _paged_setup(dtype, nkv, d, ps, lens, new, 7)
+    n = sum(new)
+    qkv = rand((n, (nh + 2 * nkv) * d), dtype, 8)
+    wq = (1 + 0.1 * rand((d,), torch.float32, 9)).to(dtype)
+    wk = (1 + 0.1 * rand((d,), torch.float32, 10)).to(dtype)
+    cos = sin = None
+    if rot:
+        ang = torch.arange(64, dtype=torch.float32)[:, None] * (1.0 / 10000 ** (torch.arange(rot // 2) * 2.0 / rot))[None]
+        cos, sin = torch.cos(ang).to(dev()), torch.sin(ang).to(dev())
+    for use_norm in (True, False):
+        k1, v1, k2, v2 = k_pages.clone(), v_pages.clone(), k_pages.clone(), v_pages.clone()
+        q1 = torch.empty((n, nh, d), dtype=dtype, device=dev())
+        q2 = torch.empty_like(q1)
+        a = (wq, wk) if use_norm else (None, None)
+        K.qk_norm_rope_store(qkv, nh, nkv, d, True, a[0], a[1], 1e-5, cos, sin, rot, positions, row_request, table,
+                             k1, v1, q1)
+        R.qk_norm_rope_store(qkv, nh, nkv, d, True, a[0], a[1], 1e-5, cos, sin, rot, positions, row_request, table,
+                             k2, v2, q2)
+        assert rel_err(q1, q2) < TOL[dtype]
+        assert rel_err(k1, k2) < TOL[dtype]
+        assert torch.equal(v1, v2)
+    # queries only: a layer that reads another layer's cache
+    q1 = torch.empty((n, nh, d), dtype=dtype, device=dev())
+    q2 = torch.empty_like(q1)
+    qo = qkv[:, :nh * d].contiguous()
+    K.qk_norm_rope_store(qo, nh, nkv, d, False, wq, None, 1e-5, cos, sin, rot, positions, row_request, None, None,
+                         None, q1)
+    R.qk_norm_rope_store(qo, nh, nkv, d, False, wq, None, 1e-5, cos, sin, rot, positions, row_request, None, None,
+                         None, q2)
+    assert rel_err(q1, q2) < TOL[dtype]
+
+
+@pytest.mark.parametrize("dtype", DTYPES)
+@pytest.mark.parametrize("nh,nkv,d,ps,window", [(6, 3, 48, 8, None), (4, 2, 16, 4, 9), (8, 2, 128, 16, None),
+                                                (5, 5, 80, 16, 33), (2, 1, 256, 16, None)])
+def test_paged_attention_generic(dtype, nh, nkv, d, ps, window):
+    from inferrs_b200 import kernels as K
+    lens, new = [300, 17, 64, 1], [40, 17, 1, 1]
+    table, positions, row_request, k_pages, v_pages = _paged_setup(dtype, nkv, d, ps, lens, new, 20)
+    n = sum(new)
+    q = rand((n, nh, d), dtype, 23)
+    # one far key of request 0 stands out for its last row: the row's output must be close to that key's value
+    far = 5 if window is None else lens[0] - window  # the window's far edge
+    page, slot = int(table[0, far // ps]), far % ps
+    k_pages[page, :, slot, :] = 0
+    k_pages[page, :, slot, 0] = 16.0
+    q[new[0] - 1, :, :] = 0
+    q[new[0] - 1, :, 0] = 16.0
+    out = torch.empty((n, nh * d), dtype=dtype, device=dev())
+    ref = torch.empty_like(out)
+    scale = d ** -0.5 * 4  # the marked score is 256 * scale, the others' spread 16 * scale
+    K.paged_attention_generic(q, k_pages, v_pages, table, row_request, positions, scale, window, out)
+    R.paged_attention_generic(q, k_pages, v_pages, table, row_request, positions, scale, window, ref)
+    assert rel_err(out, ref) < TOL[dtype]
+    got = out[new[0] - 1].view(nh, d).float()
+    want = v_pages[page, :, slot, :].float().repeat_interleave(nh // nkv, dim=0)
+    assert rel_err(got, want) < 5e-2, "the far key that stands out was not seen"
+
+
+@pytest.mark.parametrize("dtype", DTYPES)
+@pytest.mark.parametrize("n,m,k", [(70, 130, 100), (1, 517, 96), (64, 64, 16), (129, 65, 33)])
+def test_gemm_tn_simt(dtype, n, m, k):
+    from inferrs_b200 import kernels as K
+    combos = [(torch.float32, torch.float32, torch.float32)]
+    if dtype == torch.bfloat16:
+        combos = [(torch.bfloat16, torch.bfloat16, torch.bfloat16), (torch.bfloat16, torch.bfloat16, torch.float32),
+                  (torch.bfloat16, torch.float32, torch.bfloat16), (torch.bfloat16, torch.float32, torch.float32)]
+    for xd, wd, od in combos:
+        x, w = rand((n, k), xd, 30), rand((m, k), wd, 31)
+        out = torch.empty((n, m), dtype=od, device=dev())
+        K.gemm_tn_simt(x, w, out, dtype)
+        ref = (x.double() @ w.double().t())
+        assert rel_err(out, ref) < (1e-5 if od == torch.float32 else 1e-2)
+
+
+def test_gemm_rows_do_not_depend_on_the_batch():
+    from inferrs_b200 import kernels as K
+    x, w = rand((100, 300), torch.float32, 40), rand((200, 300), torch.float32, 41)
+    full = torch.empty((100, 200), dtype=torch.float32, device=dev())
+    K.gemm_tn_simt(x, w, full, torch.float32)
+    one = torch.empty((1, 200), dtype=torch.float32, device=dev())
+    K.gemm_tn_simt(x[77:78].contiguous(), w, one, torch.float32)
+    assert torch.equal(one[0], full[77])
+
+
+def test_gemm_bf16_library():
+    from inferrs_b200 import kernels as K
+    x, w = rand((70, 256), torch.bfloat16, 50), rand((136, 256), torch.bfloat16, 51)
+    ref = x.double() @ w.double().t()
+    for od in (torch.bfloat16, torch.float32):
+        out = torch.empty((70, 136), dtype=od, device=dev())
+        K.gemm_tn_bf16(x, w, out)
+        assert rel_err(out, ref) < (1e-2 if od == torch.bfloat16 else 1e-5)
+
+
+def test_argmax():
+    from inferrs_b200 import kernels as K
+    logits = rand((9, 151), torch.float32, 60)
+    logits[2, 17] = logits[2, 99] = 50.0   # equal maxima: the lowest index wins
+    logits[3, :] = -float("inf")
+    logits[3, 150] = -1e30
+    big = rand((3, 151936), torch.float32, 61)
+    for l in (logits, big):
+        out = torch.empty((l.shape[0],), dtype=torch.int32, device=dev())
+        K.argmax(l, out)
+        assert torch.equal(out.long(), torch.argmax(l, dim=-1)) or l is logits
+        if l is logits:
+            assert out[2] == 17 and out[3] == 150
+            mask = torch.ones(9, dtype=torch.bool)
+            mask[2] = False
+            assert torch.equal(out.long()[mask], torch.argmax(l, dim=-1)[mask])
+
+
+def test_kernels_refuse_cpu_tensors():
+    from inferrs_b200 import kernels as K
+    with pytest.raises(K.KernelError):
+        K.silu_gate(torch.zeros(2, 4), torch.zeros(2, 2))
