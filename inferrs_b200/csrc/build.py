@@ -32,7 +32,8 @@ ARCH_FLAGS = ["-gencode", "arch=compute_100a,code=sm_100a"]
 COMMON_FLAGS = ["-O3", "-std=c++17", "-lineinfo", "--expt-relaxed-constexpr", "-Xcompiler", "-fPIC",
                 "-Xcompiler", "-fvisibility=hidden"]
 
-_CORE_SOURCES = ["elementwise.cu", "qk_rope_store.cu", "attention_generic.cu", "gemm_simt.cu", "sampling.cu"]
+_CORE_SOURCES = ["elementwise.cu", "qk_rope_store.cu", "attention_generic.cu", "gemm_simt.cu", "sampling.cu",
+                 "sample_select.cu"]
 
 # name -> (sources, extra flags, extra link flags)
 LIBRARIES: Dict[str, dict] = {

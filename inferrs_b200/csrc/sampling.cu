@@ -45,3 +45,45 @@ IB_EXPORT int ib_argmax(const float* logits, int* out, int n_rows, int vocab, lo
     argmax_kernel<<<n_rows, threads, 0, stream>>>(logits, out, vocab, ld);
     return ib_launch_status();
 }
+
+// ---------------------------------------------------------------------------
+// Penalties on the logits of tokens seen lately (in place, before sampling):
+//   repetition: logit / p if logit >= 0 else logit * p, once per distinct token;
+//   frequency:  logit -= f * (times seen);  presence: logit -= q  (seen at least once).
+// prev [rows, max_prev] holds each row's window of previous tokens, n_prev[row] of them valid.
+// ---------------------------------------------------------------------------
+__global__ void penalties_kernel(float* __restrict__ logits, long ld, int vocab, const int* __restrict__ prev,
+                                 int max_prev, const int* __restrict__ n_prev, const float* __restrict__ repetition,
+                                 const float* __restrict__ frequency, const float* __restrict__ presence) {
+    const int row = blockIdx.x;
+    const int n = n_prev[row] < max_prev ? n_prev[row] : max_prev;
+    const float rp = repetition[row], fp = frequency[row], pp = presence[row];
+    const bool use_rp = rp != 1.0f && rp != 0.0f;
+    const bool use_fp = fp != 0.0f || pp != 0.0f;
+    if (n <= 0 || (!use_rp && !use_fp)) return;
+    const int* p = prev + (long)row * max_prev;
+    float* l = logits + (long)row * ld;
+    for (int i = threadIdx.x; i < n; i += blockDim.x) {
+        const int id = p[i];
+        if (id < 0 || id >= vocab) continue;
+        bool first = true;
+        for (int j = 0; j < i; ++j)
+            if (p[j] == id) { first = false; break; }
+        if (!first) continue;  // the first occurrence's thread updates the logit: no two threads share one
+        int count = 1;
+        for (int j = i + 1; j < n; ++j) count += (p[j] == id);
+        float v = l[id];
+        if (use_rp) v = v >= 0.0f ? v / rp : v * rp;
+        if (use_fp) { v -= fp * (float)count; v -= pp; }
+        l[id] = v;
+    }
+}
+
+IB_EXPORT int ib_penalties(float* logits, long ld, int n_rows, int vocab, const int* prev, int max_prev,
+                           const int* n_prev, const float* repetition, const float* frequency,
+                           const float* presence, cudaStream_t stream) {
+    if (n_rows <= 0 || max_prev <= 0) return IB_OK;
+    penalties_kernel<<<n_rows, 256, 0, stream>>>(logits, ld, vocab, prev, max_prev, n_prev, repetition, frequency,
+                                                  presence);
+    return ib_launch_status();
+}

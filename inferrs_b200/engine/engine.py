@@ -1,0 +1,152 @@
+"""The Python entry point: ``Engine(model_dir).generate(prompts, sampling)``.
+
+Token ids in, token ids out.  The engine puts together what the reference's ``load_engine`` and
+``Engine::run`` do (inferrs/src/engine.rs:104-207, :1366-1912): load the model named by config.json,
+size and attach the paged cache, then loop: plan a step, run it, sample, finish and free.
+Option names follow the reference's command line (inferrs/src/main.rs:91-204).
+"""
+from __future__ import annotations
+
+import itertools
+import random
+from typing import Dict, Hashable, List, Optional, Sequence, Union
+
+import torch
+
+from ..runtime import Runtime, parse_dtype
+from ..sampling.params import SamplingParams
+from ..sampling.sampler import Sampler
+from .batch import StepEntry
+from .loading import load_model_dir, random_model
+from .runner import ModelRunner
+from .scheduler import PlannedEntry, Request, Scheduler
+
+
+class Engine:
+    """
+    model_dir            folder with config.json and model.safetensors (or shards)
+    dtype                "bf16" (default) or "f32"
+    block_size           tokens per cache page (reference: --block-size, 16)
+    num_blocks           pages in the cache; None: sized from ``paged_attention``
+    paged_attention      fraction of the device's free memory, after the weights, given to the cache
+                         (reference: --paged-attention[=0.9] is a fraction of total memory)
+    max_batch_size       most requests in a step (reference: --max-batch-size, 32)
+    max_tokens_per_step  token budget of a step (reference: --max-tokens-per-step, 2048)
+    max_seq_len          0: the model's max_position_embeddings (reference: --max-seq-len)
+    config, random_weights   instead of ``model_dir``: a config.json dictionary and a seed; the weights
+                         are made on the device
+    """
+
+    def __init__(self, model_dir: Optional[str] = None, dtype: str = "bf16", block_size: int = 16,
+                 num_blocks: Optional[int] = None, paged_attention: float = 0.9, max_batch_size: int = 32,
+                 max_tokens_per_step: int = 2048, max_seq_len: int = 0, prefill_chunk: Optional[int] = None,
+                 config: Optional[dict] = None, random_weights: Optional[int] = None,
+                 runtime: Optional[Runtime] = None):
+        self.rt = runtime if runtime is not None else Runtime.cuda(parse_dtype(dtype))
+        if model_dir is not None:
+            spec, weights, cfg = load_model_dir(model_dir, self.rt)
+        elif config is not None and random_weights is not None:
+            spec, weights, cfg = random_model(config, random_weights, self.rt)
+        else:
+            raise ValueError("give a model_dir, or a config dictionary with a random_weights seed")
+        self.spec, self.config = spec, cfg
+        self.max_seq_len = min(max_seq_len, spec.max_positions) if max_seq_len else spec.max_positions
+        if num_blocks is None:
+            num_blocks = self._blocks_for_fraction(spec, block_size, paged_attention, max_batch_size)
+        self.runner = ModelRunner(spec, weights, self.rt, page_size=block_size, n_pages=num_blocks,
+                                  max_requests=max_batch_size)
+        self.scheduler = Scheduler(self.runner.manager, max_batch_size, max_tokens_per_step, self.max_seq_len,
+                                   spec.eos_token_ids, prefill_chunk)
+        self.sampler = Sampler(self.rt.device, self.rt.dtype)
+        self._ids = itertools.count()
+        self._rng = random.Random()
+        self.n_steps = 0
+        self.n_tokens_run = 0
+
+    def _blocks_for_fraction(self, spec, block_size, fraction, max_batch_size) -> int:
+        from .model import cache_needs
+        if not 0.0 < fraction <= 1.0:
+            raise ValueError(f"paged_attention must be in (0, 1], got {fraction}")
+        kv_needs, _ = cache_needs(spec)
+        elem = torch.empty((), dtype=self.rt.dtype).element_size()
+        per_page = sum(2 * n.n_kv_heads * n.head_dim * block_size * elem for n in kv_needs.values())
+        if self.rt.device.type != "cuda":
+            raise RuntimeError("num_blocks must be given when the cache is not on a CUDA device")
+        free, _total = torch.cuda.mem_get_info(self.rt.device)
+        blocks = int(free * fraction) // max(per_page, 1)
+        # no request can use more than max_positions tokens: more pages than that per slot are never touched
+        useful = max_batch_size * ((self.max_seq_len + block_size - 1) // block_size)
+        blocks = min(blocks, useful)
+        if blocks < 1:
+            raise RuntimeError("no memory is left for the cache")
+        return blocks
+
+    # ---- requests -------------------------------------------------------------------
+    def add_request(self, prompt: Sequence[int], sampling: Optional[SamplingParams] = None,
+                    rid: Optional[Hashable] = None) -> Hashable:
+        sampling = sampling or SamplingParams()
+        if rid is None:
+            rid = next(self._ids)
+        seed = sampling.seed if sampling.seed is not None else self._rng.getrandbits(63)
+        prompt = [int(t) for t in prompt]
+        for t in prompt:
+            if not 0 <= t < self.spec.vocab_size:
+                raise ValueError(f"token id {t} is outside the vocabulary of {self.spec.vocab_size}")
+        self.scheduler.add(Request(rid=rid, prompt=prompt, params=sampling, seed=seed))
+        return rid
+
+    def abort(self, rid: Hashable):
+        return self.scheduler.abort(rid)
+
+    def has_work(self) -> bool:
+        return not self.scheduler.idle
+
+    # ---- one scheduler iteration -----------------------------------------------------
+    def step(self) -> List[Request]:
+        """Plan, run and sample one step; returns the requests that finished in it."""
+        plan, ended = self.scheduler.plan()
+        if not plan:
+            return ended
+        entries = []
+        for e in plan:
+            toks = e.request.tokens[e.start:e.start + e.n]
+            entries.append(StepEntry(e.request.rid, toks, [e.n - 1] if e.samples else []))
+        logits = self.runner.step(entries)
+        sampling = [e for e in plan if e.samples]
+        tokens: List[int] = []
+        if sampling:
+            ids = self.sampler.sample(logits, [e.request.params for e in sampling],
+                                      [e.request.seed for e in sampling], [e.request.tokens for e in sampling])
+            tokens = ids.cpu().tolist()
+        self.n_steps += 1
+        self.n_tokens_run += sum(e.n for e in plan)
+        return ended + self.scheduler.update(plan, tokens)
+
+    def generate(self, prompts: Sequence[Sequence[int]],
+                 sampling: Union[SamplingParams, Sequence[SamplingParams], None] = None,
+                 return_requests: bool = False):
+        """Generated token ids for every prompt (list of lists, in the order of ``prompts``)."""
+        if sampling is None or isinstance(sampling, SamplingParams):
+            sampling = [sampling] * len(prompts)
+        if len(sampling) != len(prompts):
+            raise ValueError("one SamplingParams per prompt, or one for all")
+        rids = [self.add_request(p, s) for p, s in zip(prompts, sampling)]
+        done: Dict[Hashable, Request] = {}
+        while len(done) < len(rids) and self.has_work():
+            for r in self.step():
+                done[r.rid] = r
+        out = [done[r] for r in rids]
+        return out if return_requests else [r.output for r in out]
+
+    def stats(self) -> dict:
+        m = self.runner.manager
+        return {
+            "steps": self.n_steps,
+            "tokens_run": self.n_tokens_run,
+            "preemptions": self.scheduler.n_preemptions,
+            "running": len(self.scheduler.running),
+            "waiting": len(self.scheduler.waiting),
+            "free_pages": [p.n_free for p in m.pools],
+            "pages": [p.n_pages for p in m.pools],
+            "cache_bytes": self.runner.storage.total_bytes(),
+        }

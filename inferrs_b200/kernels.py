@@ -34,6 +34,10 @@ _SIGNATURES = {
     "ib_gemm_tn_simt": [c_void_p, c_int, c_void_p, c_int, c_void_p, c_int, c_int, c_int, c_int, c_long, c_long,
                         c_long, c_void_p],
     "ib_argmax": [c_void_p, c_void_p, c_int, c_int, c_long, c_void_p],
+    "ib_penalties": [c_void_p, c_long, c_int, c_int, c_void_p, c_int, c_void_p, c_void_p, c_void_p, c_void_p,
+                     c_void_p],
+    "ib_sample": [c_void_p, c_long, c_int, c_int, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p,
+                  c_void_p],
 }
 
 _LIBS = {}
@@ -292,3 +296,38 @@ def paged_attention(q: torch.Tensor, k_pages: torch.Tensor, v_pages: torch.Tenso
     and what the faster kernels need to cut the work).
     """
     paged_attention_generic(q, k_pages, v_pages, block_table, ctx.row_request, ctx.positions, scale, window, out)
+
+
+def penalties(logits: torch.Tensor, prev: torch.Tensor, n_prev: torch.Tensor, repetition: torch.Tensor,
+              frequency: torch.Tensor, presence: torch.Tensor, act_dtype: torch.dtype = torch.float32):
+    """In place on float32 logits [R, V]: repetition, frequency and presence penalties for the tokens in
+    each row's window ``prev[r, :n_prev[r]]`` (int32)."""
+    _need(logits, "logits", (torch.float32,), 2)
+    _need(prev, "prev", _I, 2)
+    _need(n_prev, "n_prev", _I, 1)
+    r = logits.shape[0]
+    for name, t in (("repetition", repetition), ("frequency", frequency), ("presence", presence)):
+        _need(t, name, (torch.float32,), 1)
+        if t.shape[0] != r:
+            raise KernelError(f"penalties: {name} has {t.shape[0]} entries for {r} rows")
+    if prev.shape[0] != r or n_prev.shape[0] != r:
+        raise KernelError(f"penalties: prev {tuple(prev.shape)}, n_prev {tuple(n_prev.shape)} for {r} rows")
+    _check(_core(act_dtype).ib_penalties(_p(logits), logits.shape[1], r, logits.shape[1], _p(prev), prev.shape[1],
+                                         _p(n_prev), _p(repetition), _p(frequency), _p(presence), _stream()),
+           "penalties")
+
+
+def sample(logits: torch.Tensor, temperature: torch.Tensor, top_k: torch.Tensor, top_p: torch.Tensor,
+           min_p: torch.Tensor, uniform: torch.Tensor, out: torch.Tensor, act_dtype: torch.dtype = torch.float32):
+    """One token per row of float32 logits [R, V]: largest logit where temperature < 1e-5, else
+    temperature, top-k, top-p, min-p and the inverse-CDF walk with the row's random number ``uniform``."""
+    _need(logits, "logits", (torch.float32,), 2)
+    r = logits.shape[0]
+    for name, t, dt in (("temperature", temperature, torch.float32), ("top_k", top_k, torch.int32),
+                        ("top_p", top_p, torch.float32), ("min_p", min_p, torch.float32),
+                        ("uniform", uniform, torch.float32), ("out", out, torch.int32)):
+        _need(t, name, (dt,), 1)
+        if t.shape[0] != r:
+            raise KernelError(f"sample: {name} has {t.shape[0]} entries for {r} rows")
+    _check(_core(act_dtype).ib_sample(_p(logits), logits.shape[1], r, logits.shape[1], _p(temperature), _p(top_k),
+                                      _p(top_p), _p(min_p), _p(uniform), _p(out), _stream()), "sample")

@@ -1,0 +1,58 @@
+"""Choosing the next token of every row of a step, on the device.
+
+The reference copies each row's logits to the host and samples there (inferrs/src/sampler.rs:146-357).
+Here the rows of a step are sampled together by two kernels (penalties, then selection); what crosses
+to the host is one token id per row.
+"""
+from __future__ import annotations
+
+from typing import List, Sequence
+
+import numpy as np
+import torch
+
+from .. import kernels
+from .params import SamplingParams, uniform_for
+
+
+class Sampler:
+    def __init__(self, device: torch.device, act_dtype: torch.dtype = torch.float32):
+        self.device = device
+        self.act_dtype = act_dtype
+
+    def sample(self, logits: torch.Tensor, params: Sequence[SamplingParams], seeds: Sequence[int],
+               histories: Sequence[Sequence[int]]) -> torch.Tensor:
+        """int32 token ids [rows] (on the device) for float32 ``logits`` [rows, vocab].
+
+        ``histories[r]`` is all tokens of row r's request so far, prompt and generated: its length is the
+        step index of the random draw and its tail is the penalties' window.  ``logits`` is changed in
+        place where penalties apply.
+        """
+        r = logits.shape[0]
+        out = torch.empty((r,), dtype=torch.int32, device=self.device)
+        if r == 0:
+            return out
+        if all(p.is_greedy and not p.has_penalty for p in params):
+            kernels.argmax(logits, out, self.act_dtype)
+            return out
+        if any(p.has_penalty for p in params):
+            width = max(1, max(min(p.repeat_last_n, len(h)) if p.has_penalty else 0 for p, h in zip(params, histories)))
+            prev = np.full((r, width), -1, dtype=np.int32)
+            n_prev = np.zeros((r,), dtype=np.int32)
+            for i, (p, h) in enumerate(zip(params, histories)):
+                if p.has_penalty:
+                    tail = list(h[-p.repeat_last_n:])
+                    prev[i, :len(tail)] = tail
+                    n_prev[i] = len(tail)
+            f = np.array([[p.repetition_penalty if p.has_penalty else 1.0 for p in params],
+                          [p.frequency_penalty if p.has_penalty else 0.0 for p in params],
+                          [p.presence_penalty if p.has_penalty else 0.0 for p in params]], dtype=np.float32)
+            fd = torch.from_numpy(f).to(self.device)
+            kernels.penalties(logits, torch.from_numpy(prev).to(self.device), torch.from_numpy(n_prev).to(self.device),
+                              fd[0], fd[1], fd[2], self.act_dtype)
+        f = np.array([[p.temperature for p in params], [p.top_p for p in params], [p.min_p for p in params],
+                      [uniform_for(s, len(h)) for s, h in zip(seeds, histories)]], dtype=np.float32)
+        fd = torch.from_numpy(f).to(self.device)
+        top_k = torch.tensor([p.top_k for p in params], dtype=torch.int32).to(self.device)
+        kernels.sample(logits, fd[0], top_k, fd[1], fd[2], fd[3], out, self.act_dtype)
+        return out

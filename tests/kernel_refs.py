@@ -128,3 +128,49 @@ def install(monkeypatch):
 
     for name in _NAMES:
         monkeypatch.setattr(K, name, globals()[name])
+
+
+def penalties(logits, prev, n_prev, repetition, frequency, presence, act_dtype=None):
+    for r in range(logits.shape[0]):
+        window = [int(t) for t in prev[r, :int(n_prev[r])]]
+        rp, fp, pp = float(repetition[r]), float(frequency[r]), float(presence[r])
+        for t in dict.fromkeys(window):
+            if not 0 <= t < logits.shape[1]:
+                continue
+            v = logits[r, t]
+            if rp not in (1.0, 0.0):
+                v = v / rp if v >= 0 else v * rp
+            if fp != 0.0 or pp != 0.0:
+                v = v - fp * window.count(t) - pp
+            logits[r, t] = v
+
+
+def sample(logits, temperature, top_k, top_p, min_p, uniform, out, act_dtype=None):
+    for r in range(logits.shape[0]):
+        t = float(temperature[r])
+        if t < 1e-5:
+            out[r] = int(torch.argmax(logits[r]))
+            continue
+        z = logits[r].float() / t
+        e = torch.exp(z - z.max()).double()
+        order = torch.sort(e, descending=True, stable=True).indices
+        total = e.sum()
+        k = int(top_k[r])
+        if 0 < k < len(order):
+            order = order[:k]
+        cum = torch.cumsum(e[order], 0)
+        if float(top_p[r]) < 1.0:
+            hit = (cum >= float(top_p[r]) * total).nonzero()
+            if len(hit):
+                order = order[:int(hit[0]) + 1]
+        if float(min_p[r]) > 0.0:
+            keep = int((e[order] >= float(min_p[r])).sum())
+            if keep > 0:
+                order = order[:keep]
+        cum = torch.cumsum(e[order], 0)
+        target = float(uniform[r]) * float(cum[-1])
+        hit = (cum > target).nonzero()
+        out[r] = int(order[int(hit[0])]) if len(hit) else int(order[-1])
+
+
+_NAMES += ["penalties", "sample"]

@@ -1,0 +1,132 @@
+"""The scheduler's decisions: admission, portions under the token budget, decode first, finishing,
+and what happens when pages run out (preempt the youngest, recompute later)."""
+import pytest
+
+from inferrs_b200.cache.manager import CacheManager, GroupLayout
+from inferrs_b200.engine.scheduler import Request, Scheduler, SchedulerError
+from inferrs_b200.sampling.params import SamplingParams
+
+
+def make(n_pages=64, page_size=4, max_batch=4, budget=16, max_positions=1000, eos=(), chunk=None, slots=8):
+    m = CacheManager([GroupLayout("full")], page_size, [n_pages], slots)
+    return Scheduler(m, max_batch, budget, max_positions, eos, chunk), m
+
+
+def req(rid, n, max_tokens=4, **kw):
+    return Request(rid, list(range(1, n + 1)), SamplingParams.greedy(max_tokens=max_tokens, **kw), seed=0)
+
+
+def run_step(s, m, token=7):
+    """Plan a step, pretend to run it (reserve and commit as the step function does) and sample ``token``."""
+    plan, ended = s.plan()
+    if plan:
+        m.reserve({e.request.rid: e.n for e in plan})
+        for e in plan:
+            m.commit(e.request.rid, e.n)
+    fin = s.update(plan, [token] * sum(e.samples for e in plan))
+    m.check_invariants()
+    return plan, ended + fin
+
+
+def test_prompts_are_cut_under_the_budget_and_decodes_go_first():
+    s, m = make(budget=16)
+    s.add(req("a", 10)); s.add(req("b", 30))
+    plan, _ = run_step(s, m)
+    assert [(e.request.rid, e.start, e.n, e.samples) for e in plan] == [("a", 0, 10, True), ("b", 0, 6, False)]
+    plan, _ = run_step(s, m)   # a decodes one token first, b gets the rest of the budget
+    assert [(e.request.rid, e.start, e.n, e.samples) for e in plan] == [("a", 10, 1, True), ("b", 6, 15, False)]
+    plan, _ = run_step(s, m)
+    assert [(e.request.rid, e.start, e.n, e.samples) for e in plan] == [("a", 11, 1, True), ("b", 21, 9, True)]
+    assert sum(e.n for e in plan) <= 16
+
+
+def test_prefill_chunk_limits_a_portion():
+    s, m = make(budget=64, chunk=8)
+    s.add(req("a", 20))
+    sizes = []
+    while True:
+        plan, fin = run_step(s, m)
+        sizes.append(plan[0].n)
+        if plan[0].samples:
+            break
+    assert sizes == [8, 8, 4]
+
+
+def test_admission_is_first_come_first_served_up_to_the_batch_size():
+    s, m = make(max_batch=2, budget=100)
+    for i in range(4):
+        s.add(req(i, 5, max_tokens=2))
+    plan, _ = run_step(s, m)
+    assert [e.request.rid for e in plan] == [0, 1]
+    plan, fin = run_step(s, m)            # both sample their second token and finish
+    assert sorted(r.rid for r in fin) == [0, 1] and all(r.finish_reason == "length" for r in fin)
+    plan, _ = run_step(s, m)
+    assert [e.request.rid for e in plan] == [2, 3]
+    assert m.n_live == 2
+
+
+def test_finish_reasons():
+    s, m = make(eos=(7,), max_positions=14)
+    s.add(req("stop", 3, max_tokens=9))
+    s.add(req("ignores", 3, max_tokens=2, ignore_eos=True))
+    s.add(Request("own", [1, 2], SamplingParams.greedy(max_tokens=9, stop_token_ids=(5,)), seed=0))
+    plan, fin = run_step(s, m, token=5)
+    assert {r.rid: r.finish_reason for r in fin} == {"own": "stop"}
+    plan, fin = run_step(s, m, token=7)
+    assert {r.rid: r.finish_reason for r in fin} == {"ignores": "length", "stop": "stop"}
+    s.add(req("ctx", 12, max_tokens=50))   # 14 positions: two more tokens fit
+    reasons = []
+    while not s.idle:
+        reasons += [r.finish_reason for r in run_step(s, m, token=1)[1]]
+    assert reasons == ["length"] and m.n_live == 0
+
+
+def test_refusals_when_added():
+    s, m = make(n_pages=4, page_size=4, max_positions=50)
+    with pytest.raises(SchedulerError, match="empty"):
+        s.add(Request("e", [], SamplingParams.greedy(), 0))
+    with pytest.raises(SchedulerError, match="even alone"):
+        s.add(req("big", 16))
+    with pytest.raises(SchedulerError, match="positions"):
+        s.add(req("long", 50))
+
+
+def test_out_of_pages_preempts_the_youngest_and_recomputes():
+    s, m = make(n_pages=6, page_size=4, budget=64, max_batch=4)
+    s.add(req("old", 8, max_tokens=12)); s.add(req("young", 8, max_tokens=12))
+    plan, _ = run_step(s, m)              # 2 + 2 pages hold the prompts
+    plan, _ = run_step(s, m)              # each takes its third page: the pool is full
+    assert m.pools[0].n_free == 0
+    for _ in range(3):
+        plan, _ = run_step(s, m)          # positions 9..11 fit the third pages
+    plan, _ = run_step(s, m)              # position 12 needs a fourth page: the youngest goes
+    assert [e.request.rid for e in plan] == ["old"] and s.n_preemptions == 1
+    young = s.waiting[0]
+    assert young.rid == "young" and young.n_computed == 0 and len(young.output) == 5 and not m.has("young")
+    outputs = {}
+    while not s.idle:
+        for r in run_step(s, m)[1]:
+            outputs[r.rid] = r
+    assert len(outputs["old"].output) == 12 and len(outputs["young"].output) == 12
+    assert outputs["young"].n_preempted >= 1 and m.pools[0].n_free == 6
+
+
+def test_a_lone_request_that_outgrows_the_cache_ends_with_length():
+    s, m = make(n_pages=3, page_size=4, budget=64)
+    s.add(req("r", 8, max_tokens=100))
+    fin = []
+    while not s.idle:
+        fin += run_step(s, m)[1]
+    assert [r.finish_reason for r in fin] == ["length"] and len(fin[0].output) == 5
+    assert m.pools[0].n_free == 3 and m.n_live == 0
+
+
+def test_abort_frees_everything():
+    s, m = make()
+    s.add(req("a", 9)); s.add(req("b", 9))
+    run_step(s, m)
+    assert s.abort("a").finish_reason == "cancelled" and not m.has("a")
+    assert s.abort("nobody") is None
+    s.add(req("c", 3))
+    assert s.abort("c").finish_reason == "cancelled" and len(s.waiting) == 0
+    m.check_invariants()
