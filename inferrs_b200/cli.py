@@ -1,0 +1,156 @@
+"""Command line in the manner of the reference's ``inferrs run`` and ``inferrs bench``.
+
+Option names, meanings and defaults are the reference's where it has them
+(inferrs/src/main.rs:91-204 shared options, inferrs/src/run.rs:34-146 ``run``,
+inferrs/src/bench.rs:21-38 ``bench``).  The model is a local folder (the reference's
+``load_local_model`` contract, inferrs/src/hub.rs:28-85).  Prompts are token ids: text needs a
+``tokenizer.json`` in the model folder and the ``tokenizers`` library.
+
+    python -m inferrs_b200 run MODEL_DIR --prompt-ids 1,2,3 --max-tokens 32 --temperature 0
+    python -m inferrs_b200 bench MODEL_DIR --prompt-len 128 --max-tokens 128
+"""
+from __future__ import annotations
+
+import argparse
+import json
+import os
+import statistics
+import sys
+import time
+from typing import List, Optional
+
+
+def _shared(ap: argparse.ArgumentParser):
+    ap.add_argument("model", help="folder with config.json and model.safetensors (or *.safetensors shards)")
+    ap.add_argument("--dtype", default="bf16", help="weight and activation type: bf16 or f32 (default bf16)")
+    ap.add_argument("--max-seq-len", type=int, default=0, help="maximum sequence length (0 = model default)")
+    ap.add_argument("--block-size", type=int, default=16, help="KV cache block size in tokens")
+    ap.add_argument("--max-blocks", type=int, default=0,
+                    help="KV cache blocks (0 = sized by --paged-attention)")
+    ap.add_argument("--max-batch-size", type=int, default=32, help="maximum concurrent sequences")
+    ap.add_argument("--max-tokens-per-step", type=int, default=2048, help="token budget per scheduler step")
+    ap.add_argument("--paged-attention", type=float, default=0.9, metavar="FRACTION",
+                    help="fraction of free device memory reserved for paged KV blocks")
+    ap.add_argument("--temperature", type=float, default=0.7, help="sampling temperature")
+    ap.add_argument("--top-p", type=float, default=0.9, help="nucleus sampling threshold")
+    ap.add_argument("--top-k", type=int, default=50, help="top-k sampling (0 = off)")
+    ap.add_argument("--max-tokens", type=int, default=2048, help="max tokens to generate")
+    ap.add_argument("--seed", type=int, default=None, help="seed for reproducible sampling")
+
+
+def _engine(args):
+    from .engine.engine import Engine
+    return Engine(args.model, dtype=args.dtype, block_size=args.block_size,
+                  num_blocks=args.max_blocks or None, paged_attention=args.paged_attention,
+                  max_batch_size=args.max_batch_size, max_tokens_per_step=args.max_tokens_per_step,
+                  max_seq_len=args.max_seq_len)
+
+
+def _tokenizer(model_dir: str):
+    path = os.path.join(model_dir, "tokenizer.json")
+    if not os.path.isfile(path):
+        return None
+    try:
+        from tokenizers import Tokenizer
+    except ImportError:
+        return None
+    return Tokenizer.from_file(path)
+
+
+def cmd_run(args) -> int:
+    from .sampling.params import SamplingParams
+    tok = _tokenizer(args.model)
+    if args.prompt_ids:
+        ids = [int(t) for t in args.prompt_ids.replace(",", " ").split()]
+    elif args.prompt is not None:
+        if tok is None:
+            print("run: a text prompt needs tokenizer.json in the model folder and the tokenizers library; "
+                  "use --prompt-ids", file=sys.stderr)
+            return 2
+        text = args.prompt if args.system is None else args.system + "\n" + args.prompt
+        ids = tok.encode(text).ids
+    else:
+        print("run: give a prompt or --prompt-ids", file=sys.stderr)
+        return 2
+    eng = _engine(args)
+    sp = SamplingParams(temperature=args.temperature, top_p=args.top_p, top_k=args.top_k,
+                        repetition_penalty=args.repetition_penalty, repeat_last_n=args.repeat_last_n,
+                        frequency_penalty=args.frequency_penalty, max_tokens=args.max_tokens, seed=args.seed)
+    t0 = time.perf_counter()
+    req = eng.generate([ids], sp, return_requests=True)[0]
+    dt = time.perf_counter() - t0
+    if tok is not None and not args.prompt_ids:
+        print(tok.decode(req.output))
+    else:
+        print(" ".join(str(t) for t in req.output))
+    print(f"[{len(ids)} prompt tokens, {len(req.output)} generated, finish={req.finish_reason}, {dt:.2f} s]",
+          file=sys.stderr)
+    return 0
+
+
+def cmd_bench(args) -> int:
+    """Prefill and decode rates for one sequence, as ``inferrs bench`` measures them
+    (inferrs/src/bench.rs:53-221, inferrs/src/engine.rs:2557-2641): a synthetic prompt of
+    ``--prompt-len`` equal tokens, stop tokens bypassed, ``--warmup`` + ``--runs`` runs."""
+    import torch
+    from .sampling.params import SamplingParams
+    eng = _engine(args)
+    prompt = [1 % eng.spec.vocab_size] * args.prompt_len
+    sp = SamplingParams(temperature=args.temperature, top_p=args.top_p, top_k=args.top_k,
+                        max_tokens=args.max_tokens, seed=args.seed if args.seed is not None else 0, ignore_eos=True)
+    prefill, decode, ttft, e2e = [], [], [], []
+    for run in range(args.warmup + args.runs):
+        eng.add_request(prompt, sp)
+        req = eng.scheduler.waiting[-1]
+        torch.cuda.synchronize()
+        t0 = time.perf_counter()
+        done, first = None, None
+        while done is None:
+            fin = eng.step()
+            torch.cuda.synchronize()
+            if first is None and req.output:
+                first = time.perf_counter()
+            done = fin[0] if fin else None
+        t1 = time.perf_counter()
+        if run >= args.warmup:
+            n_out = len(done.output)
+            prefill.append(args.prompt_len / (first - t0))
+            decode.append(max(n_out - 1, 1) / max(t1 - first, 1e-9))
+            ttft.append((first - t0) * 1e3)
+            e2e.append((t1 - t0) * 1e3)
+    mean = statistics.mean
+    sd = lambda v: statistics.stdev(v) if len(v) > 1 else 0.0  # noqa: E731
+    q = lambda v, p: sorted(v)[min(len(v) - 1, int(p * len(v)))]  # noqa: E731
+    out = {"prompt_len": args.prompt_len, "max_tokens": args.max_tokens, "runs": args.runs,
+           "prefill_tok_s": mean(prefill), "prefill_tok_s_sd": sd(prefill),
+           "decode_tok_s": mean(decode), "decode_tok_s_sd": sd(decode),
+           "ttft_ms": mean(ttft), "e2e_ms_p50": q(e2e, 0.5), "e2e_ms_p90": q(e2e, 0.9)}
+    print(json.dumps(out))
+    return 0
+
+
+def main(argv: Optional[List[str]] = None) -> int:
+    ap = argparse.ArgumentParser(prog="inferrs_b200", description=__doc__,
+                                 formatter_class=argparse.RawDescriptionHelpFormatter)
+    sub = ap.add_subparsers(dest="command", required=True)
+    run = sub.add_parser("run", help="generate from one prompt and exit")
+    _shared(run)
+    run.add_argument("prompt", nargs="?", default=None, help="text prompt (needs tokenizer.json)")
+    run.add_argument("--prompt-ids", default=None, help="prompt as token ids, separated by commas or spaces")
+    run.add_argument("--system", default=None, help="system prompt, put before the prompt")
+    run.add_argument("--repetition-penalty", type=float, default=1.1, help="llama.cpp-style; 1.0 = disabled")
+    run.add_argument("--repeat-last-n", type=int, default=64, help="window of the penalties; 0 = disabled")
+    run.add_argument("--frequency-penalty", type=float, default=0.0, help="OpenAI-style; 0.0 = disabled")
+    run.set_defaults(fn=cmd_run)
+    bench = sub.add_parser("bench", help="benchmark prefill and decode of one sequence")
+    _shared(bench)
+    bench.add_argument("--warmup", type=int, default=1, help="warm-up runs (discarded)")
+    bench.add_argument("--runs", type=int, default=5, help="timed runs")
+    bench.add_argument("--prompt-len", type=int, default=128, help="synthetic prompt tokens")
+    bench.set_defaults(fn=cmd_bench)
+    args = ap.parse_args(argv)
+    return args.fn(args)
+
+
+if __name__ == "__main__":
+    sys.exit(main())

@@ -64,18 +64,36 @@ class StepContext:
     def decode_only(self) -> bool:
         return self.max_q_len == 1
 
+    def attention_tiles(self, tokens_per_tile: int):
+        """(tile_req, tile_row0, n_tiles): the step's rows cut into tiles of at most ``tokens_per_tile``
+        tokens of one request each.  Made once per step and tile size, on first use."""
+        key = ("attention_tiles", tokens_per_tile)
+        if key not in self.extra:
+            req, row0, at = [], [], 0
+            for r, n in enumerate(self.q_lens):
+                for s in range(0, n, tokens_per_tile):
+                    req.append(r)
+                    row0.append(at + s)
+                at += n
+            both = torch.from_numpy(np.asarray([req, row0], dtype=np.int32)).to(self.token_ids.device)
+            self.extra[key] = (both[0], both[1], len(req))
+        return self.extra[key]
+
 
 class BatchError(ValueError):
     pass
 
 
 def build_context(entries: Sequence[StepEntry], manager: CacheManager, storage: CacheStorage, vocab_size: int,
-                  max_positions: int, device: torch.device, fixed_pages: Optional[Sequence[int]] = None
-                  ) -> StepContext:
+                  max_positions: int, device: torch.device, fixed_pages: Optional[Sequence[int]] = None,
+                  pad_to: Optional[int] = None, into: Optional[torch.Tensor] = None) -> StepContext:
     """Check the entries and lay their rows out.  Pages must already be reserved in ``manager``.
 
-    ``fixed_pages[g]`` pads group g's block table to that many columns (for replayed launches
-    whose shapes must not change); otherwise each table is as wide as its longest row.
+    ``fixed_pages[g]`` pads group g's block table to that many columns, ``pad_to`` pads a step of
+    single tokens to that many requests, and ``into`` is a device buffer that receives the data:
+    together they give a step whose shapes and addresses do not change, which a replayed CUDA
+    graph needs.  A padding request has one token at position 0 and no pages: it writes nothing
+    to the cache and its output is not used.
     """
     if not entries:
         raise BatchError("a step needs at least one entry")
@@ -110,7 +128,23 @@ def build_context(entries: Sequence[StepEntry], manager: CacheManager, storage: 
         q_lens.append(len(toks))
         kv_lens.append(held + len(toks))
         slots.append(manager.slot(e.rid))
-    n, nreq = len(ids), len(entries)
+    n_real = len(entries)
+    if pad_to is not None:
+        if any(q != 1 for q in q_lens) or len(entries) > pad_to:
+            raise BatchError("only steps of single tokens, no more than pad_to of them, can be padded")
+        for r in range(len(entries), pad_to):
+            ids.append(0)
+            positions.append(0)
+            row_request.append(r)
+            q_start.append(q_start[-1] + 1)
+            q_lens.append(1)
+            kv_lens.append(1)
+            slots.append(0)
+        wanted = list(logit_rows)
+        logit_rows = list(range(pad_to))  # fixed shape: every row's logits are made, the caller picks
+    else:
+        wanted = None
+    n, nreq = len(ids), len(q_lens)
     tables = []
     for g in range(len(manager.groups)):
         rows = [manager.block_table(e.rid, g) for e in entries]
@@ -120,7 +154,7 @@ def build_context(entries: Sequence[StepEntry], manager: CacheManager, storage: 
                 raise BatchError(f"group {g}: a block table of {width} pages exceeds the fixed {fixed_pages[g]}")
             width = fixed_pages[g]
         arr = np.full((nreq, width), -1, dtype=np.int32)
-        for r, t in enumerate(rows):
+        for r, t in enumerate(rows):  # padding requests keep -1 everywhere
             arr[r, :len(t)] = t
         tables.append(arr)
     # one host buffer, one copy
@@ -137,11 +171,17 @@ def build_context(entries: Sequence[StepEntry], manager: CacheManager, storage: 
     host = np.zeros(max(total, 4), dtype=np.int32)
     for p, o in zip(parts, offsets):
         host[o:o + p.size] = p
-    dev = torch.from_numpy(host).to(device)
+    if into is not None:
+        if into.numel() < host.size:
+            raise BatchError(f"the fixed step buffer holds {into.numel()} numbers, {host.size} are needed")
+        dev = into
+        dev[:host.size].copy_(torch.from_numpy(host))
+    else:
+        dev = torch.from_numpy(host).to(device)
     views = [dev[o:o + s] for o, s in zip(offsets, sizes)]
     return StepContext(
         token_ids=views[0], positions=views[1], row_request=views[2], q_start=views[3], kv_len=views[4],
         slots=views[5], logit_rows=views[6],
         block_tables=[views[7 + g].view(nreq, tables[g].shape[1]) for g in range(len(tables))],
         storage=storage, n_rows=n, n_requests=nreq, q_lens=q_lens, kv_lens=kv_lens, slot_list=slots,
-        max_q_len=max(q_lens), max_kv_len=max(kv_lens))
+        max_q_len=max(q_lens), max_kv_len=max(kv_lens), extra={"n_real": n_real, "wanted": wanted})

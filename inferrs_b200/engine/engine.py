@@ -54,7 +54,7 @@ class Engine:
         if num_blocks is None:
             num_blocks = self._blocks_for_fraction(spec, block_size, paged_attention, max_batch_size)
         self.runner = ModelRunner(spec, weights, self.rt, page_size=block_size, n_pages=num_blocks,
-                                  max_requests=max_batch_size)
+                                  max_requests=max_batch_size, max_context=self.max_seq_len)
         self.scheduler = Scheduler(self.runner.manager, max_batch_size, max_tokens_per_step, self.max_seq_len,
                                    spec.eos_token_ids, prefill_chunk)
         self.sampler = Sampler(self.rt.device, self.rt.dtype)
@@ -111,7 +111,7 @@ class Engine:
         for e in plan:
             toks = e.request.tokens[e.start:e.start + e.n]
             entries.append(StepEntry(e.request.rid, toks, [e.n - 1] if e.samples else []))
-        logits = self.runner.step(entries)
+        logits = self.runner.step(entries, own_output=False)
         sampling = [e for e in plan if e.samples]
         tokens: List[int] = []
         if sampling:

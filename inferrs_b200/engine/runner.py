@@ -26,7 +26,8 @@ from .model import Model, cache_needs
 
 class ModelRunner:
     def __init__(self, spec: ModelSpec, weights: Dict[str, torch.Tensor], rt: Runtime, page_size: int,
-                 n_pages: int, max_requests: int):
+                 n_pages: int, max_requests: int, use_graphs: Optional[bool] = None,
+                 max_context: Optional[int] = None):
         self.spec = spec
         self.rt = rt
         self.model = Model(spec, weights, rt)
@@ -35,6 +36,17 @@ class ModelRunner:
         self.manager = CacheManager(self.storage.layouts, page_size, self.storage.n_pages, max_requests)
         self.page_size = page_size
         self.steps_run = 0
+        # decode steps are replayed as CUDA graphs when every part says its launches do not depend on
+        # host-side values of the step (``graph_safe``)
+        parts = [p for b in self.model.blocks for p in (b.mixer, b.ffn, b.mixer_norm, b.ffn_norm)]
+        safe = all(getattr(p, "graph_safe", False) for p in parts)
+        if use_graphs is None:
+            use_graphs = rt.device.type == "cuda"
+        self.graphs = None
+        if use_graphs and safe and rt.device.type == "cuda":
+            from .graphs import DecodeGraphs
+            limit = min(max_context or spec.max_positions, spec.max_positions, n_pages * page_size)
+            self.graphs = DecodeGraphs(self, limit)
 
     # ---- requests -----------------------------------------------------------
     def admit(self, rid: Hashable) -> int:
@@ -69,9 +81,23 @@ class ModelRunner:
             self.manager.commit(e.rid, len(e.tokens))
         self.steps_run += 1
 
-    def step(self, entries: Sequence[StepEntry]) -> torch.Tensor:
-        """float32 logits [number of wanted places, vocab], in the order of entries and of ``want``."""
-        ctx = self.prepare(entries)
-        logits = self.model.forward(ctx)
+    def step(self, entries: Sequence[StepEntry], own_output: bool = True) -> torch.Tensor:
+        """float32 logits [number of wanted places, vocab], in the order of entries and of ``want``.
+
+        ``own_output=False`` may return a view of a buffer that the next step overwrites (a replayed
+        graph writes to fixed memory); the caller must be done with it before it steps again.
+        """
+        if self.graphs is not None and all(len(e.tokens) == 1 for e in entries) \
+                and all(self.manager.n_tokens(e.rid) < self.graphs.max_context for e in entries):
+            wants = {e.rid: 1 for e in entries}
+            if len(wants) != len(entries):
+                raise ValueError("a request appears twice in one step")
+            self.manager.reserve(wants)
+            logits = self.graphs.run(entries)
+            if own_output:
+                logits = logits.clone()
+        else:
+            ctx = self.prepare(entries)
+            logits = self.model.forward(ctx)
         self.commit(entries)
         return logits

@@ -33,6 +33,9 @@ _SIGNATURES = {
                                    c_int, c_int, c_int, c_int, c_float, c_int, c_void_p, c_void_p],
     "ib_gemm_tn_simt": [c_void_p, c_int, c_void_p, c_int, c_void_p, c_int, c_int, c_int, c_int, c_long, c_long,
                         c_long, c_void_p],
+    "ib_paged_attention_mma": [c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_void_p, c_void_p, c_int,
+                               c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_float, c_int, c_void_p, c_int, c_int,
+                               c_void_p, c_void_p, c_void_p],
     "ib_argmax": [c_void_p, c_void_p, c_int, c_int, c_long, c_void_p],
     "ib_penalties": [c_void_p, c_long, c_int, c_int, c_void_p, c_int, c_void_p, c_void_p, c_void_p, c_void_p,
                      c_void_p],
@@ -66,8 +69,24 @@ def _stream() -> int:
     return torch.cuda.current_stream().cuda_stream
 
 
+_LAUNCHES = 0
+
+
+def launch_count() -> int:
+    """Kernel launches of this package's own libraries so far (library matrix products are not counted)."""
+    return _LAUNCHES
+
+
+def count_launches(n: int):
+    """Add the kernels of a replayed CUDA graph to the count."""
+    global _LAUNCHES
+    _LAUNCHES += n
+
+
 def _check(code: int, what: str):
+    global _LAUNCHES
     if code == 0:
+        _LAUNCHES += 1
         return
     if code == -1:
         raise KernelError(f"{what}: these sizes are not supported by the kernel")
@@ -288,6 +307,58 @@ def linear(x: torch.Tensor, w: torch.Tensor, out: torch.Tensor, act_dtype: torch
         gemm_tn_bf16(x, w, out)
 
 
+MMA_KEYS = 64          # keys per tile of the tensor-core attention kernel
+MMA_TARGET_CTAS = 444  # CTAs that fill the machine: 148 SMs x 3 resident
+
+
+def mma_attention_supported(dtype: torch.dtype, n_heads: int, n_kv_heads: int, head_dim: int, page_size: int) -> bool:
+    return (dtype == torch.bfloat16 and head_dim in (64, 128, 256) and MMA_KEYS % page_size == 0
+            and n_heads % n_kv_heads == 0 and n_heads // n_kv_heads <= 16)
+
+
+def decode_splits(n_requests: int, n_kv_heads: int, max_kv_len: int) -> int:
+    """How many ways the decode form cuts each request's keys, so that the grid fills the machine."""
+    tiles = max(1, (max_kv_len + MMA_KEYS - 1) // MMA_KEYS)
+    want = (MMA_TARGET_CTAS + n_requests * n_kv_heads - 1) // (n_requests * n_kv_heads)
+    return max(1, min(want, tiles))
+
+
+def paged_attention_mma(q: torch.Tensor, k_pages: torch.Tensor, v_pages: torch.Tensor, block_table: torch.Tensor,
+                        tile_req: torch.Tensor, tile_row0: torch.Tensor, n_tiles: int, q_start: torch.Tensor,
+                        positions: torch.Tensor, scale: float, window: Optional[int], out: torch.Tensor,
+                        decode_form: bool, n_splits: int = 1):
+    """Tensor-core attention over the pages (bfloat16).  Prefill form: tile i holds up to 64/G tokens of request
+    tile_req[i] from row tile_row0[i].  Decode form: every tile is one token; its keys are cut ``n_splits`` ways
+    and merged through float32 scratch."""
+    bf = (torch.bfloat16,)
+    _need(q, "q", bf, 3)
+    _need(k_pages, "k_pages", bf, 4)
+    _need(v_pages, "v_pages", bf, 4)
+    _need(out, "out", bf, 2)
+    for name, t in (("block_table", block_table),):
+        _need(t, name, _I, 2)
+    for name, t in (("tile_req", tile_req), ("tile_row0", tile_row0), ("q_start", q_start), ("positions", positions)):
+        _need(t, name, _I, 1)
+    n, nh, d = q.shape
+    n_pages, nkv, page_size, dk = k_pages.shape
+    if dk != d or v_pages.shape != k_pages.shape or out.shape != (n, nh * d):
+        raise KernelError(f"paged_attention_mma: q {tuple(q.shape)}, pages {tuple(k_pages.shape)}, out {tuple(out.shape)}")
+    if not mma_attention_supported(q.dtype, nh, nkv, d, page_size):
+        raise KernelError(f"paged_attention_mma takes head_dim 64/128/256, a page size that divides {MMA_KEYS} and at "
+                          f"most 16 query heads per key/value head; got head_dim {d}, page size {page_size}, "
+                          f"{nh}/{nkv} heads")
+    if tile_req.shape[0] < n_tiles or tile_row0.shape[0] < n_tiles:
+        raise KernelError("paged_attention_mma: tile arrays are shorter than n_tiles")
+    part_o = part_ml = None
+    if decode_form and n_splits > 1:
+        part_o = torch.empty((n, nh, n_splits, d), dtype=torch.float32, device=q.device)
+        part_ml = torch.empty((n, nh, n_splits, 2), dtype=torch.float32, device=q.device)
+    _check(_core(torch.bfloat16).ib_paged_attention_mma(
+        _p(q), _p(k_pages), _p(v_pages), _p(block_table), block_table.shape[1], page_size, n_pages, _p(tile_req),
+        _p(tile_row0), n_tiles, _p(q_start), _p(positions), n, nh, nkv, d, float(scale), int(window) if window else 0,
+        _p(out), int(decode_form), int(n_splits), _p(part_o), _p(part_ml), _stream()), "paged_attention_mma")
+
+
 def paged_attention(q: torch.Tensor, k_pages: torch.Tensor, v_pages: torch.Tensor, block_table: torch.Tensor,
                     ctx, scale: float, window: Optional[int], out: torch.Tensor):
     """Attention of every row of the step over its request's pages; picks the kernel for the sizes.
@@ -295,7 +366,20 @@ def paged_attention(q: torch.Tensor, k_pages: torch.Tensor, v_pages: torch.Tenso
     ``ctx`` is the step's :class:`~inferrs_b200.engine.batch.StepContext` (row_request, positions
     and what the faster kernels need to cut the work).
     """
-    paged_attention_generic(q, k_pages, v_pages, block_table, ctx.row_request, ctx.positions, scale, window, out)
+    n, nh, d = q.shape
+    nkv, page_size = k_pages.shape[1], k_pages.shape[2]
+    if not mma_attention_supported(q.dtype, nh, nkv, d, page_size):
+        paged_attention_generic(q, k_pages, v_pages, block_table, ctx.row_request, ctx.positions, scale, window, out)
+        return
+    if ctx.decode_only:
+        # one row per request: the rows are the tiles
+        splits = decode_splits(ctx.n_requests, nkv, ctx.max_kv_len)
+        paged_attention_mma(q, k_pages, v_pages, block_table, ctx.row_request, ctx.q_start, ctx.n_requests,
+                            ctx.q_start, ctx.positions, scale, window, out, True, splits)
+    else:
+        tile_req, tile_row0, n_tiles = ctx.attention_tiles(MMA_KEYS // (nh // nkv))
+        paged_attention_mma(q, k_pages, v_pages, block_table, tile_req, tile_row0, n_tiles, ctx.q_start,
+                            ctx.positions, scale, window, out, False)
 
 
 def penalties(logits: torch.Tensor, prev: torch.Tensor, n_prev: torch.Tensor, repetition: torch.Tensor,

@@ -27,6 +27,8 @@ from .spec import AttentionSpec, TensorDecl
 
 
 class Attention:
+    graph_safe = True  # launches depend only on shapes, never on the step's host-side values
+
     @staticmethod
     def declare(spec: AttentionSpec) -> List[TensorDecl]:
         d = [TensorDecl(spec.q_proj, (spec.n_heads * spec.head_dim, spec.width)),

@@ -15,6 +15,8 @@ class RMSNorm:
     """x / sqrt(mean(x^2) + eps) * w, in float32 (inferrs-kernels/candle-kernels/src/reduce.cu:188-228),
     fused with the residual addition that precedes it in a block."""
 
+    graph_safe = True  # launches depend only on shapes, never on the step's host-side values
+
     @staticmethod
     def declare(spec: NormSpec) -> List[TensorDecl]:
         return [TensorDecl(spec.weight, (spec.size,), init="norm")]

@@ -17,6 +17,8 @@ class GatedDense:
     (inferrs-models/src/models/attention_utils.rs:94-118; inferrs-kernels/candle-kernels/src/unary.cu:58-61).
     Gate and up weights are stacked at load, so one product feeds the gate kernel."""
 
+    graph_safe = True  # launches depend only on shapes, never on the step's host-side values
+
     @staticmethod
     def declare(spec: GatedDenseSpec) -> List[TensorDecl]:
         return [TensorDecl(spec.gate_proj, (spec.inner, spec.width)),

@@ -59,6 +59,7 @@ def write_random_model(model_dir: str, config: dict, seed: int, dtype: torch.dty
     by default it is left out exactly when config.json says
     ``tie_word_embeddings: true``.
     """
+    from .. import models  # noqa: F401  (registers the architectures)
     from ..engine.model import declared_tensors  # late: engine imports weights
 
     raw = RawConfig(config, source="<random model>")

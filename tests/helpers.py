@@ -19,7 +19,14 @@ CONFIG_B = {
     "head_dim": 32, "intermediate_size": 272, "vocab_size": 517, "rope_theta": 1000000.0, "rms_norm_eps": 1e-5,
     "max_position_embeddings": 640, "tie_word_embeddings": False, "hidden_act": "silu",
 }
-PAGE_SIZE = {"A": 4, "B": 16}
+# A third shape whose head size the tensor-core attention kernels take (A and B run the generic kernel).
+CONFIG_C = {
+    "architectures": ["Qwen3ForCausalLM"], "model_type": "qwen3",
+    "num_hidden_layers": 2, "hidden_size": 160, "num_attention_heads": 6, "num_key_value_heads": 2,
+    "head_dim": 64, "intermediate_size": 208, "vocab_size": 301, "rope_theta": 50000.0, "rms_norm_eps": 1e-6,
+    "max_position_embeddings": 768, "tie_word_embeddings": True, "hidden_act": "silu",
+}
+PAGE_SIZE = {"A": 4, "B": 16, "C": 16}
 
 
 def random_tokens(n: int, vocab: int, seed: int) -> List[int]:

@@ -25,8 +25,13 @@ def rand_f32(seed, step):
 
 
 def sample_token(logits, previous, temperature=0.7, top_p=0.9, top_k=50, repetition_penalty=1.1, repeat_last_n=64,
-                 frequency_penalty=0.0, presence_penalty=0.0, min_p=0.0, seed=0):
-    """sampler.rs:146-357; ``previous`` is every token of the request so far."""
+                 frequency_penalty=0.0, presence_penalty=0.0, min_p=0.0, seed=0, precise=False):
+    """sampler.rs:146-357; ``previous`` is every token of the request so far.
+
+    The reference sums and walks in float32.  Over a list of many thousands of entries (no top-k, top-p = 1)
+    its running subtraction ``u -= p`` drifts by about 1e-4 and may stop a few entries off the exact place;
+    ``precise=True`` does the same steps on the same float32 probabilities with float64 sums, which is what a
+    sampler without that drift gives."""
     l = np.asarray(logits, dtype=np.float32).copy()
     vocab = l.shape[0]
     window = [] if repeat_last_n == 0 else list(previous[-repeat_last_n:])
@@ -50,26 +55,29 @@ def sample_token(logits, previous, temperature=0.7, top_p=0.9, top_k=50, repetit
     l = l / temp
     e = np.exp(l - l.max())                                        # :246-253
     probs = (e / e.sum(dtype=np.float32)).astype(np.float32)
+    acc = np.float64 if precise else np.float32
+    if precise:
+        probs = e.astype(np.float64) / e.astype(np.float64).sum()
     order = np.argsort(-probs, kind="stable")                      # :256-257
     if 0 < top_k < len(order):                                     # :260-262
         order = order[:top_k]
     if top_p < 1.0:                                                # :265-276
-        cum, cutoff = np.float32(0), len(order)
+        cum, cutoff = acc(0), len(order)
         for i, t in enumerate(order):
             cum += probs[t]
-            if cum >= np.float32(top_p):
+            if cum >= acc(np.float32(top_p)):
                 cutoff = i + 1
                 break
         order = order[:cutoff]
     if min_p > 0.0 and len(order):                                 # :281-287
-        thr = probs[order[0]] * np.float32(min_p)
+        thr = probs[order[0]] * acc(np.float32(min_p))
         keep = sum(1 for t in order if probs[t] >= thr)
         if keep > 0:
             order = order[:keep]
-    total = np.float32(sum(probs[t] for t in order))               # :290
+    total = acc(sum(probs[t] for t in order))                      # :290
     if total <= 0:
         return int(order[0]) if len(order) else 0
-    u = rand_f32(seed, len(previous))                              # :328-338
+    u = acc(rand_f32(seed, len(previous)))                         # :328-338
     chosen = order[-1]
     for t in order:
         norm = probs[t] / total

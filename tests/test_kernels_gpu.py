@@ -216,3 +216,73 @@ def test_kernels_refuse_cpu_tensors():
     from inferrs_b200 import kernels as K
     with pytest.raises(K.KernelError):
         K.silu_gate(torch.zeros(2, 4), torch.zeros(2, 2))
+
+
+def _tiles(new, tokens_per_tile):
+    req, row0, at = [], [], 0
+    for r, n in enumerate(new):
+        for s in range(0, n, tokens_per_tile):
+            req.append(r)
+            row0.append(at + s)
+        at += n
+    return (torch.tensor(req, dtype=torch.int32, device=dev()), torch.tensor(row0, dtype=torch.int32, device=dev()),
+            len(req))
+
+
+@pytest.mark.parametrize("nh,nkv,d,ps,window", [(8, 2, 128, 16, None), (4, 4, 64, 4, None), (6, 2, 128, 16, 70),
+                                                (16, 2, 64, 64, None), (5, 1, 256, 8, None), (32, 8, 128, 16, 33)])
+def test_paged_attention_mma_prefill_form(nh, nkv, d, ps, window):
+    from inferrs_b200 import kernels as K
+    dtype = torch.bfloat16
+    lens, new = [300, 17, 200, 64, 1], [40, 17, 200, 1, 1]
+    table, positions, row_request, k_pages, v_pages = _paged_setup(dtype, nkv, d, ps, lens, new, 20)
+    n = sum(new)
+    q = rand((n, nh, d), dtype, 23)
+    q_start = torch.tensor([0] + list(torch.tensor(new).cumsum(0)), dtype=torch.int32, device=dev())
+    far = 5 if window is None else lens[0] - window
+    page, slot = int(table[0, far // ps]), far % ps
+    k_pages[page, :, slot, :] = 0
+    k_pages[page, :, slot, 0] = 16.0
+    q[new[0] - 1, :, :] = 0
+    q[new[0] - 1, :, 0] = 16.0
+    out = torch.full((n, nh * d), float("nan"), dtype=dtype, device=dev())
+    ref = torch.empty_like(out)
+    scale = d ** -0.5 * 4
+    tile_req, tile_row0, n_tiles = _tiles(new, 64 // (nh // nkv))
+    K.paged_attention_mma(q, k_pages, v_pages, table, tile_req, tile_row0, n_tiles, q_start, positions, scale, window,
+                          out, False)
+    R.paged_attention_generic(q, k_pages, v_pages, table, row_request, positions, scale, window, ref)
+    assert rel_err(out, ref) < 2e-2
+    got = out[new[0] - 1].view(nh, d).float()
+    want = v_pages[page, :, slot, :].float().repeat_interleave(nh // nkv, dim=0)
+    assert rel_err(got, want) < 5e-2, "the far key that stands out was not seen"
+
+
+@pytest.mark.parametrize("nh,nkv,d,ps,window,splits", [(8, 2, 128, 16, None, 1), (32, 8, 128, 16, None, 7),
+                                                        (4, 4, 64, 4, 50, 3), (16, 1, 256, 32, None, 40),
+                                                        (6, 2, 128, 16, 129, 2)])
+def test_paged_attention_mma_decode_form(nh, nkv, d, ps, window, splits):
+    from inferrs_b200 import kernels as K
+    dtype = torch.bfloat16
+    lens = [300, 17, 64, 1, 65, 1000]
+    new = [1] * len(lens)
+    table, positions, row_request, k_pages, v_pages = _paged_setup(dtype, nkv, d, ps, lens, new, 30)
+    n = len(lens)
+    q = rand((n, nh, d), dtype, 33)
+    q_start = torch.arange(n + 1, dtype=torch.int32, device=dev())
+    far = 5 if window is None else lens[5] - window
+    page, slot = int(table[5, far // ps]), far % ps
+    k_pages[page, :, slot, :] = 0
+    k_pages[page, :, slot, 0] = 16.0
+    q[5, :, :] = 0
+    q[5, :, 0] = 16.0
+    out = torch.full((n, nh * d), float("nan"), dtype=dtype, device=dev())
+    ref = torch.empty_like(out)
+    scale = d ** -0.5 * 4
+    K.paged_attention_mma(q, k_pages, v_pages, table, row_request, q_start, n, q_start, positions, scale, window, out,
+                          True, splits)
+    R.paged_attention_generic(q, k_pages, v_pages, table, row_request, positions, scale, window, ref)
+    assert rel_err(out, ref) < 2e-2
+    got = out[5].view(nh, d).float()
+    want = v_pages[page, :, slot, :].float().repeat_interleave(nh // nkv, dim=0)
+    assert rel_err(got, want) < 5e-2, "the far key that stands out was not seen"

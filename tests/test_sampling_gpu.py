@@ -1,0 +1,120 @@
+"""The sampling kernels against the plain host sampler (written from the reference's), and generation
+through the Python entry point against a plain loop."""
+import numpy as np
+import pytest
+import torch
+
+import plain_qwen3
+import plain_sampler
+from helpers import CONFIG_A, CONFIG_B, PAGE_SIZE, random_tokens
+from inferrs_b200.sampling.params import SamplingParams
+
+pytestmark = pytest.mark.gpu
+
+
+def _logits(rows, vocab, seed, spread=3.0):
+    g = torch.Generator().manual_seed(seed)
+    return torch.randn((rows, vocab), generator=g) * spread
+
+
+@pytest.mark.parametrize("vocab", [517, 5000, 151936])
+@pytest.mark.parametrize("opts", [
+    dict(temperature=0.8, top_k=0, top_p=1.0, min_p=0.0),
+    dict(temperature=0.7, top_k=50, top_p=0.9, min_p=0.0),
+    dict(temperature=1.3, top_k=0, top_p=0.6, min_p=0.0),
+    dict(temperature=1.0, top_k=7, top_p=1.0, min_p=0.2),
+    dict(temperature=0.0, top_k=50, top_p=0.9, min_p=0.0),
+])
+def test_sample_kernel_matches_plain_sampler(vocab, opts):
+    from inferrs_b200.sampling.sampler import Sampler
+    rows = 12
+    logits = _logits(rows, vocab, seed=vocab % 97)
+    logits[3, 10] = logits[3, 200] = logits[3].max() + 1.0     # equal probabilities: lowest id first
+    hist = [list(range(5 + r)) for r in range(rows)]
+    sp = SamplingParams(repetition_penalty=1.0, max_tokens=4, seed=None, **opts)
+    seeds = [100 + r for r in range(rows)]
+    got = Sampler(torch.device("cuda")).sample(logits.cuda(), [sp] * rows, seeds, hist).cpu().tolist()
+    # a walk over the whole vocabulary is compared with the plain sampler's exact sums: see its docstring
+    precise = opts["top_k"] == 0 and opts["top_p"] == 1.0 and vocab > 1000
+    want = [plain_sampler.sample_token(logits[r].numpy(), hist[r], repetition_penalty=1.0, seed=seeds[r],
+                                       precise=precise, **opts) for r in range(rows)]
+    assert got == want
+
+
+def test_penalties_and_mixed_rows():
+    from inferrs_b200.sampling.sampler import Sampler
+    vocab, rows = 2000, 6
+    logits = _logits(rows, vocab, seed=5)
+    hist = [random_tokens(30 + 7 * r, vocab, seed=r) + [3, 3, 3] for r in range(rows)]
+    params = [SamplingParams(temperature=0.9, top_k=40, top_p=0.95, repetition_penalty=1.3, repeat_last_n=16,
+                             frequency_penalty=0.5, presence_penalty=0.25, max_tokens=1),
+              SamplingParams.greedy(),
+              SamplingParams(temperature=0.0, repetition_penalty=5.0, repeat_last_n=64, max_tokens=1),
+              SamplingParams(temperature=1.1, top_k=0, top_p=1.0, repetition_penalty=1.0, max_tokens=1),
+              SamplingParams(temperature=0.5, repeat_last_n=0, max_tokens=1),
+              SamplingParams(temperature=0.7, max_tokens=1)]
+    logits[2, 3] = logits[2].max() + 1.0     # the greedy row's favourite was seen: the penalty must move it
+    seeds = list(range(rows))
+    got = Sampler(torch.device("cuda")).sample(logits.cuda(), params, seeds, hist).cpu().tolist()
+    want = []
+    for r, p in enumerate(params):
+        want.append(plain_sampler.sample_token(
+            logits[r].numpy(), hist[r], temperature=p.temperature, top_p=p.top_p, top_k=p.top_k,
+            repetition_penalty=p.repetition_penalty, repeat_last_n=p.repeat_last_n,
+            frequency_penalty=p.frequency_penalty, presence_penalty=p.presence_penalty, min_p=p.min_p, seed=seeds[r]))
+    assert got == want
+    assert got[2] != 3
+
+
+def test_sampling_follows_the_distribution():
+    from inferrs_b200 import kernels as K
+    probs = torch.tensor([0.5, 0.25, 0.125, 0.0625, 0.0625])
+    n = 4000
+    logits = probs.log().repeat(n, 1).cuda().contiguous()
+    u = torch.rand(n, generator=torch.Generator().manual_seed(0)).cuda()
+    one, zero = torch.ones(n, device="cuda"), torch.zeros(n, device="cuda")
+    out = torch.empty(n, dtype=torch.int32, device="cuda")
+    K.sample(logits, one, torch.zeros(n, dtype=torch.int32, device="cuda"), one, zero, u, out)
+    freq = torch.bincount(out.long().cpu(), minlength=5).float() / n
+    assert float((freq - probs).abs().max()) < 0.03
+
+
+def _plain_generate(model_dir, prompt, n, **sampling):
+    cfg, w = plain_qwen3.read_model(model_dir)
+    toks = list(prompt)
+    for _ in range(n):
+        logits = plain_qwen3.forward(cfg, w, toks)[-1]
+        toks.append(plain_sampler.sample_token(logits.numpy(), toks, **sampling))
+    return toks[len(prompt):]
+
+
+@pytest.mark.parametrize("name", ["A", "B"])
+def test_greedy_generation_through_the_entry_point(model_dirs, name):
+    from inferrs_b200 import Engine
+    cfg = CONFIG_A if name == "A" else CONFIG_B
+    prompts = [random_tokens(n, cfg["vocab_size"], seed=70 + n) for n in (5, 17, 33)]
+    eng = Engine(model_dirs[name], dtype="f32", block_size=PAGE_SIZE[name], num_blocks=64, max_batch_size=4,
+                 max_tokens_per_step=24)
+    got = eng.generate(prompts, SamplingParams.greedy(max_tokens=16))
+    for p, g in zip(prompts, got):
+        assert g == _plain_generate(model_dirs[name], p, 16, temperature=0.0, repetition_penalty=1.0)
+    bf = Engine(model_dirs[name], dtype="bf16", block_size=PAGE_SIZE[name], num_blocks=64, max_batch_size=4)
+    out = bf.generate(prompts, SamplingParams.greedy(max_tokens=16))
+    assert all(len(o) == 16 for o in out)
+    assert bf.stats()["free_pages"] == bf.stats()["pages"]
+
+
+def test_sampled_generation_in_portions_with_preemption(model_dirs):
+    """Configuration B: prompts of 1/9/40/100 tokens in portions of 7 beside decoding, temperature 0.8, seed 4,
+    with so few pages that the youngest request is preempted and recomputed."""
+    from inferrs_b200 import Engine
+    name, cfg = "B", CONFIG_B
+    prompts = [random_tokens(n, cfg["vocab_size"], seed=80 + n) for n in (1, 9, 40, 100)]
+    opts = dict(temperature=0.8, top_k=0, top_p=1.0, repetition_penalty=1.0)
+    sp = SamplingParams(max_tokens=24, seed=4, **opts)
+    eng = Engine(model_dirs[name], dtype="f32", block_size=16, num_blocks=13, max_batch_size=4,
+                 max_tokens_per_step=12, prefill_chunk=7)
+    got = eng.generate(prompts, sp)
+    assert eng.stats()["preemptions"] > 0
+    for p, g in zip(prompts, got):
+        assert g == _plain_generate(model_dirs[name], p, 24, seed=4, **opts)
