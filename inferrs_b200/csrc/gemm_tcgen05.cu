@@ -1,0 +1,348 @@
+// y[t, f] = sum_k x[t, k] * w[f, k]  on the fifth-generation tensor cores (bfloat16 in, float32 accumulate).
+//
+// The weight matrix is the 128-row operand of tcgen05.mma and the tokens are its N dimension
+// (16..256 per tile), so a decode step with a handful of tokens still issues full-height MMAs and the
+// kernel's work is streaming W through shared memory: TMA brings 128x64 tiles of W and BNx64 tiles of x
+// into a ring of 128-byte-swizzled stages, one thread issues the MMAs, the accumulator (128 lanes x BN
+// columns of float32) lives in tensor memory, and four warps read it back with tcgen05.ld and store
+// y.  Roles: warp 0 = TMA producer, warp 1 = MMA issuer and owner of the tensor-memory allocation,
+// warps 2..5 = epilogue (one quarter of the 128 lanes each).
+//
+// With few output tiles the K range is cut over a thread-block cluster (1,1,split): every CTA of the
+// cluster accumulates its part of K, the parts are summed through distributed shared memory by the
+// cluster's first CTA, so no global scratch and no atomics are needed.
+//
+// Every wait on an mbarrier is bounded (about two seconds); a wait that runs out records a code in the
+// library's error word, the CTA lets outstanding copies land, frees its tensor memory and returns.
+#include <cuda.h>
+
+#include "common.cuh"
+
+#if IB_ACT_BF16
+
+namespace tc {
+
+constexpr int BM = 128;       // rows of W per tile (MMA M)
+constexpr int BK = 64;        // K per stage: 64 bf16 = one 128-byte swizzle row
+constexpr int UMMA_K = 16;
+constexpr int THREADS = 192;
+constexpr int A_BYTES = BM * BK * 2;
+
+__device__ int g_error = 0;   // 0 ok; else (role code) of the first wait that ran out
+
+__device__ __forceinline__ unsigned smem_u32(const void* p) { return (unsigned)__cvta_generic_to_shared(p); }
+
+__device__ __forceinline__ void mbar_init(unsigned bar, unsigned count) {
+    asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(bar), "r"(count));
+}
+__device__ __forceinline__ void mbar_expect_tx(unsigned bar, unsigned bytes) {
+    asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(bar), "r"(bytes) : "memory");
+}
+__device__ __forceinline__ bool mbar_try_wait(unsigned bar, unsigned parity) {
+    unsigned ok;
+    asm volatile("{\n\t.reg .pred p;\n\tmbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\tselp.u32 %0, 1, 0, p;\n\t}"
+                 : "=r"(ok) : "r"(bar), "r"(parity) : "memory");
+    return ok != 0;
+}
+__device__ __forceinline__ unsigned long long global_ns() {
+    unsigned long long t;
+    asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t));
+    return t;
+}
+// Bounded wait: false (and the error word set) when the phase has not completed after ~2 s.
+__device__ __noinline__ bool mbar_wait(unsigned bar, unsigned parity, int code) {
+    if (mbar_try_wait(bar, parity)) return true;
+    const unsigned long long t0 = global_ns();
+    for (unsigned it = 1;; ++it) {
+        if (mbar_try_wait(bar, parity)) return true;
+        if ((it & 1023u) == 0 && global_ns() - t0 > 2000000000ull) {
+            atomicCAS(&g_error, 0, code);
+            return false;
+        }
+    }
+}
+
+__device__ __forceinline__ void tma_load_2d(unsigned dst, const CUtensorMap* map, int x, int y, unsigned bar) {
+    asm volatile("cp.async.bulk.tensor.2d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4}], [%2];"
+                 ::"r"(dst), "l"(map), "r"(bar), "r"(x), "r"(y) : "memory");
+}
+
+// K-major operand tile with 128-byte rows and the 128-byte swizzle: 8-row groups are 1024 bytes apart.
+__device__ __forceinline__ unsigned long long smem_desc(unsigned addr) {
+    unsigned long long d = 0;
+    d |= (unsigned long long)((addr & 0x3FFFF) >> 4);   // start address, 16-byte units
+    d |= (unsigned long long)1 << 16;                   // leading byte offset (unused with swizzled K-major)
+    d |= (unsigned long long)(1024 >> 4) << 32;         // stride byte offset between 8-row groups
+    d |= (unsigned long long)1 << 46;                   // descriptor version of this architecture
+    d |= (unsigned long long)2 << 61;                   // 128-byte swizzle
+    return d;
+}
+
+__device__ __forceinline__ void umma(unsigned tmem_d, unsigned long long a, unsigned long long b, unsigned idesc,
+                                     unsigned accumulate) {
+    asm volatile("{\n\t.reg .pred p;\n\tsetp.ne.b32 p, %4, 0;\n\t"
+                 "tcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, {%5, %6, %7, %8}, p;\n\t}"
+                 ::"r"(tmem_d), "l"(a), "l"(b), "r"(idesc), "r"(accumulate), "r"(0), "r"(0), "r"(0), "r"(0) : "memory");
+}
+__device__ __forceinline__ void umma_commit(unsigned bar) {
+    asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(bar) : "memory");
+}
+__device__ __forceinline__ void tmem_ld16(unsigned taddr, float (&v)[16]) {
+    unsigned r[16];
+    asm volatile("tcgen05.ld.sync.aligned.32x32b.x16.b32 {%0,%1,%2,%3,%4,%5,%6,%7,%8,%9,%10,%11,%12,%13,%14,%15}, [%16];"
+                 : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7]),
+                   "=r"(r[8]), "=r"(r[9]), "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]), "=r"(r[14]), "=r"(r[15])
+                 : "r"(taddr));
+    asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
+#pragma unroll
+    for (int i = 0; i < 16; ++i) v[i] = __uint_as_float(r[i]);
+}
+__device__ __forceinline__ void fence_before() { asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory"); }
+__device__ __forceinline__ void fence_after() { asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory"); }
+__device__ __forceinline__ void cluster_sync_all() {
+    __syncwarp();  // lanes that skipped a single-lane role loop join the others before the aligned barrier
+    asm volatile("barrier.cluster.arrive.release.aligned;\n\tbarrier.cluster.wait.acquire.aligned;" ::: "memory");
+}
+__device__ __forceinline__ unsigned cluster_rank() {
+    unsigned r;
+    asm volatile("mov.u32 %0, %%cluster_ctarank;" : "=r"(r));
+    return r;
+}
+__device__ __forceinline__ float ld_remote_f32(unsigned local_addr, unsigned rank) {
+    unsigned remote;
+    float v;
+    asm volatile("mapa.shared::cluster.u32 %0, %1, %2;" : "=r"(remote) : "r"(local_addr), "r"(rank));
+    asm volatile("ld.shared::cluster.f32 %0, [%1];" : "=f"(v) : "r"(remote) : "memory");
+    return v;
+}
+
+struct Params {
+    void* y;
+    long ldy;
+    int n_tok, n_out, num_kb, y_is_f32;
+};
+
+template <int BN, int STAGES>
+__global__ void __launch_bounds__(THREADS, 1) gemm_kernel(const __grid_constant__ CUtensorMap map_w,
+                                                          const __grid_constant__ CUtensorMap map_x, const Params p) {
+    constexpr int B_BYTES = BN * BK * 2;
+    constexpr int TMEM_COLS = BN < 32 ? 32 : BN;
+    extern __shared__ unsigned char raw_smem[];
+    unsigned char* smem = reinterpret_cast<unsigned char*>((reinterpret_cast<uintptr_t>(raw_smem) + 1023) & ~(uintptr_t)1023);
+    unsigned char* a_tiles = smem;
+    unsigned char* b_tiles = smem + STAGES * A_BYTES;
+    unsigned long long* bars = reinterpret_cast<unsigned long long*>(b_tiles + STAGES * B_BYTES);
+    const unsigned full0 = smem_u32(bars), empty0 = smem_u32(bars + STAGES), accum = smem_u32(bars + 2 * STAGES);
+    unsigned* tmem_slot = reinterpret_cast<unsigned*>(bars + 2 * STAGES + 1);
+
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const int tile_f = blockIdx.x, tile_t = blockIdx.y;
+    const int splits = gridDim.z;
+    const int kb_per = (p.num_kb + splits - 1) / splits;
+    const int kb0 = blockIdx.z * kb_per;
+    const int nkb = (kb0 + kb_per <= p.num_kb ? kb_per : p.num_kb - kb0);  // >= 1: the host keeps splits <= num_kb / 1
+
+    if (threadIdx.x == 0) {
+        for (int s = 0; s < STAGES; ++s) { mbar_init(full0 + 8 * s, 1); mbar_init(empty0 + 8 * s, 1); }
+        mbar_init(accum, 1);
+        asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+    }
+    if (warp == 1) {
+        asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(tmem_slot)), "r"(TMEM_COLS) : "memory");
+        asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
+    }
+    fence_before();
+    __syncthreads();
+    fence_after();
+    const unsigned tmem = *tmem_slot;
+    bool ok = true;
+
+    if (warp == 0) {
+        if (lane == 0 && nkb > 0) {
+            for (int i = 0; i < nkb; ++i) {
+                const int s = i % STAGES;
+                if (i >= STAGES && !mbar_wait(empty0 + 8 * s, ((i / STAGES) - 1) & 1, 1)) { ok = false; break; }
+                mbar_expect_tx(full0 + 8 * s, A_BYTES + B_BYTES);
+                tma_load_2d(smem_u32(a_tiles + s * A_BYTES), &map_w, (kb0 + i) * BK, tile_f * BM, full0 + 8 * s);
+                tma_load_2d(smem_u32(b_tiles + s * B_BYTES), &map_x, (kb0 + i) * BK, tile_t * BN, full0 + 8 * s);
+            }
+        }
+    } else if (warp == 1) {
+        if (lane == 0) {
+            const unsigned idesc = (1u << 4) | (1u << 7) | (1u << 10) | ((unsigned)(BN >> 3) << 17) | ((unsigned)(BM >> 4) << 24);
+            for (int i = 0; i < nkb; ++i) {
+                const int s = i % STAGES;
+                if (!mbar_wait(full0 + 8 * s, (i / STAGES) & 1, 2)) { ok = false; break; }
+                fence_after();
+                const unsigned long long da = smem_desc(smem_u32(a_tiles + s * A_BYTES));
+                const unsigned long long db = smem_desc(smem_u32(b_tiles + s * B_BYTES));
+#pragma unroll
+                for (int k = 0; k < BK / UMMA_K; ++k)
+                    umma(tmem, da + (unsigned long long)(k * UMMA_K * 2 / 16), db + (unsigned long long)(k * UMMA_K * 2 / 16),
+                         idesc, (i | k) != 0);
+                umma_commit(empty0 + 8 * s);   // arrives when these MMAs have read the stage
+            }
+            umma_commit(accum);                // arrives when every MMA above has written the accumulator
+        }
+    }
+
+    const int q = warp & 3;                    // the quarter of the 128 lanes that this warp may read
+    const int row = q * 32 + lane;
+    const int feature = tile_f * BM + row;
+    float* stage = reinterpret_cast<float*>(smem);  // [BN][BM] partial sums for the cluster reduction (stages are idle by then)
+    if (warp >= 2) {
+        ok = nkb > 0 ? mbar_wait(accum, 0, 3) : true;
+        fence_after();
+        if (ok) {
+#pragma unroll 1
+            for (int c0 = 0; c0 < BN; c0 += 16) {
+                float v[16];
+                if (nkb > 0) tmem_ld16(tmem + ((unsigned)(q * 32) << 16) + c0, v);
+                else {
+#pragma unroll
+                    for (int j = 0; j < 16; ++j) v[j] = 0.0f;
+                }
+                if (splits > 1) {
+#pragma unroll
+                    for (int j = 0; j < 16; ++j) stage[(c0 + j) * BM + row] = v[j];
+                } else if (feature < p.n_out) {
+#pragma unroll
+                    for (int j = 0; j < 16; ++j) {
+                        const int tok = tile_t * BN + c0 + j;
+                        if (tok < p.n_tok) {
+                            if (p.y_is_f32) reinterpret_cast<float*>(p.y)[(long)tok * p.ldy + feature] = v[j];
+                            else reinterpret_cast<__nv_bfloat16*>(p.y)[(long)tok * p.ldy + feature] = __float2bfloat16_rn(v[j]);
+                        }
+                    }
+                }
+            }
+        }
+    }
+    if (splits > 1) {
+        cluster_sync_all();                    // every CTA's partial sums are in its shared memory
+        if (warp >= 2 && cluster_rank() == 0 && feature < p.n_out && g_error == 0) {
+            for (int c = 0; c < BN; ++c) {
+                const int tok = tile_t * BN + c;
+                if (tok >= p.n_tok) break;
+                float sum = stage[c * BM + row];
+                const unsigned local = smem_u32(&stage[c * BM + row]);
+                for (int r = 1; r < splits; ++r) sum += ld_remote_f32(local, r);
+                if (p.y_is_f32) reinterpret_cast<float*>(p.y)[(long)tok * p.ldy + feature] = sum;
+                else reinterpret_cast<__nv_bfloat16*>(p.y)[(long)tok * p.ldy + feature] = __float2bfloat16_rn(sum);
+            }
+        }
+        cluster_sync_all();                    // the first CTA has read its neighbours' shared memory
+    }
+
+    if (!ok || g_error != 0) {
+        // a wait ran out somewhere: give copies that are still in flight time to land before the CTA leaves
+        const unsigned long long t0 = global_ns();
+        while (global_ns() - t0 < 2000000ull) __nanosleep(1000);
+    }
+    fence_before();
+    __syncthreads();
+    if (warp == 1) {
+        fence_after();
+        asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem), "r"(TMEM_COLS) : "memory");
+    }
+}
+
+typedef CUresult (*EncodeTiled)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*, const cuuint64_t*,
+                                const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave, CUtensorMapSwizzle,
+                                CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+
+static EncodeTiled encode_fn() {
+    static EncodeTiled fn = nullptr;
+    if (fn == nullptr) {
+        void* sym = nullptr;
+        cudaDriverEntryPointQueryResult q;
+        if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &sym, cudaEnableDefault, &q) == cudaSuccess &&
+            q == cudaDriverEntryPointSuccess)
+            fn = reinterpret_cast<EncodeTiled>(sym);
+    }
+    return fn;
+}
+
+// a row-major [rows, k] bfloat16 matrix with row stride ld (elements), boxes of [box_rows, 64]
+static bool make_map(CUtensorMap* map, const void* base, long rows, long k, long ld, int box_rows) {
+    EncodeTiled enc = encode_fn();
+    if (enc == nullptr) return false;
+    const cuuint64_t dims[2] = {(cuuint64_t)k, (cuuint64_t)rows};
+    const cuuint64_t strides[1] = {(cuuint64_t)ld * 2};
+    const cuuint32_t box[2] = {(cuuint32_t)BK, (cuuint32_t)box_rows};
+    const cuuint32_t elem[2] = {1, 1};
+    return enc(map, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, const_cast<void*>(base), dims, strides, box, elem,
+               CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+               CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) == CUDA_SUCCESS;
+}
+
+template <int BN, int STAGES>
+static int launch(const CUtensorMap& mw, const CUtensorMap& mx, const Params& p, int splits, cudaStream_t stream) {
+    constexpr size_t smem = (size_t)STAGES * (A_BYTES + BN * BK * 2) + (2 * STAGES + 2) * 8 + 1024;
+    static bool configured = false;
+    if (!configured) {
+        cudaError_t e = cudaFuncSetAttribute(gemm_kernel<BN, STAGES>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+        if (e != cudaSuccess) return (int)e;
+        configured = true;
+    }
+    cudaLaunchConfig_t cfg = {};
+    cfg.gridDim = dim3((p.n_out + BM - 1) / BM, (p.n_tok + BN - 1) / BN, splits);
+    cfg.blockDim = dim3(THREADS);
+    cfg.dynamicSmemBytes = smem;
+    cfg.stream = stream;
+    cudaLaunchAttribute attr[1];
+    attr[0].id = cudaLaunchAttributeClusterDimension;
+    attr[0].val.clusterDim.x = 1;
+    attr[0].val.clusterDim.y = 1;
+    attr[0].val.clusterDim.z = splits;
+    cfg.attrs = attr;
+    cfg.numAttrs = 1;
+    cudaError_t e = cudaLaunchKernelEx(&cfg, gemm_kernel<BN, STAGES>, mw, mx, p);
+    return e == cudaSuccess ? ib_launch_status() : (int)e;
+}
+
+}  // namespace tc
+
+// x [n_tok, k] (row stride ldx), w [n_out, k] (row stride ldw), both bfloat16; y [n_tok, n_out] bfloat16 or float32.
+// split_k: 0 lets the function choose (1, 2 or 4 CTAs per output tile).
+IB_EXPORT int ib_gemm_tn_tcgen05(const void* x, long ldx, const void* w, long ldw, void* y, long ldy, int y_is_f32,
+                                 int n_tok, int n_out, int k, int split_k, cudaStream_t stream) {
+    if (n_tok <= 0 || n_out <= 0) return IB_OK;
+    if (k <= 0) return IB_ERR_ARGUMENT;
+    // TMA wants 16-byte aligned bases and row strides
+    if ((k % 8) || (ldx % 8) || (ldw % 8) || ((uintptr_t)x % 16) || ((uintptr_t)w % 16)) return IB_ERR_UNSUPPORTED;
+    const int bn = n_tok <= 16 ? 16 : n_tok <= 32 ? 32 : n_tok <= 64 ? 64 : n_tok <= 128 ? 128 : 256;
+    tc::Params p;
+    p.y = y; p.ldy = ldy; p.n_tok = n_tok; p.n_out = n_out; p.num_kb = (k + tc::BK - 1) / tc::BK; p.y_is_f32 = y_is_f32;
+    int splits = split_k;
+    if (splits <= 0) {
+        const long tiles = (long)((n_out + tc::BM - 1) / tc::BM) * ((n_tok + bn - 1) / bn);
+        splits = tiles >= 120 ? 1 : tiles >= 60 ? 2 : 4;
+    }
+    if (bn == 256) splits = 1;
+    while (splits > 1 && (p.num_kb + splits - 1) / splits * (splits - 1) >= p.num_kb) splits >>= 1;  // no empty part
+    if (splits != 1 && splits != 2 && splits != 4) return IB_ERR_ARGUMENT;
+    CUtensorMap mw, mx;
+    if (!tc::make_map(&mw, w, n_out, k, ldw, tc::BM) || !tc::make_map(&mx, x, n_tok, k, ldx, bn)) return IB_ERR_UNSUPPORTED;
+    switch (bn) {
+        case 16: return tc::launch<16, 10>(mw, mx, p, splits, stream);
+        case 32: return tc::launch<32, 9>(mw, mx, p, splits, stream);
+        case 64: return tc::launch<64, 8>(mw, mx, p, splits, stream);
+        case 128: return tc::launch<128, 6>(mw, mx, p, splits, stream);
+        default: return tc::launch<256, 4>(mw, mx, p, splits, stream);
+    }
+}
+
+// The error word of the kernels above: 0, or the code of the first wait that ran out (1 producer, 2 MMA
+// issuer, 3 epilogue).  Reading it synchronises with the device; `reset` clears it.
+IB_EXPORT int ib_gemm_tcgen05_error(int reset) {
+    int v = 0;
+    if (cudaMemcpyFromSymbol(&v, tc::g_error, sizeof(int)) != cudaSuccess) return -1;
+    if (reset && v != 0) {
+        const int zero = 0;
+        cudaMemcpyToSymbol(tc::g_error, &zero, sizeof(int));
+    }
+    return v;
+}
+
+#endif

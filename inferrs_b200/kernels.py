@@ -415,3 +415,47 @@ def sample(logits: torch.Tensor, temperature: torch.Tensor, top_k: torch.Tensor,
             raise KernelError(f"sample: {name} has {t.shape[0]} entries for {r} rows")
     _check(_core(act_dtype).ib_sample(_p(logits), logits.shape[1], r, logits.shape[1], _p(temperature), _p(top_k),
                                       _p(top_p), _p(min_p), _p(uniform), _p(out), _stream()), "sample")
+
+
+_GEMM_LIB = None
+
+
+def _gemm_lib():
+    global _GEMM_LIB
+    if _GEMM_LIB is None:
+        lib = load_library("gemm_bf16")
+        lib.ib_gemm_tn_tcgen05.argtypes = [c_void_p, c_long, c_void_p, c_long, c_void_p, c_long, c_int, c_int, c_int,
+                                           c_int, c_int, c_void_p]
+        lib.ib_gemm_tn_tcgen05.restype = c_int
+        lib.ib_gemm_tcgen05_error.argtypes = [c_int]
+        lib.ib_gemm_tcgen05_error.restype = c_int
+        _GEMM_LIB = lib
+    return _GEMM_LIB
+
+
+def tcgen05_gemm_supported(x: torch.Tensor, w: torch.Tensor) -> bool:
+    """TMA needs 16-byte aligned bases and row strides: K a multiple of 8 for bfloat16."""
+    return (x.dtype == torch.bfloat16 and w.dtype == torch.bfloat16 and x.shape[1] % 8 == 0
+            and x.data_ptr() % 16 == 0 and w.data_ptr() % 16 == 0)
+
+
+def gemm_tn_tcgen05(x: torch.Tensor, w: torch.Tensor, out: torch.Tensor, split_k: int = 0):
+    """out = x @ w.T with TMA-fed tcgen05 MMAs: W is the 128-row operand, the tokens are the N dimension.
+    ``split_k`` 0 lets the kernel library choose how many CTAs of a cluster share one output tile."""
+    _need(x, "x", (torch.bfloat16,), 2)
+    _need(w, "w", (torch.bfloat16,), 2)
+    _need(out, "out", _W, 2)
+    n, k = x.shape
+    m = w.shape[0]
+    if w.shape[1] != k or out.shape != (n, m):
+        raise KernelError(f"gemm: x {tuple(x.shape)}, w {tuple(w.shape)}, out {tuple(out.shape)}")
+    code = _gemm_lib().ib_gemm_tn_tcgen05(_p(x), k, _p(w), k, _p(out), m, int(out.dtype == torch.float32), n, m, k,
+                                          split_k, _stream())
+    if code == -1:
+        raise KernelError(f"gemm_tn_tcgen05: K={k} must be a multiple of 8 and the bases 16-byte aligned")
+    _check(code, "gemm_tn_tcgen05")
+
+
+def gemm_tcgen05_error(reset: bool = True) -> int:
+    """0, or the code of the first bounded wait that ran out in a tcgen05 GEMM (synchronises with the device)."""
+    return _gemm_lib().ib_gemm_tcgen05_error(int(reset))

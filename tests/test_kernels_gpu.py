@@ -286,3 +286,18 @@ def test_paged_attention_mma_decode_form(nh, nkv, d, ps, window, splits):
     got = out[5].view(nh, d).float()
     want = v_pages[page, :, slot, :].float().repeat_interleave(nh // nkv, dim=0)
     assert rel_err(got, want) < 5e-2, "the far key that stands out was not seen"
+
+
+@pytest.mark.parametrize("n,m,k", [(1, 4096, 4096), (8, 6144, 4096), (17, 300, 136), (64, 517, 96), (33, 128, 64),
+                                   (100, 1000, 512), (300, 384, 256), (16, 4096, 12288), (129, 256, 1024)])
+def test_gemm_tn_tcgen05(n, m, k):
+    from inferrs_b200 import kernels as K
+    x, w = rand((n, k), torch.bfloat16, 70), rand((m, k), torch.bfloat16, 71)
+    ref = x.double() @ w.double().t()
+    for od in (torch.bfloat16, torch.float32):
+        for split in (0, 1, 2, 4):
+            out = torch.full((n, m), float("nan"), dtype=od, device=dev())
+            K.gemm_tn_tcgen05(x, w, out, split)
+            assert K.gemm_tcgen05_error() == 0
+            # float32 sums of up to 12,288 products of magnitude ~1: about 1e-5 of the largest result
+            assert rel_err(out, ref) < (1e-2 if od == torch.bfloat16 else 3e-5), (od, split)
