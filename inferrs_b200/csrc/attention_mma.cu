@@ -385,12 +385,98 @@ IB_EXPORT int ib_paged_attention_mma(const void* q, const void* k_pages, const v
     return IB_OK;
 }
 
+// ---------------------------------------------------------------------------------------------
+// The entry point that allocates nothing (declared and described in no_alloc.h; no counterpart in
+// the reference).  Its scratch is this array in the library image; host code may not use the
+// array's name as a pointer (on the host it names a stand-in, not device memory), so the device
+// address is looked up once per device with cudaGetSymbolAddress and handed to the kernels.
+// ---------------------------------------------------------------------------------------------
+#include <mutex>
+
+#include "no_alloc.h"
+
+static __device__ __align__(256) float ib_noalloc_scratch[IB_NOALLOC_SCRATCH_FLOATS];
+
+#define IB_NOALLOC_MAX_DEVICES 64
+static float* g_noalloc_scratch_addr[IB_NOALLOC_MAX_DEVICES] = {nullptr};
+static std::mutex g_noalloc_mutex;
+
+// Device address of the scratch on the current device; looked up on the first call for that device.
+static int noalloc_scratch(float** ptr) {
+    int dev = 0;
+    cudaError_t e = cudaGetDevice(&dev);
+    if (e != cudaSuccess) return (int)e;
+    if (dev < 0 || dev >= IB_NOALLOC_MAX_DEVICES) return IB_NOALLOC_ERR_ARGUMENT;
+    std::lock_guard<std::mutex> lock(g_noalloc_mutex);
+    if (g_noalloc_scratch_addr[dev] == nullptr) {
+        void* p = nullptr;
+        e = cudaGetSymbolAddress(&p, ib_noalloc_scratch);
+        if (e != cudaSuccess) return (int)e;
+        g_noalloc_scratch_addr[dev] = static_cast<float*>(p);
+    }
+    *ptr = g_noalloc_scratch_addr[dev];
+    return IB_OK;
+}
+
+IB_EXPORT int ib_paged_attention_decode_noalloc(const void* q, const void* k_pages, const void* v_pages,
+                                                const int* block_table, int max_pages, int page_size, int n_pages,
+                                                const int* row_request, const int* q_start, const int* positions,
+                                                int n_rows, int n_heads, int n_kv_heads, int head_dim, float scale,
+                                                int window, void* out, int n_splits, cudaStream_t stream) {
+    if (n_rows <= 0 || n_heads <= 0 || n_kv_heads <= 0 || n_heads % n_kv_heads || head_dim <= 0 || page_size <= 0 ||
+        max_pages <= 0 || n_splits <= 0)
+        return IB_NOALLOC_ERR_ARGUMENT;
+    const long long need = (long long)n_rows * n_heads * n_splits * (head_dim + 2);
+    if (need > (long long)IB_NOALLOC_SCRATCH_FLOATS) return IB_NOALLOC_ERR_TOO_LARGE;
+    float* scratch = nullptr;
+    const int rc = noalloc_scratch(&scratch);
+    if (rc != IB_OK) return rc;
+    // the partial sums first, then the (maximum, sum) pairs, both inside the one array
+    float* part_o = scratch;
+    float* part_ml = scratch + (long long)n_rows * n_heads * n_splits * head_dim;
+    // with one split the regular kernel writes `out` directly and touches no scratch; the scratch is
+    // passed all the same so that both cases take the same path
+    const int code = ib_paged_attention_mma(q, k_pages, v_pages, block_table, max_pages, page_size, n_pages,
+                                            row_request, q_start, n_rows, q_start, positions, n_rows, n_heads,
+                                            n_kv_heads, head_dim, scale, window, out, 1, n_splits, part_o, part_ml,
+                                            stream);
+    if (code == IB_ERR_UNSUPPORTED) return IB_NOALLOC_ERR_UNSUPPORTED;
+    if (code == IB_ERR_ARGUMENT) return IB_NOALLOC_ERR_ARGUMENT;
+    return code;
+}
+
+IB_EXPORT const char* ib_paged_attention_decode_noalloc_strerror(int code) {
+    switch (code) {
+        case 0: return "success";
+        case IB_NOALLOC_ERR_UNSUPPORTED:
+            return "sizes not taken: head_dim must be 64, 128 or 256, the page size must divide 64, and at most 16 "
+                   "query heads may share a key/value head";
+        case IB_NOALLOC_ERR_ARGUMENT: return "a size is zero or negative, or heads are not a multiple of kv heads";
+        case IB_NOALLOC_ERR_TOO_LARGE:
+            return "n_rows * n_heads * n_splits * (head_dim + 2) exceeds the built-in scratch of 4,194,304 floats";
+        case IB_NOALLOC_ERR_BUILD: return "this build of the library has no bfloat16 kernels";
+        default: return code > 0 ? cudaGetErrorString((cudaError_t)code) : "unknown code";
+    }
+}
+
 #else  // the float32 build has no tensor-core attention: its attention is the generic kernel
 
 IB_EXPORT int ib_paged_attention_mma(const void*, const void*, const void*, const int*, int, int, int, const int*,
                                      const int*, int, const int*, const int*, int, int, int, int, float, int, void*,
                                      int, int, float*, float*, cudaStream_t) {
     return IB_ERR_UNSUPPORTED;
+}
+
+#include "no_alloc.h"
+
+IB_EXPORT int ib_paged_attention_decode_noalloc(const void*, const void*, const void*, const int*, int, int, int,
+                                                const int*, const int*, const int*, int, int, int, int, float, int,
+                                                void*, int, cudaStream_t) {
+    return IB_NOALLOC_ERR_BUILD;
+}
+
+IB_EXPORT const char* ib_paged_attention_decode_noalloc_strerror(int code) {
+    return code == IB_NOALLOC_ERR_BUILD ? "this build of the library has no bfloat16 kernels" : "unknown code";
 }
 
 #endif
