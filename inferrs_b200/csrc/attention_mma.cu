@@ -3,7 +3,7 @@
 // One CTA works on one key/value head of one tile of query rows.  The query heads that share a
 // key/value head are packed into the tile's rows: row r = (token r / G, head r % G), so the keys and
 // values are read once for all G heads.  Keys are walked in tiles of 64 (whole pages), brought into
-// shared memory with cp.async (zero-filled where a key is beyond the row's reach), two tiles in flight.
+// shared memory with cp.async (zero-filled where a key is beyond the row's reach), two or three tiles in flight.
 //
 // Two forms of the same loop:
 //   prefill form : 64 rows (64/G tokens of a prompt portion); the four warps own 16 rows each.
@@ -17,6 +17,7 @@
 
 #define AM_KEYS 64
 #define AM_THREADS 128
+#define AM_DECODE_STAGES 3  // the decode form has little arithmetic per tile: it keeps more tiles in flight
 
 __device__ __forceinline__ void am_cp_async16(void* smem, const void* gmem, bool valid) {
     const unsigned s = (unsigned)__cvta_generic_to_shared(smem);
@@ -70,11 +71,12 @@ struct AttnMmaParams {
 template <int D, bool DECODE>
 __global__ void __launch_bounds__(AM_THREADS) paged_attention_mma_kernel(const AttnMmaParams P) {
     constexpr int ROWS = DECODE ? 16 : 64;
+    constexpr int ST = DECODE ? AM_DECODE_STAGES : 2;  // key/value tiles in flight
     constexpr int CH = D / 8;  // 16-byte chunks per row
     extern __shared__ __align__(128) unsigned char am_smem[];
     __nv_bfloat16* sq = reinterpret_cast<__nv_bfloat16*>(am_smem);
     __nv_bfloat16* sk = sq + ROWS * D;
-    __nv_bfloat16* sv = sk + 2 * AM_KEYS * D;
+    __nv_bfloat16* sv = sk + ST * AM_KEYS * D;
 
     const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
     const int gid = lane >> 2, tig = lane & 3;
@@ -147,9 +149,12 @@ __global__ void __launch_bounds__(AM_THREADS) paged_attention_mma_kernel(const A
         for (int i = 0; i < 4; ++i) o[n][i] = 0.0f;
     float m_r[2] = {-INFINITY, -INFINITY}, l_r[2] = {0.0f, 0.0f};
 
-    if (t_begin < t_end) load_kv(t_begin, 0);
-    am_commit();
-    am_wait<1>();  // the queries have landed
+#pragma unroll
+    for (int i = 0; i < ST - 1; ++i) {
+        if (t_begin + i < t_end) load_kv(t_begin + i, i);
+        am_commit();
+    }
+    am_wait<ST - 1>();  // the queries have landed
     __syncthreads();
     unsigned qf[D / 16][4];
 #pragma unroll
@@ -161,10 +166,10 @@ __global__ void __launch_bounds__(AM_THREADS) paged_attention_mma_kernel(const A
 
     constexpr int NP = DECODE ? 1 : 4;  // pairs of 8-key column tiles that this warp computes per key tile
     for (int t = t_begin; t < t_end; ++t) {
-        const int buf = (t - t_begin) & 1;
-        if (t + 1 < t_end) load_kv(t + 1, buf ^ 1);
+        const int buf = (t - t_begin) % ST;
+        if (t + ST - 1 < t_end) load_kv(t + ST - 1, (t + ST - 1 - t_begin) % ST);  // the buffer of tile t - 1
         am_commit();
-        am_wait<1>();
+        am_wait<ST - 1>();
         __syncthreads();
         const __nv_bfloat16* tk = sk + buf * AM_KEYS * D;
         const __nv_bfloat16* tv = sv + buf * AM_KEYS * D;
@@ -336,7 +341,8 @@ __global__ void attention_merge_kernel(const float* __restrict__ part_o, const f
 template <int D, bool DECODE>
 static int launch_attention_mma(const AttnMmaParams& P, int n_tiles, cudaStream_t stream) {
     constexpr int ROWS = DECODE ? 16 : 64;
-    const size_t smem = (size_t)(ROWS * D + 4 * AM_KEYS * D) * sizeof(__nv_bfloat16);
+    constexpr int ST = DECODE ? AM_DECODE_STAGES : 2;
+    const size_t smem = (size_t)(ROWS * D + 2 * ST * AM_KEYS * D) * sizeof(__nv_bfloat16);
     static bool configured = false;
     if (!configured) {
         cudaError_t e = cudaFuncSetAttribute(paged_attention_mma_kernel<D, DECODE>,

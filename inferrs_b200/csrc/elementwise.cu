@@ -66,6 +66,55 @@ __global__ void add_rms_norm_kernel(float* __restrict__ residual, const act_t* _
     }
 }
 
+// Four elements per thread and step (16-byte loads of the residual), for widths that are multiples of 4.
+struct alignas(8) ActVec4 { act_t v[4]; };
+template <typename WT> struct alignas(sizeof(WT) * 4) WVec4 { WT v[4]; };
+
+template <typename WT>
+__global__ void add_rms_norm_vec4_kernel(float* __restrict__ residual, const act_t* __restrict__ delta,
+                                         const WT* __restrict__ weight, act_t* __restrict__ out,
+                                         const int* __restrict__ rows, int width, float eps) {
+    __shared__ float red[32];
+    const int r = blockIdx.x;
+    const int src = rows ? rows[r] : r;
+    float4* res = reinterpret_cast<float4*>(residual + (size_t)src * width);
+    const ActVec4* del = delta ? reinterpret_cast<const ActVec4*>(delta + (size_t)src * width) : nullptr;
+    const bool write_back = (rows == nullptr) && (del != nullptr);
+    const int n4 = width >> 2;
+    float ss = 0.0f;
+    for (int j = threadIdx.x; j < n4; j += blockDim.x) {
+        float4 v = res[j];
+        if (del) {
+            const ActVec4 d = del[j];
+            v.x += ib_to_float(d.v[0]); v.y += ib_to_float(d.v[1]);
+            v.z += ib_to_float(d.v[2]); v.w += ib_to_float(d.v[3]);
+        }
+        if (write_back) res[j] = v;
+        ss += v.x * v.x + v.y * v.y + v.z * v.z + v.w * v.w;
+    }
+    ss = ib_block_sum(ss, red);
+    const float inv = 1.0f / sqrtf(ss / (float)width + eps);
+    ActVec4* dst = reinterpret_cast<ActVec4*>(out + (size_t)r * width);
+    const WVec4<WT>* w4 = reinterpret_cast<const WVec4<WT>*>(weight);
+    for (int j = threadIdx.x; j < n4; j += blockDim.x) {
+        float4 v = res[j];  // this thread's own write, if there was one
+        if (del && !write_back) {
+            const ActVec4 d = del[j];
+            v.x += ib_to_float(d.v[0]); v.y += ib_to_float(d.v[1]);
+            v.z += ib_to_float(d.v[2]); v.w += ib_to_float(d.v[3]);
+        }
+        const WVec4<WT> w = w4[j];
+        ActVec4 o;
+        o.v[0] = ib_from_float<act_t>(v.x * inv * ib_to_float(w.v[0]));
+        o.v[1] = ib_from_float<act_t>(v.y * inv * ib_to_float(w.v[1]));
+        o.v[2] = ib_from_float<act_t>(v.z * inv * ib_to_float(w.v[2]));
+        o.v[3] = ib_from_float<act_t>(v.w * inv * ib_to_float(w.v[3]));
+        dst[j] = o;
+    }
+}
+
+static inline bool ib_aligned16(const void* p) { return p == nullptr || ((uintptr_t)p & 15) == 0; }
+
 IB_EXPORT int ib_add_rms_norm(float* residual, const void* delta, const void* weight, int weight_is_f32, void* out,
                               const int* rows, int n_rows, int width, float eps, cudaStream_t stream) {
     if (n_rows <= 0) return IB_OK;
@@ -73,6 +122,16 @@ IB_EXPORT int ib_add_rms_norm(float* residual, const void* delta, const void* we
     int threads = 128;
     if (width >= 2048) threads = 512;
     else if (width >= 512) threads = 256;
+    if ((width & 3) == 0 && ib_aligned16(residual) && ib_aligned16(delta) && ib_aligned16(weight) && ib_aligned16(out)) {
+        const int t4 = width >= 4096 ? 256 : 128;
+        if (weight_is_f32)
+            add_rms_norm_vec4_kernel<float><<<n_rows, t4, 0, stream>>>(residual, (const act_t*)delta, (const float*)weight,
+                                                                     (act_t*)out, rows, width, eps);
+        else
+            add_rms_norm_vec4_kernel<__nv_bfloat16><<<n_rows, t4, 0, stream>>>(
+                residual, (const act_t*)delta, (const __nv_bfloat16*)weight, (act_t*)out, rows, width, eps);
+        return ib_launch_status();
+    }
     if (weight_is_f32)
         add_rms_norm_kernel<float><<<n_rows, threads, 0, stream>>>(residual, (const act_t*)delta, (const float*)weight,
                                                                   (act_t*)out, rows, width, eps);
@@ -95,10 +154,35 @@ __global__ void silu_gate_kernel(const act_t* __restrict__ gate_up, act_t* __res
     }
 }
 
+// Four elements per thread and step, for inner sizes that are multiples of 4.
+__global__ void silu_gate_vec4_kernel(const act_t* __restrict__ gate_up, act_t* __restrict__ out, int inner, long total4) {
+    const int in4 = inner >> 2;
+    for (long i = (long)blockIdx.x * blockDim.x + threadIdx.x; i < total4; i += (long)gridDim.x * blockDim.x) {
+        const long r = i / in4;
+        const int j = (int)(i - r * in4);
+        const ActVec4 g = reinterpret_cast<const ActVec4*>(gate_up + r * 2 * inner)[j];
+        const ActVec4 u = reinterpret_cast<const ActVec4*>(gate_up + r * 2 * inner + inner)[j];
+        ActVec4 o;
+#pragma unroll
+        for (int k = 0; k < 4; ++k) {
+            const float gv = ib_to_float(g.v[k]);
+            o.v[k] = ib_from_float<act_t>(gv / (1.0f + expf(-gv)) * ib_to_float(u.v[k]));
+        }
+        reinterpret_cast<ActVec4*>(out + r * inner)[j] = o;
+    }
+}
+
 IB_EXPORT int ib_silu_gate(const void* gate_up, void* out, int n_rows, int inner, cudaStream_t stream) {
     if (n_rows <= 0) return IB_OK;
     if (inner <= 0) return IB_ERR_ARGUMENT;
     const long total = (long)n_rows * inner;
+    if ((inner & 3) == 0 && ib_aligned16(gate_up) && ib_aligned16(out)) {
+        const long total4 = total >> 2;
+        long b4 = (total4 + 255) / 256;
+        if (b4 > 148L * 32) b4 = 148L * 32;
+        silu_gate_vec4_kernel<<<(int)b4, 256, 0, stream>>>((const act_t*)gate_up, (act_t*)out, inner, total4);
+        return ib_launch_status();
+    }
     long blocks = (total + 255) / 256;
     if (blocks > 148L * 16) blocks = 148L * 16;
     silu_gate_kernel<<<(int)blocks, 256, 0, stream>>>((const act_t*)gate_up, (act_t*)out, inner, total);

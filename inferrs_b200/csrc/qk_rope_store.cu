@@ -36,7 +36,8 @@ __global__ void qk_norm_rope_store_kernel(
             kv_base = ((long)page * n_kv_heads * page_size + (pos % page_size)) * d;
     }
 
-    for (int head = warp; head < heads_total; head += QRS_WARPS) {
+    // one warp per head: blockIdx.y picks the group of QRS_WARPS heads
+    for (int head = blockIdx.y * QRS_WARPS + warp; head < heads_total; head += heads_total) {
         const act_t* src = qkv + (long)row * row_stride + (long)head * d;
         const int kind = head < n_heads ? 0 : (head < n_heads + n_kv_heads ? 1 : 2);  // 0 q, 1 k, 2 v
         float ss = 0.0f;
@@ -90,13 +91,15 @@ IB_EXPORT int ib_qk_norm_rope_store(const void* qkv, int row_stride, int n_rows,
     if (store_kv && (n_kv_heads <= 0 || page_size <= 0 || max_pages <= 0)) return IB_ERR_ARGUMENT;
     if (rot_dim > 0 && (cos_table == nullptr || sin_table == nullptr || table_rows <= 0)) return IB_ERR_ARGUMENT;
     const size_t smem = (size_t)QRS_WARPS * head_dim * sizeof(float);
+    const int heads_total = n_heads + (store_kv ? 2 * n_kv_heads : 0);
+    const dim3 grid(n_rows, (heads_total + QRS_WARPS - 1) / QRS_WARPS);
     if (weight_is_f32)
-        qk_norm_rope_store_kernel<float><<<n_rows, 32 * QRS_WARPS, smem, stream>>>(
+        qk_norm_rope_store_kernel<float><<<grid, 32 * QRS_WARPS, smem, stream>>>(
             (const act_t*)qkv, row_stride, n_heads, n_kv_heads, head_dim, store_kv, (const float*)q_weight,
             (const float*)k_weight, eps, cos_table, sin_table, rot_dim, positions, row_request, block_table,
             max_pages, page_size, n_pages, (act_t*)k_pages, (act_t*)v_pages, (act_t*)q_out);
     else
-        qk_norm_rope_store_kernel<__nv_bfloat16><<<n_rows, 32 * QRS_WARPS, smem, stream>>>(
+        qk_norm_rope_store_kernel<__nv_bfloat16><<<grid, 32 * QRS_WARPS, smem, stream>>>(
             (const act_t*)qkv, row_stride, n_heads, n_kv_heads, head_dim, store_kv, (const __nv_bfloat16*)q_weight,
             (const __nv_bfloat16*)k_weight, eps, cos_table, sin_table, rot_dim, positions, row_request, block_table,
             max_pages, page_size, n_pages, (act_t*)k_pages, (act_t*)v_pages, (act_t*)q_out);

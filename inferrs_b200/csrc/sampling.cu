@@ -38,9 +38,75 @@ __global__ void argmax_kernel(const float* __restrict__ logits, int* __restrict_
     }
 }
 
-IB_EXPORT int ib_argmax(const float* logits, int* out, int n_rows, int vocab, long ld, cudaStream_t stream) {
+// Two-stage form for few rows: the vocabulary is cut into chunks, one block each, so that a single row still
+// fills the machine.  A partial result is one 64-bit word, (ordered value bits << 32) | ~index, whose
+// unsigned maximum is the largest value and, among equal values, the lowest index.
+#define ARGMAX_CHUNK 8192
+
+__device__ __forceinline__ unsigned long long argmax_pack(float v, int i) {
+    unsigned b = __float_as_uint(v);
+    b = (b & 0x80000000u) ? ~b : (b | 0x80000000u);  // unsigned order = float order
+    return ((unsigned long long)b << 32) | (unsigned long long)(0xffffffffu - (unsigned)i);
+}
+
+__global__ void argmax_partial_kernel(const float* __restrict__ logits, unsigned long long* __restrict__ part,
+                                      int vocab, long ld, int n_chunks) {
+    __shared__ unsigned long long red[32];
+    const float* row = logits + (long)blockIdx.x * ld;
+    const int j0 = blockIdx.y * ARGMAX_CHUNK;
+    const int j1 = j0 + ARGMAX_CHUNK < vocab ? j0 + ARGMAX_CHUNK : vocab;
+    unsigned long long best = 0;  // below every packed value of a real number
+    for (int j = j0 + threadIdx.x; j < j1; j += blockDim.x) {
+        const float v = row[j];
+        if (v == v) {
+            const unsigned long long p = argmax_pack(v, j);
+            best = p > best ? p : best;
+        }
+    }
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) {
+        const unsigned long long other = __shfl_xor_sync(0xffffffffu, best, o);
+        best = other > best ? other : best;
+    }
+    if ((threadIdx.x & 31) == 0) red[threadIdx.x >> 5] = best;
+    __syncthreads();
+    if (threadIdx.x < 32) {
+        best = threadIdx.x < (blockDim.x >> 5) ? red[threadIdx.x] : 0;
+#pragma unroll
+        for (int o = 16; o > 0; o >>= 1) {
+            const unsigned long long other = __shfl_xor_sync(0xffffffffu, best, o);
+            best = other > best ? other : best;
+        }
+        if (threadIdx.x == 0) part[(long)blockIdx.x * n_chunks + blockIdx.y] = best;
+    }
+}
+
+__global__ void argmax_final_kernel(const unsigned long long* __restrict__ part, int* __restrict__ out, int n_chunks) {
+    unsigned long long best = 0;
+    for (int c = threadIdx.x; c < n_chunks; c += 32) {
+        const unsigned long long p = part[(long)blockIdx.x * n_chunks + c];
+        best = p > best ? p : best;
+    }
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) {
+        const unsigned long long other = __shfl_xor_sync(0xffffffffu, best, o);
+        best = other > best ? other : best;
+    }
+    if (threadIdx.x == 0) out[blockIdx.x] = best == 0 ? 0 : (int)(0xffffffffu - (unsigned)(best & 0xffffffffu));
+}
+
+// scratch: n_rows * ceil(vocab / 8192) 64-bit words, or nullptr for the one-block-per-row form
+IB_EXPORT int ib_argmax(const float* logits, int* out, int n_rows, int vocab, long ld, void* scratch,
+                        cudaStream_t stream) {
     if (n_rows <= 0) return IB_OK;
     if (vocab <= 0) return IB_ERR_ARGUMENT;
+    const int n_chunks = (vocab + ARGMAX_CHUNK - 1) / ARGMAX_CHUNK;
+    if (scratch != nullptr && n_chunks > 1) {
+        argmax_partial_kernel<<<dim3(n_rows, n_chunks), 512, 0, stream>>>(logits, (unsigned long long*)scratch, vocab,
+                                                                         ld, n_chunks);
+        argmax_final_kernel<<<n_rows, 32, 0, stream>>>((const unsigned long long*)scratch, out, n_chunks);
+        return ib_launch_status();
+    }
     const int threads = vocab >= 8192 ? 1024 : 256;
     argmax_kernel<<<n_rows, threads, 0, stream>>>(logits, out, vocab, ld);
     return ib_launch_status();

@@ -12,6 +12,7 @@ longest context, and the batch is padded with requests that own no pages.
 """
 from __future__ import annotations
 
+import gc
 from typing import Dict, List, Optional, Sequence
 
 import torch
@@ -85,8 +86,17 @@ class DecodeGraphs:
         torch.cuda.synchronize()
         graph = torch.cuda.CUDAGraph()
         n0 = kernels.launch_count()
-        with torch.cuda.graph(graph, pool=self.pool):
-            logits = r.model.forward(ctx)
+        # No Python object may be collected while the stream captures: the destructor of an older graph
+        # calls into CUDA and would invalidate the capture.
+        gc.collect()
+        was_enabled = gc.isenabled()
+        gc.disable()
+        try:
+            with torch.cuda.graph(graph, pool=self.pool):
+                logits = r.model.forward(ctx)
+        finally:
+            if was_enabled:
+                gc.enable()
         launches = kernels.launch_count() - n0
         if self.pool is None:
             self.pool = graph.pool()

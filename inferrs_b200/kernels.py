@@ -36,7 +36,7 @@ _SIGNATURES = {
     "ib_paged_attention_mma": [c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_void_p, c_void_p, c_int,
                                c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_float, c_int, c_void_p, c_int, c_int,
                                c_void_p, c_void_p, c_void_p],
-    "ib_argmax": [c_void_p, c_void_p, c_int, c_int, c_long, c_void_p],
+    "ib_argmax": [c_void_p, c_void_p, c_int, c_int, c_long, c_void_p, c_void_p],
     "ib_penalties": [c_void_p, c_long, c_int, c_int, c_void_p, c_int, c_void_p, c_void_p, c_void_p, c_void_p,
                      c_void_p],
     "ib_sample": [c_void_p, c_long, c_int, c_int, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p,
@@ -264,8 +264,12 @@ def argmax(logits: torch.Tensor, out: torch.Tensor, act_dtype: torch.dtype = tor
     _need(out, "out", _I, 1)
     if out.shape[0] != logits.shape[0]:
         raise KernelError(f"argmax: logits {tuple(logits.shape)}, out {tuple(out.shape)}")
-    _check(_core(act_dtype).ib_argmax(_p(logits), _p(out), logits.shape[0], logits.shape[1], logits.shape[1],
-                                          _stream()), "argmax")
+    rows, vocab = logits.shape
+    scratch = None
+    if vocab > ARGMAX_CHUNK:  # the vocabulary is cut into chunks so that few rows still fill the machine
+        scratch = torch.empty((rows, (vocab + ARGMAX_CHUNK - 1) // ARGMAX_CHUNK), dtype=torch.int64,
+                              device=logits.device)
+    _check(_core(act_dtype).ib_argmax(_p(logits), _p(out), rows, vocab, vocab, _p(scratch), _stream()), "argmax")
 
 
 _MM_F32_OUT = None  # does this torch give float32 results from a bfloat16 product?
@@ -307,8 +311,9 @@ def linear(x: torch.Tensor, w: torch.Tensor, out: torch.Tensor, act_dtype: torch
         gemm_tn_bf16(x, w, out)
 
 
+ARGMAX_CHUNK = 8192      # vocabulary entries per block of the two-stage argmax
 MMA_KEYS = 64          # keys per tile of the tensor-core attention kernel
-MMA_TARGET_CTAS = 444  # CTAs that fill the machine: 148 SMs x 3 resident
+MMA_TARGET_CTAS = 1184  # four waves of 2 resident CTAs on 148 SMs: many small CTAs even out the last wave
 
 
 def mma_attention_supported(dtype: torch.dtype, n_heads: int, n_kv_heads: int, head_dim: int, page_size: int) -> bool:
@@ -317,10 +322,11 @@ def mma_attention_supported(dtype: torch.dtype, n_heads: int, n_kv_heads: int, h
 
 
 def decode_splits(n_requests: int, n_kv_heads: int, max_kv_len: int) -> int:
-    """How many ways the decode form cuts each request's keys, so that the grid fills the machine."""
+    """How many ways the decode form cuts each request's keys: enough CTAs to fill the machine several
+    times over, but at least four 64-key tiles for each of them."""
     tiles = max(1, (max_kv_len + MMA_KEYS - 1) // MMA_KEYS)
     want = (MMA_TARGET_CTAS + n_requests * n_kv_heads - 1) // (n_requests * n_kv_heads)
-    return max(1, min(want, tiles))
+    return max(1, min(want, tiles // 4))
 
 
 def paged_attention_mma(q: torch.Tensor, k_pages: torch.Tensor, v_pages: torch.Tensor, block_table: torch.Tensor,
