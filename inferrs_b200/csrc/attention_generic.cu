@@ -21,6 +21,7 @@ __global__ void paged_attention_generic_kernel(
     const int* __restrict__ row_request, const int* __restrict__ positions, int n_heads, int n_kv_heads,
     int head_dim, float scale, int window, act_t* __restrict__ out) {
     extern __shared__ float smem[];
+    ib_grid_dependency_sync();
     const int row = blockIdx.x;
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const int head = blockIdx.y * ATT_WARPS + warp;
@@ -98,7 +99,7 @@ IB_EXPORT int ib_paged_attention_generic(const void* q, const void* k_pages, con
     const dim3 grid(n_rows, (n_heads + ATT_WARPS - 1) / ATT_WARPS);
     const size_t smem = (size_t)ATT_WARPS * head_dim * sizeof(float);
 #define IB_LAUNCH_ATT(DPL)                                                                                      \
-    paged_attention_generic_kernel<DPL><<<grid, 32 * ATT_WARPS, smem, stream>>>(                                \
+    ib_launch(paged_attention_generic_kernel<DPL>, grid, 32 * ATT_WARPS, smem, stream,                          \
         (const act_t*)q, (const act_t*)k_pages, (const act_t*)v_pages, block_table, max_pages, page_size,       \
         n_pages, row_request, positions, n_heads, n_kv_heads, head_dim, scale, window, (act_t*)out)
     if (head_dim <= 32) IB_LAUNCH_ATT(1);

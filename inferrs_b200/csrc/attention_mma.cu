@@ -78,6 +78,7 @@ __global__ void __launch_bounds__(AM_THREADS) paged_attention_mma_kernel(const A
     __nv_bfloat16* sk = sq + ROWS * D;
     __nv_bfloat16* sv = sk + ST * AM_KEYS * D;
 
+    ib_grid_dependency_sync();
     const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
     const int gid = lane >> 2, tig = lane & 3;
     const int tile = blockIdx.x, kvh = blockIdx.y, split = blockIdx.z;
@@ -321,6 +322,7 @@ __global__ void __launch_bounds__(AM_THREADS) paged_attention_mma_kernel(const A
 // out[row, head, :] = sum_s 2^(m_s - M) o_s / sum_s 2^(m_s - M) l_s
 __global__ void attention_merge_kernel(const float* __restrict__ part_o, const float* __restrict__ part_ml,
                                        __nv_bfloat16* __restrict__ out, int n_splits, int head_dim) {
+    ib_grid_dependency_sync();
     const long head = blockIdx.x;  // row * n_heads + head
     const float* ml = part_ml + head * n_splits * 2;
     float M = -INFINITY;
@@ -351,7 +353,7 @@ static int launch_attention_mma(const AttnMmaParams& P, int n_tiles, cudaStream_
         configured = true;
     }
     const dim3 grid(n_tiles, P.n_kv_heads, DECODE ? P.n_splits : 1);
-    paged_attention_mma_kernel<D, DECODE><<<grid, AM_THREADS, smem, stream>>>(P);
+    ib_launch(paged_attention_mma_kernel<D, DECODE>, grid, AM_THREADS, smem, stream, P);
     return ib_launch_status();
 }
 
@@ -384,8 +386,8 @@ IB_EXPORT int ib_paged_attention_mma(const void* q, const void* k_pages, const v
 #undef IB_AM_CASE
     if (rc != IB_OK) return rc;
     if (decode_form && P.n_splits > 1) {
-        attention_merge_kernel<<<n_rows * n_heads, head_dim < 128 ? 64 : 128, 0, stream>>>(
-            part_o, part_ml, (__nv_bfloat16*)out, P.n_splits, head_dim);
+        ib_launch(attention_merge_kernel, n_rows * n_heads, head_dim < 128 ? 64 : 128, 0, stream, (const float*)part_o,
+                  (const float*)part_ml, (__nv_bfloat16*)out, P.n_splits, head_dim);
         return ib_launch_status();
     }
     return IB_OK;

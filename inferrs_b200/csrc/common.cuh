@@ -63,6 +63,37 @@ __device__ __forceinline__ float ib_block_sum(float v, float* smem32) {
     return r;
 }
 
+// ---------------------------------------------------------------------------------------------
+// Programmatic dependent launch.  When the library's switch is on (ib_set_pdl), kernels are launched so
+// that they may start before the kernel before them in the stream has finished.  Every kernel of this
+// package therefore begins with ib_grid_dependency_sync(): it lets the kernel after it start in turn and
+// then waits until the kernel before it has completed and its writes are visible.  Only what no kernel
+// writes (weights, tables) may be read before that call.  With the switch off, or for a kernel launched
+// the plain way, both instructions do nothing.
+// ---------------------------------------------------------------------------------------------
+__device__ __forceinline__ void ib_grid_dependency_sync() {
+    asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
+    asm volatile("griddepcontrol.wait;" ::: "memory");
+}
+
+extern int ib_pdl_enabled;  // one per library, defined beside its exported setter ib_set_pdl
+
+template <typename... KArgs, typename... Args>
+static inline void ib_launch(void (*kernel)(KArgs...), dim3 grid, dim3 block, size_t smem, cudaStream_t stream,
+                             Args&&... args) {
+    cudaLaunchConfig_t cfg = {};
+    cfg.gridDim = grid;
+    cfg.blockDim = block;
+    cfg.dynamicSmemBytes = smem;
+    cfg.stream = stream;
+    cudaLaunchAttribute attr[1];
+    attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    attr[0].val.programmaticStreamSerializationAllowed = 1;
+    cfg.attrs = attr;
+    cfg.numAttrs = ib_pdl_enabled ? 1 : 0;
+    cudaLaunchKernelEx(&cfg, kernel, static_cast<KArgs>(args)...);
+}
+
 static inline int ib_launch_status() {
     cudaError_t e = cudaPeekAtLastError();
     return e == cudaSuccess ? IB_OK : (int)e;

@@ -5,12 +5,19 @@
 // product is stored as act_t.
 #include "common.cuh"
 
+int ib_pdl_enabled = 0;
+
+// 1: the kernels of this library are launched so that they may start before their predecessor in the stream
+// has finished (see common.cuh); 0: plain stream order.
+IB_EXPORT void ib_set_pdl(int on) { ib_pdl_enabled = on; }
+
 // ---------------------------------------------------------------------------
 // Embedding: out[row, :] = table[ids[row], :]   (no scale)
 // ---------------------------------------------------------------------------
 template <typename WT>
 __global__ void embedding_gather_kernel(const WT* __restrict__ table, const int* __restrict__ ids,
                                         float* __restrict__ out, int width, int vocab) {
+    ib_grid_dependency_sync();
     const int row = blockIdx.x;
     const int id = ids[row];
     const bool ok = id >= 0 && id < vocab;  // the host refuses such ids before the launch
@@ -25,10 +32,10 @@ IB_EXPORT int ib_embedding_gather(const void* table, int table_is_f32, const int
     if (width <= 0 || vocab <= 0) return IB_ERR_ARGUMENT;
     const int threads = width >= 1024 ? 256 : 128;
     if (table_is_f32)
-        embedding_gather_kernel<float><<<n_rows, threads, 0, stream>>>((const float*)table, ids, out, width, vocab);
+        ib_launch(embedding_gather_kernel<float>, n_rows, threads, 0, stream, (const float*)table, ids, out, width, vocab);
     else
-        embedding_gather_kernel<__nv_bfloat16>
-            <<<n_rows, threads, 0, stream>>>((const __nv_bfloat16*)table, ids, out, width, vocab);
+        ib_launch(embedding_gather_kernel<__nv_bfloat16>, n_rows, threads, 0, stream, (const __nv_bfloat16*)table, ids, out,
+                  width, vocab);
     return ib_launch_status();
 }
 
@@ -44,6 +51,7 @@ __global__ void add_rms_norm_kernel(float* __restrict__ residual, const act_t* _
                                     const WT* __restrict__ weight, act_t* __restrict__ out,
                                     const int* __restrict__ rows, int width, float eps) {
     __shared__ float red[32];
+    ib_grid_dependency_sync();
     const int r = blockIdx.x;
     const int src = rows ? rows[r] : r;
     float* res = residual + (size_t)src * width;
@@ -75,6 +83,7 @@ __global__ void add_rms_norm_vec4_kernel(float* __restrict__ residual, const act
                                          const WT* __restrict__ weight, act_t* __restrict__ out,
                                          const int* __restrict__ rows, int width, float eps) {
     __shared__ float red[32];
+    ib_grid_dependency_sync();
     const int r = blockIdx.x;
     const int src = rows ? rows[r] : r;
     float4* res = reinterpret_cast<float4*>(residual + (size_t)src * width);
@@ -125,19 +134,19 @@ IB_EXPORT int ib_add_rms_norm(float* residual, const void* delta, const void* we
     if ((width & 3) == 0 && ib_aligned16(residual) && ib_aligned16(delta) && ib_aligned16(weight) && ib_aligned16(out)) {
         const int t4 = width >= 4096 ? 256 : 128;
         if (weight_is_f32)
-            add_rms_norm_vec4_kernel<float><<<n_rows, t4, 0, stream>>>(residual, (const act_t*)delta, (const float*)weight,
-                                                                     (act_t*)out, rows, width, eps);
+            ib_launch(add_rms_norm_vec4_kernel<float>, n_rows, t4, 0, stream, residual, (const act_t*)delta,
+                      (const float*)weight, (act_t*)out, rows, width, eps);
         else
-            add_rms_norm_vec4_kernel<__nv_bfloat16><<<n_rows, t4, 0, stream>>>(
-                residual, (const act_t*)delta, (const __nv_bfloat16*)weight, (act_t*)out, rows, width, eps);
+            ib_launch(add_rms_norm_vec4_kernel<__nv_bfloat16>, n_rows, t4, 0, stream, residual, (const act_t*)delta,
+                      (const __nv_bfloat16*)weight, (act_t*)out, rows, width, eps);
         return ib_launch_status();
     }
     if (weight_is_f32)
-        add_rms_norm_kernel<float><<<n_rows, threads, 0, stream>>>(residual, (const act_t*)delta, (const float*)weight,
-                                                                  (act_t*)out, rows, width, eps);
+        ib_launch(add_rms_norm_kernel<float>, n_rows, threads, 0, stream, residual, (const act_t*)delta,
+                  (const float*)weight, (act_t*)out, rows, width, eps);
     else
-        add_rms_norm_kernel<__nv_bfloat16><<<n_rows, threads, 0, stream>>>(
-            residual, (const act_t*)delta, (const __nv_bfloat16*)weight, (act_t*)out, rows, width, eps);
+        ib_launch(add_rms_norm_kernel<__nv_bfloat16>, n_rows, threads, 0, stream, residual, (const act_t*)delta,
+                  (const __nv_bfloat16*)weight, (act_t*)out, rows, width, eps);
     return ib_launch_status();
 }
 
@@ -145,6 +154,7 @@ IB_EXPORT int ib_add_rms_norm(float* residual, const void* delta, const void* we
 // out[r, j] = silu(gate_up[r, j]) * gate_up[r, inner + j],  silu(z) = z / (1 + exp(-z))
 // ---------------------------------------------------------------------------
 __global__ void silu_gate_kernel(const act_t* __restrict__ gate_up, act_t* __restrict__ out, int inner, long total) {
+    ib_grid_dependency_sync();
     for (long i = (long)blockIdx.x * blockDim.x + threadIdx.x; i < total; i += (long)gridDim.x * blockDim.x) {
         const long r = i / inner;
         const int j = (int)(i - r * inner);
@@ -156,6 +166,7 @@ __global__ void silu_gate_kernel(const act_t* __restrict__ gate_up, act_t* __res
 
 // Four elements per thread and step, for inner sizes that are multiples of 4.
 __global__ void silu_gate_vec4_kernel(const act_t* __restrict__ gate_up, act_t* __restrict__ out, int inner, long total4) {
+    ib_grid_dependency_sync();
     const int in4 = inner >> 2;
     for (long i = (long)blockIdx.x * blockDim.x + threadIdx.x; i < total4; i += (long)gridDim.x * blockDim.x) {
         const long r = i / in4;
@@ -180,12 +191,12 @@ IB_EXPORT int ib_silu_gate(const void* gate_up, void* out, int n_rows, int inner
         const long total4 = total >> 2;
         long b4 = (total4 + 255) / 256;
         if (b4 > 148L * 32) b4 = 148L * 32;
-        silu_gate_vec4_kernel<<<(int)b4, 256, 0, stream>>>((const act_t*)gate_up, (act_t*)out, inner, total4);
+        ib_launch(silu_gate_vec4_kernel, (int)b4, 256, 0, stream, (const act_t*)gate_up, (act_t*)out, inner, total4);
         return ib_launch_status();
     }
     long blocks = (total + 255) / 256;
     if (blocks > 148L * 16) blocks = 148L * 16;
-    silu_gate_kernel<<<(int)blocks, 256, 0, stream>>>((const act_t*)gate_up, (act_t*)out, inner, total);
+    ib_launch(silu_gate_kernel, (int)blocks, 256, 0, stream, (const act_t*)gate_up, (act_t*)out, inner, total);
     return ib_launch_status();
 }
 
@@ -193,6 +204,7 @@ IB_EXPORT int ib_silu_gate(const void* gate_up, void* out, int n_rows, int inner
 // Casts between float and act_t (used where a 32-bit weight meets bfloat16 activations).
 // ---------------------------------------------------------------------------
 __global__ void act_to_float_kernel(const act_t* __restrict__ in, float* __restrict__ out, long total) {
+    ib_grid_dependency_sync();
     for (long i = (long)blockIdx.x * blockDim.x + threadIdx.x; i < total; i += (long)gridDim.x * blockDim.x)
         out[i] = ib_to_float(in[i]);
 }
@@ -201,6 +213,6 @@ IB_EXPORT int ib_act_to_float(const void* in, float* out, long total, cudaStream
     if (total <= 0) return IB_OK;
     long blocks = (total + 255) / 256;
     if (blocks > 148L * 16) blocks = 148L * 16;
-    act_to_float_kernel<<<(int)blocks, 256, 0, stream>>>((const act_t*)in, out, total);
+    ib_launch(act_to_float_kernel, (int)blocks, 256, 0, stream, (const act_t*)in, out, total);
     return ib_launch_status();
 }

@@ -29,6 +29,7 @@ constexpr int THREADS = 192;
 constexpr int A_BYTES = BM * BK * 2;
 
 __device__ int g_error = 0;   // 0 ok; else (role code) of the first wait that ran out
+static int g_pdl = 0;          // host: launch with programmatic stream serialization (see ib_gemm_tcgen05_set_pdl)
 
 __device__ __forceinline__ unsigned smem_u32(const void* p) { return (unsigned)__cvta_generic_to_shared(p); }
 
@@ -123,7 +124,7 @@ struct Params {
 };
 
 template <int BN, int STAGES>
-__global__ void __launch_bounds__(THREADS, 1) gemm_kernel(const __grid_constant__ CUtensorMap map_w,
+__global__ void __launch_bounds__(THREADS, (BN <= 64 ? 2 : 1)) gemm_kernel(const __grid_constant__ CUtensorMap map_w,
                                                           const __grid_constant__ CUtensorMap map_x, const Params p) {
     constexpr int B_BYTES = BN * BK * 2;
     constexpr int TMEM_COLS = BN < 32 ? 32 : BN;
@@ -142,6 +143,10 @@ __global__ void __launch_bounds__(THREADS, 1) gemm_kernel(const __grid_constant_
     const int kb0 = blockIdx.z * kb_per;
     const int nkb = (kb0 + kb_per <= p.num_kb ? kb_per : p.num_kb - kb0);  // >= 1: the host keeps splits <= num_kb / 1
 
+    // Under programmatic dependent launch the next kernel of the stream may start its own prologue now; this
+    // kernel in turn may have been started before its predecessor finished, so it reads the weights (which no
+    // kernel writes) at once but touches x, y and the rest only after griddepcontrol.wait.
+    asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
     if (threadIdx.x == 0) {
         for (int s = 0; s < STAGES; ++s) { mbar_init(full0 + 8 * s, 1); mbar_init(empty0 + 8 * s, 1); }
         mbar_init(accum, 1);
@@ -159,9 +164,18 @@ __global__ void __launch_bounds__(THREADS, 1) gemm_kernel(const __grid_constant_
 
     if (warp == 0) {
         if (lane == 0 && nkb > 0) {
-            for (int i = 0; i < nkb; ++i) {
+            // the first ring of weight tiles is on its way before the predecessor's results are waited for
+            const int head = nkb < STAGES ? nkb : STAGES;
+            for (int i = 0; i < head; ++i) {
+                mbar_expect_tx(full0 + 8 * i, A_BYTES + B_BYTES);
+                tma_load_2d(smem_u32(a_tiles + i * A_BYTES), &map_w, (kb0 + i) * BK, tile_f * BM, full0 + 8 * i);
+            }
+            asm volatile("griddepcontrol.wait;" ::: "memory");
+            for (int i = 0; i < head; ++i)
+                tma_load_2d(smem_u32(b_tiles + i * B_BYTES), &map_x, (kb0 + i) * BK, tile_t * BN, full0 + 8 * i);
+            for (int i = head; i < nkb; ++i) {
                 const int s = i % STAGES;
-                if (i >= STAGES && !mbar_wait(empty0 + 8 * s, ((i / STAGES) - 1) & 1, 1)) { ok = false; break; }
+                if (!mbar_wait(empty0 + 8 * s, ((i / STAGES) - 1) & 1, 1)) { ok = false; break; }
                 mbar_expect_tx(full0 + 8 * s, A_BYTES + B_BYTES);
                 tma_load_2d(smem_u32(a_tiles + s * A_BYTES), &map_w, (kb0 + i) * BK, tile_f * BM, full0 + 8 * s);
                 tma_load_2d(smem_u32(b_tiles + s * B_BYTES), &map_x, (kb0 + i) * BK, tile_t * BN, full0 + 8 * s);
@@ -191,6 +205,7 @@ __global__ void __launch_bounds__(THREADS, 1) gemm_kernel(const __grid_constant_
     const int feature = tile_f * BM + row;
     float* stage = reinterpret_cast<float*>(smem);  // [BN][BM] partial sums for the cluster reduction (stages are idle by then)
     if (warp >= 2) {
+        asm volatile("griddepcontrol.wait;" ::: "memory");   // y may still be read by the predecessor
         ok = nkb > 0 ? mbar_wait(accum, 0, 3) : true;
         fence_after();
         if (ok) {
@@ -221,14 +236,26 @@ __global__ void __launch_bounds__(THREADS, 1) gemm_kernel(const __grid_constant_
     if (splits > 1) {
         cluster_sync_all();                    // every CTA's partial sums are in its shared memory
         if (warp >= 2 && cluster_rank() == 0 && feature < p.n_out && g_error == 0) {
-            for (int c = 0; c < BN; ++c) {
-                const int tok = tile_t * BN + c;
-                if (tok >= p.n_tok) break;
-                float sum = stage[c * BM + row];
-                const unsigned local = smem_u32(&stage[c * BM + row]);
-                for (int r = 1; r < splits; ++r) sum += ld_remote_f32(local, r);
-                if (p.y_is_f32) reinterpret_cast<float*>(p.y)[(long)tok * p.ldy + feature] = sum;
-                else reinterpret_cast<__nv_bfloat16*>(p.y)[(long)tok * p.ldy + feature] = __float2bfloat16_rn(sum);
+#pragma unroll 1
+            for (int c0 = 0; c0 < BN && tile_t * BN + c0 < p.n_tok; c0 += 16) {
+                float sum[16];
+#pragma unroll
+                for (int j = 0; j < 16; ++j) sum[j] = stage[(c0 + j) * BM + row];
+                for (int r = 1; r < splits; ++r) {   // sixteen independent remote loads at a time
+                    float part[16];
+#pragma unroll
+                    for (int j = 0; j < 16; ++j) part[j] = ld_remote_f32(smem_u32(&stage[(c0 + j) * BM + row]), r);
+#pragma unroll
+                    for (int j = 0; j < 16; ++j) sum[j] += part[j];
+                }
+#pragma unroll
+                for (int j = 0; j < 16; ++j) {
+                    const int tok = tile_t * BN + c0 + j;
+                    if (tok < p.n_tok) {
+                        if (p.y_is_f32) reinterpret_cast<float*>(p.y)[(long)tok * p.ldy + feature] = sum[j];
+                        else reinterpret_cast<__nv_bfloat16*>(p.y)[(long)tok * p.ldy + feature] = __float2bfloat16_rn(sum[j]);
+                    }
+                }
             }
         }
         cluster_sync_all();                    // the first CTA has read its neighbours' shared memory
@@ -290,13 +317,15 @@ static int launch(const CUtensorMap& mw, const CUtensorMap& mx, const Params& p,
     cfg.blockDim = dim3(THREADS);
     cfg.dynamicSmemBytes = smem;
     cfg.stream = stream;
-    cudaLaunchAttribute attr[1];
+    cudaLaunchAttribute attr[2];
     attr[0].id = cudaLaunchAttributeClusterDimension;
     attr[0].val.clusterDim.x = 1;
     attr[0].val.clusterDim.y = 1;
     attr[0].val.clusterDim.z = splits;
+    attr[1].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    attr[1].val.programmaticStreamSerializationAllowed = 1;
     cfg.attrs = attr;
-    cfg.numAttrs = 1;
+    cfg.numAttrs = g_pdl ? 2 : 1;
     cudaError_t e = cudaLaunchKernelEx(&cfg, gemm_kernel<BN, STAGES>, mw, mx, p);
     return e == cudaSuccess ? ib_launch_status() : (int)e;
 }
@@ -325,13 +354,21 @@ IB_EXPORT int ib_gemm_tn_tcgen05(const void* x, long ldx, const void* w, long ld
     CUtensorMap mw, mx;
     if (!tc::make_map(&mw, w, n_out, k, ldw, tc::BM) || !tc::make_map(&mx, x, n_tok, k, ldx, bn)) return IB_ERR_UNSUPPORTED;
     switch (bn) {
-        case 16: return tc::launch<16, 10>(mw, mx, p, splits, stream);
-        case 32: return tc::launch<32, 9>(mw, mx, p, splits, stream);
-        case 64: return tc::launch<64, 8>(mw, mx, p, splits, stream);
+        // up to 64 tokens: two CTAs per SM with half the ring each, so that tile counts between one and two
+        // per SM still run as one wave in which every CTA gets the same share of the memory bandwidth
+        case 16: return tc::launch<16, 5>(mw, mx, p, splits, stream);
+        case 32: return tc::launch<32, 5>(mw, mx, p, splits, stream);
+        case 64: return tc::launch<64, 4>(mw, mx, p, splits, stream);
         case 128: return tc::launch<128, 6>(mw, mx, p, splits, stream);
         default: return tc::launch<256, 4>(mw, mx, p, splits, stream);
     }
 }
+
+// 1: later launches may start before the kernel before them in the stream has finished (programmatic dependent
+// launch); they read their weights at once and wait for that kernel before they touch anything else.  Every
+// kernel that runs between two such launches must itself call griddepcontrol.wait before its first access to
+// memory that another kernel writes.  0 (default): plain stream order.
+IB_EXPORT void ib_gemm_tcgen05_set_pdl(int on) { tc::g_pdl = on; }
 
 // The error word of the kernels above: 0, or the code of the first wait that ran out (1 producer, 2 MMA
 // issuer, 3 epilogue).  Reading it synchronises with the device; `reset` clears it.

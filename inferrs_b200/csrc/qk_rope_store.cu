@@ -19,6 +19,7 @@ __global__ void qk_norm_rope_store_kernel(
     const int* __restrict__ block_table, int max_pages, int page_size, int n_pages,
     act_t* __restrict__ k_pages, act_t* __restrict__ v_pages, act_t* __restrict__ q_out) {
     extern __shared__ float smem[];
+    ib_grid_dependency_sync();
     const int row = blockIdx.x;
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const int d = head_dim;
@@ -94,12 +95,12 @@ IB_EXPORT int ib_qk_norm_rope_store(const void* qkv, int row_stride, int n_rows,
     const int heads_total = n_heads + (store_kv ? 2 * n_kv_heads : 0);
     const dim3 grid(n_rows, (heads_total + QRS_WARPS - 1) / QRS_WARPS);
     if (weight_is_f32)
-        qk_norm_rope_store_kernel<float><<<grid, 32 * QRS_WARPS, smem, stream>>>(
+        ib_launch(qk_norm_rope_store_kernel<float>, grid, 32 * QRS_WARPS, smem, stream,
             (const act_t*)qkv, row_stride, n_heads, n_kv_heads, head_dim, store_kv, (const float*)q_weight,
             (const float*)k_weight, eps, cos_table, sin_table, rot_dim, positions, row_request, block_table,
             max_pages, page_size, n_pages, (act_t*)k_pages, (act_t*)v_pages, (act_t*)q_out);
     else
-        qk_norm_rope_store_kernel<__nv_bfloat16><<<grid, 32 * QRS_WARPS, smem, stream>>>(
+        ib_launch(qk_norm_rope_store_kernel<__nv_bfloat16>, grid, 32 * QRS_WARPS, smem, stream,
             (const act_t*)qkv, row_stride, n_heads, n_kv_heads, head_dim, store_kv, (const __nv_bfloat16*)q_weight,
             (const __nv_bfloat16*)k_weight, eps, cos_table, sin_table, rot_dim, positions, row_request, block_table,
             max_pages, page_size, n_pages, (act_t*)k_pages, (act_t*)v_pages, (act_t*)q_out);

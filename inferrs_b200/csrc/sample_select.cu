@@ -134,6 +134,7 @@ __global__ void __launch_bounds__(SMP_THREADS) sample_kernel(
     const int* __restrict__ top_k, const float* __restrict__ top_p, const float* __restrict__ min_p,
     const float* __restrict__ uniform, int* __restrict__ out) {
     __shared__ SmpShared sh;
+    ib_grid_dependency_sync();
     const int r = blockIdx.x;
     const float* row = logits + (long)r * ld;
     const float T = temperature[r];

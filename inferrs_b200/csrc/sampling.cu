@@ -6,6 +6,7 @@
 __global__ void argmax_kernel(const float* __restrict__ logits, int* __restrict__ out, int vocab, long ld) {
     __shared__ float best_v[32];
     __shared__ int best_i[32];
+    ib_grid_dependency_sync();
     const float* row = logits + (long)blockIdx.x * ld;
     float bv = -INFINITY;
     int bi = 0x7fffffff;
@@ -52,6 +53,7 @@ __device__ __forceinline__ unsigned long long argmax_pack(float v, int i) {
 __global__ void argmax_partial_kernel(const float* __restrict__ logits, unsigned long long* __restrict__ part,
                                       int vocab, long ld, int n_chunks) {
     __shared__ unsigned long long red[32];
+    ib_grid_dependency_sync();
     const float* row = logits + (long)blockIdx.x * ld;
     const int j0 = blockIdx.y * ARGMAX_CHUNK;
     const int j1 = j0 + ARGMAX_CHUNK < vocab ? j0 + ARGMAX_CHUNK : vocab;
@@ -82,6 +84,7 @@ __global__ void argmax_partial_kernel(const float* __restrict__ logits, unsigned
 }
 
 __global__ void argmax_final_kernel(const unsigned long long* __restrict__ part, int* __restrict__ out, int n_chunks) {
+    ib_grid_dependency_sync();
     unsigned long long best = 0;
     for (int c = threadIdx.x; c < n_chunks; c += 32) {
         const unsigned long long p = part[(long)blockIdx.x * n_chunks + c];
@@ -102,13 +105,13 @@ IB_EXPORT int ib_argmax(const float* logits, int* out, int n_rows, int vocab, lo
     if (vocab <= 0) return IB_ERR_ARGUMENT;
     const int n_chunks = (vocab + ARGMAX_CHUNK - 1) / ARGMAX_CHUNK;
     if (scratch != nullptr && n_chunks > 1) {
-        argmax_partial_kernel<<<dim3(n_rows, n_chunks), 512, 0, stream>>>(logits, (unsigned long long*)scratch, vocab,
-                                                                         ld, n_chunks);
-        argmax_final_kernel<<<n_rows, 32, 0, stream>>>((const unsigned long long*)scratch, out, n_chunks);
+        ib_launch(argmax_partial_kernel, dim3(n_rows, n_chunks), 512, 0, stream, logits, (unsigned long long*)scratch, vocab,
+                  ld, n_chunks);
+        ib_launch(argmax_final_kernel, n_rows, 32, 0, stream, (const unsigned long long*)scratch, out, n_chunks);
         return ib_launch_status();
     }
     const int threads = vocab >= 8192 ? 1024 : 256;
-    argmax_kernel<<<n_rows, threads, 0, stream>>>(logits, out, vocab, ld);
+    ib_launch(argmax_kernel, n_rows, threads, 0, stream, logits, out, vocab, ld);
     return ib_launch_status();
 }
 
@@ -121,6 +124,7 @@ IB_EXPORT int ib_argmax(const float* logits, int* out, int n_rows, int vocab, lo
 __global__ void penalties_kernel(float* __restrict__ logits, long ld, int vocab, const int* __restrict__ prev,
                                  int max_prev, const int* __restrict__ n_prev, const float* __restrict__ repetition,
                                  const float* __restrict__ frequency, const float* __restrict__ presence) {
+    ib_grid_dependency_sync();
     const int row = blockIdx.x;
     const int n = n_prev[row] < max_prev ? n_prev[row] : max_prev;
     const float rp = repetition[row], fp = frequency[row], pp = presence[row];

@@ -84,6 +84,8 @@ class DecodeGraphs:
         # once outside the capture: libraries initialise, the allocator warms up, and the step's keys are written
         r.model.forward(ctx)
         torch.cuda.synchronize()
+        # the captured launches may overlap their neighbours' ends (programmatic dependent launch)
+        kernels.set_pdl(True, r.rt.dtype)
         graph = torch.cuda.CUDAGraph()
         n0 = kernels.launch_count()
         # No Python object may be collected while the stream captures: the destructor of an older graph
@@ -95,6 +97,7 @@ class DecodeGraphs:
             with torch.cuda.graph(graph, pool=self.pool):
                 logits = r.model.forward(ctx)
         finally:
+            kernels.set_pdl(False, r.rt.dtype)
             if was_enabled:
                 gc.enable()
         launches = kernels.launch_count() - n0

@@ -307,6 +307,8 @@ def linear(x: torch.Tensor, w: torch.Tensor, out: torch.Tensor, act_dtype: torch
     """out = x @ w.T in the precision that ``act_dtype`` and the weight's own dtype ask for."""
     if act_dtype == torch.float32 or w.dtype == torch.float32:
         gemm_tn_simt(x, w, out, act_dtype)
+    elif x.shape[0] <= TCGEN05_MAX_TOKENS and tcgen05_gemm_supported(x, w):
+        gemm_tn_tcgen05(x, w, out)
     else:
         gemm_tn_bf16(x, w, out)
 
@@ -435,6 +437,13 @@ def _gemm_lib():
         lib.ib_gemm_tn_tcgen05.restype = c_int
         lib.ib_gemm_tcgen05_error.argtypes = [c_int]
         lib.ib_gemm_tcgen05_error.restype = c_int
+        lib.ib_gemm_tn_streamk.argtypes = [c_void_p, c_long, c_void_p, c_long, c_void_p, c_long, c_int, c_int, c_int,
+                                           c_int, c_void_p, c_void_p, c_int, c_void_p]
+        lib.ib_gemm_tn_streamk.restype = c_int
+        lib.ib_gemm_streamk_workspace_floats.argtypes = [c_int, c_int]
+        lib.ib_gemm_streamk_workspace_floats.restype = c_long
+        lib.ib_gemm_streamk_error.argtypes = [c_int]
+        lib.ib_gemm_streamk_error.restype = c_int
         _GEMM_LIB = lib
     return _GEMM_LIB
 
@@ -462,6 +471,70 @@ def gemm_tn_tcgen05(x: torch.Tensor, w: torch.Tensor, out: torch.Tensor, split_k
     _check(code, "gemm_tn_tcgen05")
 
 
+def gemm_tcgen05_set_pdl(on: bool):
+    """Let tcgen05 products start before their predecessor in the stream has finished (they prefetch weights and
+    wait for the predecessor before touching anything else).  Only safe among kernels that all wait likewise."""
+    _gemm_lib().ib_gemm_tcgen05_set_pdl(int(bool(on)))
+
+
+def set_pdl(on: bool, act_dtype: torch.dtype = torch.bfloat16):
+    """Programmatic dependent launch for every kernel of the package launched from now on: a kernel may start
+    while the one before it in the stream still runs, does what needs no input (barrier set-up, fetching
+    weights) and waits for the earlier kernel before it reads or writes anything else.  Used while a decode
+    step is captured into a CUDA graph; library kernels in between simply keep plain stream order."""
+    lib = _core(act_dtype)
+    lib.ib_set_pdl.argtypes = [c_int]
+    lib.ib_set_pdl.restype = None
+    lib.ib_set_pdl(int(bool(on)))
+    if act_dtype == torch.bfloat16:
+        gemm_tcgen05_set_pdl(on)
+
+
+TCGEN05_MAX_TOKENS = 8  # up to this many rows the own tcgen05 product is the faster one in a decode step
+
+
 def gemm_tcgen05_error(reset: bool = True) -> int:
     """0, or the code of the first bounded wait that ran out in a tcgen05 GEMM (synchronises with the device)."""
     return _gemm_lib().ib_gemm_tcgen05_error(int(reset))
+
+
+_STREAMK_WS = {}  # device index -> (partial sums, flags, number of SMs)
+
+
+def _streamk_workspace(device: torch.device, n_tok: int):
+    """The persistent product's workspace on this device: partial sums (grown on demand) and zeroed flags.
+    All launches on a device share it, so they must not overlap (the engine runs on one stream)."""
+    lib = _gemm_lib()
+    idx = device.index if device.index is not None else torch.cuda.current_device()
+    ws = _STREAMK_WS.get(idx)
+    sms = ws[2] if ws else torch.cuda.get_device_properties(idx).multi_processor_count
+    need = lib.ib_gemm_streamk_workspace_floats(n_tok, sms)
+    if ws is None or ws[0].numel() < need:
+        partial = torch.empty((need,), dtype=torch.float32, device=device)
+        flags = ws[1] if ws else torch.zeros((sms,), dtype=torch.int32, device=device)
+        ws = (partial, flags, sms)
+        _STREAMK_WS[idx] = ws
+    return ws
+
+
+def gemm_tn_streamk(x: torch.Tensor, w: torch.Tensor, out: torch.Tensor):
+    """out = x @ w.T by one persistent CTA per SM, each streaming an equal share of W through TMA into
+    tcgen05 MMAs (see csrc/gemm_streamk.cu).  Deterministic for a given shape."""
+    _need(x, "x", (torch.bfloat16,), 2)
+    _need(w, "w", (torch.bfloat16,), 2)
+    _need(out, "out", _W, 2)
+    n, k = x.shape
+    m = w.shape[0]
+    if w.shape[1] != k or out.shape != (n, m):
+        raise KernelError(f"gemm: x {tuple(x.shape)}, w {tuple(w.shape)}, out {tuple(out.shape)}")
+    partial, flags, sms = _streamk_workspace(x.device, n)
+    code = _gemm_lib().ib_gemm_tn_streamk(_p(x), k, _p(w), k, _p(out), m, int(out.dtype == torch.float32), n, m, k,
+                                          _p(partial), _p(flags), sms, _stream())
+    if code == -1:
+        raise KernelError(f"gemm_tn_streamk: K={k} must be a multiple of 8 and the bases 16-byte aligned")
+    _check(code, "gemm_tn_streamk")
+
+
+def gemm_streamk_error(reset: bool = True) -> int:
+    """0, or the code of the first bounded wait that ran out in a persistent product (synchronises)."""
+    return _gemm_lib().ib_gemm_streamk_error(int(reset))

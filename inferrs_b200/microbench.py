@@ -1,0 +1,178 @@
+"""Timing of single kernels at given sizes: the commands behind the summaries in ``profiles/``.
+
+    python -m inferrs_b200.microbench gemm --impl streamk --m 8 --n 6144 --k 4096
+    python -m inferrs_b200.microbench attention --form decode --batch 8 --context 2048
+    python -m inferrs_b200.microbench attention --form prefill --tokens 2048
+    python -m inferrs_b200.microbench chain --impl library --m 8 --layers 8
+
+Every case is timed with CUDA events after warm-up; between timed launches a buffer larger than the
+L2 cache is written, so each launch starts cold.  One JSON line per case.
+"""
+from __future__ import annotations
+
+import argparse
+import json
+import sys
+
+import torch
+
+from . import kernels
+
+
+def _time(fn, iters: int, flush: bool = True) -> float:
+    """Median microseconds of one call."""
+    for _ in range(3):
+        fn()
+    torch.cuda.synchronize()
+    scrub = torch.empty(256 * 1024 * 1024, dtype=torch.uint8, device="cuda") if flush else None
+    times = []
+    for _ in range(iters):
+        if scrub is not None:
+            scrub.zero_()
+        a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        a.record()
+        fn()
+        b.record()
+        torch.cuda.synchronize()
+        times.append(a.elapsed_time(b) * 1e3)
+    times.sort()
+    return times[len(times) // 2]
+
+
+def gemm(args) -> dict:
+    x = torch.randn(args.m, args.k, device="cuda").to(torch.bfloat16)
+    w = (torch.randn(args.n, args.k, device="cuda") * 0.02).to(torch.bfloat16)
+    out = torch.empty(args.m, args.n, dtype=torch.bfloat16, device="cuda")
+    fn = {"library": lambda: kernels.gemm_tn_bf16(x, w, out),
+          "tcgen05": lambda: kernels.gemm_tn_tcgen05(x, w, out, args.split_k),
+          "streamk": lambda: kernels.gemm_tn_streamk(x, w, out)}[args.impl]
+    us = _time(fn, args.iters)
+    ref = x.float() @ w.float().t()
+    err = float((out.float() - ref).abs().max() / ref.abs().max())
+    byts = 2 * (args.n * args.k + args.m * args.k + args.m * args.n)
+    flops = 2 * args.m * args.n * args.k
+    return {"kernel": f"gemm/{args.impl}", "m": args.m, "n": args.n, "k": args.k, "us": round(us, 2),
+            "GBps": round(byts / us / 1e3, 1), "TFLOPs": round(flops / us / 1e6, 1), "rel_err": err}
+
+
+def attention(args) -> dict:
+    nh, nkv, d, ps = args.heads, args.kv_heads, args.head_dim, args.page_size
+    dev = torch.device("cuda")
+    if args.form == "decode":
+        lens, new = [args.context] * args.batch, [1] * args.batch
+    else:
+        lens, new = [args.context_before + args.tokens], [args.tokens]
+    pages_per = [(n + ps - 1) // ps for n in lens]
+    n_pages = sum(pages_per)
+    table = torch.full((len(lens), max(pages_per)), -1, dtype=torch.int32)
+    perm = torch.randperm(n_pages).to(torch.int32)
+    at = 0
+    for r, n in enumerate(pages_per):
+        table[r, :n] = perm[at:at + n]
+        at += n
+    positions = torch.tensor([p for n, t in zip(lens, new) for p in range(n - t, n)], dtype=torch.int32, device=dev)
+    row_request = torch.tensor([r for r, t in enumerate(new) for _ in range(t)], dtype=torch.int32, device=dev)
+    q_start = torch.tensor([0] + list(torch.tensor(new).cumsum(0)), dtype=torch.int32, device=dev)
+    n = sum(new)
+    q = torch.randn(n, nh, d, device=dev).to(torch.bfloat16)
+    k_pages = torch.randn(n_pages, nkv, ps, d, device=dev).to(torch.bfloat16)
+    v_pages = torch.randn(n_pages, nkv, ps, d, device=dev).to(torch.bfloat16)
+    out = torch.empty(n, nh * d, dtype=torch.bfloat16, device=dev)
+    table = table.to(dev)
+    scale = d ** -0.5
+    if args.form == "decode":
+        splits = args.splits or kernels.decode_splits(args.batch, nkv, args.context)
+        fn = lambda: kernels.paged_attention_mma(q, k_pages, v_pages, table, row_request, q_start, n, q_start,  # noqa: E731
+                                                 positions, scale, None, out, True, splits)
+        byts = 2 * 2 * sum(lens) * nkv * d
+        flops = 4 * nh * d * sum(lens)
+        extra = {"batch": args.batch, "context": args.context, "splits": splits}
+    else:
+        tpt = kernels.MMA_KEYS // (nh // nkv)
+        req = [0] * ((args.tokens + tpt - 1) // tpt)
+        row0 = list(range(0, args.tokens, tpt))
+        tile_req = torch.tensor(req, dtype=torch.int32, device=dev)
+        tile_row0 = torch.tensor(row0, dtype=torch.int32, device=dev)
+        fn = lambda: kernels.paged_attention_mma(q, k_pages, v_pages, table, tile_req, tile_row0, len(req), q_start,  # noqa: E731
+                                                 positions, scale, None, out, False)
+        byts = 2 * 2 * lens[0] * nkv * d + 2 * 2 * n * nh * d
+        t, c = args.tokens, args.context_before
+        flops = 4 * nh * d * (t * c + t * (t + 1) // 2)
+        extra = {"tokens": args.tokens, "context_before": args.context_before}
+    us = _time(fn, args.iters)
+    return dict({"kernel": f"attention/{args.form}", "heads": nh, "kv_heads": nkv, "head_dim": d, "us": round(us, 2),
+                 "GBps": round(byts / us / 1e3, 1), "TFLOPs": round(flops / us / 1e6, 1)}, **extra)
+
+
+def chain(args) -> dict:
+    """The four projections of `layers` decoder layers back to back in one CUDA graph, every layer with weights
+    of its own: what a decode step pays for its matrix products, launch gaps and cold starts included."""
+    h, inner, qkv = args.hidden, args.inner, args.qkv
+    shapes = [(qkv, h), (h, args.attn_out), (2 * inner, h), (h, inner)]
+    ws = [[(torch.randn(n, k, device="cuda") * 0.02).to(torch.bfloat16) for n, k in shapes] for _ in range(args.layers)]
+    xs = [torch.randn(args.m, k, device="cuda").to(torch.bfloat16) for _, k in shapes]
+    outs = [torch.empty(args.m, n, dtype=torch.bfloat16, device="cuda") for n, _ in shapes]
+    fn = {"library": kernels.gemm_tn_bf16, "tcgen05": lambda x, w, o: kernels.gemm_tn_tcgen05(x, w, o, 0),
+          "streamk": kernels.gemm_tn_streamk}[args.impl]
+
+    def run():
+        for layer in ws:
+            for x, w, o in zip(xs, layer, outs):
+                fn(x, w, o)
+
+    if args.pdl:
+        kernels.gemm_tcgen05_set_pdl(True)
+    run()
+    torch.cuda.synchronize()
+    g = torch.cuda.CUDAGraph()
+    with torch.cuda.graph(g):
+        run()
+    us = _time(g.replay, args.iters, flush=False) / args.layers
+    byts = 2 * sum(n * k for n, k in shapes)
+    return {"kernel": f"gemm-chain/{args.impl}", "m": args.m, "layers": args.layers, "us_per_layer": round(us, 2),
+            "GBps": round(byts / us / 1e3, 1)}
+
+
+def main(argv=None) -> int:
+    ap = argparse.ArgumentParser(prog="inferrs_b200.microbench", description=__doc__,
+                                 formatter_class=argparse.RawDescriptionHelpFormatter)
+    sub = ap.add_subparsers(dest="what", required=True)
+    g = sub.add_parser("gemm")
+    g.add_argument("--impl", choices=["library", "tcgen05", "streamk"], default="streamk")
+    g.add_argument("--m", type=int, default=8)
+    g.add_argument("--n", type=int, default=6144)
+    g.add_argument("--k", type=int, default=4096)
+    g.add_argument("--split-k", type=int, default=0)
+    g.add_argument("--iters", type=int, default=20)
+    g.set_defaults(fn=gemm)
+    a = sub.add_parser("attention")
+    a.add_argument("--form", choices=["decode", "prefill"], default="decode")
+    a.add_argument("--batch", type=int, default=8)
+    a.add_argument("--context", type=int, default=2048)
+    a.add_argument("--tokens", type=int, default=2048)
+    a.add_argument("--context-before", type=int, default=0)
+    a.add_argument("--splits", type=int, default=0)
+    a.add_argument("--heads", type=int, default=32)
+    a.add_argument("--kv-heads", type=int, default=8)
+    a.add_argument("--head-dim", type=int, default=128)
+    a.add_argument("--page-size", type=int, default=16)
+    a.add_argument("--iters", type=int, default=20)
+    a.set_defaults(fn=attention)
+    c = sub.add_parser("chain")
+    c.add_argument("--impl", choices=["library", "tcgen05", "streamk"], default="library")
+    c.add_argument("--m", type=int, default=8)
+    c.add_argument("--layers", type=int, default=8)
+    c.add_argument("--hidden", type=int, default=4096)
+    c.add_argument("--inner", type=int, default=12288)
+    c.add_argument("--qkv", type=int, default=6144)
+    c.add_argument("--attn-out", type=int, default=4096)
+    c.add_argument("--iters", type=int, default=10)
+    c.add_argument("--pdl", action="store_true", help="tcgen05 only: programmatic dependent launch between the products")
+    c.set_defaults(fn=chain)
+    args = ap.parse_args(argv)
+    print(json.dumps(args.fn(args)))
+    return 0
+
+
+if __name__ == "__main__":
+    sys.exit(main())

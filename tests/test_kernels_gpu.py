@@ -301,3 +301,21 @@ def test_gemm_tn_tcgen05(n, m, k):
             assert K.gemm_tcgen05_error() == 0
             # float32 sums of up to 12,288 products of magnitude ~1: about 1e-5 of the largest result
             assert rel_err(out, ref) < (1e-2 if od == torch.bfloat16 else 3e-5), (od, split)
+
+
+@pytest.mark.parametrize("n,m,k", [(1, 4096, 4096), (8, 6144, 4096), (17, 300, 136), (64, 517, 96), (33, 128, 64),
+                                   (100, 1000, 512), (300, 384, 256), (16, 4096, 12288), (8, 20000, 1024),
+                                   (2, 128, 8192), (500, 4096, 512)])
+def test_gemm_tn_streamk(n, m, k):
+    from inferrs_b200 import kernels as K
+    x, w = rand((n, k), torch.bfloat16, 80), rand((m, k), torch.bfloat16, 81)
+    ref = x.double() @ w.double().t()
+    for od in (torch.bfloat16, torch.float32):
+        outs = []
+        for _ in range(3):   # the flags must be back at zero after every launch
+            out = torch.full((n, m), float("nan"), dtype=od, device=dev())
+            K.gemm_tn_streamk(x, w, out)
+            outs.append(out)
+        assert K.gemm_streamk_error() == 0
+        assert rel_err(outs[0], ref) < (1e-2 if od == torch.bfloat16 else 3e-5), od
+        assert torch.equal(outs[0], outs[1]) and torch.equal(outs[1], outs[2]), "the same shape must give the same bits"
