@@ -98,36 +98,44 @@ def build_context(entries: Sequence[StepEntry], manager: CacheManager, storage: 
     if not entries:
         raise BatchError("a step needs at least one entry")
     seen = set()
-    ids: List[int] = []
-    positions: List[int] = []
-    row_request: List[int] = []
+    id_parts, pos_parts, req_parts = [], [], []
     q_start = [0]
     kv_lens, slots, logit_rows, q_lens = [], [], [], []
     for r, e in enumerate(entries):
         if e.rid in seen:
             raise BatchError(f"request {e.rid!r} appears twice in one step")
         seen.add(e.rid)
-        toks = list(e.tokens)
-        if not toks:
+        try:
+            toks = np.asarray(e.tokens)
+        except (TypeError, ValueError):
+            raise BatchError(f"request {e.rid!r}: the tokens are not a list of integers") from None
+        if toks.ndim != 1 or toks.size == 0:
             raise BatchError(f"request {e.rid!r}: a step must bring at least one token")
+        if toks.dtype.kind not in "iu":
+            raise BatchError(f"request {e.rid!r}: token ids must be integers, got {toks.dtype}")
+        lo, hi = int(toks.min()), int(toks.max())
+        if lo < 0 or hi >= vocab_size:
+            bad = lo if lo < 0 else hi
+            raise BatchError(f"request {e.rid!r}: token id {bad!r} is outside the vocabulary of {vocab_size}")
+        n_tok = int(toks.size)
         held = manager.n_tokens(e.rid)
-        if held + len(toks) > max_positions:
-            raise BatchError(f"request {e.rid!r}: {held} + {len(toks)} tokens exceed the model's "
+        if held + n_tok > max_positions:
+            raise BatchError(f"request {e.rid!r}: {held} + {n_tok} tokens exceed the model's "
                              f"{max_positions} positions")
-        for t in toks:
-            if not (isinstance(t, (int, np.integer)) and 0 <= int(t) < vocab_size):
-                raise BatchError(f"request {e.rid!r}: token id {t!r} is outside the vocabulary of {vocab_size}")
         for w in e.want:
-            if not 0 <= int(w) < len(toks):
-                raise BatchError(f"request {e.rid!r}: wanted place {w} is outside its {len(toks)} tokens")
+            if not 0 <= int(w) < n_tok:
+                raise BatchError(f"request {e.rid!r}: wanted place {w} is outside its {n_tok} tokens")
             logit_rows.append(q_start[-1] + int(w))
-        ids.extend(int(t) for t in toks)
-        positions.extend(range(held, held + len(toks)))
-        row_request.extend([r] * len(toks))
-        q_start.append(q_start[-1] + len(toks))
-        q_lens.append(len(toks))
-        kv_lens.append(held + len(toks))
+        id_parts.append(toks.astype(np.int32, copy=False))
+        pos_parts.append(np.arange(held, held + n_tok, dtype=np.int32))
+        req_parts.append(np.full(n_tok, r, dtype=np.int32))
+        q_start.append(q_start[-1] + n_tok)
+        q_lens.append(n_tok)
+        kv_lens.append(held + n_tok)
         slots.append(manager.slot(e.rid))
+    ids = np.concatenate(id_parts).tolist() if pad_to is not None else None
+    positions = np.concatenate(pos_parts).tolist() if pad_to is not None else None
+    row_request = np.concatenate(req_parts).tolist() if pad_to is not None else None
     n_real = len(entries)
     if pad_to is not None:
         if any(q != 1 for q in q_lens) or len(entries) > pad_to:
@@ -144,7 +152,7 @@ def build_context(entries: Sequence[StepEntry], manager: CacheManager, storage: 
         logit_rows = list(range(pad_to))  # fixed shape: every row's logits are made, the caller picks
     else:
         wanted = None
-    n, nreq = len(ids), len(q_lens)
+    n, nreq = q_start[-1], len(q_lens)
     tables = []
     for g in range(len(manager.groups)):
         rows = [manager.block_table(e.rid, g) for e in entries]
@@ -158,8 +166,12 @@ def build_context(entries: Sequence[StepEntry], manager: CacheManager, storage: 
             arr[r, :len(t)] = t
         tables.append(arr)
     # one host buffer, one copy
-    parts = [np.asarray(ids, dtype=np.int32), np.asarray(positions, dtype=np.int32),
-             np.asarray(row_request, dtype=np.int32), np.asarray(q_start, dtype=np.int32),
+    if pad_to is not None:   # a short step of single tokens: plain lists, padded above
+        first = [np.asarray(ids, dtype=np.int32), np.asarray(positions, dtype=np.int32),
+                 np.asarray(row_request, dtype=np.int32)]
+    else:
+        first = [np.concatenate(id_parts), np.concatenate(pos_parts), np.concatenate(req_parts)]
+    parts = first + [np.asarray(q_start, dtype=np.int32),
              np.asarray(kv_lens, dtype=np.int32), np.asarray(slots, dtype=np.int32),
              np.asarray(logit_rows, dtype=np.int32)] + [t.reshape(-1) for t in tables]
     sizes = [p.size for p in parts]

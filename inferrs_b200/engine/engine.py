@@ -109,14 +109,14 @@ class Engine:
             return ended
         entries = []
         for e in plan:
-            toks = e.request.tokens[e.start:e.start + e.n]
-            entries.append(StepEntry(e.request.rid, toks, [e.n - 1] if e.samples else []))
+            entries.append(StepEntry(e.request.rid, e.request.token_slice(e.start, e.n),
+                                     [e.n - 1] if e.samples else []))
         logits = self.runner.step(entries, own_output=False)
         sampling = [e for e in plan if e.samples]
         tokens: List[int] = []
         if sampling:
             ids = self.sampler.sample(logits, [e.request.params for e in sampling],
-                                      [e.request.seed for e in sampling], [e.request.tokens for e in sampling])
+                                      [e.request.seed for e in sampling], [e.request for e in sampling])
             tokens = ids.cpu().tolist()
         self.n_steps += 1
         self.n_tokens_run += sum(e.n for e in plan)

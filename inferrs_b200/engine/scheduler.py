@@ -46,8 +46,29 @@ class Request:
         return self.prompt + self.output
 
     @property
+    def n_tokens(self) -> int:
+        return len(self.prompt) + len(self.output)
+
+    @property
     def n_pending(self) -> int:
         return len(self.prompt) + len(self.output) - self.n_computed
+
+    def token_slice(self, start: int, n: int) -> List[int]:
+        """tokens[start:start + n] without building the whole list."""
+        p = len(self.prompt)
+        if start >= p:
+            return self.output[start - p:start - p + n]
+        if start + n <= p:
+            return self.prompt[start:start + n]
+        return self.prompt[start:] + self.output[:start + n - p]
+
+    def tail(self, n: int) -> List[int]:
+        """The last n tokens (prompt and generated)."""
+        if n <= 0:
+            return []
+        if n <= len(self.output):
+            return self.output[-n:]
+        return self.prompt[-(n - len(self.output)):] + self.output
 
 
 @dataclass
@@ -136,22 +157,28 @@ class Scheduler:
         ended: List[Request] = []
         while True:
             budget = self.max_tokens_per_step
-            wants: Dict[Hashable, int] = {}
+            free = [pool.n_free for pool in self.manager.pools]   # pages left once the plan so far is served
             plan: List[PlannedEntry] = []
             starved: Optional[Request] = None
+
+            def fits(rid, n) -> bool:
+                need = self.manager.pages_needed(rid, n)
+                if any(need[g] > free[g] for g in range(len(free))):
+                    return False
+                for g in range(len(free)):
+                    free[g] -= need[g]
+                return True
+
             by_age = sorted(self.running, key=lambda r: r.order)
             # decoded tokens first, then portions of prompts, oldest first
             for r in [r for r in by_age if r.n_pending == 1] + [r for r in by_age if r.n_pending > 1]:
                 if budget <= 0:
                     break
                 n = min(r.n_pending, budget, self.prefill_chunk)
-                trial = dict(wants)
-                trial[r.rid] = n
-                if not self.manager.can_reserve(trial):
+                if not fits(r.rid, n):
                     starved = r
                     break
-                wants = trial
-                plan.append(PlannedEntry(r, r.n_computed, n, r.n_computed + n == len(r.prompt) + len(r.output)))
+                plan.append(PlannedEntry(r, r.n_computed, n, r.n_computed + n == r.n_tokens))
                 budget -= n
             if starved is not None:
                 if self._preempt_youngest(keep=starved):
@@ -168,15 +195,12 @@ class Scheduler:
                 r = self.waiting[0]
                 n = min(r.n_pending, budget, self.prefill_chunk)
                 self.manager.admit(r.rid)
-                trial = dict(wants)
-                trial[r.rid] = n
-                if not self.manager.can_reserve(trial):
+                if not fits(r.rid, n):
                     self.manager.release(r.rid)
                     break
                 self.waiting.popleft()
                 self.running.append(r)
-                wants = trial
-                plan.append(PlannedEntry(r, r.n_computed, n, r.n_computed + n == len(r.prompt) + len(r.output)))
+                plan.append(PlannedEntry(r, r.n_computed, n, r.n_computed + n == r.n_tokens))
                 budget -= n
             return plan, ended
 

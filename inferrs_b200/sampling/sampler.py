@@ -25,8 +25,9 @@ class Sampler:
         """int32 token ids [rows] (on the device) for float32 ``logits`` [rows, vocab].
 
         ``histories[r]`` is all tokens of row r's request so far, prompt and generated: its length is the
-        step index of the random draw and its tail is the penalties' window.  ``logits`` is changed in
-        place where penalties apply.
+        step index of the random draw and its tail is the penalties' window.  It may be a list of token ids
+        or an object with ``n_tokens`` and ``tail(n)`` (the scheduler's requests, which keep prompt and
+        output apart).  ``logits`` is changed in place where penalties apply.
         """
         r = logits.shape[0]
         out = torch.empty((r,), dtype=torch.int32, device=self.device)
@@ -35,13 +36,14 @@ class Sampler:
         if all(p.is_greedy and not p.has_penalty for p in params):
             kernels.argmax(logits, out, self.act_dtype)
             return out
+        length = [h.n_tokens if hasattr(h, "n_tokens") else len(h) for h in histories]
         if any(p.has_penalty for p in params):
-            width = max(1, max(min(p.repeat_last_n, len(h)) if p.has_penalty else 0 for p, h in zip(params, histories)))
+            width = max(1, max(min(p.repeat_last_n, n) if p.has_penalty else 0 for p, n in zip(params, length)))
             prev = np.full((r, width), -1, dtype=np.int32)
             n_prev = np.zeros((r,), dtype=np.int32)
             for i, (p, h) in enumerate(zip(params, histories)):
                 if p.has_penalty:
-                    tail = list(h[-p.repeat_last_n:])
+                    tail = h.tail(p.repeat_last_n) if hasattr(h, "tail") else list(h[-p.repeat_last_n:])
                     prev[i, :len(tail)] = tail
                     n_prev[i] = len(tail)
             f = np.array([[p.repetition_penalty if p.has_penalty else 1.0 for p in params],
@@ -51,7 +53,7 @@ class Sampler:
             kernels.penalties(logits, torch.from_numpy(prev).to(self.device), torch.from_numpy(n_prev).to(self.device),
                               fd[0], fd[1], fd[2], self.act_dtype)
         f = np.array([[p.temperature for p in params], [p.top_p for p in params], [p.min_p for p in params],
-                      [uniform_for(s, len(h)) for s, h in zip(seeds, histories)]], dtype=np.float32)
+                      [uniform_for(s, n) for s, n in zip(seeds, length)]], dtype=np.float32)
         fd = torch.from_numpy(f).to(self.device)
         top_k = torch.tensor([p.top_k for p in params], dtype=torch.int32).to(self.device)
         kernels.sample(logits, fd[0], top_k, fd[1], fd[2], fd[3], out, self.act_dtype)
