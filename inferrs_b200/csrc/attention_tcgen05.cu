@@ -1,0 +1,522 @@
+// Paged grouped-query attention for prompt portions on tcgen05 tensor cores (bfloat16, head size 128).
+//
+// One CTA owns 128 query rows of one key/value head: 128/G consecutive tokens of one request with the G
+// query heads that share the key/value head packed side by side (row = token * G + head).  Keys are
+// walked in tiles of 128 (whole pages).  Per tile:
+//   S  = Q K^T   one accumulator of 128 lanes x 128 columns in tensor memory (two of them, so that the
+//                product for the next tile is issued while this tile's softmax runs),
+//   P  = softmax step in registers: two threads per row (64 columns each) read the row of S with
+//                tcgen05.ld, keep the running maximum and sum in float32 and write exp2(S - max) as bfloat16
+//                into shared memory (two P tiles, used in turn),
+//   PV = P V     two more accumulators, used in turn; the row's threads add a tile's product into their
+//                float32 outputs one tile later, after rescaling them by the change of the maximum, so that
+//                the product runs while the next tile's softmax is computed.
+// Q, K and V arrive by TMA into 128-byte-swizzled tiles; K and V come page by page (a page of one head
+// is a contiguous [page_size, 128] block) into a two-stage ring.  V is used as the MN-major operand of
+// the second product, so no transposed copy of the cache is needed.
+//
+// Warps 0..7: softmax and output (warp w: lanes 32 (w % 4).., columns 64 (w / 4)..); warp 8: TMA producer;
+// warp 9: MMA issuer and owner of the tensor-memory allocation.  All mbarrier waits are bounded (about two seconds)
+// and report through the library's error word.
+#include <cuda.h>
+
+#include "common.cuh"
+
+#if IB_ACT_BF16
+
+namespace fa {
+
+constexpr int D = 128;            // head size
+constexpr int ROWS = 128;         // query rows per CTA
+constexpr int KEYS = 128;         // keys per tile
+constexpr int THREADS = 320;
+constexpr int SOFTMAX_THREADS = 256;
+constexpr int HALF_BYTES = 128 * 128;          // a [128 rows][64 elements] swizzled sub-tile
+constexpr int TILE_BYTES = 2 * HALF_BYTES;     // Q, K, V or P tile: 128 x 128 bfloat16
+
+__device__ int g_error = 0;
+
+__device__ __forceinline__ unsigned smem_u32(const void* p) { return (unsigned)__cvta_generic_to_shared(p); }
+__device__ __forceinline__ void mbar_init(unsigned bar, unsigned count) {
+    asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(bar), "r"(count));
+}
+__device__ __forceinline__ void mbar_expect_tx(unsigned bar, unsigned bytes) {
+    asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(bar), "r"(bytes) : "memory");
+}
+__device__ __forceinline__ void mbar_arrive(unsigned bar) {
+    asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(bar) : "memory");
+}
+__device__ __forceinline__ bool mbar_try_wait(unsigned bar, unsigned parity) {
+    unsigned ok;
+    asm volatile("{\n\t.reg .pred p;\n\tmbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\tselp.u32 %0, 1, 0, p;\n\t}"
+                 : "=r"(ok) : "r"(bar), "r"(parity) : "memory");
+    return ok != 0;
+}
+__device__ __forceinline__ unsigned long long global_ns() {
+    unsigned long long t;
+    asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t));
+    return t;
+}
+__device__ __noinline__ bool mbar_wait(unsigned bar, unsigned parity, int code) {
+    if (mbar_try_wait(bar, parity)) return true;
+    const unsigned long long t0 = global_ns();
+    for (unsigned it = 1;; ++it) {
+        if (mbar_try_wait(bar, parity)) return true;
+        if ((it & 1023u) == 0 && global_ns() - t0 > 2000000000ull) {
+            atomicCAS(&g_error, 0, code);
+            return false;
+        }
+    }
+}
+__device__ __forceinline__ void tma_load_2d(unsigned dst, const CUtensorMap* map, int x, int y, unsigned bar) {
+    asm volatile("cp.async.bulk.tensor.2d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4}], [%2];"
+                 ::"r"(dst), "l"(map), "r"(bar), "r"(x), "r"(y) : "memory");
+}
+__device__ __forceinline__ void tma_load_3d(unsigned dst, const CUtensorMap* map, int x, int y, int z, unsigned bar) {
+    asm volatile("cp.async.bulk.tensor.3d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4, %5}], [%2];"
+                 ::"r"(dst), "l"(map), "r"(bar), "r"(x), "r"(y), "r"(z) : "memory");
+}
+// K-major tile (rows of 128 bytes, 128-byte swizzle, 8-row groups 1024 bytes apart)
+__device__ __forceinline__ unsigned long long desc_k_major(unsigned addr) {
+    unsigned long long d = 0;
+    d |= (unsigned long long)((addr & 0x3FFFF) >> 4);
+    d |= (unsigned long long)1 << 16;
+    d |= (unsigned long long)(1024 >> 4) << 32;
+    d |= (unsigned long long)1 << 46;
+    d |= (unsigned long long)2 << 61;
+    return d;
+}
+// MN-major tile: [k rows][64 elements of the MN dimension] per 128-byte row, 128-byte swizzle; 8-row groups of the
+// K dimension are 1024 bytes apart (stride offset), 64-element groups of the MN dimension `mn_group_bytes` apart
+// (leading offset).
+__device__ __forceinline__ unsigned long long desc_mn_major(unsigned addr, unsigned mn_group_bytes) {
+    unsigned long long d = 0;
+    d |= (unsigned long long)((addr & 0x3FFFF) >> 4);
+    d |= (unsigned long long)((mn_group_bytes >> 4) & 0x3FFF) << 16;
+    d |= (unsigned long long)(1024 >> 4) << 32;
+    d |= (unsigned long long)1 << 46;
+    d |= (unsigned long long)2 << 61;
+    return d;
+}
+__device__ __forceinline__ void umma(unsigned tmem_d, unsigned long long a, unsigned long long b, unsigned idesc,
+                                     unsigned accumulate) {
+    asm volatile("{\n\t.reg .pred p;\n\tsetp.ne.b32 p, %4, 0;\n\t"
+                 "tcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, {%5, %6, %7, %8}, p;\n\t}"
+                 ::"r"(tmem_d), "l"(a), "l"(b), "r"(idesc), "r"(accumulate), "r"(0), "r"(0), "r"(0), "r"(0) : "memory");
+}
+__device__ __forceinline__ void umma_commit(unsigned bar) {
+    asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(bar) : "memory");
+}
+__device__ __forceinline__ void tmem_ld16(unsigned taddr, float (&v)[16]) {
+    unsigned r[16];
+    asm volatile("tcgen05.ld.sync.aligned.32x32b.x16.b32 {%0,%1,%2,%3,%4,%5,%6,%7,%8,%9,%10,%11,%12,%13,%14,%15}, [%16];"
+                 : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7]),
+                   "=r"(r[8]), "=r"(r[9]), "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]), "=r"(r[14]), "=r"(r[15])
+                 : "r"(taddr));
+    asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
+#pragma unroll
+    for (int i = 0; i < 16; ++i) v[i] = __uint_as_float(r[i]);
+}
+__device__ __forceinline__ void tmem_ld32_issue(unsigned taddr, unsigned (&r)[32]) {
+    asm volatile("tcgen05.ld.sync.aligned.32x32b.x32.b32 "
+                 "{%0,%1,%2,%3,%4,%5,%6,%7,%8,%9,%10,%11,%12,%13,%14,%15,%16,%17,%18,%19,%20,%21,%22,%23,%24,%25,%26,%27,%28,%29,%30,%31}, [%32];"
+                 : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7]),
+                   "=r"(r[8]), "=r"(r[9]), "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]), "=r"(r[14]), "=r"(r[15]),
+                   "=r"(r[16]), "=r"(r[17]), "=r"(r[18]), "=r"(r[19]), "=r"(r[20]), "=r"(r[21]), "=r"(r[22]), "=r"(r[23]),
+                   "=r"(r[24]), "=r"(r[25]), "=r"(r[26]), "=r"(r[27]), "=r"(r[28]), "=r"(r[29]), "=r"(r[30]), "=r"(r[31])
+                 : "r"(taddr));
+}
+__device__ __forceinline__ void tmem_ld_wait() { asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory"); }
+__device__ __forceinline__ void softmax_sync() { asm volatile("bar.sync 1, 256;" ::: "memory"); }  // warps 0..7
+__device__ __forceinline__ void fence_before() { asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory"); }
+__device__ __forceinline__ void fence_after() { asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory"); }
+__device__ __forceinline__ float ex2(float x) {   // 2^x, one instruction; 2^-inf = 0
+    float y;
+    asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
+    return y;
+}
+__device__ __forceinline__ unsigned pack_bf16(float lo, float hi) {
+    __nv_bfloat162 v = __floats2bfloat162_rn(lo, hi);
+    return *reinterpret_cast<unsigned*>(&v);
+}
+
+struct Params {
+    const int* block_table;   // [R, max_pages]
+    const int* tile_req;      // [tiles]
+    const int* tile_row0;     // [tiles] first token row of the tile
+    const int* q_start;       // [R + 1]
+    const int* positions;     // [N]
+    __nv_bfloat16* out;       // [N, n_heads * 128]
+    int max_pages, page_size, n_pages, n_heads, n_kv_heads, window;
+    float scale_log2;
+};
+
+__global__ void __launch_bounds__(THREADS, 1) attention_kernel(const __grid_constant__ CUtensorMap map_q,
+                                                               const __grid_constant__ CUtensorMap map_k,
+                                                               const __grid_constant__ CUtensorMap map_v,
+                                                               const Params P) {
+    extern __shared__ unsigned char raw_smem[];
+    unsigned char* smem = reinterpret_cast<unsigned char*>((reinterpret_cast<uintptr_t>(raw_smem) + 1023) & ~(uintptr_t)1023);
+    unsigned char* sq = smem;                       // Q tile
+    unsigned char* sp = sq + TILE_BYTES;            // P tiles, used in turn
+    unsigned char* sk = sp + 2 * TILE_BYTES;        // K tiles, two stages
+    unsigned char* sv = sk + 2 * TILE_BYTES;        // V tiles, two stages
+    unsigned long long* bars = reinterpret_cast<unsigned long long*>(sv + 2 * TILE_BYTES);
+    const unsigned q_full = smem_u32(bars), k_full0 = smem_u32(bars + 1), k_empty0 = smem_u32(bars + 3);
+    const unsigned v_full0 = smem_u32(bars + 5), v_empty0 = smem_u32(bars + 7);
+    const unsigned s_full0 = smem_u32(bars + 9), s_empty0 = smem_u32(bars + 11);
+    const unsigned p_full0 = smem_u32(bars + 13), pv_full0 = smem_u32(bars + 15);
+    unsigned* tmem_slot = reinterpret_cast<unsigned*>(bars + 17);
+    float* xchg = reinterpret_cast<float*>(bars + 18);   // [2 halves][128 rows]: row maxima, later row sums
+
+    ib_grid_dependency_sync();
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    // the last tiles of a prompt see the most keys: they are started first, so that the grid's tail is short
+    const int tile = gridDim.x - 1 - blockIdx.x, kvh = blockIdx.y;
+    const int req = P.tile_req[tile], row0 = P.tile_row0[tile];
+    const int G = P.n_heads / P.n_kv_heads;
+    const int tpt = ROWS / G;                       // tokens per tile
+    int n_tok = P.q_start[req + 1] - row0;
+    if (n_tok > tpt) n_tok = tpt;
+    const int p0 = P.positions[row0];
+    const int pmax = p0 + n_tok - 1;
+    const int lo_min = (P.window > 0 && p0 - P.window + 1 > 0) ? p0 - P.window + 1 : 0;
+    const int t_begin = lo_min / KEYS, t_end = pmax / KEYS + 1;   // key tiles
+    const int n_tiles = t_end - t_begin;
+
+    if (threadIdx.x == 0) {
+        mbar_init(q_full, 1);
+        for (int s = 0; s < 2; ++s) {
+            mbar_init(k_full0 + 8 * s, 1); mbar_init(k_empty0 + 8 * s, 1);
+            mbar_init(v_full0 + 8 * s, 1); mbar_init(v_empty0 + 8 * s, 1);
+            mbar_init(s_full0 + 8 * s, 1); mbar_init(s_empty0 + 8 * s, 8);
+            mbar_init(p_full0 + 8 * s, 8); mbar_init(pv_full0 + 8 * s, 1);
+        }
+        asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+    }
+    if (warp == 9) {
+        asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(tmem_slot)), "r"(512) : "memory");
+        asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
+    }
+    fence_before();
+    __syncthreads();
+    fence_after();
+    const unsigned tmem = *tmem_slot;      // columns 0..127 S0, 128..255 S1, 256..383 PV0, 384..511 PV1
+    bool ok = true;
+
+    if (warp == 8) {
+        // TMA producer.  Lane 0 brings the queries; lane p brings page p of every key tile (four boxes: two
+        // 64-column halves of K and of V), and looks the page up one tile ahead of its use.
+        if (lane == 0) {
+            mbar_expect_tx(q_full, TILE_BYTES);   // [tokens][G heads][128] as two 64-column halves
+            tma_load_3d(smem_u32(sq), &map_q, 0, kvh * G, row0, q_full);
+            tma_load_3d(smem_u32(sq + HALF_BYTES), &map_q, 64, kvh * G, row0, q_full);
+        }
+        const int* bt = P.block_table + (long)req * P.max_pages;
+        const int pages_per_tile = KEYS / P.page_size;   // at most 16
+        auto lookup = [&](int i) -> int {
+            if (lane >= pages_per_tile) return 0;
+            const int j = (t_begin + i) * KEYS + lane * P.page_size;
+            int page = (j <= pmax && j / P.page_size < P.max_pages) ? bt[j / P.page_size] : -1;
+            if (page < 0 || page >= P.n_pages) page = 0;   // never seen by a query; any finite data will do
+            return page;
+        };
+        // Keys run one tile ahead of values: K(i) is free again as soon as the scores of tile i - 2 are done,
+        // V(i) only after the second product of tile i - 2, and the scores of a tile are issued a tile early.
+        auto load_tile = [&](int i, int page, bool keys) {
+            const int s = i & 1;
+            const unsigned full = (keys ? k_full0 : v_full0) + 8 * s;
+            if (lane == 0) mbar_expect_tx(full, TILE_BYTES);
+            __syncwarp();
+            if (lane < pages_per_tile) {
+                const int grow = (page * P.n_kv_heads + kvh) * P.page_size;
+                const unsigned off = (unsigned)(lane * P.page_size) * 128u;
+                unsigned char* dst = (keys ? sk : sv) + s * TILE_BYTES;
+                tma_load_2d(smem_u32(dst) + off, keys ? &map_k : &map_v, 0, grow, full);
+                tma_load_2d(smem_u32(dst + HALF_BYTES) + off, keys ? &map_k : &map_v, 64, grow, full);
+            }
+        };
+        // order: K(0), then for every i: K(i + 1), V(i)
+        int page_k = n_tiles > 0 ? lookup(0) : 0;
+        if (n_tiles > 0) load_tile(0, page_k, true);
+        int page_v = page_k;
+        for (int i = 0; i < n_tiles; ++i) {
+            if (i + 1 < n_tiles) {
+                page_k = lookup(i + 1);
+                if (i + 1 >= 2 && ok && !mbar_wait(k_empty0 + 8 * ((i + 1) & 1), (((i + 1) >> 1) - 1) & 1, 1)) ok = false;
+                ok = __all_sync(0xffffffffu, ok);
+                if (!ok) break;
+                load_tile(i + 1, page_k, true);
+            }
+            if (i >= 2 && ok && !mbar_wait(v_empty0 + 8 * (i & 1), ((i >> 1) - 1) & 1, 1)) ok = false;
+            ok = __all_sync(0xffffffffu, ok);
+            if (!ok) break;
+            load_tile(i, page_v, false);
+            page_v = page_k;
+        }
+    } else if (warp == 9) {
+        if (lane == 0) {
+            // both products: M = 128, N = 128, bfloat16 in, float32 out; the second takes V as MN-major B
+            const unsigned idesc_qk = (1u << 4) | (1u << 7) | (1u << 10) | ((unsigned)(KEYS >> 3) << 17) | ((unsigned)(ROWS >> 4) << 24);
+            const unsigned idesc_pv = idesc_qk | (1u << 16);
+            auto issue_qk = [&](int i) {   // S(i) = Q K(i)^T into buffer i & 1
+                const int s = i & 1;
+#pragma unroll
+                for (int k = 0; k < D / 16; ++k) {
+                    const unsigned off = (k >> 2) * HALF_BYTES + (k & 3) * 32;
+                    umma(tmem + s * 128, desc_k_major(smem_u32(sq) + off), desc_k_major(smem_u32(sk + s * TILE_BYTES) + off),
+                         idesc_qk, k != 0);
+                }
+                umma_commit(s_full0 + 8 * s);
+                umma_commit(k_empty0 + 8 * s);   // K(i) is free once these products are done
+            };
+            if (n_tiles > 0) {
+                ok = mbar_wait(q_full, 0, 2) && mbar_wait(k_full0, 0, 2);
+                fence_after();
+                if (ok) issue_qk(0);
+            }
+            for (int i = 0; i < n_tiles && ok; ++i) {
+                const int s = i & 1;
+                if (i + 1 < n_tiles) {     // the next tile's scores, while this tile's softmax runs
+                    const int s1 = (i + 1) & 1;
+                    if (!mbar_wait(k_full0 + 8 * s1, ((i + 1) >> 1) & 1, 2)) { ok = false; break; }
+                    if (i + 1 >= 2 && !mbar_wait(s_empty0 + 8 * s1, (((i + 1) >> 1) - 1) & 1, 3)) { ok = false; break; }
+                    fence_after();
+                    issue_qk(i + 1);
+                }
+                if (!mbar_wait(p_full0 + 8 * s, (i >> 1) & 1, 4)) { ok = false; break; }
+                if (!mbar_wait(v_full0 + 8 * s, (i >> 1) & 1, 2)) { ok = false; break; }
+                fence_after();
+#pragma unroll
+                for (int k = 0; k < KEYS / 16; ++k) {
+                    const unsigned aoff = (k >> 2) * HALF_BYTES + (k & 3) * 32;   // P: K-major, 16 keys = 32 bytes
+                    const unsigned boff = k * 16 * 128;                            // V: 16 key rows further
+                    umma(tmem + 256 + s * 128, desc_k_major(smem_u32(sp + s * TILE_BYTES) + aoff),
+                         desc_mn_major(smem_u32(sv + s * TILE_BYTES) + boff, HALF_BYTES), idesc_pv, k != 0);
+                }
+                umma_commit(pv_full0 + 8 * s);
+                umma_commit(v_empty0 + 8 * s);    // V(i) is free once these products are done
+            }
+        }
+    } else if (warp < 8) {
+        // softmax and output: two threads per row of the tile; this one has columns 64 * ch .. 64 * ch + 63
+        const int ch = warp >> 2;
+        const int r = (warp & 3) * 32 + lane;
+        const int ti = r / G, g = r - ti * G;
+        const bool row_valid = ti < n_tok;
+        const int pos = row_valid ? p0 + ti : -1;
+        const int lo = (row_valid && P.window > 0 && pos - P.window + 1 > 0) ? pos - P.window + 1 : 0;
+        float o[64];
+#pragma unroll
+        for (int e = 0; e < 64; ++e) o[e] = 0.0f;
+        float m = -INFINITY, l = 0.0f, corr_pending = 1.0f;
+        const unsigned lane_addr = (unsigned)((warp & 3) * 32) << 16;
+        auto add_product = [&](int i, float corr) {   // o = o * corr + (P V)(i), this thread's 64 columns
+            unsigned a[32], b[32];
+            tmem_ld32_issue(tmem + lane_addr + 256 + (i & 1) * 128 + ch * 64, a);
+            tmem_ld32_issue(tmem + lane_addr + 256 + (i & 1) * 128 + ch * 64 + 32, b);
+            tmem_ld_wait();
+#pragma unroll
+            for (int j = 0; j < 32; ++j) {
+                o[j] = o[j] * corr + __uint_as_float(a[j]);
+                o[32 + j] = o[32 + j] * corr + __uint_as_float(b[j]);
+            }
+        };
+        // After a wait has run out the loop goes on without waiting, so that every thread still meets the
+        // others at the named barriers the same number of times; the output is not stored then.
+        for (int i = 0; i < n_tiles; ++i) {
+            const int s = i & 1;
+            if (ok && !mbar_wait(s_full0 + 8 * s, (i >> 1) & 1, 5)) ok = false;
+            fence_after();
+            const int key0 = (t_begin + i) * KEYS + ch * 64;
+            unsigned a[32], b[32];
+            tmem_ld32_issue(tmem + lane_addr + s * 128 + ch * 64, a);
+            tmem_ld32_issue(tmem + lane_addr + s * 128 + ch * 64 + 32, b);
+            tmem_ld_wait();
+            // a tile whose 64 keys this row sees in full needs no comparisons (all tiles but the first and last few)
+            const bool all_visible = key0 >= lo && key0 + 63 <= pos;
+            float mx = -INFINITY;
+            if (all_visible) {
+#pragma unroll
+                for (int j = 0; j < 32; ++j) mx = fmaxf(mx, fmaxf(__uint_as_float(a[j]), __uint_as_float(b[j])));
+            } else {
+#pragma unroll
+                for (int j = 0; j < 32; ++j) {
+                    const int ka = key0 + j, kb = key0 + 32 + j;
+                    if (!(ka >= lo && ka <= pos)) a[j] = 0xff800000u;   // -inf
+                    if (!(kb >= lo && kb <= pos)) b[j] = 0xff800000u;
+                    mx = fmaxf(mx, fmaxf(__uint_as_float(a[j]), __uint_as_float(b[j])));
+                }
+            }
+            // the row's maximum over both halves (raw scores; the scale is positive)
+            xchg[ch * 128 + r] = mx;
+            softmax_sync();
+            mx = fmaxf(mx, xchg[(ch ^ 1) * 128 + r]) * P.scale_log2;
+            const float m_new = fmaxf(m, mx);
+            const float m_safe = m_new == -INFINITY ? 0.0f : m_new;
+            const float corr = m == -INFINITY ? 0.0f : ex2(m - m_safe);
+            float sum = 0.0f;
+            unsigned char* prow = sp + s * TILE_BYTES + ch * HALF_BYTES + r * 128;
+#pragma unroll
+            for (int c = 0; c < 8; ++c) {
+                float p[8];
+#pragma unroll
+                for (int j = 0; j < 8; ++j) {
+                    const int e = 8 * c + j;
+                    const float x = __uint_as_float(e < 32 ? a[e] : b[e - 32]);
+                    p[j] = ex2(fmaf(x, P.scale_log2, -m_safe));   // exp2(-inf) = 0 for keys that are not seen
+                    sum += p[j];
+                }
+                uint4 w;
+                w.x = pack_bf16(p[0], p[1]); w.y = pack_bf16(p[2], p[3]);
+                w.z = pack_bf16(p[4], p[5]); w.w = pack_bf16(p[6], p[7]);
+                *reinterpret_cast<uint4*>(prow + ((c ^ (r & 7)) << 4)) = w;
+            }
+            l = l * corr + sum;
+            m = m_new;
+            // S(i) has been read and P(i) written: tell the MMA issuer (one arrival per warp)
+            fence_before();
+            asm volatile("fence.proxy.async.shared::cta;" ::: "memory");   // generic writes -> the tensor core's reads
+            __syncwarp();
+            if (lane == 0) { mbar_arrive(s_empty0 + 8 * s); mbar_arrive(p_full0 + 8 * s); }
+            // the product of the tile before this one has had this tile's softmax to finish
+            if (i > 0) {
+                if (ok && !mbar_wait(pv_full0 + 8 * ((i - 1) & 1), ((i - 1) >> 1) & 1, 6)) ok = false;
+                fence_after();
+                add_product(i - 1, corr_pending);
+                fence_before();
+            }
+            corr_pending = corr;
+            softmax_sync();   // xchg is written again in the next iteration
+        }
+        if (ok && n_tiles > 0) {
+            const int i = n_tiles - 1;
+            if (mbar_wait(pv_full0 + 8 * (i & 1), (i >> 1) & 1, 6)) {
+                fence_after();
+                add_product(i, corr_pending);
+                fence_before();
+            } else {
+                ok = false;
+            }
+        }
+        // the row's sum over both halves
+        xchg[ch * 128 + r] = l;
+        softmax_sync();
+        l += xchg[(ch ^ 1) * 128 + r];
+        if (row_valid && ok) {
+            const float inv = l > 0.0f ? 1.0f / l : 0.0f;
+            __nv_bfloat16* dst = P.out + ((long)(row0 + ti) * P.n_heads + kvh * G + g) * D + ch * 64;
+#pragma unroll
+            for (int c0 = 0; c0 < 64; c0 += 8) {
+                uint4 w;
+                w.x = pack_bf16(o[c0] * inv, o[c0 + 1] * inv); w.y = pack_bf16(o[c0 + 2] * inv, o[c0 + 3] * inv);
+                w.z = pack_bf16(o[c0 + 4] * inv, o[c0 + 5] * inv); w.w = pack_bf16(o[c0 + 6] * inv, o[c0 + 7] * inv);
+                *reinterpret_cast<uint4*>(dst + c0) = w;
+            }
+        }
+    }
+
+    if (!ok || g_error != 0) {
+        const unsigned long long t0 = global_ns();
+        while (global_ns() - t0 < 2000000ull) __nanosleep(1000);
+    }
+    fence_before();
+    __syncthreads();
+    if (warp == 9) {
+        fence_after();
+        asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem), "r"(512) : "memory");
+    }
+}
+
+typedef CUresult (*EncodeTiled)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*, const cuuint64_t*,
+                                const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave, CUtensorMapSwizzle,
+                                CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+
+static EncodeTiled encode_fn() {
+    static EncodeTiled fn = nullptr;
+    if (fn == nullptr) {
+        void* sym = nullptr;
+        cudaDriverEntryPointQueryResult q;
+        if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &sym, cudaEnableDefault, &q) == cudaSuccess &&
+            q == cudaDriverEntryPointSuccess)
+            fn = reinterpret_cast<EncodeTiled>(sym);
+    }
+    return fn;
+}
+
+}  // namespace fa
+
+// Prefill-form attention for head size 128, bfloat16: tile i holds up to 128/G tokens of request tile_req[i]
+// from row tile_row0[i].  Same arguments and results as ib_paged_attention_mma with decode_form = 0.
+IB_EXPORT int ib_paged_attention_tcgen05(const void* q, const void* k_pages, const void* v_pages, const int* block_table,
+                                         int max_pages, int page_size, int n_pages, const int* tile_req,
+                                         const int* tile_row0, int n_tiles, const int* q_start, const int* positions,
+                                         int n_rows, int n_heads, int n_kv_heads, int head_dim, float scale, int window,
+                                         void* out, cudaStream_t stream) {
+    if (n_tiles <= 0) return IB_OK;
+    if (n_heads <= 0 || n_kv_heads <= 0 || n_heads % n_kv_heads || page_size <= 0 || max_pages <= 0) return IB_ERR_ARGUMENT;
+    const int G = n_heads / n_kv_heads;
+    if (head_dim != fa::D || fa::KEYS % page_size || page_size < 8 || fa::ROWS % G) return IB_ERR_UNSUPPORTED;
+    if (!(scale > 0.0f)) return IB_ERR_UNSUPPORTED;   // the row maximum is taken before the scale is applied
+    fa::EncodeTiled enc = fa::encode_fn();
+    if (enc == nullptr) return IB_ERR_UNSUPPORTED;
+    CUtensorMap mq, mk, mv;
+    {
+        // q [n_rows tokens][n_heads][128]: boxes of [128/G tokens][G heads][64]
+        const cuuint64_t dims[3] = {128, (cuuint64_t)n_heads, (cuuint64_t)n_rows};
+        const cuuint64_t strides[2] = {128 * 2, (cuuint64_t)n_heads * 128 * 2};
+        const cuuint32_t box[3] = {64, (cuuint32_t)G, (cuuint32_t)(fa::ROWS / G)};
+        const cuuint32_t elem[3] = {1, 1, 1};
+        if (enc(&mq, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 3, const_cast<void*>(q), dims, strides, box, elem,
+                CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+                CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) != CUDA_SUCCESS)
+            return IB_ERR_UNSUPPORTED;
+    }
+    for (int which = 0; which < 2; ++which) {
+        // pages [n_pages * n_kv_heads * page_size rows][128]: boxes of [page_size][64]
+        const cuuint64_t dims[2] = {128, (cuuint64_t)n_pages * n_kv_heads * page_size};
+        const cuuint64_t strides[1] = {128 * 2};
+        const cuuint32_t box[2] = {64, (cuuint32_t)page_size};
+        const cuuint32_t elem[2] = {1, 1};
+        if (enc(which ? &mv : &mk, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, const_cast<void*>(which ? v_pages : k_pages), dims,
+                strides, box, elem, CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B,
+                CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) != CUDA_SUCCESS)
+            return IB_ERR_UNSUPPORTED;
+    }
+    fa::Params P;
+    P.block_table = block_table; P.tile_req = tile_req; P.tile_row0 = tile_row0; P.q_start = q_start;
+    P.positions = positions; P.out = (__nv_bfloat16*)out; P.max_pages = max_pages; P.page_size = page_size;
+    P.n_pages = n_pages; P.n_heads = n_heads; P.n_kv_heads = n_kv_heads; P.window = window;
+    P.scale_log2 = scale * 1.4426950408889634f;
+    const size_t smem = 7 * fa::TILE_BYTES + 18 * 8 + 2 * 128 * 4 + 1024;
+    static bool configured = false;
+    if (!configured) {
+        cudaError_t e = cudaFuncSetAttribute(fa::attention_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+        if (e != cudaSuccess) return (int)e;
+        configured = true;
+    }
+    ib_launch(fa::attention_kernel, dim3(n_tiles, n_kv_heads), fa::THREADS, smem, stream, mq, mk, mv, P);
+    return ib_launch_status();
+}
+
+IB_EXPORT int ib_attention_tcgen05_error(int reset) {
+    int v = 0;
+    if (cudaMemcpyFromSymbol(&v, fa::g_error, sizeof(int)) != cudaSuccess) return -1;
+    if (reset && v != 0) {
+        const int zero = 0;
+        cudaMemcpyToSymbol(fa::g_error, &zero, sizeof(int));
+    }
+    return v;
+}
+
+#else  // the float32 build has no tensor-core attention
+
+IB_EXPORT int ib_paged_attention_tcgen05(const void*, const void*, const void*, const int*, int, int, int, const int*,
+                                         const int*, int, const int*, const int*, int, int, int, int, float, int, void*,
+                                         cudaStream_t) {
+    return IB_ERR_UNSUPPORTED;
+}
+
+IB_EXPORT int ib_attention_tcgen05_error(int) { return 0; }
+
+#endif

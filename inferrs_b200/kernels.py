@@ -36,6 +36,10 @@ _SIGNATURES = {
     "ib_paged_attention_mma": [c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_void_p, c_void_p, c_int,
                                c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_float, c_int, c_void_p, c_int, c_int,
                                c_void_p, c_void_p, c_void_p],
+    "ib_paged_attention_tcgen05": [c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_void_p, c_void_p,
+                                   c_int, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_float, c_int, c_void_p,
+                                   c_void_p],
+    "ib_attention_tcgen05_error": [c_int],
     "ib_argmax": [c_void_p, c_void_p, c_int, c_int, c_long, c_void_p, c_void_p],
     "ib_penalties": [c_void_p, c_long, c_int, c_int, c_void_p, c_int, c_void_p, c_void_p, c_void_p, c_void_p,
                      c_void_p],
@@ -367,6 +371,46 @@ def paged_attention_mma(q: torch.Tensor, k_pages: torch.Tensor, v_pages: torch.T
         _p(out), int(decode_form), int(n_splits), _p(part_o), _p(part_ml), _stream()), "paged_attention_mma")
 
 
+TC_ROWS = 128  # query rows per tile of the tcgen05 attention kernel
+
+
+def tcgen05_attention_supported(dtype: torch.dtype, n_heads: int, n_kv_heads: int, head_dim: int, page_size: int) -> bool:
+    g = n_heads // max(n_kv_heads, 1)
+    return (dtype == torch.bfloat16 and head_dim == 128 and page_size >= 8 and 128 % page_size == 0
+            and n_heads % n_kv_heads == 0 and TC_ROWS % g == 0)
+
+
+def paged_attention_tcgen05(q: torch.Tensor, k_pages: torch.Tensor, v_pages: torch.Tensor, block_table: torch.Tensor,
+                            tile_req: torch.Tensor, tile_row0: torch.Tensor, n_tiles: int, q_start: torch.Tensor,
+                            positions: torch.Tensor, scale: float, window: Optional[int], out: torch.Tensor):
+    """Attention of prompt portions on tcgen05 tensor cores (bfloat16, head_dim 128): tile i holds up to
+    128/G tokens of request tile_req[i] from row tile_row0[i]; Q, K, V by TMA, scores and P V in tensor memory."""
+    bf = (torch.bfloat16,)
+    _need(q, "q", bf, 3)
+    _need(k_pages, "k_pages", bf, 4)
+    _need(v_pages, "v_pages", bf, 4)
+    _need(out, "out", bf, 2)
+    _need(block_table, "block_table", _I, 2)
+    for name, t in (("tile_req", tile_req), ("tile_row0", tile_row0), ("q_start", q_start), ("positions", positions)):
+        _need(t, name, _I, 1)
+    n, nh, d = q.shape
+    n_pages, nkv, page_size, dk = k_pages.shape
+    if dk != d or v_pages.shape != k_pages.shape or out.shape != (n, nh * d):
+        raise KernelError(f"paged_attention_tcgen05: q {tuple(q.shape)}, pages {tuple(k_pages.shape)}, out {tuple(out.shape)}")
+    if not tcgen05_attention_supported(q.dtype, nh, nkv, d, page_size):
+        raise KernelError(f"paged_attention_tcgen05 takes head_dim 128, a page size of 8..128 that divides 128 and a "
+                          f"group size that divides 128; got head_dim {d}, page size {page_size}, {nh}/{nkv} heads")
+    _check(_core(torch.bfloat16).ib_paged_attention_tcgen05(
+        _p(q), _p(k_pages), _p(v_pages), _p(block_table), block_table.shape[1], page_size, n_pages, _p(tile_req),
+        _p(tile_row0), n_tiles, _p(q_start), _p(positions), n, nh, nkv, d, float(scale), int(window) if window else 0,
+        _p(out), _stream()), "paged_attention_tcgen05")
+
+
+def attention_tcgen05_error(reset: bool = True) -> int:
+    """0, or the code of the first bounded wait that ran out in the tcgen05 attention kernel (synchronises)."""
+    return _core(torch.bfloat16).ib_attention_tcgen05_error(int(reset))
+
+
 def paged_attention(q: torch.Tensor, k_pages: torch.Tensor, v_pages: torch.Tensor, block_table: torch.Tensor,
                     ctx, scale: float, window: Optional[int], out: torch.Tensor):
     """Attention of every row of the step over its request's pages; picks the kernel for the sizes.
@@ -384,6 +428,10 @@ def paged_attention(q: torch.Tensor, k_pages: torch.Tensor, v_pages: torch.Tenso
         splits = decode_splits(ctx.n_requests, nkv, ctx.max_kv_len)
         paged_attention_mma(q, k_pages, v_pages, block_table, ctx.row_request, ctx.q_start, ctx.n_requests,
                             ctx.q_start, ctx.positions, scale, window, out, True, splits)
+    elif tcgen05_attention_supported(q.dtype, nh, nkv, d, page_size):
+        tile_req, tile_row0, n_tiles = ctx.attention_tiles(TC_ROWS // (nh // nkv))
+        paged_attention_tcgen05(q, k_pages, v_pages, block_table, tile_req, tile_row0, n_tiles, ctx.q_start,
+                                ctx.positions, scale, window, out)
     else:
         tile_req, tile_row0, n_tiles = ctx.attention_tiles(MMA_KEYS // (nh // nkv))
         paged_attention_mma(q, k_pages, v_pages, block_table, tile_req, tile_row0, n_tiles, ctx.q_start,

@@ -88,19 +88,23 @@ def attention(args) -> dict:
         flops = 4 * nh * d * sum(lens)
         extra = {"batch": args.batch, "context": args.context, "splits": splits}
     else:
-        tpt = kernels.MMA_KEYS // (nh // nkv)
+        tpt = (kernels.TC_ROWS if args.impl == "tcgen05" else kernels.MMA_KEYS) // (nh // nkv)
         req = [0] * ((args.tokens + tpt - 1) // tpt)
         row0 = list(range(0, args.tokens, tpt))
         tile_req = torch.tensor(req, dtype=torch.int32, device=dev)
         tile_row0 = torch.tensor(row0, dtype=torch.int32, device=dev)
-        fn = lambda: kernels.paged_attention_mma(q, k_pages, v_pages, table, tile_req, tile_row0, len(req), q_start,  # noqa: E731
-                                                 positions, scale, None, out, False)
+        if args.impl == "tcgen05":
+            fn = lambda: kernels.paged_attention_tcgen05(q, k_pages, v_pages, table, tile_req, tile_row0, len(req),  # noqa: E731
+                                                         q_start, positions, scale, None, out)
+        else:
+            fn = lambda: kernels.paged_attention_mma(q, k_pages, v_pages, table, tile_req, tile_row0, len(req),  # noqa: E731
+                                                     q_start, positions, scale, None, out, False)
         byts = 2 * 2 * lens[0] * nkv * d + 2 * 2 * n * nh * d
         t, c = args.tokens, args.context_before
         flops = 4 * nh * d * (t * c + t * (t + 1) // 2)
         extra = {"tokens": args.tokens, "context_before": args.context_before}
     us = _time(fn, args.iters)
-    return dict({"kernel": f"attention/{args.form}", "heads": nh, "kv_heads": nkv, "head_dim": d, "us": round(us, 2),
+    return dict({"kernel": f"attention/{args.form}" + (f"/{args.impl}" if args.form == "prefill" else ""), "heads": nh, "kv_heads": nkv, "head_dim": d, "us": round(us, 2),
                  "GBps": round(byts / us / 1e3, 1), "TFLOPs": round(flops / us / 1e6, 1)}, **extra)
 
 
@@ -147,6 +151,7 @@ def main(argv=None) -> int:
     g.set_defaults(fn=gemm)
     a = sub.add_parser("attention")
     a.add_argument("--form", choices=["decode", "prefill"], default="decode")
+    a.add_argument("--impl", choices=["mma", "tcgen05"], default="tcgen05", help="prefill form: which kernel")
     a.add_argument("--batch", type=int, default=8)
     a.add_argument("--context", type=int, default=2048)
     a.add_argument("--tokens", type=int, default=2048)
