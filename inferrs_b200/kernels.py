@@ -40,6 +40,9 @@ _SIGNATURES = {
                                    c_int, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_float, c_int, c_void_p,
                                    c_void_p],
     "ib_attention_tcgen05_error": [c_int],
+    "ib_paged_attention_decode": [c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_void_p, c_int, c_int,
+                                  c_int, c_int, c_float, c_int, c_void_p, c_int, c_void_p, c_void_p, c_void_p, c_void_p],
+    "ib_attention_decode_error": [c_int],
     "ib_argmax": [c_void_p, c_void_p, c_int, c_int, c_long, c_void_p, c_void_p],
     "ib_penalties": [c_void_p, c_long, c_int, c_int, c_void_p, c_int, c_void_p, c_void_p, c_void_p, c_void_p,
                      c_void_p],
@@ -371,6 +374,75 @@ def paged_attention_mma(q: torch.Tensor, k_pages: torch.Tensor, v_pages: torch.T
         _p(out), int(decode_form), int(n_splits), _p(part_o), _p(part_ml), _stream()), "paged_attention_mma")
 
 
+_DECODE_COUNTERS = {}  # device index -> zeroed int32 counters of the decode attention kernel
+
+
+def tma_decode_attention_supported(dtype: torch.dtype, n_heads: int, n_kv_heads: int, head_dim: int, page_size: int) -> bool:
+    return (dtype == torch.bfloat16 and head_dim == 128 and page_size >= 8 and MMA_KEYS % page_size == 0
+            and n_heads % n_kv_heads == 0 and n_heads // n_kv_heads <= 16)
+
+
+DECODE_RESIDENT_CTAS = 296  # two CTAs of the decode attention kernel fit on each of the 148 SMs
+
+
+def decode_max_splits(n_requests: int, n_kv_heads: int, max_kv_len: int) -> int:
+    """Upper bound of the slices per request that the decode kernel's grid provides (the kernel itself uses no more
+    than the request's real length gives four tiles to).  Few requests: as many slices as still run as one wave
+    of resident CTAs, because a CTA's fixed start-up cost is paid once per wave.  Many requests: the number of
+    slices (up to 8) whose last wave is fullest."""
+    tiles = max(1, (max_kv_len + MMA_KEYS - 1) // MMA_KEYS)
+    pairs = max(1, n_requests * n_kv_heads)
+    most = max(1, (tiles + 3) // 4)
+    if pairs <= DECODE_RESIDENT_CTAS:
+        return max(1, min(most, DECODE_RESIDENT_CTAS // pairs))
+    best, best_eff = 1, 0.0
+    for s in range(1, min(most, 8) + 1):
+        waves = pairs * s / DECODE_RESIDENT_CTAS
+        eff = waves / -(-pairs * s // DECODE_RESIDENT_CTAS)
+        if eff > best_eff + 1e-9:
+            best, best_eff = s, eff
+    return best
+
+
+def paged_attention_decode(q: torch.Tensor, k_pages: torch.Tensor, v_pages: torch.Tensor, block_table: torch.Tensor,
+                           positions: torch.Tensor, scale: float, window: Optional[int], out: torch.Tensor,
+                           max_splits: int):
+    """Attention of one new token per request (row r = request r) over its pages: TMA-fed key/value tiles, split
+    over the keys, merged by the slice that finishes last (bfloat16, head_dim 128)."""
+    bf = (torch.bfloat16,)
+    _need(q, "q", bf, 3)
+    _need(k_pages, "k_pages", bf, 4)
+    _need(v_pages, "v_pages", bf, 4)
+    _need(out, "out", bf, 2)
+    _need(block_table, "block_table", _I, 2)
+    _need(positions, "positions", _I, 1)
+    n, nh, d = q.shape
+    n_pages, nkv, page_size, dk = k_pages.shape
+    if dk != d or v_pages.shape != k_pages.shape or out.shape != (n, nh * d) or block_table.shape[0] < n:
+        raise KernelError(f"paged_attention_decode: q {tuple(q.shape)}, pages {tuple(k_pages.shape)}, out {tuple(out.shape)}")
+    if not tma_decode_attention_supported(q.dtype, nh, nkv, d, page_size):
+        raise KernelError(f"paged_attention_decode takes head_dim 128, a page size of 8..64 that divides 64 and at most "
+                          f"16 query heads per key/value head; got head_dim {d}, page size {page_size}, {nh}/{nkv} heads")
+    idx = q.device.index if q.device.index is not None else torch.cuda.current_device()
+    counters = _DECODE_COUNTERS.get(idx)
+    if counters is None or counters.numel() < n * nkv:
+        counters = torch.zeros((max(65536, n * nkv),), dtype=torch.int32, device=q.device)
+        _DECODE_COUNTERS[idx] = counters
+    part_o = part_ml = None
+    if max_splits > 1:
+        part_o = torch.empty((n, nh, max_splits, d), dtype=torch.float32, device=q.device)
+        part_ml = torch.empty((n, nh, max_splits, 2), dtype=torch.float32, device=q.device)
+    _check(_core(torch.bfloat16).ib_paged_attention_decode(
+        _p(q), _p(k_pages), _p(v_pages), _p(block_table), block_table.shape[1], page_size, n_pages, _p(positions), n,
+        nh, nkv, d, float(scale), int(window) if window else 0, _p(out), int(max_splits), _p(part_o), _p(part_ml),
+        _p(counters), _stream()), "paged_attention_decode")
+
+
+def attention_decode_error(reset: bool = True) -> int:
+    """0, or the code of the first bounded wait that ran out in the decode attention kernel (synchronises)."""
+    return _core(torch.bfloat16).ib_attention_decode_error(int(reset))
+
+
 TC_ROWS = 128  # query rows per tile of the tcgen05 attention kernel
 
 
@@ -423,7 +495,10 @@ def paged_attention(q: torch.Tensor, k_pages: torch.Tensor, v_pages: torch.Tenso
     if not mma_attention_supported(q.dtype, nh, nkv, d, page_size):
         paged_attention_generic(q, k_pages, v_pages, block_table, ctx.row_request, ctx.positions, scale, window, out)
         return
-    if ctx.decode_only:
+    if ctx.decode_only and tma_decode_attention_supported(q.dtype, nh, nkv, d, page_size):
+        paged_attention_decode(q, k_pages, v_pages, block_table, ctx.positions, scale, window, out,
+                               decode_max_splits(ctx.n_requests, nkv, ctx.max_kv_len))
+    elif ctx.decode_only:
         # one row per request: the rows are the tiles
         splits = decode_splits(ctx.n_requests, nkv, ctx.max_kv_len)
         paged_attention_mma(q, k_pages, v_pages, block_table, ctx.row_request, ctx.q_start, ctx.n_requests,

@@ -81,9 +81,14 @@ def attention(args) -> dict:
     table = table.to(dev)
     scale = d ** -0.5
     if args.form == "decode":
-        splits = args.splits or kernels.decode_splits(args.batch, nkv, args.context)
-        fn = lambda: kernels.paged_attention_mma(q, k_pages, v_pages, table, row_request, q_start, n, q_start,  # noqa: E731
-                                                 positions, scale, None, out, True, splits)
+        if args.impl == "mma":
+            splits = args.splits or kernels.decode_splits(args.batch, nkv, args.context)
+            fn = lambda: kernels.paged_attention_mma(q, k_pages, v_pages, table, row_request, q_start, n, q_start,  # noqa: E731
+                                                     positions, scale, None, out, True, splits)
+        else:
+            splits = args.splits or kernels.decode_max_splits(args.batch, nkv, args.max_context or args.context)
+            fn = lambda: kernels.paged_attention_decode(q, k_pages, v_pages, table, positions, scale, None, out,  # noqa: E731
+                                                        splits)
         byts = 2 * 2 * sum(lens) * nkv * d
         flops = 4 * nh * d * sum(lens)
         extra = {"batch": args.batch, "context": args.context, "splits": splits}
@@ -151,12 +156,13 @@ def main(argv=None) -> int:
     g.set_defaults(fn=gemm)
     a = sub.add_parser("attention")
     a.add_argument("--form", choices=["decode", "prefill"], default="decode")
-    a.add_argument("--impl", choices=["mma", "tcgen05"], default="tcgen05", help="prefill form: which kernel")
+    a.add_argument("--impl", choices=["mma", "tcgen05"], default="tcgen05", help="which kernel (decode form: mma = cp.async kernel, tcgen05 = TMA-fed kernel)")
     a.add_argument("--batch", type=int, default=8)
     a.add_argument("--context", type=int, default=2048)
     a.add_argument("--tokens", type=int, default=2048)
     a.add_argument("--context-before", type=int, default=0)
     a.add_argument("--splits", type=int, default=0)
+    a.add_argument("--max-context", type=int, default=0, help="decode form: the context that the grid is sized for")
     a.add_argument("--heads", type=int, default=32)
     a.add_argument("--kv-heads", type=int, default=8)
     a.add_argument("--head-dim", type=int, default=128)

@@ -349,3 +349,32 @@ def test_paged_attention_tcgen05(nh, nkv, ps, window):
     got = out[new[0] - 1].view(nh, d).float()
     want = v_pages[page, :, slot, :].float().repeat_interleave(nh // nkv, dim=0)
     assert rel_err(got, want) < 5e-2, "the far key that stands out was not seen"
+
+
+@pytest.mark.parametrize("nh,nkv,ps,window,max_splits", [(8, 2, 16, None, 1), (32, 8, 16, None, 9), (4, 4, 8, 50, 3),
+                                                          (16, 1, 32, None, 40), (6, 2, 64, 129, 2), (32, 8, 16, None, 64)])
+def test_paged_attention_decode(nh, nkv, ps, window, max_splits):
+    from inferrs_b200 import kernels as K
+    dtype, d = torch.bfloat16, 128
+    lens = [300, 17, 64, 1, 65, 1000, 2049, 513]
+    new = [1] * len(lens)
+    table, positions, row_request, k_pages, v_pages = _paged_setup(dtype, nkv, d, ps, lens, new, 30)
+    n = len(lens)
+    q = rand((n, nh, d), dtype, 33)
+    far = 5 if window is None else lens[5] - window
+    page, slot = int(table[5, far // ps]), far % ps
+    k_pages[page, :, slot, :] = 0
+    k_pages[page, :, slot, 0] = 16.0
+    q[5, :, :] = 0
+    q[5, :, 0] = 16.0
+    ref = torch.empty((n, nh * d), dtype=dtype, device=dev())
+    scale = d ** -0.5 * 4
+    R.paged_attention_generic(q, k_pages, v_pages, table, row_request, positions, scale, window, ref)
+    for _ in range(2):   # the counters must be back at zero after a launch
+        out = torch.full((n, nh * d), float("nan"), dtype=dtype, device=dev())
+        K.paged_attention_decode(q, k_pages, v_pages, table, positions, scale, window, out, max_splits)
+        assert K.attention_decode_error() == 0
+        assert rel_err(out, ref) < 2e-2
+    got = out[5].view(nh, d).float()
+    want = v_pages[page, :, slot, :].float().repeat_interleave(nh // nkv, dim=0)
+    assert rel_err(got, want) < 5e-2, "the far key that stands out was not seen"
