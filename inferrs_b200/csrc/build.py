@@ -162,6 +162,12 @@ def build_library(name: str, force: bool = False, ptxas_verbose: bool = False) -
     link = [nvcc, "-shared"] + ARCH_FLAGS + ["-o", tmp] + objs + lib["link"]
     _run_with_heartbeat([link], f"{name} (link)", False)
     os.replace(tmp, final)
+    for old in os.listdir(out_dir):   # builds of earlier source states of this library
+        if old.startswith(name + ".") and old.endswith(".so") and old != os.path.basename(final):
+            try:
+                os.remove(os.path.join(out_dir, old))
+            except OSError:
+                pass
     for o in objs:
         try:
             os.remove(o)
