@@ -74,7 +74,9 @@ __global__ void add_rms_norm_kernel(float* __restrict__ residual, const act_t* _
     }
 }
 
-// Four elements per thread and step (16-byte loads of the residual), for widths that are multiples of 4.
+// Four elements per thread and step (16-byte loads of the residual), for widths that are multiples of 4 and
+// at most 4 * NORM_KEEP * (threads per block).
+#define NORM_KEEP 4
 struct alignas(8) ActVec4 { act_t v[4]; };
 template <typename WT> struct alignas(sizeof(WT) * 4) WVec4 { WT v[4]; };
 
@@ -90,28 +92,33 @@ __global__ void add_rms_norm_vec4_kernel(float* __restrict__ residual, const act
     const ActVec4* del = delta ? reinterpret_cast<const ActVec4*>(delta + (size_t)src * width) : nullptr;
     const bool write_back = (rows == nullptr) && (del != nullptr);
     const int n4 = width >> 2;
+    // the row stays in registers between the two passes (the host picks a block size that makes it fit)
+    float4 keep[NORM_KEEP];
     float ss = 0.0f;
-    for (int j = threadIdx.x; j < n4; j += blockDim.x) {
-        float4 v = res[j];
-        if (del) {
-            const ActVec4 d = del[j];
-            v.x += ib_to_float(d.v[0]); v.y += ib_to_float(d.v[1]);
-            v.z += ib_to_float(d.v[2]); v.w += ib_to_float(d.v[3]);
+#pragma unroll
+    for (int k = 0; k < NORM_KEEP; ++k) {
+        const int j = threadIdx.x + k * blockDim.x;
+        if (j < n4) {
+            float4 v = res[j];
+            if (del) {
+                const ActVec4 d = del[j];
+                v.x += ib_to_float(d.v[0]); v.y += ib_to_float(d.v[1]);
+                v.z += ib_to_float(d.v[2]); v.w += ib_to_float(d.v[3]);
+            }
+            if (write_back) res[j] = v;
+            ss += v.x * v.x + v.y * v.y + v.z * v.z + v.w * v.w;
+            keep[k] = v;
         }
-        if (write_back) res[j] = v;
-        ss += v.x * v.x + v.y * v.y + v.z * v.z + v.w * v.w;
     }
     ss = ib_block_sum(ss, red);
     const float inv = 1.0f / sqrtf(ss / (float)width + eps);
     ActVec4* dst = reinterpret_cast<ActVec4*>(out + (size_t)r * width);
     const WVec4<WT>* w4 = reinterpret_cast<const WVec4<WT>*>(weight);
-    for (int j = threadIdx.x; j < n4; j += blockDim.x) {
-        float4 v = res[j];  // this thread's own write, if there was one
-        if (del && !write_back) {
-            const ActVec4 d = del[j];
-            v.x += ib_to_float(d.v[0]); v.y += ib_to_float(d.v[1]);
-            v.z += ib_to_float(d.v[2]); v.w += ib_to_float(d.v[3]);
-        }
+#pragma unroll
+    for (int k = 0; k < NORM_KEEP; ++k) {
+        const int j = threadIdx.x + k * blockDim.x;
+        if (j >= n4) break;
+        const float4 v = keep[k];
         const WVec4<WT> w = w4[j];
         ActVec4 o;
         o.v[0] = ib_from_float<act_t>(v.x * inv * ib_to_float(w.v[0]));
@@ -131,8 +138,11 @@ IB_EXPORT int ib_add_rms_norm(float* residual, const void* delta, const void* we
     int threads = 128;
     if (width >= 2048) threads = 512;
     else if (width >= 512) threads = 256;
-    if ((width & 3) == 0 && ib_aligned16(residual) && ib_aligned16(delta) && ib_aligned16(weight) && ib_aligned16(out)) {
-        const int t4 = width >= 4096 ? 256 : 128;
+    if ((width & 3) == 0 && width <= 4 * NORM_KEEP * 1024 && ib_aligned16(residual) && ib_aligned16(delta) &&
+        ib_aligned16(weight) && ib_aligned16(out)) {
+        int t4 = 128;   // enough threads that NORM_KEEP float4 per thread hold the row
+        while (4 * NORM_KEEP * t4 < width) t4 <<= 1;
+        if (width >= 4096 && t4 < 256) t4 = 256;
         if (weight_is_f32)
             ib_launch(add_rms_norm_vec4_kernel<float>, n_rows, t4, 0, stream, residual, (const act_t*)delta,
                       (const float*)weight, (act_t*)out, rows, width, eps);
@@ -164,6 +174,30 @@ __global__ void silu_gate_kernel(const act_t* __restrict__ gate_up, act_t* __res
     }
 }
 
+#if IB_ACT_BF16
+// Eight bfloat16 (16 bytes) per thread and step, for inner sizes that are multiples of 8.
+__global__ void silu_gate_vec8_kernel(const act_t* __restrict__ gate_up, act_t* __restrict__ out, int inner, long total8) {
+    ib_grid_dependency_sync();
+    const int in8 = inner >> 3;
+    for (long i = (long)blockIdx.x * blockDim.x + threadIdx.x; i < total8; i += (long)gridDim.x * blockDim.x) {
+        const long r = i / in8;
+        const int j = (int)(i - r * in8);
+        const uint4 g = reinterpret_cast<const uint4*>(gate_up + r * 2 * inner)[j];
+        const uint4 u = reinterpret_cast<const uint4*>(gate_up + r * 2 * inner + inner)[j];
+        const __nv_bfloat162* gp = reinterpret_cast<const __nv_bfloat162*>(&g);
+        const __nv_bfloat162* up = reinterpret_cast<const __nv_bfloat162*>(&u);
+        uint4 o;
+        __nv_bfloat162* op = reinterpret_cast<__nv_bfloat162*>(&o);
+#pragma unroll
+        for (int k = 0; k < 4; ++k) {
+            const float2 gv = __bfloat1622float2(gp[k]), uv = __bfloat1622float2(up[k]);
+            op[k] = __floats2bfloat162_rn(gv.x / (1.0f + expf(-gv.x)) * uv.x, gv.y / (1.0f + expf(-gv.y)) * uv.y);
+        }
+        reinterpret_cast<uint4*>(out + r * inner)[j] = o;
+    }
+}
+#endif
+
 // Four elements per thread and step, for inner sizes that are multiples of 4.
 __global__ void silu_gate_vec4_kernel(const act_t* __restrict__ gate_up, act_t* __restrict__ out, int inner, long total4) {
     ib_grid_dependency_sync();
@@ -187,6 +221,15 @@ IB_EXPORT int ib_silu_gate(const void* gate_up, void* out, int n_rows, int inner
     if (n_rows <= 0) return IB_OK;
     if (inner <= 0) return IB_ERR_ARGUMENT;
     const long total = (long)n_rows * inner;
+#if IB_ACT_BF16
+    if ((inner & 7) == 0 && ib_aligned16(gate_up) && ib_aligned16(out)) {
+        const long total8 = total >> 3;
+        long b8 = (total8 + 255) / 256;
+        if (b8 > 148L * 32) b8 = 148L * 32;
+        ib_launch(silu_gate_vec8_kernel, (int)b8, 256, 0, stream, (const act_t*)gate_up, (act_t*)out, inner, total8);
+        return ib_launch_status();
+    }
+#endif
     if ((inner & 3) == 0 && ib_aligned16(gate_up) && ib_aligned16(out)) {
         const long total4 = total >> 2;
         long b4 = (total4 + 255) / 256;

@@ -80,6 +80,66 @@ __global__ void qk_norm_rope_store_kernel(
     }
 }
 
+#if IB_ACT_BF16
+// Head size 128 rotated in full, bfloat16: one warp per (row, head), lane l holds elements 4l..4l+3 and gets the
+// elements 64 further (or nearer) from lane l ^ 16; no shared memory.
+template <typename WT>
+__global__ void qk_norm_rope_store_d128_kernel(
+    const __nv_bfloat16* __restrict__ qkv, int row_stride, int n_heads, int n_kv_heads, int store_kv,
+    const WT* __restrict__ q_weight, const WT* __restrict__ k_weight, float eps,
+    const float* __restrict__ cos_table, const float* __restrict__ sin_table,
+    const int* __restrict__ positions, const int* __restrict__ row_request,
+    const int* __restrict__ block_table, int max_pages, int page_size, int n_pages,
+    __nv_bfloat16* __restrict__ k_pages, __nv_bfloat16* __restrict__ v_pages, __nv_bfloat16* __restrict__ q_out) {
+    ib_grid_dependency_sync();
+    const int row = blockIdx.x;
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const int heads_total = n_heads + (store_kv ? 2 * n_kv_heads : 0);
+    const int head = blockIdx.y * QRS_WARPS + warp;
+    if (head >= heads_total) return;
+    const int kind = head < n_heads ? 0 : (head < n_heads + n_kv_heads ? 1 : 2);
+    const int pos = positions[row];
+    const uint2 raw = *reinterpret_cast<const uint2*>(qkv + (long)row * row_stride + (long)head * 128 + 4 * lane);
+    const float2 x01 = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(&raw.x));
+    const float2 x23 = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(&raw.y));
+    float x[4] = {x01.x, x01.y, x23.x, x23.y};
+    __nv_bfloat16* dst;
+    if (kind == 0) {
+        dst = q_out + ((long)row * n_heads + head) * 128;
+    } else {
+        const int req = row_request[row];
+        const int page = block_table[(long)req * max_pages + pos / page_size];
+        if (page < 0 || page >= n_pages) return;
+        const int kvh = head - n_heads - (kind == 2 ? n_kv_heads : 0);
+        dst = (kind == 1 ? k_pages : v_pages) + (((long)page * n_kv_heads + kvh) * page_size + (pos % page_size)) * 128;
+    }
+    if (kind != 2) {
+        const WT* w = kind == 0 ? q_weight : k_weight;
+        if (w != nullptr) {
+            float ss = x[0] * x[0] + x[1] * x[1] + x[2] * x[2] + x[3] * x[3];
+            ss = ib_warp_sum(ss);
+            const float inv = 1.0f / sqrtf(ss / 128.0f + eps);
+#pragma unroll
+            for (int e = 0; e < 4; ++e) x[e] = x[e] * inv * ib_to_float(w[4 * lane + e]);
+        }
+        // element i < 64 pairs with i + 64: lanes 0..15 hold the first halves, lanes 16..31 the second
+        const int i0 = 4 * (lane & 15);
+        const float4 c = *reinterpret_cast<const float4*>(cos_table + (long)pos * 64 + i0);
+        const float4 s = *reinterpret_cast<const float4*>(sin_table + (long)pos * 64 + i0);
+        const float cs[4] = {c.x, c.y, c.z, c.w}, sn[4] = {s.x, s.y, s.z, s.w};
+#pragma unroll
+        for (int e = 0; e < 4; ++e) {
+            const float other = __shfl_xor_sync(0xffffffffu, x[e], 16);
+            x[e] = lane < 16 ? x[e] * cs[e] - other * sn[e] : other * sn[e] + x[e] * cs[e];
+        }
+    }
+    uint2 o;
+    *reinterpret_cast<__nv_bfloat162*>(&o.x) = __floats2bfloat162_rn(x[0], x[1]);
+    *reinterpret_cast<__nv_bfloat162*>(&o.y) = __floats2bfloat162_rn(x[2], x[3]);
+    *reinterpret_cast<uint2*>(dst + 4 * lane) = o;
+}
+#endif
+
 IB_EXPORT int ib_qk_norm_rope_store(const void* qkv, int row_stride, int n_rows, int n_heads, int n_kv_heads,
                                     int head_dim, int store_kv, const void* q_weight, const void* k_weight,
                                     int weight_is_f32, float eps, const float* cos_table, const float* sin_table,
@@ -94,6 +154,23 @@ IB_EXPORT int ib_qk_norm_rope_store(const void* qkv, int row_stride, int n_rows,
     const size_t smem = (size_t)QRS_WARPS * head_dim * sizeof(float);
     const int heads_total = n_heads + (store_kv ? 2 * n_kv_heads : 0);
     const dim3 grid(n_rows, (heads_total + QRS_WARPS - 1) / QRS_WARPS);
+#if IB_ACT_BF16
+    if (head_dim == 128 && rot_dim == 128 && (row_stride % 4) == 0 && ((uintptr_t)qkv % 8) == 0 &&
+        ((uintptr_t)cos_table % 16) == 0 && ((uintptr_t)sin_table % 16) == 0) {
+        if (weight_is_f32)
+            ib_launch(qk_norm_rope_store_d128_kernel<float>, grid, 32 * QRS_WARPS, 0, stream, (const __nv_bfloat16*)qkv,
+                      row_stride, n_heads, n_kv_heads, store_kv, (const float*)q_weight, (const float*)k_weight, eps,
+                      cos_table, sin_table, positions, row_request, block_table, max_pages, page_size, n_pages,
+                      (__nv_bfloat16*)k_pages, (__nv_bfloat16*)v_pages, (__nv_bfloat16*)q_out);
+        else
+            ib_launch(qk_norm_rope_store_d128_kernel<__nv_bfloat16>, grid, 32 * QRS_WARPS, 0, stream,
+                      (const __nv_bfloat16*)qkv, row_stride, n_heads, n_kv_heads, store_kv,
+                      (const __nv_bfloat16*)q_weight, (const __nv_bfloat16*)k_weight, eps, cos_table, sin_table,
+                      positions, row_request, block_table, max_pages, page_size, n_pages, (__nv_bfloat16*)k_pages,
+                      (__nv_bfloat16*)v_pages, (__nv_bfloat16*)q_out);
+        return ib_launch_status();
+    }
+#endif
     if (weight_is_f32)
         ib_launch(qk_norm_rope_store_kernel<float>, grid, 32 * QRS_WARPS, smem, stream,
             (const act_t*)qkv, row_stride, n_heads, n_kv_heads, head_dim, store_kv, (const float*)q_weight,

@@ -18,7 +18,7 @@ def model_dirs(tmp_path_factory):
     """Model folders of the two tiny configurations, written once per session into a temporary folder."""
     import torch
 
-    from helpers import CONFIG_A, CONFIG_B, CONFIG_C
+    from helpers import CONFIG_A, CONFIG_B, CONFIG_C, CONFIG_D
     from inferrs_b200.weights.random_init import write_random_model
 
     base = tmp_path_factory.mktemp("models")
@@ -26,4 +26,5 @@ def model_dirs(tmp_path_factory):
         "A": write_random_model(str(base / "A"), CONFIG_A, seed=0, dtype=torch.bfloat16),
         "B": write_random_model(str(base / "B"), CONFIG_B, seed=2, dtype=torch.bfloat16),
         "C": write_random_model(str(base / "C"), CONFIG_C, seed=5, dtype=torch.bfloat16),
+        "D": write_random_model(str(base / "D"), CONFIG_D, seed=6, dtype=torch.bfloat16),
     }

@@ -26,7 +26,15 @@ CONFIG_C = {
     "head_dim": 64, "intermediate_size": 208, "vocab_size": 301, "rope_theta": 50000.0, "rms_norm_eps": 1e-6,
     "max_position_embeddings": 768, "tie_word_embeddings": True, "hidden_act": "silu",
 }
-PAGE_SIZE = {"A": 4, "B": 16, "C": 16}
+# A fourth shape with the head size of the published checkpoints (128): the bfloat16 engine then runs the TMA and
+# tcgen05 attention kernels and, in decode steps, the tcgen05 matrix product under programmatic dependent launch.
+CONFIG_D = {
+    "architectures": ["Qwen3ForCausalLM"], "model_type": "qwen3",
+    "num_hidden_layers": 2, "hidden_size": 192, "num_attention_heads": 6, "num_key_value_heads": 2,
+    "head_dim": 128, "intermediate_size": 328, "vocab_size": 389, "rope_theta": 1000000.0, "rms_norm_eps": 1e-6,
+    "max_position_embeddings": 1024, "tie_word_embeddings": False, "hidden_act": "silu",
+}
+PAGE_SIZE = {"A": 4, "B": 16, "C": 16, "D": 16}
 
 
 def random_tokens(n: int, vocab: int, seed: int) -> List[int]:

@@ -4,7 +4,7 @@ import pytest
 import torch
 
 import plain_qwen3
-from helpers import CONFIG_A, CONFIG_B, CONFIG_C, PAGE_SIZE, cut, random_tokens, rel_err
+from helpers import CONFIG_A, CONFIG_B, CONFIG_C, CONFIG_D, PAGE_SIZE, cut, random_tokens, rel_err
 from inferrs_b200.engine.batch import StepEntry
 from inferrs_b200.engine.loading import load_model_dir
 from inferrs_b200.engine.runner import ModelRunner
@@ -12,7 +12,7 @@ from inferrs_b200.runtime import Runtime
 
 pytestmark = pytest.mark.gpu
 
-CONFIGS = {"A": CONFIG_A, "B": CONFIG_B, "C": CONFIG_C}
+CONFIGS = {"A": CONFIG_A, "B": CONFIG_B, "C": CONFIG_C, "D": CONFIG_D}
 # float32: the north-star bound.  bfloat16: the plain implementation rounds where the engine stores
 # bfloat16, so what is left is the order of sums and a few roundings that fall differently.
 TOL = {torch.float32: 1e-4, torch.bfloat16: 3e-2}
@@ -41,7 +41,7 @@ def check(got, want, dtype, what=""):
 
 
 @pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
-@pytest.mark.parametrize("name", ["A", "B", "C"])
+@pytest.mark.parametrize("name", ["A", "B", "C", "D"])
 def test_whole(model_dirs, name, dtype):
     runner = make_runner(model_dirs[name], dtype, PAGE_SIZE[name], n_pages=128)
     for i, n in enumerate([1, 5, 17, 33, 100]):
@@ -53,7 +53,7 @@ def test_whole(model_dirs, name, dtype):
 
 
 @pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
-@pytest.mark.parametrize("name", ["A", "B", "C"])
+@pytest.mark.parametrize("name", ["A", "B", "C", "D"])
 def test_prefill_then_last_32_one_by_one(model_dirs, name, dtype):
     toks = random_tokens(150, CONFIGS[name]["vocab_size"], seed=11)
     want = plain_logits(model_dirs[name], toks, dtype)
@@ -66,7 +66,7 @@ def test_prefill_then_last_32_one_by_one(model_dirs, name, dtype):
 
 
 @pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
-@pytest.mark.parametrize("name", ["A", "B", "C"])
+@pytest.mark.parametrize("name", ["A", "B", "C", "D"])
 def test_portions_of_changing_size(model_dirs, name, dtype):
     toks = random_tokens(131, CONFIGS[name]["vocab_size"], seed=12)
     want = plain_logits(model_dirs[name], toks, dtype)
@@ -80,7 +80,7 @@ def test_portions_of_changing_size(model_dirs, name, dtype):
 
 
 @pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
-@pytest.mark.parametrize("name", ["A", "B", "C"])
+@pytest.mark.parametrize("name", ["A", "B", "C", "D"])
 def test_mixed_requests_with_page_reuse(model_dirs, name, dtype):
     ps = PAGE_SIZE[name]
     lens = [70, 23, 97, 31, 18, 64, 5, 49]
@@ -123,7 +123,7 @@ def test_mixed_requests_with_page_reuse(model_dirs, name, dtype):
 
 
 @pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
-@pytest.mark.parametrize("name", ["B", "C"])
+@pytest.mark.parametrize("name", ["B", "C", "D"])
 def test_long_decode(model_dirs, name, dtype):
     toks = random_tokens(400, CONFIGS[name]["vocab_size"], seed=31)
     want = plain_logits(model_dirs[name], toks, dtype)

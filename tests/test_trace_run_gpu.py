@@ -9,7 +9,7 @@ import pytest
 import torch
 
 import plain_qwen3
-from helpers import CONFIG_A, CONFIG_B, cut, random_tokens, rel_err
+from helpers import CONFIG_A, CONFIG_B, CONFIG_D, cut, random_tokens, rel_err
 
 pytestmark = pytest.mark.gpu
 ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
@@ -33,9 +33,9 @@ def read(out_dir, step, vocab):
     return torch.from_numpy(np.fromfile(os.path.join(out_dir, f"{step}.f32"), dtype="<f4").reshape(-1, vocab).copy())
 
 
-@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
-def test_replay_mixed_trace(model_dirs, tmp_path, dtype):
-    name, cfg = "B", CONFIG_B
+@pytest.mark.parametrize("dtype,name", [("float32", "B"), ("bfloat16", "B"), ("bfloat16", "D")])
+def test_replay_mixed_trace(model_dirs, tmp_path, dtype, name):
+    cfg = CONFIG_B if name == "B" else CONFIG_D
     vocab = cfg["vocab_size"]
     lens = {"a": 90, "b": 37, "c": 64, "d": 120, "e": 50}
     toks = {k: random_tokens(n, vocab, seed=ord(k)) for k, n in lens.items()}
