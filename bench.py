@@ -23,7 +23,7 @@ import time
 ROOT = os.path.dirname(os.path.abspath(__file__))
 sys.path.insert(0, ROOT)
 
-# BASELINE.json configs[2]: Qwen3-8B shape
+# The layer sizes of Qwen3-8B, the model the reference quotes its decode throughput on.
 CONFIG_8B = {
     "architectures": ["Qwen3ForCausalLM"], "model_type": "qwen3",
     "num_hidden_layers": 36, "hidden_size": 4096, "num_attention_heads": 32, "num_key_value_heads": 8,
@@ -50,13 +50,13 @@ class ClockSampler:
     Q = ("clocks.sm,clocks.max.sm,clocks_event_reasons.hw_slowdown,clocks_event_reasons.hw_thermal_slowdown,"
          "clocks_event_reasons.sw_thermal_slowdown,clocks_event_reasons.sw_power_cap")
 
-    def __init__(self):
-        self.rows, self.proc = [], None
+    def __init__(self, interval_ms=200):
+        self.rows, self.proc, self.interval_ms = [], None, interval_ms
 
     def start(self):
         try:
             self.proc = subprocess.Popen(["nvidia-smi", "-i", "0", f"--query-gpu={self.Q}", "--format=csv,noheader,nounits",
-                                          "-lms", "100"], stdout=subprocess.PIPE, stderr=subprocess.DEVNULL, text=True)
+                                          "-lms", str(self.interval_ms)], stdout=subprocess.PIPE, stderr=subprocess.DEVNULL, text=True)
         except OSError:
             self.proc = None
             return
@@ -91,6 +91,7 @@ def main() -> int:
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--batch", type=int, default=8)
     ap.add_argument("--layers", type=int, default=FULL_LAYERS, help="fewer layers than the model has, for quick runs")
+    ap.add_argument("--clock-interval-ms", type=int, default=200, help="how often nvidia-smi is asked for the clocks")
     ap.add_argument("--no-points", action="store_true", help="skip the batch 1 and 64 points and the prefill")
     args = ap.parse_args()
 
@@ -162,7 +163,7 @@ def main() -> int:
             runner.release(r)
         return t0.elapsed_time(t1) / steps, launches
 
-    clocks = ClockSampler()
+    clocks = ClockSampler(args.clock_interval_ms)
     clocks.start()
     time.sleep(0.3)
     lo = clocks.mark()
@@ -174,7 +175,7 @@ def main() -> int:
     achieved = step_bytes / (ms * 1e-3) / 1e9
 
     # end to end: the engine's own loop, host token ids in, host token ids out, every step
-    sp = SamplingParams.greedy(max_tokens=args.steps + args.warmup, ignore_eos=True)
+    sp = SamplingParams.greedy(max_tokens=args.steps + args.warmup + 16, ignore_eos=True)  # none ends inside the timed loop
     for _ in range(args.batch):
         eng.add_request(prompt(), sp)
     reqs = list(eng.scheduler.waiting)

@@ -210,7 +210,7 @@ __global__ void __launch_bounds__(THREADS, 1) streamk_kernel(const __grid_consta
             const int tile_t = tile / p.tiles_f, tile_f = tile - tile_t * p.tiles_f;
             const int feature = tile_f * BM + row;
             const int buf = seg & 1;
-            if (!mbar_wait(accf0 + 8 * buf, (unsigned)(seg >> 1) & 1, 3)) { ok = false; break; }
+            if (!__all_sync(0xffffffffu, mbar_wait(accf0 + 8 * buf, (unsigned)(seg >> 1) & 1, 3))) { ok = false; break; }  // warp-wide
             fence_after();
             // a slice that covers its whole tile is stored; any other is kept as a partial sum
             float* keep = !ends_tile ? tail : (kb_begin > 0 ? head : nullptr);

@@ -9,8 +9,11 @@
 // warps 2..5 = epilogue (one quarter of the 128 lanes each).
 //
 // With few output tiles the K range is cut over a thread-block cluster (1,1,split): every CTA of the
-// cluster accumulates its part of K, the parts are summed through distributed shared memory by the
-// cluster's first CTA, so no global scratch and no atomics are needed.
+// cluster accumulates its part of K and the parts are summed through distributed shared memory, so no
+// global scratch and no atomics are needed.  Up to 32 tokens every CTA of the cluster owns an equal share
+// of the tile's rows: each CTA stores the other shares of its partial sums straight into their owners'
+// shared memory, one cluster barrier follows, and every owner adds the parts in the order of the CTAs'
+// ranks and stores its rows.  Wider tiles are summed by the cluster's first CTA, which reads the others.
 //
 // Every wait on an mbarrier is bounded (about two seconds); a wait that runs out records a code in the
 // library's error word, the CTA lets outstanding copies land, frees its tensor memory and returns.
@@ -68,6 +71,17 @@ __device__ __forceinline__ void tma_load_2d(unsigned dst, const CUtensorMap* map
                  ::"r"(dst), "l"(map), "r"(bar), "r"(x), "r"(y) : "memory");
 }
 
+__device__ __forceinline__ void tma_load_2d_hint(unsigned dst, const CUtensorMap* map, int x, int y, unsigned bar,
+                                                 unsigned long long policy) {
+    asm volatile("cp.async.bulk.tensor.2d.shared::cluster.global.mbarrier::complete_tx::bytes.L2::cache_hint [%0], [%1, {%3, %4}], [%2], %5;"
+                 ::"r"(dst), "l"(map), "r"(bar), "r"(x), "r"(y), "l"(policy) : "memory");
+}
+__device__ __forceinline__ unsigned long long policy_evict_first() {
+    unsigned long long p;
+    asm volatile("createpolicy.fractional.L2::evict_first.b64 %0, 1.0;" : "=l"(p));
+    return p;
+}
+
 // K-major operand tile with 128-byte rows and the 128-byte swizzle: 8-row groups are 1024 bytes apart.
 __device__ __forceinline__ unsigned long long smem_desc(unsigned addr) {
     unsigned long long d = 0;
@@ -104,6 +118,14 @@ __device__ __forceinline__ void cluster_sync_all() {
     __syncwarp();  // lanes that skipped a single-lane role loop join the others before the aligned barrier
     asm volatile("barrier.cluster.arrive.release.aligned;\n\tbarrier.cluster.wait.acquire.aligned;" ::: "memory");
 }
+__device__ __forceinline__ void cluster_arrive() {
+    __syncwarp();
+    asm volatile("barrier.cluster.arrive.release.aligned;" ::: "memory");
+}
+__device__ __forceinline__ void cluster_wait() {
+    __syncwarp();
+    asm volatile("barrier.cluster.wait.acquire.aligned;" ::: "memory");
+}
 __device__ __forceinline__ unsigned cluster_rank() {
     unsigned r;
     asm volatile("mov.u32 %0, %%cluster_ctarank;" : "=r"(r));
@@ -117,17 +139,36 @@ __device__ __forceinline__ float ld_remote_f32(unsigned local_addr, unsigned ran
     return v;
 }
 
+__device__ __forceinline__ void st_remote_f32(unsigned local_addr, unsigned rank, float v) {
+    unsigned remote;
+    asm volatile("mapa.shared::cluster.u32 %0, %1, %2;" : "=r"(remote) : "r"(local_addr), "r"(rank));
+    asm volatile("st.shared::cluster.f32 [%0], %1;" ::"r"(remote), "f"(v) : "memory");
+}
+
 struct Params {
     void* y;
     long ldy;
     int n_tok, n_out, num_kb, y_is_f32;
+    int inner;   // gated form: rows of the gate matrix; the up matrix follows it in w
 };
 
-template <int BN, int STAGES>
+#ifdef IB_GEMM_TIMELINE
+// A build for looking at how launches overlap: every CTA records when it started, when its predecessor was
+// done, when its first tile had landed, when its accumulator was complete and when it left (globaltimer, ns).
+#define TL_MAX 65536
+__device__ unsigned long long g_tl[TL_MAX * 8];
+__device__ unsigned g_tl_count = 0;
+#define TL_MARK(slot, i) do { if ((slot) < TL_MAX) g_tl[(size_t)(slot) * 8 + (i)] = global_ns(); } while (0)
+#else
+#define TL_MARK(slot, i) do { } while (0)
+#endif
+
+template <int BN, int STAGES, int MODE>
 __global__ void __launch_bounds__(THREADS, (BN <= 64 ? 2 : 1)) gemm_kernel(const __grid_constant__ CUtensorMap map_w,
                                                           const __grid_constant__ CUtensorMap map_x, const Params p) {
     constexpr int B_BYTES = BN * BK * 2;
     constexpr int TMEM_COLS = BN < 32 ? 32 : BN;
+    constexpr bool SCATTER = BN <= 32;   // how a cluster sums its parts: see the head of this file
     extern __shared__ unsigned char raw_smem[];
     unsigned char* smem = reinterpret_cast<unsigned char*>((reinterpret_cast<uintptr_t>(raw_smem) + 1023) & ~(uintptr_t)1023);
     unsigned char* a_tiles = smem;
@@ -135,6 +176,7 @@ __global__ void __launch_bounds__(THREADS, (BN <= 64 ? 2 : 1)) gemm_kernel(const
     unsigned long long* bars = reinterpret_cast<unsigned long long*>(b_tiles + STAGES * B_BYTES);
     const unsigned full0 = smem_u32(bars), empty0 = smem_u32(bars + STAGES), accum = smem_u32(bars + 2 * STAGES);
     unsigned* tmem_slot = reinterpret_cast<unsigned*>(bars + 2 * STAGES + 1);
+    float* recv = reinterpret_cast<float*>(bars + 2 * STAGES + 2);   // [rank of the sender][BN][rows owned], SCATTER only
 
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const int tile_f = blockIdx.x, tile_t = blockIdx.y;
@@ -147,6 +189,20 @@ __global__ void __launch_bounds__(THREADS, (BN <= 64 ? 2 : 1)) gemm_kernel(const
     // kernel in turn may have been started before its predecessor finished, so it reads the weights (which no
     // kernel writes) at once but touches x, y and the rest only after griddepcontrol.wait.
     asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
+#ifdef IB_GEMM_TIMELINE
+    __shared__ unsigned tl_slot_s;
+    if (threadIdx.x == 0) {
+        tl_slot_s = atomicAdd(&g_tl_count, 1u);
+        if (tl_slot_s < TL_MAX) {
+            unsigned smid;
+            asm volatile("mov.u32 %0, %%smid;" : "=r"(smid));
+            g_tl[(size_t)tl_slot_s * 8 + 5] = smid;
+            g_tl[(size_t)tl_slot_s * 8 + 6] = ((unsigned long long)gridDim.x << 32) | ((unsigned long long)gridDim.z << 16) | (unsigned)p.num_kb;
+            g_tl[(size_t)tl_slot_s * 8 + 7] = ((unsigned long long)blockIdx.x << 16) | blockIdx.z;
+        }
+        TL_MARK(tl_slot_s, 0);
+    }
+#endif
     if (threadIdx.x == 0) {
         for (int s = 0; s < STAGES; ++s) { mbar_init(full0 + 8 * s, 1); mbar_init(empty0 + 8 * s, 1); }
         mbar_init(accum, 1);
@@ -161,23 +217,41 @@ __global__ void __launch_bounds__(THREADS, (BN <= 64 ? 2 : 1)) gemm_kernel(const
     fence_after();
     const unsigned tmem = *tmem_slot;
     bool ok = true;
+    // A CTA's shared memory may be written by its cluster only once the CTA runs: every CTA says so here and
+    // looks at the others' word just before its first store to them, long after they have given it.
+    if (splits > 1 && SCATTER) cluster_arrive();
+#ifdef IB_GEMM_TIMELINE
+    const unsigned tl_slot = tl_slot_s;
+#endif
 
     if (warp == 0) {
         if (lane == 0 && nkb > 0) {
+            // the weights are read once: their lines are the first to leave the L2 cache again
+            const unsigned long long pol = policy_evict_first();
+            auto load_w = [&](int i, int s) {   // k-block i of this CTA's part into stage s
+                const unsigned dst = smem_u32(a_tiles + s * A_BYTES);
+                if (MODE == 1) {   // 64 rows of the gate matrix above the same 64 rows of the up matrix
+                    tma_load_2d_hint(dst, &map_w, (kb0 + i) * BK, tile_f * 64, full0 + 8 * s, pol);
+                    tma_load_2d_hint(dst + A_BYTES / 2, &map_w, (kb0 + i) * BK, p.inner + tile_f * 64, full0 + 8 * s, pol);
+                } else {
+                    tma_load_2d_hint(dst, &map_w, (kb0 + i) * BK, tile_f * BM, full0 + 8 * s, pol);
+                }
+            };
             // the first ring of weight tiles is on its way before the predecessor's results are waited for
             const int head = nkb < STAGES ? nkb : STAGES;
             for (int i = 0; i < head; ++i) {
                 mbar_expect_tx(full0 + 8 * i, A_BYTES + B_BYTES);
-                tma_load_2d(smem_u32(a_tiles + i * A_BYTES), &map_w, (kb0 + i) * BK, tile_f * BM, full0 + 8 * i);
+                load_w(i, i);
             }
             asm volatile("griddepcontrol.wait;" ::: "memory");
+            TL_MARK(tl_slot, 1);
             for (int i = 0; i < head; ++i)
                 tma_load_2d(smem_u32(b_tiles + i * B_BYTES), &map_x, (kb0 + i) * BK, tile_t * BN, full0 + 8 * i);
             for (int i = head; i < nkb; ++i) {
                 const int s = i % STAGES;
                 if (!mbar_wait(empty0 + 8 * s, ((i / STAGES) - 1) & 1, 1)) { ok = false; break; }
                 mbar_expect_tx(full0 + 8 * s, A_BYTES + B_BYTES);
-                tma_load_2d(smem_u32(a_tiles + s * A_BYTES), &map_w, (kb0 + i) * BK, tile_f * BM, full0 + 8 * s);
+                load_w(i, s);
                 tma_load_2d(smem_u32(b_tiles + s * B_BYTES), &map_x, (kb0 + i) * BK, tile_t * BN, full0 + 8 * s);
             }
         }
@@ -187,6 +261,7 @@ __global__ void __launch_bounds__(THREADS, (BN <= 64 ? 2 : 1)) gemm_kernel(const
             for (int i = 0; i < nkb; ++i) {
                 const int s = i % STAGES;
                 if (!mbar_wait(full0 + 8 * s, (i / STAGES) & 1, 2)) { ok = false; break; }
+                if (i == 0) TL_MARK(tl_slot, 2);
                 fence_after();
                 const unsigned long long da = smem_desc(smem_u32(a_tiles + s * A_BYTES));
                 const unsigned long long db = smem_desc(smem_u32(b_tiles + s * B_BYTES));
@@ -202,11 +277,68 @@ __global__ void __launch_bounds__(THREADS, (BN <= 64 ? 2 : 1)) gemm_kernel(const
 
     const int q = warp & 3;                    // the quarter of the 128 lanes that this warp may read
     const int row = q * 32 + lane;
-    const int feature = tile_f * BM + row;
+    const int feature = MODE == 1 ? tile_f * 64 + (row & 63) : tile_f * BM + row;
     float* stage = reinterpret_cast<float*>(smem);  // [BN][BM] partial sums for the cluster reduction (stages are idle by then)
+    if (splits > 1 && SCATTER) cluster_wait();
+    const unsigned my_rank = splits > 1 ? cluster_rank() : 0;
+    const int owned = BM / splits;             // SCATTER: rows of the tile that each CTA of the cluster sums and stores
+    const unsigned owner = (unsigned)(q * 32 / owned);
+    const int row_local = row - (int)owner * owned;
+    if constexpr (MODE == 1) {
+        // Gated form (one CTA per tile, no cluster): lanes 0..63 of the accumulator hold 64 features of the
+        // gate product, lanes 64..127 the same features of the up product.  The upper two warps hand their
+        // values over through shared memory; the lower two compute silu(gate) * up and store.  Both factors
+        // are rounded to bfloat16 first, as they are when the product and the gate run as two kernels.
+        if (warp >= 2) {
+            asm volatile("griddepcontrol.wait;" ::: "memory");   // y may still be read by the predecessor
+            ok = nkb > 0 ? mbar_wait(accum, 0, 3) : true;
+            ok = __all_sync(0xffffffffu, ok);   // one answer per warp: the tensor-memory loads below are warp-wide
+            if (threadIdx.x == 64) TL_MARK(tl_slot, 3);
+            fence_after();
+            float* up_vals = recv;              // [BN][64]
+            if (ok && q >= 2) {
+#pragma unroll 1
+                for (int c0 = 0; c0 < BN && tile_t * BN + c0 < p.n_tok; c0 += 16) {
+                    float v[16];
+                    if (nkb > 0) tmem_ld16(tmem + ((unsigned)(q * 32) << 16) + c0, v);
+                    else {
+#pragma unroll
+                        for (int j = 0; j < 16; ++j) v[j] = 0.0f;
+                    }
+#pragma unroll
+                    for (int j = 0; j < 16; ++j) up_vals[(c0 + j) * 64 + (row - 64)] = v[j];
+                }
+            }
+            asm volatile("bar.sync 1, 128;" ::: "memory");   // the four epilogue warps
+            if (ok && q < 2) {                  // whole warps: the tensor-memory load below is warp-wide
+                const bool store = feature < p.n_out && g_error == 0;
+#pragma unroll 1
+                for (int c0 = 0; c0 < BN && tile_t * BN + c0 < p.n_tok; c0 += 16) {
+                    float v[16];
+                    if (nkb > 0) tmem_ld16(tmem + ((unsigned)(q * 32) << 16) + c0, v);
+                    else {
+#pragma unroll
+                        for (int j = 0; j < 16; ++j) v[j] = 0.0f;
+                    }
+#pragma unroll
+                    for (int j = 0; j < 16; ++j) {
+                        const int tok = tile_t * BN + c0 + j;
+                        if (tok < p.n_tok && store) {
+                            const float g = __bfloat162float(__float2bfloat16_rn(v[j]));
+                            const float u = __bfloat162float(__float2bfloat16_rn(up_vals[(c0 + j) * 64 + row]));
+                            reinterpret_cast<__nv_bfloat16*>(p.y)[(long)tok * p.ldy + feature] =
+                                __float2bfloat16_rn(g / (1.0f + expf(-g)) * u);
+                        }
+                    }
+                }
+            }
+        }
+    } else {
     if (warp >= 2) {
         asm volatile("griddepcontrol.wait;" ::: "memory");   // y may still be read by the predecessor
         ok = nkb > 0 ? mbar_wait(accum, 0, 3) : true;
+        ok = __all_sync(0xffffffffu, ok);       // one answer per warp: the tensor-memory loads below are warp-wide
+        if (threadIdx.x == 64) TL_MARK(tl_slot, 3);
         fence_after();
         if (ok) {
 #pragma unroll 1
@@ -217,7 +349,20 @@ __global__ void __launch_bounds__(THREADS, (BN <= 64 ? 2 : 1)) gemm_kernel(const
 #pragma unroll
                     for (int j = 0; j < 16; ++j) v[j] = 0.0f;
                 }
-                if (splits > 1) {
+                if (splits > 1 && SCATTER) {
+                    // this warp's 32 rows go to the CTA that owns them (which may be this one)
+                    if (tile_t * BN + c0 < p.n_tok) {
+                        float* slot = recv + ((size_t)my_rank * BN + c0) * owned + row_local;
+                        if (owner == my_rank) {
+#pragma unroll
+                            for (int j = 0; j < 16; ++j) slot[j * owned] = v[j];
+                        } else {
+#pragma unroll
+                            for (int j = 0; j < 16; ++j)
+                                if (tile_t * BN + c0 + j < p.n_tok) st_remote_f32(smem_u32(slot + j * owned), owner, v[j]);
+                        }
+                    }
+                } else if (splits > 1) {
 #pragma unroll
                     for (int j = 0; j < 16; ++j) stage[(c0 + j) * BM + row] = v[j];
                 } else if (feature < p.n_out) {
@@ -233,9 +378,34 @@ __global__ void __launch_bounds__(THREADS, (BN <= 64 ? 2 : 1)) gemm_kernel(const
             }
         }
     }
-    if (splits > 1) {
+    if (splits > 1 && SCATTER) {
+        cluster_sync_all();                    // every part of the rows this CTA owns is in its shared memory
+        if (warp >= 2 && owner == my_rank && feature < p.n_out && g_error == 0) {
+#pragma unroll 1
+            for (int c0 = 0; c0 < BN && tile_t * BN + c0 < p.n_tok; c0 += 16) {
+                float sum[16];
+#pragma unroll
+                for (int j = 0; j < 16; ++j) sum[j] = 0.0f;
+                for (int r = 0; r < splits; ++r) {   // in the order of the ranks, whoever does the adding
+                    const float* part = recv + ((size_t)r * BN + c0) * owned + row_local;
+#pragma unroll
+                    for (int j = 0; j < 16; ++j)
+                        if (tile_t * BN + c0 + j < p.n_tok) sum[j] += part[j * owned];
+                }
+#pragma unroll
+                for (int j = 0; j < 16; ++j) {
+                    const int tok = tile_t * BN + c0 + j;
+                    if (tok < p.n_tok) {
+                        if (p.y_is_f32) reinterpret_cast<float*>(p.y)[(long)tok * p.ldy + feature] = sum[j];
+                        else reinterpret_cast<__nv_bfloat16*>(p.y)[(long)tok * p.ldy + feature] = __float2bfloat16_rn(sum[j]);
+                    }
+                }
+            }
+        }
+        // nobody touches another CTA's shared memory after the barrier: the CTAs may leave in any order
+    } else if (splits > 1) {
         cluster_sync_all();                    // every CTA's partial sums are in its shared memory
-        if (warp >= 2 && cluster_rank() == 0 && feature < p.n_out && g_error == 0) {
+        if (warp >= 2 && my_rank == 0 && feature < p.n_out && g_error == 0) {
 #pragma unroll 1
             for (int c0 = 0; c0 < BN && tile_t * BN + c0 < p.n_tok; c0 += 16) {
                 float sum[16];
@@ -261,6 +431,8 @@ __global__ void __launch_bounds__(THREADS, (BN <= 64 ? 2 : 1)) gemm_kernel(const
         cluster_sync_all();                    // the first CTA has read its neighbours' shared memory
     }
 
+    }
+
     if (!ok || g_error != 0) {
         // a wait ran out somewhere: give copies that are still in flight time to land before the CTA leaves
         const unsigned long long t0 = global_ns();
@@ -268,6 +440,7 @@ __global__ void __launch_bounds__(THREADS, (BN <= 64 ? 2 : 1)) gemm_kernel(const
     }
     fence_before();
     __syncthreads();
+    if (threadIdx.x == 0) TL_MARK(tl_slot, 4);
     if (warp == 1) {
         fence_after();
         asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem), "r"(TMEM_COLS) : "memory");
@@ -303,17 +476,19 @@ static bool make_map(CUtensorMap* map, const void* base, long rows, long k, long
                CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) == CUDA_SUCCESS;
 }
 
-template <int BN, int STAGES>
+template <int BN, int STAGES, int MODE = 0>
 static int launch(const CUtensorMap& mw, const CUtensorMap& mx, const Params& p, int splits, cudaStream_t stream) {
-    constexpr size_t smem = (size_t)STAGES * (A_BYTES + BN * BK * 2) + (2 * STAGES + 2) * 8 + 1024;
+    constexpr size_t smem = (size_t)STAGES * (A_BYTES + BN * BK * 2) + (2 * STAGES + 2) * 8 + 1024 +
+                            (BN <= 32 ? (size_t)BN * BM * 4 : 0);   // + the parts received from the cluster
     static bool configured = false;
     if (!configured) {
-        cudaError_t e = cudaFuncSetAttribute(gemm_kernel<BN, STAGES>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+        cudaError_t e = cudaFuncSetAttribute(gemm_kernel<BN, STAGES, MODE>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
         if (e != cudaSuccess) return (int)e;
         configured = true;
     }
     cudaLaunchConfig_t cfg = {};
-    cfg.gridDim = dim3((p.n_out + BM - 1) / BM, (p.n_tok + BN - 1) / BN, splits);
+    const int rows_per_tile = MODE == 1 ? 64 : BM;
+    cfg.gridDim = dim3((p.n_out + rows_per_tile - 1) / rows_per_tile, (p.n_tok + BN - 1) / BN, splits);
     cfg.blockDim = dim3(THREADS);
     cfg.dynamicSmemBytes = smem;
     cfg.stream = stream;
@@ -326,7 +501,7 @@ static int launch(const CUtensorMap& mw, const CUtensorMap& mx, const Params& p,
     attr[1].val.programmaticStreamSerializationAllowed = 1;
     cfg.attrs = attr;
     cfg.numAttrs = g_pdl ? 2 : 1;
-    cudaError_t e = cudaLaunchKernelEx(&cfg, gemm_kernel<BN, STAGES>, mw, mx, p);
+    cudaError_t e = cudaLaunchKernelEx(&cfg, gemm_kernel<BN, STAGES, MODE>, mw, mx, p);
     return e == cudaSuccess ? ib_launch_status() : (int)e;
 }
 
@@ -343,6 +518,7 @@ IB_EXPORT int ib_gemm_tn_tcgen05(const void* x, long ldx, const void* w, long ld
     const int bn = n_tok <= 16 ? 16 : n_tok <= 32 ? 32 : n_tok <= 64 ? 64 : n_tok <= 128 ? 128 : 256;
     tc::Params p;
     p.y = y; p.ldy = ldy; p.n_tok = n_tok; p.n_out = n_out; p.num_kb = (k + tc::BK - 1) / tc::BK; p.y_is_f32 = y_is_f32;
+    p.inner = 0;
     int splits = split_k;
     if (splits <= 0) {
         const long tiles = (long)((n_out + tc::BM - 1) / tc::BM) * ((n_tok + bn - 1) / bn);
@@ -357,11 +533,27 @@ IB_EXPORT int ib_gemm_tn_tcgen05(const void* x, long ldx, const void* w, long ld
         // up to 64 tokens: two CTAs per SM with half the ring each, so that tile counts between one and two
         // per SM still run as one wave in which every CTA gets the same share of the memory bandwidth
         case 16: return tc::launch<16, 5>(mw, mx, p, splits, stream);
-        case 32: return tc::launch<32, 5>(mw, mx, p, splits, stream);
+        case 32: return tc::launch<32, 4>(mw, mx, p, splits, stream);
         case 64: return tc::launch<64, 4>(mw, mx, p, splits, stream);
         case 128: return tc::launch<128, 6>(mw, mx, p, splits, stream);
         default: return tc::launch<256, 4>(mw, mx, p, splits, stream);
     }
+}
+
+// y[t, f] = silu(x[t] . w[f]) * (x[t] . w[inner + f]) for f < inner: the gate and up products of a gated feed-forward
+// and the gate itself in one kernel.  w [2 * inner, k] holds the gate matrix above the up matrix; y [n_tok, inner]
+// bfloat16.  Up to 16 tokens (IB_ERR_UNSUPPORTED beyond; the caller then runs product and gate separately).
+IB_EXPORT int ib_gemm_swiglu_tcgen05(const void* x, long ldx, const void* w, long ldw, void* y, long ldy, int n_tok,
+                                     int inner, int k, cudaStream_t stream) {
+    if (n_tok <= 0 || inner <= 0) return IB_OK;
+    if (k <= 0) return IB_ERR_ARGUMENT;
+    if ((k % 8) || (ldx % 8) || (ldw % 8) || ((uintptr_t)x % 16) || ((uintptr_t)w % 16) || n_tok > 16) return IB_ERR_UNSUPPORTED;
+    tc::Params p;
+    p.y = y; p.ldy = ldy; p.n_tok = n_tok; p.n_out = inner; p.num_kb = (k + tc::BK - 1) / tc::BK; p.y_is_f32 = 0;
+    p.inner = inner;
+    CUtensorMap mw, mx;
+    if (!tc::make_map(&mw, w, 2L * inner, k, ldw, 64) || !tc::make_map(&mx, x, n_tok, k, ldx, 16)) return IB_ERR_UNSUPPORTED;
+    return tc::launch<16, 5, 1>(mw, mx, p, 1, stream);
 }
 
 // 1: later launches may start before the kernel before them in the stream has finished (programmatic dependent
@@ -369,6 +561,7 @@ IB_EXPORT int ib_gemm_tn_tcgen05(const void* x, long ldx, const void* w, long ld
 // kernel that runs between two such launches must itself call griddepcontrol.wait before its first access to
 // memory that another kernel writes.  0 (default): plain stream order.
 IB_EXPORT void ib_gemm_tcgen05_set_pdl(int on) { tc::g_pdl = on; }
+
 
 // The error word of the kernels above: 0, or the code of the first wait that ran out (1 producer, 2 MMA
 // issuer, 3 epilogue).  Reading it synchronises with the device; `reset` clears it.
@@ -381,5 +574,19 @@ IB_EXPORT int ib_gemm_tcgen05_error(int reset) {
     }
     return v;
 }
+
+#ifdef IB_GEMM_TIMELINE
+// Copies the records of up to `max_ctas` CTAs (8 words each) to `dst` (host) and clears them; returns how many.
+IB_EXPORT int ib_gemm_timeline(unsigned long long* dst, int max_ctas) {
+    unsigned n = 0;
+    if (cudaMemcpyFromSymbol(&n, tc::g_tl_count, sizeof(n)) != cudaSuccess) return -1;
+    if (n > TL_MAX) n = TL_MAX;
+    if ((int)n > max_ctas) n = max_ctas;
+    if (n && cudaMemcpyFromSymbol(dst, tc::g_tl, (size_t)n * 8 * sizeof(unsigned long long)) != cudaSuccess) return -1;
+    const unsigned zero = 0;
+    cudaMemcpyToSymbol(tc::g_tl_count, &zero, sizeof(zero));
+    return (int)n;
+}
+#endif
 
 #endif

@@ -10,11 +10,32 @@
 
 #define QRS_WARPS 4
 
+// A row whose position lies outside the rotation tables is left out, and the first such row is recorded here
+// (row + 1; 0: none) for the host to read with ib_row_fault.  A row whose page is not in the cache (-1 in the
+// block table: a request that stands in to fill a batch) writes no key or value; that is no fault.
+__device__ int ib_row_fault_word = 0;
+
+__device__ __forceinline__ void ib_note_row_fault(int row) {
+    if ((threadIdx.x & 31) == 0) atomicCAS(&ib_row_fault_word, 0, row + 1);
+}
+
+// The recorded fault (row + 1, 0 if none), or a negative cudaError_t; waits for the device.
+IB_EXPORT int ib_row_fault(int reset) {
+    int v = 0;
+    cudaError_t e = cudaMemcpyFromSymbol(&v, ib_row_fault_word, sizeof(int));
+    if (e != cudaSuccess) return -(int)e;
+    if (reset && v != 0) {
+        const int zero = 0;
+        cudaMemcpyToSymbol(ib_row_fault_word, &zero, sizeof(int));
+    }
+    return v;
+}
+
 template <typename WT>
 __global__ void qk_norm_rope_store_kernel(
     const act_t* __restrict__ qkv, int row_stride, int n_heads, int n_kv_heads, int head_dim, int store_kv,
     const WT* __restrict__ q_weight, const WT* __restrict__ k_weight, float eps,
-    const float* __restrict__ cos_table, const float* __restrict__ sin_table, int rot_dim,
+    const float* __restrict__ cos_table, const float* __restrict__ sin_table, int rot_dim, int table_rows,
     const int* __restrict__ positions, const int* __restrict__ row_request,
     const int* __restrict__ block_table, int max_pages, int page_size, int n_pages,
     act_t* __restrict__ k_pages, act_t* __restrict__ v_pages, act_t* __restrict__ q_out) {
@@ -27,12 +48,14 @@ __global__ void qk_norm_rope_store_kernel(
     float* sh = smem + warp * d;
     const int pos = positions[row];
     const int heads_total = n_heads + (store_kv ? 2 * n_kv_heads : 0);
+    // a position outside the rotation tables: the row is left out and the fault is recorded
+    if (pos < 0 || (rot_dim > 0 && pos >= table_rows)) { ib_note_row_fault(row); return; }
 
     // Where this row's key and value go: page and place within the page.
     long kv_base = -1;  // element offset of (page, kv head 0, slot, 0)
     if (store_kv) {
         const int req = row_request[row];
-        const int page = block_table[(long)req * max_pages + pos / page_size];
+        const int page = pos / page_size < max_pages ? block_table[(long)req * max_pages + pos / page_size] : -1;
         if (page >= 0 && page < n_pages)
             kv_base = ((long)page * n_kv_heads * page_size + (pos % page_size)) * d;
     }
@@ -81,13 +104,14 @@ __global__ void qk_norm_rope_store_kernel(
 }
 
 #if IB_ACT_BF16
-// Head size 128 rotated in full, bfloat16: one warp per (row, head), lane l holds elements 4l..4l+3 and gets the
-// elements 64 further (or nearer) from lane l ^ 16; no shared memory.
-template <typename WT>
+// Head size 128 rotated in full, bfloat16: one warp per (row, HPW heads), lane l holds elements 4l..4l+3 of each
+// head and gets the elements 64 further (or nearer) from lane l ^ 16; no shared memory.  All HPW loads are issued
+// before the first is used: with thousands of rows the kernel is bound by the bytes it keeps in flight.
+template <typename WT, int HPW>
 __global__ void qk_norm_rope_store_d128_kernel(
     const __nv_bfloat16* __restrict__ qkv, int row_stride, int n_heads, int n_kv_heads, int store_kv,
     const WT* __restrict__ q_weight, const WT* __restrict__ k_weight, float eps,
-    const float* __restrict__ cos_table, const float* __restrict__ sin_table,
+    const float* __restrict__ cos_table, const float* __restrict__ sin_table, int table_rows,
     const int* __restrict__ positions, const int* __restrict__ row_request,
     const int* __restrict__ block_table, int max_pages, int page_size, int n_pages,
     __nv_bfloat16* __restrict__ k_pages, __nv_bfloat16* __restrict__ v_pages, __nv_bfloat16* __restrict__ q_out) {
@@ -95,48 +119,62 @@ __global__ void qk_norm_rope_store_d128_kernel(
     const int row = blockIdx.x;
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const int heads_total = n_heads + (store_kv ? 2 * n_kv_heads : 0);
-    const int head = blockIdx.y * QRS_WARPS + warp;
-    if (head >= heads_total) return;
-    const int kind = head < n_heads ? 0 : (head < n_heads + n_kv_heads ? 1 : 2);
+    const int head0 = (blockIdx.y * QRS_WARPS + warp) * HPW;
+    if (head0 >= heads_total) return;
     const int pos = positions[row];
-    const uint2 raw = *reinterpret_cast<const uint2*>(qkv + (long)row * row_stride + (long)head * 128 + 4 * lane);
-    const float2 x01 = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(&raw.x));
-    const float2 x23 = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(&raw.y));
-    float x[4] = {x01.x, x01.y, x23.x, x23.y};
-    __nv_bfloat16* dst;
-    if (kind == 0) {
-        dst = q_out + ((long)row * n_heads + head) * 128;
-    } else {
+    if (pos < 0 || pos >= table_rows) { ib_note_row_fault(row); return; }
+    uint2 raw[HPW];
+#pragma unroll
+    for (int h = 0; h < HPW; ++h)
+        if (head0 + h < heads_total)
+            raw[h] = *reinterpret_cast<const uint2*>(qkv + (long)row * row_stride + (long)(head0 + h) * 128 + 4 * lane);
+    long kv_base = -1;  // element offset of (page, kv head 0, place in the page, 0)
+    if (store_kv && head0 + HPW > n_heads) {
         const int req = row_request[row];
-        const int page = block_table[(long)req * max_pages + pos / page_size];
-        if (page < 0 || page >= n_pages) return;
-        const int kvh = head - n_heads - (kind == 2 ? n_kv_heads : 0);
-        dst = (kind == 1 ? k_pages : v_pages) + (((long)page * n_kv_heads + kvh) * page_size + (pos % page_size)) * 128;
+        const int page = pos / page_size < max_pages ? block_table[(long)req * max_pages + pos / page_size] : -1;
+        if (page >= 0 && page < n_pages) kv_base = ((long)page * n_kv_heads * page_size + (pos % page_size)) * 128;
     }
-    if (kind != 2) {
-        const WT* w = kind == 0 ? q_weight : k_weight;
-        if (w != nullptr) {
-            float ss = x[0] * x[0] + x[1] * x[1] + x[2] * x[2] + x[3] * x[3];
-            ss = ib_warp_sum(ss);
-            const float inv = 1.0f / sqrtf(ss / 128.0f + eps);
+    // element i < 64 pairs with i + 64: lanes 0..15 hold the first halves, lanes 16..31 the second
+    const int i0 = 4 * (lane & 15);
+    const float4 c = *reinterpret_cast<const float4*>(cos_table + (long)pos * 64 + i0);
+    const float4 s = *reinterpret_cast<const float4*>(sin_table + (long)pos * 64 + i0);
+    const float cs[4] = {c.x, c.y, c.z, c.w}, sn[4] = {s.x, s.y, s.z, s.w};
 #pragma unroll
-            for (int e = 0; e < 4; ++e) x[e] = x[e] * inv * ib_to_float(w[4 * lane + e]);
+    for (int h = 0; h < HPW; ++h) {
+        const int head = head0 + h;
+        if (head >= heads_total) break;
+        const int kind = head < n_heads ? 0 : (head < n_heads + n_kv_heads ? 1 : 2);
+        const float2 x01 = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(&raw[h].x));
+        const float2 x23 = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(&raw[h].y));
+        float x[4] = {x01.x, x01.y, x23.x, x23.y};
+        __nv_bfloat16* dst;
+        if (kind == 0) {
+            dst = q_out + ((long)row * n_heads + head) * 128;
+        } else {
+            if (kv_base < 0) continue;
+            const int kvh = head - n_heads - (kind == 2 ? n_kv_heads : 0);
+            dst = (kind == 1 ? k_pages : v_pages) + kv_base + (long)kvh * page_size * 128;
         }
-        // element i < 64 pairs with i + 64: lanes 0..15 hold the first halves, lanes 16..31 the second
-        const int i0 = 4 * (lane & 15);
-        const float4 c = *reinterpret_cast<const float4*>(cos_table + (long)pos * 64 + i0);
-        const float4 s = *reinterpret_cast<const float4*>(sin_table + (long)pos * 64 + i0);
-        const float cs[4] = {c.x, c.y, c.z, c.w}, sn[4] = {s.x, s.y, s.z, s.w};
+        if (kind != 2) {
+            const WT* w = kind == 0 ? q_weight : k_weight;
+            if (w != nullptr) {
+                float ss = x[0] * x[0] + x[1] * x[1] + x[2] * x[2] + x[3] * x[3];
+                ss = ib_warp_sum(ss);
+                const float inv = 1.0f / sqrtf(ss / 128.0f + eps);
 #pragma unroll
-        for (int e = 0; e < 4; ++e) {
-            const float other = __shfl_xor_sync(0xffffffffu, x[e], 16);
-            x[e] = lane < 16 ? x[e] * cs[e] - other * sn[e] : other * sn[e] + x[e] * cs[e];
+                for (int e = 0; e < 4; ++e) x[e] = x[e] * inv * ib_to_float(w[4 * lane + e]);
+            }
+#pragma unroll
+            for (int e = 0; e < 4; ++e) {
+                const float other = __shfl_xor_sync(0xffffffffu, x[e], 16);
+                x[e] = lane < 16 ? x[e] * cs[e] - other * sn[e] : other * sn[e] + x[e] * cs[e];
+            }
         }
+        uint2 o;
+        *reinterpret_cast<__nv_bfloat162*>(&o.x) = __floats2bfloat162_rn(x[0], x[1]);
+        *reinterpret_cast<__nv_bfloat162*>(&o.y) = __floats2bfloat162_rn(x[2], x[3]);
+        *reinterpret_cast<uint2*>(dst + 4 * lane) = o;
     }
-    uint2 o;
-    *reinterpret_cast<__nv_bfloat162*>(&o.x) = __floats2bfloat162_rn(x[0], x[1]);
-    *reinterpret_cast<__nv_bfloat162*>(&o.y) = __floats2bfloat162_rn(x[2], x[3]);
-    *reinterpret_cast<uint2*>(dst + 4 * lane) = o;
 }
 #endif
 
@@ -157,29 +195,32 @@ IB_EXPORT int ib_qk_norm_rope_store(const void* qkv, int row_stride, int n_rows,
 #if IB_ACT_BF16
     if (head_dim == 128 && rot_dim == 128 && (row_stride % 4) == 0 && ((uintptr_t)qkv % 8) == 0 &&
         ((uintptr_t)cos_table % 16) == 0 && ((uintptr_t)sin_table % 16) == 0) {
-        if (weight_is_f32)
-            ib_launch(qk_norm_rope_store_d128_kernel<float>, grid, 32 * QRS_WARPS, 0, stream, (const __nv_bfloat16*)qkv,
-                      row_stride, n_heads, n_kv_heads, store_kv, (const float*)q_weight, (const float*)k_weight, eps,
-                      cos_table, sin_table, positions, row_request, block_table, max_pages, page_size, n_pages,
-                      (__nv_bfloat16*)k_pages, (__nv_bfloat16*)v_pages, (__nv_bfloat16*)q_out);
-        else
-            ib_launch(qk_norm_rope_store_d128_kernel<__nv_bfloat16>, grid, 32 * QRS_WARPS, 0, stream,
-                      (const __nv_bfloat16*)qkv, row_stride, n_heads, n_kv_heads, store_kv,
-                      (const __nv_bfloat16*)q_weight, (const __nv_bfloat16*)k_weight, eps, cos_table, sin_table,
-                      positions, row_request, block_table, max_pages, page_size, n_pages, (__nv_bfloat16*)k_pages,
-                      (__nv_bfloat16*)v_pages, (__nv_bfloat16*)q_out);
+#define IB_LAUNCH_D128(WT, HPW)                                                                                    \
+    ib_launch(qk_norm_rope_store_d128_kernel<WT, HPW>, dim3(n_rows, (heads_total + QRS_WARPS * HPW - 1) / (QRS_WARPS * HPW)), \
+              32 * QRS_WARPS, 0, stream, (const __nv_bfloat16*)qkv, row_stride, n_heads, n_kv_heads, store_kv,          \
+              (const WT*)q_weight, (const WT*)k_weight, eps, cos_table, sin_table, table_rows, positions, row_request,  \
+              block_table, max_pages, page_size, n_pages, (__nv_bfloat16*)k_pages, (__nv_bfloat16*)v_pages,            \
+              (__nv_bfloat16*)q_out)
+        // few rows: one head per warp, for the shortest chain; many rows: four heads per warp, for bytes in flight
+        if (n_rows >= 256) {
+            if (weight_is_f32) IB_LAUNCH_D128(float, 4); else IB_LAUNCH_D128(__nv_bfloat16, 4);
+        } else {
+            if (weight_is_f32) IB_LAUNCH_D128(float, 1); else IB_LAUNCH_D128(__nv_bfloat16, 1);
+        }
+#undef IB_LAUNCH_D128
         return ib_launch_status();
     }
 #endif
     if (weight_is_f32)
         ib_launch(qk_norm_rope_store_kernel<float>, grid, 32 * QRS_WARPS, smem, stream,
             (const act_t*)qkv, row_stride, n_heads, n_kv_heads, head_dim, store_kv, (const float*)q_weight,
-            (const float*)k_weight, eps, cos_table, sin_table, rot_dim, positions, row_request, block_table,
+            (const float*)k_weight, eps, cos_table, sin_table, rot_dim, table_rows, positions, row_request, block_table,
             max_pages, page_size, n_pages, (act_t*)k_pages, (act_t*)v_pages, (act_t*)q_out);
     else
         ib_launch(qk_norm_rope_store_kernel<__nv_bfloat16>, grid, 32 * QRS_WARPS, smem, stream,
             (const act_t*)qkv, row_stride, n_heads, n_kv_heads, head_dim, store_kv, (const __nv_bfloat16*)q_weight,
-            (const __nv_bfloat16*)k_weight, eps, cos_table, sin_table, rot_dim, positions, row_request, block_table,
+            (const __nv_bfloat16*)k_weight, eps, cos_table, sin_table, rot_dim, table_rows, positions, row_request,
+            block_table,
             max_pages, page_size, n_pages, (act_t*)k_pages, (act_t*)v_pages, (act_t*)q_out);
     return ib_launch_status();
 }

@@ -101,6 +101,11 @@ class Engine:
     def has_work(self) -> bool:
         return not self.scheduler.idle
 
+    def warm_up(self, batch_sizes: Optional[Sequence[int]] = None) -> List[int]:
+        """Capture the decode graphs for the given numbers of requests (all, if none is given) before the
+        first request comes, so that no request waits for a capture."""
+        return self.runner.warm_up(batch_sizes)
+
     # ---- one scheduler iteration -----------------------------------------------------
     def step(self) -> List[Request]:
         """Plan, run and sample one step; returns the requests that finished in it."""

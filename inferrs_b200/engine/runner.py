@@ -63,6 +63,30 @@ class ModelRunner:
     def n_tokens(self, rid: Hashable) -> int:
         return self.manager.n_tokens(rid)
 
+    def warm_up(self, batch_sizes: Optional[Sequence[int]] = None) -> List[int]:
+        """Capture the decode graphs now instead of at the first step of each batch size (a capture takes
+        as long as a few hundred steps).  Only while no request is live; returns the sizes captured."""
+        if self.graphs is None or self.manager.n_live:
+            return []
+        done = []
+        for bucket in self.graphs.buckets:
+            if bucket in self.graphs.captured or (batch_sizes is not None and not any(
+                    self.graphs.bucket_for(min(b, self.graphs.buckets[-1])) == bucket for b in batch_sizes)):
+                continue
+            rids = [("warm-up", i) for i in range(bucket)]
+            wants = {rid: 1 for rid in rids}
+            for rid in rids:
+                self.admit(rid)
+            try:
+                if self.manager.can_reserve(wants):
+                    self.manager.reserve(wants)
+                    self.graphs.run([StepEntry(rid, [0], [0]) for rid in rids])
+                    done.append(bucket)
+            finally:
+                for rid in rids:
+                    self.release(rid)
+        return done
+
     # ---- the step -----------------------------------------------------------
     def prepare(self, entries: Sequence[StepEntry], fixed_pages: Optional[Sequence[int]] = None) -> StepContext:
         """Reserve pages for all entries (all or nothing: OutOfPages leaves the cache untouched) and

@@ -40,6 +40,7 @@ _SIGNATURES = {
                                    c_int, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_float, c_int, c_void_p,
                                    c_void_p],
     "ib_attention_tcgen05_error": [c_int],
+    "ib_row_fault": [c_int],
     "ib_paged_attention_decode": [c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_void_p, c_int, c_int,
                                   c_int, c_int, c_float, c_int, c_void_p, c_int, c_void_p, c_void_p, c_void_p, c_void_p],
     "ib_attention_decode_error": [c_int],
@@ -223,6 +224,15 @@ def qk_norm_rope_store(qkv: torch.Tensor, n_heads: int, n_kv_heads: int, head_di
         "qk_norm_rope_store")
 
 
+def row_fault(act_dtype: torch.dtype, reset: bool = True) -> Optional[int]:
+    """The first row that a kernel left out because its position lay outside the rotation tables (None if
+    there was none).  Waits for the device."""
+    v = _core(act_dtype).ib_row_fault(int(reset))
+    if v < 0:
+        raise KernelError(f"row_fault: CUDA error {-v}")
+    return None if v == 0 else v - 1
+
+
 def paged_attention_generic(q: torch.Tensor, k_pages: torch.Tensor, v_pages: torch.Tensor, block_table: torch.Tensor,
                             row_request: torch.Tensor, positions: torch.Tensor, scale: float, window: Optional[int],
                             out: torch.Tensor):
@@ -318,6 +328,21 @@ def linear(x: torch.Tensor, w: torch.Tensor, out: torch.Tensor, act_dtype: torch
         gemm_tn_tcgen05(x, w, out)
     else:
         gemm_tn_bf16(x, w, out)
+
+
+def gated_linear(x: torch.Tensor, w_gate_up: torch.Tensor, out: torch.Tensor, act_dtype: torch.dtype):
+    """out = silu(x @ gate.T) * (x @ up.T), ``w_gate_up`` [2 * inner, k] holding the gate matrix above the up
+    matrix.  A few bfloat16 rows run as one tcgen05 kernel; everything else as the product and the gate kernel."""
+    inner = out.shape[1]
+    if w_gate_up.shape[0] != 2 * inner:
+        raise KernelError(f"gated_linear: weights {tuple(w_gate_up.shape)} do not match out {tuple(out.shape)}")
+    if act_dtype == torch.bfloat16 and w_gate_up.dtype == torch.bfloat16 and x.shape[0] <= TCGEN05_MAX_TOKENS \
+            and tcgen05_gemm_supported(x, w_gate_up):
+        gemm_swiglu_tcgen05(x, w_gate_up, out)
+        return
+    gu = torch.empty((x.shape[0], 2 * inner), dtype=act_dtype, device=x.device)
+    linear(x, w_gate_up, gu, act_dtype)
+    silu_gate(gu, out)
 
 
 ARGMAX_CHUNK = 8192      # vocabulary entries per block of the two-stage argmax
@@ -558,6 +583,9 @@ def _gemm_lib():
         lib.ib_gemm_tn_tcgen05.argtypes = [c_void_p, c_long, c_void_p, c_long, c_void_p, c_long, c_int, c_int, c_int,
                                            c_int, c_int, c_void_p]
         lib.ib_gemm_tn_tcgen05.restype = c_int
+        lib.ib_gemm_swiglu_tcgen05.argtypes = [c_void_p, c_long, c_void_p, c_long, c_void_p, c_long, c_int, c_int, c_int,
+                                               c_void_p]
+        lib.ib_gemm_swiglu_tcgen05.restype = c_int
         lib.ib_gemm_tcgen05_error.argtypes = [c_int]
         lib.ib_gemm_tcgen05_error.restype = c_int
         lib.ib_gemm_tn_streamk.argtypes = [c_void_p, c_long, c_void_p, c_long, c_void_p, c_long, c_int, c_int, c_int,
@@ -592,6 +620,22 @@ def gemm_tn_tcgen05(x: torch.Tensor, w: torch.Tensor, out: torch.Tensor, split_k
     if code == -1:
         raise KernelError(f"gemm_tn_tcgen05: K={k} must be a multiple of 8 and the bases 16-byte aligned")
     _check(code, "gemm_tn_tcgen05")
+
+
+def gemm_swiglu_tcgen05(x: torch.Tensor, w_gate_up: torch.Tensor, out: torch.Tensor):
+    """out[t, f] = silu(x[t] . w[f]) * (x[t] . w[inner + f]): both products of a gated feed-forward and the gate
+    in one tcgen05 kernel (64 gate rows and the same 64 up rows per tile).  Up to 16 rows of x."""
+    _need(x, "x", (torch.bfloat16,), 2)
+    _need(w_gate_up, "w_gate_up", (torch.bfloat16,), 2)
+    _need(out, "out", (torch.bfloat16,), 2)
+    n, k = x.shape
+    inner = out.shape[1]
+    if w_gate_up.shape != (2 * inner, k) or out.shape[0] != n:
+        raise KernelError(f"gemm_swiglu: x {tuple(x.shape)}, w {tuple(w_gate_up.shape)}, out {tuple(out.shape)}")
+    code = _gemm_lib().ib_gemm_swiglu_tcgen05(_p(x), k, _p(w_gate_up), k, _p(out), inner, n, inner, k, _stream())
+    if code == -1:
+        raise KernelError(f"gemm_swiglu_tcgen05: at most 16 rows (got {n}), K={k} a multiple of 8, 16-byte aligned bases")
+    _check(code, "gemm_swiglu_tcgen05")
 
 
 def gemm_tcgen05_set_pdl(on: bool):

@@ -15,7 +15,8 @@ from .spec import GatedDenseSpec, TensorDecl
 class GatedDense:
     """down( silu(gate(x)) * up(x) ), silu(z) = z / (1 + exp(-z))
     (inferrs-models/src/models/attention_utils.rs:94-118; inferrs-kernels/candle-kernels/src/unary.cu:58-61).
-    Gate and up weights are stacked at load, so one product feeds the gate kernel."""
+    Gate and up weights are stacked at load: one product feeds the gate kernel, or, for a few rows, one
+    kernel does both products and the gate."""
 
     graph_safe = True  # launches depend only on shapes, never on the step's host-side values
 
@@ -34,9 +35,8 @@ class GatedDense:
         self.down = Linear(weights[spec.down_proj], rt)
 
     def forward(self, ctx, h: torch.Tensor) -> torch.Tensor:
-        gu = self.gate_up(h)
         a = torch.empty((h.shape[0], self.spec.inner), dtype=self.rt.dtype, device=h.device)
-        kernels.silu_gate(gu, a)
+        kernels.gated_linear(h, self.gate_up.weight, a, self.rt.dtype)
         return self.down(a)
 
 

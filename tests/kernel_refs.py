@@ -114,12 +114,17 @@ def linear(x, w, out, act_dtype=None):
     out.copy_((x.float() @ w.float().t()).to(out.dtype))
 
 
+def gated_linear(x, w_gate_up, out, act_dtype=None):
+    gu = (x.float() @ w_gate_up.float().t()).to(out.dtype)
+    silu_gate(gu, out)
+
+
 def argmax(logits, out, act_dtype=None):
     out.copy_(torch.argmax(logits, dim=-1).to(out.dtype))
 
 
 _NAMES = ["embedding_gather", "add_rms_norm", "silu_gate", "qk_norm_rope_store", "paged_attention_generic",
-          "paged_attention", "gemm_tn_simt", "gemm_tn_bf16", "linear", "argmax"]
+          "paged_attention", "gemm_tn_simt", "gemm_tn_bf16", "linear", "gated_linear", "argmax"]
 
 
 def install(monkeypatch):

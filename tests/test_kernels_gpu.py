@@ -131,6 +131,49 @@ def test_qk_norm_rope_store(dtype, nh, nkv, d, rot, ps):
     assert rel_err(q1, q2) < TOL[dtype]
 
 
+@pytest.mark.parametrize("nh,nkv", [(8, 2), (5, 1), (3, 3)])
+def test_qk_norm_rope_store_many_rows(nh, nkv):
+    """Hundreds of rows at head size 128 in bfloat16: the form that takes four heads per warp (head counts
+    that are no multiple of four leave a warp with fewer)."""
+    from inferrs_b200 import kernels as K
+    dtype, d, ps = torch.bfloat16, 128, 16
+    lens, new = [310, 75], [290, 75]
+    table, positions, row_request, k_pages, v_pages = _paged_setup(dtype, nkv, d, ps, lens, new, 17)
+    n = sum(new)
+    qkv = rand((n, (nh + 2 * nkv) * d), dtype, 18)
+    wq = (1 + 0.1 * rand((d,), torch.float32, 19)).to(dtype)
+    wk = (1 + 0.1 * rand((d,), torch.float32, 20)).to(dtype)
+    ang = torch.arange(320, dtype=torch.float32)[:, None] * (1.0 / 10000 ** (torch.arange(d // 2) * 2.0 / d))[None]
+    cos, sin = torch.cos(ang).to(dev()), torch.sin(ang).to(dev())
+    k1, v1, k2, v2 = k_pages.clone(), v_pages.clone(), k_pages.clone(), v_pages.clone()
+    q1 = torch.empty((n, nh, d), dtype=dtype, device=dev())
+    q2 = torch.empty_like(q1)
+    K.qk_norm_rope_store(qkv, nh, nkv, d, True, wq, wk, 1e-6, cos, sin, d, positions, row_request, table, k1, v1, q1)
+    R.qk_norm_rope_store(qkv, nh, nkv, d, True, wq, wk, 1e-6, cos, sin, d, positions, row_request, table, k2, v2, q2)
+    assert rel_err(q1, q2) < TOL[dtype]
+    assert rel_err(k1, k2) < TOL[dtype]
+    assert torch.equal(v1, v2)
+    assert K.row_fault(dtype) is None
+
+
+@pytest.mark.parametrize("dtype,d", [(torch.float32, 48), (torch.bfloat16, 128)])
+def test_a_position_outside_the_rotation_tables_is_left_out_and_reported(dtype, d):
+    """The kernel reads no table row that does not exist: such a row writes nothing and is reported."""
+    from inferrs_b200 import kernels as K
+    nh, nkv, ps = 4, 2, 16
+    table, positions, row_request, k_pages, v_pages = _paged_setup(dtype, nkv, d, ps, [40], [6], 27)
+    qkv = rand((6, (nh + 2 * nkv) * d), dtype, 28)
+    ang = torch.arange(37, dtype=torch.float32)[:, None] * (1.0 / 10000 ** (torch.arange(d // 2) * 2.0 / d))[None]
+    cos, sin = torch.cos(ang).to(dev()), torch.sin(ang).to(dev())   # positions 34..39 come; the tables end at 36
+    k1, v1 = k_pages.clone(), v_pages.clone()
+    q1 = torch.full((6, nh, d), 7.0, dtype=dtype, device=dev())
+    assert K.row_fault(dtype) is None
+    K.qk_norm_rope_store(qkv, nh, nkv, d, True, None, None, 1e-6, cos, sin, d, positions, row_request, table, k1, v1, q1)
+    assert K.row_fault(dtype) in (3, 4, 5)
+    assert K.row_fault(dtype) is None          # reading it clears it
+    assert bool((q1[3:] == 7.0).all()) and not bool((q1[:3] == 7.0).any())
+
+
 @pytest.mark.parametrize("dtype", DTYPES)
 @pytest.mark.parametrize("nh,nkv,d,ps,window", [(6, 3, 48, 8, None), (4, 2, 16, 4, 9), (8, 2, 128, 16, None),
                                                 (5, 5, 80, 16, 33), (2, 1, 256, 16, None)])
@@ -301,6 +344,32 @@ def test_gemm_tn_tcgen05(n, m, k):
             assert K.gemm_tcgen05_error() == 0
             # float32 sums of up to 12,288 products of magnitude ~1: about 1e-5 of the largest result
             assert rel_err(out, ref) < (1e-2 if od == torch.bfloat16 else 3e-5), (od, split)
+
+
+@pytest.mark.parametrize("n,inner,k", [(1, 192, 256), (8, 12288, 4096), (5, 200, 136), (16, 64, 64), (3, 1000, 520)])
+def test_gemm_swiglu_tcgen05(n, inner, k):
+    """Both products of a gated feed-forward and the gate in one kernel, against the two-step reference; inner
+    sizes that are no multiple of the 64-row tile, a K that ends inside a 64-wide block."""
+    from inferrs_b200 import kernels as K
+    x = rand((n, k), torch.bfloat16, 41)
+    w = rand((2 * inner, k), torch.bfloat16, 42, scale=k ** -0.5)
+    out = torch.empty((n, inner), dtype=torch.bfloat16, device=dev())
+    K.gemm_swiglu_tcgen05(x, w, out)
+    gu = (x.float() @ w.float().t())
+    g, u = gu[:, :inner].bfloat16().float(), gu[:, inner:].bfloat16().float()
+    want = g / (1.0 + torch.exp(-g)) * u
+    assert K.gemm_tcgen05_error() == 0
+    assert rel_err(out, want) < 1e-2
+    # the same through the dispatcher, and the two-kernel form for more rows than the fused kernel takes
+    out2 = torch.empty_like(out)
+    K.gated_linear(x, w, out2, torch.bfloat16)
+    assert torch.equal(out, out2)
+    xl = rand((40, k), torch.bfloat16, 43)
+    outl = torch.empty((40, inner), dtype=torch.bfloat16, device=dev())
+    K.gated_linear(xl, w, outl, torch.bfloat16)
+    gl = (xl.float() @ w.float().t())
+    g, u = gl[:, :inner].bfloat16().float(), gl[:, inner:].bfloat16().float()
+    assert rel_err(outl, g / (1.0 + torch.exp(-g)) * u) < 1e-2
 
 
 @pytest.mark.parametrize("n,m,k", [(1, 4096, 4096), (8, 6144, 4096), (17, 300, 136), (64, 517, 96), (33, 128, 64),

@@ -118,3 +118,21 @@ def test_sampled_generation_in_portions_with_preemption(model_dirs):
     assert eng.stats()["preemptions"] > 0
     for p, g in zip(prompts, got):
         assert g == _plain_generate(model_dirs[name], p, 24, seed=4, **opts)
+
+
+def test_warm_up_captures_every_batch_size_and_changes_nothing(model_dirs):
+    """Graphs captured before the first request (with stand-in requests that are released again) give the
+    tokens that graphs captured on demand give; the cache is whole afterwards."""
+    from inferrs_b200 import Engine
+    prompts = [random_tokens(n, CONFIG_B["vocab_size"], seed=90 + n) for n in (3, 12, 21)]
+    kw = dict(dtype="f32", block_size=PAGE_SIZE["B"], num_blocks=64, max_batch_size=6)
+    cold = Engine(model_dirs["B"], **kw)
+    want = cold.generate(prompts, SamplingParams.greedy(max_tokens=12))
+    warm = Engine(model_dirs["B"], **kw)
+    assert warm.warm_up([3]) == [4]
+    assert warm.warm_up() == [1, 2, 6]
+    assert warm.warm_up() == []
+    warm.runner.manager.check_invariants()
+    assert warm.stats()["free_pages"] == warm.stats()["pages"]
+    assert warm.generate(prompts, SamplingParams.greedy(max_tokens=12)) == want
+    assert sorted(warm.runner.graphs.captured) == [1, 2, 4, 6]
