@@ -108,7 +108,11 @@ __global__ void __launch_bounds__(THREADS, 2) decode_kernel(const __grid_constan
     const unsigned full0 = smem_u32(bars), empty0 = smem_u32(bars + STAGES);
     int* s_flag = reinterpret_cast<int*>(bars + 2 * STAGES);
 
-    ib_grid_dependency_sync();
+    // Under programmatic dependent launch this kernel may start while the kernels before it still run.  What
+    // they do not write is used at once: the step's description (positions, block table) and the keys and
+    // values of earlier steps, so the first tiles of the ring are on their way early.  The queries and the
+    // tile that holds this step's own key and value are touched only after griddepcontrol.wait.
+    asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const int req = blockIdx.x, kvh = blockIdx.y, split = blockIdx.z;
     const int G = P.n_heads / P.n_kv_heads;
@@ -131,6 +135,7 @@ __global__ void __launch_bounds__(THREADS, 2) decode_kernel(const __grid_constan
     __syncthreads();   // the barriers are ready: the producer starts at once
     bool ok = true;
     if (warp < 4) {
+        asm volatile("griddepcontrol.wait;" ::: "memory");
         // queries of the group: rows 0..G-1, the rest of the 16 rows are zero (the four compute warps only)
         for (int idx = threadIdx.x; idx < 16 * (D / 8); idx += 128) {
             const int r = idx / (D / 8), c = idx - r * (D / 8);
@@ -157,7 +162,14 @@ __global__ void __launch_bounds__(THREADS, 2) decode_kernel(const __grid_constan
             return page;
         };
         int page_next = n_tiles > 0 ? lookup(0) : 0;
+        // tiles that end before this step's position hold only keys of earlier steps: up to a ring of them
+        // is asked for before the kernels before this one are waited for
+        int n_early = pos / KEYS - t_begin;
+        n_early = n_early < 0 ? 0 : (n_early > n_tiles ? n_tiles : n_early);
+        n_early = n_early > STAGES ? STAGES : n_early;
+        bool waited = false;
         for (int i = 0; i < n_tiles; ++i) {
+            if (i == n_early) { asm volatile("griddepcontrol.wait;" ::: "memory"); waited = true; }
             const int s = i % STAGES;
             const int page = page_next;
             if (i + 1 < n_tiles) page_next = lookup(i + 1);
@@ -175,6 +187,7 @@ __global__ void __launch_bounds__(THREADS, 2) decode_kernel(const __grid_constan
                 tma_load_2d(smem_u32(sv + s * TILE_BYTES + HALF_BYTES) + off, &map_v, 64, grow, full0 + 8 * s);
             }
         }
+        if (!waited) asm volatile("griddepcontrol.wait;" ::: "memory");   // the loop never reached it
     } else {
 #pragma unroll
         for (int n = 0; n < D / 8; ++n)

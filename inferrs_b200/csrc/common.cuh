@@ -76,6 +76,15 @@ __device__ __forceinline__ void ib_grid_dependency_sync() {
     asm volatile("griddepcontrol.wait;" ::: "memory");
 }
 
+// The two halves on their own, for kernels that fetch what no kernel writes (weights, tables, the step's
+// description) between them.
+__device__ __forceinline__ void ib_grid_dependency_launch() {
+    asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
+}
+__device__ __forceinline__ void ib_grid_dependency_wait() {
+    asm volatile("griddepcontrol.wait;" ::: "memory");
+}
+
 extern int ib_pdl_enabled;  // one per library, defined beside its exported setter ib_set_pdl
 
 template <typename... KArgs, typename... Args>

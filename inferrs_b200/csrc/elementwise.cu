@@ -85,13 +85,22 @@ __global__ void add_rms_norm_vec4_kernel(float* __restrict__ residual, const act
                                          const WT* __restrict__ weight, act_t* __restrict__ out,
                                          const int* __restrict__ rows, int width, float eps) {
     __shared__ float red[32];
-    ib_grid_dependency_sync();
+    ib_grid_dependency_launch();
+    const int n4 = width >> 2;
+    // the norm's weights are fetched while the kernel before this one still runs
+    const WVec4<WT>* w4 = reinterpret_cast<const WVec4<WT>*>(weight);
+    WVec4<WT> wk[NORM_KEEP];
+#pragma unroll
+    for (int k = 0; k < NORM_KEEP; ++k) {
+        const int j = threadIdx.x + k * blockDim.x;
+        if (j < n4) wk[k] = w4[j];
+    }
+    ib_grid_dependency_wait();
     const int r = blockIdx.x;
     const int src = rows ? rows[r] : r;
     float4* res = reinterpret_cast<float4*>(residual + (size_t)src * width);
     const ActVec4* del = delta ? reinterpret_cast<const ActVec4*>(delta + (size_t)src * width) : nullptr;
     const bool write_back = (rows == nullptr) && (del != nullptr);
-    const int n4 = width >> 2;
     // the row stays in registers between the two passes (the host picks a block size that makes it fit)
     float4 keep[NORM_KEEP];
     float ss = 0.0f;
@@ -113,13 +122,12 @@ __global__ void add_rms_norm_vec4_kernel(float* __restrict__ residual, const act
     ss = ib_block_sum(ss, red);
     const float inv = 1.0f / sqrtf(ss / (float)width + eps);
     ActVec4* dst = reinterpret_cast<ActVec4*>(out + (size_t)r * width);
-    const WVec4<WT>* w4 = reinterpret_cast<const WVec4<WT>*>(weight);
 #pragma unroll
     for (int k = 0; k < NORM_KEEP; ++k) {
         const int j = threadIdx.x + k * blockDim.x;
         if (j >= n4) break;
         const float4 v = keep[k];
-        const WVec4<WT> w = w4[j];
+        const WVec4<WT> w = wk[k];
         ActVec4 o;
         o.v[0] = ib_from_float<act_t>(v.x * inv * ib_to_float(w.v[0]));
         o.v[1] = ib_from_float<act_t>(v.y * inv * ib_to_float(w.v[1]));

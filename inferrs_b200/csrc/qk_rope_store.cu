@@ -115,7 +115,9 @@ __global__ void qk_norm_rope_store_d128_kernel(
     const int* __restrict__ positions, const int* __restrict__ row_request,
     const int* __restrict__ block_table, int max_pages, int page_size, int n_pages,
     __nv_bfloat16* __restrict__ k_pages, __nv_bfloat16* __restrict__ v_pages, __nv_bfloat16* __restrict__ q_out) {
-    ib_grid_dependency_sync();
+    // the step's description, the tables and the weights are written by no kernel: they are fetched while the
+    // kernel before this one still runs; the projection's output only after it has finished
+    ib_grid_dependency_launch();
     const int row = blockIdx.x;
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const int heads_total = n_heads + (store_kv ? 2 * n_kv_heads : 0);
@@ -123,11 +125,6 @@ __global__ void qk_norm_rope_store_d128_kernel(
     if (head0 >= heads_total) return;
     const int pos = positions[row];
     if (pos < 0 || pos >= table_rows) { ib_note_row_fault(row); return; }
-    uint2 raw[HPW];
-#pragma unroll
-    for (int h = 0; h < HPW; ++h)
-        if (head0 + h < heads_total)
-            raw[h] = *reinterpret_cast<const uint2*>(qkv + (long)row * row_stride + (long)(head0 + h) * 128 + 4 * lane);
     long kv_base = -1;  // element offset of (page, kv head 0, place in the page, 0)
     if (store_kv && head0 + HPW > n_heads) {
         const int req = row_request[row];
@@ -139,6 +136,18 @@ __global__ void qk_norm_rope_store_d128_kernel(
     const float4 c = *reinterpret_cast<const float4*>(cos_table + (long)pos * 64 + i0);
     const float4 s = *reinterpret_cast<const float4*>(sin_table + (long)pos * 64 + i0);
     const float cs[4] = {c.x, c.y, c.z, c.w}, sn[4] = {s.x, s.y, s.z, s.w};
+    float wq[4] = {1.0f, 1.0f, 1.0f, 1.0f}, wk[4] = {1.0f, 1.0f, 1.0f, 1.0f};
+#pragma unroll
+    for (int e = 0; e < 4; ++e) {
+        if (q_weight != nullptr && head0 < n_heads) wq[e] = ib_to_float(q_weight[4 * lane + e]);
+        if (k_weight != nullptr && head0 + HPW > n_heads) wk[e] = ib_to_float(k_weight[4 * lane + e]);
+    }
+    ib_grid_dependency_wait();
+    uint2 raw[HPW];
+#pragma unroll
+    for (int h = 0; h < HPW; ++h)
+        if (head0 + h < heads_total)
+            raw[h] = *reinterpret_cast<const uint2*>(qkv + (long)row * row_stride + (long)(head0 + h) * 128 + 4 * lane);
 #pragma unroll
     for (int h = 0; h < HPW; ++h) {
         const int head = head0 + h;
@@ -162,7 +171,7 @@ __global__ void qk_norm_rope_store_d128_kernel(
                 ss = ib_warp_sum(ss);
                 const float inv = 1.0f / sqrtf(ss / 128.0f + eps);
 #pragma unroll
-                for (int e = 0; e < 4; ++e) x[e] = x[e] * inv * ib_to_float(w[4 * lane + e]);
+                for (int e = 0; e < 4; ++e) x[e] = x[e] * inv * (kind == 0 ? wq[e] : wk[e]);
             }
 #pragma unroll
             for (int e = 0; e < 4; ++e) {

@@ -73,7 +73,17 @@ def _core(act_dtype: torch.dtype):
     return lib
 
 
+_RAW_STREAM = getattr(torch._C, "_cuda_getCurrentRawStream", None)
+_DEVICE_INDEX = None
+
+
 def _stream() -> int:
+    """The current CUDA stream's handle (the short way where this torch has it: a launch asks for it every time)."""
+    global _DEVICE_INDEX
+    if _RAW_STREAM is not None:
+        if _DEVICE_INDEX is None:
+            _DEVICE_INDEX = torch.cuda.current_device()   # one process drives one GPU
+        return _RAW_STREAM(_DEVICE_INDEX)
     return torch.cuda.current_stream().cuda_stream
 
 

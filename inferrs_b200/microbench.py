@@ -4,6 +4,7 @@
     python -m inferrs_b200.microbench attention --form decode --batch 8 --context 2048
     python -m inferrs_b200.microbench attention --form prefill --tokens 2048
     python -m inferrs_b200.microbench chain --impl library --m 8 --layers 8
+    python -m inferrs_b200.microbench step --form decode --batch 8 --context 2048 --layers 8
 
 Every case is timed with CUDA events after warm-up; between timed launches a buffer larger than the
 L2 cache is written, so each launch starts cold.  One JSON line per case.
@@ -142,6 +143,78 @@ def chain(args) -> dict:
             "GBps": round(byts / us / 1e3, 1)}
 
 
+def step(args) -> dict:
+    """A whole step of a random model with Qwen3-8B layer sizes (fewer layers, so that it is quick): the
+    time per layer of a decode step at a batch size and context length, or of one prompt portion."""
+    from .engine.batch import StepEntry
+    from .engine.loading import random_model
+    from .engine.runner import ModelRunner
+    from .runtime import Runtime
+    config = {"architectures": ["Qwen3ForCausalLM"], "model_type": "qwen3", "num_hidden_layers": args.layers,
+              "hidden_size": args.hidden, "num_attention_heads": args.heads, "num_key_value_heads": args.kv_heads,
+              "head_dim": args.head_dim, "intermediate_size": args.inner, "vocab_size": args.vocab,
+              "rope_theta": 1000000.0, "rms_norm_eps": 1e-6, "max_position_embeddings": args.max_context,
+              "tie_word_embeddings": False, "hidden_act": "silu"}
+    rt = Runtime.cuda(torch.bfloat16)
+    spec, weights, _ = random_model(config, 0, rt)
+    ps = args.page_size
+    n_req = args.batch if args.form == "decode" else 1
+    per_req = (args.max_context + ps - 1) // ps
+    runner = ModelRunner(spec, weights, rt, page_size=ps, n_pages=n_req * per_req, max_requests=n_req,
+                         max_context=args.max_context)
+    g = torch.Generator().manual_seed(1)
+    toks = lambda n: torch.randint(0, args.vocab, (n,), generator=g).tolist()  # noqa: E731
+    h, inner, nh, nkv, d = args.hidden, args.inner, args.heads, args.kv_heads, args.head_dim
+    layer_params = (nh + 2 * nkv) * d * h + nh * d * h + 3 * h * inner
+    if args.form == "decode":
+        rids = list(range(args.batch))
+        for i in range(0, args.batch, 4):
+            for r in rids[i:i + 4]:
+                runner.admit(r)
+            runner.step([StepEntry(r, toks(args.context), []) for r in rids[i:i + 4]])
+        one = toks(args.batch)
+        n_steps = min(args.iters, args.max_context - args.context - 4)
+        for _ in range(3):
+            runner.step([StepEntry(r, [t], [0]) for r, t in zip(rids, one)], own_output=False)
+        torch.cuda.synchronize()
+        a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        a.record()
+        for _ in range(n_steps):
+            runner.step([StepEntry(r, [t], [0]) for r, t in zip(rids, one)], own_output=False)
+        b.record()
+        torch.cuda.synchronize()
+        us = a.elapsed_time(b) * 1e3 / n_steps
+        head_bytes = 2 * args.vocab * h
+        byts = 2 * args.layers * layer_params + head_bytes + args.batch * args.context * 2 * args.layers * nkv * d * 2
+        return {"kernel": "step/decode", "batch": args.batch, "context": args.context, "layers": args.layers,
+                "us_per_step": round(us, 1), "us_per_layer": round((us - head_bytes / 6.3e6) / args.layers, 2),
+                "tokens_per_s_at_36_layers": round(args.batch * 1e6 / ((us - head_bytes / 6.3e6) / args.layers * 36
+                                                                       + head_bytes / 6.3e6), 1),
+                "GBps": round(byts / us / 1e3, 1), "note": "per layer: the step less the head product at 6.3 TB/s"}
+    times = []
+    for i in range(args.iters + 2):
+        runner.admit(i)
+        if args.context_before:
+            runner.step([StepEntry(i, toks(args.context_before), [])])
+        p = toks(args.tokens)
+        torch.cuda.synchronize()
+        a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        a.record()
+        runner.step([StepEntry(i, p, [args.tokens - 1])])
+        b.record()
+        torch.cuda.synchronize()
+        runner.release(i)
+        if i >= 2:
+            times.append(a.elapsed_time(b) * 1e3)
+    times.sort()
+    us = times[len(times) // 2]
+    t, c = args.tokens, args.context_before
+    flops = args.layers * (2 * t * layer_params + 4 * nh * d * (t * c + t * (t + 1) // 2)) + 2 * args.vocab * h
+    return {"kernel": "step/prefill", "tokens": t, "context_before": c, "layers": args.layers,
+            "us_per_step": round(us, 1), "us_per_layer": round(us / args.layers, 1),
+            "TFLOPs": round(flops / us / 1e6, 1)}
+
+
 def main(argv=None) -> int:
     ap = argparse.ArgumentParser(prog="inferrs_b200.microbench", description=__doc__,
                                  formatter_class=argparse.RawDescriptionHelpFormatter)
@@ -180,6 +253,23 @@ def main(argv=None) -> int:
     c.add_argument("--iters", type=int, default=10)
     c.add_argument("--pdl", action="store_true", help="tcgen05 only: programmatic dependent launch between the products")
     c.set_defaults(fn=chain)
+    st = sub.add_parser("step")
+    st.add_argument("--form", choices=["decode", "prefill"], default="decode")
+    st.add_argument("--batch", type=int, default=8)
+    st.add_argument("--context", type=int, default=2048)
+    st.add_argument("--tokens", type=int, default=2048)
+    st.add_argument("--context-before", type=int, default=0)
+    st.add_argument("--max-context", type=int, default=4096)
+    st.add_argument("--layers", type=int, default=8)
+    st.add_argument("--hidden", type=int, default=4096)
+    st.add_argument("--inner", type=int, default=12288)
+    st.add_argument("--heads", type=int, default=32)
+    st.add_argument("--kv-heads", type=int, default=8)
+    st.add_argument("--head-dim", type=int, default=128)
+    st.add_argument("--vocab", type=int, default=151936)
+    st.add_argument("--page-size", type=int, default=16)
+    st.add_argument("--iters", type=int, default=64)
+    st.set_defaults(fn=step)
     args = ap.parse_args(argv)
     print(json.dumps(args.fn(args)))
     return 0
