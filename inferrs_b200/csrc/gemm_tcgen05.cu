@@ -282,7 +282,7 @@ __global__ void __launch_bounds__(THREADS, (BN <= 64 ? 2 : 1)) gemm_kernel(const
     if (splits > 1 && SCATTER) cluster_wait();
     const unsigned my_rank = splits > 1 ? cluster_rank() : 0;
     const int owned = BM / splits;             // SCATTER: rows of the tile that each CTA of the cluster sums and stores
-    const unsigned owner = (unsigned)(q * 32 / owned);
+    const unsigned owner = (unsigned)(row / owned);   // per lane: with eight CTAs a warp's rows have two owners
     const int row_local = row - (int)owner * owned;
     if constexpr (MODE == 1) {
         // Gated form (one CTA per tile, no cluster): lanes 0..63 of the accumulator hold 64 features of the
@@ -508,7 +508,7 @@ static int launch(const CUtensorMap& mw, const CUtensorMap& mx, const Params& p,
 }  // namespace tc
 
 // x [n_tok, k] (row stride ldx), w [n_out, k] (row stride ldw), both bfloat16; y [n_tok, n_out] bfloat16 or float32.
-// split_k: 0 lets the function choose (1, 2 or 4 CTAs per output tile).
+// split_k: 0 lets the function choose (1, 2 or 4 CTAs per output tile); 8 is taken for up to 32 tokens (4 stands in beyond).
 IB_EXPORT int ib_gemm_tn_tcgen05(const void* x, long ldx, const void* w, long ldw, void* y, long ldy, int y_is_f32,
                                  int n_tok, int n_out, int k, int split_k, cudaStream_t stream) {
     if (n_tok <= 0 || n_out <= 0) return IB_OK;
@@ -526,7 +526,8 @@ IB_EXPORT int ib_gemm_tn_tcgen05(const void* x, long ldx, const void* w, long ld
     }
     if (bn == 256) splits = 1;
     while (splits > 1 && (p.num_kb + splits - 1) / splits * (splits - 1) >= p.num_kb) splits >>= 1;  // no empty part
-    if (splits != 1 && splits != 2 && splits != 4) return IB_ERR_ARGUMENT;
+    if (splits != 1 && splits != 2 && splits != 4 && splits != 8) return IB_ERR_ARGUMENT;
+    if (splits == 8 && bn > 32) splits = 4;               // eight only where the owners sum the parts
     CUtensorMap mw, mx;
     if (!tc::make_map(&mw, w, n_out, k, ldw, tc::BM) || !tc::make_map(&mx, x, n_tok, k, ldx, bn)) return IB_ERR_UNSUPPORTED;
     switch (bn) {

@@ -10,6 +10,8 @@ from __future__ import annotations
 import ctypes
 from typing import Optional
 
+import os
+
 import torch
 
 from .csrc.build import load_library
@@ -346,7 +348,8 @@ def gated_linear(x: torch.Tensor, w_gate_up: torch.Tensor, out: torch.Tensor, ac
     inner = out.shape[1]
     if w_gate_up.shape[0] != 2 * inner:
         raise KernelError(f"gated_linear: weights {tuple(w_gate_up.shape)} do not match out {tuple(out.shape)}")
-    if act_dtype == torch.bfloat16 and w_gate_up.dtype == torch.bfloat16 and x.shape[0] <= TCGEN05_MAX_TOKENS \
+    if act_dtype == torch.bfloat16 and w_gate_up.dtype == torch.bfloat16 \
+            and x.shape[0] <= min(TCGEN05_MAX_TOKENS, SWIGLU_MAX_TOKENS) \
             and tcgen05_gemm_supported(x, w_gate_up):
         gemm_swiglu_tcgen05(x, w_gate_up, out)
         return
@@ -667,7 +670,10 @@ def set_pdl(on: bool, act_dtype: torch.dtype = torch.bfloat16):
         gemm_tcgen05_set_pdl(on)
 
 
-TCGEN05_MAX_TOKENS = 8  # up to this many rows the own tcgen05 product is the faster one in a decode step
+# up to this many rows the own tcgen05 product is the faster one in a decode step (the environment variable is
+# there for measuring other thresholds)
+TCGEN05_MAX_TOKENS = int(os.environ.get("INFERRS_B200_TCGEN05_MAX_TOKENS", "16"))
+SWIGLU_MAX_TOKENS = 16  # rows that the fused gate/up kernel takes
 
 
 def gemm_tcgen05_error(reset: bool = True) -> int:

@@ -338,7 +338,7 @@ def test_gemm_tn_tcgen05(n, m, k):
     x, w = rand((n, k), torch.bfloat16, 70), rand((m, k), torch.bfloat16, 71)
     ref = x.double() @ w.double().t()
     for od in (torch.bfloat16, torch.float32):
-        for split in (0, 1, 2, 4):
+        for split in (0, 1, 2, 4, 8):
             out = torch.full((n, m), float("nan"), dtype=od, device=dev())
             K.gemm_tn_tcgen05(x, w, out, split)
             assert K.gemm_tcgen05_error() == 0
