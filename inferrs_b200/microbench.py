@@ -5,6 +5,7 @@
     python -m inferrs_b200.microbench attention --form prefill --tokens 2048
     python -m inferrs_b200.microbench chain --impl library --m 8 --layers 8
     python -m inferrs_b200.microbench step --form decode --batch 8 --context 2048 --layers 8
+    python -m inferrs_b200.microbench step --form decode --batch 8 --context 2048 --layers 3 --trace
 
 Every case is timed with CUDA events after warm-up; between timed launches a buffer larger than the
 L2 cache is written, so each launch starts cold.  One JSON line per case.
@@ -143,6 +144,30 @@ def chain(args) -> dict:
             "GBps": round(byts / us / 1e3, 1)}
 
 
+def _trace(fn, args) -> dict:
+    """When every kernel of one step started and ended on the device (CUPTI activity records through
+    torch.profiler): kernels that were launched early show their overlap with the kernels before them.
+    Times under the profiler are a little longer than without it: read the shares."""
+    from torch.profiler import ProfilerActivity, profile
+    with profile(activities=[ProfilerActivity.CUDA]) as prof:
+        fn()
+        fn()
+        torch.cuda.synchronize()
+    ev = [e for e in prof.events() if e.device_type == torch.autograd.DeviceType.CUDA and "Memcpy" not in e.name]
+    ev.sort(key=lambda e: e.time_range.start)
+    ev = ev[len(ev) // 2:]                      # the second of the two steps
+    t0 = ev[0].time_range.start
+    print(f"{'start us':>9} {'end us':>9} {'after the kernel before':>24}  kernel")
+    prev_end = None
+    for e in ev:
+        a, b = e.time_range.start - t0, e.time_range.end - t0
+        step_us = "" if prev_end is None else f"{b - prev_end:8.2f}"
+        print(f"{a:9.2f} {b:9.2f} {step_us:>24}  {e.name[:60]}")
+        prev_end = b if prev_end is None else max(prev_end, b)
+    return {"kernel": "step/decode trace", "batch": args.batch, "context": args.context, "layers": args.layers,
+            "kernels": len(ev), "us_first_start_to_last_end": round(prev_end, 1)}
+
+
 def step(args) -> dict:
     """A whole step of a random model with Qwen3-8B layer sizes (fewer layers, so that it is quick): the
     time per layer of a decode step at a batch size and context length, or of one prompt portion."""
@@ -177,6 +202,9 @@ def step(args) -> dict:
         for _ in range(3):
             runner.step([StepEntry(r, [t], [0]) for r, t in zip(rids, one)], own_output=False)
         torch.cuda.synchronize()
+        if args.trace:
+            return _trace(lambda: runner.step([StepEntry(r, [t], [0]) for r, t in zip(rids, one)], own_output=False),
+                          args)
         a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
         a.record()
         for _ in range(n_steps):
@@ -269,6 +297,7 @@ def main(argv=None) -> int:
     st.add_argument("--vocab", type=int, default=151936)
     st.add_argument("--page-size", type=int, default=16)
     st.add_argument("--iters", type=int, default=64)
+    st.add_argument("--trace", action="store_true", help="decode form: print when every kernel of one step started and ended")
     st.set_defaults(fn=step)
     args = ap.parse_args(argv)
     print(json.dumps(args.fn(args)))
