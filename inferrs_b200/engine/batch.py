@@ -196,4 +196,4 @@ def build_context(entries: Sequence[StepEntry], manager: CacheManager, storage: 
         slots=views[5], logit_rows=views[6],
         block_tables=[views[7 + g].view(nreq, tables[g].shape[1]) for g in range(len(tables))],
         storage=storage, n_rows=n, n_requests=nreq, q_lens=q_lens, kv_lens=kv_lens, slot_list=slots,
-        max_q_len=max(q_lens), max_kv_len=max(kv_lens), extra={"n_real": n_real, "wanted": wanted})
+        max_q_len=max(q_lens), max_kv_len=max(kv_lens), extra={"n_real": n_real, "wanted": wanted, "host": host})

@@ -294,3 +294,55 @@ def test_toy_mixer_with_state_is_registered_built_and_stepped(dtype):
     runner.release("again")
     tail = run_cut(runner, "tail", toks[0][30:], [30])
     assert rel_err(tail, whole[0][30:]) > 10 * tol
+
+
+def test_replayed_steps_keep_their_description_up_to_date_in_place():
+    """Decode steps are replayed graphs whose description is updated in place on the host when the same
+    requests come again one token further: after every step it must equal the description built anew,
+    across page edges, with a window group that gives pages back, and when requests come and go."""
+    import numpy as np
+    from inferrs_b200.engine import graphs as G
+    from inferrs_b200.engine.batch import build_context
+    spec, _ = spec_from_config(CONFIG_B)
+    layers = list(spec.layers)
+    layers[1] = dataclasses.replace(layers[1], mixer=dataclasses.replace(layers[1].mixer, window=24))
+    spec = dataclasses.replace(spec, layers=tuple(layers))
+    rt = Runtime.cuda(torch.float32)
+    weights = weights_for(declared_tensors(spec), torch.float32, seed=8)
+    runner = ModelRunner(spec, weights, rt, page_size=16, n_pages=40, max_requests=4)
+    dg = runner.graphs
+    assert dg is not None
+    built = {"in_place": 0, "anew": 0}
+    original = dg._describe
+
+    def checked(cap, entries, bucket):
+        calls = []
+        real = G.build_context
+        G.build_context = lambda *a, **k: (calls.append(1), real(*a, **k))[1]
+        try:
+            original(cap, entries, bucket)
+        finally:
+            G.build_context = real
+        built["anew" if calls else "in_place"] += 1
+        ctx = build_context(entries, runner.manager, runner.storage, spec.vocab_size, spec.max_positions,
+                            torch.device("cpu"), fixed_pages=dg.fixed_pages, pad_to=bucket)
+        host = ctx.extra["host"]
+        assert np.array_equal(cap.master[:host.size], host)
+
+    dg._describe = checked
+    vocab = CONFIG_B["vocab_size"]
+    for rid, n in (("a", 13), ("b", 30), ("c", 47)):
+        runner.admit(rid)
+        runner.step([StepEntry(rid, random_tokens(n, vocab, seed=n), [])])
+    live = ["a", "b", "c"]
+    for step in range(70):
+        if step == 25:
+            runner.release("b")
+            live.remove("b")
+        if step == 40:
+            runner.admit("d")
+            runner.step([StepEntry("d", random_tokens(5, vocab, seed=5), [])])
+            live.append("d")
+        runner.step([StepEntry(rid, [(7 * step + i) % vocab], [0]) for i, rid in enumerate(live)])
+    assert built["in_place"] > 50 and built["anew"] >= 3
+    runner.manager.check_invariants()
