@@ -1,0 +1,118 @@
+"""The layer sizes of Qwen3-8B (two layers of them, the whole vocabulary) against the plain implementation,
+in float32 and in bfloat16, in the four ways of cutting requests into steps.  At these sizes the bfloat16 run
+goes through the kernels that serving uses: the tcgen05 products for few rows and the library's for many, the
+gated product, the TMA decode attention and the tcgen05 prefill attention."""
+import pytest
+import torch
+
+import plain_qwen3
+from helpers import cut, random_tokens, rel_err
+from inferrs_b200.engine.batch import StepEntry
+from inferrs_b200.engine.loading import random_model
+from inferrs_b200.engine.runner import ModelRunner
+from inferrs_b200.runtime import Runtime
+
+pytestmark = pytest.mark.gpu
+
+CONFIG = {
+    "architectures": ["Qwen3ForCausalLM"], "model_type": "qwen3",
+    "num_hidden_layers": 2, "hidden_size": 4096, "num_attention_heads": 32, "num_key_value_heads": 8,
+    "head_dim": 128, "intermediate_size": 12288, "vocab_size": 151936, "rope_theta": 1000000.0,
+    "rms_norm_eps": 1e-6, "max_position_embeddings": 4096, "tie_word_embeddings": False, "hidden_act": "silu",
+}
+N_TOKENS = 88
+LAST = 32
+TOL = {torch.float32: 1e-4, torch.bfloat16: 3e-2}
+
+
+@pytest.fixture(scope="module", params=[torch.float32, torch.bfloat16], ids=["float32", "bfloat16"])
+def setup(request):
+    dtype = request.param
+    rt = Runtime.cuda(dtype)
+    spec, weights, _ = random_model(CONFIG, 5, rt)
+    host = {k: v.float().cpu() for k, v in weights.items()}
+    prompts = [random_tokens(N_TOKENS, CONFIG["vocab_size"], seed=20 + i) for i in range(2)]
+    store = None if dtype == torch.float32 else dtype
+    want = [plain_qwen3.forward(CONFIG, host, p, store=store)[-LAST:] for p in prompts]
+    del host
+    runner = ModelRunner(spec, weights, rt, page_size=16, n_pages=14, max_requests=4)
+    yield dtype, runner, prompts, want
+    del runner, weights
+    torch.cuda.empty_cache()
+
+
+def check(got, want, dtype, what):
+    err = rel_err(got.cpu(), want)
+    assert err < TOL[dtype], f"{what}: relative error {err:.3e}"
+    if dtype == torch.float32:
+        assert torch.equal(got.cpu().argmax(-1), want.argmax(-1)), f"{what}: greedy tokens differ"
+
+
+def run_cut(runner, rid, toks, sizes):
+    """The logits of the last LAST tokens of a request fed in portions of the given sizes."""
+    runner.admit(rid)
+    rows, at = [], 0
+    for n in sizes:
+        want = [i for i in range(n) if at + i >= len(toks) - LAST]
+        out = runner.step([StepEntry(rid, toks[at:at + n], want)])
+        if want:
+            rows.append(out)
+        at += n
+    runner.release(rid)
+    return torch.cat(rows)
+
+
+def test_whole(setup):
+    dtype, runner, prompts, want = setup
+    check(run_cut(runner, "w", prompts[0], [N_TOKENS]), want[0], dtype, "whole")
+
+
+def test_most_in_one_step_then_one_by_one(setup):
+    dtype, runner, prompts, want = setup
+    check(run_cut(runner, "d", prompts[0], [N_TOKENS - LAST] + [1] * LAST), want[0], dtype, "decoded")
+
+
+def test_portions_of_changing_size(setup):
+    dtype, runner, prompts, want = setup
+    check(run_cut(runner, "p", prompts[1], cut(N_TOKENS, [7, 2, 13, 3, 2, 30])), want[1], dtype, "portions")
+
+
+def test_mixed_with_pages_used_again(setup):
+    """Both requests live at once, portions of one beside decoded tokens of the other, in a pool of 14 pages
+    (two requests of 88 tokens need 12) after the tests above have used and given back every page."""
+    dtype, runner, prompts, want = setup
+    a, b = prompts
+    runner.admit("a")
+    runner.admit("b")
+    got = {"a": [], "b": []}
+    at = {"a": 0, "b": 0}
+
+    def entry(rid, toks, n):
+        w = [i for i in range(n) if at[rid] + i >= N_TOKENS - LAST]
+        e = StepEntry(rid, toks[at[rid]:at[rid] + n], w)
+        at[rid] += n
+        return e, bool(w)
+
+    plan = [(40, 0), (16, 30), (1, 11), (1, 2), (1, 13)] + [(1, 1)] * 29 + [(0, 1)] * 3
+    for na, nb in plan:
+        entries, keep = [], []
+        for rid, toks, n in (("a", a, na), ("b", b, nb)):
+            n = min(n, N_TOKENS - at[rid])
+            if n > 0:
+                e, has = entry(rid, toks, n)
+                entries.append(e)
+                keep.append((rid, len(e.want)))
+        if not entries:
+            continue
+        out = runner.step(entries)
+        row = 0
+        for rid, k in keep:
+            if k:
+                got[rid].append(out[row:row + k])
+                row += k
+    assert at == {"a": N_TOKENS, "b": N_TOKENS}
+    check(torch.cat(got["a"]), want[0], dtype, "mixed a")
+    check(torch.cat(got["b"]), want[1], dtype, "mixed b")
+    runner.release("a")
+    runner.release("b")
+    runner.manager.check_invariants()
