@@ -16,14 +16,20 @@ pages there are *state slots*: one slot per live request, the index into
 per-request tensors of fixed size (sampler state, and the state of mixers that
 keep one).
 
+The book itself is kept by native code (``csrc/host_runtime.cpp``, built with the C++ compiler at first
+use like the kernels): this module is its Python front and turns its answers into exceptions.  A model
+of the same book in plain Python lives beside the tests and is compared with it call for call.
+
 Nothing here touches the device; :mod:`inferrs_b200.cache.storage` owns the
 tensors that the ids point into.
 """
 from __future__ import annotations
 
-from collections import deque
-from dataclasses import dataclass, field
-from typing import Deque, Dict, Hashable, List, Optional, Sequence
+import ctypes
+from dataclasses import dataclass
+from typing import Dict, Hashable, List, Optional, Sequence
+
+from ..csrc.build import load_library
 
 RELEASED = -1  # block-table entry of a page that was given back (a window passed it)
 
@@ -36,43 +42,6 @@ class OutOfPages(CacheError):
     """Not enough free pages (or no free state slot) for what was asked; nothing was changed."""
 
 
-class PagePool:
-    """Page ids 0..n-1 with a FIFO free list: pages are taken from the front and given back
-    to the back, as the reference's pool does (kv_cache.rs:104-139)."""
-
-    def __init__(self, n_pages: int):
-        if n_pages <= 0:
-            raise CacheError(f"a page pool needs at least one page, got {n_pages}")
-        self.n_pages = n_pages
-        self._free: Deque[int] = deque(range(n_pages))
-        self._held = [False] * n_pages
-
-    @property
-    def n_free(self) -> int:
-        return len(self._free)
-
-    def take(self, n: int) -> List[int]:
-        if n > len(self._free):
-            raise OutOfPages(f"{n} pages wanted, {len(self._free)} free of {self.n_pages}")
-        ids = [self._free.popleft() for _ in range(n)]
-        for i in ids:
-            self._held[i] = True
-        return ids
-
-    def give_back(self, ids: Sequence[int]):
-        for i in ids:
-            if not 0 <= i < self.n_pages:
-                raise CacheError(f"page id {i} is outside the pool of {self.n_pages}")
-            if not self._held[i]:
-                raise CacheError(f"page {i} is given back twice")
-        for i in ids:
-            self._held[i] = False
-            self._free.append(i)
-
-    def is_held(self, i: int) -> bool:
-        return self._held[i]
-
-
 @dataclass(frozen=True)
 class GroupLayout:
     """What the manager needs to know of a group: which keys stay visible."""
@@ -81,12 +50,48 @@ class GroupLayout:
     window: Optional[int] = None  # None: all keys; w: a query at i sees keys j with i - w < j <= i
 
 
-@dataclass
-class _Request:
-    slot: int
-    n_tokens: int = 0                     # tokens whose keys and values are in the cache
-    n_reserved: int = 0                   # tokens that pages have been taken for (>= n_tokens)
-    tables: List[List[int]] = field(default_factory=list)  # per group: page number -> page id or RELEASED
+_ERR_UNKNOWN_REQUEST, _ERR_ALREADY_LIVE, _ERR_NO_SLOT, _ERR_OUT_OF_PAGES = -1, -2, -3, -4
+_ERR_BAD_COUNT, _ERR_BEYOND_RESERVED, _ERR_DOUBLE_FREE, _ERR_ARGUMENT = -5, -6, -7, -8
+ERR_TOKEN, ERR_POSITIONS, ERR_TABLE_WIDTH = -9, -10, -11   # ibh_describe_decode's own refusals
+
+_LIB = None
+
+
+def host_library():
+    """The native host runtime with its argument types set."""
+    global _LIB
+    if _LIB is None:
+        lib = load_library("host_runtime")
+        i, p, l = ctypes.c_int, ctypes.c_void_p, ctypes.c_int64
+        lib.ibh_cache_new.argtypes = [i, p, p, i, i]
+        lib.ibh_cache_new.restype = p
+        lib.ibh_cache_delete.argtypes = [p]
+        lib.ibh_cache_delete.restype = None
+        for name, args in {
+            "ibh_cache_admit": [p, l], "ibh_cache_has": [p, l], "ibh_cache_n_live": [p],
+            "ibh_cache_n_free_slots": [p], "ibh_cache_n_free_pages": [p, i], "ibh_cache_slot": [p, l],
+            "ibh_cache_n_tokens": [p, l], "ibh_cache_block_table": [p, l, i, p, i],
+            "ibh_cache_pages_needed": [p, l, i, p], "ibh_cache_can_reserve": [p, i, p, p],
+            "ibh_cache_reserve": [p, i, p, p], "ibh_cache_commit": [p, l, i], "ibh_cache_release": [p, l],
+            "ibh_cache_check": [p, ctypes.c_char_p, i],
+            "ibh_describe_decode": [p, i, p, p, i, p, i, i, p, i, p],
+        }.items():
+            f = getattr(lib, name)
+            f.argtypes = args
+            f.restype = i
+        _LIB = lib
+    return _LIB
+
+
+class _PoolView:
+    """What callers read of one group's pool: its size and how many pages are free."""
+
+    def __init__(self, manager: "CacheManager", group: int, n_pages: int):
+        self._m, self._g, self.n_pages = manager, group, n_pages
+
+    @property
+    def n_free(self) -> int:
+        return self._m._lib.ibh_cache_n_free_pages(self._m._h, self._g)
 
 
 class CacheManager:
@@ -101,71 +106,103 @@ class CacheManager:
             raise CacheError(f"page_size must be positive, got {page_size}")
         if len(n_pages) != len(groups):
             raise CacheError("one page count per group is needed")
+        if not groups:
+            raise CacheError("at least one group is needed")
         if max_requests <= 0:
             raise CacheError(f"max_requests must be positive, got {max_requests}")
         for g in groups:
             if g.window is not None and g.window <= 0:
                 raise CacheError(f"group {g.name}: window must be positive, got {g.window}")
+        for n in n_pages:
+            if n <= 0:
+                raise CacheError(f"a page pool needs at least one page, got {n}")
         self.groups = list(groups)
         self.page_size = page_size
-        self.pools = [PagePool(n) for n in n_pages]
         self.max_requests = max_requests
-        self._free_slots: Deque[int] = deque(range(max_requests))
-        self._requests: Dict[Hashable, _Request] = {}
+        self._lib = host_library()
+        windows = (ctypes.c_int * len(groups))(*[-1 if g.window is None else g.window for g in groups])
+        counts = (ctypes.c_int * len(groups))(*[int(n) for n in n_pages])
+        self._h = self._lib.ibh_cache_new(len(groups), windows, counts, page_size, max_requests)
+        if not self._h:
+            raise CacheError("the native cache manager refused these sizes")
+        self.pools = [_PoolView(self, g, int(n)) for g, n in enumerate(n_pages)]
+        self._handles: Dict[Hashable, int] = {}   # request id -> the number that native code knows it by
+        self._next_handle = 0
+        self._scratch = (ctypes.c_int * 256)()
+
+    def __del__(self):
+        h, self._h = getattr(self, "_h", None), None
+        if h:
+            self._lib.ibh_cache_delete(h)
 
     # ---- requests and slots -------------------------------------------------
-    def has(self, rid: Hashable) -> bool:
-        return rid in self._requests
-
-    @property
-    def n_live(self) -> int:
-        return len(self._requests)
-
-    @property
-    def n_free_slots(self) -> int:
-        return len(self._free_slots)
-
-    def admit(self, rid: Hashable) -> int:
-        """Give the request a state slot and empty block tables; returns the slot."""
-        if rid in self._requests:
-            raise CacheError(f"request {rid!r} is already live")
-        if not self._free_slots:
-            raise OutOfPages(f"no free state slot ({self.max_requests} requests are live)")
-        slot = self._free_slots.popleft()
-        self._requests[rid] = _Request(slot=slot, tables=[[] for _ in self.groups])
-        return slot
-
-    def _get(self, rid: Hashable) -> _Request:
+    def _handle(self, rid: Hashable) -> int:
         try:
-            return self._requests[rid]
+            return self._handles[rid]
         except KeyError:
             raise CacheError(f"request {rid!r} is not live") from None
 
+    def handle(self, rid: Hashable) -> int:
+        """The number by which native code knows a live request (for calls that pass many at once)."""
+        return self._handle(rid)
+
+    def has(self, rid: Hashable) -> bool:
+        return rid in self._handles
+
+    @property
+    def n_live(self) -> int:
+        return len(self._handles)
+
+    @property
+    def n_free_slots(self) -> int:
+        return self._lib.ibh_cache_n_free_slots(self._h)
+
+    def admit(self, rid: Hashable) -> int:
+        """Give the request a state slot and empty block tables; returns the slot."""
+        if rid in self._handles:
+            raise CacheError(f"request {rid!r} is already live")
+        handle = self._next_handle
+        slot = self._lib.ibh_cache_admit(self._h, handle)
+        if slot == _ERR_NO_SLOT:
+            raise OutOfPages(f"no free state slot ({self.max_requests} requests are live)")
+        if slot < 0:
+            raise CacheError(f"request {rid!r}: the native cache manager answered {slot}")
+        self._next_handle += 1
+        self._handles[rid] = handle
+        return slot
+
     def slot(self, rid: Hashable) -> int:
-        return self._get(rid).slot
+        return self._lib.ibh_cache_slot(self._h, self._handle(rid))
 
     def n_tokens(self, rid: Hashable) -> int:
-        return self._get(rid).n_tokens
+        return self._lib.ibh_cache_n_tokens(self._h, self._handle(rid))
 
     def block_table(self, rid: Hashable, group: int) -> List[int]:
-        return self._get(rid).tables[group]
+        if not 0 <= group < len(self.groups):
+            raise CacheError(f"group {group} does not exist")
+        handle = self._handle(rid)
+        n = self._lib.ibh_cache_block_table(self._h, handle, group, self._scratch, len(self._scratch))
+        if n > len(self._scratch):
+            self._scratch = (ctypes.c_int * (2 * n))()
+            n = self._lib.ibh_cache_block_table(self._h, handle, group, self._scratch, len(self._scratch))
+        return self._scratch[:n]
 
     # ---- pages --------------------------------------------------------------
-    def _pages_for(self, n_tokens: int) -> int:
-        return (n_tokens + self.page_size - 1) // self.page_size
-
     def pages_needed(self, rid: Hashable, n_new: int) -> List[int]:
         """Pages that each group has to take so that ``n_new`` more tokens fit."""
-        r = self._get(rid)
-        total = self._pages_for(r.n_tokens + n_new)
-        return [max(0, total - len(t)) for t in r.tables]
+        out = (ctypes.c_int * len(self.groups))()
+        self._lib.ibh_cache_pages_needed(self._h, self._handle(rid), int(n_new), out)
+        return list(out)
+
+    def _arrays(self, wants: Dict[Hashable, int]):
+        n = len(wants)
+        rids = (ctypes.c_int64 * n)(*[self._handle(rid) for rid in wants])
+        counts = (ctypes.c_int * n)(*[int(v) for v in wants.values()])
+        return n, rids, counts
 
     def can_reserve(self, wants: Dict[Hashable, int]) -> bool:
-        need = [0] * len(self.groups)
-        for rid, n_new in wants.items():
-            for g, n in enumerate(self.pages_needed(rid, n_new)):
-                need[g] += n
-        return all(need[g] <= self.pools[g].n_free for g in range(len(self.groups)))
+        n, rids, counts = self._arrays(wants)
+        return self._lib.ibh_cache_can_reserve(self._h, n, rids, counts) == 1
 
     def reserve(self, wants: Dict[Hashable, int]):
         """Take the pages for ``wants[rid]`` more tokens of every request named, or raise
@@ -173,65 +210,48 @@ class CacheManager:
         for rid, n_new in wants.items():
             if n_new <= 0:
                 raise CacheError(f"request {rid!r}: a step must bring at least one token, got {n_new}")
-        if not self.can_reserve(wants):
-            need = [sum(self.pages_needed(rid, n)[g] for rid, n in wants.items()) for g in range(len(self.groups))]
+        n, rids, counts = self._arrays(wants)
+        code = self._lib.ibh_cache_reserve(self._h, n, rids, counts)
+        if code == _ERR_OUT_OF_PAGES:
+            need = [sum(self.pages_needed(rid, k)[g] for rid, k in wants.items()) for g in range(len(self.groups))]
             raise OutOfPages("pages wanted per group " + str(need) + ", free " + str([p.n_free for p in self.pools]))
-        for rid, n_new in wants.items():
-            r = self._get(rid)
-            for g, n in enumerate(self.pages_needed(rid, n_new)):
-                r.tables[g].extend(self.pools[g].take(n))
-            r.n_reserved = r.n_tokens + n_new
+        if code != 0:
+            raise CacheError(f"reserve: the native cache manager answered {code}")
 
     def commit(self, rid: Hashable, n_new: int):
         """The step wrote ``n_new`` tokens; give back the pages that every later query's window has passed."""
-        r = self._get(rid)
-        if r.n_tokens + n_new > r.n_reserved:
-            raise CacheError(f"request {rid!r}: commit of {n_new} tokens beyond the {r.n_reserved} reserved")
-        r.n_tokens += n_new
-        for g, layout in enumerate(self.groups):
-            if layout.window is None:
-                continue
-            # the next query stands at position >= n_tokens and sees keys >= n_tokens - window + 1
-            first_needed = r.n_tokens - layout.window + 1
-            if first_needed <= 0:
-                continue
-            dead = first_needed // self.page_size  # pages 0..dead-1 hold only keys < first_needed
-            gone = [p for p in r.tables[g][:dead] if p != RELEASED]
-            if gone:
-                self.pools[g].give_back(gone)
-                for i in range(dead):
-                    r.tables[g][i] = RELEASED
+        code = self._lib.ibh_cache_commit(self._h, self._handle(rid), int(n_new))
+        if code == _ERR_BEYOND_RESERVED:
+            raise CacheError(f"request {rid!r}: commit of {n_new} tokens beyond those reserved")
+        if code != 0:
+            raise CacheError(f"commit: the native cache manager answered {code}")
 
     def release(self, rid: Hashable):
         """The request is over: all its pages and its slot are free again."""
-        r = self._get(rid)
-        for g, table in enumerate(r.tables):
-            self.pools[g].give_back([p for p in table if p != RELEASED])
-        self._free_slots.append(r.slot)
-        del self._requests[rid]
+        code = self._lib.ibh_cache_release(self._h, self._handle(rid))
+        del self._handles[rid]
+        if code != 0:
+            raise CacheError(f"release: the native cache manager answered {code}")
 
     # ---- checks -------------------------------------------------------------
     def check_invariants(self):
         """No page lost, none held by two requests, free list and tables disjoint."""
-        for g, pool in enumerate(self.pools):
-            seen: Dict[int, Hashable] = {}
-            for rid, r in self._requests.items():
-                for p in r.tables[g]:
-                    if p == RELEASED:
-                        continue
-                    if p in seen:
-                        raise CacheError(f"group {g}: page {p} is held by {seen[p]!r} and {rid!r}")
-                    if not pool.is_held(p):
-                        raise CacheError(f"group {g}: page {p} of {rid!r} is marked free")
-                    seen[p] = rid
-            free = list(pool._free)
-            if len(set(free)) != len(free):
-                raise CacheError(f"group {g}: a page is twice in the free list")
-            if set(free) & set(seen):
-                raise CacheError(f"group {g}: a held page is in the free list")
-            if len(free) + len(seen) != pool.n_pages:
-                raise CacheError(f"group {g}: {pool.n_pages - len(free) - len(seen)} pages are lost")
-        slots = [r.slot for r in self._requests.values()]
-        if len(set(slots)) != len(slots) or set(slots) & set(self._free_slots) \
-                or len(slots) + len(self._free_slots) != self.max_requests:
-            raise CacheError("state slots are lost or held twice")
+        msg = ctypes.create_string_buffer(256)
+        if self._lib.ibh_cache_check(self._h, msg, 256) != 0:
+            raise CacheError(msg.value.decode())
+        if self._lib.ibh_cache_n_live(self._h) != len(self._handles):
+            raise CacheError("the front and the native book disagree on the live requests")
+
+    def describe_decode(self, rids: Sequence[Hashable], tokens: Sequence[int], bucket: int,
+                        fixed_pages: Sequence[int], vocab_size: int, max_positions: int, out_ptr: int, cap: int):
+        """Write the description of a step of single tokens, padded to ``bucket`` requests, to ``cap`` int32
+        at ``out_ptr`` (host memory), in the layout of :func:`inferrs_b200.engine.batch.build_context`.
+        Returns (numbers written, 0) or (a negative refusal, index of the entry it is about)."""
+        n = len(rids)
+        handles = (ctypes.c_int64 * n)(*[self._handle(rid) for rid in rids])
+        toks = (ctypes.c_int * n)(*tokens)
+        pages = (ctypes.c_int * len(self.groups))(*fixed_pages)
+        bad = ctypes.c_int(0)
+        code = self._lib.ibh_describe_decode(self._h, n, handles, toks, bucket, pages, vocab_size, max_positions,
+                                             out_ptr, cap, ctypes.byref(bad))
+        return code, bad.value

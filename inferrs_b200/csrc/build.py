@@ -41,11 +41,23 @@ LIBRARIES: Dict[str, dict] = {
     "core_f32": {"sources": _CORE_SOURCES, "flags": ["-DIB_ACT_BF16=0"], "link": []},
     "core_bf16": {"sources": _CORE_SOURCES, "flags": ["-DIB_ACT_BF16=1"], "link": []},
     "gemm_bf16": {"sources": ["gemm_tcgen05.cu", "gemm_streamk.cu"], "flags": ["-DIB_ACT_BF16=1"], "link": []},
+    # host code only (the cache's book-keeping and the step description): the C++ compiler alone builds it
+    "host_runtime": {"sources": ["host_runtime.cpp"], "flags": [], "link": [], "host": True},
 }
+
+HOST_FLAGS = ["-O2", "-std=c++17", "-fPIC", "-fvisibility=hidden", "-Wall"]
 
 
 class BuildError(RuntimeError):
     pass
+
+
+def find_cxx() -> str:
+    for cand in (os.environ.get("CXX"), shutil.which("g++"), shutil.which("c++"), shutil.which("clang++")):
+        if cand and (os.path.isfile(cand) or shutil.which(cand)):
+            return shutil.which(cand) or cand
+    raise BuildError("no C++ compiler was found (looked at $CXX, g++, c++, clang++); the host runtime of "
+                     "inferrs_b200 cannot be built and there is no other implementation")
 
 
 def find_nvcc() -> str:
@@ -69,7 +81,8 @@ def library_hash(name: str) -> str:
         h.update(f.encode())
         with open(os.path.join(HERE, f), "rb") as fh:
             h.update(fh.read())
-    h.update(" ".join(ARCH_FLAGS + COMMON_FLAGS + lib["flags"] + lib["link"]).encode())
+    flags = HOST_FLAGS if lib.get("host") else ARCH_FLAGS + COMMON_FLAGS
+    h.update(" ".join(flags + lib["flags"] + lib["link"]).encode())
     return h.hexdigest()[:16]
 
 
@@ -126,7 +139,7 @@ def _run_with_heartbeat(cmds: Sequence[Sequence[str]], what: str, verbose_flags:
         done.set()
     for cmd, rc, out in results:
         if rc != 0:
-            raise BuildError(f"nvcc failed ({rc}) for: {' '.join(cmd)}\n{out}")
+            raise BuildError(f"the compiler failed ({rc}) for: {' '.join(cmd)}\n{out}")
         if verbose_flags and out.strip():
             print(out, file=sys.stderr, flush=True)
 
@@ -139,27 +152,30 @@ def build_library(name: str, force: bool = False, ptxas_verbose: bool = False) -
         p = library_path(name)
         if p:
             return p
-    nvcc = find_nvcc()
+    lib = LIBRARIES[name]
+    host = bool(lib.get("host"))
+    compiler = find_cxx() if host else find_nvcc()
     out_dir = next((d for d in build_dirs() if _writable_dir(d)), None)
     if out_dir is None:
         raise BuildError(f"no writable folder for built kernels among {build_dirs()}")
-    lib = LIBRARIES[name]
     tag = library_hash(name)
-    print(f"[inferrs_b200] compiling kernel library {name} for sm_100a ({len(lib['sources'])} files) into {out_dir}",
-          file=sys.stderr, flush=True)
+    what = "host library" if host else "kernel library"
+    print(f"[inferrs_b200] compiling {what} {name}{'' if host else ' for sm_100a'} ({len(lib['sources'])} files) "
+          f"into {out_dir}", file=sys.stderr, flush=True)
     t0 = time.time()
     objs, cmds = [], []
     for src in lib["sources"]:
         obj = os.path.join(out_dir, f"{name}.{tag}.{os.path.splitext(src)[0]}.o")
         objs.append(obj)
-        cmd = [nvcc] + ARCH_FLAGS + COMMON_FLAGS + lib["flags"] + ["-I", HERE, "-c", os.path.join(HERE, src), "-o", obj]
-        if ptxas_verbose:
+        flags = HOST_FLAGS if host else ARCH_FLAGS + COMMON_FLAGS
+        cmd = [compiler] + flags + lib["flags"] + ["-I", HERE, "-c", os.path.join(HERE, src), "-o", obj]
+        if ptxas_verbose and not host:
             cmd += ["-Xptxas", "-v"]
         cmds.append(cmd)
     _run_with_heartbeat(cmds, name, ptxas_verbose)
     final = os.path.join(out_dir, f"{name}.{tag}.so")
     tmp = final + f".tmp{os.getpid()}"
-    link = [nvcc, "-shared"] + ARCH_FLAGS + ["-o", tmp] + objs + lib["link"]
+    link = [compiler, "-shared"] + ([] if host else ARCH_FLAGS) + ["-o", tmp] + objs + lib["link"]
     _run_with_heartbeat([link], f"{name} (link)", False)
     os.replace(tmp, final)
     for old in os.listdir(out_dir):   # builds of earlier source states of this library

@@ -1,0 +1,346 @@
+// Host side of the cache in native code: page pools, block tables, state slots, and the description of a
+// replayed decode step.  No CUDA here; the Python package drives it through the C interface at the end
+// (inferrs_b200/cache/manager.py is its front, and says what each call means).
+//
+// The reference keeps the same book in Rust: a pool of fixed-size blocks with a FIFO free list
+// (inferrs-models/src/kv_cache.rs:80-139), a table per request (:154-222), release at the request's end
+// (inferrs/src/engine.rs:746-748).  Here there is one pool and one table per *group* of caches with the same
+// needs; a group with a window gives pages back as soon as every later query's window has passed them.
+#include <cstdint>
+#include <cstdio>
+#include <cstring>
+#include <deque>
+#include <string>
+#include <unordered_map>
+#include <vector>
+
+namespace {
+
+constexpr int RELEASED = -1;
+
+// return codes of the C interface
+constexpr int OK = 0;
+constexpr int ERR_UNKNOWN_REQUEST = -1;
+constexpr int ERR_ALREADY_LIVE = -2;
+constexpr int ERR_NO_SLOT = -3;
+constexpr int ERR_OUT_OF_PAGES = -4;
+constexpr int ERR_BAD_COUNT = -5;
+constexpr int ERR_BEYOND_RESERVED = -6;
+constexpr int ERR_DOUBLE_FREE = -7;
+constexpr int ERR_ARGUMENT = -8;
+constexpr int ERR_TOKEN = -9;
+constexpr int ERR_POSITIONS = -10;
+constexpr int ERR_TABLE_WIDTH = -11;
+
+struct Pool {
+    int n_pages = 0;
+    std::deque<int> free_list;   // taken from the front, given back to the back
+    std::vector<char> held;
+
+    explicit Pool(int n) : n_pages(n), held(n, 0) {
+        for (int i = 0; i < n; ++i) free_list.push_back(i);
+    }
+    int n_free() const { return (int)free_list.size(); }
+    int take() {
+        const int id = free_list.front();
+        free_list.pop_front();
+        held[id] = 1;
+        return id;
+    }
+    bool give_back(int id) {
+        if (id < 0 || id >= n_pages || !held[id]) return false;
+        held[id] = 0;
+        free_list.push_back(id);
+        return true;
+    }
+};
+
+struct Request {
+    int slot = 0;
+    int n_tokens = 0;     // tokens whose keys and values are in the cache
+    int n_reserved = 0;   // tokens that pages have been taken for
+    std::vector<std::vector<int>> tables;   // per group: page number -> page id or RELEASED
+};
+
+struct Cache {
+    int page_size = 0, max_requests = 0;
+    std::vector<int> windows;   // per group, -1: all keys stay visible
+    std::vector<Pool> pools;
+    std::deque<int> free_slots;
+    std::unordered_map<int64_t, Request> requests;
+
+    int pages_for(int n_tokens) const { return (n_tokens + page_size - 1) / page_size; }
+
+    Request* get(int64_t rid) {
+        auto it = requests.find(rid);
+        return it == requests.end() ? nullptr : &it->second;
+    }
+
+    // pages that each group has to take so that n_new more tokens of the request fit
+    void pages_needed(const Request& r, int n_new, int* out) const {
+        const int total = pages_for(r.n_tokens + n_new);
+        for (size_t g = 0; g < pools.size(); ++g) {
+            const int have = (int)r.tables[g].size();
+            out[g] = total > have ? total - have : 0;
+        }
+    }
+
+    int can_reserve(int n, const int64_t* rids, const int* n_new) {
+        std::vector<int> need(pools.size(), 0), one(pools.size());
+        for (int i = 0; i < n; ++i) {
+            Request* r = get(rids[i]);
+            if (r == nullptr) return ERR_UNKNOWN_REQUEST;
+            pages_needed(*r, n_new[i], one.data());
+            for (size_t g = 0; g < pools.size(); ++g) need[g] += one[g];
+        }
+        for (size_t g = 0; g < pools.size(); ++g)
+            if (need[g] > pools[g].n_free()) return 0;
+        return 1;
+    }
+
+    int reserve(int n, const int64_t* rids, const int* n_new) {
+        for (int i = 0; i < n; ++i)
+            if (n_new[i] <= 0) return ERR_BAD_COUNT;
+        const int can = can_reserve(n, rids, n_new);
+        if (can < 0) return can;
+        if (can == 0) return ERR_OUT_OF_PAGES;
+        std::vector<int> one(pools.size());
+        for (int i = 0; i < n; ++i) {
+            Request* r = get(rids[i]);
+            pages_needed(*r, n_new[i], one.data());
+            for (size_t g = 0; g < pools.size(); ++g)
+                for (int k = 0; k < one[g]; ++k) r->tables[g].push_back(pools[g].take());
+            r->n_reserved = r->n_tokens + n_new[i];
+        }
+        return OK;
+    }
+
+    int commit(int64_t rid, int n_new) {
+        Request* r = get(rid);
+        if (r == nullptr) return ERR_UNKNOWN_REQUEST;
+        if (r->n_tokens + n_new > r->n_reserved) return ERR_BEYOND_RESERVED;
+        r->n_tokens += n_new;
+        for (size_t g = 0; g < pools.size(); ++g) {
+            if (windows[g] < 0) continue;
+            // the next query stands at position >= n_tokens and sees keys >= n_tokens - window + 1
+            const int first_needed = r->n_tokens - windows[g] + 1;
+            if (first_needed <= 0) continue;
+            int dead = first_needed / page_size;   // pages 0..dead-1 hold only keys before first_needed
+            if (dead > (int)r->tables[g].size()) dead = (int)r->tables[g].size();
+            for (int i = 0; i < dead; ++i) {
+                int& p = r->tables[g][i];
+                if (p != RELEASED) {
+                    if (!pools[g].give_back(p)) return ERR_DOUBLE_FREE;
+                    p = RELEASED;
+                }
+            }
+        }
+        return OK;
+    }
+
+    int release(int64_t rid) {
+        auto it = requests.find(rid);
+        if (it == requests.end()) return ERR_UNKNOWN_REQUEST;
+        Request& r = it->second;
+        for (size_t g = 0; g < pools.size(); ++g)
+            for (int p : r.tables[g])
+                if (p != RELEASED && !pools[g].give_back(p)) return ERR_DOUBLE_FREE;
+        free_slots.push_back(r.slot);
+        requests.erase(it);
+        return OK;
+    }
+
+    // No page lost, none held by two requests, free list and tables disjoint; the same for the slots.
+    int check(std::string& msg) const {
+        for (size_t g = 0; g < pools.size(); ++g) {
+            const Pool& pool = pools[g];
+            std::vector<int64_t> owner(pool.n_pages, INT64_MIN);
+            int n_seen = 0;
+            for (const auto& kv : requests) {
+                for (int p : kv.second.tables[g]) {
+                    if (p == RELEASED) continue;
+                    if (p < 0 || p >= pool.n_pages) { msg = "a block table holds a page id outside its pool"; return 1; }
+                    if (owner[p] != INT64_MIN) { msg = "a page is held by two requests"; return 1; }
+                    if (!pool.held[p]) { msg = "a page of a request is marked free"; return 1; }
+                    owner[p] = kv.first;
+                    ++n_seen;
+                }
+            }
+            std::vector<char> in_free(pool.n_pages, 0);
+            for (int p : pool.free_list) {
+                if (in_free[p]) { msg = "a page is twice in the free list"; return 1; }
+                in_free[p] = 1;
+                if (owner[p] != INT64_MIN) { msg = "a held page is in the free list"; return 1; }
+            }
+            if ((int)pool.free_list.size() + n_seen != pool.n_pages) { msg = "pages are lost"; return 1; }
+        }
+        std::vector<char> slot_used(max_requests, 0);
+        size_t n = 0;
+        for (const auto& kv : requests) {
+            const int s = kv.second.slot;
+            if (s < 0 || s >= max_requests || slot_used[s]) { msg = "state slots are lost or held twice"; return 1; }
+            slot_used[s] = 1;
+            ++n;
+        }
+        for (int s : free_slots) {
+            if (s < 0 || s >= max_requests || slot_used[s]) { msg = "state slots are lost or held twice"; return 1; }
+            slot_used[s] = 1;
+            ++n;
+        }
+        if ((int)n != max_requests) { msg = "state slots are lost or held twice"; return 1; }
+        return 0;
+    }
+};
+
+}  // namespace
+
+#define IBH_EXPORT extern "C" __attribute__((visibility("default")))
+
+// windows[g] < 0: group g keeps all keys.  Returns nullptr for sizes that make no sense.
+IBH_EXPORT void* ibh_cache_new(int n_groups, const int* windows, const int* n_pages, int page_size, int max_requests) {
+    if (n_groups <= 0 || page_size <= 0 || max_requests <= 0) return nullptr;
+    for (int g = 0; g < n_groups; ++g)
+        if (n_pages[g] <= 0 || windows[g] == 0) return nullptr;
+    Cache* c = new Cache();
+    c->page_size = page_size;
+    c->max_requests = max_requests;
+    for (int g = 0; g < n_groups; ++g) {
+        c->windows.push_back(windows[g] < 0 ? -1 : windows[g]);
+        c->pools.emplace_back(n_pages[g]);
+    }
+    for (int s = 0; s < max_requests; ++s) c->free_slots.push_back(s);
+    return c;
+}
+
+IBH_EXPORT void ibh_cache_delete(void* h) { delete static_cast<Cache*>(h); }
+
+// The request gets a state slot (returned, >= 0) and empty block tables.
+IBH_EXPORT int ibh_cache_admit(void* h, int64_t rid) {
+    Cache* c = static_cast<Cache*>(h);
+    if (c->requests.count(rid)) return ERR_ALREADY_LIVE;
+    if (c->free_slots.empty()) return ERR_NO_SLOT;
+    Request r;
+    r.slot = c->free_slots.front();
+    c->free_slots.pop_front();
+    r.tables.resize(c->pools.size());
+    const int slot = r.slot;
+    c->requests.emplace(rid, std::move(r));
+    return slot;
+}
+
+IBH_EXPORT int ibh_cache_has(void* h, int64_t rid) { return static_cast<Cache*>(h)->requests.count(rid) ? 1 : 0; }
+IBH_EXPORT int ibh_cache_n_live(void* h) { return (int)static_cast<Cache*>(h)->requests.size(); }
+IBH_EXPORT int ibh_cache_n_free_slots(void* h) { return (int)static_cast<Cache*>(h)->free_slots.size(); }
+IBH_EXPORT int ibh_cache_n_free_pages(void* h, int g) { return static_cast<Cache*>(h)->pools[g].n_free(); }
+
+IBH_EXPORT int ibh_cache_slot(void* h, int64_t rid) {
+    Request* r = static_cast<Cache*>(h)->get(rid);
+    return r == nullptr ? ERR_UNKNOWN_REQUEST : r->slot;
+}
+
+IBH_EXPORT int ibh_cache_n_tokens(void* h, int64_t rid) {
+    Request* r = static_cast<Cache*>(h)->get(rid);
+    return r == nullptr ? ERR_UNKNOWN_REQUEST : r->n_tokens;
+}
+
+// Copies the request's block table of group g to out (at most cap entries); returns its length.
+IBH_EXPORT int ibh_cache_block_table(void* h, int64_t rid, int g, int* out, int cap) {
+    Cache* c = static_cast<Cache*>(h);
+    Request* r = c->get(rid);
+    if (r == nullptr) return ERR_UNKNOWN_REQUEST;
+    if (g < 0 || g >= (int)c->pools.size()) return ERR_ARGUMENT;
+    const std::vector<int>& t = r->tables[g];
+    const int n = (int)t.size() < cap ? (int)t.size() : cap;
+    if (n > 0) std::memcpy(out, t.data(), (size_t)n * sizeof(int));
+    return (int)t.size();
+}
+
+IBH_EXPORT int ibh_cache_pages_needed(void* h, int64_t rid, int n_new, int* out) {
+    Cache* c = static_cast<Cache*>(h);
+    Request* r = c->get(rid);
+    if (r == nullptr) return ERR_UNKNOWN_REQUEST;
+    c->pages_needed(*r, n_new, out);
+    return OK;
+}
+
+// 1 if the pages for n_new[i] more tokens of every request rids[i] are free, 0 if not.
+IBH_EXPORT int ibh_cache_can_reserve(void* h, int n, const int64_t* rids, const int* n_new) {
+    return static_cast<Cache*>(h)->can_reserve(n, rids, n_new);
+}
+
+// Takes those pages, or changes nothing and says why.
+IBH_EXPORT int ibh_cache_reserve(void* h, int n, const int64_t* rids, const int* n_new) {
+    return static_cast<Cache*>(h)->reserve(n, rids, n_new);
+}
+
+IBH_EXPORT int ibh_cache_commit(void* h, int64_t rid, int n_new) { return static_cast<Cache*>(h)->commit(rid, n_new); }
+IBH_EXPORT int ibh_cache_release(void* h, int64_t rid) { return static_cast<Cache*>(h)->release(rid); }
+
+IBH_EXPORT int ibh_cache_check(void* h, char* msg, int cap) {
+    std::string m;
+    const int bad = static_cast<Cache*>(h)->check(m);
+    if (bad && cap > 0) std::snprintf(msg, (size_t)cap, "%s", m.c_str());
+    return bad;
+}
+
+// The description of a step in which each of the n requests brings one token, padded to `bucket` requests, in
+// the layout that the captured graphs read (every part starts on a multiple of four numbers):
+//   token ids [bucket] | positions [bucket] | request of each row [bucket] | first row of each request [bucket + 1]
+//   | keys each request sees [bucket] | state slots [bucket] | rows whose logits are made [bucket]
+//   | per group: block tables [bucket, fixed_pages[g]]
+// A request that only fills the batch has token 0 at position 0, one key and no pages (-1 everywhere).
+// The pages for the step's tokens are reserved already.  Returns the count of numbers written, or an error with
+// the index of the offending entry in *bad.
+IBH_EXPORT int ibh_describe_decode(void* h, int n, const int64_t* rids, const int* tokens, int bucket,
+                                   const int* fixed_pages, int vocab_size, int max_positions, int* out, int cap,
+                                   int* bad) {
+    Cache* c = static_cast<Cache*>(h);
+    if (n <= 0 || n > bucket || out == nullptr) return ERR_ARGUMENT;
+    const int n_groups = (int)c->pools.size();
+    auto round4 = [](int v) { return (v + 3) / 4 * 4; };
+    int off[8];
+    off[0] = 0;
+    off[1] = off[0] + round4(bucket);
+    off[2] = off[1] + round4(bucket);
+    off[3] = off[2] + round4(bucket);
+    off[4] = off[3] + round4(bucket + 1);
+    off[5] = off[4] + round4(bucket);
+    off[6] = off[5] + round4(bucket);
+    off[7] = off[6] + round4(bucket);
+    int total = off[7];
+    for (int g = 0; g < n_groups; ++g) total += round4(bucket * fixed_pages[g]);
+    if (total > cap) return ERR_ARGUMENT;
+    std::memset(out, 0, (size_t)total * sizeof(int));
+    for (int i = 0; i < bucket; ++i) {
+        out[off[2] + i] = i;
+        out[off[3] + i] = i;
+        out[off[4] + i] = 1;
+        out[off[6] + i] = i;
+    }
+    out[off[3] + bucket] = bucket;
+    int at = off[7];
+    std::vector<int> table_at(n_groups);
+    for (int g = 0; g < n_groups; ++g) {
+        table_at[g] = at;
+        const int count = bucket * fixed_pages[g];
+        for (int k = 0; k < count; ++k) out[at + k] = RELEASED;
+        at += round4(count);
+    }
+    for (int i = 0; i < n; ++i) {
+        if (bad != nullptr) *bad = i;
+        Request* r = c->get(rids[i]);
+        if (r == nullptr) return ERR_UNKNOWN_REQUEST;
+        if (tokens[i] < 0 || tokens[i] >= vocab_size) return ERR_TOKEN;
+        if (r->n_tokens + 1 > max_positions) return ERR_POSITIONS;
+        out[off[0] + i] = tokens[i];
+        out[off[1] + i] = r->n_tokens;
+        out[off[4] + i] = r->n_tokens + 1;
+        out[off[5] + i] = r->slot;
+        for (int g = 0; g < n_groups; ++g) {
+            const std::vector<int>& t = r->tables[g];
+            if ((int)t.size() > fixed_pages[g]) return ERR_TABLE_WIDTH;
+            if (!t.empty()) std::memcpy(out + table_at[g] + (size_t)i * fixed_pages[g], t.data(), t.size() * sizeof(int));
+        }
+    }
+    return total;
+}

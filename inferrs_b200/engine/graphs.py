@@ -10,17 +10,14 @@ Captured are exactly the calls that an uncaptured step makes (``Model.forward``)
 fixed address: the description lives in one fixed int32 buffer, block tables are padded to the
 longest context, and the batch is padded with requests that own no pages.
 
-The description of a replayed step reaches the device from pinned host memory.  When the same requests
-come again, each one token further (the usual case while decoding), the host copy of the last
-description is brought up to date in place (token, position, length, a page number now and then)
-instead of being built anew.
+The description of a replayed step is written by the native cache manager straight into pinned host
+memory (``ibh_describe_decode``) and reaches the device in one asynchronous copy.
 """
 from __future__ import annotations
 
 import gc
 from typing import Dict, List, Optional, Sequence
 
-import numpy as np
 import torch
 
 from .. import kernels
@@ -39,15 +36,11 @@ def buckets_up_to(n: int) -> List[int]:
 class _Captured:
     def __init__(self, graph, buffer, logits, launches):
         self.graph, self.buffer, self.logits, self.launches = graph, buffer, logits, launches
-        # host side of the description: the numbers themselves, and two pinned copies that take turns as the
-        # source of the transfer (a copy may still be waiting in the stream when the next step is described)
-        self.master = np.zeros((buffer.numel(),), dtype=np.int32)
+        # host side of the description: two pinned copies that take turns as the source of the transfer (a
+        # copy may still be waiting in the stream when the next step is described)
         self.staging = [torch.zeros((buffer.numel(),), dtype=torch.int32).pin_memory() for _ in range(2)]
         self.copied = [None, None]          # the event after each pinned copy's last transfer
         self.turn = 0
-        self.rids = None                    # the requests of the last description, in order
-        self.held: List[int] = []           # tokens each of them had in the cache before that step
-        self.table_lens: List[List[int]] = []
 
 
 class DecodeGraphs:
@@ -76,71 +69,28 @@ class DecodeGraphs:
         return 8 * per_part + sum((bucket * p + 3) // 4 * 4 for p in self.fixed_pages) + 16
 
     # ---- the description of a replayed step -------------------------------------------
-    def _offsets(self, bucket: int) -> List[int]:
-        """Where the parts of a bucket's description start (the layout that ``build_context`` gives it)."""
-        sizes = [bucket, bucket, bucket, bucket + 1, bucket, bucket, bucket] + [bucket * p for p in self.fixed_pages]
-        out, total = [], 0
-        for n in sizes:
-            out.append(total)
-            total += (n + 3) // 4 * 4
-        return out
-
     def _describe(self, cap: _Captured, entries: Sequence[StepEntry], bucket: int):
-        """Bring the device's description up to date for these entries."""
+        """Bring the device's description up to date for these entries: native code writes it into pinned
+        memory from the cache's book, one asynchronous copy takes it to the device."""
         r = self.runner
-        m = r.manager
-        rids = tuple(e.rid for e in entries)
-        off = self._offsets(bucket)
-        fast = cap.rids == rids
-        if fast:
-            for i, e in enumerate(entries):
-                if m.n_tokens(e.rid) != cap.held[i] + 1 or cap.held[i] + 2 > r.spec.max_positions:
-                    fast = False
-                    break
-        if fast:
-            vocab = r.spec.vocab_size
-            host = cap.master
-            for i, e in enumerate(entries):
-                tok = e.tokens[0]
-                if not 0 <= tok < vocab:
-                    fast = False     # the full path says what is wrong with it
-                    break
-                held = cap.held[i] + 1
-                cap.held[i] = held
-                host[off[0] + i] = tok
-                host[off[1] + i] = held
-                host[off[4] + i] = held + 1
-                for g, layout in enumerate(m.groups):
-                    table = m.block_table(e.rid, g)
-                    width = self.fixed_pages[g]
-                    base = off[7 + g] + i * width
-                    if layout.window is not None:            # pages behind the window are given back: the whole row
-                        if len(table) > width:
-                            fast = False
-                            break
-                        host[base:base + len(table)] = table
-                    elif len(table) != cap.table_lens[g][i]:
-                        if len(table) > width:
-                            fast = False
-                            break
-                        host[base + cap.table_lens[g][i]:base + len(table)] = table[cap.table_lens[g][i]:]
-                    cap.table_lens[g][i] = len(table)
-                if not fast:
-                    break
-        if not fast:
-            ctx = build_context(entries, m, r.storage, r.spec.vocab_size, r.spec.max_positions, torch.device("cpu"),
-                                fixed_pages=self.fixed_pages, pad_to=bucket)
-            host = ctx.extra["host"]
-            cap.master[:host.size] = host
-            cap.rids = rids
-            cap.held = [m.n_tokens(e.rid) for e in entries]
-            cap.table_lens = [[len(m.block_table(e.rid, g)) for e in entries] for g in range(len(m.groups))]
         k = cap.turn
         cap.turn ^= 1
         if cap.copied[k] is not None:
-            cap.copied[k].synchronize()
-        cap.staging[k].numpy()[:] = cap.master
-        cap.buffer.copy_(cap.staging[k], non_blocking=True)
+            cap.copied[k].synchronize()     # the transfer that last read this pinned copy has been done
+        stage = cap.staging[k]
+        tokens = [e.tokens[0] for e in entries]
+        vocab = r.spec.vocab_size
+        code = -1
+        if all(isinstance(t, int) and 0 <= t < vocab for t in tokens):
+            code, _ = r.manager.describe_decode([e.rid for e in entries], tokens, bucket, self.fixed_pages, vocab,
+                                                r.spec.max_positions, stage.data_ptr(), stage.numel())
+        if code < 0:
+            # something is wrong with an entry: the general builder says what (or builds it, if it can)
+            ctx = build_context(entries, r.manager, r.storage, vocab, r.spec.max_positions, torch.device("cpu"),
+                                fixed_pages=self.fixed_pages, pad_to=bucket)
+            host = ctx.extra["host"]
+            stage.numpy()[:host.size] = host
+        cap.buffer.copy_(stage, non_blocking=True)
         ev = cap.copied[k] or torch.cuda.Event()
         ev.record()
         cap.copied[k] = ev

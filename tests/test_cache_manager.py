@@ -1,23 +1,37 @@
-"""The cache manager: no page lost, held twice or freed twice, under random orders of requests."""
+"""The cache manager (native code behind a Python front): no page lost, held twice or freed twice, under
+random orders of requests, and every answer equal to the plain model's."""
 import random
 
 import pytest
 
-from inferrs_b200.cache.manager import RELEASED, CacheError, CacheManager, GroupLayout, OutOfPages, PagePool
+import plain_cache
+from inferrs_b200.cache.manager import RELEASED, CacheError, CacheManager, GroupLayout, OutOfPages
 
 
-def test_pool_is_fifo_and_refuses_double_free():
-    p = PagePool(4)
+def test_the_plain_models_pool_is_fifo_and_refuses_double_free():
+    p = plain_cache.PagePool(4)
     assert p.take(3) == [0, 1, 2]
     p.give_back([1])
     assert p.take(2) == [3, 1]          # freed pages go to the back (kv_cache.rs:128-139)
-    with pytest.raises(OutOfPages):
+    with pytest.raises(plain_cache.OutOfPages):
         p.take(2)
     p.give_back([0])
-    with pytest.raises(CacheError, match="twice"):
+    with pytest.raises(plain_cache.CacheError, match="twice"):
         p.give_back([0])
-    with pytest.raises(CacheError, match="outside"):
+    with pytest.raises(plain_cache.CacheError, match="outside"):
         p.give_back([9])
+
+
+def test_pages_come_back_in_the_order_they_were_freed():
+    """The native pool is first in, first out as the reference's is (kv_cache.rs:104-139): tables show it."""
+    m = CacheManager([GroupLayout("full")], page_size=1, n_pages=[4], max_requests=2)
+    m.admit("a")
+    m.reserve({"a": 3}); m.commit("a", 3)
+    assert m.block_table("a", 0) == [0, 1, 2]
+    m.release("a")
+    m.admit("b")
+    m.reserve({"b": 3}); m.commit("b", 3)
+    assert m.block_table("b", 0) == [3, 0, 1]
 
 
 def test_reserve_is_all_or_nothing():
@@ -102,3 +116,100 @@ def test_random_orders_never_lose_a_page(seed):
     for rid in list(live):
         m.release(rid)
     assert [p.n_free for p in m.pools] == [p.n_pages for p in m.pools] and m.n_free_slots == 4
+
+
+@pytest.mark.parametrize("seed", range(8))
+def test_native_manager_answers_as_the_plain_model_does(seed):
+    """The same random calls go to the native manager and to the plain model: free pages, slots, token counts,
+    block tables (so also the order in which pages are used again) and refusals must agree after every call."""
+    rng = random.Random(100 + seed)
+    windows = [None, rng.choice([2, 5, 9, 33])] if seed % 2 else [rng.choice([4, 17]), None, None]
+    page_size = rng.choice([1, 3, 16])
+    n_pages = [rng.randint(5, 30) for _ in windows]
+    nat = CacheManager([GroupLayout(f"g{i}", w) for i, w in enumerate(windows)], page_size, n_pages, max_requests=5)
+    ref = plain_cache.CacheManager([plain_cache.GroupLayout(f"g{i}", w) for i, w in enumerate(windows)], page_size,
+                                   n_pages, max_requests=5)
+    live, next_id = [], 0
+    for _ in range(500):
+        op = rng.random()
+        if op < 0.2:
+            rid = ("r", next_id)
+            next_id += 1
+            if len(live) < 5:
+                assert nat.admit(rid) == ref.admit(rid)
+                live.append(rid)
+            else:
+                with pytest.raises(OutOfPages):
+                    nat.admit(rid)
+                with pytest.raises(plain_cache.OutOfPages):
+                    ref.admit(rid)
+        elif op < 0.35 and live:
+            rid = live.pop(rng.randrange(len(live)))
+            nat.release(rid)
+            ref.release(rid)
+        elif live:
+            wants = {rid: rng.randint(1, 20) for rid in rng.sample(live, rng.randint(1, len(live)))}
+            assert nat.can_reserve(wants) == ref.can_reserve(wants)
+            for rid, n in wants.items():
+                assert nat.pages_needed(rid, n) == ref.pages_needed(rid, n)
+            try:
+                ref.reserve(wants)
+            except plain_cache.OutOfPages:
+                with pytest.raises(OutOfPages):
+                    nat.reserve(wants)
+            else:
+                nat.reserve(wants)
+                for rid, n in wants.items():
+                    k = rng.randint(1, n)           # a step may write fewer tokens than were reserved
+                    nat.commit(rid, k)
+                    ref.commit(rid, k)
+        assert [p.n_free for p in nat.pools] == [p.n_free for p in ref.pools]
+        assert nat.n_free_slots == ref.n_free_slots and nat.n_live == ref.n_live
+        for rid in live:
+            assert nat.n_tokens(rid) == ref.n_tokens(rid) and nat.slot(rid) == ref.slot(rid)
+            for g in range(len(windows)):
+                assert nat.block_table(rid, g) == ref.block_table(rid, g)
+        nat.check_invariants()
+        ref.check_invariants()
+    with pytest.raises(CacheError, match="not live"):
+        nat.n_tokens(("r", -1))
+
+
+@pytest.mark.parametrize("seed", range(4))
+def test_native_description_of_a_decode_step_equals_the_general_builders(seed):
+    """Token ids, positions, lengths, slots and block tables of a step of single tokens, padded to a bucket, as
+    native code lays them out, against the general builder (which the step function uses for every other step)."""
+    import numpy as np
+    import torch
+    from inferrs_b200.engine.batch import StepEntry, build_context
+    rng = random.Random(seed)
+    windows = [None, 11] if seed % 2 else [None]
+    m = CacheManager([GroupLayout(f"g{i}", w) for i, w in enumerate(windows)], page_size=4,
+                     n_pages=[160] * len(windows), max_requests=6)
+    vocab, max_pos, bucket = 1000, 200, 8
+    fixed = [(max_pos + 3) // 4] * len(windows)
+    live = []
+    for i in range(5):
+        m.admit(i)
+        n = rng.randint(1, 60)
+        m.reserve({i: n}); m.commit(i, n)
+        live.append(i)
+    for _ in range(40):
+        chosen = rng.sample(live, rng.randint(1, len(live)))
+        m.reserve({rid: 1 for rid in chosen})
+        tokens = [rng.randrange(vocab) for _ in chosen]
+        out = np.full(4096, 12345, dtype=np.int32)
+        code, _ = m.describe_decode(chosen, tokens, bucket, fixed, vocab, max_pos, out.ctypes.data, out.size)
+        ctx = build_context([StepEntry(rid, [t], [0]) for rid, t in zip(chosen, tokens)], m, None, vocab, max_pos,
+                            torch.device("cpu"), fixed_pages=fixed, pad_to=bucket)
+        host = ctx.extra["host"]
+        assert code == host.size and np.array_equal(out[:code], host)
+        for rid in chosen:
+            m.commit(rid, 1)
+    # refusals: a token outside the vocabulary, a request that is full, a request that is not live
+    m.reserve({0: 1})
+    out = np.zeros(4096, dtype=np.int32)
+    assert m.describe_decode([0], [vocab], bucket, fixed, vocab, max_pos, out.ctypes.data, out.size)[0] < 0
+    assert m.describe_decode([0], [1], bucket, fixed, vocab, m.n_tokens(0), out.ctypes.data, out.size)[0] < 0
+    with pytest.raises(CacheError, match="not live"):
+        m.describe_decode([99], [1], bucket, fixed, vocab, max_pos, out.ctypes.data, out.size)

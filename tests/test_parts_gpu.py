@@ -296,12 +296,11 @@ def test_toy_mixer_with_state_is_registered_built_and_stepped(dtype):
     assert rel_err(tail, whole[0][30:]) > 10 * tol
 
 
-def test_replayed_steps_keep_their_description_up_to_date_in_place():
-    """Decode steps are replayed graphs whose description is updated in place on the host when the same
-    requests come again one token further: after every step it must equal the description built anew,
-    across page edges, with a window group that gives pages back, and when requests come and go."""
+def test_replayed_steps_get_the_description_that_the_general_builder_gives():
+    """Decode steps are replayed graphs whose description native code writes from the cache's book: after
+    every step it must equal what the general builder gives for the same entries, across page edges, with a
+    window group that gives pages back, and when requests come and go."""
     import numpy as np
-    from inferrs_b200.engine import graphs as G
     from inferrs_b200.engine.batch import build_context
     spec, _ = spec_from_config(CONFIG_B)
     layers = list(spec.layers)
@@ -312,22 +311,19 @@ def test_replayed_steps_keep_their_description_up_to_date_in_place():
     runner = ModelRunner(spec, weights, rt, page_size=16, n_pages=40, max_requests=4)
     dg = runner.graphs
     assert dg is not None
-    built = {"in_place": 0, "anew": 0}
+    checked_steps = []
     original = dg._describe
 
     def checked(cap, entries, bucket):
-        calls = []
-        real = G.build_context
-        G.build_context = lambda *a, **k: (calls.append(1), real(*a, **k))[1]
-        try:
-            original(cap, entries, bucket)
-        finally:
-            G.build_context = real
-        built["anew" if calls else "in_place"] += 1
+        turn = cap.turn
+        original(cap, entries, bucket)
         ctx = build_context(entries, runner.manager, runner.storage, spec.vocab_size, spec.max_positions,
                             torch.device("cpu"), fixed_pages=dg.fixed_pages, pad_to=bucket)
         host = ctx.extra["host"]
-        assert np.array_equal(cap.master[:host.size], host)
+        torch.cuda.synchronize()
+        assert np.array_equal(cap.staging[turn].numpy()[:host.size], host)
+        assert np.array_equal(cap.buffer.cpu().numpy()[:host.size], host)
+        checked_steps.append(len(entries))
 
     dg._describe = checked
     vocab = CONFIG_B["vocab_size"]
@@ -344,5 +340,5 @@ def test_replayed_steps_keep_their_description_up_to_date_in_place():
             runner.step([StepEntry("d", random_tokens(5, vocab, seed=5), [])])
             live.append("d")
         runner.step([StepEntry(rid, [(7 * step + i) % vocab], [0]) for i, rid in enumerate(live)])
-    assert built["in_place"] > 50 and built["anew"] >= 3
+    assert len(checked_steps) > 60 and set(checked_steps) == {2, 3}
     runner.manager.check_invariants()
