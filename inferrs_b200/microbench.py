@@ -42,6 +42,21 @@ def _time(fn, iters: int, flush: bool = True) -> float:
 
 
 def gemm(args) -> dict:
+    if args.impl == "gated":
+        # n counts the rows of the stacked gate and up matrices: the output has n / 2 columns
+        inner = args.n // 2
+        x = torch.randn(args.m, args.k, device="cuda").to(torch.bfloat16)
+        w = (torch.randn(2 * inner, args.k, device="cuda") * 0.02).to(torch.bfloat16)
+        out = torch.empty(args.m, inner, dtype=torch.bfloat16, device="cuda")
+        us = _time(lambda: kernels.gemm_swiglu_tcgen05(x, w, out), args.iters)
+        gu = x.float() @ w.float().t()
+        g, u = gu[:, :inner].bfloat16().float(), gu[:, inner:].bfloat16().float()
+        ref = g / (1.0 + torch.exp(-g)) * u
+        err = float((out.float() - ref).abs().max() / ref.abs().max())
+        byts = 2 * (2 * inner * args.k + args.m * args.k + args.m * inner)
+        return {"kernel": "gemm/gated", "m": args.m, "n": 2 * inner, "k": args.k, "us": round(us, 2),
+                "GBps": round(byts / us / 1e3, 1), "TFLOPs": round(4 * args.m * inner * args.k / us / 1e6, 1),
+                "rel_err": err}
     x = torch.randn(args.m, args.k, device="cuda").to(torch.bfloat16)
     w = (torch.randn(args.n, args.k, device="cuda") * 0.02).to(torch.bfloat16)
     out = torch.empty(args.m, args.n, dtype=torch.bfloat16, device="cuda")
@@ -248,7 +263,8 @@ def main(argv=None) -> int:
                                  formatter_class=argparse.RawDescriptionHelpFormatter)
     sub = ap.add_subparsers(dest="what", required=True)
     g = sub.add_parser("gemm")
-    g.add_argument("--impl", choices=["library", "tcgen05", "streamk"], default="streamk")
+    g.add_argument("--impl", choices=["library", "tcgen05", "streamk", "gated"], default="streamk",
+                   help="gated: both products of a gated feed-forward and the gate in one tcgen05 kernel")
     g.add_argument("--m", type=int, default=8)
     g.add_argument("--n", type=int, default=6144)
     g.add_argument("--k", type=int, default=4096)
