@@ -93,6 +93,8 @@ struct Params {
     float* part_o;             // [R, n_heads, max_splits, 128]
     float* part_ml;            // [R, n_heads, max_splits, 2]
     int* counters;             // [R * n_kv_heads], zero between launches
+    const int* rows;           // [R] or null: the row of q, positions and out that place i of the grid works on
+    const int* reqs;           // [R] or null: its request (row of the block table); a negative row is no work
     int max_pages, page_size, n_pages, n_heads, n_kv_heads, window, max_splits;
     float scale_log2;
 };
@@ -114,9 +116,14 @@ __global__ void __launch_bounds__(THREADS, 2) decode_kernel(const __grid_constan
     // tile that holds this step's own key and value are touched only after griddepcontrol.wait.
     asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-    const int req = blockIdx.x, kvh = blockIdx.y, split = blockIdx.z;
+    // place i of the grid is row i of request i in a step of single tokens; in a step that also holds prompt
+    // portions a list says which rows are single tokens and whose they are
+    const int place = blockIdx.x, kvh = blockIdx.y, split = blockIdx.z;
+    const int row = P.rows != nullptr ? P.rows[place] : place;
+    if (row < 0) return;
+    const int req = P.reqs != nullptr ? P.reqs[place] : place;
     const int G = P.n_heads / P.n_kv_heads;
-    const int pos = P.positions[req];
+    const int pos = P.positions[row];
     const int lo = (P.window > 0 && pos - P.window + 1 > 0) ? pos - P.window + 1 : 0;
     const int t_first = lo / KEYS, t_last = pos / KEYS + 1;
     const int n_all = t_last - t_first;
@@ -140,7 +147,7 @@ __global__ void __launch_bounds__(THREADS, 2) decode_kernel(const __grid_constan
         for (int idx = threadIdx.x; idx < 16 * (D / 8); idx += 128) {
             const int r = idx / (D / 8), c = idx - r * (D / 8);
             uint4 v = make_uint4(0, 0, 0, 0);
-            if (r < G) v = *reinterpret_cast<const uint4*>(P.q + ((long)req * P.n_heads + kvh * G + r) * D + c * 8);
+            if (r < G) v = *reinterpret_cast<const uint4*>(P.q + ((long)row * P.n_heads + kvh * G + r) * D + c * 8);
             *reinterpret_cast<uint4*>(sq + r * D + c * 8) = v;
         }
         asm volatile("bar.sync 1, 128;" ::: "memory");
@@ -298,7 +305,8 @@ __global__ void __launch_bounds__(THREADS, 2) decode_kernel(const __grid_constan
         }
     }
     __syncthreads();
-    const long head0 = (long)req * P.n_heads + kvh * G;
+    const long head0 = (long)row * P.n_heads + kvh * G;       // of q and out
+    const long part0 = (long)place * P.n_heads + kvh * G;     // of the slices' scratch
     for (int idx = threadIdx.x; idx < G * D; idx += THREADS) {
         const int g = idx / D, e = idx - g * D;
         float M = -INFINITY;
@@ -314,10 +322,10 @@ __global__ void __launch_bounds__(THREADS, 2) decode_kernel(const __grid_constan
             }
         }
         if (n_splits > 1) {
-            P.part_o[((head0 + g) * P.max_splits + split) * D + e] = acc;
+            P.part_o[((part0 + g) * P.max_splits + split) * D + e] = acc;
             if (e == 0) {
-                P.part_ml[((head0 + g) * P.max_splits + split) * 2] = M;
-                P.part_ml[((head0 + g) * P.max_splits + split) * 2 + 1] = L;
+                P.part_ml[((part0 + g) * P.max_splits + split) * 2] = M;
+                P.part_ml[((part0 + g) * P.max_splits + split) * 2 + 1] = L;
             }
         } else {
             P.out[(head0 + g) * D + e] = __float2bfloat16_rn(L > 0.0f ? acc / L : 0.0f);
@@ -328,23 +336,23 @@ __global__ void __launch_bounds__(THREADS, 2) decode_kernel(const __grid_constan
         __threadfence();
         __syncthreads();
         if (threadIdx.x == 0) {
-            const int old = atomicAdd(P.counters + req * P.n_kv_heads + kvh, 1);
+            const int old = atomicAdd(P.counters + place * P.n_kv_heads + kvh, 1);
             *s_flag = old == n_splits - 1;
-            if (old == n_splits - 1) P.counters[req * P.n_kv_heads + kvh] = 0;   // zero again for the next launch
+            if (old == n_splits - 1) P.counters[place * P.n_kv_heads + kvh] = 0;   // zero again for the next launch
         }
         __syncthreads();
         if (*s_flag) {
             __threadfence();
             for (int idx = threadIdx.x; idx < G * D; idx += THREADS) {
                 const int g = idx / D, e = idx - g * D;
-                const float* ml = P.part_ml + (head0 + g) * P.max_splits * 2;
+                const float* ml = P.part_ml + (part0 + g) * P.max_splits * 2;
                 float M = -INFINITY;
                 for (int s = 0; s < n_splits; ++s) M = fmaxf(M, __ldcg(ml + 2 * s));
                 float acc = 0.0f, L = 0.0f;
                 if (M > -INFINITY) {
                     for (int s = 0; s < n_splits; ++s) {
                         const float f = exp2f(__ldcg(ml + 2 * s) - M);
-                        acc += f * __ldcg(P.part_o + ((head0 + g) * P.max_splits + s) * D + e);
+                        acc += f * __ldcg(P.part_o + ((part0 + g) * P.max_splits + s) * D + e);
                         L += f * __ldcg(ml + 2 * s + 1);
                     }
                 }
@@ -376,15 +384,17 @@ static EncodeTiled encode_fn() {
 
 }  // namespace dec
 
-// One new token per request (row r = request r).  part_o [rows, n_heads, max_splits, 128] and part_ml
+// One new token per request: row r = request r, or, with `rows` and `reqs` (n_rows entries each), row rows[i] of
+// request reqs[i] (a negative row is skipped).  part_o [rows, n_heads, max_splits, 128] and part_ml
 // [rows, n_heads, max_splits, 2] are float32 scratch; counters [rows * n_kv_heads] are ints that are zero
 // (the kernel leaves them zero).  Launches that share scratch and counters must not overlap.
 IB_EXPORT int ib_paged_attention_decode(const void* q, const void* k_pages, const void* v_pages, const int* block_table,
                                         int max_pages, int page_size, int n_pages, const int* positions, int n_rows,
                                         int n_heads, int n_kv_heads, int head_dim, float scale, int window, void* out,
                                         int max_splits, float* part_o, float* part_ml, int* counters,
-                                        cudaStream_t stream) {
+                                        const int* rows, const int* reqs, cudaStream_t stream) {
     if (n_rows <= 0) return IB_OK;
+    if ((rows == nullptr) != (reqs == nullptr)) return IB_ERR_ARGUMENT;
     if (n_heads <= 0 || n_kv_heads <= 0 || n_heads % n_kv_heads || page_size <= 0 || max_pages <= 0 || max_splits <= 0)
         return IB_ERR_ARGUMENT;
     const int G = n_heads / n_kv_heads;
@@ -405,7 +415,8 @@ IB_EXPORT int ib_paged_attention_decode(const void* q, const void* k_pages, cons
     }
     dec::Params P;
     P.q = (const __nv_bfloat16*)q; P.block_table = block_table; P.positions = positions; P.out = (__nv_bfloat16*)out;
-    P.part_o = part_o; P.part_ml = part_ml; P.counters = counters; P.max_pages = max_pages; P.page_size = page_size;
+    P.part_o = part_o; P.part_ml = part_ml; P.counters = counters; P.rows = rows; P.reqs = reqs;
+    P.max_pages = max_pages; P.page_size = page_size;
     P.n_pages = n_pages; P.n_heads = n_heads; P.n_kv_heads = n_kv_heads; P.window = window; P.max_splits = max_splits;
     P.scale_log2 = scale * 1.4426950408889634f;
     const size_t smem = 2 * dec::STAGES * dec::TILE_BYTES + 16 * dec::D * 2 + (2 * dec::STAGES + 1) * 8 + 1024;
@@ -432,7 +443,8 @@ IB_EXPORT int ib_attention_decode_error(int reset) {
 #else
 
 IB_EXPORT int ib_paged_attention_decode(const void*, const void*, const void*, const int*, int, int, int, const int*, int,
-                                        int, int, int, float, int, void*, int, float*, float*, int*, cudaStream_t) {
+                                        int, int, int, float, int, void*, int, float*, float*, int*, const int*,
+                                        const int*, cudaStream_t) {
     return IB_ERR_UNSUPPORTED;
 }
 

@@ -83,6 +83,7 @@ __global__ void __launch_bounds__(AM_THREADS) paged_attention_mma_kernel(const A
     const int gid = lane >> 2, tig = lane & 3;
     const int tile = blockIdx.x, kvh = blockIdx.y, split = blockIdx.z;
     const int req = P.tile_req[tile], row0 = P.tile_row0[tile];
+    if (req < 0) return;                            // a place in a tile list of fixed length that holds no tile
     const int G = P.n_heads / P.n_kv_heads;
     const int tpt = DECODE ? 1 : (64 / G);
     int n_tok = P.q_start[req + 1] - row0;

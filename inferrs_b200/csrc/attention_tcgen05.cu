@@ -174,6 +174,7 @@ __global__ void __launch_bounds__(THREADS, 1) attention_kernel(const __grid_cons
     // the last tiles of a prompt see the most keys: they are started first, so that the grid's tail is short
     const int tile = gridDim.x - 1 - blockIdx.x, kvh = blockIdx.y;
     const int req = P.tile_req[tile], row0 = P.tile_row0[tile];
+    if (req < 0) return;                            // a place in a tile list of fixed length that holds no tile
     const int G = P.n_heads / P.n_kv_heads;
     const int tpt = ROWS / G;                       // tokens per tile
     int n_tok = P.q_start[req + 1] - row0;

@@ -64,19 +64,35 @@ class StepContext:
     def decode_only(self) -> bool:
         return self.max_q_len == 1
 
-    def attention_tiles(self, tokens_per_tile: int):
+    def attention_tiles(self, tokens_per_tile: int, portions_only: bool = False):
         """(tile_req, tile_row0, n_tiles): the step's rows cut into tiles of at most ``tokens_per_tile``
-        tokens of one request each.  Made once per step and tile size, on first use."""
-        key = ("attention_tiles", tokens_per_tile)
+        tokens of one request each; with ``portions_only`` without the requests that bring a single token
+        (:meth:`single_rows` has those).  Made once per step and tile size, on first use."""
+        key = ("attention_tiles", tokens_per_tile, portions_only)
         if key not in self.extra:
             req, row0, at = [], [], 0
             for r, n in enumerate(self.q_lens):
-                for s in range(0, n, tokens_per_tile):
-                    req.append(r)
-                    row0.append(at + s)
+                if not (portions_only and n == 1):
+                    for s in range(0, n, tokens_per_tile):
+                        req.append(r)
+                        row0.append(at + s)
                 at += n
-            both = torch.from_numpy(np.asarray([req, row0], dtype=np.int32)).to(self.token_ids.device)
+            both = torch.from_numpy(np.asarray([req, row0], dtype=np.int32).reshape(2, -1)).to(self.token_ids.device)
             self.extra[key] = (both[0], both[1], len(req))
+        return self.extra[key]
+
+    def single_rows(self):
+        """(rows, requests, count) of the requests that bring a single token to the step."""
+        key = "single_rows"
+        if key not in self.extra:
+            rows, reqs, at = [], [], 0
+            for r, n in enumerate(self.q_lens):
+                if n == 1:
+                    rows.append(at)
+                    reqs.append(r)
+                at += n
+            both = torch.from_numpy(np.asarray([rows, reqs], dtype=np.int32).reshape(2, -1)).to(self.token_ids.device)
+            self.extra[key] = (both[0], both[1], len(rows))
         return self.extra[key]
 
 
@@ -86,7 +102,9 @@ class BatchError(ValueError):
 
 def build_context(entries: Sequence[StepEntry], manager: CacheManager, storage: CacheStorage, vocab_size: int,
                   max_positions: int, device: torch.device, fixed_pages: Optional[Sequence[int]] = None,
-                  pad_to: Optional[int] = None, into: Optional[torch.Tensor] = None) -> StepContext:
+                  pad_to: Optional[int] = None, into: Optional[torch.Tensor] = None,
+                  pad_rows: Optional[int] = None, pad_requests: Optional[int] = None,
+                  pad_wanted: Optional[int] = None, tile_sizes: Sequence[int] = ()) -> StepContext:
     """Check the entries and lay their rows out.  Pages must already be reserved in ``manager``.
 
     ``fixed_pages[g]`` pads group g's block table to that many columns, ``pad_to`` pads a step of
@@ -94,6 +112,12 @@ def build_context(entries: Sequence[StepEntry], manager: CacheManager, storage: 
     together they give a step whose shapes and addresses do not change, which a replayed CUDA
     graph needs.  A padding request has one token at position 0 and no pages: it writes nothing
     to the cache and its output is not used.
+
+    ``pad_rows`` does the same for a step of any portions: the rows are padded to ``pad_rows`` (the
+    added rows belong to one padding request without pages), the requests to ``pad_requests``, the
+    wanted places to ``pad_wanted`` (row 0 stands in), and for every (number of tokens, portions
+    only) pair in ``tile_sizes`` the list of attention tiles is laid out with a fixed length, -1
+    marking the places that hold no tile; so is the list of the requests that bring a single token.
     """
     if not entries:
         raise BatchError("a step needs at least one entry")
@@ -137,6 +161,45 @@ def build_context(entries: Sequence[StepEntry], manager: CacheManager, storage: 
     positions = np.concatenate(pos_parts).tolist() if pad_to is not None else None
     row_request = np.concatenate(req_parts).tolist() if pad_to is not None else None
     n_real = len(entries)
+    tiles_fixed = {}
+    if pad_rows is not None:
+        if pad_to is not None or pad_requests is None or pad_wanted is None:
+            raise BatchError("pad_rows needs pad_requests and pad_wanted, and excludes pad_to")
+        n_rows_real = q_start[-1]
+        if n_rows_real > pad_rows or n_real + 1 > pad_requests or len(logit_rows) > pad_wanted:
+            raise BatchError(f"{n_rows_real} rows, {n_real} requests and {len(logit_rows)} wanted places do not fit "
+                             f"the fixed step of {pad_rows} rows, {pad_requests} requests, {pad_wanted} places")
+        for tpt, portions_only in tile_sizes:   # the tiles of the real requests; the padding request gets none
+            t_max = pad_rows // tpt + pad_requests
+            req = np.full(t_max, -1, dtype=np.int32)
+            row0 = np.zeros(t_max, dtype=np.int32)
+            k = 0
+            for r in range(n_real):
+                if portions_only and q_lens[r] == 1:
+                    continue
+                for s0 in range(0, q_lens[r], tpt):
+                    req[k] = r
+                    row0[k] = q_start[r] + s0
+                    k += 1
+            tiles_fixed[(tpt, portions_only)] = (req, row0, t_max)
+        single = np.full((2, pad_requests), -1, dtype=np.int32)   # rows and requests of the single tokens
+        k = 0
+        for r in range(n_real):
+            if q_lens[r] == 1:
+                single[0, k], single[1, k] = q_start[r], r
+                k += 1
+        extra_rows = pad_rows - n_rows_real
+        id_parts.append(np.zeros(extra_rows, dtype=np.int32))
+        pos_parts.append(np.zeros(extra_rows, dtype=np.int32))
+        req_parts.append(np.full(extra_rows, n_real, dtype=np.int32))
+        for r in range(n_real, pad_requests):
+            k = extra_rows if r == n_real else 0
+            q_start.append(q_start[-1] + k)
+            q_lens.append(k)
+            kv_lens.append(max(k, 1))
+            slots.append(0)
+        wanted = list(logit_rows)
+        logit_rows = logit_rows + [0] * (pad_wanted - len(logit_rows))
     if pad_to is not None:
         if any(q != 1 for q in q_lens) or len(entries) > pad_to:
             raise BatchError("only steps of single tokens, no more than pad_to of them, can be padded")
@@ -150,7 +213,7 @@ def build_context(entries: Sequence[StepEntry], manager: CacheManager, storage: 
             slots.append(0)
         wanted = list(logit_rows)
         logit_rows = list(range(pad_to))  # fixed shape: every row's logits are made, the caller picks
-    else:
+    elif pad_rows is None:
         wanted = None
     n, nreq = q_start[-1], len(q_lens)
     tables = []
@@ -174,6 +237,14 @@ def build_context(entries: Sequence[StepEntry], manager: CacheManager, storage: 
     parts = first + [np.asarray(q_start, dtype=np.int32),
              np.asarray(kv_lens, dtype=np.int32), np.asarray(slots, dtype=np.int32),
              np.asarray(logit_rows, dtype=np.int32)] + [t.reshape(-1) for t in tables]
+    tile_at = {}
+    for key, (req, row0, t_max) in tiles_fixed.items():
+        tile_at[key] = len(parts)
+        parts += [req, row0]
+    single_at = None
+    if pad_rows is not None:
+        single_at = len(parts)
+        parts += [single[0], single[1]]
     sizes = [p.size for p in parts]
     # every part starts on a 16-byte boundary, which vector loads and bulk copies need
     offsets, total = [], 0
@@ -191,9 +262,14 @@ def build_context(entries: Sequence[StepEntry], manager: CacheManager, storage: 
     else:
         dev = torch.from_numpy(host).to(device)
     views = [dev[o:o + s] for o, s in zip(offsets, sizes)]
+    extra = {"n_real": n_real, "wanted": wanted, "host": host}
+    for key, at in tile_at.items():
+        extra[("attention_tiles",) + key] = (views[at], views[at + 1], tiles_fixed[key][2])
+    if single_at is not None:
+        extra["single_rows"] = (views[single_at], views[single_at + 1], pad_requests)
     return StepContext(
         token_ids=views[0], positions=views[1], row_request=views[2], q_start=views[3], kv_len=views[4],
         slots=views[5], logit_rows=views[6],
         block_tables=[views[7 + g].view(nreq, tables[g].shape[1]) for g in range(len(tables))],
         storage=storage, n_rows=n, n_requests=nreq, q_lens=q_lens, kv_lens=kv_lens, slot_list=slots,
-        max_q_len=max(q_lens), max_kv_len=max(kv_lens), extra={"n_real": n_real, "wanted": wanted, "host": host})
+        max_q_len=max(q_lens) if pad_rows is None else max(2, max(q_lens)), max_kv_len=max(kv_lens), extra=extra)

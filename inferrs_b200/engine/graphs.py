@@ -142,3 +142,105 @@ class DecodeGraphs:
         cap = _Captured(graph, buffer, logits, launches)
         self.captured[bucket] = cap
         return cap
+
+
+class PortionGraphs:
+    """Steps with prompt portions (alone or beside decoded tokens) as replayed graphs too.
+
+    Such a step is padded to a fixed shape: its rows to the next of a few row counts (the added rows belong to
+    one padding request without pages: they write nothing to the cache and nobody reads what they compute), its
+    requests to the most the cache admits plus that one, its wanted places to as many.  The attention kernels
+    get their tiles from a list of fixed length in the description, in which -1 marks a place without a tile.
+    What the host pays per step is then the description and one graph launch instead of a dozen launches per
+    layer; for small models and short portions that is the difference between a step bound by the host and one
+    bound by the GPU.  The first step of every row count runs once plainly (which also tells which tile sizes
+    the model's attention layers ask for) and is then captured.
+    """
+
+    ROW_BUCKETS = (32, 64, 128, 256, 512, 1024, 2048, 4096)
+
+    def __init__(self, runner, decode: DecodeGraphs, max_rows: int):
+        self.runner = runner
+        self.decode = decode                      # shares its memory pool and its limits
+        self.fixed_pages = decode.fixed_pages
+        self.max_context = decode.max_context
+        self.n_requests = runner.manager.max_requests + 1
+        self.n_wanted = max(self.n_requests, 64)   # wanted places that a captured step provides
+        self.buckets = [b for b in self.ROW_BUCKETS if b <= max(max_rows, self.ROW_BUCKETS[0])]
+        self.captured: Dict[int, _Captured] = {}
+        self.tile_sizes = None        # (tokens per tile, portions only) pairs that the attention layers ask for
+
+    def bucket_for(self, n_rows: int) -> Optional[int]:
+        return next((b for b in self.buckets if b >= n_rows), None)
+
+    def takes(self, entries: Sequence[StepEntry]) -> bool:
+        n_rows = sum(len(e.tokens) for e in entries)
+        n_wanted = sum(len(e.want) for e in entries)
+        m = self.runner.manager
+        return (self.bucket_for(n_rows) is not None and len(entries) < self.n_requests and n_wanted <= self.n_wanted
+                and all(m.n_tokens(e.rid) + len(e.tokens) <= self.max_context for e in entries))
+
+    def _build(self, entries, bucket, device, into=None) -> StepContext:
+        r = self.runner
+        ctx = build_context(entries, r.manager, r.storage, r.spec.vocab_size, r.spec.max_positions, device,
+                            fixed_pages=self.fixed_pages, into=into, pad_rows=bucket, pad_requests=self.n_requests,
+                            pad_wanted=self.n_wanted, tile_sizes=self.tile_sizes)
+        ctx.max_kv_len = self.max_context
+        return ctx
+
+    def run(self, entries: Sequence[StepEntry]) -> torch.Tensor:
+        """Logits [wanted rows, vocab]; pages are already reserved."""
+        r = self.runner
+        bucket = self.bucket_for(sum(len(e.tokens) for e in entries))
+        n_wanted = sum(len(e.want) for e in entries)
+        cap = self.captured.get(bucket)
+        if cap is None:
+            cap = self._capture(entries, bucket)
+        else:
+            k = cap.turn
+            cap.turn ^= 1
+            if cap.copied[k] is not None:
+                cap.copied[k].synchronize()
+            host = self._build(entries, bucket, torch.device("cpu")).extra["host"]
+            stage = cap.staging[k]
+            stage.numpy()[:host.size] = host
+            cap.buffer.copy_(stage, non_blocking=True)
+            ev = cap.copied[k] or torch.cuda.Event()
+            ev.record()
+            cap.copied[k] = ev
+            cap.graph.replay()
+            kernels.count_launches(cap.launches)
+        return cap.logits[:n_wanted]
+
+    def _capture(self, entries: Sequence[StepEntry], bucket: int) -> _Captured:
+        r = self.runner
+        if self.tile_sizes is None:
+            # once plainly: the attention layers ask the context for their tiles, which tells their sizes
+            plain = build_context(entries, r.manager, r.storage, r.spec.vocab_size, r.spec.max_positions, r.rt.device)
+            r.model.forward(plain)
+            self.tile_sizes = sorted(k[1:] for k in plain.extra if isinstance(k, tuple) and k[0] == "attention_tiles")
+        size = self._build(entries, bucket, torch.device("cpu")).extra["host"].size
+        buffer = torch.zeros((size + 16,), dtype=torch.int32, device=r.rt.device)
+        ctx = self._build(entries, bucket, r.rt.device, into=buffer)
+        r.model.forward(ctx)
+        torch.cuda.synchronize()
+        kernels.set_pdl(True, r.rt.dtype)
+        graph = torch.cuda.CUDAGraph()
+        n0 = kernels.launch_count()
+        gc.collect()                # see DecodeGraphs._capture
+        was_enabled = gc.isenabled()
+        gc.disable()
+        try:
+            with torch.cuda.graph(graph, pool=self.decode.pool):
+                logits = r.model.forward(ctx)
+        finally:
+            kernels.set_pdl(False, r.rt.dtype)
+            if was_enabled:
+                gc.enable()
+        launches = kernels.launch_count() - n0
+        if self.decode.pool is None:
+            self.decode.pool = graph.pool()
+        graph.replay()
+        cap = _Captured(graph, buffer, logits, launches)
+        self.captured[bucket] = cap
+        return cap

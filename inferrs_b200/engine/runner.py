@@ -27,7 +27,7 @@ from .model import Model, cache_needs
 class ModelRunner:
     def __init__(self, spec: ModelSpec, weights: Dict[str, torch.Tensor], rt: Runtime, page_size: int,
                  n_pages: int, max_requests: int, use_graphs: Optional[bool] = None,
-                 max_context: Optional[int] = None):
+                 max_context: Optional[int] = None, graph_rows: int = 2048):
         self.spec = spec
         self.rt = rt
         self.model = Model(spec, weights, rt)
@@ -43,10 +43,13 @@ class ModelRunner:
         if use_graphs is None:
             use_graphs = rt.device.type == "cuda"
         self.graphs = None
+        self.portion_graphs = None     # steps with prompt portions of up to ``graph_rows`` rows (0: never)
         if use_graphs and safe and rt.device.type == "cuda":
-            from .graphs import DecodeGraphs
+            from .graphs import DecodeGraphs, PortionGraphs
             limit = min(max_context or spec.max_positions, spec.max_positions, n_pages * page_size)
             self.graphs = DecodeGraphs(self, limit)
+            if graph_rows > 0:
+                self.portion_graphs = PortionGraphs(self, self.graphs, graph_rows)
 
     # ---- requests -----------------------------------------------------------
     def admit(self, rid: Hashable) -> int:
@@ -64,8 +67,10 @@ class ModelRunner:
         return self.manager.n_tokens(rid)
 
     def warm_up(self, batch_sizes: Optional[Sequence[int]] = None) -> List[int]:
-        """Capture the decode graphs now instead of at the first step of each batch size (a capture takes
-        as long as a few hundred steps).  Only while no request is live; returns the sizes captured."""
+        """Capture the graphs now instead of at the first step of each size (a capture takes as long as a few
+        hundred steps): the decode steps of the given batch sizes, or, if none is given, of all sizes and the
+        steps with prompt portions of every row count as well.  Only while no request is live; returns the
+        batch sizes captured (and the row counts, negated)."""
         if self.graphs is None or self.manager.n_live:
             return []
         done = []
@@ -84,6 +89,22 @@ class ModelRunner:
                     done.append(bucket)
             finally:
                 for rid in rids:
+                    self.release(rid)
+        if self.portion_graphs is not None and batch_sizes is None:
+            # the steps with prompt portions too: one stand-in request with as many tokens as each row count has
+            pg = self.portion_graphs
+            for rows in pg.buckets:
+                n = min(rows, pg.max_context - 1)
+                if rows in pg.captured or pg.bucket_for(n) != rows:
+                    continue
+                rid = ("warm-up", "rows", rows)
+                self.admit(rid)
+                try:
+                    if self.manager.can_reserve({rid: n}):
+                        self.manager.reserve({rid: n})
+                        pg.run([StepEntry(rid, [0] * n, [n - 1])])
+                        done.append(-rows)
+                finally:
                     self.release(rid)
         return done
 
@@ -118,6 +139,14 @@ class ModelRunner:
                 raise ValueError("a request appears twice in one step")
             self.manager.reserve(wants)
             logits = self.graphs.run(entries)
+            if own_output:
+                logits = logits.clone()
+        elif self.portion_graphs is not None and self.portion_graphs.takes(entries):
+            wants = {e.rid: len(e.tokens) for e in entries}
+            if len(wants) != len(entries):
+                raise ValueError("a request appears twice in one step")
+            self.manager.reserve(wants)
+            logits = self.portion_graphs.run(entries)
             if own_output:
                 logits = logits.clone()
         else:

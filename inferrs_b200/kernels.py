@@ -44,7 +44,8 @@ _SIGNATURES = {
     "ib_attention_tcgen05_error": [c_int],
     "ib_row_fault": [c_int],
     "ib_paged_attention_decode": [c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_void_p, c_int, c_int,
-                                  c_int, c_int, c_float, c_int, c_void_p, c_int, c_void_p, c_void_p, c_void_p, c_void_p],
+                                  c_int, c_int, c_float, c_int, c_void_p, c_int, c_void_p, c_void_p, c_void_p, c_void_p,
+                                  c_void_p, c_void_p],
     "ib_attention_decode_error": [c_int],
     "ib_argmax": [c_void_p, c_void_p, c_int, c_int, c_long, c_void_p, c_void_p],
     "ib_penalties": [c_void_p, c_long, c_int, c_int, c_void_p, c_int, c_void_p, c_void_p, c_void_p, c_void_p,
@@ -439,9 +440,11 @@ def decode_max_splits(n_requests: int, n_kv_heads: int, max_kv_len: int) -> int:
 
 def paged_attention_decode(q: torch.Tensor, k_pages: torch.Tensor, v_pages: torch.Tensor, block_table: torch.Tensor,
                            positions: torch.Tensor, scale: float, window: Optional[int], out: torch.Tensor,
-                           max_splits: int):
+                           max_splits: int, rows: Optional[torch.Tensor] = None, reqs: Optional[torch.Tensor] = None):
     """Attention of one new token per request (row r = request r) over its pages: TMA-fed key/value tiles, split
-    over the keys, merged by the slice that finishes last (bfloat16, head_dim 128)."""
+    over the keys, merged by the slice that finishes last (bfloat16, head_dim 128).  With ``rows`` and ``reqs``
+    (int32, equally long) only the rows named are worked on, row ``rows[i]`` being a single token of request
+    ``reqs[i]``; a negative row is skipped.  The other rows of ``out`` are left alone."""
     bf = (torch.bfloat16,)
     _need(q, "q", bf, 3)
     _need(k_pages, "k_pages", bf, 4)
@@ -449,10 +452,18 @@ def paged_attention_decode(q: torch.Tensor, k_pages: torch.Tensor, v_pages: torc
     _need(out, "out", bf, 2)
     _need(block_table, "block_table", _I, 2)
     _need(positions, "positions", _I, 1)
-    n, nh, d = q.shape
+    n_q, nh, d = q.shape
     n_pages, nkv, page_size, dk = k_pages.shape
-    if dk != d or v_pages.shape != k_pages.shape or out.shape != (n, nh * d) or block_table.shape[0] < n:
+    _need(rows, "rows", _I, 1, optional=True)
+    _need(reqs, "reqs", _I, 1, optional=True)
+    if (rows is None) != (reqs is None) or (rows is not None and rows.shape != reqs.shape):
+        raise KernelError("paged_attention_decode: rows and reqs come together and are equally long")
+    n = n_q if rows is None else rows.shape[0]
+    if dk != d or v_pages.shape != k_pages.shape or out.shape != (n_q, nh * d) or positions.shape[0] != n_q \
+            or (rows is None and block_table.shape[0] < n):
         raise KernelError(f"paged_attention_decode: q {tuple(q.shape)}, pages {tuple(k_pages.shape)}, out {tuple(out.shape)}")
+    if n == 0:
+        return
     if not tma_decode_attention_supported(q.dtype, nh, nkv, d, page_size):
         raise KernelError(f"paged_attention_decode takes head_dim 128, a page size of 8..64 that divides 64 and at most "
                           f"16 query heads per key/value head; got head_dim {d}, page size {page_size}, {nh}/{nkv} heads")
@@ -468,7 +479,7 @@ def paged_attention_decode(q: torch.Tensor, k_pages: torch.Tensor, v_pages: torc
     _check(_core(torch.bfloat16).ib_paged_attention_decode(
         _p(q), _p(k_pages), _p(v_pages), _p(block_table), block_table.shape[1], page_size, n_pages, _p(positions), n,
         nh, nkv, d, float(scale), int(window) if window else 0, _p(out), int(max_splits), _p(part_o), _p(part_ml),
-        _p(counters), _stream()), "paged_attention_decode")
+        _p(counters), _p(rows), _p(reqs), _stream()), "paged_attention_decode")
 
 
 def attention_decode_error(reset: bool = True) -> int:
@@ -536,6 +547,18 @@ def paged_attention(q: torch.Tensor, k_pages: torch.Tensor, v_pages: torch.Tenso
         splits = decode_splits(ctx.n_requests, nkv, ctx.max_kv_len)
         paged_attention_mma(q, k_pages, v_pages, block_table, ctx.row_request, ctx.q_start, ctx.n_requests,
                             ctx.q_start, ctx.positions, scale, window, out, True, splits)
+    elif tcgen05_attention_supported(q.dtype, nh, nkv, d, page_size) \
+            and tma_decode_attention_supported(q.dtype, nh, nkv, d, page_size):
+        # portions of prompts and single tokens side by side: the single tokens go to the decode kernel (a tile
+        # of the prefill kernel would hold one token of 32), the portions to the prefill kernel
+        rows, reqs, n_single = ctx.single_rows()
+        if n_single > 0:
+            paged_attention_decode(q, k_pages, v_pages, block_table, ctx.positions, scale, window, out,
+                                   decode_max_splits(n_single, nkv, ctx.max_kv_len), rows, reqs)
+        tile_req, tile_row0, n_tiles = ctx.attention_tiles(TC_ROWS // (nh // nkv), portions_only=True)
+        if n_tiles > 0:
+            paged_attention_tcgen05(q, k_pages, v_pages, block_table, tile_req, tile_row0, n_tiles, ctx.q_start,
+                                    ctx.positions, scale, window, out)
     elif tcgen05_attention_supported(q.dtype, nh, nkv, d, page_size):
         tile_req, tile_row0, n_tiles = ctx.attention_tiles(TC_ROWS // (nh // nkv))
         paged_attention_tcgen05(q, k_pages, v_pages, block_table, tile_req, tile_row0, n_tiles, ctx.q_start,

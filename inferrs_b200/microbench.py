@@ -6,6 +6,9 @@
     python -m inferrs_b200.microbench chain --impl library --m 8 --layers 8
     python -m inferrs_b200.microbench step --form decode --batch 8 --context 2048 --layers 8
     python -m inferrs_b200.microbench step --form decode --batch 8 --context 2048 --layers 3 --trace
+    python -m inferrs_b200.microbench workload --shape 0.6b --requests 256 --prompt-min 16 --prompt-max 1024
+    python -m inferrs_b200.microbench workload --shape 32b --requests 8 --prompt-min 8192 --prompt-max 8192 \
+        --max-context 16384
 
 Every case is timed with CUDA events after warm-up; between timed launches a buffer larger than the
 L2 cache is written, so each launch starts cold.  One JSON line per case.
@@ -258,6 +261,67 @@ def step(args) -> dict:
             "TFLOPs": round(flops / us / 1e6, 1)}
 
 
+SHAPES = {
+    # layer sizes of the published Qwen3 checkpoints (random weights are made on the device)
+    "0.6b": dict(num_hidden_layers=28, hidden_size=1024, num_attention_heads=16, num_key_value_heads=8, head_dim=128,
+                 intermediate_size=3072, tie_word_embeddings=True),
+    "8b": dict(num_hidden_layers=36, hidden_size=4096, num_attention_heads=32, num_key_value_heads=8, head_dim=128,
+               intermediate_size=12288, tie_word_embeddings=False),
+    "32b": dict(num_hidden_layers=64, hidden_size=5120, num_attention_heads=64, num_key_value_heads=8, head_dim=128,
+                intermediate_size=25600, tie_word_embeddings=False),
+}
+
+
+def workload(args) -> dict:
+    """Requests through the engine's own scheduler, host token ids in and out, timed by the wall clock:
+    ``--requests`` prompts with lengths uniform in [--prompt-min, --prompt-max], ``--max-tokens`` greedy tokens
+    each, all added at once (continuous batching with prompts cut into portions of ``--prefill-chunk``)."""
+    import time
+
+    from .engine.engine import Engine
+    from .sampling.params import SamplingParams
+    config = dict({"architectures": ["Qwen3ForCausalLM"], "model_type": "qwen3", "vocab_size": args.vocab,
+                   "rope_theta": 1000000.0, "rms_norm_eps": 1e-6, "hidden_act": "silu",
+                   "max_position_embeddings": args.max_context}, **SHAPES[args.shape])
+    if args.layers:
+        config["num_hidden_layers"] = args.layers
+    per_request = (args.prompt_max + args.max_tokens + args.page_size) // args.page_size
+    eng = Engine(config=config, random_weights=0, dtype="bf16", block_size=args.page_size,
+                 num_blocks=args.requests * per_request, max_batch_size=args.requests,
+                 max_tokens_per_step=args.tokens_per_step, prefill_chunk=args.prefill_chunk)
+    eng.warm_up()
+    g = torch.Generator().manual_seed(7)
+    lens = torch.randint(args.prompt_min, args.prompt_max + 1, (args.requests,), generator=g).tolist()
+    sp = SamplingParams.greedy(max_tokens=args.max_tokens, ignore_eos=True)
+    for n in lens:
+        eng.add_request(torch.randint(0, args.vocab, (n,), generator=g).tolist(), sp)
+    torch.cuda.synchronize()
+    t0 = time.perf_counter()
+    first_decode = None
+    steps = mixed = 0
+    while eng.has_work():
+        waiting_before = len(eng.scheduler.waiting) + sum(r.n_pending > 1 for r in eng.scheduler.running)
+        eng.step()
+        steps += 1
+        mixed += waiting_before > 0
+        if first_decode is None and waiting_before == 0:
+            torch.cuda.synchronize()
+            first_decode = time.perf_counter()
+    torch.cuda.synchronize()
+    t1 = time.perf_counter()
+    st = eng.stats()
+    out = {"kernel": "workload", "shape": args.shape, "layers": config["num_hidden_layers"], "requests": args.requests,
+           "prompt_tokens": sum(lens), "generated_tokens": args.requests * args.max_tokens, "steps": steps,
+           "steps_with_prompt_portions": mixed, "preemptions": st["preemptions"], "seconds": round(t1 - t0, 3),
+           "generated_tokens_per_s": round(args.requests * args.max_tokens / (t1 - t0), 1),
+           "all_tokens_per_s": round((sum(lens) + args.requests * args.max_tokens) / (t1 - t0), 1)}
+    if first_decode is not None:
+        out["until_all_prompts_are_in_s"] = round(first_decode - t0, 3)
+        out["prompt_tokens_per_s_until_then"] = round(sum(lens) / (first_decode - t0), 1)
+        out["decode_tokens_per_s_after"] = round(args.requests * (steps - mixed - 1) / max(t1 - first_decode, 1e-9), 1)
+    return out
+
+
 def main(argv=None) -> int:
     ap = argparse.ArgumentParser(prog="inferrs_b200.microbench", description=__doc__,
                                  formatter_class=argparse.RawDescriptionHelpFormatter)
@@ -315,6 +379,19 @@ def main(argv=None) -> int:
     st.add_argument("--iters", type=int, default=64)
     st.add_argument("--trace", action="store_true", help="decode form: print when every kernel of one step started and ended")
     st.set_defaults(fn=step)
+    wl = sub.add_parser("workload")
+    wl.add_argument("--shape", choices=sorted(SHAPES), default="0.6b")
+    wl.add_argument("--layers", type=int, default=0, help="fewer layers than the shape has, for quick runs")
+    wl.add_argument("--requests", type=int, default=256)
+    wl.add_argument("--prompt-min", type=int, default=16)
+    wl.add_argument("--prompt-max", type=int, default=1024)
+    wl.add_argument("--max-tokens", type=int, default=128)
+    wl.add_argument("--tokens-per-step", type=int, default=2048)
+    wl.add_argument("--prefill-chunk", type=int, default=2048)
+    wl.add_argument("--max-context", type=int, default=4096)
+    wl.add_argument("--vocab", type=int, default=151936)
+    wl.add_argument("--page-size", type=int, default=16)
+    wl.set_defaults(fn=workload)
     args = ap.parse_args(argv)
     print(json.dumps(args.fn(args)))
     return 0

@@ -133,3 +133,53 @@ def test_long_decode(model_dirs, name, dtype):
     for t in range(3, 400):
         rows.append(runner.step([StepEntry("r", toks[t:t + 1], [0])]))
     check(torch.cat(rows), want, dtype, "long decode")
+
+
+@pytest.mark.parametrize("name,dtype", [("B", torch.float32), ("C", torch.bfloat16), ("D", torch.bfloat16),
+                                        ("D", torch.float32)])
+def test_steps_with_portions_are_replayed_graphs(model_dirs, name, dtype):
+    """Steps with prompt portions are captured once per padded row count and replayed: the second request goes
+    through replays only (other tokens, other pages, other lengths in the same shapes), two requests side by
+    side share steps, and every logit still equals the plain implementation's."""
+    cfg = CONFIGS[name]
+    runner = make_runner(model_dirs[name], dtype, PAGE_SIZE[name], n_pages=96)
+    pg = runner.portion_graphs
+    assert pg is not None
+    sizes = [40, 7, 2, 33, 90, 3, 1, 1, 25]
+    n = sum(sizes)
+    prompts = [random_tokens(n, cfg["vocab_size"], seed=60 + i) for i in range(4)]
+    want = [plain_logits(model_dirs[name], p, dtype) for p in prompts]
+    for i in (0, 1):
+        runner.admit(i)
+        rows, at = [], 0
+        for s in sizes:
+            w = list(range(max(0, s - 20), s))              # the last places of every portion
+            rows.append((at + w[0], runner.step([StepEntry(i, prompts[i][at:at + s], w)])))
+            at += s
+        for first, out in rows:
+            check(out, want[i][first:first + out.shape[0]], dtype, f"request {i} from {first}")
+        if i == 0:
+            captured = sorted(pg.captured)
+            assert captured == [32, 64, 128], captured
+    assert sorted(pg.captured) == captured, "the second request must not have needed a new capture"
+    # two requests in the same steps, one a portion ahead of the other
+    runner.admit(2)
+    runner.admit(3)
+    at = {2: 0, 3: 0}
+    order = [(2, 0), (2, 1), (3, 0), (2, 2), (3, 1), (3, 2), (2, 3), (3, 3), (2, 4), (3, 4)]
+    k = 0
+    while k < len(order):
+        entries, meta = [], []
+        for rid, idx in order[k:k + 2]:
+            if any(m[0] == rid for m in meta):
+                break
+            s = sizes[idx]
+            w = [s - 1]
+            entries.append(StepEntry(rid, prompts[rid][at[rid]:at[rid] + s], w))
+            meta.append((rid, at[rid] + s - 1))
+            at[rid] += s
+        k += len(entries)
+        out = runner.step(entries)
+        for row, (rid, pos) in enumerate(meta):
+            check(out[row:row + 1], want[rid][pos:pos + 1], dtype, f"request {rid} at {pos}")
+    runner.manager.check_invariants()

@@ -130,7 +130,7 @@ def test_warm_up_captures_every_batch_size_and_changes_nothing(model_dirs):
     want = cold.generate(prompts, SamplingParams.greedy(max_tokens=12))
     warm = Engine(model_dirs["B"], **kw)
     assert warm.warm_up([3]) == [4]
-    assert warm.warm_up() == [1, 2, 6]
+    assert warm.warm_up() == [1, 2, 6, -32, -64, -128, -256, -512, -1024]   # row counts that the context of 640 reaches
     assert warm.warm_up() == []
     warm.runner.manager.check_invariants()
     assert warm.stats()["free_pages"] == warm.stats()["pages"]
