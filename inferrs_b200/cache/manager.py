@@ -75,6 +75,7 @@ def host_library():
             "ibh_cache_reserve": [p, i, p, p], "ibh_cache_commit": [p, l, i], "ibh_cache_release": [p, l],
             "ibh_cache_check": [p, ctypes.c_char_p, i],
             "ibh_describe_decode": [p, i, p, p, i, p, i, i, p, i, p],
+            "ibh_describe_step": [p, i, p, p, p, p, p, i, i, i, p, i, p, p, i, i, p, i, p],
         }.items():
             f = getattr(lib, name)
             f.argtypes = args
@@ -254,4 +255,31 @@ class CacheManager:
         bad = ctypes.c_int(0)
         code = self._lib.ibh_describe_decode(self._h, n, handles, toks, bucket, pages, vocab_size, max_positions,
                                              out_ptr, cap, ctypes.byref(bad))
+        return code, bad.value
+
+    def describe_step(self, rids: Sequence[Hashable], tokens: Sequence[Sequence[int]], wants: Sequence[Sequence[int]],
+                      pad_rows: int, pad_requests: int, pad_wanted: int, fixed_pages: Sequence[int],
+                      tile_sizes: Sequence[tuple], vocab_size: int, max_positions: int, out_ptr: int, cap: int):
+        """The same for a step of any portions, padded to ``pad_rows`` rows, ``pad_requests`` requests and
+        ``pad_wanted`` wanted places, with a tile list of fixed length for every (tokens per tile, portions only)
+        pair: the layout of ``build_context(..., pad_rows=...)``.  Returns (numbers written, 0) or (a negative
+        refusal, index of the entry it is about)."""
+        import numpy as np
+        n = len(rids)
+        handles = (ctypes.c_int64 * n)(*[self._handle(rid) for rid in rids])
+        n_tok = (ctypes.c_int * n)(*[len(t) for t in tokens])
+        n_want = (ctypes.c_int * n)(*[len(w) for w in wants])
+        flat = np.fromiter((t for ts in tokens for t in ts), dtype=np.int64)
+        if flat.size and (flat.min() < 0 or flat.max() >= vocab_size):
+            return ERR_TOKEN, 0
+        flat = flat.astype(np.int32)
+        flat_w = np.fromiter((w for ws in wants for w in ws), dtype=np.int64).astype(np.int32)
+        pages = (ctypes.c_int * len(self.groups))(*fixed_pages)
+        k = len(tile_sizes)
+        tile_tokens = (ctypes.c_int * max(k, 1))(*[t for t, _ in tile_sizes])
+        tile_portions = (ctypes.c_int * max(k, 1))(*[int(bool(po)) for _, po in tile_sizes])
+        bad = ctypes.c_int(0)
+        code = self._lib.ibh_describe_step(self._h, n, handles, n_tok, flat.ctypes.data, n_want, flat_w.ctypes.data,
+                                           pad_rows, pad_requests, pad_wanted, pages, k, tile_tokens, tile_portions,
+                                           vocab_size, max_positions, out_ptr, cap, ctypes.byref(bad))
         return code, bad.value

@@ -344,3 +344,125 @@ IBH_EXPORT int ibh_describe_decode(void* h, int n, const int64_t* rids, const in
     }
     return total;
 }
+
+// The description of a step of any portions, padded to a fixed shape (the layout that the captured graphs of
+// such steps read; every part starts on a multiple of four numbers):
+//   token ids [pad_rows] | positions [pad_rows] | request of each row [pad_rows] | first row of each request
+//   [pad_requests + 1] | keys each request sees [pad_requests] | state slots [pad_requests] | rows whose logits
+//   are made [pad_wanted] | per group: block tables [pad_requests, fixed_pages[g]] | per tile size: request and
+//   first row of every attention tile [pad_rows / size + pad_requests each] | rows and requests of the requests
+//   that bring a single token [pad_requests each]
+// Request i brings n_tok[i] tokens (concatenated in `tokens`) and wants the logits at n_want[i] of its places
+// (concatenated in `wants`).  The rows that fill the step up belong to one more request without pages, at position
+// 0; the requests after it are empty.  -1 marks table entries, tiles and single-token places that are not there.
+// A tile size with tile_portions[k] != 0 leaves the single-token requests out.  The pages for the step's tokens are
+// reserved already.  Returns the count of numbers written, or an error with the offending entry in *bad.
+IBH_EXPORT int ibh_describe_step(void* h, int n, const int64_t* rids, const int* n_tok, const int* tokens,
+                                 const int* n_want, const int* wants, int pad_rows, int pad_requests, int pad_wanted,
+                                 const int* fixed_pages, int n_tile_sizes, const int* tile_tokens,
+                                 const int* tile_portions, int vocab_size, int max_positions, int* out, int cap,
+                                 int* bad) {
+    Cache* c = static_cast<Cache*>(h);
+    if (n <= 0 || n + 1 > pad_requests || out == nullptr || pad_rows <= 0 || pad_wanted < 0) return ERR_ARGUMENT;
+    const int n_groups = (int)c->pools.size();
+    auto round4 = [](int v) { return (v + 3) / 4 * 4; };
+    int total_rows = 0, total_want = 0;
+    for (int i = 0; i < n; ++i) {
+        if (n_tok[i] <= 0 || n_want[i] < 0) { if (bad) *bad = i; return ERR_BAD_COUNT; }
+        total_rows += n_tok[i];
+        total_want += n_want[i];
+    }
+    if (total_rows > pad_rows || total_want > pad_wanted) return ERR_ARGUMENT;
+    // where the parts start
+    std::vector<int> off;
+    int at = 0;
+    auto part = [&](int count) { off.push_back(at); at += round4(count); };
+    part(pad_rows); part(pad_rows); part(pad_rows); part(pad_requests + 1); part(pad_requests); part(pad_requests);
+    part(pad_wanted);
+    for (int g = 0; g < n_groups; ++g) part(pad_requests * fixed_pages[g]);
+    std::vector<int> t_max(n_tile_sizes);
+    for (int k = 0; k < n_tile_sizes; ++k) {
+        if (tile_tokens[k] <= 0) return ERR_ARGUMENT;
+        t_max[k] = pad_rows / tile_tokens[k] + pad_requests;
+        part(t_max[k]);
+        part(t_max[k]);
+    }
+    part(pad_requests);
+    part(pad_requests);
+    if (at > cap) return ERR_ARGUMENT;
+    std::memset(out, 0, (size_t)at * sizeof(int));
+    int* ids = out + off[0];
+    int* pos = out + off[1];
+    int* row_req = out + off[2];
+    int* q_start = out + off[3];
+    int* kv_len = out + off[4];
+    int* slots = out + off[5];
+    int* logit_rows = out + off[6];
+    for (int g = 0; g < n_groups; ++g) {
+        int* t = out + off[7 + g];
+        for (int k = 0; k < pad_requests * fixed_pages[g]; ++k) t[k] = RELEASED;
+    }
+    const int tiles_at = 7 + n_groups;
+    for (int k = 0; k < n_tile_sizes; ++k)
+        for (int j = 0; j < t_max[k]; ++j) out[off[tiles_at + 2 * k] + j] = -1;
+    int* single_rows = out + off[tiles_at + 2 * n_tile_sizes];
+    int* single_reqs = out + off[tiles_at + 2 * n_tile_sizes + 1];
+    for (int j = 0; j < pad_requests; ++j) single_rows[j] = single_reqs[j] = -1;
+
+    std::vector<int> n_tiles(n_tile_sizes, 0);
+    int row = 0, tok_at = 0, want_at = 0, n_logit = 0, n_single = 0;
+    for (int i = 0; i < n; ++i) {
+        if (bad != nullptr) *bad = i;
+        Request* r = c->get(rids[i]);
+        if (r == nullptr) return ERR_UNKNOWN_REQUEST;
+        const int t = n_tok[i];
+        if (r->n_tokens + t > max_positions) return ERR_POSITIONS;
+        q_start[i] = row;
+        kv_len[i] = r->n_tokens + t;
+        slots[i] = r->slot;
+        for (int j = 0; j < t; ++j) {
+            const int id = tokens[tok_at + j];
+            if (id < 0 || id >= vocab_size) return ERR_TOKEN;
+            ids[row + j] = id;
+            pos[row + j] = r->n_tokens + j;
+            row_req[row + j] = i;
+        }
+        for (int j = 0; j < n_want[i]; ++j) {
+            const int w = wants[want_at + j];
+            if (w < 0 || w >= t) return ERR_BAD_COUNT;
+            logit_rows[n_logit++] = row + w;
+        }
+        for (int g = 0; g < n_groups; ++g) {
+            const std::vector<int>& table = r->tables[g];
+            if ((int)table.size() > fixed_pages[g]) return ERR_TABLE_WIDTH;
+            if (!table.empty())
+                std::memcpy(out + off[7 + g] + (size_t)i * fixed_pages[g], table.data(), table.size() * sizeof(int));
+        }
+        for (int k = 0; k < n_tile_sizes; ++k) {
+            if (tile_portions[k] && t == 1) continue;
+            for (int s0 = 0; s0 < t; s0 += tile_tokens[k]) {
+                out[off[tiles_at + 2 * k] + n_tiles[k]] = i;
+                out[off[tiles_at + 2 * k + 1] + n_tiles[k]] = row + s0;
+                ++n_tiles[k];
+            }
+        }
+        if (t == 1) {
+            single_rows[n_single] = row;
+            single_reqs[n_single] = i;
+            ++n_single;
+        }
+        row += t;
+        tok_at += t;
+        want_at += n_want[i];
+    }
+    // the request that takes the rows that fill the step up, then the empty ones
+    const int extra = pad_rows - row;
+    for (int j = 0; j < extra; ++j) row_req[row + j] = n;
+    for (int i = n; i < pad_requests; ++i) {
+        const int k = i == n ? extra : 0;
+        q_start[i] = i == n ? row : pad_rows;
+        kv_len[i] = k > 1 ? k : 1;
+    }
+    q_start[pad_requests] = pad_rows;
+    return at;
+}

@@ -201,9 +201,18 @@ class PortionGraphs:
             cap.turn ^= 1
             if cap.copied[k] is not None:
                 cap.copied[k].synchronize()
-            host = self._build(entries, bucket, torch.device("cpu")).extra["host"]
             stage = cap.staging[k]
-            stage.numpy()[:host.size] = host
+            try:
+                code, _ = r.manager.describe_step(
+                    [e.rid for e in entries], [e.tokens for e in entries], [e.want for e in entries], bucket,
+                    self.n_requests, self.n_wanted, self.fixed_pages, self.tile_sizes, r.spec.vocab_size,
+                    r.spec.max_positions, stage.data_ptr(), stage.numel())
+            except (TypeError, ValueError, OverflowError):
+                code = -1
+            if code < 0:
+                # something is wrong with an entry: the general builder says what (or builds it, if it can)
+                host = self._build(entries, bucket, torch.device("cpu")).extra["host"]
+                stage.numpy()[:host.size] = host
             cap.buffer.copy_(stage, non_blocking=True)
             ev = cap.copied[k] or torch.cuda.Event()
             ev.record()

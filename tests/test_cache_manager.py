@@ -213,3 +213,46 @@ def test_native_description_of_a_decode_step_equals_the_general_builders(seed):
     assert m.describe_decode([0], [1], bucket, fixed, vocab, m.n_tokens(0), out.ctypes.data, out.size)[0] < 0
     with pytest.raises(CacheError, match="not live"):
         m.describe_decode([99], [1], bucket, fixed, vocab, max_pos, out.ctypes.data, out.size)
+
+
+@pytest.mark.parametrize("seed", range(4))
+def test_native_description_of_a_padded_step_equals_the_general_builders(seed):
+    """Steps of any portions, padded to a fixed shape with tile lists of fixed length: native code against the
+    general builder, number for number."""
+    import numpy as np
+    import torch
+    from inferrs_b200.engine.batch import StepEntry, build_context
+    rng = random.Random(50 + seed)
+    windows = [None, 13] if seed % 2 else [None]
+    m = CacheManager([GroupLayout(f"g{i}", w) for i, w in enumerate(windows)], page_size=4,
+                     n_pages=[400] * len(windows), max_requests=6)
+    vocab, max_pos = 1000, 300
+    fixed = [(max_pos + 3) // 4] * len(windows)
+    tile_sizes = [(32, True), (16, False)] if seed < 2 else [(64, True)]
+    live = list(range(5))
+    for i in live:
+        m.admit(i)
+    for _ in range(40):
+        chosen = rng.sample(live, rng.randint(1, len(live)))
+        counts = [rng.choice([1, 1, 2, 7, 33]) for _ in chosen]
+        if any(m.n_tokens(rid) + n > max_pos for rid, n in zip(chosen, counts)):
+            break
+        m.reserve(dict(zip(chosen, counts)))
+        tokens = [[rng.randrange(vocab) for _ in range(n)] for n in counts]
+        wants = [sorted(rng.sample(range(n), rng.randint(0, min(n, 3)))) for n in counts]
+        rows = 64 if sum(counts) <= 64 else 256
+        out = np.full(8192, 12345, dtype=np.int32)
+        code, _ = m.describe_step(chosen, tokens, wants, rows, 7, 20, fixed, tile_sizes, vocab, max_pos,
+                                  out.ctypes.data, out.size)
+        ctx = build_context([StepEntry(rid, t, w) for rid, t, w in zip(chosen, tokens, wants)], m, None, vocab, max_pos,
+                            torch.device("cpu"), fixed_pages=fixed, pad_rows=rows, pad_requests=7, pad_wanted=20,
+                            tile_sizes=tile_sizes)
+        host = ctx.extra["host"]
+        assert code == host.size, (code, host.size)
+        assert np.array_equal(out[:code], host)
+        for rid, n in zip(chosen, counts):
+            m.commit(rid, n)
+    m.reserve({0: 2})
+    out = np.zeros(8192, dtype=np.int32)
+    assert m.describe_step([0], [[1, vocab]], [[0]], 64, 7, 20, fixed, tile_sizes, vocab, max_pos, out.ctypes.data, out.size)[0] < 0
+    assert m.describe_step([0], [[1, 2]], [[2]], 64, 7, 20, fixed, tile_sizes, vocab, max_pos, out.ctypes.data, out.size)[0] < 0
