@@ -74,6 +74,7 @@ def host_library():
             "ibh_cache_pages_needed": [p, l, i, p], "ibh_cache_can_reserve": [p, i, p, p],
             "ibh_cache_reserve": [p, i, p, p], "ibh_cache_commit": [p, l, i], "ibh_cache_release": [p, l],
             "ibh_cache_check": [p, ctypes.c_char_p, i],
+            "ibh_cache_fit_in_order": [p, i, p, p, p],
             "ibh_describe_decode": [p, i, p, p, i, p, i, i, p, i, p],
             "ibh_describe_step": [p, i, p, p, p, p, p, i, i, i, p, i, p, p, i, i, p, i, p],
         }.items():
@@ -204,6 +205,21 @@ class CacheManager:
     def can_reserve(self, wants: Dict[Hashable, int]) -> bool:
         n, rids, counts = self._arrays(wants)
         return self._lib.ibh_cache_can_reserve(self._h, n, rids, counts) == 1
+
+    def fit_in_order(self, rids: Sequence[Hashable], n_new: Sequence[int], free: List[int]) -> int:
+        """For a scheduler that walks its requests in order: ``free[g]`` pages of every group are still
+        unspoken for; request ``rids[i]`` would take the pages for ``n_new[i]`` more tokens.  Subtracts what each
+        one needs from ``free`` (in place) as long as it fits and stops at the first that does not; returns
+        how many fitted.  Nothing is taken from the pools."""
+        n = len(rids)
+        handles = (ctypes.c_int64 * n)(*[self._handle(rid) for rid in rids])
+        counts = (ctypes.c_int * n)(*n_new)
+        left = (ctypes.c_int * len(self.groups))(*free)
+        k = self._lib.ibh_cache_fit_in_order(self._h, n, handles, counts, left)
+        if k < 0:
+            raise CacheError(f"fit_in_order: the native cache manager answered {k}")
+        free[:] = list(left)
+        return k
 
     def reserve(self, wants: Dict[Hashable, int]):
         """Take the pages for ``wants[rid]`` more tokens of every request named, or raise

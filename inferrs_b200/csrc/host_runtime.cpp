@@ -466,3 +466,22 @@ IBH_EXPORT int ibh_describe_step(void* h, int n, const int64_t* rids, const int*
     q_start[pad_requests] = pad_rows;
     return at;
 }
+
+// For a scheduler that walks its requests in order: free[g] pages of every group are still unspoken for; request
+// i would take the pages for n_new[i] more tokens.  Goes through the requests in the order given, subtracts what
+// each one needs from free[] as long as it fits, and stops at the first that does not.  Returns how many fitted
+// (n if all did); free[] then holds what is left after those.  Nothing is taken from the pools.
+IBH_EXPORT int ibh_cache_fit_in_order(void* h, int n, const int64_t* rids, const int* n_new, int* free_pages) {
+    Cache* c = static_cast<Cache*>(h);
+    const int n_groups = (int)c->pools.size();
+    std::vector<int> need(n_groups);
+    for (int i = 0; i < n; ++i) {
+        Request* r = c->get(rids[i]);
+        if (r == nullptr) return ERR_UNKNOWN_REQUEST;
+        c->pages_needed(*r, n_new[i], need.data());
+        for (int g = 0; g < n_groups; ++g)
+            if (need[g] > free_pages[g]) return i;
+        for (int g = 0; g < n_groups; ++g) free_pages[g] -= need[g];
+    }
+    return n;
+}

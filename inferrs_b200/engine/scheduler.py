@@ -171,15 +171,21 @@ class Scheduler:
 
             by_age = sorted(self.running, key=lambda r: r.order)
             # decoded tokens first, then portions of prompts, oldest first
-            for r in [r for r in by_age if r.n_pending == 1] + [r for r in by_age if r.n_pending > 1]:
+            order = [r for r in by_age if r.n_pending == 1] + [r for r in by_age if r.n_pending > 1]
+            counts = []
+            for r in order:
                 if budget <= 0:
                     break
                 n = min(r.n_pending, budget, self.prefill_chunk)
-                if not fits(r.rid, n):
-                    starved = r
-                    break
-                plan.append(PlannedEntry(r, r.n_computed, n, r.n_computed + n == r.n_tokens))
+                counts.append(n)
                 budget -= n
+            order = order[:len(counts)]
+            fitted = self.manager.fit_in_order([r.rid for r in order], counts, free) if order else 0
+            for r, n in zip(order[:fitted], counts[:fitted]):
+                plan.append(PlannedEntry(r, r.n_computed, n, r.n_computed + n == r.n_tokens))
+            if fitted < len(order):
+                starved = order[fitted]
+                budget += sum(counts[fitted:])
             if starved is not None:
                 if self._preempt_youngest(keep=starved):
                     continue  # plan again with the pages that came back

@@ -153,6 +153,16 @@ class CacheManager:
                 need[g] += n
         return all(need[g] <= self.pools[g].n_free for g in range(len(self.groups)))
 
+    def fit_in_order(self, rids, n_new, free) -> int:
+        """How many of the requests, taken in order, fit into ``free`` pages per group (changed in place)."""
+        for i, (rid, n) in enumerate(zip(rids, n_new)):
+            need = self.pages_needed(rid, n)
+            if any(need[g] > free[g] for g in range(len(free))):
+                return i
+            for g in range(len(free)):
+                free[g] -= need[g]
+        return len(rids)
+
     def reserve(self, wants: Dict[Hashable, int]):
         """Take the pages for ``wants[rid]`` more tokens of every request named, or raise
         OutOfPages and change nothing."""

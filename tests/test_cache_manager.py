@@ -152,6 +152,10 @@ def test_native_manager_answers_as_the_plain_model_does(seed):
             assert nat.can_reserve(wants) == ref.can_reserve(wants)
             for rid, n in wants.items():
                 assert nat.pages_needed(rid, n) == ref.pages_needed(rid, n)
+            free_a = [max(0, p.n_free - rng.randint(0, 6)) for p in nat.pools]
+            free_b = list(free_a)
+            assert nat.fit_in_order(list(wants), list(wants.values()), free_a) == \
+                ref.fit_in_order(list(wants), list(wants.values()), free_b) and free_a == free_b
             try:
                 ref.reserve(wants)
             except plain_cache.OutOfPages:
