@@ -35,13 +35,16 @@ class Engine:
     max_seq_len          0: the model's max_position_embeddings (reference: --max-seq-len)
     config, random_weights   instead of ``model_dir``: a config.json dictionary and a seed; the weights
                          are made on the device
+    overlap              decode steps are launched one ahead: while the device runs a step, the host reads the
+                         tokens of the step before and plans; a request that turns out to have ended runs one
+                         step in vain.  Results are the same; ``step`` then reports a request's end one call later.
     """
 
     def __init__(self, model_dir: Optional[str] = None, dtype: str = "bf16", block_size: int = 16,
                  num_blocks: Optional[int] = None, paged_attention: float = 0.9, max_batch_size: int = 32,
                  max_tokens_per_step: int = 2048, max_seq_len: int = 0, prefill_chunk: Optional[int] = None,
                  config: Optional[dict] = None, random_weights: Optional[int] = None,
-                 runtime: Optional[Runtime] = None):
+                 runtime: Optional[Runtime] = None, overlap: bool = True):
         self.rt = runtime if runtime is not None else Runtime.cuda(parse_dtype(dtype))
         if model_dir is not None:
             spec, weights, cfg = load_model_dir(model_dir, self.rt)
@@ -62,6 +65,11 @@ class Engine:
         self._rng = random.Random()
         self.n_steps = 0
         self.n_tokens_run = 0
+        # the step whose tokens the host has not read yet: (plan, token ids on the device, pinned copy, event)
+        self.overlap = bool(overlap) and self.rt.device.type == "cuda" and self.runner.graphs is not None
+        self._in_flight = None
+        self._pinned = []
+        self.n_steps_in_vain = 0
 
     def _blocks_for_fraction(self, spec, block_size, fraction, max_batch_size) -> int:
         from .model import cache_needs
@@ -99,7 +107,7 @@ class Engine:
         return self.scheduler.abort(rid)
 
     def has_work(self) -> bool:
-        return not self.scheduler.idle
+        return not self.scheduler.idle or self._in_flight is not None
 
     def warm_up(self, batch_sizes: Optional[Sequence[int]] = None) -> List[int]:
         """Capture the decode graphs for the given numbers of requests (all, if none is given) before the
@@ -107,25 +115,101 @@ class Engine:
         return self.runner.warm_up(batch_sizes)
 
     # ---- one scheduler iteration -----------------------------------------------------
-    def step(self) -> List[Request]:
-        """Plan, run and sample one step; returns the requests that finished in it."""
-        plan, ended = self.scheduler.plan()
-        if not plan:
-            return ended
+    def _launch(self, plan: List[PlannedEntry], device_tokens: Optional[torch.Tensor] = None, pending: int = 0):
+        """Run the planned step and sample; the token ids stay on the device, a copy is on its way to pinned
+        memory.  Returns the step as it is kept until its tokens are read."""
         entries = []
         for e in plan:
-            entries.append(StepEntry(e.request.rid, e.request.token_slice(e.start, e.n),
-                                     [e.n - 1] if e.samples else []))
-        logits = self.runner.step(entries, own_output=False)
+            toks = [0] if device_tokens is not None else e.request.token_slice(e.start, e.n)
+            entries.append(StepEntry(e.request.rid, toks, [e.n - 1] if e.samples else []))
+        logits = self.runner.step(entries, own_output=False, device_tokens=device_tokens)
         sampling = [e for e in plan if e.samples]
-        tokens: List[int] = []
+        ids = host = event = None
         if sampling:
             ids = self.sampler.sample(logits, [e.request.params for e in sampling],
-                                      [e.request.seed for e in sampling], [e.request for e in sampling])
-            tokens = ids.cpu().tolist()
+                                      [e.request.seed for e in sampling], [e.request for e in sampling], pending)
+            if self.overlap:
+                host = self._pinned.pop() if self._pinned else \
+                    torch.empty((self.scheduler.max_batch_size,), dtype=torch.int32).pin_memory()
+                host[:ids.shape[0]].copy_(ids, non_blocking=True)
+                event = torch.cuda.Event()
+                event.record()
         self.n_steps += 1
         self.n_tokens_run += sum(e.n for e in plan)
-        return ended + self.scheduler.update(plan, tokens)
+        return plan, ids, host, event
+
+    def _finish(self, step) -> List[Request]:
+        """Read a launched step's tokens and record it; returns the requests that ended with it."""
+        plan, ids, host, event = step
+        tokens: List[int] = []
+        if ids is not None:
+            if event is not None:
+                event.synchronize()
+                tokens = host[:ids.shape[0]].tolist()
+                self._pinned.append(host)
+            else:
+                tokens = ids.cpu().tolist()
+        # a request that ended while this step was already on its way ran in vain: it is left out
+        alive, kept, it = [], [], iter(tokens)
+        for e in plan:
+            tok = next(it) if e.samples else None
+            if e.request.finish_reason is None:
+                alive.append(e)
+                if e.samples:
+                    kept.append(tok)
+            else:
+                self.n_steps_in_vain += 1
+        return self.scheduler.update(alive, kept)
+
+    def _next_decode_plan(self, step) -> Optional[List[PlannedEntry]]:
+        """The step after ``step`` if it can be told before ``step``'s tokens are known: every running request has
+        just been sampled and brings exactly the sampled token next.  None if anything else may happen (prompts
+        waiting or under way, penalties that need the token, too few pages): then the tokens are read first."""
+        plan, ids, _, _ = step
+        sch = self.scheduler
+        if ids is None or sch.waiting or len(plan) != len(sch.running) or not all(e.samples for e in plan):
+            return None
+        nxt = []
+        for e in plan:
+            r = e.request
+            if r.finish_reason is not None or r.params.has_penalty:
+                return None
+            # with the token that is on its way the request has len(output) + 1 tokens: does it go on after it?
+            if len(r.output) + 1 >= r.params.max_tokens or r.n_tokens + 1 >= sch.max_positions:
+                return None
+            nxt.append(PlannedEntry(r, r.n_tokens, 1, True))
+        free = [pool.n_free for pool in self.runner.manager.pools]
+        # the cache has this step's token committed already: one more token each
+        if self.runner.manager.fit_in_order([e.request.rid for e in nxt], [1] * len(nxt), free) != len(nxt):
+            return None
+        if not self.runner.takes_device_tokens([StepEntry(e.request.rid, [0], [0]) for e in nxt]):
+            return None
+        return nxt
+
+    def step(self) -> List[Request]:
+        """Plan, run and sample one step; returns the requests that are known to have finished.  With
+        ``overlap`` the step is launched before the tokens of the one before it are read, where that can be."""
+        finished: List[Request] = []
+        prev, self._in_flight = self._in_flight, None
+        if prev is not None:
+            nxt = self._next_decode_plan(prev)
+            if nxt is not None:
+                self._in_flight = self._launch(nxt, device_tokens=prev[1], pending=1)
+                return self._finish(prev)
+            finished = self._finish(prev)
+        plan, ended = self.scheduler.plan()
+        if not plan:
+            return finished + ended
+        launched = self._launch(plan)
+        if self.overlap:
+            self._in_flight = launched
+            return finished + ended
+        return finished + ended + self._finish(launched)
+
+    def flush(self) -> List[Request]:
+        """Read the tokens of a step that is still on its way; returns the requests that ended with it."""
+        prev, self._in_flight = self._in_flight, None
+        return self._finish(prev) if prev is not None else []
 
     def generate(self, prompts: Sequence[Sequence[int]],
                  sampling: Union[SamplingParams, Sequence[SamplingParams], None] = None,
@@ -149,6 +233,7 @@ class Engine:
             "steps": self.n_steps,
             "tokens_run": self.n_tokens_run,
             "preemptions": self.scheduler.n_preemptions,
+            "steps_in_vain": self.n_steps_in_vain,
             "running": len(self.scheduler.running),
             "waiting": len(self.scheduler.waiting),
             "free_pages": [p.n_free for p in m.pools],

@@ -95,16 +95,25 @@ class DecodeGraphs:
         ev.record()
         cap.copied[k] = ev
 
-    def run(self, entries: Sequence[StepEntry]) -> torch.Tensor:
-        """Logits [wanted rows, vocab] of a step of single tokens; pages are already reserved."""
+    def run(self, entries: Sequence[StepEntry], device_tokens: Optional[torch.Tensor] = None) -> torch.Tensor:
+        """Logits [wanted rows, vocab] of a step of single tokens; pages are already reserved.  With
+        ``device_tokens`` (int32 on the device, one per entry) the entries' own token ids are stand-ins: the step
+        takes its tokens from there, in stream order, so it can be launched before the host has seen them."""
         bucket = self.bucket_for(len(entries))
         cap = self.captured.get(bucket)
         if cap is None:
             cap = self._capture(entries, bucket)
-        else:
-            self._describe(cap, entries, bucket)
-            cap.graph.replay()
-            kernels.count_launches(cap.launches)
+            if device_tokens is None:
+                return self._wanted(cap, entries)
+        self._describe(cap, entries, bucket)
+        if device_tokens is not None:
+            cap.buffer[:len(entries)].copy_(device_tokens[:len(entries)])   # the token ids lead the description
+        cap.graph.replay()
+        kernels.count_launches(cap.launches)
+        return self._wanted(cap, entries)
+
+    @staticmethod
+    def _wanted(cap: _Captured, entries: Sequence[StepEntry]) -> torch.Tensor:
         wanted = [i for i, e in enumerate(entries) for _ in e.want]
         if wanted == list(range(len(entries))):
             return cap.logits[:len(entries)]

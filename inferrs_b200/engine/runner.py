@@ -126,19 +126,29 @@ class ModelRunner:
             self.manager.commit(e.rid, len(e.tokens))
         self.steps_run += 1
 
-    def step(self, entries: Sequence[StepEntry], own_output: bool = True) -> torch.Tensor:
+    def takes_device_tokens(self, entries: Sequence[StepEntry]) -> bool:
+        """Whether :meth:`step` can run these entries with their token ids still on the device."""
+        return self.graphs is not None and all(len(e.tokens) == 1 for e in entries) \
+            and all(self.manager.n_tokens(e.rid) < self.graphs.max_context for e in entries)
+
+    def step(self, entries: Sequence[StepEntry], own_output: bool = True,
+             device_tokens: Optional[torch.Tensor] = None) -> torch.Tensor:
         """float32 logits [number of wanted places, vocab], in the order of entries and of ``want``.
 
         ``own_output=False`` may return a view of a buffer that the next step overwrites (a replayed
         graph writes to fixed memory); the caller must be done with it before it steps again.
+        ``device_tokens`` (int32 on the device, one per entry): the step of single tokens takes its token ids
+        from there instead of from the entries (see :meth:`takes_device_tokens`).
         """
+        if device_tokens is not None and not self.takes_device_tokens(entries):
+            raise ValueError("only a replayed step of single tokens can take its token ids from the device")
         if self.graphs is not None and all(len(e.tokens) == 1 for e in entries) \
                 and all(self.manager.n_tokens(e.rid) < self.graphs.max_context for e in entries):
             wants = {e.rid: 1 for e in entries}
             if len(wants) != len(entries):
                 raise ValueError("a request appears twice in one step")
             self.manager.reserve(wants)
-            logits = self.graphs.run(entries)
+            logits = self.graphs.run(entries, device_tokens)
             if own_output:
                 logits = logits.clone()
         elif self.portion_graphs is not None and self.portion_graphs.takes(entries):

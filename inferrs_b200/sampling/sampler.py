@@ -21,13 +21,15 @@ class Sampler:
         self.act_dtype = act_dtype
 
     def sample(self, logits: torch.Tensor, params: Sequence[SamplingParams], seeds: Sequence[int],
-               histories: Sequence[Sequence[int]]) -> torch.Tensor:
+               histories: Sequence[Sequence[int]], pending: int = 0) -> torch.Tensor:
         """int32 token ids [rows] (on the device) for float32 ``logits`` [rows, vocab].
 
         ``histories[r]`` is all tokens of row r's request so far, prompt and generated: its length is the
         step index of the random draw and its tail is the penalties' window.  It may be a list of token ids
         or an object with ``n_tokens`` and ``tail(n)`` (the scheduler's requests, which keep prompt and
-        output apart).  ``logits`` is changed in place where penalties apply.
+        output apart).  ``logits`` is changed in place where penalties apply.  ``pending``: tokens of every
+        request that are on their way but not in its history yet (they count for the step index of the draw;
+        penalties cannot be applied then).
         """
         r = logits.shape[0]
         out = torch.empty((r,), dtype=torch.int32, device=self.device)
@@ -36,8 +38,10 @@ class Sampler:
         if all(p.is_greedy and not p.has_penalty for p in params):
             kernels.argmax(logits, out, self.act_dtype)
             return out
-        length = [h.n_tokens if hasattr(h, "n_tokens") else len(h) for h in histories]
+        length = [(h.n_tokens if hasattr(h, "n_tokens") else len(h)) + pending for h in histories]
         if any(p.has_penalty for p in params):
+            if pending:
+                raise ValueError("penalties need the whole history: they cannot be applied while tokens are pending")
             width = max(1, max(min(p.repeat_last_n, n) if p.has_penalty else 0 for p, n in zip(params, length)))
             prev = np.full((r, width), -1, dtype=np.int32)
             n_prev = np.zeros((r,), dtype=np.int32)

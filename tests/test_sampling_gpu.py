@@ -136,3 +136,39 @@ def test_warm_up_captures_every_batch_size_and_changes_nothing(model_dirs):
     assert warm.stats()["free_pages"] == warm.stats()["pages"]
     assert warm.generate(prompts, SamplingParams.greedy(max_tokens=12)) == want
     assert sorted(warm.runner.graphs.captured) == [1, 2, 4, 6]
+
+
+@pytest.mark.parametrize("name,dtype", [("B", "f32"), ("D", "bf16")])
+def test_steps_launched_one_ahead_give_the_same_tokens(model_dirs, name, dtype):
+    """With ``overlap`` a decode step is launched before the host has read the tokens of the step before it (the
+    device hands them on).  Greedy and seeded sampling, requests that stop at a token nobody could foresee, and
+    a cache so small that requests are preempted must all give what the engine gives step by step."""
+    from inferrs_b200 import Engine
+    cfg = CONFIG_B if name == "B" else __import__("helpers").CONFIG_D
+    prompts = [random_tokens(n, cfg["vocab_size"], seed=40 + n) for n in (5, 17, 33, 60)]
+    kw = dict(dtype=dtype, block_size=16, num_blocks=64, max_batch_size=4, max_tokens_per_step=48)
+
+    def both(params, **more):
+        a = Engine(model_dirs[name], overlap=False, **dict(kw, **more))
+        b = Engine(model_dirs[name], overlap=True, **dict(kw, **more))
+        assert b.overlap and not a.overlap
+        ra = a.generate(prompts, params, return_requests=True)
+        rb = b.generate(prompts, params, return_requests=True)
+        assert [r.output for r in ra] == [r.output for r in rb]
+        assert [r.finish_reason for r in ra] == [r.finish_reason for r in rb]
+        assert b.stats()["free_pages"] == b.stats()["pages"] and not b.has_work()
+        return ra, b
+
+    ra, b = both(SamplingParams.greedy(max_tokens=40))
+    assert b.n_steps_in_vain == 0
+    # a token that one of the requests reaches for the first time in the middle of its decoding
+    first_seen = [(i, r.output[i]) for r in ra for i in range(4, 36) if r.output[i] not in r.output[:i]
+                  and all(r.output[i] not in o.output[:4] for o in ra)]
+    assert first_seen, "the test wants a token that first comes up while all requests decode"
+    stop = first_seen[0][1]
+    ra, b = both(SamplingParams(temperature=0.0, repetition_penalty=1.0, max_tokens=40, stop_token_ids=(stop,)))
+    assert any(r.finish_reason == "stop" and 4 < len(r.output) < 40 for r in ra) and b.n_steps_in_vain >= 1
+    both(SamplingParams(temperature=0.8, top_k=0, top_p=1.0, repetition_penalty=1.0, max_tokens=30, seed=9))
+    both(SamplingParams(temperature=0.7, max_tokens=20, seed=3))          # the reference's defaults: penalties
+    ra, b = both(SamplingParams.greedy(max_tokens=40), num_blocks=9)      # too few pages for all four at once
+    assert b.stats()["preemptions"] > 0
