@@ -187,6 +187,106 @@ __global__ void qk_norm_rope_store_d128_kernel(
 }
 #endif
 
+#if IB_ACT_BF16
+// The same for thousands of rows, where the bytes in flight decide: sixteen lanes per head with eight elements
+// (16 bytes) each, so a warp takes two heads at a time and eight heads in all, all loads issued before the
+// first is used.  Element i < 64 pairs with i + 64: lane l of a head's sixteen pairs with lane l ^ 8.
+template <typename WT>
+__global__ void qk_norm_rope_store_d128_wide_kernel(
+    const __nv_bfloat16* __restrict__ qkv, int row_stride, int n_heads, int n_kv_heads, int store_kv,
+    const WT* __restrict__ q_weight, const WT* __restrict__ k_weight, float eps,
+    const float* __restrict__ cos_table, const float* __restrict__ sin_table, int table_rows,
+    const int* __restrict__ positions, const int* __restrict__ row_request,
+    const int* __restrict__ block_table, int max_pages, int page_size, int n_pages,
+    __nv_bfloat16* __restrict__ k_pages, __nv_bfloat16* __restrict__ v_pages, __nv_bfloat16* __restrict__ q_out) {
+    constexpr int HPW = 8;                       // heads per warp
+    ib_grid_dependency_launch();
+    const int row = blockIdx.x;
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const int heads_total = n_heads + (store_kv ? 2 * n_kv_heads : 0);
+    const int head0 = (blockIdx.y * (blockDim.x >> 5) + warp) * HPW;
+    if (head0 >= heads_total) return;
+    const int pos = positions[row];
+    if (pos < 0 || pos >= table_rows) { ib_note_row_fault(row); return; }
+    long kv_base = -1;
+    if (store_kv && head0 + HPW > n_heads) {
+        const int req = row_request[row];
+        const int page = pos / page_size < max_pages ? block_table[(long)req * max_pages + pos / page_size] : -1;
+        if (page >= 0 && page < n_pages) kv_base = ((long)page * n_kv_heads * page_size + (pos % page_size)) * 128;
+    }
+    const int sub = lane >> 4, l16 = lane & 15;  // which of the two heads of a pass, and the place in it
+    const int e0 = 8 * l16;                      // this lane's eight elements of the head
+    const int i0 = 8 * (l16 & 7);                // their index into the rotation tables (e0 mod 64)
+    float cs[8], sn[8];
+    {
+        const float4 c0 = *reinterpret_cast<const float4*>(cos_table + (long)pos * 64 + i0);
+        const float4 c1 = *reinterpret_cast<const float4*>(cos_table + (long)pos * 64 + i0 + 4);
+        const float4 s0 = *reinterpret_cast<const float4*>(sin_table + (long)pos * 64 + i0);
+        const float4 s1 = *reinterpret_cast<const float4*>(sin_table + (long)pos * 64 + i0 + 4);
+        cs[0] = c0.x; cs[1] = c0.y; cs[2] = c0.z; cs[3] = c0.w; cs[4] = c1.x; cs[5] = c1.y; cs[6] = c1.z; cs[7] = c1.w;
+        sn[0] = s0.x; sn[1] = s0.y; sn[2] = s0.z; sn[3] = s0.w; sn[4] = s1.x; sn[5] = s1.y; sn[6] = s1.z; sn[7] = s1.w;
+    }
+    float wq[8], wk[8];
+#pragma unroll
+    for (int e = 0; e < 8; ++e) {
+        wq[e] = (q_weight != nullptr && head0 < n_heads) ? ib_to_float(q_weight[e0 + e]) : 1.0f;
+        wk[e] = (k_weight != nullptr && head0 + HPW > n_heads) ? ib_to_float(k_weight[e0 + e]) : 1.0f;
+    }
+    ib_grid_dependency_wait();
+    uint4 raw[HPW / 2];
+#pragma unroll
+    for (int j = 0; j < HPW / 2; ++j) {
+        const int head = head0 + 2 * j + sub;
+        if (head < heads_total)
+            raw[j] = *reinterpret_cast<const uint4*>(qkv + (long)row * row_stride + (long)head * 128 + e0);
+    }
+#pragma unroll
+    for (int j = 0; j < HPW / 2; ++j) {
+        const int head = head0 + 2 * j + sub;
+        const bool live = head < heads_total;   // the other half of the warp may still have a head: no early exit
+        const int kind = head < n_heads ? 0 : (head < n_heads + n_kv_heads ? 1 : 2);
+        float x[8];
+        const __nv_bfloat162* h2 = reinterpret_cast<const __nv_bfloat162*>(&raw[j]);
+#pragma unroll
+        for (int e = 0; e < 4; ++e) {
+            const float2 f = live ? __bfloat1622float2(h2[e]) : make_float2(0.0f, 0.0f);
+            x[2 * e] = f.x;
+            x[2 * e + 1] = f.y;
+        }
+        const WT* w = kind == 0 ? q_weight : k_weight;
+        float ss = 0.0f;
+#pragma unroll
+        for (int e = 0; e < 8; ++e) ss += x[e] * x[e];
+#pragma unroll
+        for (int o = 8; o > 0; o >>= 1) ss += __shfl_xor_sync(0xffffffffu, ss, o);   // over the head's sixteen lanes
+        if (kind != 2 && w != nullptr) {
+            const float inv = 1.0f / sqrtf(ss / 128.0f + eps);
+#pragma unroll
+            for (int e = 0; e < 8; ++e) x[e] = x[e] * inv * (kind == 0 ? wq[e] : wk[e]);
+        }
+#pragma unroll
+        for (int e = 0; e < 8; ++e) {
+            const float other = __shfl_xor_sync(0xffffffffu, x[e], 8);
+            if (kind != 2) x[e] = l16 < 8 ? x[e] * cs[e] - other * sn[e] : other * sn[e] + x[e] * cs[e];
+        }
+        if (!live) continue;
+        __nv_bfloat16* dst;
+        if (kind == 0) {
+            dst = q_out + ((long)row * n_heads + head) * 128;
+        } else {
+            if (kv_base < 0) continue;
+            const int kvh = head - n_heads - (kind == 2 ? n_kv_heads : 0);
+            dst = (kind == 1 ? k_pages : v_pages) + kv_base + (long)kvh * page_size * 128;
+        }
+        uint4 o;
+        __nv_bfloat162* o2 = reinterpret_cast<__nv_bfloat162*>(&o);
+#pragma unroll
+        for (int e = 0; e < 4; ++e) o2[e] = __floats2bfloat162_rn(x[2 * e], x[2 * e + 1]);
+        *reinterpret_cast<uint4*>(dst + e0) = o;
+    }
+}
+#endif
+
 IB_EXPORT int ib_qk_norm_rope_store(const void* qkv, int row_stride, int n_rows, int n_heads, int n_kv_heads,
                                     int head_dim, int store_kv, const void* q_weight, const void* k_weight,
                                     int weight_is_f32, float eps, const float* cos_table, const float* sin_table,
@@ -210,8 +310,21 @@ IB_EXPORT int ib_qk_norm_rope_store(const void* qkv, int row_stride, int n_rows,
               (const WT*)q_weight, (const WT*)k_weight, eps, cos_table, sin_table, table_rows, positions, row_request,  \
               block_table, max_pages, page_size, n_pages, (__nv_bfloat16*)k_pages, (__nv_bfloat16*)v_pages,            \
               (__nv_bfloat16*)q_out)
-        // few rows: one head per warp, for the shortest chain; many rows: four heads per warp, for bytes in flight
-        if (n_rows >= 256) {
+        // few rows: one head per warp, for the shortest chain; many rows: eight heads per warp and sixteen bytes
+        // per lane, for bytes in flight (the cache pages and the output must then be 16-byte aligned)
+        if (n_rows >= 256 && (row_stride % 8) == 0 && ((uintptr_t)qkv % 16) == 0 && ((uintptr_t)q_out % 16) == 0 &&
+            (!store_kv || (((uintptr_t)k_pages % 16) == 0 && ((uintptr_t)v_pages % 16) == 0))) {
+            int warps = (heads_total + 7) / 8;
+            if (warps > 8) warps = 8;
+            const dim3 wide_grid(n_rows, (heads_total + 8 * warps - 1) / (8 * warps));
+#define IB_LAUNCH_WIDE(WT)                                                                                            \
+    ib_launch(qk_norm_rope_store_d128_wide_kernel<WT>, wide_grid, 32 * warps, 0, stream, (const __nv_bfloat16*)qkv,   \
+              row_stride, n_heads, n_kv_heads, store_kv, (const WT*)q_weight, (const WT*)k_weight, eps, cos_table,     \
+              sin_table, table_rows, positions, row_request, block_table, max_pages, page_size, n_pages,               \
+              (__nv_bfloat16*)k_pages, (__nv_bfloat16*)v_pages, (__nv_bfloat16*)q_out)
+            if (weight_is_f32) IB_LAUNCH_WIDE(float); else IB_LAUNCH_WIDE(__nv_bfloat16);
+#undef IB_LAUNCH_WIDE
+        } else if (n_rows >= 256) {
             if (weight_is_f32) IB_LAUNCH_D128(float, 4); else IB_LAUNCH_D128(__nv_bfloat16, 4);
         } else {
             if (weight_is_f32) IB_LAUNCH_D128(float, 1); else IB_LAUNCH_D128(__nv_bfloat16, 1);
