@@ -30,7 +30,7 @@ constexpr int D = 128;            // head size
 constexpr int ROWS = 128;         // query rows per CTA
 constexpr int KEYS = 128;         // keys per tile
 constexpr int THREADS = 320;
-constexpr int SOFTMAX_THREADS = 256;
+constexpr int SMEM_SLACK = 512;   // bytes that the 1 KB alignment of the tiles may cost (the base is asked to be aligned)
 constexpr int HALF_BYTES = 128 * 128;          // a [128 rows][64 elements] swizzled sub-tile
 constexpr int TILE_BYTES = 2 * HALF_BYTES;     // Q, K, V or P tile: 128 x 128 bfloat16
 
@@ -127,7 +127,8 @@ __device__ __forceinline__ void tmem_ld32_issue(unsigned taddr, unsigned (&r)[32
                  : "r"(taddr));
 }
 __device__ __forceinline__ void tmem_ld_wait() { asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory"); }
-__device__ __forceinline__ void softmax_sync() { asm volatile("bar.sync 1, 256;" ::: "memory"); }  // warps 0..7
+// the two warps that share the rows 32 q .. 32 q + 31 (one per half of the columns) meet: barriers 2..5
+__device__ __forceinline__ void pair_sync(int q) { asm volatile("bar.sync %0, 64;" ::"r"(2 + q) : "memory"); }
 __device__ __forceinline__ void fence_before() { asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory"); }
 __device__ __forceinline__ void fence_after() { asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory"); }
 __device__ __forceinline__ float ex2(float x) {   // 2^x, one instruction; 2^-inf = 0
@@ -155,8 +156,12 @@ __global__ void __launch_bounds__(THREADS, 1) attention_kernel(const __grid_cons
                                                                const __grid_constant__ CUtensorMap map_k,
                                                                const __grid_constant__ CUtensorMap map_v,
                                                                const Params P) {
-    extern __shared__ unsigned char raw_smem[];
+    extern __shared__ __align__(1024) unsigned char raw_smem[];
     unsigned char* smem = reinterpret_cast<unsigned char*>((reinterpret_cast<uintptr_t>(raw_smem) + 1023) & ~(uintptr_t)1023);
+    if (smem - raw_smem > SMEM_SLACK) {   // the tiles would not fit behind a base this far off a 1 KB boundary
+        if (threadIdx.x == 0) atomicCAS(&g_error, 0, 9);
+        return;
+    }
     unsigned char* sq = smem;                       // Q tile
     unsigned char* sp = sq + TILE_BYTES;            // P tiles, used in turn
     unsigned char* sk = sp + 2 * TILE_BYTES;        // K tiles, two stages
@@ -167,7 +172,7 @@ __global__ void __launch_bounds__(THREADS, 1) attention_kernel(const __grid_cons
     const unsigned s_full0 = smem_u32(bars + 9), s_empty0 = smem_u32(bars + 11);
     const unsigned p_full0 = smem_u32(bars + 13), pv_full0 = smem_u32(bars + 15);
     unsigned* tmem_slot = reinterpret_cast<unsigned*>(bars + 17);
-    float* xchg = reinterpret_cast<float*>(bars + 18);   // [2 halves][128 rows]: row maxima, later row sums
+    float* xchg = reinterpret_cast<float*>(bars + 18);   // [2 in turn][2 halves][128 rows]: row maxima, later row sums
 
     ib_grid_dependency_sync();
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
@@ -323,8 +328,8 @@ __global__ void __launch_bounds__(THREADS, 1) attention_kernel(const __grid_cons
                 o[32 + j] = o[32 + j] * corr + __uint_as_float(b[j]);
             }
         };
-        // After a wait has run out the loop goes on without waiting, so that every thread still meets the
-        // others at the named barriers the same number of times; the output is not stored then.
+        // After a wait has run out the loop goes on without waiting, so that every thread still meets its
+        // partner at the named barrier the same number of times; the output is not stored then.
         for (int i = 0; i < n_tiles; ++i) {
             const int s = i & 1;
             if (ok && !mbar_wait(s_full0 + 8 * s, (i >> 1) & 1, 5)) ok = false;
@@ -336,27 +341,34 @@ __global__ void __launch_bounds__(THREADS, 1) attention_kernel(const __grid_cons
             tmem_ld_wait();
             // a tile whose 64 keys this row sees in full needs no comparisons (all tiles but the first and last few)
             const bool all_visible = key0 >= lo && key0 + 63 <= pos;
-            float mx = -INFINITY;
+            // (four running maxima, and four running sums below: one chain of 64 dependent operations would
+            // leave the two warps of a scheduler waiting on each other's latencies)
+            float mx4[4] = {-INFINITY, -INFINITY, -INFINITY, -INFINITY};
             if (all_visible) {
 #pragma unroll
-                for (int j = 0; j < 32; ++j) mx = fmaxf(mx, fmaxf(__uint_as_float(a[j]), __uint_as_float(b[j])));
+                for (int j = 0; j < 32; ++j)
+                    mx4[j & 3] = fmaxf(mx4[j & 3], fmaxf(__uint_as_float(a[j]), __uint_as_float(b[j])));
             } else {
 #pragma unroll
                 for (int j = 0; j < 32; ++j) {
                     const int ka = key0 + j, kb = key0 + 32 + j;
                     if (!(ka >= lo && ka <= pos)) a[j] = 0xff800000u;   // -inf
                     if (!(kb >= lo && kb <= pos)) b[j] = 0xff800000u;
-                    mx = fmaxf(mx, fmaxf(__uint_as_float(a[j]), __uint_as_float(b[j])));
+                    mx4[j & 3] = fmaxf(mx4[j & 3], fmaxf(__uint_as_float(a[j]), __uint_as_float(b[j])));
                 }
             }
+            float mx = fmaxf(fmaxf(mx4[0], mx4[1]), fmaxf(mx4[2], mx4[3]));
             // the row's maximum over both halves (raw scores; the scale is positive)
-            xchg[ch * 128 + r] = mx;
-            softmax_sync();
-            mx = fmaxf(mx, xchg[(ch ^ 1) * 128 + r]) * P.scale_log2;
+            // (two exchange buffers in turn: the partner has read buffer i & 1 before it can arrive at the next
+            // tile's barrier, which this thread passes before it writes that buffer again two tiles on)
+            float* xb = xchg + (i & 1) * 256;
+            xb[ch * 128 + r] = mx;
+            pair_sync(warp & 3);
+            mx = fmaxf(mx, xb[(ch ^ 1) * 128 + r]) * P.scale_log2;
             const float m_new = fmaxf(m, mx);
             const float m_safe = m_new == -INFINITY ? 0.0f : m_new;
             const float corr = m == -INFINITY ? 0.0f : ex2(m - m_safe);
-            float sum = 0.0f;
+            float sum4[4] = {0.0f, 0.0f, 0.0f, 0.0f};
             unsigned char* prow = sp + s * TILE_BYTES + ch * HALF_BYTES + r * 128;
 #pragma unroll
             for (int c = 0; c < 8; ++c) {
@@ -366,14 +378,14 @@ __global__ void __launch_bounds__(THREADS, 1) attention_kernel(const __grid_cons
                     const int e = 8 * c + j;
                     const float x = __uint_as_float(e < 32 ? a[e] : b[e - 32]);
                     p[j] = ex2(fmaf(x, P.scale_log2, -m_safe));   // exp2(-inf) = 0 for keys that are not seen
-                    sum += p[j];
+                    sum4[j & 3] += p[j];
                 }
                 uint4 w;
                 w.x = pack_bf16(p[0], p[1]); w.y = pack_bf16(p[2], p[3]);
                 w.z = pack_bf16(p[4], p[5]); w.w = pack_bf16(p[6], p[7]);
                 *reinterpret_cast<uint4*>(prow + ((c ^ (r & 7)) << 4)) = w;
             }
-            l = l * corr + sum;
+            l = l * corr + ((sum4[0] + sum4[1]) + (sum4[2] + sum4[3]));
             m = m_new;
             // S(i) has been read and P(i) written: tell the MMA issuer (one arrival per warp)
             fence_before();
@@ -388,7 +400,6 @@ __global__ void __launch_bounds__(THREADS, 1) attention_kernel(const __grid_cons
                 fence_before();
             }
             corr_pending = corr;
-            softmax_sync();   // xchg is written again in the next iteration
         }
         if (ok && n_tiles > 0) {
             const int i = n_tiles - 1;
@@ -401,9 +412,10 @@ __global__ void __launch_bounds__(THREADS, 1) attention_kernel(const __grid_cons
             }
         }
         // the row's sum over both halves
-        xchg[ch * 128 + r] = l;
-        softmax_sync();
-        l += xchg[(ch ^ 1) * 128 + r];
+        float* xb = xchg + (n_tiles & 1) * 256;
+        xb[ch * 128 + r] = l;
+        pair_sync(warp & 3);
+        l += xb[(ch ^ 1) * 128 + r];
         if (row_valid && ok) {
             const float inv = l > 0.0f ? 1.0f / l : 0.0f;
             __nv_bfloat16* dst = P.out + ((long)(row0 + ti) * P.n_heads + kvh * G + g) * D + ch * 64;
@@ -489,7 +501,7 @@ IB_EXPORT int ib_paged_attention_tcgen05(const void* q, const void* k_pages, con
     P.positions = positions; P.out = (__nv_bfloat16*)out; P.max_pages = max_pages; P.page_size = page_size;
     P.n_pages = n_pages; P.n_heads = n_heads; P.n_kv_heads = n_kv_heads; P.window = window;
     P.scale_log2 = scale * 1.4426950408889634f;
-    const size_t smem = 7 * fa::TILE_BYTES + 18 * 8 + 2 * 128 * 4 + 1024;
+    const size_t smem = 7 * fa::TILE_BYTES + 18 * 8 + 4 * 128 * 4 + fa::SMEM_SLACK;
     static bool configured = false;
     if (!configured) {
         cudaError_t e = cudaFuncSetAttribute(fa::attention_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);

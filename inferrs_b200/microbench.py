@@ -182,8 +182,8 @@ def _trace(fn, args) -> dict:
         step_us = "" if prev_end is None else f"{b - prev_end:8.2f}"
         print(f"{a:9.2f} {b:9.2f} {step_us:>24}  {e.name[:60]}")
         prev_end = b if prev_end is None else max(prev_end, b)
-    return {"kernel": "step/decode trace", "batch": args.batch, "context": args.context, "layers": args.layers,
-            "kernels": len(ev), "us_first_start_to_last_end": round(prev_end, 1)}
+    return {"kernel": f"step/{args.form} trace", "batch": args.batch, "context": args.context, "tokens": args.tokens,
+            "layers": args.layers, "kernels": len(ev), "us_first_start_to_last_end": round(prev_end, 1)}
 
 
 def step(args) -> dict:
@@ -237,6 +237,20 @@ def step(args) -> dict:
                 "tokens_per_s_at_36_layers": round(args.batch * 1e6 / ((us - head_bytes / 6.3e6) / args.layers * 36
                                                                        + head_bytes / 6.3e6), 1),
                 "GBps": round(byts / us / 1e3, 1), "note": "per layer: the step less the head product at 6.3 TB/s"}
+    if args.trace:
+        state = {"i": 1000}
+
+        def one_prompt():
+            i = state["i"]
+            state["i"] += 1
+            runner.admit(i)
+            if args.context_before:
+                runner.step([StepEntry(i, toks(args.context_before), [])])
+            runner.step([StepEntry(i, toks(args.tokens), [args.tokens - 1])])
+            runner.release(i)
+        for _ in range(3):
+            one_prompt()
+        return _trace(one_prompt, args)
     times = []
     for i in range(args.iters + 2):
         runner.admit(i)
@@ -377,7 +391,7 @@ def main(argv=None) -> int:
     st.add_argument("--vocab", type=int, default=151936)
     st.add_argument("--page-size", type=int, default=16)
     st.add_argument("--iters", type=int, default=64)
-    st.add_argument("--trace", action="store_true", help="decode form: print when every kernel of one step started and ended")
+    st.add_argument("--trace", action="store_true", help="print when every kernel of one step started and ended")
     st.set_defaults(fn=step)
     wl = sub.add_parser("workload")
     wl.add_argument("--shape", choices=sorted(SHAPES), default="0.6b")
