@@ -301,7 +301,8 @@ def workload(args) -> dict:
         config["num_hidden_layers"] = args.layers
     per_request = (args.prompt_max + args.max_tokens + args.page_size) // args.page_size
     eng = Engine(config=config, random_weights=0, dtype="bf16", block_size=args.page_size,
-                 num_blocks=args.requests * per_request, max_batch_size=args.requests,
+                 num_blocks=max(per_request, int(args.requests * per_request * args.cache_share)),
+                 max_batch_size=args.requests,
                  max_tokens_per_step=args.tokens_per_step, prefill_chunk=args.prefill_chunk)
     eng.warm_up()
     g = torch.Generator().manual_seed(7)
@@ -324,6 +325,9 @@ def workload(args) -> dict:
     torch.cuda.synchronize()
     t1 = time.perf_counter()
     st = eng.stats()
+    eng.runner.manager.check_invariants()
+    if st["free_pages"] != st["pages"]:
+        raise RuntimeError(f"pages were not given back: {st}")
     out = {"kernel": "workload", "shape": args.shape, "layers": config["num_hidden_layers"], "requests": args.requests,
            "prompt_tokens": sum(lens), "generated_tokens": args.requests * args.max_tokens, "steps": steps,
            "steps_with_prompt_portions": mixed, "preemptions": st["preemptions"], "seconds": round(t1 - t0, 3),
@@ -405,6 +409,8 @@ def main(argv=None) -> int:
     wl.add_argument("--max-context", type=int, default=4096)
     wl.add_argument("--vocab", type=int, default=151936)
     wl.add_argument("--page-size", type=int, default=16)
+    wl.add_argument("--cache-share", type=float, default=1.0,
+                    help="pages as a share of what all requests need at once (less: requests are preempted)")
     wl.set_defaults(fn=workload)
     args = ap.parse_args(argv)
     print(json.dumps(args.fn(args)))
