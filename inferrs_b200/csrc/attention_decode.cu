@@ -7,7 +7,7 @@
 // float32, P V with mma.sync.  The warps' partial results are merged through shared memory, and the
 // slices' results through float32 scratch: every CTA adds one to a counter of its (request, head group),
 // and the CTA that finds it was the last one merges all slices and writes the output, so no second
-// kernel is needed.  How many slices are used is decided from the request's real length (at least four
+// kernel is needed.  How many slices are used is decided from the request's real length (at least `min_tiles`
 // tiles per slice); CTAs of unused slices leave at once.
 #include <cuda.h>
 
@@ -23,7 +23,6 @@ constexpr int STAGES = 3;
 constexpr int HALF_BYTES = KEYS * 128;      // [64 keys][64 dims] swizzled
 constexpr int TILE_BYTES = 2 * HALF_BYTES;  // K or V tile
 constexpr int THREADS = 160;                // 4 compute warps + producer warp
-constexpr int MIN_TILES_PER_SPLIT = 4;
 
 __device__ int g_error = 0;
 
@@ -95,7 +94,7 @@ struct Params {
     int* counters;             // [R * n_kv_heads], zero between launches
     const int* rows;           // [R] or null: the row of q, positions and out that place i of the grid works on
     const int* reqs;           // [R] or null: its request (row of the block table); a negative row is no work
-    int max_pages, page_size, n_pages, n_heads, n_kv_heads, window, max_splits;
+    int max_pages, page_size, n_pages, n_heads, n_kv_heads, window, max_splits, min_tiles;
     float scale_log2;
 };
 
@@ -127,7 +126,7 @@ __global__ void __launch_bounds__(THREADS, 2) decode_kernel(const __grid_constan
     const int lo = (P.window > 0 && pos - P.window + 1 > 0) ? pos - P.window + 1 : 0;
     const int t_first = lo / KEYS, t_last = pos / KEYS + 1;
     const int n_all = t_last - t_first;
-    int n_splits = (n_all + MIN_TILES_PER_SPLIT - 1) / MIN_TILES_PER_SPLIT;
+    int n_splits = (n_all + P.min_tiles - 1) / P.min_tiles;
     if (n_splits > P.max_splits) n_splits = P.max_splits;
     if (split >= n_splits) return;                           // an unused slice
     const int per = (n_all + n_splits - 1) / n_splits;
@@ -391,9 +390,10 @@ static EncodeTiled encode_fn() {
 IB_EXPORT int ib_paged_attention_decode(const void* q, const void* k_pages, const void* v_pages, const int* block_table,
                                         int max_pages, int page_size, int n_pages, const int* positions, int n_rows,
                                         int n_heads, int n_kv_heads, int head_dim, float scale, int window, void* out,
-                                        int max_splits, float* part_o, float* part_ml, int* counters,
+                                        int max_splits, int min_tiles, float* part_o, float* part_ml, int* counters,
                                         const int* rows, const int* reqs, cudaStream_t stream) {
     if (n_rows <= 0) return IB_OK;
+    if (min_tiles <= 0) return IB_ERR_ARGUMENT;
     if ((rows == nullptr) != (reqs == nullptr)) return IB_ERR_ARGUMENT;
     if (n_heads <= 0 || n_kv_heads <= 0 || n_heads % n_kv_heads || page_size <= 0 || max_pages <= 0 || max_splits <= 0)
         return IB_ERR_ARGUMENT;
@@ -418,6 +418,7 @@ IB_EXPORT int ib_paged_attention_decode(const void* q, const void* k_pages, cons
     P.part_o = part_o; P.part_ml = part_ml; P.counters = counters; P.rows = rows; P.reqs = reqs;
     P.max_pages = max_pages; P.page_size = page_size;
     P.n_pages = n_pages; P.n_heads = n_heads; P.n_kv_heads = n_kv_heads; P.window = window; P.max_splits = max_splits;
+    P.min_tiles = min_tiles;
     P.scale_log2 = scale * 1.4426950408889634f;
     const size_t smem = 2 * dec::STAGES * dec::TILE_BYTES + 16 * dec::D * 2 + (2 * dec::STAGES + 1) * 8 + 1024;
     static bool configured = false;
@@ -443,7 +444,7 @@ IB_EXPORT int ib_attention_decode_error(int reset) {
 #else
 
 IB_EXPORT int ib_paged_attention_decode(const void*, const void*, const void*, const int*, int, int, int, const int*, int,
-                                        int, int, int, float, int, void*, int, float*, float*, int*, const int*,
+                                        int, int, int, float, int, void*, int, int, float*, float*, int*, const int*,
                                         const int*, cudaStream_t) {
     return IB_ERR_UNSUPPORTED;
 }

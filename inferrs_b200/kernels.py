@@ -44,8 +44,8 @@ _SIGNATURES = {
     "ib_attention_tcgen05_error": [c_int],
     "ib_row_fault": [c_int],
     "ib_paged_attention_decode": [c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_void_p, c_int, c_int,
-                                  c_int, c_int, c_float, c_int, c_void_p, c_int, c_void_p, c_void_p, c_void_p, c_void_p,
-                                  c_void_p, c_void_p],
+                                  c_int, c_int, c_float, c_int, c_void_p, c_int, c_int, c_void_p, c_void_p, c_void_p,
+                                  c_void_p, c_void_p, c_void_p],
     "ib_attention_decode_error": [c_int],
     "ib_argmax": [c_void_p, c_void_p, c_int, c_int, c_long, c_void_p, c_void_p],
     "ib_penalties": [c_void_p, c_long, c_int, c_int, c_void_p, c_int, c_void_p, c_void_p, c_void_p, c_void_p,
@@ -440,7 +440,8 @@ def decode_max_splits(n_requests: int, n_kv_heads: int, max_kv_len: int) -> int:
 
 def paged_attention_decode(q: torch.Tensor, k_pages: torch.Tensor, v_pages: torch.Tensor, block_table: torch.Tensor,
                            positions: torch.Tensor, scale: float, window: Optional[int], out: torch.Tensor,
-                           max_splits: int, rows: Optional[torch.Tensor] = None, reqs: Optional[torch.Tensor] = None):
+                           max_splits: int, rows: Optional[torch.Tensor] = None, reqs: Optional[torch.Tensor] = None,
+                           min_tiles: int = 4):
     """Attention of one new token per request (row r = request r) over its pages: TMA-fed key/value tiles, split
     over the keys, merged by the slice that finishes last (bfloat16, head_dim 128).  With ``rows`` and ``reqs``
     (int32, equally long) only the rows named are worked on, row ``rows[i]`` being a single token of request
@@ -478,8 +479,8 @@ def paged_attention_decode(q: torch.Tensor, k_pages: torch.Tensor, v_pages: torc
         part_ml = torch.empty((n, nh, max_splits, 2), dtype=torch.float32, device=q.device)
     _check(_core(torch.bfloat16).ib_paged_attention_decode(
         _p(q), _p(k_pages), _p(v_pages), _p(block_table), block_table.shape[1], page_size, n_pages, _p(positions), n,
-        nh, nkv, d, float(scale), int(window) if window else 0, _p(out), int(max_splits), _p(part_o), _p(part_ml),
-        _p(counters), _p(rows), _p(reqs), _stream()), "paged_attention_decode")
+        nh, nkv, d, float(scale), int(window) if window else 0, _p(out), int(max_splits), int(min_tiles), _p(part_o),
+        _p(part_ml), _p(counters), _p(rows), _p(reqs), _stream()), "paged_attention_decode")
 
 
 def attention_decode_error(reset: bool = True) -> int:
