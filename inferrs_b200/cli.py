@@ -77,13 +77,19 @@ def cmd_run(args) -> int:
                         repetition_penalty=args.repetition_penalty, repeat_last_n=args.repeat_last_n,
                         frequency_penalty=args.frequency_penalty, max_tokens=args.max_tokens, seed=args.seed)
     t0 = time.perf_counter()
-    req = eng.generate([ids], sp, return_requests=True)[0]
+    out: List[int] = []
+    text = ""
+    for t in eng.stream(ids, sp):        # printed as it comes
+        out.append(t)
+        if tok is not None and not args.prompt_ids:
+            whole = tok.decode(out)
+            print(whole[len(text):], end="", flush=True)
+            text = whole
+        else:
+            print(t, end=" ", flush=True)
+    print()
     dt = time.perf_counter() - t0
-    if tok is not None and not args.prompt_ids:
-        print(tok.decode(req.output))
-    else:
-        print(" ".join(str(t) for t in req.output))
-    print(f"[{len(ids)} prompt tokens, {len(req.output)} generated, finish={req.finish_reason}, {dt:.2f} s]",
+    print(f"[{len(ids)} prompt tokens, {len(out)} generated, finish={eng.last_streamed.finish_reason}, {dt:.2f} s]",
           file=sys.stderr)
     return 0
 

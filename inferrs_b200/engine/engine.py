@@ -227,6 +227,24 @@ class Engine:
         out = [done[r] for r in rids]
         return out if return_requests else [r.output for r in out]
 
+    def stream(self, prompt: Sequence[int], sampling: Optional[SamplingParams] = None):
+        """Generated token ids of one prompt, one after the other as the steps bring them (the reference's
+        ``run`` prints text as it comes, inferrs/src/run.rs:34-146).  Other requests may be live meanwhile."""
+        rid = self.add_request(prompt, sampling)
+        request = next(r for r in self.scheduler.waiting if r.rid == rid)
+        self.last_streamed = request      # for callers that want the reason of its end afterwards
+        sent = 0
+        while request.finish_reason is None and self.has_work():
+            self.step()
+            while sent < len(request.output):
+                yield request.output[sent]
+                sent += 1
+        if request.finish_reason is None:
+            self.flush()
+        while sent < len(request.output):
+            yield request.output[sent]
+            sent += 1
+
     def stats(self) -> dict:
         m = self.runner.manager
         return {

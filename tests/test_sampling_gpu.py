@@ -172,3 +172,33 @@ def test_steps_launched_one_ahead_give_the_same_tokens(model_dirs, name, dtype):
     both(SamplingParams(temperature=0.7, max_tokens=20, seed=3))          # the reference's defaults: penalties
     ra, b = both(SamplingParams.greedy(max_tokens=40), num_blocks=9)      # too few pages for all four at once
     assert b.stats()["preemptions"] > 0
+
+
+def test_tokens_come_one_by_one_and_through_the_command_line(model_dirs):
+    """``Engine.stream`` yields what ``generate`` returns, token by token, also while another request is live;
+    the ``run`` command prints the same ids."""
+    import subprocess
+    import sys
+    from helpers import CONFIG_D
+    from inferrs_b200 import Engine
+    prompt = random_tokens(23, CONFIG_D["vocab_size"], seed=77)
+    other = random_tokens(9, CONFIG_D["vocab_size"], seed=78)
+    sp = SamplingParams.greedy(max_tokens=14)
+    kw = dict(dtype="bf16", block_size=16, num_blocks=32, max_batch_size=4)
+    want = Engine(model_dirs["D"], **kw).generate([prompt, other], sp)
+    eng = Engine(model_dirs["D"], **kw)
+    eng.add_request(other, sp, rid="other")
+    got = list(eng.stream(prompt, sp))
+    assert got == want[0]
+    while eng.has_work():
+        eng.step()
+    assert eng.stats()["free_pages"] == eng.stats()["pages"]
+    root = __import__("os").path.dirname(__import__("os").path.dirname(__import__("os").path.abspath(__file__)))
+    out = subprocess.run([sys.executable, "-m", "inferrs_b200", "run", model_dirs["D"], "--prompt-ids",
+                          ",".join(map(str, prompt)), "--max-tokens", "14", "--temperature", "0",
+                          "--max-blocks", "32", "--max-batch-size", "4"],
+                         cwd=root, capture_output=True, text=True, timeout=300)
+    assert out.returncode == 0, out.stderr
+    # greedy through the command line applies the reference's default repetition penalty: compare with the same
+    ref = Engine(model_dirs["D"], **kw).generate([prompt], SamplingParams(temperature=0.0, max_tokens=14))
+    assert [int(t) for t in out.stdout.split()] == ref[0]
