@@ -163,11 +163,16 @@ class Engine:
 
     def _next_decode_plan(self, step) -> Optional[List[PlannedEntry]]:
         """The step after ``step`` if it can be told before ``step``'s tokens are known: every running request has
-        just been sampled and brings exactly the sampled token next.  None if anything else may happen (prompts
-        waiting or under way, penalties that need the token, too few pages): then the tokens are read first."""
+        just been sampled and brings exactly the sampled token next.  None if anything else may happen (a prompt
+        that can be let in or is under way, penalties that need the token, too few pages): then the tokens are
+        read first."""
         plan, ids, _, _ = step
         sch = self.scheduler
-        if ids is None or sch.waiting or len(plan) != len(sch.running) or not all(e.samples for e in plan):
+        if ids is None or len(plan) != len(sch.running) or not all(e.samples for e in plan):
+            return None
+        # a waiting request that could be let in now needs a planned step; one that finds no room anyway (all
+        # slots taken) waits a step longer for the slot of a request that is just ending
+        if sch.waiting and len(sch.running) < sch.max_batch_size and self.runner.manager.n_free_slots > 0:
             return None
         nxt = []
         for e in plan:

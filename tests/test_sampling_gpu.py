@@ -202,3 +202,18 @@ def test_tokens_come_one_by_one_and_through_the_command_line(model_dirs):
     # greedy through the command line applies the reference's default repetition penalty: compare with the same
     ref = Engine(model_dirs["D"], **kw).generate([prompt], SamplingParams(temperature=0.0, max_tokens=14))
     assert [int(t) for t in out.stdout.split()] == ref[0]
+
+
+def test_steps_go_one_ahead_while_requests_wait_for_a_slot(model_dirs):
+    """More requests than slots: the waiting ones cannot be let in while all slots are taken, so decode steps still
+    go one ahead; the tokens are those of the engine that reads every step's tokens first."""
+    from inferrs_b200 import Engine
+    prompts = [random_tokens(n, CONFIG_B["vocab_size"], seed=90 + n) for n in (5, 9, 14, 3, 21, 8, 12)]
+    params = [SamplingParams.greedy(max_tokens=6 + 3 * i) for i in range(len(prompts))]
+    kw = dict(dtype="f32", block_size=16, num_blocks=64, max_batch_size=3, max_tokens_per_step=32)
+    a = Engine(model_dirs["B"], overlap=False, **kw)
+    b = Engine(model_dirs["B"], overlap=True, **kw)
+    assert a.generate(prompts, params) == b.generate(prompts, params)
+    # most decode steps of the second engine were launched before the step before them had been read
+    assert b.n_steps <= a.n_steps + len(prompts) + b.n_steps_in_vain
+    assert b.stats()["free_pages"] == b.stats()["pages"] and not b.has_work()
