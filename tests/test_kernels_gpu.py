@@ -447,3 +447,47 @@ def test_paged_attention_decode(nh, nkv, ps, window, max_splits):
     got = out[5].view(nh, d).float()
     want = v_pages[page, :, slot, :].float().repeat_interleave(nh // nkv, dim=0)
     assert rel_err(got, want) < 5e-2, "the far key that stands out was not seen"
+
+
+@pytest.mark.parametrize("nh,nkv,ps,window", [(8, 2, 16, None), (32, 8, 16, 300)])
+def test_attention_of_a_step_with_portions_and_single_tokens(nh, nkv, ps, window):
+    """The way a replayed step with prompt portions uses the two kernels: the portions' tiles in a list of fixed
+    length in which -1 marks empty places (prefill kernel), the rows that are single tokens in another such list
+    (decode kernel); together they must give every row of the step, and leave the rows of no request alone."""
+    from inferrs_b200 import kernels as K
+    dtype, d = torch.bfloat16, 128
+    lens, new = [300, 650, 200, 64, 1, 700, 90], [40, 1, 200, 1, 1, 1, 33]
+    table, positions, row_request, k_pages, v_pages = _paged_setup(dtype, nkv, d, ps, lens, new, 20)
+    n_real = sum(new)
+    n = n_real + 7                                    # seven rows that fill the step up
+    pad = torch.zeros(7, dtype=torch.int32, device=dev())
+    positions = torch.cat([positions, pad])
+    row_request = torch.cat([row_request, pad + len(lens)])
+    table = torch.cat([table, torch.full((2, table.shape[1]), -1, dtype=torch.int32, device=dev())])
+    q = rand((n, nh, d), dtype, 23)
+    starts = [0] + list(torch.tensor(new).cumsum(0))
+    q_start = torch.tensor(starts + [n, n], dtype=torch.int32, device=dev())   # the filling request and an empty one
+    tpt = 128 // (nh // nkv)
+    req, row0 = [], []
+    for r, t in enumerate(new):
+        if t > 1:
+            for s0 in range(0, t, tpt):
+                req.append(r)
+                row0.append(int(starts[r]) + s0)
+    t_max = len(req) + 5
+    tile_req = torch.tensor(req + [-1] * 5, dtype=torch.int32, device=dev())
+    tile_row0 = torch.tensor(row0 + [0] * 5, dtype=torch.int32, device=dev())
+    singles = [(int(starts[r]), r) for r, t in enumerate(new) if t == 1]
+    rows = torch.tensor([s[0] for s in singles] + [-1, -1, -1], dtype=torch.int32, device=dev())
+    reqs = torch.tensor([s[1] for s in singles] + [-1, -1, -1], dtype=torch.int32, device=dev())
+    scale = d ** -0.5 * 2
+    out = torch.full((n, nh * d), 5.0, dtype=dtype, device=dev())
+    K.paged_attention_decode(q, k_pages, v_pages, table, positions, scale, window, out, 4, rows, reqs)
+    K.paged_attention_tcgen05(q, k_pages, v_pages, table, tile_req, tile_row0, t_max, q_start, positions, scale, window,
+                              out)
+    assert K.attention_tcgen05_error() == 0 and K.attention_decode_error() == 0
+    ref = torch.empty((n_real, nh * d), dtype=dtype, device=dev())
+    R.paged_attention_generic(q[:n_real].contiguous(), k_pages, v_pages, table, row_request[:n_real].contiguous(),
+                              positions[:n_real].contiguous(), scale, window, ref)
+    assert rel_err(out[:n_real], ref) < 2e-2
+    assert bool((out[n_real:] == 5.0).all()), "rows of no request must be left alone"
