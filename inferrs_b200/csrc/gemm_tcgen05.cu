@@ -543,18 +543,19 @@ IB_EXPORT int ib_gemm_tn_tcgen05(const void* x, long ldx, const void* w, long ld
 
 // y[t, f] = silu(x[t] . w[f]) * (x[t] . w[inner + f]) for f < inner: the gate and up products of a gated feed-forward
 // and the gate itself in one kernel.  w [2 * inner, k] holds the gate matrix above the up matrix; y [n_tok, inner]
-// bfloat16.  Up to 16 tokens (IB_ERR_UNSUPPORTED beyond; the caller then runs product and gate separately).
+// bfloat16.  Up to 32 tokens (IB_ERR_UNSUPPORTED beyond; the caller then runs product and gate separately).
 IB_EXPORT int ib_gemm_swiglu_tcgen05(const void* x, long ldx, const void* w, long ldw, void* y, long ldy, int n_tok,
                                      int inner, int k, cudaStream_t stream) {
     if (n_tok <= 0 || inner <= 0) return IB_OK;
     if (k <= 0) return IB_ERR_ARGUMENT;
-    if ((k % 8) || (ldx % 8) || (ldw % 8) || ((uintptr_t)x % 16) || ((uintptr_t)w % 16) || n_tok > 16) return IB_ERR_UNSUPPORTED;
+    if ((k % 8) || (ldx % 8) || (ldw % 8) || ((uintptr_t)x % 16) || ((uintptr_t)w % 16) || n_tok > 32) return IB_ERR_UNSUPPORTED;
+    const int bn = n_tok <= 16 ? 16 : 32;
     tc::Params p;
     p.y = y; p.ldy = ldy; p.n_tok = n_tok; p.n_out = inner; p.num_kb = (k + tc::BK - 1) / tc::BK; p.y_is_f32 = 0;
     p.inner = inner;
     CUtensorMap mw, mx;
-    if (!tc::make_map(&mw, w, 2L * inner, k, ldw, 64) || !tc::make_map(&mx, x, n_tok, k, ldx, 16)) return IB_ERR_UNSUPPORTED;
-    return tc::launch<16, 5, 1>(mw, mx, p, 1, stream);
+    if (!tc::make_map(&mw, w, 2L * inner, k, ldw, 64) || !tc::make_map(&mx, x, n_tok, k, ldx, bn)) return IB_ERR_UNSUPPORTED;
+    return bn == 16 ? tc::launch<16, 5, 1>(mw, mx, p, 1, stream) : tc::launch<32, 4, 1>(mw, mx, p, 1, stream);
 }
 
 // 1: later launches may start before the kernel before them in the stream has finished (programmatic dependent

@@ -656,7 +656,7 @@ def gemm_tn_tcgen05(x: torch.Tensor, w: torch.Tensor, out: torch.Tensor, split_k
 
 def gemm_swiglu_tcgen05(x: torch.Tensor, w_gate_up: torch.Tensor, out: torch.Tensor):
     """out[t, f] = silu(x[t] . w[f]) * (x[t] . w[inner + f]): both products of a gated feed-forward and the gate
-    in one tcgen05 kernel (64 gate rows and the same 64 up rows per tile).  Up to 16 rows of x."""
+    in one tcgen05 kernel (64 gate rows and the same 64 up rows per tile).  Up to 32 rows of x."""
     _need(x, "x", (torch.bfloat16,), 2)
     _need(w_gate_up, "w_gate_up", (torch.bfloat16,), 2)
     _need(out, "out", (torch.bfloat16,), 2)
@@ -666,7 +666,7 @@ def gemm_swiglu_tcgen05(x: torch.Tensor, w_gate_up: torch.Tensor, out: torch.Ten
         raise KernelError(f"gemm_swiglu: x {tuple(x.shape)}, w {tuple(w_gate_up.shape)}, out {tuple(out.shape)}")
     code = _gemm_lib().ib_gemm_swiglu_tcgen05(_p(x), k, _p(w_gate_up), k, _p(out), inner, n, inner, k, _stream())
     if code == -1:
-        raise KernelError(f"gemm_swiglu_tcgen05: at most 16 rows (got {n}), K={k} a multiple of 8, 16-byte aligned bases")
+        raise KernelError(f"gemm_swiglu_tcgen05: at most 32 rows (got {n}), K={k} a multiple of 8, 16-byte aligned bases")
     _check(code, "gemm_swiglu_tcgen05")
 
 
@@ -692,7 +692,7 @@ def set_pdl(on: bool, act_dtype: torch.dtype = torch.bfloat16):
 # up to this many rows the own tcgen05 product is the faster one in a decode step (the environment variable is
 # there for measuring other thresholds)
 TCGEN05_MAX_TOKENS = int(os.environ.get("INFERRS_B200_TCGEN05_MAX_TOKENS", "16"))
-SWIGLU_MAX_TOKENS = 16  # rows that the fused gate/up kernel takes
+SWIGLU_MAX_TOKENS = 32  # rows that the fused gate/up kernel takes
 
 
 def gemm_tcgen05_error(reset: bool = True) -> int:

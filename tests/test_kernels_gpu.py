@@ -346,7 +346,8 @@ def test_gemm_tn_tcgen05(n, m, k):
             assert rel_err(out, ref) < (1e-2 if od == torch.bfloat16 else 3e-5), (od, split)
 
 
-@pytest.mark.parametrize("n,inner,k", [(1, 192, 256), (8, 12288, 4096), (5, 200, 136), (16, 64, 64), (3, 1000, 520)])
+@pytest.mark.parametrize("n,inner,k", [(1, 192, 256), (8, 12288, 4096), (5, 200, 136), (16, 64, 64), (3, 1000, 520),
+                                       (17, 328, 192), (32, 1000, 520)])
 def test_gemm_swiglu_tcgen05(n, inner, k):
     """Both products of a gated feed-forward and the gate in one kernel, against the two-step reference; inner
     sizes that are no multiple of the 64-row tile, a K that ends inside a 64-wide block."""
