@@ -127,7 +127,8 @@ class Engine:
         ids = host = event = None
         if sampling:
             ids = self.sampler.sample(logits, [e.request.params for e in sampling],
-                                      [e.request.seed for e in sampling], [e.request for e in sampling], pending)
+                                      [e.request.seed for e in sampling], [e.request for e in sampling], pending,
+                                      device_tokens)
             if self.overlap:
                 host = self._pinned.pop() if self._pinned else \
                     torch.empty((self.scheduler.max_batch_size,), dtype=torch.int32).pin_memory()
@@ -164,8 +165,7 @@ class Engine:
     def _next_decode_plan(self, step) -> Optional[List[PlannedEntry]]:
         """The step after ``step`` if it can be told before ``step``'s tokens are known: every running request has
         just been sampled and brings exactly the sampled token next.  None if anything else may happen (a prompt
-        that can be let in or is under way, penalties that need the token, too few pages): then the tokens are
-        read first."""
+        that can be let in or is under way, too few pages): then the tokens are read first."""
         plan, ids, _, _ = step
         sch = self.scheduler
         if ids is None or len(plan) != len(sch.running) or not all(e.samples for e in plan):
@@ -177,7 +177,7 @@ class Engine:
         nxt = []
         for e in plan:
             r = e.request
-            if r.finish_reason is not None or r.params.has_penalty:
+            if r.finish_reason is not None:
                 return None
             # with the token that is on its way the request has len(output) + 1 tokens: does it go on after it?
             if len(r.output) + 1 >= r.params.max_tokens or r.n_tokens + 1 >= sch.max_positions:
