@@ -40,7 +40,8 @@ def peaks():
     if os.path.isfile(p):
         with open(p) as f:
             d = json.load(f)
-        return {"hbm_gbs": float(d["hbm_gbs"]), "bf16_tflops": float(d["bf16_tflops"]), "source": "measured"}
+        return {"hbm_gbs": float(d["hbm_gbs"]), "bf16_tflops": float(d["bf16_tflops"]),
+                "bf16_tflops_sustained": float(d.get("bf16_tflops_sustained", 0.0)), "source": "measured"}
     return dict(FALLBACK_PEAKS, source="fallback")
 
 
@@ -242,6 +243,10 @@ def main() -> int:
                           "frac": round(flops / (pms * 1e-3) / (pk["bf16_tflops"] * 1e12), 4),
                           "tflops": round(flops / (pms * 1e-3) / 1e12, 1), "peak_tflops": pk["bf16_tflops"],
                           "of": pk["source"]}
+        if pk.get("bf16_tflops_sustained"):
+            # the same library product back to back for seconds, under the power cap: what a step of tens of
+            # milliseconds can be compared with; "frac" stays the fraction of the burst figure
+            out["prefill"]["frac_of_sustained"] = round(flops / (pms * 1e-3) / (pk["bf16_tflops_sustained"] * 1e12), 4)
         points = {}
         for b in (1, 64):
             pms_b, _ = decode_steps(b, 64 if b == 64 else 128, 4)
