@@ -40,6 +40,28 @@ IB_EXPORT int ib_embedding_gather(const void* table, int table_is_f32, const int
 }
 
 // ---------------------------------------------------------------------------
+// Token ids that are still on the device: ids[i] < 0 stands for carry[-1 - ids[i]], the token that an
+// earlier step sampled and the host has not read yet.  Runs in the stream before the step that reads ids.
+// ---------------------------------------------------------------------------
+__global__ void resolve_tokens_kernel(int* __restrict__ ids, int n, const int* __restrict__ carry, int n_carry) {
+    ib_grid_dependency_sync();
+    const int i = blockIdx.x * blockDim.x + threadIdx.x;
+    if (i >= n) return;
+    const int v = ids[i];
+    if (v < 0) {
+        const int src = -1 - v;
+        ids[i] = src < n_carry ? carry[src] : -1;   // the embedding gives zeros for an id that is no token
+    }
+}
+
+IB_EXPORT int ib_resolve_tokens(int* ids, int n, const int* carry, int n_carry, cudaStream_t stream) {
+    if (n <= 0) return IB_OK;
+    if (n_carry < 0 || (n_carry > 0 && carry == nullptr)) return IB_ERR_ARGUMENT;
+    ib_launch(resolve_tokens_kernel, (n + 255) / 256, 256, 0, stream, ids, n, carry, n_carry);
+    return ib_launch_status();
+}
+
+// ---------------------------------------------------------------------------
 // x += delta (kept in the float residual), out = x / sqrt(mean(x^2) + eps) * w
 //
 // rows == nullptr : row r of residual/delta -> row r of out; the sum is written back.

@@ -35,9 +35,12 @@ class Engine:
     max_seq_len          0: the model's max_position_embeddings (reference: --max-seq-len)
     config, random_weights   instead of ``model_dir``: a config.json dictionary and a seed; the weights
                          are made on the device
-    overlap              decode steps are launched one ahead: while the device runs a step, the host reads the
-                         tokens of the step before and plans; a request that turns out to have ended runs one
-                         step in vain.  Results are the same; ``step`` then reports a request's end one call later.
+    overlap              steps are launched one ahead: while the device runs a step, the host plans and launches
+                         the next one (a token that the running step samples is handed on to it on the device)
+                         and only then reads the running step's tokens; a request that turns out to have ended
+                         runs one step in vain.  Results are the same; ``step`` then reports a request's end one
+                         call later.  Where the next step needs a running request's pages, ends a request for
+                         sure or is no replayed graph, the tokens are read first.
     """
 
     def __init__(self, model_dir: Optional[str] = None, dtype: str = "bf16", block_size: int = 16,
@@ -70,6 +73,8 @@ class Engine:
         self._in_flight = None
         self._pinned = []
         self.n_steps_in_vain = 0
+        self.n_steps_ahead = 0              # steps launched before the tokens of the step before them were read
+        self.n_portion_steps_ahead = 0      # ... of them, steps with prompt portions
 
     def _blocks_for_fraction(self, spec, block_size, fraction, max_batch_size) -> int:
         from .model import cache_needs
@@ -115,23 +120,41 @@ class Engine:
         return self.runner.warm_up(batch_sizes)
 
     # ---- one scheduler iteration -----------------------------------------------------
-    def _launch(self, plan: List[PlannedEntry], device_tokens: Optional[torch.Tensor] = None, pending: int = 0):
+    def _launch(self, plan: List[PlannedEntry], before=None):
         """Run the planned step and sample; the token ids stay on the device, a copy is on its way to pinned
-        memory.  Returns the step as it is kept until its tokens are read."""
-        entries = []
+        memory.  ``before`` is the launched step whose tokens the host has not read yet: an entry whose token is
+        among them takes it from there on the device.  Returns the step as it is kept until its tokens are read."""
+        place = {}
+        if before is not None and before[1] is not None:
+            place = {id(e.request): i for i, e in enumerate(x for x in before[0] if x.samples)}
+        entries, sources = [], []
         for e in plan:
-            toks = [0] if device_tokens is not None else e.request.token_slice(e.start, e.n)
-            entries.append(StepEntry(e.request.rid, toks, [e.n - 1] if e.samples else []))
-        logits = self.runner.step(entries, own_output=False, device_tokens=device_tokens)
-        sampling = [e for e in plan if e.samples]
+            r = e.request
+            if e.start + e.n > r.n_tokens:      # the entry reaches past what the host knows: the token on its way
+                if e.n != 1 or id(r) not in place:
+                    raise RuntimeError(f"request {r.rid!r}: its next token is neither known nor on its way")
+                toks, src = [0], place[id(r)]
+            else:
+                toks, src = r.token_slice(e.start, e.n), -1
+            entries.append(StepEntry(r.rid, toks, [e.n - 1] if e.samples else []))
+            sources.append(src)
+        carried = any(s >= 0 for s in sources)
+        logits = self.runner.step(entries, own_output=False, carry=(before[1], sources) if carried else None)
+        self.scheduler.advance(plan)
+        sampling = [(e, s) for e, s in zip(plan, sources) if e.samples]
         ids = host = event = None
         if sampling:
-            ids = self.sampler.sample(logits, [e.request.params for e in sampling],
-                                      [e.request.seed for e in sampling], [e.request for e in sampling], pending,
-                                      device_tokens)
+            pending = [int(s >= 0) for _, s in sampling]
+            pending_ids = None
+            if any(pending) and any(e.request.params.has_penalty for e, _ in sampling):
+                index = torch.tensor([max(s, 0) for _, s in sampling], dtype=torch.int64, device=self.rt.device)
+                pending_ids = before[1].index_select(0, index)
+            ids = self.sampler.sample(logits, [e.request.params for e, _ in sampling],
+                                      [e.request.seed for e, _ in sampling], [e.request for e, _ in sampling],
+                                      pending, pending_ids)
             if self.overlap:
                 host = self._pinned.pop() if self._pinned else \
-                    torch.empty((self.scheduler.max_batch_size,), dtype=torch.int32).pin_memory()
+                    torch.empty((max(self.scheduler.max_batch_size, ids.shape[0]),), dtype=torch.int32).pin_memory()
                 host[:ids.shape[0]].copy_(ids, non_blocking=True)
                 event = torch.cuda.Event()
                 event.record()
@@ -140,7 +163,7 @@ class Engine:
         return plan, ids, host, event
 
     def _finish(self, step) -> List[Request]:
-        """Read a launched step's tokens and record it; returns the requests that ended with it."""
+        """Read a launched step's tokens and record them; returns the requests that ended with it."""
         plan, ids, host, event = step
         tokens: List[int] = []
         if ids is not None:
@@ -160,52 +183,51 @@ class Engine:
                     kept.append(tok)
             else:
                 self.n_steps_in_vain += 1
-        return self.scheduler.update(alive, kept)
+        return self.scheduler.deliver(alive, kept)
 
-    def _next_decode_plan(self, step) -> Optional[List[PlannedEntry]]:
-        """The step after ``step`` if it can be told before ``step``'s tokens are known: every running request has
-        just been sampled and brings exactly the sampled token next.  None if anything else may happen (a prompt
-        that can be let in or is under way, too few pages): then the tokens are read first."""
-        plan, ids, _, _ = step
+    def _ends_for_sure(self, step) -> bool:
+        """Whether a request of the launched step ends with the token that is on its way whatever that token is
+        (its last allowed token, or the last position): the step after it is then planned with that known."""
         sch = self.scheduler
-        if ids is None or len(plan) != len(sch.running) or not all(e.samples for e in plan):
-            return None
-        # a waiting request that could be let in now needs a planned step; one that finds no room anyway (all
-        # slots taken) waits a step longer for the slot of a request that is just ending
-        if sch.waiting and len(sch.running) < sch.max_batch_size and self.runner.manager.n_free_slots > 0:
-            return None
-        nxt = []
-        for e in plan:
+        for e in step[0]:
             r = e.request
-            if r.finish_reason is not None:
-                return None
-            # with the token that is on its way the request has len(output) + 1 tokens: does it go on after it?
-            if len(r.output) + 1 >= r.params.max_tokens or r.n_tokens + 1 >= sch.max_positions:
-                return None
-            nxt.append(PlannedEntry(r, r.n_tokens, 1, True))
-        free = [pool.n_free for pool in self.runner.manager.pools]
-        # the cache has this step's token committed already: one more token each
-        if self.runner.manager.fit_in_order([e.request.rid for e in nxt], [1] * len(nxt), free) != len(nxt):
-            return None
-        if not self.runner.takes_device_tokens([StepEntry(e.request.rid, [0], [0]) for e in nxt]):
-            return None
-        return nxt
+            if e.samples and r.finish_reason is None and (
+                    len(r.output) + r.n_in_flight >= r.params.max_tokens
+                    or r.n_tokens + r.n_in_flight >= sch.max_positions):
+                return True
+        return False
 
     def step(self) -> List[Request]:
         """Plan, run and sample one step; returns the requests that are known to have finished.  With
         ``overlap`` the step is launched before the tokens of the one before it are read, where that can be."""
         finished: List[Request] = []
         prev, self._in_flight = self._in_flight, None
-        if prev is not None:
-            nxt = self._next_decode_plan(prev)
-            if nxt is not None:
-                self._in_flight = self._launch(nxt, device_tokens=prev[1], pending=1)
-                return self._finish(prev)
-            finished = self._finish(prev)
-        plan, ended = self.scheduler.plan()
+        if prev is not None and self._ends_for_sure(prev):
+            finished += self._finish(prev)
+            prev = None
+        planned = self.scheduler.plan(may_preempt=prev is None)
+        if planned is None:
+            # pages are short: the step on its way may end a request; only then is a request's work thrown away
+            finished += self._finish(prev)
+            prev = None
+            planned = self.scheduler.plan()
+        plan, ended = planned
+        if prev is not None and any(e.start + e.n > e.request.n_tokens for e in plan):
+            entries = [StepEntry(e.request.rid, [0] * e.n, []) for e in plan]
+            if not self.runner.takes_carried_tokens(entries):
+                # this step needs its tokens on the host: read them, and leave out who ended with them
+                finished += self._finish(prev)
+                prev = None
+                plan = [e for e in plan if e.request.finish_reason is None]
         if not plan:
+            if prev is not None:
+                finished += self._finish(prev)
             return finished + ended
-        launched = self._launch(plan)
+        launched = self._launch(plan, before=prev)
+        if prev is not None:
+            self.n_steps_ahead += 1
+            self.n_portion_steps_ahead += any(e.n > 1 for e in plan)
+            finished += self._finish(prev)
         if self.overlap:
             self._in_flight = launched
             return finished + ended
@@ -257,6 +279,8 @@ class Engine:
             "tokens_run": self.n_tokens_run,
             "preemptions": self.scheduler.n_preemptions,
             "steps_in_vain": self.n_steps_in_vain,
+            "steps_ahead": self.n_steps_ahead,
+            "portion_steps_ahead": self.n_portion_steps_ahead,
             "running": len(self.scheduler.running),
             "waiting": len(self.scheduler.waiting),
             "free_pages": [p.n_free for p in m.pools],

@@ -43,6 +43,21 @@ class _Captured:
         self.turn = 0
 
 
+def name_carried_tokens(stage: torch.Tensor, entries: Sequence[StepEntry], sources: Sequence[int]):
+    """In a description in pinned memory, replace the token id of every entry that has a source (>= 0) by the
+    stand-in -1 - source: ``kernels.resolve_tokens`` puts the token itself there on the device.  Such an entry
+    brings exactly one token; the token ids lead the description, in the order of the entries."""
+    view = stage.numpy()
+    row = 0
+    for e, src in zip(entries, sources):
+        if src >= 0:
+            if len(e.tokens) != 1:
+                raise ValueError(f"request {e.rid!r}: only a single token can be taken from the step before")
+            view[row] = -1 - src
+        row += len(e.tokens)
+    return row
+
+
 class DecodeGraphs:
     def __init__(self, runner, max_context: int):
         self.runner = runner
@@ -69,7 +84,7 @@ class DecodeGraphs:
         return 8 * per_part + sum((bucket * p + 3) // 4 * 4 for p in self.fixed_pages) + 16
 
     # ---- the description of a replayed step -------------------------------------------
-    def _describe(self, cap: _Captured, entries: Sequence[StepEntry], bucket: int):
+    def _describe(self, cap: _Captured, entries: Sequence[StepEntry], bucket: int, carry=None):
         """Bring the device's description up to date for these entries: native code writes it into pinned
         memory from the cache's book, one asynchronous copy takes it to the device."""
         r = self.runner
@@ -90,24 +105,27 @@ class DecodeGraphs:
                                 fixed_pages=self.fixed_pages, pad_to=bucket)
             host = ctx.extra["host"]
             stage.numpy()[:host.size] = host
+        if carry is not None:
+            name_carried_tokens(stage, entries, carry[1])
         cap.buffer.copy_(stage, non_blocking=True)
         ev = cap.copied[k] or torch.cuda.Event()
         ev.record()
         cap.copied[k] = ev
+        if carry is not None:
+            kernels.resolve_tokens(cap.buffer[:len(entries)], carry[0], r.rt.dtype)
 
-    def run(self, entries: Sequence[StepEntry], device_tokens: Optional[torch.Tensor] = None) -> torch.Tensor:
-        """Logits [wanted rows, vocab] of a step of single tokens; pages are already reserved.  With
-        ``device_tokens`` (int32 on the device, one per entry) the entries' own token ids are stand-ins: the step
-        takes its tokens from there, in stream order, so it can be launched before the host has seen them."""
+    def run(self, entries: Sequence[StepEntry], carry=None) -> torch.Tensor:
+        """Logits [wanted rows, vocab] of a step of single tokens; pages are already reserved.  ``carry`` is
+        (int32 token ids on the device, for every entry its place among them or -1): an entry with a place
+        takes its token from there, in stream order, and its own token id is a stand-in; so the step can be
+        launched before the host has seen the tokens that the step before it sampled."""
         bucket = self.bucket_for(len(entries))
         cap = self.captured.get(bucket)
         if cap is None:
             cap = self._capture(entries, bucket)
-            if device_tokens is None:
+            if carry is None:
                 return self._wanted(cap, entries)
-        self._describe(cap, entries, bucket)
-        if device_tokens is not None:
-            cap.buffer[:len(entries)].copy_(device_tokens[:len(entries)])   # the token ids lead the description
+        self._describe(cap, entries, bucket, carry)
         cap.graph.replay()
         kernels.count_launches(cap.launches)
         return self._wanted(cap, entries)
@@ -197,37 +215,43 @@ class PortionGraphs:
         ctx.max_kv_len = self.max_context
         return ctx
 
-    def run(self, entries: Sequence[StepEntry]) -> torch.Tensor:
-        """Logits [wanted rows, vocab]; pages are already reserved."""
+    def run(self, entries: Sequence[StepEntry], carry=None) -> torch.Tensor:
+        """Logits [wanted rows, vocab]; pages are already reserved.  ``carry`` as in :meth:`DecodeGraphs.run`."""
         r = self.runner
-        bucket = self.bucket_for(sum(len(e.tokens) for e in entries))
+        n_rows = sum(len(e.tokens) for e in entries)
+        bucket = self.bucket_for(n_rows)
         n_wanted = sum(len(e.want) for e in entries)
         cap = self.captured.get(bucket)
         if cap is None:
             cap = self._capture(entries, bucket)
-        else:
-            k = cap.turn
-            cap.turn ^= 1
-            if cap.copied[k] is not None:
-                cap.copied[k].synchronize()
-            stage = cap.staging[k]
-            try:
-                code, _ = r.manager.describe_step(
-                    [e.rid for e in entries], [e.tokens for e in entries], [e.want for e in entries], bucket,
-                    self.n_requests, self.n_wanted, self.fixed_pages, self.tile_sizes, r.spec.vocab_size,
-                    r.spec.max_positions, stage.data_ptr(), stage.numel())
-            except (TypeError, ValueError, OverflowError):
-                code = -1
-            if code < 0:
-                # something is wrong with an entry: the general builder says what (or builds it, if it can)
-                host = self._build(entries, bucket, torch.device("cpu")).extra["host"]
-                stage.numpy()[:host.size] = host
-            cap.buffer.copy_(stage, non_blocking=True)
-            ev = cap.copied[k] or torch.cuda.Event()
-            ev.record()
-            cap.copied[k] = ev
-            cap.graph.replay()
-            kernels.count_launches(cap.launches)
+            if carry is None:
+                return cap.logits[:n_wanted]
+        k = cap.turn
+        cap.turn ^= 1
+        if cap.copied[k] is not None:
+            cap.copied[k].synchronize()
+        stage = cap.staging[k]
+        try:
+            code, _ = r.manager.describe_step(
+                [e.rid for e in entries], [e.tokens for e in entries], [e.want for e in entries], bucket,
+                self.n_requests, self.n_wanted, self.fixed_pages, self.tile_sizes, r.spec.vocab_size,
+                r.spec.max_positions, stage.data_ptr(), stage.numel())
+        except (TypeError, ValueError, OverflowError):
+            code = -1
+        if code < 0:
+            # something is wrong with an entry: the general builder says what (or builds it, if it can)
+            host = self._build(entries, bucket, torch.device("cpu")).extra["host"]
+            stage.numpy()[:host.size] = host
+        if carry is not None:
+            name_carried_tokens(stage, entries, carry[1])
+        cap.buffer.copy_(stage, non_blocking=True)
+        ev = cap.copied[k] or torch.cuda.Event()
+        ev.record()
+        cap.copied[k] = ev
+        if carry is not None:
+            kernels.resolve_tokens(cap.buffer[:n_rows], carry[0], r.rt.dtype)
+        cap.graph.replay()
+        kernels.count_launches(cap.launches)
         return cap.logits[:n_wanted]
 
     def _capture(self, entries: Sequence[StepEntry], bucket: int) -> _Captured:

@@ -126,29 +126,38 @@ class ModelRunner:
             self.manager.commit(e.rid, len(e.tokens))
         self.steps_run += 1
 
-    def takes_device_tokens(self, entries: Sequence[StepEntry]) -> bool:
-        """Whether :meth:`step` can run these entries with their token ids still on the device."""
+    def _decode_graph_takes(self, entries: Sequence[StepEntry]) -> bool:
         return self.graphs is not None and all(len(e.tokens) == 1 for e in entries) \
             and all(self.manager.n_tokens(e.rid) < self.graphs.max_context for e in entries)
 
-    def step(self, entries: Sequence[StepEntry], own_output: bool = True,
-             device_tokens: Optional[torch.Tensor] = None) -> torch.Tensor:
+    def takes_carried_tokens(self, entries: Sequence[StepEntry]) -> bool:
+        """Whether :meth:`step` can run these entries while some of their token ids are still on the device:
+        replayed steps can (their description is completed on the device)."""
+        return self._decode_graph_takes(entries) or \
+            (self.portion_graphs is not None and self.portion_graphs.takes(entries))
+
+    def step(self, entries: Sequence[StepEntry], own_output: bool = True, carry=None) -> torch.Tensor:
         """float32 logits [number of wanted places, vocab], in the order of entries and of ``want``.
 
         ``own_output=False`` may return a view of a buffer that the next step overwrites (a replayed
         graph writes to fixed memory); the caller must be done with it before it steps again.
-        ``device_tokens`` (int32 on the device, one per entry): the step of single tokens takes its token ids
-        from there instead of from the entries (see :meth:`takes_device_tokens`).
+        ``carry`` = (int32 token ids on the device, for every entry its place among them or -1): an entry with a
+        place brings one token whose id is still on the device, sampled by the step before; the id in the entry
+        is a stand-in (see :meth:`takes_carried_tokens`).
         """
-        if device_tokens is not None and not self.takes_device_tokens(entries):
-            raise ValueError("only a replayed step of single tokens can take its token ids from the device")
-        if self.graphs is not None and all(len(e.tokens) == 1 for e in entries) \
-                and all(self.manager.n_tokens(e.rid) < self.graphs.max_context for e in entries):
+        if carry is not None:
+            if len(carry[1]) != len(entries) or any(s >= carry[0].shape[0] for s in carry[1]):
+                raise ValueError("carried tokens: one place per entry, each within the given token ids")
+            if any(s >= 0 and len(e.tokens) != 1 for e, s in zip(entries, carry[1])):
+                raise ValueError("carried tokens: only an entry of a single token can take it from the device")
+            if not self.takes_carried_tokens(entries):
+                raise ValueError("only a replayed step can take token ids that are still on the device")
+        if self._decode_graph_takes(entries):
             wants = {e.rid: 1 for e in entries}
             if len(wants) != len(entries):
                 raise ValueError("a request appears twice in one step")
             self.manager.reserve(wants)
-            logits = self.graphs.run(entries, device_tokens)
+            logits = self.graphs.run(entries, carry)
             if own_output:
                 logits = logits.clone()
         elif self.portion_graphs is not None and self.portion_graphs.takes(entries):
@@ -156,7 +165,7 @@ class ModelRunner:
             if len(wants) != len(entries):
                 raise ValueError("a request appears twice in one step")
             self.manager.reserve(wants)
-            logits = self.portion_graphs.run(entries)
+            logits = self.portion_graphs.run(entries, carry)
             if own_output:
                 logits = logits.clone()
         else:

@@ -36,7 +36,8 @@ class Request:
     params: SamplingParams
     seed: int
     output: List[int] = field(default_factory=list)
-    n_computed: int = 0             # tokens whose keys and values are in the cache
+    n_computed: int = 0             # tokens whose keys and values are in the cache (or will be after a launched step)
+    n_in_flight: int = 0            # tokens that launched steps have sampled and the host has not read yet
     finish_reason: Optional[str] = None
     n_preempted: int = 0
     order: int = 0                  # arrival number: smaller is older
@@ -51,7 +52,8 @@ class Request:
 
     @property
     def n_pending(self) -> int:
-        return len(self.prompt) + len(self.output) - self.n_computed
+        """Tokens that still have to run; one of them may be a token that is on its way from the device."""
+        return len(self.prompt) + len(self.output) + self.n_in_flight - self.n_computed
 
     def token_slice(self, start: int, n: int) -> List[int]:
         """tokens[start:start + n] without building the whole list."""
@@ -149,10 +151,13 @@ class Scheduler:
         self.waiting.appendleft(v)
         return True
 
-    def plan(self) -> Tuple[List[PlannedEntry], List[Request]]:
+    def plan(self, may_preempt: bool = True) -> Optional[Tuple[List[PlannedEntry], List[Request]]]:
         """(entries of the next step, requests that ended while planning because they outgrew the cache).
 
         Pages are not taken here; the step function reserves exactly what this plan was checked for.
+        ``may_preempt=False``: None, with nothing changed, if the step cannot be planned without taking a running
+        request's pages away or ending one (a caller that has a step on its way asks so, reads that step's tokens
+        and plans again).
         """
         ended: List[Request] = []
         while True:
@@ -182,11 +187,15 @@ class Scheduler:
             order = order[:len(counts)]
             fitted = self.manager.fit_in_order([r.rid for r in order], counts, free) if order else 0
             for r, n in zip(order[:fitted], counts[:fitted]):
-                plan.append(PlannedEntry(r, r.n_computed, n, r.n_computed + n == r.n_tokens))
+                plan.append(PlannedEntry(r, r.n_computed, n, n == r.n_pending))
             if fitted < len(order):
                 starved = order[fitted]
                 budget += sum(counts[fitted:])
             if starved is not None:
+                if not may_preempt:
+                    return None
+                if any(r.n_in_flight for r in self.running):
+                    raise SchedulerError("a launched step's tokens must be delivered before a plan that may preempt")
                 if self._preempt_youngest(keep=starved):
                     continue  # plan again with the pages that came back
                 # the request is alone and still does not fit: it has outgrown the cache
@@ -206,7 +215,7 @@ class Scheduler:
                     break
                 self.waiting.popleft()
                 self.running.append(r)
-                plan.append(PlannedEntry(r, r.n_computed, n, r.n_computed + n == r.n_tokens))
+                plan.append(PlannedEntry(r, r.n_computed, n, n == r.n_pending))
                 budget -= n
             return plan, ended
 
@@ -220,21 +229,35 @@ class Scheduler:
             return "length"
         return None
 
-    def update(self, plan: Sequence[PlannedEntry], sampled: Sequence[int]) -> List[Request]:
-        """Record the step: ``sampled`` holds one token per planned entry with ``samples``, in plan order.
-        Returns the requests that finished; their pages and slots are free again."""
+    def advance(self, plan: Sequence[PlannedEntry]):
+        """The planned step has been launched: its tokens count as run, and every entry that samples has a token on
+        its way that the host does not know yet."""
+        for e in plan:
+            e.request.n_computed += e.n
+            if e.samples:
+                e.request.n_in_flight += 1
+
+    def deliver(self, plan: Sequence[PlannedEntry], sampled: Sequence[int]) -> List[Request]:
+        """The tokens of a launched step have arrived: ``sampled`` holds one per planned entry with ``samples``,
+        in plan order.  Returns the requests that finished; their pages and slots are free again."""
         finished: List[Request] = []
         it = iter(sampled)
         for e in plan:
+            if not e.samples:
+                continue
             r = e.request
-            r.n_computed += e.n
-            if e.samples:
-                tok = int(next(it))
-                r.output.append(tok)
-                reason = self.stop_reason(r, tok)
-                if reason is not None:
-                    r.finish_reason = reason
-                    self.running.remove(r)
-                    self.manager.release(r.rid)
-                    finished.append(r)
+            tok = int(next(it))
+            r.n_in_flight -= 1
+            r.output.append(tok)
+            reason = self.stop_reason(r, tok)
+            if reason is not None:
+                r.finish_reason = reason
+                self.running.remove(r)
+                self.manager.release(r.rid)
+                finished.append(r)
         return finished
+
+    def update(self, plan: Sequence[PlannedEntry], sampled: Sequence[int]) -> List[Request]:
+        """Record a step whose tokens are known: :meth:`advance` and :meth:`deliver` in one."""
+        self.advance(plan)
+        return self.deliver(plan, sampled)

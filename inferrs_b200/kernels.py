@@ -25,6 +25,7 @@ class KernelError(RuntimeError):
 
 _SIGNATURES = {
     "ib_embedding_gather": [c_void_p, c_int, c_void_p, c_void_p, c_int, c_int, c_int, c_void_p],
+    "ib_resolve_tokens": [c_void_p, c_int, c_void_p, c_int, c_void_p],
     "ib_add_rms_norm": [c_void_p, c_void_p, c_void_p, c_int, c_void_p, c_void_p, c_int, c_int, c_float, c_void_p],
     "ib_silu_gate": [c_void_p, c_void_p, c_int, c_int, c_void_p],
     "ib_act_to_float": [c_void_p, c_void_p, c_long, c_void_p],
@@ -149,6 +150,15 @@ def embedding_gather(table: torch.Tensor, ids: torch.Tensor, out: torch.Tensor, 
         raise KernelError(f"embedding_gather: ids {tuple(ids.shape)}, table {tuple(table.shape)}, out {tuple(out.shape)}")
     _check(_core(act_dtype).ib_embedding_gather(_p(table), int(table.dtype == torch.float32), _p(ids), _p(out), n,
                                                 width, table.shape[0], _stream()), "embedding_gather")
+
+
+def resolve_tokens(ids: torch.Tensor, carry: torch.Tensor, act_dtype: torch.dtype):
+    """ids[i] = carry[-1 - ids[i]] wherever ids[i] < 0: a step's description names tokens that an earlier step
+    sampled and the host has not read yet by their place in that step's output."""
+    _need(ids, "ids", _I, 1)
+    _need(carry, "carry", _I, 1)
+    _check(_core(act_dtype).ib_resolve_tokens(_p(ids), ids.shape[0], _p(carry), carry.shape[0], _stream()),
+           "resolve_tokens")
 
 
 def add_rms_norm(residual: torch.Tensor, delta: Optional[torch.Tensor], weight: torch.Tensor, eps: float,

@@ -183,3 +183,61 @@ def test_steps_with_portions_are_replayed_graphs(model_dirs, name, dtype):
         for row, (rid, pos) in enumerate(meta):
             check(out[row:row + 1], want[rid][pos:pos + 1], dtype, f"request {rid} at {pos}")
     runner.manager.check_invariants()
+
+
+@pytest.mark.parametrize("name,dtype", [("B", torch.float32), ("D", torch.bfloat16)])
+def test_replayed_steps_take_tokens_that_are_still_on_the_device(model_dirs, name, dtype):
+    """A step may name a token by its place in an int32 tensor on the device instead of by its id (the engine
+    launches a step before it has read what the step before it sampled): a step of single tokens and a step
+    with a portion beside single tokens, some tokens carried and some known, give the logits that the same step
+    gives with all ids known; a step that is no replayed graph refuses."""
+    cfg = CONFIGS[name]
+    vocab = cfg["vocab_size"]
+    prompts = [random_tokens(n, vocab, seed=30 + n) for n in (21, 5, 34, 12)]
+    nxt = [random_tokens(3, vocab, seed=70 + i) for i in range(4)]
+
+    def play(carried):
+        runner = make_runner(model_dirs[name], dtype, PAGE_SIZE[name], n_pages=64)
+        outs = []
+        for i in (0, 1, 2):
+            runner.admit(i)
+            runner.step([StepEntry(i, prompts[i], [])])
+        # the tokens of the next steps as an earlier step's output would hold them, in another order
+        ids = torch.tensor([nxt[2][0], 0, nxt[0][0], nxt[1][0], nxt[0][1], nxt[2][1]], dtype=torch.int32, device="cuda")
+        place = {(2, 0): 0, (0, 0): 2, (1, 0): 3, (0, 1): 4, (2, 1): 5}
+        # three single tokens: request 1's is known, the others come from the device
+        entries = [StepEntry(i, [nxt[i][0]], [0]) for i in (0, 1, 2)]
+        if carried:
+            entries = [StepEntry(0, [0], [0]), entries[1], StepEntry(2, [0], [0])]
+            outs.append(runner.step(entries, carry=(ids, [place[(0, 0)], -1, place[(2, 0)]])))
+        else:
+            outs.append(runner.step(entries))
+        # a new request's portion beside two single tokens, one of them carried
+        runner.admit(3)
+        entries = [StepEntry(0, [nxt[0][1]], [0]), StepEntry(3, prompts[3], [len(prompts[3]) - 1]),
+                   StepEntry(2, [nxt[2][1]], [0])]
+        if carried:
+            entries[2] = StepEntry(2, [0], [0])
+            outs.append(runner.step(entries, carry=(ids, [-1, -1, place[(2, 1)]])))
+        else:
+            outs.append(runner.step(entries))
+        runner.manager.check_invariants()
+        return outs, runner
+
+    want, _ = play(False)
+    got, runner = play(True)
+    for a, b in zip(got, want):
+        assert torch.equal(a, b)
+    for i in (0, 2):
+        full = plain_logits(model_dirs[name], prompts[i] + nxt[i][:2], dtype)
+        check(got[0][i:i + 1], full[len(prompts[i]):len(prompts[i]) + 1], dtype, f"request {i}")
+    with pytest.raises(ValueError, match="place"):
+        runner.step([StepEntry(0, [0], [0])], carry=(torch.zeros(2, dtype=torch.int32, device="cuda"), [2]))
+    with pytest.raises(ValueError, match="single token"):
+        runner.step([StepEntry(1, [0, 0], [1])], carry=(torch.zeros(2, dtype=torch.int32, device="cuda"), [1]))
+    runner.manager.check_invariants()
+    plain_runner = make_runner(model_dirs[name], dtype, PAGE_SIZE[name], n_pages=64)
+    plain_runner.graphs = plain_runner.portion_graphs = None
+    plain_runner.admit(0)
+    with pytest.raises(ValueError, match="replayed"):
+        plain_runner.step([StepEntry(0, [0], [0])], carry=(torch.zeros(1, dtype=torch.int32, device="cuda"), [0]))

@@ -314,9 +314,9 @@ def test_replayed_steps_get_the_description_that_the_general_builder_gives():
     checked_steps = []
     original = dg._describe
 
-    def checked(cap, entries, bucket):
+    def checked(cap, entries, bucket, carry=None):
         turn = cap.turn
-        original(cap, entries, bucket)
+        original(cap, entries, bucket, carry)
         ctx = build_context(entries, runner.manager, runner.storage, spec.vocab_size, spec.max_positions,
                             torch.device("cpu"), fixed_pages=dg.fixed_pages, pad_to=bucket)
         host = ctx.extra["host"]

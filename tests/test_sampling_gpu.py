@@ -217,3 +217,56 @@ def test_steps_go_one_ahead_while_requests_wait_for_a_slot(model_dirs):
     # most decode steps of the second engine were launched before the step before them had been read
     assert b.n_steps <= a.n_steps + len(prompts) + b.n_steps_in_vain
     assert b.stats()["free_pages"] == b.stats()["pages"] and not b.has_work()
+
+
+@pytest.mark.parametrize("name,dtype", [("B", "f32"), ("D", "bf16")])
+def test_steps_with_prompt_portions_go_one_ahead_too(model_dirs, name, dtype):
+    """Requests come while others decode, and their prompts are cut into portions: the step with the next portions
+    and the others' next tokens is launched before the tokens of the step before it are read (a request that has
+    just finished its prompt hands its first token on to its first decode step on the device).  Tokens, reasons
+    and the cache's state are those of the engine that reads every step first; with penalties and stops too."""
+    from inferrs_b200 import Engine
+    cfg = CONFIG_B if name == "B" else __import__("helpers").CONFIG_D
+    prompts = [random_tokens(n, cfg["vocab_size"], seed=60 + n) for n in (70, 9, 41, 26, 55, 3)]
+    # in bfloat16 a row's rounding depends on which kernels the step's size selects: there all requests are
+    # present from the start and none ends before the last prompt is in, so that both engines run the same steps
+    late = dtype == "f32"
+    kw = dict(dtype=dtype, block_size=16, num_blocks=64, max_batch_size=4 if late else 6, max_tokens_per_step=24,
+              prefill_chunk=16)
+
+    def run(overlap, params, late_every=3):
+        eng = Engine(model_dirs[name], overlap=overlap, **kw)
+        first = 2 if late else len(prompts)
+        rids = [eng.add_request(p, q) for p, q in zip(prompts[:first], params[:first])]
+        done, k, nxt = {}, 0, first
+        while eng.has_work() or nxt < len(prompts):
+            for r in eng.step():
+                done[r.rid] = r
+            k += 1
+            if nxt < len(prompts) and k % late_every == 0:     # the next request arrives while the others run
+                rids.append(eng.add_request(prompts[nxt], params[nxt]))
+                nxt += 1
+        for r in eng.flush():
+            done[r.rid] = r
+        assert eng.stats()["free_pages"] == eng.stats()["pages"] and not eng.has_work()
+        eng.runner.manager.check_invariants()
+        return [(done[r].output, done[r].finish_reason) for r in rids], eng
+
+    greedy = [SamplingParams.greedy(max_tokens=16 + 4 * i) for i in range(len(prompts))]
+    want, a = run(False, greedy)
+    got, b = run(True, greedy)
+    assert got == want
+    assert b.stats()["portion_steps_ahead"] >= 8 and b.stats()["steps_ahead"] > b.stats()["portion_steps_ahead"]
+    assert a.stats()["steps_ahead"] == 0
+    # a stop token that the first request reaches while the later prompts are still coming in
+    stop = want[0][0][6 if late else 15]
+    stops = [SamplingParams(temperature=0.0, repetition_penalty=1.0, max_tokens=16 + 4 * i, stop_token_ids=(stop,))
+             for i in range(len(prompts))]
+    want, _ = run(False, stops)
+    got, b = run(True, stops)
+    assert got == want and any(reason == "stop" for _, reason in want)
+    # the reference's default options (penalties over a window, top-k, top-p) with seeds
+    sampled = [SamplingParams(temperature=0.7, max_tokens=16 + 2 * i, seed=5 + i) for i in range(len(prompts))]
+    want, _ = run(False, sampled)
+    got, b = run(True, sampled)
+    assert got == want and b.stats()["portion_steps_ahead"] >= 8

@@ -130,3 +130,79 @@ def test_abort_frees_everything():
     s.add(req("c", 3))
     assert s.abort("c").finish_reason == "cancelled" and len(s.waiting) == 0
     m.check_invariants()
+
+
+def launch(s, m, may_preempt=True):
+    """Plan and launch a step as the engine does when it goes one ahead: the tokens are not known yet."""
+    planned = s.plan(may_preempt=may_preempt)
+    if planned is None:
+        return None
+    plan, ended = planned
+    assert not ended
+    m.reserve({e.request.rid: e.n for e in plan})
+    for e in plan:
+        m.commit(e.request.rid, e.n)
+    s.advance(plan)
+    return plan
+
+
+def shape(plan):
+    return [(e.request.rid, e.start, e.n, e.samples) for e in plan]
+
+
+def test_the_next_step_is_planned_before_the_tokens_of_the_last_are_known():
+    """``advance`` at the launch, ``deliver`` when the tokens come: in between the request counts one token that
+    nobody knows yet, and the next plan gives it a step of one token at the place after its known tokens."""
+    s, m = make(budget=16, eos=(99,))
+    s.add(req("a", 10, max_tokens=8)); s.add(req("b", 30, max_tokens=8))
+    p1 = launch(s, m)
+    assert shape(p1) == [("a", 0, 10, True), ("b", 0, 6, False)]
+    a = p1[0].request
+    assert (a.n_tokens, a.n_in_flight, a.n_pending) == (10, 1, 1)
+    p2 = launch(s, m, may_preempt=False)        # a's first token is still on its way
+    assert shape(p2) == [("a", 10, 1, True), ("b", 6, 15, False)]
+    assert p2[0].start + p2[0].n > a.n_tokens    # the engine sees from this that the token comes from the device
+    assert a.n_in_flight == 2 and a.n_pending == 1
+    assert s.deliver(p1, [5]) == []
+    assert (a.output, a.n_in_flight, a.n_pending) == ([5], 1, 1)
+    p3 = launch(s, m, may_preempt=False)
+    assert shape(p3) == [("a", 11, 1, True), ("b", 21, 9, True)]
+    # the token of the second step ends a: the third step, already launched, ran a in vain
+    fin = s.deliver(p2, [99])
+    assert [r.rid for r in fin] == ["a"] and a.finish_reason == "stop" and not m.has("a")
+    alive = [e for e in p3 if e.request.finish_reason is None]
+    assert s.deliver(alive, [6]) == []
+    b = p3[1].request
+    assert (b.output, b.n_in_flight, b.n_pending) == ([6], 0, 1)
+    m.check_invariants()
+    # update is both at once
+    plan, _ = s.plan()
+    m.reserve({e.request.rid: e.n for e in plan})
+    m.commit("b", 1)
+    s.update(plan, [7])
+    assert (b.output, b.n_in_flight, b.n_computed) == ([6, 7], 0, 31)
+
+
+def test_a_plan_that_would_preempt_is_not_made_while_a_step_is_on_its_way():
+    """Too few pages for the next tokens: asked not to preempt, the scheduler answers None and changes nothing; a
+    plan that may preempt is refused while tokens are on their way (the youngest request's last token would be
+    lost) and made once they are delivered."""
+    s, m = make(n_pages=4, page_size=4, budget=32)
+    s.add(req("old", 7, max_tokens=20)); s.add(req("young", 7, max_tokens=20))
+    p1 = launch(s, m)
+    assert shape(p1) == [("old", 0, 7, True), ("young", 0, 7, True)]     # two pages each: the cache is full
+    p2 = launch(s, m, may_preempt=False)
+    assert shape(p2) == [("old", 7, 1, True), ("young", 7, 1, True)]     # the eighth places are in the pages held
+    s.deliver(p1, [3, 4])
+    before = (m.pools[0].n_free, [r.rid for r in s.running], [r.rid for r in s.waiting], s.n_preemptions)
+    assert s.plan(may_preempt=False) is None                             # a ninth place needs a third page
+    assert before == (m.pools[0].n_free, [r.rid for r in s.running], [r.rid for r in s.waiting], s.n_preemptions)
+    with pytest.raises(SchedulerError, match="delivered"):
+        s.plan()
+    s.deliver(p2, [5, 6])
+    plan, ended = s.plan()
+    assert not ended and s.n_preemptions == 1
+    assert shape(plan) == [("old", 8, 1, True)]
+    young = p1[1].request
+    assert young in s.waiting and young.n_computed == 0 and young.output == [4, 6] and young.n_in_flight == 0
+    m.check_invariants()
