@@ -67,6 +67,10 @@ def host_library():
         lib.ibh_cache_new.restype = p
         lib.ibh_cache_delete.argtypes = [p]
         lib.ibh_cache_delete.restype = None
+        lib.ibh_sched_new.argtypes = [p, i, i, i, i, p, i]
+        lib.ibh_sched_new.restype = p
+        lib.ibh_sched_delete.argtypes = [p]
+        lib.ibh_sched_delete.restype = None
         for name, args in {
             "ibh_cache_admit": [p, l], "ibh_cache_has": [p, l], "ibh_cache_n_live": [p],
             "ibh_cache_n_free_slots": [p], "ibh_cache_n_free_pages": [p, i], "ibh_cache_slot": [p, l],
@@ -77,6 +81,11 @@ def host_library():
             "ibh_cache_fit_in_order": [p, i, p, p, p],
             "ibh_describe_decode": [p, i, p, p, i, p, i, i, p, i, p],
             "ibh_describe_step": [p, i, p, p, p, p, p, i, i, i, p, i, p, p, i, i, p, i, p],
+            "ibh_sched_add": [p, l, i, i, i, p, i], "ibh_sched_abort": [p, l],
+            "ibh_sched_plan": [p, i, i, p, p, p, p, p, p, p, p, p],
+            "ibh_sched_advance": [p, i, p, p, p], "ibh_sched_deliver": [p, i, p, p, p],
+            "ibh_sched_counts": [p, l, p], "ibh_sched_n_waiting": [p], "ibh_sched_n_running": [p],
+            "ibh_sched_n_preemptions": [p],
         }.items():
             f = getattr(lib, name)
             f.argtypes = args
@@ -150,6 +159,22 @@ class CacheManager:
 
     def has(self, rid: Hashable) -> bool:
         return rid in self._handles
+
+    # the native scheduler admits and releases requests in the native book itself; the front follows
+    def new_handle(self) -> int:
+        """A number that no request has had yet (the native scheduler knows a request by it from its arrival)."""
+        self._next_handle += 1
+        return self._next_handle - 1
+
+    def adopt(self, rid: Hashable, handle: int):
+        """Native code has admitted the request under ``handle``."""
+        if rid in self._handles:
+            raise CacheError(f"request {rid!r} is already live")
+        self._handles[rid] = handle
+
+    def forget(self, rid: Hashable):
+        """Native code has released the request."""
+        self._handles.pop(rid, None)
 
     @property
     def n_live(self) -> int:

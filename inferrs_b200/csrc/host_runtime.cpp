@@ -6,6 +6,7 @@
 // (inferrs-models/src/kv_cache.rs:80-139), a table per request (:154-222), release at the request's end
 // (inferrs/src/engine.rs:746-748).  Here there is one pool and one table per *group* of caches with the same
 // needs; a group with a window gives pages back as soon as every later query's window has passed them.
+#include <algorithm>
 #include <cstdint>
 #include <cstdio>
 #include <cstring>
@@ -70,6 +71,35 @@ struct Cache {
     std::unordered_map<int64_t, Request> requests;
 
     int pages_for(int n_tokens) const { return (n_tokens + page_size - 1) / page_size; }
+
+    // the request gets a state slot (returned, >= 0) and empty block tables
+    int admit(int64_t rid) {
+        if (requests.count(rid)) return ERR_ALREADY_LIVE;
+        if (free_slots.empty()) return ERR_NO_SLOT;
+        Request r;
+        r.slot = free_slots.front();
+        free_slots.pop_front();
+        r.tables.resize(pools.size());
+        const int slot = r.slot;
+        requests.emplace(rid, std::move(r));
+        return slot;
+    }
+
+    // Free[g] pages of every group are still unspoken for; request i would take the pages for n_new[i] more
+    // tokens.  Subtracts what each one needs from free_pages[] as long as it fits and stops at the first that
+    // does not; returns how many fitted.  Nothing is taken from the pools.
+    int fit_in_order(int n, const int64_t* rids, const int* n_new, int* free_pages) {
+        std::vector<int> need(pools.size());
+        for (int i = 0; i < n; ++i) {
+            Request* r = get(rids[i]);
+            if (r == nullptr) return ERR_UNKNOWN_REQUEST;
+            pages_needed(*r, n_new[i], need.data());
+            for (size_t g = 0; g < pools.size(); ++g)
+                if (need[g] > free_pages[g]) return i;
+            for (size_t g = 0; g < pools.size(); ++g) free_pages[g] -= need[g];
+        }
+        return n;
+    }
 
     Request* get(int64_t rid) {
         auto it = requests.find(rid);
@@ -215,18 +245,7 @@ IBH_EXPORT void* ibh_cache_new(int n_groups, const int* windows, const int* n_pa
 IBH_EXPORT void ibh_cache_delete(void* h) { delete static_cast<Cache*>(h); }
 
 // The request gets a state slot (returned, >= 0) and empty block tables.
-IBH_EXPORT int ibh_cache_admit(void* h, int64_t rid) {
-    Cache* c = static_cast<Cache*>(h);
-    if (c->requests.count(rid)) return ERR_ALREADY_LIVE;
-    if (c->free_slots.empty()) return ERR_NO_SLOT;
-    Request r;
-    r.slot = c->free_slots.front();
-    c->free_slots.pop_front();
-    r.tables.resize(c->pools.size());
-    const int slot = r.slot;
-    c->requests.emplace(rid, std::move(r));
-    return slot;
-}
+IBH_EXPORT int ibh_cache_admit(void* h, int64_t rid) { return static_cast<Cache*>(h)->admit(rid); }
 
 IBH_EXPORT int ibh_cache_has(void* h, int64_t rid) { return static_cast<Cache*>(h)->requests.count(rid) ? 1 : 0; }
 IBH_EXPORT int ibh_cache_n_live(void* h) { return (int)static_cast<Cache*>(h)->requests.size(); }
@@ -472,16 +491,337 @@ IBH_EXPORT int ibh_describe_step(void* h, int n, const int64_t* rids, const int*
 // each one needs from free[] as long as it fits, and stops at the first that does not.  Returns how many fitted
 // (n if all did); free[] then holds what is left after those.  Nothing is taken from the pools.
 IBH_EXPORT int ibh_cache_fit_in_order(void* h, int n, const int64_t* rids, const int* n_new, int* free_pages) {
-    Cache* c = static_cast<Cache*>(h);
-    const int n_groups = (int)c->pools.size();
-    std::vector<int> need(n_groups);
-    for (int i = 0; i < n; ++i) {
-        Request* r = c->get(rids[i]);
-        if (r == nullptr) return ERR_UNKNOWN_REQUEST;
-        c->pages_needed(*r, n_new[i], need.data());
-        for (int g = 0; g < n_groups; ++g)
-            if (need[g] > free_pages[g]) return i;
-        for (int g = 0; g < n_groups; ++g) free_pages[g] -= need[g];
-    }
-    return n;
+    return static_cast<Cache*>(h)->fit_in_order(n, rids, n_new, free_pages);
 }
+
+// ---------------------------------------------------------------------------------------------------------
+// The scheduler's decisions in native code: which requests run in the next step and with how many tokens.
+//
+// The reference's loop admits requests while fewer than max_batch_size are active, runs one forward pass per
+// sequence per turn, never cuts a prompt and fails a request when blocks run out
+// (inferrs/src/engine.rs:1380-1912, :2093-2095).  Here every step is one batch under a token budget: decoded
+// tokens first, then portions of running prompts, then admissions, first come first served; when pages run
+// out the youngest running request is preempted and recomputed later.  The scheduler knows requests by number
+// and by their counts only; token ids, sampling options and results stay with the Python front
+// (inferrs_b200/engine/scheduler.py), which says what each call means.
+// ---------------------------------------------------------------------------------------------------------
+namespace {
+
+constexpr int ERR_EMPTY_PROMPT = -20;
+constexpr int ERR_PROMPT_TOO_LONG = -21;
+constexpr int ERR_NEVER_FITS = -22;
+constexpr int ERR_IN_FLIGHT = -23;
+constexpr int ERR_CAPACITY = -24;
+constexpr int ERR_NOT_RUNNING = -25;
+
+enum { WAITING = 0, RUNNING = 1, FINISHED = 2 };
+enum { REASON_NONE = 0, REASON_STOP = 1, REASON_LENGTH = 2 };
+
+struct SchedRequest {
+    int n_prompt = 0, n_output = 0;
+    int n_computed = 0;    // tokens that launched steps have run
+    int n_in_flight = 0;   // tokens that launched steps have sampled and nobody has delivered yet
+    int max_tokens = 0, ignore_eos = 0;
+    std::vector<int> stop_ids;
+    long order = 0;        // arrival number: smaller is older
+    int n_preempted = 0;
+    int state = WAITING;
+    int n_pending() const { return n_prompt + n_output + n_in_flight - n_computed; }
+};
+
+struct Scheduler {
+    Cache* cache = nullptr;
+    int max_batch = 0, budget = 0, chunk = 0, max_positions = 0;
+    std::vector<int> eos;
+    std::unordered_map<int64_t, SchedRequest> requests;
+    std::deque<int64_t> waiting;
+    std::vector<int64_t> running;   // in the order of their admission
+    long arrivals = 0;
+    int n_preemptions = 0;
+
+    SchedRequest* get(int64_t rid) {
+        auto it = requests.find(rid);
+        return it == requests.end() ? nullptr : &it->second;
+    }
+
+    void drop_running(int64_t rid) {
+        for (size_t i = 0; i < running.size(); ++i)
+            if (running[i] == rid) {
+                running.erase(running.begin() + i);
+                return;
+            }
+    }
+
+    int add(int64_t rid, int n_prompt, int max_tokens, int ignore_eos, const int* stop, int n_stop) {
+        if (requests.count(rid)) return ERR_ALREADY_LIVE;
+        if (n_prompt <= 0) return ERR_EMPTY_PROMPT;
+        if (n_prompt >= max_positions) return ERR_PROMPT_TOO_LONG;
+        const int pages = cache->pages_for(n_prompt + 1);
+        for (const Pool& pool : cache->pools)
+            if (pages > pool.n_pages) return ERR_NEVER_FITS;
+        SchedRequest r;
+        r.n_prompt = n_prompt;
+        r.max_tokens = max_tokens;
+        r.ignore_eos = ignore_eos;
+        r.stop_ids.assign(stop, stop + n_stop);
+        r.order = arrivals++;
+        requests.emplace(rid, std::move(r));
+        waiting.push_back(rid);
+        return OK;
+    }
+
+    // 1: it was running (pages and slot are free again), 2: it was waiting, 0: unknown or over already
+    int abort(int64_t rid) {
+        SchedRequest* r = get(rid);
+        if (r == nullptr) return 0;
+        int was = 0;
+        if (r->state == RUNNING) {
+            drop_running(rid);
+            cache->release(rid);
+            was = 1;
+        } else if (r->state == WAITING) {
+            for (size_t i = 0; i < waiting.size(); ++i)
+                if (waiting[i] == rid) {
+                    waiting.erase(waiting.begin() + i);
+                    break;
+                }
+            was = 2;
+        }
+        requests.erase(rid);
+        return was;
+    }
+
+    // The youngest running request other than `keep` gives its pages and slot back and returns to the head of
+    // the waiting queue; everything it has (prompt and generated tokens) is run again later.
+    bool preempt_youngest(int64_t keep, std::vector<int64_t>& preempted) {
+        int64_t victim = -1;
+        long youngest = -1;
+        for (int64_t rid : running) {
+            if (rid == keep) continue;
+            const SchedRequest& r = requests[rid];
+            if (r.order > youngest) {
+                youngest = r.order;
+                victim = rid;
+            }
+        }
+        if (victim < 0) return false;
+        drop_running(victim);
+        cache->release(victim);
+        SchedRequest& v = requests[victim];
+        v.n_computed = 0;
+        v.n_preempted += 1;
+        v.state = WAITING;
+        n_preemptions += 1;
+        waiting.push_front(victim);
+        preempted.push_back(victim);
+        return true;
+    }
+
+    struct Entry {
+        int64_t rid;
+        int start, n, samples;
+    };
+
+    // 0: planned; 1: not planned, because it would take a running request's pages or end one and may_preempt is 0
+    // (nothing has changed then); < 0: an error.
+    int plan(int may_preempt, std::vector<Entry>& out, std::vector<int64_t>& preempted, std::vector<int64_t>& ended,
+             std::vector<int64_t>& admitted) {
+        const int n_groups = (int)cache->pools.size();
+        std::vector<int> free_pages(n_groups), need(n_groups);
+        std::vector<int64_t> order;
+        std::vector<int> counts;
+        while (true) {
+            int left = budget;
+            for (int g = 0; g < n_groups; ++g) free_pages[g] = cache->pools[g].n_free();
+            out.clear();
+            // decoded tokens first, then portions of prompts, oldest first
+            std::vector<int64_t> by_age(running);
+            std::stable_sort(by_age.begin(), by_age.end(),
+                             [&](int64_t a, int64_t b) { return requests[a].order < requests[b].order; });
+            order.clear();
+            for (int64_t rid : by_age)
+                if (requests[rid].n_pending() == 1) order.push_back(rid);
+            for (int64_t rid : by_age)
+                if (requests[rid].n_pending() > 1) order.push_back(rid);
+            counts.clear();
+            for (int64_t rid : order) {
+                if (left <= 0) break;
+                int n = requests[rid].n_pending();
+                if (n > left) n = left;
+                if (n > chunk) n = chunk;
+                counts.push_back(n);
+                left -= n;
+            }
+            order.resize(counts.size());
+            int fitted = 0;
+            if (!order.empty()) {
+                fitted = cache->fit_in_order((int)order.size(), order.data(), counts.data(), free_pages.data());
+                if (fitted < 0) return fitted;
+            }
+            for (int i = 0; i < fitted; ++i) {
+                const SchedRequest& r = requests[order[i]];
+                out.push_back({order[i], r.n_computed, counts[i], counts[i] == r.n_pending() ? 1 : 0});
+            }
+            if (fitted < (int)order.size()) {
+                const int64_t starved = order[fitted];
+                if (!may_preempt) {
+                    out.clear();
+                    return 1;
+                }
+                for (int64_t rid : running)
+                    if (requests[rid].n_in_flight) return ERR_IN_FLIGHT;
+                if (preempt_youngest(starved, preempted)) continue;   // plan again with the pages that came back
+                // the request is alone and still does not fit: it has outgrown the cache
+                drop_running(starved);
+                cache->release(starved);
+                requests.erase(starved);
+                ended.push_back(starved);
+                continue;
+            }
+            // admission, first come first served
+            while (!waiting.empty() && left > 0 && (int)running.size() < max_batch && !cache->free_slots.empty()) {
+                const int64_t rid = waiting.front();
+                SchedRequest& r = requests[rid];
+                int n = r.n_pending();
+                if (n > left) n = left;
+                if (n > chunk) n = chunk;
+                const int slot = cache->admit(rid);
+                if (slot < 0) return slot;
+                cache->pages_needed(*cache->get(rid), n, need.data());
+                bool fits = true;
+                for (int g = 0; g < n_groups; ++g) fits = fits && need[g] <= free_pages[g];
+                if (!fits) {
+                    cache->release(rid);
+                    break;
+                }
+                for (int g = 0; g < n_groups; ++g) free_pages[g] -= need[g];
+                waiting.pop_front();
+                running.push_back(rid);
+                r.state = RUNNING;
+                admitted.push_back(rid);
+                out.push_back({rid, r.n_computed, n, n == r.n_pending() ? 1 : 0});
+                left -= n;
+            }
+            return 0;
+        }
+    }
+
+    int advance(int n, const int64_t* rids, const int* n_tok, const int* samples) {
+        for (int i = 0; i < n; ++i)
+            if (get(rids[i]) == nullptr) return ERR_UNKNOWN_REQUEST;
+        for (int i = 0; i < n; ++i) {
+            SchedRequest& r = requests[rids[i]];
+            r.n_computed += n_tok[i];
+            if (samples[i]) r.n_in_flight += 1;
+        }
+        return OK;
+    }
+
+    int stop_reason(const SchedRequest& r, int token) const {
+        if (!r.ignore_eos) {
+            for (int t : eos)
+                if (t == token) return REASON_STOP;
+            for (int t : r.stop_ids)
+                if (t == token) return REASON_STOP;
+        }
+        if (r.n_output >= r.max_tokens) return REASON_LENGTH;
+        if (r.n_prompt + r.n_output >= max_positions) return REASON_LENGTH;
+        return REASON_NONE;
+    }
+
+    // one sampled token per request named; reasons[i] says whether and why request i is over with it
+    int deliver(int n, const int64_t* rids, const int* tokens, int* reasons) {
+        for (int i = 0; i < n; ++i) {
+            SchedRequest* r = get(rids[i]);
+            if (r == nullptr) return ERR_UNKNOWN_REQUEST;
+            if (r->state != RUNNING || r->n_in_flight <= 0) return ERR_NOT_RUNNING;
+        }
+        for (int i = 0; i < n; ++i) {
+            SchedRequest& r = requests[rids[i]];
+            r.n_in_flight -= 1;
+            r.n_output += 1;
+            reasons[i] = stop_reason(r, tokens[i]);
+            if (reasons[i] != REASON_NONE) {
+                drop_running(rids[i]);
+                cache->release(rids[i]);
+                requests.erase(rids[i]);
+            }
+        }
+        return OK;
+    }
+};
+
+}  // namespace
+
+IBH_EXPORT void* ibh_sched_new(void* cache, int max_batch, int budget, int chunk, int max_positions, const int* eos,
+                               int n_eos) {
+    if (cache == nullptr || max_batch <= 0 || budget <= 0 || chunk <= 0 || n_eos < 0) return nullptr;
+    Scheduler* s = new Scheduler();
+    s->cache = static_cast<Cache*>(cache);
+    s->max_batch = max_batch;
+    s->budget = budget;
+    s->chunk = chunk;
+    s->max_positions = max_positions;
+    s->eos.assign(eos, eos + n_eos);
+    return s;
+}
+
+IBH_EXPORT void ibh_sched_delete(void* h) { delete static_cast<Scheduler*>(h); }
+
+IBH_EXPORT int ibh_sched_add(void* h, int64_t rid, int n_prompt, int max_tokens, int ignore_eos, const int* stop,
+                             int n_stop) {
+    return static_cast<Scheduler*>(h)->add(rid, n_prompt, max_tokens, ignore_eos, stop, n_stop < 0 ? 0 : n_stop);
+}
+
+IBH_EXPORT int ibh_sched_abort(void* h, int64_t rid) { return static_cast<Scheduler*>(h)->abort(rid); }
+
+// The next step.  entries[3 * i ..] = (start, tokens, samples) of request rids[i], for i < *n_entries; then the
+// requests that were preempted, ended ("length": alone and still too large for the cache) and admitted while
+// planning, each list in the order in which it happened.  cap bounds every list.  Returns 0, 1 (not planned:
+// see Scheduler::plan) or an error.
+IBH_EXPORT int ibh_sched_plan(void* h, int may_preempt, int cap, int64_t* rids, int* entries, int* n_entries,
+                              int64_t* preempted, int* n_preempted, int64_t* ended, int* n_ended, int64_t* admitted,
+                              int* n_admitted) {
+    Scheduler* s = static_cast<Scheduler*>(h);
+    std::vector<Scheduler::Entry> out;
+    std::vector<int64_t> pre, end, adm;
+    const int code = s->plan(may_preempt, out, pre, end, adm);
+    *n_entries = *n_preempted = *n_ended = *n_admitted = 0;
+    if (code != 0) return code;
+    if ((int)out.size() > cap || (int)pre.size() > cap || (int)end.size() > cap || (int)adm.size() > cap) return ERR_CAPACITY;
+    for (size_t i = 0; i < out.size(); ++i) {
+        rids[i] = out[i].rid;
+        entries[3 * i] = out[i].start;
+        entries[3 * i + 1] = out[i].n;
+        entries[3 * i + 2] = out[i].samples;
+    }
+    std::copy(pre.begin(), pre.end(), preempted);
+    std::copy(end.begin(), end.end(), ended);
+    std::copy(adm.begin(), adm.end(), admitted);
+    *n_entries = (int)out.size();
+    *n_preempted = (int)pre.size();
+    *n_ended = (int)end.size();
+    *n_admitted = (int)adm.size();
+    return 0;
+}
+
+IBH_EXPORT int ibh_sched_advance(void* h, int n, const int64_t* rids, const int* n_tok, const int* samples) {
+    return static_cast<Scheduler*>(h)->advance(n, rids, n_tok, samples);
+}
+
+IBH_EXPORT int ibh_sched_deliver(void* h, int n, const int64_t* rids, const int* tokens, int* reasons) {
+    return static_cast<Scheduler*>(h)->deliver(n, rids, tokens, reasons);
+}
+
+// counts of one request: out = (n_prompt, n_output, n_computed, n_in_flight, n_preempted, state); -1 if unknown
+IBH_EXPORT int ibh_sched_counts(void* h, int64_t rid, int* out) {
+    SchedRequest* r = static_cast<Scheduler*>(h)->get(rid);
+    if (r == nullptr) return ERR_UNKNOWN_REQUEST;
+    out[0] = r->n_prompt; out[1] = r->n_output; out[2] = r->n_computed; out[3] = r->n_in_flight;
+    out[4] = r->n_preempted; out[5] = r->state;
+    return OK;
+}
+
+IBH_EXPORT int ibh_sched_n_waiting(void* h) { return (int)static_cast<Scheduler*>(h)->waiting.size(); }
+IBH_EXPORT int ibh_sched_n_running(void* h) { return (int)static_cast<Scheduler*>(h)->running.size(); }
+IBH_EXPORT int ibh_sched_n_preemptions(void* h) { return static_cast<Scheduler*>(h)->n_preemptions; }

@@ -16,16 +16,19 @@ its prompt and what it has generated so far as its new prompt (it is recomputed 
 that cannot fit even alone is refused when it is added, or ends with reason "length" when it grows
 to that size.
 
-The scheduler decides only; it owns no device memory and runs no kernel.  It asks the cache manager
-how many pages a plan needs and admits/releases requests there.
+The scheduler decides only; it owns no device memory and runs no kernel.  The decisions are made in native
+code (``csrc/host_runtime.cpp``, beside the cache's book, which it asks how many pages a plan needs and where it
+admits and releases requests); this module is its front: it keeps the requests' tokens, options and results
+and follows what the native scheduler decides.
 """
 from __future__ import annotations
 
+import ctypes
 from collections import deque
 from dataclasses import dataclass, field
 from typing import Deque, Dict, Hashable, List, Optional, Sequence, Tuple
 
-from ..cache.manager import CacheManager
+from ..cache.manager import CacheManager, host_library
 from ..sampling.params import SamplingParams
 
 
@@ -41,6 +44,7 @@ class Request:
     finish_reason: Optional[str] = None
     n_preempted: int = 0
     order: int = 0                  # arrival number: smaller is older
+    handle: int = -1                # the number by which native code knows the request
 
     @property
     def tokens(self) -> List[int]:
@@ -86,6 +90,11 @@ class SchedulerError(ValueError):
 
 
 class Scheduler:
+    _ERRORS = {-20: "the prompt is empty", -21: "the prompt leaves no room within the model's positions",
+               -22: "the prompt does not fit the cache even alone",
+               -23: "a launched step's tokens must be delivered before a plan that may preempt"}
+    _REASONS = {1: "stop", 2: "length"}
+
     def __init__(self, manager: CacheManager, max_batch_size: int, max_tokens_per_step: int,
                  max_positions: int, eos_token_ids: Sequence[int] = (), prefill_chunk: Optional[int] = None):
         if max_batch_size <= 0 or max_tokens_per_step <= 0:
@@ -95,40 +104,73 @@ class Scheduler:
         self.max_tokens_per_step = max_tokens_per_step
         self.prefill_chunk = prefill_chunk or max_tokens_per_step
         self.max_positions = max_positions
-        self.eos_token_ids = tuple(eos_token_ids)
+        self.eos_token_ids = tuple(int(t) for t in eos_token_ids)
         self.waiting: Deque[Request] = deque()
         self.running: List[Request] = []
         self._arrivals = 0
-        self.n_preemptions = 0
+        self._lib = host_library()
+        eos = (ctypes.c_int * max(1, len(self.eos_token_ids)))(*self.eos_token_ids)
+        self._h = self._lib.ibh_sched_new(manager._h, self.max_batch_size, max_tokens_per_step, self.prefill_chunk,
+                                          max_positions, eos, len(self.eos_token_ids))
+        if not self._h:
+            raise SchedulerError("the native scheduler refused these sizes")
+        self._by_handle: Dict[int, Request] = {}
+        self._cap = 0
+        self._grow(max(64, 2 * self.max_batch_size))
+
+    def __del__(self):
+        h, self._h = getattr(self, "_h", None), None
+        if h:
+            self._lib.ibh_sched_delete(h)
+
+    def _grow(self, cap: int):
+        """Room for the lists that a plan returns."""
+        self._cap = cap
+        self._rids = (ctypes.c_int64 * cap)()
+        self._entries = (ctypes.c_int * (3 * cap))()
+        self._lists = [(ctypes.c_int64 * cap)() for _ in range(3)]
+        self._counts = [ctypes.c_int() for _ in range(4)]
+
+    @property
+    def n_preemptions(self) -> int:
+        return self._lib.ibh_sched_n_preemptions(self._h)
 
     # ---- adding and removing --------------------------------------------------
-    def _pages_alone(self, n_tokens: int) -> bool:
-        pages = (n_tokens + self.manager.page_size - 1) // self.manager.page_size
-        return all(pages <= pool.n_pages for pool in self.manager.pools)
-
     def add(self, request: Request):
-        if not request.prompt:
+        p = request.params
+        stop = [int(t) for t in p.stop_token_ids]
+        request.handle = self.manager.new_handle()
+        code = self._lib.ibh_sched_add(self._h, request.handle, len(request.prompt), int(p.max_tokens),
+                                       int(bool(p.ignore_eos)), (ctypes.c_int * max(1, len(stop)))(*stop), len(stop))
+        if code == -20:
             raise SchedulerError(f"request {request.rid!r}: the prompt is empty")
-        if len(request.prompt) >= self.max_positions:
+        if code == -21:
             raise SchedulerError(f"request {request.rid!r}: a prompt of {len(request.prompt)} tokens leaves no room "
                                  f"within the model's {self.max_positions} positions")
-        if not self._pages_alone(len(request.prompt) + 1):
+        if code == -22:
             raise SchedulerError(f"request {request.rid!r}: a prompt of {len(request.prompt)} tokens does not fit "
                                  f"the cache even alone")
+        if code != 0:
+            raise SchedulerError(f"request {request.rid!r}: the native scheduler answered {code}")
         request.order = self._arrivals
         self._arrivals += 1
+        self._by_handle[request.handle] = request
         self.waiting.append(request)
+        if len(self._by_handle) + 8 > self._cap:
+            self._grow(2 * self._cap)
 
     def abort(self, rid: Hashable) -> Optional[Request]:
-        for r in list(self.running):
+        for r in list(self.running) + list(self.waiting):
             if r.rid == rid:
-                self.running.remove(r)
-                self.manager.release(rid)
-                r.finish_reason = "cancelled"
-                return r
-        for r in list(self.waiting):
-            if r.rid == rid:
-                self.waiting.remove(r)
+                was = self._lib.ibh_sched_abort(self._h, r.handle)
+                if was == 1:
+                    self.running.remove(r)
+                    self.manager.forget(rid)
+                elif was == 2:
+                    self.waiting.remove(r)
+                else:
+                    raise SchedulerError(f"request {rid!r}: the native scheduler does not know it")
+                del self._by_handle[r.handle]
                 r.finish_reason = "cancelled"
                 return r
         return None
@@ -138,19 +180,6 @@ class Scheduler:
         return not self.waiting and not self.running
 
     # ---- planning ---------------------------------------------------------------
-    def _preempt_youngest(self, keep: Request) -> bool:
-        victims = [r for r in self.running if r is not keep]
-        if not victims:
-            return False
-        v = max(victims, key=lambda r: r.order)
-        self.running.remove(v)
-        self.manager.release(v.rid)
-        v.n_computed = 0
-        v.n_preempted += 1
-        self.n_preemptions += 1
-        self.waiting.appendleft(v)
-        return True
-
     def plan(self, may_preempt: bool = True) -> Optional[Tuple[List[PlannedEntry], List[Request]]]:
         """(entries of the next step, requests that ended while planning because they outgrew the cache).
 
@@ -159,68 +188,46 @@ class Scheduler:
         request's pages away or ending one (a caller that has a step on its way asks so, reads that step's tokens
         and plans again).
         """
+        c = self._counts
+        code = self._lib.ibh_sched_plan(self._h, int(bool(may_preempt)), self._cap, self._rids, self._entries,
+                                        ctypes.byref(c[0]), self._lists[0], ctypes.byref(c[1]), self._lists[1],
+                                        ctypes.byref(c[2]), self._lists[2], ctypes.byref(c[3]))
+        if code == 1:
+            return None
+        if code in self._ERRORS:
+            raise SchedulerError(self._ERRORS[code])
+        if code != 0:
+            raise SchedulerError(f"plan: the native scheduler answered {code}")
+        # follow what happened, in the order in which it can have happened: preemptions and ends come before
+        # the admissions of the plan that was made in the end
+        for h in self._lists[0][:c[1].value]:
+            v = self._by_handle[h]
+            self.running.remove(v)
+            self.manager.forget(v.rid)
+            v.n_computed = 0
+            v.n_preempted += 1
+            self.waiting.appendleft(v)
         ended: List[Request] = []
-        while True:
-            budget = self.max_tokens_per_step
-            free = [pool.n_free for pool in self.manager.pools]   # pages left once the plan so far is served
-            plan: List[PlannedEntry] = []
-            starved: Optional[Request] = None
-
-            def fits(rid, n) -> bool:
-                need = self.manager.pages_needed(rid, n)
-                if any(need[g] > free[g] for g in range(len(free))):
-                    return False
-                for g in range(len(free)):
-                    free[g] -= need[g]
-                return True
-
-            by_age = sorted(self.running, key=lambda r: r.order)
-            # decoded tokens first, then portions of prompts, oldest first
-            order = [r for r in by_age if r.n_pending == 1] + [r for r in by_age if r.n_pending > 1]
-            counts = []
-            for r in order:
-                if budget <= 0:
-                    break
-                n = min(r.n_pending, budget, self.prefill_chunk)
-                counts.append(n)
-                budget -= n
-            order = order[:len(counts)]
-            fitted = self.manager.fit_in_order([r.rid for r in order], counts, free) if order else 0
-            for r, n in zip(order[:fitted], counts[:fitted]):
-                plan.append(PlannedEntry(r, r.n_computed, n, n == r.n_pending))
-            if fitted < len(order):
-                starved = order[fitted]
-                budget += sum(counts[fitted:])
-            if starved is not None:
-                if not may_preempt:
-                    return None
-                if any(r.n_in_flight for r in self.running):
-                    raise SchedulerError("a launched step's tokens must be delivered before a plan that may preempt")
-                if self._preempt_youngest(keep=starved):
-                    continue  # plan again with the pages that came back
-                # the request is alone and still does not fit: it has outgrown the cache
-                self.running.remove(starved)
-                self.manager.release(starved.rid)
-                starved.finish_reason = "length"
-                ended.append(starved)
-                continue
-            # admission, first come first served
-            while self.waiting and budget > 0 and len(self.running) < self.max_batch_size \
-                    and self.manager.n_free_slots > 0:
-                r = self.waiting[0]
-                n = min(r.n_pending, budget, self.prefill_chunk)
-                self.manager.admit(r.rid)
-                if not fits(r.rid, n):
-                    self.manager.release(r.rid)
-                    break
-                self.waiting.popleft()
-                self.running.append(r)
-                plan.append(PlannedEntry(r, r.n_computed, n, n == r.n_pending))
-                budget -= n
-            return plan, ended
+        for h in self._lists[1][:c[2].value]:
+            r = self._by_handle.pop(h)
+            self.running.remove(r)
+            self.manager.forget(r.rid)
+            r.finish_reason = "length"
+            ended.append(r)
+        for h in self._lists[2][:c[3].value]:
+            r = self.waiting.popleft()
+            if r.handle != h:
+                raise SchedulerError("the front and the native scheduler disagree about the waiting queue")
+            self.manager.adopt(r.rid, h)
+            self.running.append(r)
+        e = self._entries
+        plan = [PlannedEntry(self._by_handle[self._rids[i]], e[3 * i], e[3 * i + 1], bool(e[3 * i + 2]))
+                for i in range(c[0].value)]
+        return plan, ended
 
     # ---- after the step ---------------------------------------------------------
     def stop_reason(self, r: Request, token: int) -> Optional[str]:
+        """Why the request is over once ``token`` has been added to its output (None: it goes on)."""
         if not r.params.ignore_eos and (token in self.eos_token_ids or token in r.params.stop_token_ids):
             return "stop"
         if len(r.output) >= r.params.max_tokens:
@@ -232,6 +239,14 @@ class Scheduler:
     def advance(self, plan: Sequence[PlannedEntry]):
         """The planned step has been launched: its tokens count as run, and every entry that samples has a token on
         its way that the host does not know yet."""
+        n = len(plan)
+        if n == 0:
+            return
+        code = self._lib.ibh_sched_advance(self._h, n, (ctypes.c_int64 * n)(*[e.request.handle for e in plan]),
+                                           (ctypes.c_int * n)(*[e.n for e in plan]),
+                                           (ctypes.c_int * n)(*[int(e.samples) for e in plan]))
+        if code != 0:
+            raise SchedulerError(f"advance: the native scheduler answered {code}")
         for e in plan:
             e.request.n_computed += e.n
             if e.samples:
@@ -240,20 +255,27 @@ class Scheduler:
     def deliver(self, plan: Sequence[PlannedEntry], sampled: Sequence[int]) -> List[Request]:
         """The tokens of a launched step have arrived: ``sampled`` holds one per planned entry with ``samples``,
         in plan order.  Returns the requests that finished; their pages and slots are free again."""
+        sampling = [e.request for e in plan if e.samples]
+        n = len(sampling)
+        if n == 0:
+            return []
+        tokens = [int(t) for t in sampled]
+        if len(tokens) != n:
+            raise SchedulerError(f"deliver: {len(tokens)} tokens for {n} entries that sample")
+        reasons = (ctypes.c_int * n)()
+        code = self._lib.ibh_sched_deliver(self._h, n, (ctypes.c_int64 * n)(*[r.handle for r in sampling]),
+                                           (ctypes.c_int * n)(*tokens), reasons)
+        if code != 0:
+            raise SchedulerError(f"deliver: the native scheduler answered {code}")
         finished: List[Request] = []
-        it = iter(sampled)
-        for e in plan:
-            if not e.samples:
-                continue
-            r = e.request
-            tok = int(next(it))
+        for r, tok, reason in zip(sampling, tokens, reasons):
             r.n_in_flight -= 1
             r.output.append(tok)
-            reason = self.stop_reason(r, tok)
-            if reason is not None:
-                r.finish_reason = reason
+            if reason:
+                r.finish_reason = self._REASONS[reason]
                 self.running.remove(r)
-                self.manager.release(r.rid)
+                self.manager.forget(r.rid)
+                del self._by_handle[r.handle]
                 finished.append(r)
         return finished
 
@@ -261,3 +283,17 @@ class Scheduler:
         """Record a step whose tokens are known: :meth:`advance` and :meth:`deliver` in one."""
         self.advance(plan)
         return self.deliver(plan, sampled)
+
+    def check(self):
+        """The front's view of every request against the native scheduler's (for tests)."""
+        out = (ctypes.c_int * 6)()
+        for state, group in ((0, self.waiting), (1, self.running)):
+            for r in group:
+                if self._lib.ibh_sched_counts(self._h, r.handle, out) != 0:
+                    raise SchedulerError(f"request {r.rid!r} is unknown to the native scheduler")
+                mine = (len(r.prompt), len(r.output), r.n_computed, r.n_in_flight, r.n_preempted, state)
+                if tuple(out) != mine:
+                    raise SchedulerError(f"request {r.rid!r}: front {mine}, native {tuple(out)}")
+        if (self._lib.ibh_sched_n_waiting(self._h), self._lib.ibh_sched_n_running(self._h)) != \
+                (len(self.waiting), len(self.running)):
+            raise SchedulerError("the front and the native scheduler count their requests differently")

@@ -206,3 +206,98 @@ def test_a_plan_that_would_preempt_is_not_made_while_a_step_is_on_its_way():
     young = p1[1].request
     assert young in s.waiting and young.n_computed == 0 and young.output == [4, 6] and young.n_in_flight == 0
     m.check_invariants()
+
+
+@pytest.mark.parametrize("seed", range(6))
+def test_the_native_scheduler_decides_as_the_plain_model_does(seed):
+    """Random requests (lengths, token limits, stop tokens), random sampled tokens, a cache so small that requests
+    are preempted and some outgrow it, aborts, and steps launched one ahead: the native scheduler over the native
+    cache book and the plain Python model over the plain book must make the same plans, end the same requests
+    for the same reasons and hand out the same pages."""
+    import random
+    import plain_cache
+    import plain_scheduler
+    rng = random.Random(seed)
+    page_size, n_pages, slots = rng.choice([(4, 24, 5), (8, 10, 4), (4, 40, 3)])
+    budget, chunk, max_batch = rng.choice([(16, None, 4), (24, 8, 5), (9, 5, 3)])
+    max_positions, eos = 90, (3,)
+    m = CacheManager([GroupLayout("full")], page_size, [n_pages], slots)
+    s = Scheduler(m, max_batch, budget, max_positions, eos, chunk)
+    pm = plain_cache.CacheManager([plain_cache.GroupLayout("full")], page_size, [n_pages], slots)
+    ps = plain_scheduler.Scheduler(pm, max_batch, budget, max_positions, eos, chunk)
+
+    def new_request(i):
+        n = rng.choice([1, 2, 5, 9, 17, 30, 60])
+        params = SamplingParams(temperature=0.0, max_tokens=rng.choice([1, 3, 8, 40]),
+                                stop_token_ids=rng.choice([(), (5,), (5, 6)]), ignore_eos=rng.random() < 0.2)
+        prompt = [rng.randrange(10) for _ in range(n)]
+        return (Request(i, list(prompt), params, seed=0), plain_scheduler.Request(i, list(prompt), params, seed=0))
+
+    def shape_of(plan):
+        return [(e.request.rid, e.start, e.n, e.samples) for e in plan]
+
+    def launch_both(may_preempt):
+        a, b = s.plan(may_preempt=may_preempt), ps.plan(may_preempt=may_preempt)
+        assert (a is None) == (b is None)
+        if a is None:
+            return None
+        (plan, ended), (pplan, pended) = a, b
+        assert shape_of(plan) == shape_of(pplan)
+        assert [(r.rid, r.finish_reason) for r in ended] == [(r.rid, r.finish_reason) for r in pended]
+        for mgr, pl in ((m, plan), (pm, pplan)):
+            if pl:
+                mgr.reserve({e.request.rid: e.n for e in pl})
+                for e in pl:
+                    mgr.commit(e.request.rid, e.n)
+        s.advance(plan)
+        ps.advance(pplan)
+        for e in plan:
+            assert list(m.block_table(e.request.rid, 0)) == list(pm.block_table(e.request.rid, 0))
+        return plan, pplan
+
+    def deliver_both(step):
+        plan, pplan = step
+        alive = [e for e in plan if e.request.finish_reason is None]
+        palive = [e for e in pplan if e.request.finish_reason is None]
+        tokens = [rng.randrange(10) for e in alive if e.samples]
+        fin, pfin = s.deliver(alive, tokens), ps.deliver(palive, tokens)
+        assert [(r.rid, r.finish_reason, r.output) for r in fin] == [(r.rid, r.finish_reason, r.output) for r in pfin]
+
+    n_added, in_flight, n_ahead = 0, None, 0
+    for turn in range(300):
+        if n_added < 40 and rng.random() < 0.35:
+            a, b = new_request(n_added)
+            try:
+                s.add(a)
+                refused = False
+            except SchedulerError:
+                refused = True
+            if refused:
+                with pytest.raises(plain_scheduler.SchedulerError):
+                    ps.add(b)
+            else:
+                ps.add(b)
+            n_added += 1
+        if rng.random() < 0.04 and (s.running or s.waiting):
+            victim = rng.choice([r.rid for r in list(s.running) + list(s.waiting)])
+            assert s.abort(victim).finish_reason == ps.abort(victim).finish_reason == "cancelled"
+        # as the engine does: the next step is launched before the last one's tokens are delivered where that can
+        # be; else the tokens come first
+        step = None
+        if in_flight is not None and rng.random() < 0.8:
+            step = launch_both(may_preempt=False)
+            n_ahead += step is not None
+        if in_flight is not None:
+            deliver_both(in_flight)
+            in_flight = None
+        if step is None:
+            step = launch_both(may_preempt=True)
+        in_flight = step if step and step[0] else None
+        s.check()
+        m.check_invariants()
+        pm.check_invariants()
+        assert [r.rid for r in s.running] == [r.rid for r in ps.running]
+        assert [r.rid for r in s.waiting] == [r.rid for r in ps.waiting]
+        assert s.n_preemptions == ps.n_preemptions
+        assert m.pools[0].n_free == pm.pools[0].n_free
+    assert n_ahead > 20 and n_added == 40
