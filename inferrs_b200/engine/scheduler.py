@@ -226,16 +226,6 @@ class Scheduler:
         return plan, ended
 
     # ---- after the step ---------------------------------------------------------
-    def stop_reason(self, r: Request, token: int) -> Optional[str]:
-        """Why the request is over once ``token`` has been added to its output (None: it goes on)."""
-        if not r.params.ignore_eos and (token in self.eos_token_ids or token in r.params.stop_token_ids):
-            return "stop"
-        if len(r.output) >= r.params.max_tokens:
-            return "length"
-        if len(r.prompt) + len(r.output) >= self.max_positions:
-            return "length"
-        return None
-
     def advance(self, plan: Sequence[PlannedEntry]):
         """The planned step has been launched: its tokens count as run, and every entry that samples has a token on
         its way that the host does not know yet."""
