@@ -18,10 +18,13 @@
 #include <cuda.h>
 
 #include "common.cuh"
+#include "sm100.cuh"
 
 #if IB_ACT_BF16
 
 namespace sk {
+
+using namespace sm100;
 
 constexpr int BM = 128;
 constexpr int BK = 64;
@@ -31,72 +34,11 @@ constexpr int A_BYTES = BM * BK * 2;
 
 __device__ int g_error = 0;
 
-__device__ __forceinline__ unsigned smem_u32(const void* p) { return (unsigned)__cvta_generic_to_shared(p); }
-__device__ __forceinline__ void mbar_init(unsigned bar, unsigned count) {
-    asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(bar), "r"(count));
+// a bounded wait that reports through this file's error word
+__device__ __forceinline__ bool mbar_wait(unsigned bar, unsigned parity, int code) {
+    return mbar_wait_bounded(bar, parity, &g_error, code);
 }
-__device__ __forceinline__ void mbar_expect_tx(unsigned bar, unsigned bytes) {
-    asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(bar), "r"(bytes) : "memory");
-}
-__device__ __forceinline__ void mbar_arrive(unsigned bar) {
-    asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(bar) : "memory");
-}
-__device__ __forceinline__ bool mbar_try_wait(unsigned bar, unsigned parity) {
-    unsigned ok;
-    asm volatile("{\n\t.reg .pred p;\n\tmbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\tselp.u32 %0, 1, 0, p;\n\t}"
-                 : "=r"(ok) : "r"(bar), "r"(parity) : "memory");
-    return ok != 0;
-}
-__device__ __forceinline__ unsigned long long global_ns() {
-    unsigned long long t;
-    asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t));
-    return t;
-}
-__device__ __noinline__ bool mbar_wait(unsigned bar, unsigned parity, int code) {
-    if (mbar_try_wait(bar, parity)) return true;
-    const unsigned long long t0 = global_ns();
-    for (unsigned it = 1;; ++it) {
-        if (mbar_try_wait(bar, parity)) return true;
-        if ((it & 1023u) == 0 && global_ns() - t0 > 2000000000ull) {
-            atomicCAS(&g_error, 0, code);
-            return false;
-        }
-    }
-}
-__device__ __forceinline__ void tma_load_2d(unsigned dst, const CUtensorMap* map, int x, int y, unsigned bar) {
-    asm volatile("cp.async.bulk.tensor.2d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4}], [%2];"
-                 ::"r"(dst), "l"(map), "r"(bar), "r"(x), "r"(y) : "memory");
-}
-__device__ __forceinline__ unsigned long long smem_desc(unsigned addr) {
-    unsigned long long d = 0;
-    d |= (unsigned long long)((addr & 0x3FFFF) >> 4);
-    d |= (unsigned long long)1 << 16;
-    d |= (unsigned long long)(1024 >> 4) << 32;
-    d |= (unsigned long long)1 << 46;
-    d |= (unsigned long long)2 << 61;
-    return d;
-}
-__device__ __forceinline__ void umma(unsigned tmem_d, unsigned long long a, unsigned long long b, unsigned idesc,
-                                     unsigned accumulate) {
-    asm volatile("{\n\t.reg .pred p;\n\tsetp.ne.b32 p, %4, 0;\n\t"
-                 "tcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, {%5, %6, %7, %8}, p;\n\t}"
-                 ::"r"(tmem_d), "l"(a), "l"(b), "r"(idesc), "r"(accumulate), "r"(0), "r"(0), "r"(0), "r"(0) : "memory");
-}
-__device__ __forceinline__ void umma_commit(unsigned bar) {
-    asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(bar) : "memory");
-}
-__device__ __forceinline__ void tmem_ld16(unsigned taddr, float (&v)[16]) {
-    unsigned r[16];
-    asm volatile("tcgen05.ld.sync.aligned.32x32b.x16.b32 {%0,%1,%2,%3,%4,%5,%6,%7,%8,%9,%10,%11,%12,%13,%14,%15}, [%16];"
-                 : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7]),
-                   "=r"(r[8]), "=r"(r[9]), "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]), "=r"(r[14]), "=r"(r[15])
-                 : "r"(taddr));
-    asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
-#pragma unroll
-    for (int i = 0; i < 16; ++i) v[i] = __uint_as_float(r[i]);
-}
-__device__ __forceinline__ void fence_before() { asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory"); }
-__device__ __forceinline__ void fence_after() { asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory"); }
+
 __device__ __forceinline__ void epilogue_sync() { asm volatile("bar.sync 1, 128;" ::: "memory"); }  // warps 2..5
 __device__ __forceinline__ int ld_acquire(const int* p) {
     int v;
@@ -178,8 +120,8 @@ __global__ void __launch_bounds__(THREADS, 1) streamk_kernel(const __grid_consta
                 if (first && seg >= 2 && !mbar_wait(acce0 + 8 * buf, (unsigned)((seg >> 1) - 1) & 1, 4)) { ok = false; break; }
                 if (!mbar_wait(full0 + 8 * s, (unsigned)(i / STAGES) & 1, 2)) { ok = false; break; }
                 fence_after();
-                const unsigned long long da = smem_desc(smem_u32(a_tiles + s * A_BYTES));
-                const unsigned long long db = smem_desc(smem_u32(b_tiles + s * B_BYTES));
+                const unsigned long long da = desc_k_major(smem_u32(a_tiles + s * A_BYTES));
+                const unsigned long long db = desc_k_major(smem_u32(b_tiles + s * B_BYTES));
 #pragma unroll
                 for (int k = 0; k < BK / UMMA_K; ++k)
                     umma(tmem + buf * BN, da + (unsigned long long)(k * UMMA_K * 2 / 16),
@@ -305,22 +247,6 @@ __global__ void __launch_bounds__(THREADS, 1) streamk_kernel(const __grid_consta
         fence_after();
         asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem), "r"(TMEM_COLS) : "memory");
     }
-}
-
-typedef CUresult (*EncodeTiled)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*, const cuuint64_t*,
-                                const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave, CUtensorMapSwizzle,
-                                CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
-
-static EncodeTiled encode_fn() {
-    static EncodeTiled fn = nullptr;
-    if (fn == nullptr) {
-        void* sym = nullptr;
-        cudaDriverEntryPointQueryResult q;
-        if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &sym, cudaEnableDefault, &q) == cudaSuccess &&
-            q == cudaDriverEntryPointSuccess)
-            fn = reinterpret_cast<EncodeTiled>(sym);
-    }
-    return fn;
 }
 
 static bool make_map(CUtensorMap* map, const void* base, long rows, long k, long ld, int box_rows) {
