@@ -62,6 +62,13 @@ __device__ __forceinline__ float ex2(float x) {   // 2^x, one instruction; 2^-in
     return y;
 }
 
+#ifdef IB_ATTN_EVENTS
+__device__ long long g_ev[64 * 32];   // [event code][key tile]: clock64 of the chosen CTA's chosen lanes
+#define EV(code, i) do { if (rec && (i) < 32) g_ev[(code) * 32 + (i)] = clock64(); } while (0)
+#else
+#define EV(code, i) do { } while (0)
+#endif
+
 struct Params {
     const int* block_table;   // [R, max_pages]
     const int* tile_req;      // [tiles]
@@ -97,6 +104,9 @@ __global__ void __launch_bounds__(THREADS, 1) attention_kernel(const __grid_cons
 
     ib_grid_dependency_sync();
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+#ifdef IB_ATTN_EVENTS
+    const bool rec = blockIdx.x == 0 && blockIdx.y == 0 && lane == 0 && (warp == 0 || warp == 4 || warp >= 8);
+#endif
     // the last tiles of a prompt see the most keys: they are started first, so that the grid's tail is short
     const int tile = gridDim.x - 1 - blockIdx.x, kvh = blockIdx.y;
     const int req = P.tile_req[tile], row0 = P.tile_row0[tile];
@@ -173,11 +183,13 @@ __global__ void __launch_bounds__(THREADS, 1) attention_kernel(const __grid_cons
                 if (i + 1 >= 2 && ok && !mbar_wait(k_empty0 + 8 * ((i + 1) & 1), (((i + 1) >> 1) - 1) & 1, 1)) ok = false;
                 ok = __all_sync(0xffffffffu, ok);
                 if (!ok) break;
+                EV(10, i + 1);
                 load_tile(i + 1, page_k, true);
             }
             if (i >= 2 && ok && !mbar_wait(v_empty0 + 8 * (i & 1), ((i >> 1) - 1) & 1, 1)) ok = false;
             ok = __all_sync(0xffffffffu, ok);
             if (!ok) break;
+            EV(11, i);
             load_tile(i, page_v, false);
             page_v = page_k;
         }
@@ -209,11 +221,15 @@ __global__ void __launch_bounds__(THREADS, 1) attention_kernel(const __grid_cons
                     if (!mbar_wait(k_full0 + 8 * s1, ((i + 1) >> 1) & 1, 2)) { ok = false; break; }
                     if (i + 1 >= 2 && !mbar_wait(s_empty0 + 8 * s1, (((i + 1) >> 1) - 1) & 1, 3)) { ok = false; break; }
                     fence_after();
+                    EV(20, i + 1);
                     issue_qk(i + 1);
                 }
+                EV(21, i);
                 if (!mbar_wait(p_full0 + 8 * s, (i >> 1) & 1, 4)) { ok = false; break; }
+                EV(22, i);
                 if (!mbar_wait(v_full0 + 8 * s, (i >> 1) & 1, 2)) { ok = false; break; }
                 fence_after();
+                EV(23, i);
 #pragma unroll
                 for (int k = 0; k < KEYS / 16; ++k) {
                     const unsigned aoff = (k >> 2) * HALF_BYTES + (k & 3) * 32;   // P: K-major, 16 keys = 32 bytes
@@ -223,6 +239,7 @@ __global__ void __launch_bounds__(THREADS, 1) attention_kernel(const __grid_cons
                 }
                 umma_commit(pv_full0 + 8 * s);
                 umma_commit(v_empty0 + 8 * s);    // V(i) is free once these products are done
+                EV(24, i);
             }
         }
     } else if (warp < 8) {
@@ -253,13 +270,16 @@ __global__ void __launch_bounds__(THREADS, 1) attention_kernel(const __grid_cons
         // partner at the named barrier the same number of times; the output is not stored then.
         for (int i = 0; i < n_tiles; ++i) {
             const int s = i & 1;
+            EV(30 + ch, i);
             if (ok && !mbar_wait(s_full0 + 8 * s, (i >> 1) & 1, 5)) ok = false;
             fence_after();
+            EV(32 + ch, i);
             const int key0 = (t_begin + i) * KEYS + ch * 64;
             unsigned a[32], b[32];
             tmem_ld32_issue(tmem + lane_addr + s * 128 + ch * 64, a);
             tmem_ld32_issue(tmem + lane_addr + s * 128 + ch * 64 + 32, b);
             tmem_ld_wait();
+            EV(34 + ch, i);
             // a tile whose 64 keys this row sees in full needs no comparisons (all tiles but the first and last few)
             const bool all_visible = key0 >= lo && key0 + 63 <= pos;
             // (four running maxima, and four running sums below: one chain of 64 dependent operations would
@@ -284,7 +304,9 @@ __global__ void __launch_bounds__(THREADS, 1) attention_kernel(const __grid_cons
             // tile's barrier, which this thread passes before it writes that buffer again two tiles on)
             float* xb = xchg + (i & 1) * 256;
             xb[ch * 128 + r] = mx;
+            EV(36 + ch, i);
             pair_sync(warp & 3);
+            EV(38 + ch, i);
             mx = fmaxf(mx, xb[(ch ^ 1) * 128 + r]) * P.scale_log2;
             const float m_new = fmaxf(m, mx);
             const float m_safe = m_new == -INFINITY ? 0.0f : m_new;
@@ -313,12 +335,15 @@ __global__ void __launch_bounds__(THREADS, 1) attention_kernel(const __grid_cons
             asm volatile("fence.proxy.async.shared::cta;" ::: "memory");   // generic writes -> the tensor core's reads
             __syncwarp();
             if (lane == 0) { mbar_arrive(s_empty0 + 8 * s); mbar_arrive(p_full0 + 8 * s); }
+            EV(40 + ch, i);
             // the product of the tile before this one has had this tile's softmax to finish
             if (i > 0) {
                 if (ok && !mbar_wait(pv_full0 + 8 * ((i - 1) & 1), ((i - 1) >> 1) & 1, 6)) ok = false;
                 fence_after();
+                EV(42 + ch, i);
                 add_product(i - 1, corr_pending);
                 fence_before();
+                EV(44 + ch, i);
             }
             corr_pending = corr;
         }
@@ -362,6 +387,15 @@ __global__ void __launch_bounds__(THREADS, 1) attention_kernel(const __grid_cons
     }
 }
 
+#ifdef IB_ATTN_EVENTS
+}  // namespace fa
+IB_EXPORT int ib_attention_events(long long* dst, int cap) {
+    if (cap < 64 * 32) return -1;
+    cudaMemcpyFromSymbol(dst, fa::g_ev, sizeof(long long) * 64 * 32);
+    return 64 * 32;
+}
+namespace fa {
+#endif
 }  // namespace fa
 
 // Prefill-form attention for head size 128, bfloat16: tile i holds up to 128/G tokens of request tile_req[i]
