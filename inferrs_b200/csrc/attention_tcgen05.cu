@@ -15,8 +15,9 @@
 // is a contiguous [page_size, 128] block) into a two-stage ring.  V is used as the MN-major operand of
 // the second product, so no transposed copy of the cache is needed.
 //
-// Warps 0..7: softmax and output (warp w: lanes 32 (w % 4).., columns 64 (w / 4)..); warp 8: TMA producer;
-// warp 9: MMA issuer and owner of the tensor-memory allocation.  All mbarrier waits are bounded (about two seconds)
+// Warps 0..7: softmax and output (warp w: lanes 32 (w % 4).., columns 64 (w / 4)..); warp 8: TMA producer of
+// Q and K; warp 9: issuer of Q K^T and owner of the tensor-memory allocation; warp 10: TMA producer of V; warp
+// 11: issuer of P V.  All mbarrier waits are bounded (about two seconds)
 // and report through the library's error word.
 #include <cuda.h>
 
@@ -32,7 +33,7 @@ using namespace sm100;
 constexpr int D = 128;            // head size
 constexpr int ROWS = 128;         // query rows per CTA
 constexpr int KEYS = 128;         // keys per tile
-constexpr int THREADS = 320;
+constexpr int THREADS = 384;
 constexpr int SMEM_SLACK = 512;   // bytes that the 1 KB alignment of the tiles may cost (the base is asked to be aligned)
 constexpr int HALF_BYTES = 128 * 128;          // a [128 rows][64 elements] swizzled sub-tile
 constexpr int TILE_BYTES = 2 * HALF_BYTES;     // Q, K, V or P tile: 128 x 128 bfloat16
@@ -141,10 +142,10 @@ __global__ void __launch_bounds__(THREADS, 1) attention_kernel(const __grid_cons
     const unsigned tmem = *tmem_slot;      // columns 0..127 S0, 128..255 S1, 256..383 PV0, 384..511 PV1
     bool ok = true;
 
-    if (warp == 8) {
-        // TMA producer.  Lane 0 brings the queries; lane p brings page p of every key tile (four boxes: two
-        // 64-column halves of K and of V), and looks the page up one tile ahead of its use.
-        if (lane == 0) {
+    if (warp == 8 || warp == 10) {
+        // TMA producers: warp 8 brings the queries and the key tiles, warp 10 the value tiles.  Lane p brings page
+        // p of every tile (two boxes: the 64-column halves) and looks the page up one tile ahead of its use.
+        if (warp == 8 && lane == 0) {
             mbar_expect_tx(q_full, TILE_BYTES);   // [tokens][G heads][128] as two 64-column halves
             tma_load_3d(smem_u32(sq), &map_q, 0, kvh * G, row0, q_full);
             tma_load_3d(smem_u32(sq + HALF_BYTES), &map_q, 64, kvh * G, row0, q_full);
@@ -158,8 +159,6 @@ __global__ void __launch_bounds__(THREADS, 1) attention_kernel(const __grid_cons
             if (page < 0 || page >= P.n_pages) page = 0;   // never seen by a query; any finite data will do
             return page;
         };
-        // Keys run one tile ahead of values: K(i) is free again as soon as the scores of tile i - 2 are done,
-        // V(i) only after the second product of tile i - 2, and the scores of a tile are issued a tile early.
         auto load_tile = [&](int i, int page, bool keys) {
             const int s = i & 1;
             const unsigned full = (keys ? k_full0 : v_full0) + 8 * s;
@@ -173,33 +172,36 @@ __global__ void __launch_bounds__(THREADS, 1) attention_kernel(const __grid_cons
                 tma_load_2d(smem_u32(dst + HALF_BYTES) + off, keys ? &map_k : &map_v, 64, grow, full);
             }
         };
-        // order: K(0), then for every i: K(i + 1), V(i)
-        int page_k = n_tiles > 0 ? lookup(0) : 0;
-        if (n_tiles > 0) load_tile(0, page_k, true);
-        int page_v = page_k;
+        // The key tiles and the value tiles are asked for by a warp each: asking for a tile is sixteen pages of
+        // two boxes, about as long as the products of a tile take.  Keys run a tile ahead: K(i) is free again as
+        // soon as the scores of tile i - 2 are done, V(i) only after the second product of tile i - 2.
+        const bool keys = warp == 8;
+        const unsigned empty0 = keys ? k_empty0 : v_empty0;
+        int page = n_tiles > 0 ? lookup(0) : 0;
         for (int i = 0; i < n_tiles; ++i) {
-            if (i + 1 < n_tiles) {
-                page_k = lookup(i + 1);
-                if (i + 1 >= 2 && ok && !mbar_wait(k_empty0 + 8 * ((i + 1) & 1), (((i + 1) >> 1) - 1) & 1, 1)) ok = false;
-                ok = __all_sync(0xffffffffu, ok);
-                if (!ok) break;
-                EV(10, i + 1);
-                load_tile(i + 1, page_k, true);
-            }
-            if (i >= 2 && ok && !mbar_wait(v_empty0 + 8 * (i & 1), ((i >> 1) - 1) & 1, 1)) ok = false;
+            const int page_next = i + 1 < n_tiles ? lookup(i + 1) : 0;
+            if (i >= 2 && ok && !mbar_wait(empty0 + 8 * (i & 1), ((i >> 1) - 1) & 1, 1)) ok = false;
             ok = __all_sync(0xffffffffu, ok);
             if (!ok) break;
-            EV(11, i);
-            load_tile(i, page_v, false);
-            page_v = page_k;
+            EV(keys ? 10 : 11, i);
+            load_tile(i, page, keys);
+            page = page_next;
         }
-    } else if (warp == 9) {
-        if (lane == 0) {
-            // both products: M = 128, N = 128, bfloat16 in, float32 out; the second takes V as MN-major B
-            const unsigned idesc_qk = (1u << 4) | (1u << 7) | (1u << 10) | ((unsigned)(KEYS >> 3) << 17) | ((unsigned)(ROWS >> 4) << 24);
-            const unsigned idesc_pv = idesc_qk | (1u << 16);
-            auto issue_qk = [&](int i) {   // S(i) = Q K(i)^T into buffer i & 1
+    } else if (warp == 9 || warp == 11) {
+        // The two products of a tile are issued by a thread each (warp 9: S = Q K^T, warp 11: P V): a thread that
+        // issues is held at the pace of the tensor pipe, and every wait on a barrier costs it a few hundred
+        // cycles; one thread for both left the pipe idle two thirds of the time.
+        // Both products: M = 128, N = 128, bfloat16 in, float32 out; the second takes V as MN-major B.
+        const unsigned idesc_qk = (1u << 4) | (1u << 7) | (1u << 10) | ((unsigned)(KEYS >> 3) << 17) | ((unsigned)(ROWS >> 4) << 24);
+        const unsigned idesc_pv = idesc_qk | (1u << 16);
+        if (warp == 9 && lane == 0) {
+            for (int i = 0; i < n_tiles; ++i) {   // S(i) = Q K(i)^T into buffer i & 1, a tile ahead of its softmax
                 const int s = i & 1;
+                if (i == 0 && !mbar_wait(q_full, 0, 2)) { ok = false; break; }
+                if (!mbar_wait(k_full0 + 8 * s, (i >> 1) & 1, 2)) { ok = false; break; }
+                if (i >= 2 && !mbar_wait(s_empty0 + 8 * s, ((i >> 1) - 1) & 1, 3)) { ok = false; break; }
+                fence_after();
+                EV(20, i);
 #pragma unroll
                 for (int k = 0; k < D / 16; ++k) {
                     const unsigned off = (k >> 2) * HALF_BYTES + (k & 3) * 32;
@@ -208,22 +210,10 @@ __global__ void __launch_bounds__(THREADS, 1) attention_kernel(const __grid_cons
                 }
                 umma_commit(s_full0 + 8 * s);
                 umma_commit(k_empty0 + 8 * s);   // K(i) is free once these products are done
-            };
-            if (n_tiles > 0) {
-                ok = mbar_wait(q_full, 0, 2) && mbar_wait(k_full0, 0, 2);
-                fence_after();
-                if (ok) issue_qk(0);
             }
-            for (int i = 0; i < n_tiles && ok; ++i) {
+        } else if (warp == 11 && lane == 0) {
+            for (int i = 0; i < n_tiles; ++i) {
                 const int s = i & 1;
-                if (i + 1 < n_tiles) {     // the next tile's scores, while this tile's softmax runs
-                    const int s1 = (i + 1) & 1;
-                    if (!mbar_wait(k_full0 + 8 * s1, ((i + 1) >> 1) & 1, 2)) { ok = false; break; }
-                    if (i + 1 >= 2 && !mbar_wait(s_empty0 + 8 * s1, (((i + 1) >> 1) - 1) & 1, 3)) { ok = false; break; }
-                    fence_after();
-                    EV(20, i + 1);
-                    issue_qk(i + 1);
-                }
                 EV(21, i);
                 if (!mbar_wait(p_full0 + 8 * s, (i >> 1) & 1, 4)) { ok = false; break; }
                 EV(22, i);
