@@ -34,8 +34,8 @@ __device__ __forceinline__ unsigned long long global_ns() {
 }
 // A wait with a limit of about two seconds: when it runs out, `code` is recorded in *error_word (if that still
 // holds 0) and false comes back; the caller then leaves its loops, lets outstanding copies land and returns.
-static __device__ __noinline__ bool mbar_wait_bounded(unsigned bar, unsigned parity, int* error_word, int code) {
-    if (mbar_try_wait(bar, parity)) return true;
+// A barrier that has completed already costs one inlined test and no call.
+static __device__ __noinline__ bool mbar_wait_slow(unsigned bar, unsigned parity, int* error_word, int code) {
     const unsigned long long t0 = global_ns();
     for (unsigned it = 1;; ++it) {
         if (mbar_try_wait(bar, parity)) return true;
@@ -44,6 +44,10 @@ static __device__ __noinline__ bool mbar_wait_bounded(unsigned bar, unsigned par
             return false;
         }
     }
+}
+__device__ __forceinline__ bool mbar_wait_bounded(unsigned bar, unsigned parity, int* error_word, int code) {
+    if (mbar_try_wait(bar, parity)) return true;
+    return mbar_wait_slow(bar, parity, error_word, code);
 }
 
 // ---- bulk tensor copies into shared memory; x is the innermost coordinate (x * element size: a multiple of 16 bytes)
