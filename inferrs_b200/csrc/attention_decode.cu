@@ -263,6 +263,7 @@ __global__ void __launch_bounds__(THREADS, 2) decode_kernel(const __grid_constan
 #pragma unroll
         for (int h = 0; h < 2; ++h) {
             const int r = gid + 8 * h;
+            if (r >= G) continue;                             // rows beyond the group's heads hold nothing
             if (tig == 0) { sm[warp * 16 + r] = m_r[h]; sl[warp * 16 + r] = l_r[h]; }
 #pragma unroll
             for (int n = 0; n < D / 8; ++n) {
@@ -310,20 +311,43 @@ __global__ void __launch_bounds__(THREADS, 2) decode_kernel(const __grid_constan
         __syncthreads();
         if (*s_flag) {
             __threadfence();
-            for (int idx = threadIdx.x; idx < G * D; idx += THREADS) {
-                const int g = idx / D, e = idx - g * D;
+            // four output elements per thread, all slices' parts asked for before the first is used
+            for (int idx = threadIdx.x; idx < G * (D / 4); idx += THREADS) {
+                const int g = idx / (D / 4), e = (idx - g * (D / 4)) * 4;
                 const float* ml = P.part_ml + (part0 + g) * P.max_splits * 2;
+                const float* po = P.part_o + (part0 + g) * P.max_splits * D + e;
+                constexpr int MAX_SLICES = 8;   // more slices go through the loop below in groups of eight
                 float M = -INFINITY;
                 for (int s = 0; s < n_splits; ++s) M = fmaxf(M, __ldcg(ml + 2 * s));
-                float acc = 0.0f, L = 0.0f;
+                float4 acc = make_float4(0.0f, 0.0f, 0.0f, 0.0f);
+                float L = 0.0f;
                 if (M > -INFINITY) {
-                    for (int s = 0; s < n_splits; ++s) {
-                        const float f = exp2f(__ldcg(ml + 2 * s) - M);
-                        acc += f * __ldcg(P.part_o + ((part0 + g) * P.max_splits + s) * D + e);
-                        L += f * __ldcg(ml + 2 * s + 1);
+                    for (int s0 = 0; s0 < n_splits; s0 += MAX_SLICES) {
+                        float4 part[MAX_SLICES];
+                        float mm[MAX_SLICES], ll[MAX_SLICES];
+#pragma unroll
+                        for (int j = 0; j < MAX_SLICES; ++j) {
+                            const bool live = s0 + j < n_splits;
+                            part[j] = live ? __ldcg(reinterpret_cast<const float4*>(po + (long)(s0 + j) * D))
+                                           : make_float4(0.0f, 0.0f, 0.0f, 0.0f);
+                            mm[j] = live ? __ldcg(ml + 2 * (s0 + j)) : -INFINITY;
+                            ll[j] = live ? __ldcg(ml + 2 * (s0 + j) + 1) : 0.0f;
+                        }
+#pragma unroll
+                        for (int j = 0; j < MAX_SLICES; ++j) {
+                            const float f = exp2f(mm[j] - M);
+                            acc.x += f * part[j].x; acc.y += f * part[j].y; acc.z += f * part[j].z; acc.w += f * part[j].w;
+                            L += f * ll[j];
+                        }
                     }
                 }
-                P.out[(head0 + g) * D + e] = __float2bfloat16_rn(L > 0.0f ? acc / L : 0.0f);
+                if (!(L > 0.0f)) { acc = make_float4(0.0f, 0.0f, 0.0f, 0.0f); L = 1.0f; }
+                __nv_bfloat162 lo2 = __floats2bfloat162_rn(acc.x / L, acc.y / L);
+                __nv_bfloat162 hi2 = __floats2bfloat162_rn(acc.z / L, acc.w / L);
+                uint2 w;
+                w.x = *reinterpret_cast<unsigned*>(&lo2);
+                w.y = *reinterpret_cast<unsigned*>(&hi2);
+                *reinterpret_cast<uint2*>(P.out + (head0 + g) * D + e) = w;
             }
         }
     }
