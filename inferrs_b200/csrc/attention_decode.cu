@@ -267,36 +267,43 @@ __global__ void __launch_bounds__(THREADS, 2) decode_kernel(const __grid_constan
             if (tig == 0) { sm[warp * 16 + r] = m_r[h]; sl[warp * 16 + r] = l_r[h]; }
 #pragma unroll
             for (int n = 0; n < D / 8; ++n) {
-                so[(warp * 16 + r) * D + n * 8 + 2 * tig] = o[n][2 * h];
-                so[(warp * 16 + r) * D + n * 8 + 2 * tig + 1] = o[n][2 * h + 1];
+                *reinterpret_cast<float2*>(so + (warp * 16 + r) * D + n * 8 + 2 * tig) = make_float2(o[n][2 * h], o[n][2 * h + 1]);
             }
         }
     }
     __syncthreads();
     const long head0 = (long)row * P.n_heads + kvh * G;       // of q and out
     const long part0 = (long)place * P.n_heads + kvh * G;     // of the slices' scratch
-    for (int idx = threadIdx.x; idx < G * D; idx += THREADS) {
-        const int g = idx / D, e = idx - g * D;
+    for (int idx = threadIdx.x; idx < G * (D / 4); idx += THREADS) {   // four elements per thread: one pass
+        const int g = idx / (D / 4), e = (idx - g * (D / 4)) * 4;
         float M = -INFINITY;
 #pragma unroll
         for (int w = 0; w < 4; ++w) M = fmaxf(M, sm[w * 16 + g]);
-        float acc = 0.0f, L = 0.0f;
+        float4 acc = make_float4(0.0f, 0.0f, 0.0f, 0.0f);
+        float L = 0.0f;
         if (M > -INFINITY) {
 #pragma unroll
             for (int w = 0; w < 4; ++w) {
                 const float f = exp2f(sm[w * 16 + g] - M);
-                acc += f * so[(w * 16 + g) * D + e];
+                const float4 v = *reinterpret_cast<const float4*>(so + (w * 16 + g) * D + e);
+                acc.x += f * v.x; acc.y += f * v.y; acc.z += f * v.z; acc.w += f * v.w;
                 L += f * sl[w * 16 + g];
             }
         }
         if (n_splits > 1) {
-            P.part_o[((part0 + g) * P.max_splits + split) * D + e] = acc;
+            *reinterpret_cast<float4*>(P.part_o + ((part0 + g) * P.max_splits + split) * D + e) = acc;
             if (e == 0) {
                 P.part_ml[((part0 + g) * P.max_splits + split) * 2] = M;
                 P.part_ml[((part0 + g) * P.max_splits + split) * 2 + 1] = L;
             }
         } else {
-            P.out[(head0 + g) * D + e] = __float2bfloat16_rn(L > 0.0f ? acc / L : 0.0f);
+            if (!(L > 0.0f)) { acc = make_float4(0.0f, 0.0f, 0.0f, 0.0f); L = 1.0f; }
+            __nv_bfloat162 lo2 = __floats2bfloat162_rn(acc.x / L, acc.y / L);
+            __nv_bfloat162 hi2 = __floats2bfloat162_rn(acc.z / L, acc.w / L);
+            uint2 w2;
+            w2.x = *reinterpret_cast<unsigned*>(&lo2);
+            w2.y = *reinterpret_cast<unsigned*>(&hi2);
+            *reinterpret_cast<uint2*>(P.out + (head0 + g) * D + e) = w2;
         }
     }
     if (n_splits > 1) {
