@@ -34,7 +34,7 @@ COMMON_FLAGS = ["-O3", "-std=c++17", "-lineinfo", "--expt-relaxed-constexpr", "-
 
 _CORE_SOURCES = ["elementwise.cu", "qk_rope_store.cu", "attention_generic.cu", "gemm_simt.cu", "sampling.cu",
                  "sample_select.cu", "attention_mma.cu", "attention_tcgen05.cu",
-                 "attention_decode.cu"]
+                 "attention_pair_tcgen05.cu", "attention_decode.cu"]
 
 # name -> (sources, extra flags, extra link flags)
 LIBRARIES: Dict[str, dict] = {

@@ -195,7 +195,8 @@ class PortionGraphs:
         self.n_wanted = max(self.n_requests, 64)   # wanted places that a captured step provides
         self.buckets = [b for b in self.ROW_BUCKETS if b <= max(max_rows, self.ROW_BUCKETS[0])]
         self.captured: Dict[int, _Captured] = {}
-        self.tile_sizes = None        # (tokens per tile, portions only) pairs that the attention layers ask for
+        # per row count: the (tokens per tile, portions only) pairs that the attention layers ask for at that size
+        self.tile_sizes: Dict[int, list] = {}
 
     def bucket_for(self, n_rows: int) -> Optional[int]:
         return next((b for b in self.buckets if b >= n_rows), None)
@@ -211,7 +212,7 @@ class PortionGraphs:
         r = self.runner
         ctx = build_context(entries, r.manager, r.storage, r.spec.vocab_size, r.spec.max_positions, device,
                             fixed_pages=self.fixed_pages, into=into, pad_rows=bucket, pad_requests=self.n_requests,
-                            pad_wanted=self.n_wanted, tile_sizes=self.tile_sizes)
+                            pad_wanted=self.n_wanted, tile_sizes=self.tile_sizes[bucket])
         ctx.max_kv_len = self.max_context
         return ctx
 
@@ -234,7 +235,7 @@ class PortionGraphs:
         try:
             code, _ = r.manager.describe_step(
                 [e.rid for e in entries], [e.tokens for e in entries], [e.want for e in entries], bucket,
-                self.n_requests, self.n_wanted, self.fixed_pages, self.tile_sizes, r.spec.vocab_size,
+                self.n_requests, self.n_wanted, self.fixed_pages, self.tile_sizes[bucket], r.spec.vocab_size,
                 r.spec.max_positions, stage.data_ptr(), stage.numel())
         except (TypeError, ValueError, OverflowError):
             code = -1
@@ -256,11 +257,14 @@ class PortionGraphs:
 
     def _capture(self, entries: Sequence[StepEntry], bucket: int) -> _Captured:
         r = self.runner
-        if self.tile_sizes is None:
-            # once plainly: the attention layers ask the context for their tiles, which tells their sizes
+        if bucket not in self.tile_sizes:
+            # once plainly: the attention layers ask the context for their tiles, which tells their sizes (they may
+            # depend on how many rows the step has: the plain step says that it stands for the padded one)
             plain = build_context(entries, r.manager, r.storage, r.spec.vocab_size, r.spec.max_positions, r.rt.device)
+            plain.extra["dispatch_rows"] = bucket
             r.model.forward(plain)
-            self.tile_sizes = sorted(k[1:] for k in plain.extra if isinstance(k, tuple) and k[0] == "attention_tiles")
+            self.tile_sizes[bucket] = sorted(k[1:] for k in plain.extra
+                                             if isinstance(k, tuple) and k[0] == "attention_tiles")
         size = self._build(entries, bucket, torch.device("cpu")).extra["host"].size
         buffer = torch.zeros((size + 16,), dtype=torch.int32, device=r.rt.device)
         ctx = self._build(entries, bucket, r.rt.device, into=buffer)

@@ -43,6 +43,10 @@ _SIGNATURES = {
                                    c_int, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_float, c_int, c_void_p,
                                    c_void_p],
     "ib_attention_tcgen05_error": [c_int],
+    "ib_paged_attention_pair_tcgen05": [c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_void_p, c_void_p,
+                                        c_int, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_float, c_int, c_void_p,
+                                        c_void_p],
+    "ib_attention_pair_tcgen05_error": [c_int],
     "ib_row_fault": [c_int],
     "ib_paged_attention_decode": [c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_void_p, c_int, c_int,
                                   c_int, c_int, c_float, c_int, c_void_p, c_int, c_int, c_void_p, c_void_p, c_void_p,
@@ -533,6 +537,51 @@ def paged_attention_tcgen05(q: torch.Tensor, k_pages: torch.Tensor, v_pages: tor
         _p(out), _stream()), "paged_attention_tcgen05")
 
 
+TC_PAIR_ROWS = 256  # query rows per tile of the tcgen05 attention kernel with two query tiles per CTA
+PAIR_MIN_CTAS = 128  # that kernel serves steps with at least this many of its CTAs (fewer leave SMs without work)
+
+
+def tcgen05_pair_attention_supported(dtype: torch.dtype, n_heads: int, n_kv_heads: int, head_dim: int,
+                                     page_size: int) -> bool:
+    g = n_heads // max(n_kv_heads, 1)
+    return (dtype == torch.bfloat16 and head_dim == 128 and page_size >= 8 and 64 % page_size == 0
+            and n_heads % n_kv_heads == 0 and 128 % g == 0)
+
+
+def paged_attention_pair_tcgen05(q: torch.Tensor, k_pages: torch.Tensor, v_pages: torch.Tensor,
+                                 block_table: torch.Tensor, tile_req: torch.Tensor, tile_row0: torch.Tensor, n_tiles: int,
+                                 q_start: torch.Tensor, positions: torch.Tensor, scale: float, window: Optional[int],
+                                 out: torch.Tensor):
+    """Attention of prompt portions on tcgen05 tensor cores with two query tiles per CTA that take turns
+    (bfloat16, head_dim 128): tile i holds up to 256/G tokens of request tile_req[i] from row tile_row0[i]; the
+    output is accumulated in tensor memory."""
+    bf = (torch.bfloat16,)
+    _need(q, "q", bf, 3)
+    _need(k_pages, "k_pages", bf, 4)
+    _need(v_pages, "v_pages", bf, 4)
+    _need(out, "out", bf, 2)
+    _need(block_table, "block_table", _I, 2)
+    for name, t in (("tile_req", tile_req), ("tile_row0", tile_row0), ("q_start", q_start), ("positions", positions)):
+        _need(t, name, _I, 1)
+    n, nh, d = q.shape
+    n_pages, nkv, page_size, dk = k_pages.shape
+    if dk != d or v_pages.shape != k_pages.shape or out.shape != (n, nh * d):
+        raise KernelError(f"paged_attention_pair_tcgen05: q {tuple(q.shape)}, pages {tuple(k_pages.shape)}, "
+                          f"out {tuple(out.shape)}")
+    if not tcgen05_pair_attention_supported(q.dtype, nh, nkv, d, page_size):
+        raise KernelError(f"paged_attention_pair_tcgen05 takes head_dim 128, a page size of 8..64 that divides 64 and "
+                          f"a group size that divides 128; got head_dim {d}, page size {page_size}, {nh}/{nkv} heads")
+    _check(_core(torch.bfloat16).ib_paged_attention_pair_tcgen05(
+        _p(q), _p(k_pages), _p(v_pages), _p(block_table), block_table.shape[1], page_size, n_pages, _p(tile_req),
+        _p(tile_row0), n_tiles, _p(q_start), _p(positions), n, nh, nkv, d, float(scale), int(window) if window else 0,
+        _p(out), _stream()), "paged_attention_pair_tcgen05")
+
+
+def attention_pair_tcgen05_error(reset: bool = True) -> int:
+    """0, or the code of the first bounded wait that ran out in the kernel above (synchronises)."""
+    return _core(torch.bfloat16).ib_attention_pair_tcgen05_error(int(reset))
+
+
 def attention_tcgen05_error(reset: bool = True) -> int:
     """0, or the code of the first bounded wait that ran out in the tcgen05 attention kernel (synchronises)."""
     return _core(torch.bfloat16).ib_attention_tcgen05_error(int(reset))
@@ -550,6 +599,14 @@ def paged_attention(q: torch.Tensor, k_pages: torch.Tensor, v_pages: torch.Tenso
     if not mma_attention_supported(q.dtype, nh, nkv, d, page_size):
         paged_attention_generic(q, k_pages, v_pages, block_table, ctx.row_request, ctx.positions, scale, window, out)
         return
+    # Prompt portions: tiles of 256 rows (two query tiles per CTA) where they still give every SM a CTA, else
+    # tiles of 128 rows.  A step that stands for a padded one (before its graph is captured) says so.
+    pair_tokens = TC_PAIR_ROWS // (nh // nkv)
+    rows_for_dispatch = ctx.extra.get("dispatch_rows", ctx.n_rows)
+    pair = tcgen05_pair_attention_supported(q.dtype, nh, nkv, d, page_size) \
+        and (rows_for_dispatch // pair_tokens) * nkv >= PAIR_MIN_CTAS
+    prefill_kernel = paged_attention_pair_tcgen05 if pair else paged_attention_tcgen05
+    prefill_tokens = pair_tokens if pair else TC_ROWS // (nh // nkv)
     if ctx.decode_only and tma_decode_attention_supported(q.dtype, nh, nkv, d, page_size):
         paged_attention_decode(q, k_pages, v_pages, block_table, ctx.positions, scale, window, out,
                                decode_max_splits(ctx.n_requests, nkv, ctx.max_kv_len))
@@ -566,14 +623,14 @@ def paged_attention(q: torch.Tensor, k_pages: torch.Tensor, v_pages: torch.Tenso
         if n_single > 0:
             paged_attention_decode(q, k_pages, v_pages, block_table, ctx.positions, scale, window, out,
                                    decode_max_splits(n_single, nkv, ctx.max_kv_len), rows, reqs)
-        tile_req, tile_row0, n_tiles = ctx.attention_tiles(TC_ROWS // (nh // nkv), portions_only=True)
+        tile_req, tile_row0, n_tiles = ctx.attention_tiles(prefill_tokens, portions_only=True)
         if n_tiles > 0:
-            paged_attention_tcgen05(q, k_pages, v_pages, block_table, tile_req, tile_row0, n_tiles, ctx.q_start,
-                                    ctx.positions, scale, window, out)
+            prefill_kernel(q, k_pages, v_pages, block_table, tile_req, tile_row0, n_tiles, ctx.q_start,
+                           ctx.positions, scale, window, out)
     elif tcgen05_attention_supported(q.dtype, nh, nkv, d, page_size):
-        tile_req, tile_row0, n_tiles = ctx.attention_tiles(TC_ROWS // (nh // nkv))
-        paged_attention_tcgen05(q, k_pages, v_pages, block_table, tile_req, tile_row0, n_tiles, ctx.q_start,
-                                ctx.positions, scale, window, out)
+        tile_req, tile_row0, n_tiles = ctx.attention_tiles(prefill_tokens)
+        prefill_kernel(q, k_pages, v_pages, block_table, tile_req, tile_row0, n_tiles, ctx.q_start,
+                       ctx.positions, scale, window, out)
     else:
         tile_req, tile_row0, n_tiles = ctx.attention_tiles(MMA_KEYS // (nh // nkv))
         paged_attention_mma(q, k_pages, v_pages, block_table, tile_req, tile_row0, n_tiles, ctx.q_start,

@@ -149,7 +149,7 @@ def attention(args) -> dict:
         flops = 4 * nh * d * sum(lens)
         extra = {"batch": args.batch, "context": args.context, "splits": splits}
     else:
-        tpt = (kernels.TC_ROWS if args.impl == "tcgen05" else kernels.MMA_KEYS) // (nh // nkv)
+        tpt = {"tcgen05": kernels.TC_ROWS, "tcgen05-pair": kernels.TC_PAIR_ROWS, "mma": kernels.MMA_KEYS}[args.impl] // (nh // nkv)
         req = [0] * ((args.tokens + tpt - 1) // tpt)
         row0 = list(range(0, args.tokens, tpt))
         tile_req = torch.tensor(req, dtype=torch.int32, device=dev)
@@ -157,6 +157,9 @@ def attention(args) -> dict:
         if args.impl == "tcgen05":
             fn = lambda: kernels.paged_attention_tcgen05(q, k_pages, v_pages, table, tile_req, tile_row0, len(req),  # noqa: E731
                                                          q_start, positions, scale, None, out)
+        elif args.impl == "tcgen05-pair":
+            fn = lambda: kernels.paged_attention_pair_tcgen05(q, k_pages, v_pages, table, tile_req, tile_row0, len(req),  # noqa: E731
+                                                              q_start, positions, scale, None, out)
         else:
             fn = lambda: kernels.paged_attention_mma(q, k_pages, v_pages, table, tile_req, tile_row0, len(req),  # noqa: E731
                                                      q_start, positions, scale, None, out, False)
@@ -393,7 +396,7 @@ def main(argv=None) -> int:
     g.set_defaults(fn=gemm)
     a = sub.add_parser("attention")
     a.add_argument("--form", choices=["decode", "prefill"], default="decode")
-    a.add_argument("--impl", choices=["mma", "tcgen05"], default="tcgen05", help="which kernel (decode form: mma = cp.async kernel, tcgen05 = TMA-fed kernel)")
+    a.add_argument("--impl", choices=["mma", "tcgen05", "tcgen05-pair"], default="tcgen05", help="which kernel (decode form: mma = cp.async kernel, tcgen05 = TMA-fed kernel)")
     a.add_argument("--batch", type=int, default=8)
     a.add_argument("--context", type=int, default=2048)
     a.add_argument("--tokens", type=int, default=2048)

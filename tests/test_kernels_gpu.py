@@ -421,6 +421,41 @@ def test_paged_attention_tcgen05(nh, nkv, ps, window):
     assert rel_err(got, want) < 5e-2, "the far key that stands out was not seen"
 
 
+@pytest.mark.parametrize("nh,nkv,ps,window", [(8, 2, 16, None), (32, 8, 16, None), (6, 2 * 3, 16, 70), (4, 1, 64, None),
+                                              (16, 1, 8, 200), (2, 2, 32, None)])
+def test_paged_attention_pair_tcgen05(nh, nkv, ps, window):
+    """The kernel with two query tiles per CTA: tiles of 256/G tokens, so that requests with one token, with fewer
+    tokens than one query tile holds, with a few more, and with many all occur; one far key and the last query of
+    the first request are made so that this key alone decides that row (the reference maximum of the row jumps
+    when its tile comes, and the output accumulated so far must be scaled away)."""
+    from inferrs_b200 import kernels as K
+    dtype, d = torch.bfloat16, 128
+    lens, new = [300, 17, 200, 64, 1, 700], [40, 17, 200, 1, 1, 333]
+    table, positions, row_request, k_pages, v_pages = _paged_setup(dtype, nkv, d, ps, lens, new, 20)
+    n = sum(new)
+    q = rand((n, nh, d), dtype, 23)
+    q_start = torch.tensor([0] + list(torch.tensor(new).cumsum(0)), dtype=torch.int32, device=dev())
+    far = 150 if window is None else lens[0] - window
+    page, slot = int(table[0, far // ps]), far % ps
+    k_pages[page, :, slot, :] = 0
+    k_pages[page, :, slot, 0] = 16.0
+    q[new[0] - 1, :, :] = 0
+    q[new[0] - 1, :, 0] = 16.0
+    out = torch.full((n, nh * d), float("nan"), dtype=dtype, device=dev())
+    ref = torch.empty_like(out)
+    scale = d ** -0.5 * 4
+    tile_req, tile_row0, n_tiles = _tiles(new, 256 // (nh // nkv))
+    K.paged_attention_pair_tcgen05(q, k_pages, v_pages, table, tile_req, tile_row0, n_tiles, q_start, positions, scale,
+                                   window, out)
+    assert K.attention_pair_tcgen05_error() == 0
+    R.paged_attention_generic(q, k_pages, v_pages, table, row_request, positions, scale, window, ref)
+    assert not torch.isnan(out.float()).any()
+    assert rel_err(out, ref) < 2e-2
+    got = out[new[0] - 1].view(nh, d).float()
+    want = v_pages[page, :, slot, :].float().repeat_interleave(nh // nkv, dim=0)
+    assert rel_err(got, want) < 5e-2, "the far key that stands out was not seen"
+
+
 @pytest.mark.parametrize("nh,nkv,ps,window,max_splits", [(8, 2, 16, None, 1), (32, 8, 16, None, 9), (4, 4, 8, 50, 3),
                                                           (16, 1, 32, None, 40), (6, 2, 64, 129, 2), (32, 8, 16, None, 64)])
 def test_paged_attention_decode(nh, nkv, ps, window, max_splits):
