@@ -241,3 +241,51 @@ def test_replayed_steps_take_tokens_that_are_still_on_the_device(model_dirs, nam
     plain_runner.admit(0)
     with pytest.raises(ValueError, match="replayed"):
         plain_runner.step([StepEntry(0, [0], [0])], carry=(torch.zeros(1, dtype=torch.int32, device="cuda"), [0]))
+
+
+def test_portions_through_the_kernel_with_two_query_tiles(tmp_path, monkeypatch):
+    """The prefill attention kernel with two query tiles per CTA serves only large steps; here it is made to serve
+    every step with a portion (head size 128, two query heads per key/value head, so a tile holds 2 x 64
+    tokens): one request in portions that end inside the first query tile, inside the second and at their edges,
+    then a request's portions beside decoded tokens of another, as replayed graphs; all logits against the plain
+    implementation."""
+    from inferrs_b200 import kernels
+    from inferrs_b200.weights.random_init import write_random_model
+    monkeypatch.setattr(kernels, "PAIR_MIN_CTAS", 1)
+    calls = {"pair": 0}
+    original = kernels.paged_attention_pair_tcgen05
+
+    def counted(*a, **k):
+        calls["pair"] += 1
+        return original(*a, **k)
+
+    monkeypatch.setattr(kernels, "paged_attention_pair_tcgen05", counted)
+    cfg = dict(CONFIG_D, num_attention_heads=4, num_key_value_heads=2, hidden_size=160, intermediate_size=264)
+    model_dir = str(tmp_path / "pair")
+    write_random_model(model_dir, cfg, seed=11, dtype=torch.bfloat16)
+    dtype = torch.bfloat16
+    runner = make_runner(model_dir, dtype, 16, n_pages=96)
+    sizes = [30, 64, 34, 128, 1, 65, 129, 3, 90]
+    toks = [random_tokens(sum(sizes), cfg["vocab_size"], seed=70 + i) for i in range(3)]
+    want = [plain_logits(model_dir, t, dtype) for t in toks]
+    runner.admit(0)
+    at = 0
+    for s in sizes:
+        out = runner.step([StepEntry(0, toks[0][at:at + s], list(range(s)))])
+        check(out, want[0][at:at + s], dtype, f"portion of {s} from {at}")
+        at += s
+    assert calls["pair"] >= 4    # launched from Python where a step is not a replayed graph, and at every capture
+    # a request's portions beside the decoded tokens of another, which has 100 tokens already
+    runner.admit(1)
+    runner.admit(2)
+    runner.step([StepEntry(2, toks[2][:100], [])])
+    at1, at2 = 0, 100
+    for s in (50, 85, 7, 120):
+        entries = [StepEntry(1, toks[1][at1:at1 + s], [s - 1]), StepEntry(2, toks[2][at2:at2 + 1], [0])]
+        out = runner.step(entries)
+        check(out[0:1], want[1][at1 + s - 1:at1 + s], dtype, f"request 1 at {at1 + s - 1}")
+        check(out[1:2], want[2][at2:at2 + 1], dtype, f"request 2 at {at2}")
+        at1 += s
+        at2 += 1
+    assert kernels.attention_pair_tcgen05_error() == 0
+    runner.manager.check_invariants()
