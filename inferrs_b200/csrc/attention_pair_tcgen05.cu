@@ -88,7 +88,7 @@ __global__ void __launch_bounds__(THREADS, 1) attention_pair_kernel(const __grid
     const int req = P.tile_req[tile], row0 = P.tile_row0[tile];
     if (req < 0) return;                            // a place in a tile list of fixed length that holds no tile
     const int G = P.n_heads / P.n_kv_heads;
-    const int tpt = ROWS / G;                       // tokens per query tile
+    const int tpt = ROWS / G;                       // tokens per query tile (a group size that does not divide 128 leaves rows unused)
     int n_tok = P.q_start[req + 1] - row0;          // tokens of both query tiles
     if (n_tok > 2 * tpt) n_tok = 2 * tpt;
     const int p0 = P.positions[row0];
@@ -130,7 +130,7 @@ __global__ void __launch_bounds__(THREADS, 1) attention_pair_kernel(const __grid
         // p of every tile (two boxes: the 64-column halves) and looks the page up one tile ahead of its use.
         if (warp == 8 && lane == 0) {
             const int n_q = n_tok_t[1] > 0 ? 2 : 1;
-            mbar_expect_tx(q_full, n_q * Q_TILE);   // per tile [tokens][G heads][128] as two 64-column halves
+            mbar_expect_tx(q_full, n_q * tpt * G * 256);   // per tile [tokens][G heads][128] as two 64-column halves
             for (int t = 0; t < n_q; ++t) {
                 tma_load_3d(smem_u32(sq + t * Q_TILE), &map_q, 0, kvh * G, row0 + t * tpt, q_full);
                 tma_load_3d(smem_u32(sq + t * Q_TILE + Q_HALF), &map_q, 64, kvh * G, row0 + t * tpt, q_full);
@@ -358,7 +358,7 @@ IB_EXPORT int ib_paged_attention_pair_tcgen05(const void* q, const void* k_pages
     if (n_tiles <= 0) return IB_OK;
     if (n_heads <= 0 || n_kv_heads <= 0 || n_heads % n_kv_heads || page_size <= 0 || max_pages <= 0) return IB_ERR_ARGUMENT;
     const int G = n_heads / n_kv_heads;
-    if (head_dim != fp::D || fp::KEYS % page_size || page_size < 8 || fp::ROWS % G) return IB_ERR_UNSUPPORTED;
+    if (head_dim != fp::D || fp::KEYS % page_size || page_size < 8 || G > fp::ROWS) return IB_ERR_UNSUPPORTED;
     if (!(scale > 0.0f)) return IB_ERR_UNSUPPORTED;   // the row maximum is taken before the scale is applied
     sm100::EncodeTiled enc = sm100::encode_fn();
     if (enc == nullptr) return IB_ERR_UNSUPPORTED;

@@ -97,7 +97,7 @@ __global__ void __launch_bounds__(THREADS, 1) attention_kernel(const __grid_cons
     const int req = P.tile_req[tile], row0 = P.tile_row0[tile];
     if (req < 0) return;                            // a place in a tile list of fixed length that holds no tile
     const int G = P.n_heads / P.n_kv_heads;
-    const int tpt = ROWS / G;                       // tokens per tile
+    const int tpt = ROWS / G;                       // tokens per tile (a group size that does not divide 128 leaves rows unused)
     int n_tok = P.q_start[req + 1] - row0;
     if (n_tok > tpt) n_tok = tpt;
     const int p0 = P.positions[row0];
@@ -130,7 +130,7 @@ __global__ void __launch_bounds__(THREADS, 1) attention_kernel(const __grid_cons
         // TMA producers: warp 8 brings the queries and the key tiles, warp 10 the value tiles.  Lane p brings page
         // p of every tile (two boxes: the 64-column halves) and looks the page up one tile ahead of its use.
         if (warp == 8 && lane == 0) {
-            mbar_expect_tx(q_full, TILE_BYTES);   // [tokens][G heads][128] as two 64-column halves
+            mbar_expect_tx(q_full, tpt * G * 256);   // [tokens][G heads][128] as two 64-column halves (rows beyond tokens x G stay unwritten: no row reads another)
             tma_load_3d(smem_u32(sq), &map_q, 0, kvh * G, row0, q_full);
             tma_load_3d(smem_u32(sq + HALF_BYTES), &map_q, 64, kvh * G, row0, q_full);
         }
@@ -382,7 +382,7 @@ IB_EXPORT int ib_paged_attention_tcgen05(const void* q, const void* k_pages, con
     if (n_tiles <= 0) return IB_OK;
     if (n_heads <= 0 || n_kv_heads <= 0 || n_heads % n_kv_heads || page_size <= 0 || max_pages <= 0) return IB_ERR_ARGUMENT;
     const int G = n_heads / n_kv_heads;
-    if (head_dim != fa::D || fa::KEYS % page_size || page_size < 8 || fa::ROWS % G) return IB_ERR_UNSUPPORTED;
+    if (head_dim != fa::D || fa::KEYS % page_size || page_size < 8 || G > fa::ROWS) return IB_ERR_UNSUPPORTED;
     if (!(scale > 0.0f)) return IB_ERR_UNSUPPORTED;   // the row maximum is taken before the scale is applied
     fa::EncodeTiled enc = fa::encode_fn();
     if (enc == nullptr) return IB_ERR_UNSUPPORTED;

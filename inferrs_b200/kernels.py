@@ -508,7 +508,7 @@ TC_ROWS = 128  # query rows per tile of the tcgen05 attention kernel
 def tcgen05_attention_supported(dtype: torch.dtype, n_heads: int, n_kv_heads: int, head_dim: int, page_size: int) -> bool:
     g = n_heads // max(n_kv_heads, 1)
     return (dtype == torch.bfloat16 and head_dim == 128 and page_size >= 8 and 128 % page_size == 0
-            and n_heads % n_kv_heads == 0 and TC_ROWS % g == 0)
+            and n_heads % n_kv_heads == 0 and 1 <= g <= TC_ROWS)
 
 
 def paged_attention_tcgen05(q: torch.Tensor, k_pages: torch.Tensor, v_pages: torch.Tensor, block_table: torch.Tensor,
@@ -530,7 +530,7 @@ def paged_attention_tcgen05(q: torch.Tensor, k_pages: torch.Tensor, v_pages: tor
         raise KernelError(f"paged_attention_tcgen05: q {tuple(q.shape)}, pages {tuple(k_pages.shape)}, out {tuple(out.shape)}")
     if not tcgen05_attention_supported(q.dtype, nh, nkv, d, page_size):
         raise KernelError(f"paged_attention_tcgen05 takes head_dim 128, a page size of 8..128 that divides 128 and a "
-                          f"group size that divides 128; got head_dim {d}, page size {page_size}, {nh}/{nkv} heads")
+                          f"group size of at most 128; got head_dim {d}, page size {page_size}, {nh}/{nkv} heads")
     _check(_core(torch.bfloat16).ib_paged_attention_tcgen05(
         _p(q), _p(k_pages), _p(v_pages), _p(block_table), block_table.shape[1], page_size, n_pages, _p(tile_req),
         _p(tile_row0), n_tiles, _p(q_start), _p(positions), n, nh, nkv, d, float(scale), int(window) if window else 0,
@@ -541,11 +541,17 @@ TC_PAIR_ROWS = 256  # query rows per tile of the tcgen05 attention kernel with t
 PAIR_MIN_CTAS = 128  # that kernel serves steps with at least this many of its CTAs (fewer leave SMs without work)
 
 
+def pair_tile_tokens(n_heads: int, n_kv_heads: int) -> int:
+    """Tokens that a tile of the kernel with two query tiles holds: each query tile takes as many whole tokens (all
+    heads of the group) as fit into its 128 rows."""
+    return 2 * ((TC_PAIR_ROWS // 2) // (n_heads // n_kv_heads))
+
+
 def tcgen05_pair_attention_supported(dtype: torch.dtype, n_heads: int, n_kv_heads: int, head_dim: int,
                                      page_size: int) -> bool:
     g = n_heads // max(n_kv_heads, 1)
     return (dtype == torch.bfloat16 and head_dim == 128 and page_size >= 8 and 64 % page_size == 0
-            and n_heads % n_kv_heads == 0 and 128 % g == 0)
+            and n_heads % n_kv_heads == 0 and 1 <= g <= 128)
 
 
 def paged_attention_pair_tcgen05(q: torch.Tensor, k_pages: torch.Tensor, v_pages: torch.Tensor,
@@ -553,8 +559,8 @@ def paged_attention_pair_tcgen05(q: torch.Tensor, k_pages: torch.Tensor, v_pages
                                  q_start: torch.Tensor, positions: torch.Tensor, scale: float, window: Optional[int],
                                  out: torch.Tensor):
     """Attention of prompt portions on tcgen05 tensor cores with two query tiles per CTA that take turns
-    (bfloat16, head_dim 128): tile i holds up to 256/G tokens of request tile_req[i] from row tile_row0[i]; the
-    output is accumulated in tensor memory."""
+    (bfloat16, head_dim 128): tile i holds up to ``pair_tile_tokens`` tokens of request tile_req[i] from row
+    tile_row0[i]; the output is accumulated in tensor memory."""
     bf = (torch.bfloat16,)
     _need(q, "q", bf, 3)
     _need(k_pages, "k_pages", bf, 4)
@@ -570,7 +576,7 @@ def paged_attention_pair_tcgen05(q: torch.Tensor, k_pages: torch.Tensor, v_pages
                           f"out {tuple(out.shape)}")
     if not tcgen05_pair_attention_supported(q.dtype, nh, nkv, d, page_size):
         raise KernelError(f"paged_attention_pair_tcgen05 takes head_dim 128, a page size of 8..64 that divides 64 and "
-                          f"a group size that divides 128; got head_dim {d}, page size {page_size}, {nh}/{nkv} heads")
+                          f"a group size of at most 128; got head_dim {d}, page size {page_size}, {nh}/{nkv} heads")
     _check(_core(torch.bfloat16).ib_paged_attention_pair_tcgen05(
         _p(q), _p(k_pages), _p(v_pages), _p(block_table), block_table.shape[1], page_size, n_pages, _p(tile_req),
         _p(tile_row0), n_tiles, _p(q_start), _p(positions), n, nh, nkv, d, float(scale), int(window) if window else 0,
@@ -601,7 +607,7 @@ def paged_attention(q: torch.Tensor, k_pages: torch.Tensor, v_pages: torch.Tenso
         return
     # Prompt portions: tiles of 256 rows (two query tiles per CTA) where they still give every SM a CTA, else
     # tiles of 128 rows.  A step that stands for a padded one (before its graph is captured) says so.
-    pair_tokens = TC_PAIR_ROWS // (nh // nkv)
+    pair_tokens = pair_tile_tokens(nh, nkv)
     rows_for_dispatch = ctx.extra.get("dispatch_rows", ctx.n_rows)
     pair = tcgen05_pair_attention_supported(q.dtype, nh, nkv, d, page_size) \
         and (rows_for_dispatch // pair_tokens) * nkv >= PAIR_MIN_CTAS

@@ -149,7 +149,8 @@ def attention(args) -> dict:
         flops = 4 * nh * d * sum(lens)
         extra = {"batch": args.batch, "context": args.context, "splits": splits}
     else:
-        tpt = {"tcgen05": kernels.TC_ROWS, "tcgen05-pair": kernels.TC_PAIR_ROWS, "mma": kernels.MMA_KEYS}[args.impl] // (nh // nkv)
+        tpt = kernels.pair_tile_tokens(nh, nkv) if args.impl == "tcgen05-pair" else \
+            (kernels.TC_ROWS if args.impl == "tcgen05" else kernels.MMA_KEYS) // (nh // nkv)
         req = [0] * ((args.tokens + tpt - 1) // tpt)
         row0 = list(range(0, args.tokens, tpt))
         tile_req = torch.tensor(req, dtype=torch.int32, device=dev)

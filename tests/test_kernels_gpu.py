@@ -392,7 +392,7 @@ def test_gemm_tn_streamk(n, m, k):
 
 
 @pytest.mark.parametrize("nh,nkv,ps,window", [(8, 2, 16, None), (32, 8, 16, None), (6, 2 * 3, 16, 70), (4, 1, 64, None),
-                                              (16, 1, 8, 200), (2, 2, 128, None)])
+                                              (16, 1, 8, 200), (2, 2, 128, None), (10, 2, 16, None), (6, 2, 32, 90)])
 def test_paged_attention_tcgen05(nh, nkv, ps, window):
     from inferrs_b200 import kernels as K
     dtype, d = torch.bfloat16, 128
@@ -422,7 +422,7 @@ def test_paged_attention_tcgen05(nh, nkv, ps, window):
 
 
 @pytest.mark.parametrize("nh,nkv,ps,window", [(8, 2, 16, None), (32, 8, 16, None), (6, 2 * 3, 16, 70), (4, 1, 64, None),
-                                              (16, 1, 8, 200), (2, 2, 32, None)])
+                                              (16, 1, 8, 200), (2, 2, 32, None), (10, 2, 16, None), (6, 2, 32, 90)])
 def test_paged_attention_pair_tcgen05(nh, nkv, ps, window):
     """The kernel with two query tiles per CTA: tiles of 256/G tokens, so that requests with one token, with fewer
     tokens than one query tile holds, with a few more, and with many all occur; one far key and the last query of
@@ -444,7 +444,7 @@ def test_paged_attention_pair_tcgen05(nh, nkv, ps, window):
     out = torch.full((n, nh * d), float("nan"), dtype=dtype, device=dev())
     ref = torch.empty_like(out)
     scale = d ** -0.5 * 4
-    tile_req, tile_row0, n_tiles = _tiles(new, 256 // (nh // nkv))
+    tile_req, tile_row0, n_tiles = _tiles(new, K.pair_tile_tokens(nh, nkv))
     K.paged_attention_pair_tcgen05(q, k_pages, v_pages, table, tile_req, tile_row0, n_tiles, q_start, positions, scale,
                                    window, out)
     assert K.attention_pair_tcgen05_error() == 0
