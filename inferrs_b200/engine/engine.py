@@ -69,7 +69,7 @@ class Engine:
         self.n_steps = 0
         self.n_tokens_run = 0
         # the step whose tokens the host has not read yet: (plan, token ids on the device, pinned copy, event)
-        self.overlap = bool(overlap) and self.rt.device.type == "cuda" and self.runner.graphs is not None
+        self.overlap = bool(overlap) and self.runner.graphs is not None   # replayed graphs are on a CUDA device only
         self._in_flight = None
         self._pinned = []
         self.n_steps_in_vain = 0
@@ -152,7 +152,8 @@ class Engine:
             ids = self.sampler.sample(logits, [e.request.params for e, _ in sampling],
                                       [e.request.seed for e, _ in sampling], [e.request for e, _ in sampling],
                                       pending, pending_ids)
-            if self.overlap:
+            if self.overlap and ids.device.type == "cuda":
+                # the token ids start their way to pinned memory now; an event says when they are there
                 host = self._pinned.pop() if self._pinned else \
                     torch.empty((max(self.scheduler.max_batch_size, ids.shape[0]),), dtype=torch.int32).pin_memory()
                 host[:ids.shape[0]].copy_(ids, non_blocking=True)
