@@ -323,6 +323,8 @@ SHAPES = {
                  intermediate_size=3072, tie_word_embeddings=True),
     "8b": dict(num_hidden_layers=36, hidden_size=4096, num_attention_heads=32, num_key_value_heads=8, head_dim=128,
                intermediate_size=12288, tie_word_embeddings=False),
+    "14b": dict(num_hidden_layers=40, hidden_size=5120, num_attention_heads=40, num_key_value_heads=8, head_dim=128,
+                intermediate_size=17408, tie_word_embeddings=False),   # five query heads per key/value head
     "32b": dict(num_hidden_layers=64, hidden_size=5120, num_attention_heads=64, num_key_value_heads=8, head_dim=128,
                 intermediate_size=25600, tie_word_embeddings=False),
 }
