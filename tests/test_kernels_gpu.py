@@ -35,6 +35,26 @@ def test_embedding_gather(dtype, wdtype):
 
 
 @pytest.mark.parametrize("dtype", DTYPES)
+@pytest.mark.parametrize("n", [1, 37, 1000])
+def test_resolve_tokens(dtype, n):
+    """ids[i] < 0 names place -1 - ids[i] of the tokens that an earlier step sampled; other ids stay; a place
+    beyond those tokens becomes an id that is no token (the embedding gives zeros for it)."""
+    from inferrs_b200 import kernels as K
+    g = torch.Generator().manual_seed(n)
+    carry = torch.randint(0, 5000, (11,), generator=g, dtype=torch.int32).to(dev())
+    ids = torch.randint(0, 5000, (n,), generator=g, dtype=torch.int32)
+    places = torch.randint(0, 11, (n,), generator=g, dtype=torch.int32)
+    named = torch.rand(n, generator=g) < 0.4
+    given = torch.where(named, -1 - places, ids)
+    want = torch.where(named, carry.cpu()[places.long()], ids)
+    if n > 2:
+        given[2], want[2] = -1 - 11, -1        # a place that does not exist
+    got = given.to(dev())
+    K.resolve_tokens(got, carry, dtype)
+    assert torch.equal(got.cpu(), want)
+
+
+@pytest.mark.parametrize("dtype", DTYPES)
 @pytest.mark.parametrize("width", [200, 96, 4096, 5000])
 def test_add_rms_norm(dtype, width):
     from inferrs_b200 import kernels as K
