@@ -188,9 +188,10 @@ __global__ void qk_norm_rope_store_d128_kernel(
 #endif
 
 #if IB_ACT_BF16
-// The same for thousands of rows, where the bytes in flight decide: sixteen lanes per head with eight elements
-// (16 bytes) each, so a warp takes two heads at a time and eight heads in all, all loads issued before the
-// first is used.  Element i < 64 pairs with i + 64: lane l of a head's sixteen pairs with lane l ^ 8.
+// The same for thousands of rows, where bytes in flight and instructions per byte decide: sixteen lanes per
+// head, each with four elements of the head's first half and the four that rotate with them in the second half
+// (element i pairs with i + 64), so the rotation needs no exchange between lanes.  A warp takes two heads at a
+// time and eight heads in all; all loads are issued before the first is used.
 template <typename WT>
 __global__ void qk_norm_rope_store_d128_wide_kernel(
     const __nv_bfloat16* __restrict__ qkv, int row_stride, int n_heads, int n_kv_heads, int store_kv,
@@ -215,43 +216,43 @@ __global__ void qk_norm_rope_store_d128_wide_kernel(
         if (page >= 0 && page < n_pages) kv_base = ((long)page * n_kv_heads * page_size + (pos % page_size)) * 128;
     }
     const int sub = lane >> 4, l16 = lane & 15;  // which of the two heads of a pass, and the place in it
-    const int e0 = 8 * l16;                      // this lane's eight elements of the head
-    const int i0 = 8 * (l16 & 7);                // their index into the rotation tables (e0 mod 64)
-    float cs[8], sn[8];
-    {
-        const float4 c0 = *reinterpret_cast<const float4*>(cos_table + (long)pos * 64 + i0);
-        const float4 c1 = *reinterpret_cast<const float4*>(cos_table + (long)pos * 64 + i0 + 4);
-        const float4 s0 = *reinterpret_cast<const float4*>(sin_table + (long)pos * 64 + i0);
-        const float4 s1 = *reinterpret_cast<const float4*>(sin_table + (long)pos * 64 + i0 + 4);
-        cs[0] = c0.x; cs[1] = c0.y; cs[2] = c0.z; cs[3] = c0.w; cs[4] = c1.x; cs[5] = c1.y; cs[6] = c1.z; cs[7] = c1.w;
-        sn[0] = s0.x; sn[1] = s0.y; sn[2] = s0.z; sn[3] = s0.w; sn[4] = s1.x; sn[5] = s1.y; sn[6] = s1.z; sn[7] = s1.w;
-    }
-    float wq[8], wk[8];
+    const int e0 = 4 * l16;                      // this lane's elements e0 .. e0 + 3 and 64 + e0 .. 64 + e0 + 3
+    const float4 cs = *reinterpret_cast<const float4*>(cos_table + (long)pos * 64 + e0);
+    const float4 sn = *reinterpret_cast<const float4*>(sin_table + (long)pos * 64 + e0);
+    float wq[8], wk[8];                          // norm weights of the two runs of four
 #pragma unroll
     for (int e = 0; e < 8; ++e) {
-        wq[e] = (q_weight != nullptr && head0 < n_heads) ? ib_to_float(q_weight[e0 + e]) : 1.0f;
-        wk[e] = (k_weight != nullptr && head0 + HPW > n_heads) ? ib_to_float(k_weight[e0 + e]) : 1.0f;
+        const int at = (e < 4 ? e0 : 60 + e0) + e;   // e0 + e, or 64 + e0 + (e - 4)
+        wq[e] = (q_weight != nullptr && head0 < n_heads) ? ib_to_float(q_weight[at]) : 1.0f;
+        wk[e] = (k_weight != nullptr && head0 + HPW > n_heads) ? ib_to_float(k_weight[at]) : 1.0f;
     }
     ib_grid_dependency_wait();
-    uint4 raw[HPW / 2];
+    uint2 raw_lo[HPW / 2], raw_hi[HPW / 2];
 #pragma unroll
     for (int j = 0; j < HPW / 2; ++j) {
         const int head = head0 + 2 * j + sub;
-        if (head < heads_total)
-            raw[j] = *reinterpret_cast<const uint4*>(qkv + (long)row * row_stride + (long)head * 128 + e0);
+        if (head < heads_total) {
+            const __nv_bfloat16* src = qkv + (long)row * row_stride + (long)head * 128 + e0;
+            raw_lo[j] = *reinterpret_cast<const uint2*>(src);
+            raw_hi[j] = *reinterpret_cast<const uint2*>(src + 64);
+        }
     }
 #pragma unroll
     for (int j = 0; j < HPW / 2; ++j) {
         const int head = head0 + 2 * j + sub;
         const bool live = head < heads_total;   // the other half of the warp may still have a head: no early exit
         const int kind = head < n_heads ? 0 : (head < n_heads + n_kv_heads ? 1 : 2);
-        float x[8];
-        const __nv_bfloat162* h2 = reinterpret_cast<const __nv_bfloat162*>(&raw[j]);
+        float x[8];                              // 0..3: first half, 4..7: their partners in the second half
+        {
+            const __nv_bfloat162* lo2 = reinterpret_cast<const __nv_bfloat162*>(&raw_lo[j]);
+            const __nv_bfloat162* hi2 = reinterpret_cast<const __nv_bfloat162*>(&raw_hi[j]);
 #pragma unroll
-        for (int e = 0; e < 4; ++e) {
-            const float2 f = live ? __bfloat1622float2(h2[e]) : make_float2(0.0f, 0.0f);
-            x[2 * e] = f.x;
-            x[2 * e + 1] = f.y;
+            for (int e = 0; e < 2; ++e) {
+                const float2 a = live ? __bfloat1622float2(lo2[e]) : make_float2(0.0f, 0.0f);
+                const float2 b = live ? __bfloat1622float2(hi2[e]) : make_float2(0.0f, 0.0f);
+                x[2 * e] = a.x; x[2 * e + 1] = a.y;
+                x[4 + 2 * e] = b.x; x[4 + 2 * e + 1] = b.y;
+            }
         }
         const WT* w = kind == 0 ? q_weight : k_weight;
         float ss = 0.0f;
@@ -264,10 +265,14 @@ __global__ void qk_norm_rope_store_d128_wide_kernel(
 #pragma unroll
             for (int e = 0; e < 8; ++e) x[e] = x[e] * inv * (kind == 0 ? wq[e] : wk[e]);
         }
+        if (kind != 2) {
+            const float c[4] = {cs.x, cs.y, cs.z, cs.w}, s4[4] = {sn.x, sn.y, sn.z, sn.w};
 #pragma unroll
-        for (int e = 0; e < 8; ++e) {
-            const float other = __shfl_xor_sync(0xffffffffu, x[e], 8);
-            if (kind != 2) x[e] = l16 < 8 ? x[e] * cs[e] - other * sn[e] : other * sn[e] + x[e] * cs[e];
+            for (int e = 0; e < 4; ++e) {
+                const float lo = x[e], hi = x[4 + e];
+                x[e] = lo * c[e] - hi * s4[e];
+                x[4 + e] = lo * s4[e] + hi * c[e];
+            }
         }
         if (!live) continue;
         __nv_bfloat16* dst;
@@ -278,11 +283,14 @@ __global__ void qk_norm_rope_store_d128_wide_kernel(
             const int kvh = head - n_heads - (kind == 2 ? n_kv_heads : 0);
             dst = (kind == 1 ? k_pages : v_pages) + kv_base + (long)kvh * page_size * 128;
         }
-        uint4 o;
-        __nv_bfloat162* o2 = reinterpret_cast<__nv_bfloat162*>(&o);
-#pragma unroll
-        for (int e = 0; e < 4; ++e) o2[e] = __floats2bfloat162_rn(x[2 * e], x[2 * e + 1]);
-        *reinterpret_cast<uint4*>(dst + e0) = o;
+        uint2 o_lo, o_hi;
+        __nv_bfloat162 t;
+        t = __floats2bfloat162_rn(x[0], x[1]); o_lo.x = *reinterpret_cast<unsigned*>(&t);
+        t = __floats2bfloat162_rn(x[2], x[3]); o_lo.y = *reinterpret_cast<unsigned*>(&t);
+        t = __floats2bfloat162_rn(x[4], x[5]); o_hi.x = *reinterpret_cast<unsigned*>(&t);
+        t = __floats2bfloat162_rn(x[6], x[7]); o_hi.y = *reinterpret_cast<unsigned*>(&t);
+        *reinterpret_cast<uint2*>(dst + e0) = o_lo;
+        *reinterpret_cast<uint2*>(dst + 64 + e0) = o_hi;
     }
 }
 #endif
