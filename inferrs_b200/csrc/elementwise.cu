@@ -205,26 +205,30 @@ __global__ void silu_gate_kernel(const act_t* __restrict__ gate_up, act_t* __res
 }
 
 #if IB_ACT_BF16
-// Eight bfloat16 (16 bytes) per thread and step, for inner sizes that are multiples of 8.
-__global__ void silu_gate_vec8_kernel(const act_t* __restrict__ gate_up, act_t* __restrict__ out, int inner, long total8) {
+// Eight bfloat16 (16 bytes) per thread, for inner sizes that are multiples of 8: one row per blockIdx.y, so no
+// thread divides to find its row.  With thousands of rows this kernel is bound by its instructions, not by
+// memory, if exponential and division are the exact ones (about twenty instructions per element); the results
+// are rounded to bfloat16, so the fast forms (ex2- and rcp-based, two units in the last place of float32) give
+// the same bits but for a rare tie.
+__global__ void silu_gate_vec8_kernel(const act_t* __restrict__ gate_up, act_t* __restrict__ out, int inner) {
     ib_grid_dependency_sync();
     const int in8 = inner >> 3;
-    for (long i = (long)blockIdx.x * blockDim.x + threadIdx.x; i < total8; i += (long)gridDim.x * blockDim.x) {
-        const long r = i / in8;
-        const int j = (int)(i - r * in8);
-        const uint4 g = reinterpret_cast<const uint4*>(gate_up + r * 2 * inner)[j];
-        const uint4 u = reinterpret_cast<const uint4*>(gate_up + r * 2 * inner + inner)[j];
-        const __nv_bfloat162* gp = reinterpret_cast<const __nv_bfloat162*>(&g);
-        const __nv_bfloat162* up = reinterpret_cast<const __nv_bfloat162*>(&u);
-        uint4 o;
-        __nv_bfloat162* op = reinterpret_cast<__nv_bfloat162*>(&o);
+    const int j = blockIdx.x * blockDim.x + threadIdx.x;
+    if (j >= in8) return;
+    const long r = blockIdx.y;
+    const uint4 g = reinterpret_cast<const uint4*>(gate_up + r * 2 * inner)[j];
+    const uint4 u = reinterpret_cast<const uint4*>(gate_up + r * 2 * inner + inner)[j];
+    const __nv_bfloat162* gp = reinterpret_cast<const __nv_bfloat162*>(&g);
+    const __nv_bfloat162* up = reinterpret_cast<const __nv_bfloat162*>(&u);
+    uint4 o;
+    __nv_bfloat162* op = reinterpret_cast<__nv_bfloat162*>(&o);
 #pragma unroll
-        for (int k = 0; k < 4; ++k) {
-            const float2 gv = __bfloat1622float2(gp[k]), uv = __bfloat1622float2(up[k]);
-            op[k] = __floats2bfloat162_rn(gv.x / (1.0f + expf(-gv.x)) * uv.x, gv.y / (1.0f + expf(-gv.y)) * uv.y);
-        }
-        reinterpret_cast<uint4*>(out + r * inner)[j] = o;
+    for (int k = 0; k < 4; ++k) {
+        const float2 gv = __bfloat1622float2(gp[k]), uv = __bfloat1622float2(up[k]);
+        op[k] = __floats2bfloat162_rn(__fdividef(gv.x, 1.0f + __expf(-gv.x)) * uv.x,
+                                      __fdividef(gv.y, 1.0f + __expf(-gv.y)) * uv.y);
     }
+    reinterpret_cast<uint4*>(out + r * inner)[j] = o;
 }
 #endif
 
@@ -253,10 +257,13 @@ IB_EXPORT int ib_silu_gate(const void* gate_up, void* out, int n_rows, int inner
     const long total = (long)n_rows * inner;
 #if IB_ACT_BF16
     if ((inner & 7) == 0 && ib_aligned16(gate_up) && ib_aligned16(out)) {
-        const long total8 = total >> 3;
-        long b8 = (total8 + 255) / 256;
-        if (b8 > 148L * 32) b8 = 148L * 32;
-        ib_launch(silu_gate_vec8_kernel, (int)b8, 256, 0, stream, (const act_t*)gate_up, (act_t*)out, inner, total8);
+        const int in8 = inner >> 3;
+        const int threads = in8 >= 256 ? 256 : ((in8 + 31) / 32) * 32;
+        for (int r0 = 0; r0 < n_rows; r0 += 65535) {   // blockIdx.y holds at most 65,535 rows
+            const int rows = n_rows - r0 < 65535 ? n_rows - r0 : 65535;
+            ib_launch(silu_gate_vec8_kernel, dim3((in8 + threads - 1) / threads, rows), threads, 0, stream,
+                      (const act_t*)gate_up + (long)r0 * 2 * inner, (act_t*)out + (long)r0 * inner, inner);
+        }
         return ib_launch_status();
     }
 #endif

@@ -92,6 +92,29 @@ def test_silu_gate(dtype):
     assert rel_err(out, ref) < TOL[dtype]
 
 
+@pytest.mark.parametrize("dtype", DTYPES)
+@pytest.mark.parametrize("rows,inner", [(33, 152), (300, 1536), (5, 8)])
+def test_silu_gate_wide_rows(dtype, rows, inner):
+    """Inner sizes that are multiples of 8 (the form with sixteen bytes per thread in bfloat16), gates so large
+    and so small that the exponential overflows or vanishes, and every element on its own against the formula."""
+    from inferrs_b200 import kernels as K
+    gu = rand((rows, 2 * inner), dtype, 5, scale=3.0)
+    gu[0, :8] = torch.tensor([100.0, -100.0, 88.0, -88.0, 30.0, -30.0, 0.0, -0.0], dtype=dtype, device=dev())
+    gu[0, inner:inner + 8] = 1.5
+    out = torch.full((rows, inner), float("nan"), dtype=dtype, device=dev())
+    ref = torch.empty_like(out)
+    K.silu_gate(gu, out)
+    R.silu_gate(gu, ref)
+    assert not torch.isnan(out.float()).any()
+    assert rel_err(out, ref) < TOL[dtype]
+    want = torch.tensor([150.0, 0.0, 132.0, 0.0, 45.0, 0.0, 0.0, 0.0])
+    assert torch.allclose(out[0, :8].float().cpu(), want, rtol=1e-2, atol=1e-6)
+    g, u = gu[:, :inner].float(), gu[:, inner:].float()
+    exact = (g / (1.0 + torch.exp(-g)) * u)
+    worst = ((out.float() - exact).abs() / (exact.abs() + 1e-3)).max()
+    assert worst < (1e-5 if dtype == torch.float32 else 8e-3), worst     # bfloat16 keeps eight bits
+
+
 def _paged_setup(dtype, n_kv, d, page_size, lens, new, seed, n_pages=None):
     """Requests with lens[r] cached tokens of which the last new[r] are this step's rows."""
     g = torch.Generator().manual_seed(seed)
