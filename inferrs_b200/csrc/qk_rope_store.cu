@@ -220,11 +220,23 @@ __global__ void qk_norm_rope_store_d128_wide_kernel(
     const float4 cs = *reinterpret_cast<const float4*>(cos_table + (long)pos * 64 + e0);
     const float4 sn = *reinterpret_cast<const float4*>(sin_table + (long)pos * 64 + e0);
     float wq[8], wk[8];                          // norm weights of the two runs of four
+    {
+        const bool has_q = q_weight != nullptr && head0 < n_heads, has_k = k_weight != nullptr && head0 + HPW > n_heads;
+        auto four = [&](const WT* w, int at, float* out4) {   // w[at .. at + 3], at a multiple of four
+            if constexpr (sizeof(WT) == 2) {
+                const uint2 v = *reinterpret_cast<const uint2*>(w + at);
+                const float2 a = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(&v.x));
+                const float2 b = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(&v.y));
+                out4[0] = a.x; out4[1] = a.y; out4[2] = b.x; out4[3] = b.y;
+            } else {
+                const float4 v = *reinterpret_cast<const float4*>(w + at);
+                out4[0] = v.x; out4[1] = v.y; out4[2] = v.z; out4[3] = v.w;
+            }
+        };
 #pragma unroll
-    for (int e = 0; e < 8; ++e) {
-        const int at = (e < 4 ? e0 : 60 + e0) + e;   // e0 + e, or 64 + e0 + (e - 4)
-        wq[e] = (q_weight != nullptr && head0 < n_heads) ? ib_to_float(q_weight[at]) : 1.0f;
-        wk[e] = (k_weight != nullptr && head0 + HPW > n_heads) ? ib_to_float(k_weight[at]) : 1.0f;
+        for (int e = 0; e < 8; ++e) wq[e] = wk[e] = 1.0f;
+        if (has_q) { four(q_weight, e0, wq); four(q_weight, 64 + e0, wq + 4); }
+        if (has_k) { four(k_weight, e0, wk); four(k_weight, 64 + e0, wk + 4); }
     }
     ib_grid_dependency_wait();
     uint2 raw_lo[HPW / 2], raw_hi[HPW / 2];
@@ -261,7 +273,9 @@ __global__ void qk_norm_rope_store_d128_wide_kernel(
 #pragma unroll
         for (int o = 8; o > 0; o >>= 1) ss += __shfl_xor_sync(0xffffffffu, ss, o);   // over the head's sixteen lanes
         if (kind != 2 && w != nullptr) {
-            const float inv = 1.0f / sqrtf(ss / 128.0f + eps);
+            // the reciprocal square root in one step (two units in the last place of float32): with thousands of rows
+            // this kernel is bound by its instructions, and the result is rounded to bfloat16
+            const float inv = rsqrtf(ss * (1.0f / 128.0f) + eps);
 #pragma unroll
             for (int e = 0; e < 8; ++e) x[e] = x[e] * inv * (kind == 0 ? wq[e] : wk[e]);
         }
@@ -321,6 +335,7 @@ IB_EXPORT int ib_qk_norm_rope_store(const void* qkv, int row_stride, int n_rows,
         // few rows: one head per warp, for the shortest chain; many rows: eight heads per warp and sixteen bytes
         // per lane, for bytes in flight (the cache pages and the output must then be 16-byte aligned)
         if (n_rows >= 256 && (row_stride % 8) == 0 && ((uintptr_t)qkv % 16) == 0 && ((uintptr_t)q_out % 16) == 0 &&
+            ((uintptr_t)q_weight % 16) == 0 && ((uintptr_t)k_weight % 16) == 0 &&
             (!store_kv || (((uintptr_t)k_pages % 16) == 0 && ((uintptr_t)v_pages % 16) == 0))) {
             int warps = (heads_total + 7) / 8;
             if (warps > 8) warps = 8;
