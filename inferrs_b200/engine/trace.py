@@ -14,8 +14,9 @@ import sys
 import numpy as np
 import torch
 
+from ..cache.manager import CacheError
 from ..runtime import Runtime
-from .batch import StepEntry
+from .batch import BatchError, StepEntry
 from .loading import load_model_dir
 from .runner import ModelRunner
 
@@ -57,10 +58,21 @@ def main(argv=None) -> int:
             print(f"trace_run: line {line_no} is not a step: {e}", file=sys.stderr)
             return 2
         if entries:
-            for e in entries:
-                if not runner.has(e.rid):
-                    runner.admit(e.rid)
-            logits = runner.step(entries)
+            # A step that the cache cannot hold (more tokens than --max-tokens allows, more requests than
+            # --max-requests) or that is no step (a token outside the vocabulary, a wanted place outside the
+            # tokens) ends the replay with status 3 and one line that says why; the cache is as it was before it.
+            admitted = []
+            try:
+                for e in entries:
+                    if not runner.has(e.rid):
+                        runner.admit(e.rid)
+                        admitted.append(e.rid)
+                logits = runner.step(entries)
+            except (CacheError, BatchError, ValueError) as e:
+                for rid in admitted:
+                    runner.release(rid)
+                print(f"trace_run: step {step}: {e}", file=sys.stderr)
+                return 3
             if logits.shape[0] > 0:
                 arr = logits.to(torch.float32).cpu().numpy().astype("<f4", copy=False)
                 tmp = os.path.join(args.out, f"{step}.f32.tmp")

@@ -87,3 +87,20 @@ def test_step_without_wanted_rows_writes_no_file(model_dirs, tmp_path):
     assert sorted(os.listdir(out_dir)) == ["1.f32"]
     mcfg, w = plain_qwen3.read_model(model_dirs["A"])
     assert rel_err(read(out_dir, 1, CONFIG_A["vocab_size"])[0], plain_qwen3.forward(mcfg, w, toks)[19]) < 1e-4
+
+
+def test_a_step_that_does_not_fit_ends_the_replay_with_a_status(model_dirs, tmp_path):
+    """More tokens than --max-tokens gives pages for: the step before is answered, the step that does not fit is
+    not; the program says why on standard error and exits with status 3 (no traceback)."""
+    toks = random_tokens(200, CONFIG_A["vocab_size"], seed=2)
+    out_dir = str(tmp_path / "o")
+    p = subprocess.Popen([sys.executable, os.path.join(ROOT, "bin", "trace_run"), "--model", model_dirs["A"], "--dtype",
+                          "float32", "--out", out_dir, "--max-tokens", "128"],
+                         stdin=subprocess.PIPE, stdout=subprocess.PIPE, stderr=subprocess.PIPE, text=True)
+    steps = [{"step": 0, "entries": [{"id": "a", "tokens": toks[:100], "want": [99]}], "end": []},
+             {"step": 1, "entries": [{"id": "b", "tokens": toks[100:160], "want": [0]}], "end": []}]
+    out, err = p.communicate("".join(json.dumps(s) + "\n" for s in steps), timeout=300)
+    assert p.returncode == 3, (p.returncode, err[-500:])
+    assert out.split("\n")[0] == "done 0" and "done 1" not in out
+    assert "trace_run: step 1:" in err and "Traceback" not in err
+    assert sorted(os.listdir(out_dir)) == ["0.f32"]
