@@ -142,3 +142,17 @@ def test_steps_one_ahead_give_what_the_plain_loop_gives(seed):
     ahead = results[True][1]
     assert ahead.n_steps_ahead > 10 and ahead.runner.n_carried > 10
     assert results[False][1].n_steps_ahead == 0 and results[False][1].runner.n_carried == 0
+
+
+def test_carried_tokens_are_named_in_the_description():
+    """In a step's description the token ids come first, in the order of the entries; an entry whose token is still
+    on the device gets -1 - place there, and only an entry of one token may have a place."""
+    from inferrs_b200.engine.batch import StepEntry
+    from inferrs_b200.engine.graphs import name_carried_tokens
+    stage = torch.arange(100, 120, dtype=torch.int32)
+    entries = [StepEntry("a", [7], [0]), StepEntry("b", [1, 2, 3], []), StepEntry("c", [9], [0]), StepEntry("d", [4], [0])]
+    rows = name_carried_tokens(stage, entries, [2, -1, -1, 0])
+    assert rows == 6
+    assert stage.tolist()[:8] == [-3, 101, 102, 103, 104, -1, 106, 107]
+    with pytest.raises(ValueError, match="single token"):
+        name_carried_tokens(stage, entries, [-1, 1, -1, -1])
