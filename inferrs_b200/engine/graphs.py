@@ -1,4 +1,4 @@
-"""Decode steps as replayed CUDA graphs.
+"""Steps as replayed CUDA graphs: decode steps (``DecodeGraphs``) and steps with prompt portions (``PortionGraphs``).
 
 A step in which every request brings one token runs the same kernels with the same shapes every
 time; only the numbers in the step's description change.  Such a step is captured once per batch
@@ -11,7 +11,9 @@ fixed address: the description lives in one fixed int32 buffer, block tables are
 longest context, and the batch is padded with requests that own no pages.
 
 The description of a replayed step is written by the native cache manager straight into pinned host
-memory (``ibh_describe_decode``) and reaches the device in one asynchronous copy.
+memory (``ibh_describe_decode``, ``ibh_describe_step``) and reaches the device in one asynchronous copy.  A
+token that an earlier step sampled and the host has not read yet is named there by its place in that step's
+output; a small kernel puts the id itself there before the graph is replayed (``name_carried_tokens``).
 """
 from __future__ import annotations
 
