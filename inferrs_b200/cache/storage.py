@@ -68,8 +68,9 @@ class CacheStorage:
         for g, k in enumerate(keys):
             self.kv.append(torch.zeros((len(members[g]), 2, self.n_pages[g], k.n_kv_heads, page_size, k.head_dim),
                                        dtype=dtype, device=device))
+        # one slot more than there are requests: the requests that only pad a replayed step write their state there
         self.states: Dict[int, torch.Tensor] = {
-            cid: torch.zeros((max_requests,) + tuple(need.shape), dtype=need.dtype, device=device)
+            cid: torch.zeros((max_requests + 1,) + tuple(need.shape), dtype=need.dtype, device=device)
             for cid, need in state_needs.items()}
 
     def pages(self, cache_id: int) -> Tuple[torch.Tensor, torch.Tensor, int]:
@@ -85,6 +86,14 @@ class CacheStorage:
         """A new request takes the slot: its fixed-size states start at zero."""
         for t in self.states.values():
             t[slot].zero_()
+
+    def snapshot_states(self) -> Dict[int, torch.Tensor]:
+        """Copies of all fixed-size states (for a caller that has to run a step more than once)."""
+        return {cid: t.clone() for cid, t in self.states.items()}
+
+    def restore_states(self, saved: Dict[int, torch.Tensor]):
+        for cid, t in saved.items():
+            self.states[cid].copy_(t)
 
     def bytes_per_token(self) -> int:
         """Bytes of keys and values that one token adds, over all groups."""

@@ -87,7 +87,10 @@ __global__ void __launch_bounds__(THREADS, 2) decode_kernel(const __grid_constan
     // portions a list says which rows are single tokens and whose they are
     const int place = blockIdx.x, kvh = blockIdx.y, split = blockIdx.z;
     const int row = P.rows != nullptr ? P.rows[place] : place;
-    if (row < 0) return;
+    // A CTA that has nothing to do still waits for the kernels before this one: a grid that has let its
+    // dependents start must not complete before its own predecessors have, or the kernel after it could read
+    // what they have not written yet.
+    if (row < 0) { asm volatile("griddepcontrol.wait;" ::: "memory"); return; }
     const int req = P.reqs != nullptr ? P.reqs[place] : place;
     const int G = P.n_heads / P.n_kv_heads;
     const int pos = P.positions[row];
@@ -96,7 +99,7 @@ __global__ void __launch_bounds__(THREADS, 2) decode_kernel(const __grid_constan
     const int n_all = t_last - t_first;
     int n_splits = (n_all + P.min_tiles - 1) / P.min_tiles;
     if (n_splits > P.max_splits) n_splits = P.max_splits;
-    if (split >= n_splits) return;                           // an unused slice
+    if (split >= n_splits) { asm volatile("griddepcontrol.wait;" ::: "memory"); return; }   // an unused slice
     const int per = (n_all + n_splits - 1) / n_splits;
     const int t_begin = t_first + split * per;
     const int t_end = t_begin + per < t_last ? t_begin + per : t_last;
@@ -132,7 +135,10 @@ __global__ void __launch_bounds__(THREADS, 2) decode_kernel(const __grid_constan
             if (lane >= pages_per_tile) return 0;
             const int j = (t_begin + i) * KEYS + lane * P.page_size;
             int page = (j <= pos && j / P.page_size < P.max_pages) ? bt[j / P.page_size] : -1;
-            if (page < 0 || page >= P.n_pages) page = 0;   // beyond the request: masked, any finite data will do
+            // No page (beyond the request, or given back): the copy is aimed past the last page, where TMA reads
+            // nothing and fills the tile with zeros.  No query sees these keys, but their values are multiplied
+            // by a probability of zero, and what an earlier owner left in a page could be no number at all.
+            if (page < 0 || page >= P.n_pages) page = P.n_pages;
             return page;
         };
         int page_next = n_tiles > 0 ? lookup(0) : 0;
@@ -358,7 +364,7 @@ __global__ void __launch_bounds__(THREADS, 2) decode_kernel(const __grid_constan
             }
         }
     }
-    if (!ok || g_error != 0) {
+    if (!ok) {   // a wait of this CTA ran out: let its copies land before the shared memory is given back
         const unsigned long long t0 = global_ns();
         while (global_ns() - t0 < 2000000ull) __nanosleep(1000);
     }
@@ -404,12 +410,8 @@ IB_EXPORT int ib_paged_attention_decode(const void* q, const void* k_pages, cons
     P.min_tiles = min_tiles;
     P.scale_log2 = scale * 1.4426950408889634f;
     const size_t smem = 2 * dec::STAGES * dec::TILE_BYTES + 16 * dec::D * 2 + (2 * dec::STAGES + 1) * 8 + 1024;
-    static bool configured = false;
-    if (!configured) {
-        cudaError_t e = cudaFuncSetAttribute(dec::decode_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
-        if (e != cudaSuccess) return (int)e;
-        configured = true;
-    }
+    static IbDeviceSet configured;   // the attribute is kept per device
+    if (const int e = ib_allow_dynamic_smem(configured, dec::decode_kernel, smem)) return e;
     ib_launch(dec::decode_kernel, dim3(n_rows, n_kv_heads, max_splits), dec::THREADS, smem, stream, mk, mv, P);
     return ib_launch_status();
 }

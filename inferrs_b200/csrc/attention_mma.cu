@@ -346,13 +346,8 @@ static int launch_attention_mma(const AttnMmaParams& P, int n_tiles, cudaStream_
     constexpr int ROWS = DECODE ? 16 : 64;
     constexpr int ST = DECODE ? AM_DECODE_STAGES : 2;
     const size_t smem = (size_t)(ROWS * D + 2 * ST * AM_KEYS * D) * sizeof(__nv_bfloat16);
-    static bool configured = false;
-    if (!configured) {
-        cudaError_t e = cudaFuncSetAttribute(paged_attention_mma_kernel<D, DECODE>,
-                                             cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
-        if (e != cudaSuccess) return (int)e;
-        configured = true;
-    }
+    static IbDeviceSet configured;   // the attribute is kept per device
+    if (const int e = ib_allow_dynamic_smem(configured, paged_attention_mma_kernel<D, DECODE>, smem)) return e;
     const dim3 grid(n_tiles, P.n_kv_heads, DECODE ? P.n_splits : 1);
     ib_launch(paged_attention_mma_kernel<D, DECODE>, grid, AM_THREADS, smem, stream, P);
     return ib_launch_status();

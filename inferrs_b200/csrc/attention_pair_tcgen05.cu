@@ -142,7 +142,10 @@ __global__ void __launch_bounds__(THREADS, 1) attention_pair_kernel(const __grid
             if (lane >= pages_per_tile) return 0;
             const int j = (t_begin + i) * KEYS + lane * P.page_size;
             int page = (j <= pmax && j / P.page_size < P.max_pages) ? bt[j / P.page_size] : -1;
-            if (page < 0 || page >= P.n_pages) page = 0;   // never seen by a query; any finite data will do
+            // No page (beyond the request, or given back): the copy is aimed past the last page, where TMA reads
+            // nothing and fills the tile with zeros.  No query sees these keys, but their values are multiplied
+            // by a probability of zero, and what an earlier owner left in a page could be no number at all.
+            if (page < 0 || page >= P.n_pages) page = P.n_pages;
             return page;
         };
         const bool keys = warp == 8;
@@ -334,7 +337,7 @@ __global__ void __launch_bounds__(THREADS, 1) attention_pair_kernel(const __grid
         }
     }
 
-    if (!ok || g_error != 0) {
+    if (!ok) {   // a wait of this CTA ran out: copies still in flight get time to land before it leaves
         const unsigned long long t0 = global_ns();
         while (global_ns() - t0 < 2000000ull) __nanosleep(1000);
     }
@@ -391,12 +394,8 @@ IB_EXPORT int ib_paged_attention_pair_tcgen05(const void* q, const void* k_pages
     P.n_pages = n_pages; P.n_heads = n_heads; P.n_kv_heads = n_kv_heads; P.window = window;
     P.scale_log2 = scale * 1.4426950408889634f;
     const size_t smem = 2 * fp::Q_TILE + 4 * fp::P_TILE + 4 * fp::KV_TILE + 26 * 8 + fp::SMEM_SLACK;
-    static bool configured = false;
-    if (!configured) {
-        cudaError_t e = cudaFuncSetAttribute(fp::attention_pair_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
-        if (e != cudaSuccess) return (int)e;
-        configured = true;
-    }
+    static IbDeviceSet configured;   // the attribute is kept per device
+    if (const int e = ib_allow_dynamic_smem(configured, fp::attention_pair_kernel, smem)) return e;
     ib_launch(fp::attention_pair_kernel, dim3(n_tiles, n_kv_heads), fp::THREADS, smem, stream, mq, mk, mv, P);
     return ib_launch_status();
 }

@@ -47,12 +47,6 @@ __device__ __forceinline__ bool mbar_wait(unsigned bar, unsigned parity, int cod
 
 // the two warps that share the rows 32 q .. 32 q + 31 (one per half of the columns) meet: barriers 2..5
 __device__ __forceinline__ void pair_sync(int q) { asm volatile("bar.sync %0, 64;" ::"r"(2 + q) : "memory"); }
-#ifdef IB_ATTN_EVENTS
-__device__ long long g_ev[64 * 32];   // [event code][key tile]: clock64 of the chosen CTA's chosen lanes
-#define EV(code, i) do { if (rec && (i) < 32) g_ev[(code) * 32 + (i)] = clock64(); } while (0)
-#else
-#define EV(code, i) do { } while (0)
-#endif
 
 struct Params {
     const int* block_table;   // [R, max_pages]
@@ -89,9 +83,6 @@ __global__ void __launch_bounds__(THREADS, 1) attention_kernel(const __grid_cons
 
     ib_grid_dependency_sync();
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-#ifdef IB_ATTN_EVENTS
-    const bool rec = blockIdx.x == 0 && blockIdx.y == 0 && lane == 0 && (warp == 0 || warp == 4 || warp >= 8);
-#endif
     // the last tiles of a prompt see the most keys: they are started first, so that the grid's tail is short
     const int tile = gridDim.x - 1 - blockIdx.x, kvh = blockIdx.y;
     const int req = P.tile_req[tile], row0 = P.tile_row0[tile];
@@ -140,7 +131,10 @@ __global__ void __launch_bounds__(THREADS, 1) attention_kernel(const __grid_cons
             if (lane >= pages_per_tile) return 0;
             const int j = (t_begin + i) * KEYS + lane * P.page_size;
             int page = (j <= pmax && j / P.page_size < P.max_pages) ? bt[j / P.page_size] : -1;
-            if (page < 0 || page >= P.n_pages) page = 0;   // never seen by a query; any finite data will do
+            // No page (beyond the request, or given back): the copy is aimed past the last page, where TMA reads
+            // nothing and fills the tile with zeros.  No query sees these keys, but their values are multiplied
+            // by a probability of zero, and what an earlier owner left in a page could be no number at all.
+            if (page < 0 || page >= P.n_pages) page = P.n_pages;
             return page;
         };
         auto load_tile = [&](int i, int page, bool keys) {
@@ -167,7 +161,6 @@ __global__ void __launch_bounds__(THREADS, 1) attention_kernel(const __grid_cons
             if (i >= 2 && ok && !mbar_wait(empty0 + 8 * (i & 1), ((i >> 1) - 1) & 1, 1)) ok = false;
             ok = __all_sync(0xffffffffu, ok);
             if (!ok) break;
-            EV(keys ? 10 : 11, i);
             load_tile(i, page, keys);
             page = page_next;
         }
@@ -185,7 +178,6 @@ __global__ void __launch_bounds__(THREADS, 1) attention_kernel(const __grid_cons
                 if (!mbar_wait(k_full0 + 8 * s, (i >> 1) & 1, 2)) { ok = false; break; }
                 if (i >= 2 && !mbar_wait(s_empty0 + 8 * s, ((i >> 1) - 1) & 1, 3)) { ok = false; break; }
                 fence_after();
-                EV(20, i);
 #pragma unroll
                 for (int k = 0; k < D / 16; ++k) {
                     const unsigned off = (k >> 2) * HALF_BYTES + (k & 3) * 32;
@@ -198,12 +190,9 @@ __global__ void __launch_bounds__(THREADS, 1) attention_kernel(const __grid_cons
         } else if (warp == 11 && lane == 0) {
             for (int i = 0; i < n_tiles; ++i) {
                 const int s = i & 1;
-                EV(21, i);
                 if (!mbar_wait(p_full0 + 8 * s, (i >> 1) & 1, 4)) { ok = false; break; }
-                EV(22, i);
                 if (!mbar_wait(v_full0 + 8 * s, (i >> 1) & 1, 2)) { ok = false; break; }
                 fence_after();
-                EV(23, i);
 #pragma unroll
                 for (int k = 0; k < KEYS / 16; ++k) {
                     const unsigned aoff = (k >> 2) * HALF_BYTES + (k & 3) * 32;   // P: K-major, 16 keys = 32 bytes
@@ -213,7 +202,6 @@ __global__ void __launch_bounds__(THREADS, 1) attention_kernel(const __grid_cons
                 }
                 umma_commit(pv_full0 + 8 * s);
                 umma_commit(v_empty0 + 8 * s);    // V(i) is free once these products are done
-                EV(24, i);
             }
         }
     } else if (warp < 8) {
@@ -244,16 +232,13 @@ __global__ void __launch_bounds__(THREADS, 1) attention_kernel(const __grid_cons
         // partner at the named barrier the same number of times; the output is not stored then.
         for (int i = 0; i < n_tiles; ++i) {
             const int s = i & 1;
-            EV(30 + ch, i);
             if (ok && !mbar_wait(s_full0 + 8 * s, (i >> 1) & 1, 5)) ok = false;
             fence_after();
-            EV(32 + ch, i);
             const int key0 = (t_begin + i) * KEYS + ch * 64;
             unsigned a[32], b[32];
             tmem_ld32_issue(tmem + lane_addr + s * 128 + ch * 64, a);
             tmem_ld32_issue(tmem + lane_addr + s * 128 + ch * 64 + 32, b);
             tmem_ld_wait();
-            EV(34 + ch, i);
             // a tile whose 64 keys this row sees in full needs no comparisons (all tiles but the first and last few)
             const bool all_visible = key0 >= lo && key0 + 63 <= pos;
             // (four running maxima, and four running sums below: one chain of 64 dependent operations would
@@ -278,9 +263,7 @@ __global__ void __launch_bounds__(THREADS, 1) attention_kernel(const __grid_cons
             // tile's barrier, which this thread passes before it writes that buffer again two tiles on)
             float* xb = xchg + (i & 1) * 256;
             xb[ch * 128 + r] = mx;
-            EV(36 + ch, i);
             pair_sync(warp & 3);
-            EV(38 + ch, i);
             mx = fmaxf(mx, xb[(ch ^ 1) * 128 + r]) * P.scale_log2;
             const float m_new = fmaxf(m, mx);
             const float m_safe = m_new == -INFINITY ? 0.0f : m_new;
@@ -309,15 +292,12 @@ __global__ void __launch_bounds__(THREADS, 1) attention_kernel(const __grid_cons
             asm volatile("fence.proxy.async.shared::cta;" ::: "memory");   // generic writes -> the tensor core's reads
             __syncwarp();
             if (lane == 0) { mbar_arrive(s_empty0 + 8 * s); mbar_arrive(p_full0 + 8 * s); }
-            EV(40 + ch, i);
             // the product of the tile before this one has had this tile's softmax to finish
             if (i > 0) {
                 if (ok && !mbar_wait(pv_full0 + 8 * ((i - 1) & 1), ((i - 1) >> 1) & 1, 6)) ok = false;
                 fence_after();
-                EV(42 + ch, i);
                 add_product(i - 1, corr_pending);
                 fence_before();
-                EV(44 + ch, i);
             }
             corr_pending = corr;
         }
@@ -349,7 +329,7 @@ __global__ void __launch_bounds__(THREADS, 1) attention_kernel(const __grid_cons
         }
     }
 
-    if (!ok || g_error != 0) {
+    if (!ok) {   // a wait of this CTA ran out: copies still in flight get time to land before it leaves
         const unsigned long long t0 = global_ns();
         while (global_ns() - t0 < 2000000ull) __nanosleep(1000);
     }
@@ -361,15 +341,6 @@ __global__ void __launch_bounds__(THREADS, 1) attention_kernel(const __grid_cons
     }
 }
 
-#ifdef IB_ATTN_EVENTS
-}  // namespace fa
-IB_EXPORT int ib_attention_events(long long* dst, int cap) {
-    if (cap < 64 * 32) return -1;
-    cudaMemcpyFromSymbol(dst, fa::g_ev, sizeof(long long) * 64 * 32);
-    return 64 * 32;
-}
-namespace fa {
-#endif
 }  // namespace fa
 
 // Prefill-form attention for head size 128, bfloat16: tile i holds up to 128/G tokens of request tile_req[i]
@@ -415,12 +386,8 @@ IB_EXPORT int ib_paged_attention_tcgen05(const void* q, const void* k_pages, con
     P.n_pages = n_pages; P.n_heads = n_heads; P.n_kv_heads = n_kv_heads; P.window = window;
     P.scale_log2 = scale * 1.4426950408889634f;
     const size_t smem = 7 * fa::TILE_BYTES + 18 * 8 + 4 * 128 * 4 + fa::SMEM_SLACK;
-    static bool configured = false;
-    if (!configured) {
-        cudaError_t e = cudaFuncSetAttribute(fa::attention_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
-        if (e != cudaSuccess) return (int)e;
-        configured = true;
-    }
+    static IbDeviceSet configured;   // the attribute is kept per device
+    if (const int e = ib_allow_dynamic_smem(configured, fa::attention_kernel, smem)) return e;
     ib_launch(fa::attention_kernel, dim3(n_tiles, n_kv_heads), fa::THREADS, smem, stream, mq, mk, mv, P);
     return ib_launch_status();
 }

@@ -10,6 +10,8 @@
 #include <cuda_runtime.h>
 #include <stdint.h>
 
+#include <atomic>
+
 #ifndef IB_ACT_BF16
 #error "build with -DIB_ACT_BF16=0 or -DIB_ACT_BF16=1"
 #endif
@@ -101,6 +103,24 @@ static inline void ib_launch(void (*kernel)(KArgs...), dim3 grid, dim3 block, si
     cfg.attrs = attr;
     cfg.numAttrs = ib_pdl_enabled ? 1 : 0;
     cudaLaunchKernelEx(&cfg, kernel, static_cast<KArgs>(args)...);
+}
+
+// Dynamic shared memory beyond 48 KB has to be allowed per kernel and per device.  `done` remembers the devices
+// of this process on which a kernel has it already (one bit each; a device beyond the 64th is set every time).
+// Setting it twice is harmless, so two threads that meet here need no lock.
+struct IbDeviceSet { std::atomic<unsigned long long> bits{0}; };
+
+template <typename Kernel>
+static inline int ib_allow_dynamic_smem(IbDeviceSet& done, Kernel kernel, size_t bytes) {
+    int dev = 0;
+    cudaError_t e = cudaGetDevice(&dev);
+    if (e != cudaSuccess) return (int)e;
+    const bool tracked = dev >= 0 && dev < 64;
+    if (tracked && ((done.bits.load(std::memory_order_acquire) >> dev) & 1ull)) return IB_OK;
+    e = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)bytes);
+    if (e != cudaSuccess) return (int)e;
+    if (tracked) done.bits.fetch_or(1ull << dev, std::memory_order_release);
+    return IB_OK;
 }
 
 static inline int ib_launch_status() {

@@ -12,30 +12,32 @@ int ib_pdl_enabled = 0;
 IB_EXPORT void ib_set_pdl(int on) { ib_pdl_enabled = on; }
 
 // ---------------------------------------------------------------------------
-// Embedding: out[row, :] = table[ids[row], :]   (no scale)
+// Embedding: out[row, :] = table[ids[row], :] * scale   (the product is formed in float32; scale 1 for
+// architectures that do not scale their embeddings)
 // ---------------------------------------------------------------------------
 template <typename WT>
 __global__ void embedding_gather_kernel(const WT* __restrict__ table, const int* __restrict__ ids,
-                                        float* __restrict__ out, int width, int vocab) {
+                                        float* __restrict__ out, int width, int vocab, float scale) {
     ib_grid_dependency_sync();
     const int row = blockIdx.x;
     const int id = ids[row];
     const bool ok = id >= 0 && id < vocab;  // the host refuses such ids before the launch
     const WT* src = table + (size_t)(ok ? id : 0) * width;
     float* dst = out + (size_t)row * width;
-    for (int j = threadIdx.x; j < width; j += blockDim.x) dst[j] = ok ? ib_to_float(src[j]) : 0.0f;
+    for (int j = threadIdx.x; j < width; j += blockDim.x) dst[j] = ok ? ib_to_float(src[j]) * scale : 0.0f;
 }
 
 IB_EXPORT int ib_embedding_gather(const void* table, int table_is_f32, const int* ids, float* out, int n_rows,
-                                  int width, int vocab, cudaStream_t stream) {
+                                  int width, int vocab, float scale, cudaStream_t stream) {
     if (n_rows <= 0) return IB_OK;
     if (width <= 0 || vocab <= 0) return IB_ERR_ARGUMENT;
     const int threads = width >= 1024 ? 256 : 128;
     if (table_is_f32)
-        ib_launch(embedding_gather_kernel<float>, n_rows, threads, 0, stream, (const float*)table, ids, out, width, vocab);
+        ib_launch(embedding_gather_kernel<float>, n_rows, threads, 0, stream, (const float*)table, ids, out, width, vocab,
+                  scale);
     else
         ib_launch(embedding_gather_kernel<__nv_bfloat16>, n_rows, threads, 0, stream, (const __nv_bfloat16*)table, ids, out,
-                  width, vocab);
+                  width, vocab, scale);
     return ib_launch_status();
 }
 
@@ -187,6 +189,89 @@ IB_EXPORT int ib_add_rms_norm(float* residual, const void* delta, const void* we
     else
         ib_launch(add_rms_norm_kernel<__nv_bfloat16>, n_rows, threads, 0, stream, residual, (const act_t*)delta,
                   (const __nv_bfloat16*)weight, (act_t*)out, rows, width, eps);
+    return ib_launch_status();
+}
+
+// ---------------------------------------------------------------------------
+// A norm on a sub-layer's output (before it is added to the residual stream): out = x / sqrt(mean(x^2) + eps) * w
+// for rows of act_t.  And the form of the fused kernel above for a sub-layer without a norm: x += delta, out = x
+// as act_t.
+// ---------------------------------------------------------------------------
+template <typename WT>
+__global__ void rms_norm_rows_kernel(const act_t* __restrict__ x, const WT* __restrict__ weight,
+                                     act_t* __restrict__ out, int width, float eps) {
+    __shared__ float red[32];
+    ib_grid_dependency_sync();
+    const act_t* src = x + (size_t)blockIdx.x * width;
+    float ss = 0.0f;
+    for (int j = threadIdx.x; j < width; j += blockDim.x) {
+        const float v = ib_to_float(src[j]);
+        ss += v * v;
+    }
+    ss = ib_block_sum(ss, red);
+    const float inv = 1.0f / sqrtf(ss / (float)width + eps);
+    act_t* dst = out + (size_t)blockIdx.x * width;
+    for (int j = threadIdx.x; j < width; j += blockDim.x)
+        dst[j] = ib_from_float<act_t>(ib_to_float(src[j]) * inv * ib_to_float(weight[j]));
+}
+
+IB_EXPORT int ib_rms_norm_rows(const void* x, const void* weight, int weight_is_f32, void* out, int n_rows, int width,
+                               float eps, cudaStream_t stream) {
+    if (n_rows <= 0) return IB_OK;
+    if (width <= 0 || weight == nullptr) return IB_ERR_ARGUMENT;
+    const int threads = width >= 2048 ? 512 : (width >= 512 ? 256 : 128);
+    if (weight_is_f32)
+        ib_launch(rms_norm_rows_kernel<float>, n_rows, threads, 0, stream, (const act_t*)x, (const float*)weight,
+                  (act_t*)out, width, eps);
+    else
+        ib_launch(rms_norm_rows_kernel<__nv_bfloat16>, n_rows, threads, 0, stream, (const act_t*)x,
+                  (const __nv_bfloat16*)weight, (act_t*)out, width, eps);
+    return ib_launch_status();
+}
+
+__global__ void add_cast_kernel(float* __restrict__ residual, const act_t* __restrict__ delta, act_t* __restrict__ out,
+                                const int* __restrict__ rows, int width) {
+    ib_grid_dependency_sync();
+    const int r = blockIdx.x;
+    const int src = rows ? rows[r] : r;
+    float* res = residual + (size_t)src * width;
+    const act_t* del = delta ? delta + (size_t)src * width : nullptr;
+    act_t* dst = out + (size_t)r * width;
+    for (int j = threadIdx.x; j < width; j += blockDim.x) {
+        float v = res[j];
+        if (del) v += ib_to_float(del[j]);
+        if (del && rows == nullptr) res[j] = v;
+        dst[j] = ib_from_float<act_t>(v);
+    }
+}
+
+IB_EXPORT int ib_add_cast(float* residual, const void* delta, void* out, const int* rows, int n_rows, int width,
+                          cudaStream_t stream) {
+    if (n_rows <= 0) return IB_OK;
+    if (width <= 0) return IB_ERR_ARGUMENT;
+    ib_launch(add_cast_kernel, n_rows, width >= 1024 ? 256 : 128, 0, stream, residual, (const act_t*)delta, (act_t*)out,
+              rows, width);
+    return ib_launch_status();
+}
+
+// ---------------------------------------------------------------------------
+// What some architectures do to their logits, in place on float32: x *= scale, then, with cap > 0,
+// x = cap * tanh(x / cap).
+// ---------------------------------------------------------------------------
+__global__ void logit_scale_softcap_kernel(float* __restrict__ logits, long total, float scale, float cap) {
+    ib_grid_dependency_sync();
+    for (long i = (long)blockIdx.x * blockDim.x + threadIdx.x; i < total; i += (long)gridDim.x * blockDim.x) {
+        float v = logits[i] * scale;
+        if (cap > 0.0f) v = cap * tanhf(v / cap);
+        logits[i] = v;
+    }
+}
+
+IB_EXPORT int ib_logit_scale_softcap(float* logits, long total, float scale, float cap, cudaStream_t stream) {
+    if (total <= 0) return IB_OK;
+    long blocks = (total + 255) / 256;
+    if (blocks > 148L * 16) blocks = 148L * 16;
+    ib_launch(logit_scale_softcap_kernel, (int)blocks, 256, 0, stream, logits, total, scale, cap);
     return ib_launch_status();
 }
 

@@ -80,16 +80,6 @@ struct Params {
     int inner;   // gated form: rows of the gate matrix; the up matrix follows it in w
 };
 
-#ifdef IB_GEMM_TIMELINE
-// A build for looking at how launches overlap: every CTA records when it started, when its predecessor was
-// done, when its first tile had landed, when its accumulator was complete and when it left (globaltimer, ns).
-#define TL_MAX 65536
-__device__ unsigned long long g_tl[TL_MAX * 8];
-__device__ unsigned g_tl_count = 0;
-#define TL_MARK(slot, i) do { if ((slot) < TL_MAX) g_tl[(size_t)(slot) * 8 + (i)] = global_ns(); } while (0)
-#else
-#define TL_MARK(slot, i) do { } while (0)
-#endif
 
 template <int BN, int STAGES, int MODE>
 __global__ void __launch_bounds__(THREADS, (BN <= 64 ? 2 : 1)) gemm_kernel(const __grid_constant__ CUtensorMap map_w,
@@ -117,20 +107,6 @@ __global__ void __launch_bounds__(THREADS, (BN <= 64 ? 2 : 1)) gemm_kernel(const
     // kernel in turn may have been started before its predecessor finished, so it reads the weights (which no
     // kernel writes) at once but touches x, y and the rest only after griddepcontrol.wait.
     asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
-#ifdef IB_GEMM_TIMELINE
-    __shared__ unsigned tl_slot_s;
-    if (threadIdx.x == 0) {
-        tl_slot_s = atomicAdd(&g_tl_count, 1u);
-        if (tl_slot_s < TL_MAX) {
-            unsigned smid;
-            asm volatile("mov.u32 %0, %%smid;" : "=r"(smid));
-            g_tl[(size_t)tl_slot_s * 8 + 5] = smid;
-            g_tl[(size_t)tl_slot_s * 8 + 6] = ((unsigned long long)gridDim.x << 32) | ((unsigned long long)gridDim.z << 16) | (unsigned)p.num_kb;
-            g_tl[(size_t)tl_slot_s * 8 + 7] = ((unsigned long long)blockIdx.x << 16) | blockIdx.z;
-        }
-        TL_MARK(tl_slot_s, 0);
-    }
-#endif
     if (threadIdx.x == 0) {
         for (int s = 0; s < STAGES; ++s) { mbar_init(full0 + 8 * s, 1); mbar_init(empty0 + 8 * s, 1); }
         mbar_init(accum, 1);
@@ -148,9 +124,6 @@ __global__ void __launch_bounds__(THREADS, (BN <= 64 ? 2 : 1)) gemm_kernel(const
     // A CTA's shared memory may be written by its cluster only once the CTA runs: every CTA says so here and
     // looks at the others' word just before its first store to them, long after they have given it.
     if (splits > 1 && SCATTER) cluster_arrive();
-#ifdef IB_GEMM_TIMELINE
-    const unsigned tl_slot = tl_slot_s;
-#endif
 
     if (warp == 0) {
         if (lane == 0 && nkb > 0) {
@@ -172,7 +145,6 @@ __global__ void __launch_bounds__(THREADS, (BN <= 64 ? 2 : 1)) gemm_kernel(const
                 load_w(i, i);
             }
             asm volatile("griddepcontrol.wait;" ::: "memory");
-            TL_MARK(tl_slot, 1);
             for (int i = 0; i < head; ++i)
                 tma_load_2d(smem_u32(b_tiles + i * B_BYTES), &map_x, (kb0 + i) * BK, tile_t * BN, full0 + 8 * i);
             for (int i = head; i < nkb; ++i) {
@@ -189,7 +161,6 @@ __global__ void __launch_bounds__(THREADS, (BN <= 64 ? 2 : 1)) gemm_kernel(const
             for (int i = 0; i < nkb; ++i) {
                 const int s = i % STAGES;
                 if (!mbar_wait(full0 + 8 * s, (i / STAGES) & 1, 2)) { ok = false; break; }
-                if (i == 0) TL_MARK(tl_slot, 2);
                 fence_after();
                 const unsigned long long da = desc_k_major(smem_u32(a_tiles + s * A_BYTES));
                 const unsigned long long db = desc_k_major(smem_u32(b_tiles + s * B_BYTES));
@@ -221,7 +192,6 @@ __global__ void __launch_bounds__(THREADS, (BN <= 64 ? 2 : 1)) gemm_kernel(const
             asm volatile("griddepcontrol.wait;" ::: "memory");   // y may still be read by the predecessor
             ok = nkb > 0 ? mbar_wait(accum, 0, 3) : true;
             ok = __all_sync(0xffffffffu, ok);   // one answer per warp: the tensor-memory loads below are warp-wide
-            if (threadIdx.x == 64) TL_MARK(tl_slot, 3);
             fence_after();
             float* up_vals = recv;              // [BN][64]
             if (ok && q >= 2) {
@@ -266,7 +236,6 @@ __global__ void __launch_bounds__(THREADS, (BN <= 64 ? 2 : 1)) gemm_kernel(const
         asm volatile("griddepcontrol.wait;" ::: "memory");   // y may still be read by the predecessor
         ok = nkb > 0 ? mbar_wait(accum, 0, 3) : true;
         ok = __all_sync(0xffffffffu, ok);       // one answer per warp: the tensor-memory loads below are warp-wide
-        if (threadIdx.x == 64) TL_MARK(tl_slot, 3);
         fence_after();
         if (ok) {
 #pragma unroll 1
@@ -361,14 +330,13 @@ __global__ void __launch_bounds__(THREADS, (BN <= 64 ? 2 : 1)) gemm_kernel(const
 
     }
 
-    if (!ok || g_error != 0) {
+    if (!ok) {   // a wait of this CTA ran out: copies still in flight get time to land before it leaves
         // a wait ran out somewhere: give copies that are still in flight time to land before the CTA leaves
         const unsigned long long t0 = global_ns();
         while (global_ns() - t0 < 2000000ull) __nanosleep(1000);
     }
     fence_before();
     __syncthreads();
-    if (threadIdx.x == 0) TL_MARK(tl_slot, 4);
     if (warp == 1) {
         fence_after();
         asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem), "r"(TMEM_COLS) : "memory");
@@ -392,12 +360,8 @@ template <int BN, int STAGES, int MODE = 0>
 static int launch(const CUtensorMap& mw, const CUtensorMap& mx, const Params& p, int splits, cudaStream_t stream) {
     constexpr size_t smem = (size_t)STAGES * (A_BYTES + BN * BK * 2) + (2 * STAGES + 2) * 8 + 1024 +
                             (BN <= 32 ? (size_t)BN * BM * 4 : 0);   // + the parts received from the cluster
-    static bool configured = false;
-    if (!configured) {
-        cudaError_t e = cudaFuncSetAttribute(gemm_kernel<BN, STAGES, MODE>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
-        if (e != cudaSuccess) return (int)e;
-        configured = true;
-    }
+    static IbDeviceSet configured;   // the attribute is kept per device
+    if (const int e = ib_allow_dynamic_smem(configured, gemm_kernel<BN, STAGES, MODE>, smem)) return e;
     cudaLaunchConfig_t cfg = {};
     const int rows_per_tile = MODE == 1 ? 64 : BM;
     cfg.gridDim = dim3((p.n_out + rows_per_tile - 1) / rows_per_tile, (p.n_tok + BN - 1) / BN, splits);
@@ -488,18 +452,5 @@ IB_EXPORT int ib_gemm_tcgen05_error(int reset) {
     return v;
 }
 
-#ifdef IB_GEMM_TIMELINE
-// Copies the records of up to `max_ctas` CTAs (8 words each) to `dst` (host) and clears them; returns how many.
-IB_EXPORT int ib_gemm_timeline(unsigned long long* dst, int max_ctas) {
-    unsigned n = 0;
-    if (cudaMemcpyFromSymbol(&n, tc::g_tl_count, sizeof(n)) != cudaSuccess) return -1;
-    if (n > TL_MAX) n = TL_MAX;
-    if ((int)n > max_ctas) n = max_ctas;
-    if (n && cudaMemcpyFromSymbol(dst, tc::g_tl, (size_t)n * 8 * sizeof(unsigned long long)) != cudaSuccess) return -1;
-    const unsigned zero = 0;
-    cudaMemcpyToSymbol(tc::g_tl_count, &zero, sizeof(zero));
-    return (int)n;
-}
-#endif
 
 #endif

@@ -307,7 +307,8 @@ IBH_EXPORT int ibh_cache_check(void* h, char* msg, int cap) {
 //   token ids [bucket] | positions [bucket] | request of each row [bucket] | first row of each request [bucket + 1]
 //   | keys each request sees [bucket] | state slots [bucket] | rows whose logits are made [bucket]
 //   | per group: block tables [bucket, fixed_pages[g]]
-// A request that only fills the batch has token 0 at position 0, one key and no pages (-1 everywhere).
+// A request that only fills the batch has token 0 at position 0, one key, no pages (-1 everywhere) and state slot
+// max_requests, which no request ever gets (the state tensors have that one slot more).
 // The pages for the step's tokens are reserved already.  Returns the count of numbers written, or an error with
 // the index of the offending entry in *bad.
 IBH_EXPORT int ibh_describe_decode(void* h, int n, const int64_t* rids, const int* tokens, int bucket,
@@ -334,6 +335,7 @@ IBH_EXPORT int ibh_describe_decode(void* h, int n, const int64_t* rids, const in
         out[off[2] + i] = i;
         out[off[3] + i] = i;
         out[off[4] + i] = 1;
+        out[off[5] + i] = c->max_requests;   // a request that only fills the batch: the slot that no request ever gets
         out[off[6] + i] = i;
     }
     out[off[3] + bucket] = bucket;
@@ -427,6 +429,7 @@ IBH_EXPORT int ibh_describe_step(void* h, int n, const int64_t* rids, const int*
     int* single_rows = out + off[tiles_at + 2 * n_tile_sizes];
     int* single_reqs = out + off[tiles_at + 2 * n_tile_sizes + 1];
     for (int j = 0; j < pad_requests; ++j) single_rows[j] = single_reqs[j] = -1;
+    for (int j = 0; j < pad_requests; ++j) slots[j] = c->max_requests;   // the slot that no request ever gets
 
     std::vector<int> n_tiles(n_tile_sizes, 0);
     int row = 0, tok_at = 0, want_at = 0, n_logit = 0, n_single = 0;

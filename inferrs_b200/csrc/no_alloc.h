@@ -43,8 +43,9 @@ extern "C" {
 //   out          [n_rows, n_heads * head_dim] bfloat16
 //
 // It calls no cudaMalloc, cudaFree or other allocating routine.  The first call on a device looks
-// up the device address of the built-in scratch (cudaGetSymbolAddress, with that device current)
-// and keeps it; make that first call before any stream capture begins on that device.
+// up the device address of the built-in scratch (cudaGetSymbolAddress, with that device current),
+// allows the kernel its dynamic shared memory on that device, and keeps both per device; make
+// that first call before any stream capture begins on that device.
 //
 // All calls on a device share the one scratch array.  Nothing in it has to start at zero (every
 // cell that is read has been written by the same call), and what a call leaves there is of no use

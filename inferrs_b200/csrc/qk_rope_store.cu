@@ -31,6 +31,14 @@ IB_EXPORT int ib_row_fault(int reset) {
     return v;
 }
 
+// A request's last row of the step clears the places behind its value in the value's page.  The attention kernels
+// that fetch whole pages give those places a probability of zero, but zero times what an earlier owner of the
+// page may have left there (an infinity, no number at all) would not be zero.  Keys need no clearing: a score is
+// replaced, not multiplied, where a key is not visible.
+__device__ __forceinline__ bool ib_last_row_of_request(const int* __restrict__ row_request, int row, int n_rows) {
+    return row + 1 >= n_rows || row_request[row + 1] != row_request[row];
+}
+
 template <typename WT>
 __global__ void qk_norm_rope_store_kernel(
     const act_t* __restrict__ qkv, int row_stride, int n_heads, int n_kv_heads, int head_dim, int store_kv,
@@ -59,6 +67,7 @@ __global__ void qk_norm_rope_store_kernel(
         if (page >= 0 && page < n_pages)
             kv_base = ((long)page * n_kv_heads * page_size + (pos % page_size)) * d;
     }
+    const bool clear_tail = kv_base >= 0 && ib_last_row_of_request(row_request, row, gridDim.x);
 
     // one warp per head: blockIdx.y picks the group of QRS_WARPS heads
     for (int head = blockIdx.y * QRS_WARPS + warp; head < heads_total; head += heads_total) {
@@ -80,6 +89,10 @@ __global__ void qk_norm_rope_store_kernel(
         }
         if (kind == 2) {
             for (int j = lane; j < d; j += 32) dst[j] = ib_from_float<act_t>(sh[j]);
+            if (clear_tail) {
+                const int behind = (page_size - 1 - pos % page_size) * d;
+                for (int j = lane; j < behind; j += 32) dst[d + j] = ib_from_float<act_t>(0.0f);
+            }
             __syncwarp();
             continue;
         }
@@ -124,13 +137,14 @@ __global__ void qk_norm_rope_store_d128_kernel(
     const int head0 = (blockIdx.y * QRS_WARPS + warp) * HPW;
     if (head0 >= heads_total) return;
     const int pos = positions[row];
-    if (pos < 0 || pos >= table_rows) { ib_note_row_fault(row); return; }
+    if (pos < 0 || pos >= table_rows) { ib_note_row_fault(row); ib_grid_dependency_wait(); return; }
     long kv_base = -1;  // element offset of (page, kv head 0, place in the page, 0)
     if (store_kv && head0 + HPW > n_heads) {
         const int req = row_request[row];
         const int page = pos / page_size < max_pages ? block_table[(long)req * max_pages + pos / page_size] : -1;
         if (page >= 0 && page < n_pages) kv_base = ((long)page * n_kv_heads * page_size + (pos % page_size)) * 128;
     }
+    const bool clear_tail = kv_base >= 0 && ib_last_row_of_request(row_request, row, gridDim.x);
     // element i < 64 pairs with i + 64: lanes 0..15 hold the first halves, lanes 16..31 the second
     const int i0 = 4 * (lane & 15);
     const float4 c = *reinterpret_cast<const float4*>(cos_table + (long)pos * 64 + i0);
@@ -183,6 +197,9 @@ __global__ void qk_norm_rope_store_d128_kernel(
         *reinterpret_cast<__nv_bfloat162*>(&o.x) = __floats2bfloat162_rn(x[0], x[1]);
         *reinterpret_cast<__nv_bfloat162*>(&o.y) = __floats2bfloat162_rn(x[2], x[3]);
         *reinterpret_cast<uint2*>(dst + 4 * lane) = o;
+        if (kind == 2 && clear_tail)
+            for (int k = 1; k < page_size - pos % page_size; ++k)
+                *reinterpret_cast<uint2*>(dst + k * 128 + 4 * lane) = make_uint2(0u, 0u);
     }
 }
 #endif
@@ -208,13 +225,14 @@ __global__ void qk_norm_rope_store_d128_wide_kernel(
     const int head0 = (blockIdx.y * (blockDim.x >> 5) + warp) * HPW;
     if (head0 >= heads_total) return;
     const int pos = positions[row];
-    if (pos < 0 || pos >= table_rows) { ib_note_row_fault(row); return; }
+    if (pos < 0 || pos >= table_rows) { ib_note_row_fault(row); ib_grid_dependency_wait(); return; }
     long kv_base = -1;
     if (store_kv && head0 + HPW > n_heads) {
         const int req = row_request[row];
         const int page = pos / page_size < max_pages ? block_table[(long)req * max_pages + pos / page_size] : -1;
         if (page >= 0 && page < n_pages) kv_base = ((long)page * n_kv_heads * page_size + (pos % page_size)) * 128;
     }
+    const bool clear_tail = kv_base >= 0 && ib_last_row_of_request(row_request, row, gridDim.x);
     const int sub = lane >> 4, l16 = lane & 15;  // which of the two heads of a pass, and the place in it
     const int e0 = 4 * l16;                      // this lane's elements e0 .. e0 + 3 and 64 + e0 .. 64 + e0 + 3
     const float4 cs = *reinterpret_cast<const float4*>(cos_table + (long)pos * 64 + e0);
@@ -305,6 +323,11 @@ __global__ void qk_norm_rope_store_d128_wide_kernel(
         t = __floats2bfloat162_rn(x[6], x[7]); o_hi.y = *reinterpret_cast<unsigned*>(&t);
         *reinterpret_cast<uint2*>(dst + e0) = o_lo;
         *reinterpret_cast<uint2*>(dst + 64 + e0) = o_hi;
+        if (kind == 2 && clear_tail)
+            for (int k = 1; k < page_size - pos % page_size; ++k) {
+                *reinterpret_cast<uint2*>(dst + k * 128 + e0) = make_uint2(0u, 0u);
+                *reinterpret_cast<uint2*>(dst + k * 128 + 64 + e0) = make_uint2(0u, 0u);
+            }
     }
 }
 #endif

@@ -110,8 +110,9 @@ def build_context(entries: Sequence[StepEntry], manager: CacheManager, storage: 
     ``fixed_pages[g]`` pads group g's block table to that many columns, ``pad_to`` pads a step of
     single tokens to that many requests, and ``into`` is a device buffer that receives the data:
     together they give a step whose shapes and addresses do not change, which a replayed CUDA
-    graph needs.  A padding request has one token at position 0 and no pages: it writes nothing
-    to the cache and its output is not used.
+    graph needs.  A padding request has one token at position 0, no pages and the state slot after
+    the last real one: it writes nothing to the cache or to a live request's state, and its
+    output is not used.
 
     ``pad_rows`` does the same for a step of any portions: the rows are padded to ``pad_rows`` (the
     added rows belong to one padding request without pages), the requests to ``pad_requests``, the
@@ -197,7 +198,7 @@ def build_context(entries: Sequence[StepEntry], manager: CacheManager, storage: 
             q_start.append(q_start[-1] + k)
             q_lens.append(k)
             kv_lens.append(max(k, 1))
-            slots.append(0)
+            slots.append(manager.max_requests)   # the slot that no request ever gets
         wanted = list(logit_rows)
         logit_rows = logit_rows + [0] * (pad_wanted - len(logit_rows))
     if pad_to is not None:
@@ -210,7 +211,7 @@ def build_context(entries: Sequence[StepEntry], manager: CacheManager, storage: 
             q_start.append(q_start[-1] + 1)
             q_lens.append(1)
             kv_lens.append(1)
-            slots.append(0)
+            slots.append(manager.max_requests)   # the slot that no request ever gets
         wanted = list(logit_rows)
         logit_rows = list(range(pad_to))  # fixed shape: every row's logits are made, the caller picks
     elif pad_rows is None:

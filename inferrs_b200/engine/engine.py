@@ -62,7 +62,8 @@ class Engine:
         self.runner = ModelRunner(spec, weights, self.rt, page_size=block_size, n_pages=num_blocks,
                                   max_requests=max_batch_size, max_context=self.max_seq_len)
         self.scheduler = Scheduler(self.runner.manager, max_batch_size, max_tokens_per_step, self.max_seq_len,
-                                   spec.eos_token_ids, prefill_chunk)
+                                   spec.eos_token_ids, prefill_chunk,
+                                   on_admit=lambda rid, slot: self.runner.storage.clear_slot(slot))
         self.sampler = Sampler(self.rt.device, self.rt.dtype)
         self._ids = itertools.count()
         self._rng = random.Random()

@@ -145,8 +145,12 @@ class DecodeGraphs:
         r = self.runner
         buffer = torch.zeros((self._buffer_size(bucket),), dtype=torch.int32, device=r.rt.device)
         ctx = self._context(entries, bucket, buffer)
-        # once outside the capture: libraries initialise, the allocator warms up, and the step's keys are written
+        # once outside the capture: libraries initialise, the allocator warms up, and the step's keys are written.
+        # Writing the same keys twice changes nothing, but a mixer's fixed-size state would move twice: it is put
+        # back before the step runs for good (the replay below).
+        saved = r.storage.snapshot_states()
         r.model.forward(ctx)
+        r.storage.restore_states(saved)
         torch.cuda.synchronize()
         # the captured launches may overlap their neighbours' ends (programmatic dependent launch)
         kernels.set_pdl(True, r.rt.dtype)
@@ -264,13 +268,17 @@ class PortionGraphs:
             # depend on how many rows the step has: the plain step says that it stands for the padded one)
             plain = build_context(entries, r.manager, r.storage, r.spec.vocab_size, r.spec.max_positions, r.rt.device)
             plain.extra["dispatch_rows"] = bucket
+            saved = r.storage.snapshot_states()     # see DecodeGraphs._capture
             r.model.forward(plain)
+            r.storage.restore_states(saved)
             self.tile_sizes[bucket] = sorted(k[1:] for k in plain.extra
                                              if isinstance(k, tuple) and k[0] == "attention_tiles")
         size = self._build(entries, bucket, torch.device("cpu")).extra["host"].size
         buffer = torch.zeros((size + 16,), dtype=torch.int32, device=r.rt.device)
         ctx = self._build(entries, bucket, r.rt.device, into=buffer)
+        saved = r.storage.snapshot_states()
         r.model.forward(ctx)
+        r.storage.restore_states(saved)
         torch.cuda.synchronize()
         kernels.set_pdl(True, r.rt.dtype)
         graph = torch.cuda.CUDAGraph()

@@ -13,7 +13,8 @@ import torch
 
 from .. import kernels
 from ..cache.storage import KVNeed, StateNeed
-from ..parts.basic import Linear
+from ..parts.basic import Linear, NoNorm
+from ..parts.blocks import BuiltSubLayer
 from ..parts.registry import part_class
 from ..parts.spec import ModelSpec, TensorDecl
 from ..runtime import Runtime
@@ -27,10 +28,13 @@ def declared_tensors(spec: ModelSpec) -> List[TensorDecl]:
     """Every tensor the model's parts expect, in a fixed order, each name once."""
     decls: List[TensorDecl] = [TensorDecl(spec.embedding, (spec.vocab_size, spec.width))]
     for layer in spec.layers:
-        decls += part_class("norm", layer.mixer_norm).declare(layer.mixer_norm)
-        decls += part_class("mixer", layer.mixer).declare(layer.mixer)
-        decls += part_class("norm", layer.ffn_norm).declare(layer.ffn_norm)
-        decls += part_class("feed_forward", layer.ffn).declare(layer.ffn)
+        for sub in layer.sublayers:
+            _check_category(sub.category)
+            if sub.norm is not None:
+                decls += part_class("norm", sub.norm).declare(sub.norm)
+            decls += part_class(sub.category, sub.part).declare(sub.part)
+            if sub.post_norm is not None:
+                decls += part_class("norm", sub.post_norm).declare(sub.post_norm)
     decls += part_class("norm", spec.final_norm).declare(spec.final_norm)
     decls.append(TensorDecl(spec.lm_head, (spec.vocab_size, spec.width), optional=spec.lm_head_optional))
     seen, out = {}, []
@@ -44,6 +48,22 @@ def declared_tensors(spec: ModelSpec) -> List[TensorDecl]:
     return out
 
 
+def _check_category(category: str):
+    if category not in ("mixer", "feed_forward"):
+        raise ModelError(f"a sub-layer is a 'mixer' or a 'feed_forward', got category '{category}'")
+
+
+def _mixers(spec: ModelSpec, layer: int):
+    """The mixer descriptions of a layer with their classes.  Every mixer of a layer gets the schedule entry's one
+    cache id, so at most one of them may keep a cache or a state."""
+    out = [(m, part_class("mixer", m)) for m in spec.layers[layer].parts_of("mixer")]
+    keepers = [m for m, cls in out if cls.cache_need(m) is not None or cls.state_need(m) is not None]
+    if len(keepers) > 1:
+        raise ModelError(f"layer {layer} has {len(keepers)} mixers that keep a cache or a state; a schedule entry "
+                         f"names one cache, so a layer can have one such mixer")
+    return out
+
+
 def check_schedule(spec: ModelSpec):
     """The schedule names existing layers; every cache has exactly one writer, which runs before its readers."""
     if not spec.schedule:
@@ -52,15 +72,16 @@ def check_schedule(spec: ModelSpec):
     for i, e in enumerate(spec.schedule):
         if not 0 <= e.layer < len(spec.layers):
             raise ModelError(f"schedule entry {i} names layer {e.layer}; the model has {len(spec.layers)}")
-        mixer = spec.layers[e.layer].mixer
-        cls = part_class("mixer", mixer)
-        writes = cls.writes_cache(mixer) if hasattr(cls, "writes_cache") else True
-        if writes:
-            if e.cache in writers:
-                raise ModelError(f"cache {e.cache} is written by schedule entries {writers[e.cache]} and {i}")
-            writers[e.cache] = i
-        elif e.cache not in writers:
-            raise ModelError(f"schedule entry {i} reads cache {e.cache} before any entry has written it")
+        for mixer, cls in _mixers(spec, e.layer):
+            if cls.cache_need(mixer) is None and cls.state_need(mixer) is None:
+                continue
+            writes = cls.writes_cache(mixer) if hasattr(cls, "writes_cache") else True
+            if writes:
+                if e.cache in writers:
+                    raise ModelError(f"cache {e.cache} is written by schedule entries {writers[e.cache]} and {i}")
+                writers[e.cache] = i
+            elif e.cache not in writers:
+                raise ModelError(f"schedule entry {i} reads cache {e.cache} before any entry has written it")
 
 
 def cache_needs(spec: ModelSpec):
@@ -69,18 +90,17 @@ def cache_needs(spec: ModelSpec):
     kv: Dict[int, KVNeed] = {}
     states: Dict[int, StateNeed] = {}
     for e in spec.schedule:
-        mixer = spec.layers[e.layer].mixer
-        cls = part_class("mixer", mixer)
-        need = cls.cache_need(mixer)
-        if need is not None:
-            if e.cache in kv and kv[e.cache] != need:
-                raise ModelError(f"cache {e.cache} is used with different needs: {kv[e.cache]} and {need}")
-            kv[e.cache] = need
-        st = cls.state_need(mixer)
-        if st is not None:
-            if e.cache in states and states[e.cache] != st:
-                raise ModelError(f"state {e.cache} is used with different needs")
-            states[e.cache] = st
+        for mixer, cls in _mixers(spec, e.layer):
+            need = cls.cache_need(mixer)
+            if need is not None:
+                if e.cache in kv and kv[e.cache] != need:
+                    raise ModelError(f"cache {e.cache} is used with different needs: {kv[e.cache]} and {need}")
+                kv[e.cache] = need
+            st = cls.state_need(mixer)
+            if st is not None:
+                if e.cache in states and states[e.cache] != st:
+                    raise ModelError(f"state {e.cache} is used with different needs")
+                states[e.cache] = st
     return kv, states
 
 
@@ -92,12 +112,17 @@ class Model:
         self.embedding = weights[spec.embedding]
         self.blocks = []
         for layer in spec.layers:
-            mixer_norm = part_class("norm", layer.mixer_norm)(layer.mixer_norm, weights, rt)
-            mixer = part_class("mixer", layer.mixer)(layer.mixer, weights, rt)
-            ffn_norm = part_class("norm", layer.ffn_norm)(layer.ffn_norm, weights, rt)
-            ffn = part_class("feed_forward", layer.ffn)(layer.ffn, weights, rt)
-            self.blocks.append(part_class("arrangement", _Arrangement(layer.arrangement))(
-                layer, mixer_norm, mixer, ffn_norm, ffn))
+            built = []
+            for sub in layer.sublayers:
+                _check_category(sub.category)
+                # "no norm" is a part too: it is where the sub-layer before is added to the residual stream
+                norm = part_class("norm", sub.norm)(sub.norm, weights, rt) if sub.norm is not None \
+                    else NoNorm(None, weights, rt)
+                post = part_class("norm", sub.post_norm)(sub.post_norm, weights, rt) \
+                    if sub.post_norm is not None else None
+                built.append(BuiltSubLayer(sub.category, part_class(sub.category, sub.part)(sub.part, weights, rt),
+                                           norm, post))
+            self.blocks.append(part_class("arrangement", _Arrangement(layer.arrangement))(layer, built))
         self.final_norm = part_class("norm", spec.final_norm)(spec.final_norm, weights, rt)
         head = weights.get(spec.lm_head)
         if head is None:
@@ -111,14 +136,19 @@ class Model:
         """Run the step's rows through all scheduled layers; float32 logits [wanted rows, vocab]."""
         n = ctx.token_ids.shape[0]
         residual = torch.empty((n, self.spec.width), dtype=torch.float32, device=self.rt.device)
-        kernels.embedding_gather(self.embedding, ctx.token_ids, residual, self.rt.dtype)
+        kernels.embedding_gather(self.embedding, ctx.token_ids, residual, self.rt.dtype,
+                                 1.0 if self.spec.embedding_scale is None else self.spec.embedding_scale)
         pending: Optional[torch.Tensor] = None
         for entry in self.spec.schedule:
             pending = self.blocks[entry.layer].forward(ctx, entry.cache, residual, pending)
         if ctx.logit_rows.shape[0] == 0:
             return torch.empty((0, self.spec.vocab_size), dtype=torch.float32, device=self.rt.device)
         h = self.final_norm.add_norm(residual, pending, rows=ctx.logit_rows)
-        return self.head(h, out_dtype=torch.float32)
+        logits = self.head(h, out_dtype=torch.float32)
+        if self.spec.logit_scale is not None or self.spec.logit_softcap is not None:
+            kernels.logit_scale_softcap(logits, 1.0 if self.spec.logit_scale is None else self.spec.logit_scale,
+                                        self.spec.logit_softcap, self.rt.dtype)
+        return logits
 
 
 class _Arrangement:

@@ -38,7 +38,7 @@ class ModelRunner:
         self.steps_run = 0
         # decode steps are replayed as CUDA graphs when every part says its launches do not depend on
         # host-side values of the step (``graph_safe``)
-        parts = [p for b in self.model.blocks for p in (b.mixer, b.ffn, b.mixer_norm, b.ffn_norm)]
+        parts = [p for b in self.model.blocks for p in b.parts()] + [self.model.final_norm]
         safe = all(getattr(p, "graph_safe", False) for p in parts)
         if use_graphs is None:
             use_graphs = rt.device.type == "cuda"

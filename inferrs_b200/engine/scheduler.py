@@ -26,7 +26,7 @@ from __future__ import annotations
 import ctypes
 from collections import deque
 from dataclasses import dataclass, field
-from typing import Deque, Dict, Hashable, List, Optional, Sequence, Tuple
+from typing import Callable, Deque, Dict, Hashable, List, Optional, Sequence, Tuple
 
 from ..cache.manager import CacheManager, host_library
 from ..sampling.params import SamplingParams
@@ -96,10 +96,15 @@ class Scheduler:
     _REASONS = {1: "stop", 2: "length"}
 
     def __init__(self, manager: CacheManager, max_batch_size: int, max_tokens_per_step: int,
-                 max_positions: int, eos_token_ids: Sequence[int] = (), prefill_chunk: Optional[int] = None):
+                 max_positions: int, eos_token_ids: Sequence[int] = (), prefill_chunk: Optional[int] = None,
+                 on_admit: Optional[Callable[[Hashable, int], None]] = None):
+        """``on_admit(rid, slot)`` is called for every request that a plan admits, a preempted request that
+        comes back included, before the plan is returned: whoever owns per-request state of fixed size starts
+        it afresh there (a request that is computed again must not find what its first run left)."""
         if max_batch_size <= 0 or max_tokens_per_step <= 0:
             raise SchedulerError("max_batch_size and max_tokens_per_step must be positive")
         self.manager = manager
+        self.on_admit = on_admit
         self.max_batch_size = min(max_batch_size, manager.max_requests)
         self.max_tokens_per_step = max_tokens_per_step
         self.prefill_chunk = prefill_chunk or max_tokens_per_step
@@ -220,6 +225,8 @@ class Scheduler:
                 raise SchedulerError("the front and the native scheduler disagree about the waiting queue")
             self.manager.adopt(r.rid, h)
             self.running.append(r)
+            if self.on_admit is not None:
+                self.on_admit(r.rid, self.manager.slot(r.rid))
         e = self._entries
         plan = [PlannedEntry(self._by_handle[self._rids[i]], e[3 * i], e[3 * i + 1], bool(e[3 * i + 2]))
                 for i in range(c[0].value)]

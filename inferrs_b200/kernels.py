@@ -24,7 +24,10 @@ class KernelError(RuntimeError):
 
 
 _SIGNATURES = {
-    "ib_embedding_gather": [c_void_p, c_int, c_void_p, c_void_p, c_int, c_int, c_int, c_void_p],
+    "ib_embedding_gather": [c_void_p, c_int, c_void_p, c_void_p, c_int, c_int, c_int, c_float, c_void_p],
+    "ib_rms_norm_rows": [c_void_p, c_void_p, c_int, c_void_p, c_int, c_int, c_float, c_void_p],
+    "ib_add_cast": [c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int, c_void_p],
+    "ib_logit_scale_softcap": [c_void_p, c_long, c_float, c_float, c_void_p],
     "ib_resolve_tokens": [c_void_p, c_int, c_void_p, c_int, c_void_p],
     "ib_add_rms_norm": [c_void_p, c_void_p, c_void_p, c_int, c_void_p, c_void_p, c_int, c_int, c_float, c_void_p],
     "ib_silu_gate": [c_void_p, c_void_p, c_int, c_int, c_void_p],
@@ -144,8 +147,9 @@ _W = (torch.float32, torch.bfloat16)
 _I = (torch.int32,)
 
 
-def embedding_gather(table: torch.Tensor, ids: torch.Tensor, out: torch.Tensor, act_dtype: torch.dtype):
-    """out[r, :] = table[ids[r], :] as float32."""
+def embedding_gather(table: torch.Tensor, ids: torch.Tensor, out: torch.Tensor, act_dtype: torch.dtype,
+                     scale: float = 1.0):
+    """out[r, :] = table[ids[r], :] * scale as float32."""
     _need(table, "table", _W, 2)
     _need(ids, "ids", _I, 1)
     _need(out, "out", (torch.float32,), 2)
@@ -153,7 +157,7 @@ def embedding_gather(table: torch.Tensor, ids: torch.Tensor, out: torch.Tensor, 
     if ids.shape[0] != n or table.shape[1] != width:
         raise KernelError(f"embedding_gather: ids {tuple(ids.shape)}, table {tuple(table.shape)}, out {tuple(out.shape)}")
     _check(_core(act_dtype).ib_embedding_gather(_p(table), int(table.dtype == torch.float32), _p(ids), _p(out), n,
-                                                width, table.shape[0], _stream()), "embedding_gather")
+                                                width, table.shape[0], float(scale), _stream()), "embedding_gather")
 
 
 def resolve_tokens(ids: torch.Tensor, carry: torch.Tensor, act_dtype: torch.dtype):
@@ -184,6 +188,45 @@ def add_rms_norm(residual: torch.Tensor, delta: Optional[torch.Tensor], weight: 
                           f"out {tuple(out.shape)}, delta {None if delta is None else tuple(delta.shape)}")
     _check(_core(act).ib_add_rms_norm(_p(residual), _p(delta), _p(weight), int(weight.dtype == torch.float32),
                                       _p(out), _p(rows), n_out, width, float(eps), _stream()), "add_rms_norm")
+
+
+def rms_norm_rows(x: torch.Tensor, weight: torch.Tensor, eps: float, out: torch.Tensor):
+    """out = rms_norm(x) * weight for rows in the activation dtype (a norm on a sub-layer's output)."""
+    act = out.dtype
+    _need(x, "x", (act,), 2)
+    _need(weight, "weight", _W, 1)
+    _need(out, "out", _W, 2)
+    if out.shape != x.shape or weight.shape[0] != x.shape[1]:
+        raise KernelError(f"rms_norm_rows: x {tuple(x.shape)}, weight {tuple(weight.shape)}, out {tuple(out.shape)}")
+    _check(_core(act).ib_rms_norm_rows(_p(x), _p(weight), int(weight.dtype == torch.float32), _p(out), x.shape[0],
+                                       x.shape[1], float(eps), _stream()), "rms_norm_rows")
+
+
+def add_cast(residual: torch.Tensor, delta: Optional[torch.Tensor], out: torch.Tensor,
+             rows: Optional[torch.Tensor] = None):
+    """residual += delta (float32, in place when ``rows`` is None); out = residual in the activation dtype:
+    what a sub-layer without a norm reads."""
+    act = out.dtype
+    _need(residual, "residual", (torch.float32,), 2)
+    _need(delta, "delta", (act,), 2, optional=True)
+    _need(out, "out", _W, 2)
+    _need(rows, "rows", _I, 1, optional=True)
+    n, width = residual.shape
+    n_out = n if rows is None else rows.shape[0]
+    if out.shape != (n_out, width) or (delta is not None and delta.shape != residual.shape):
+        raise KernelError(f"add_cast: residual {tuple(residual.shape)}, out {tuple(out.shape)}, "
+                          f"delta {None if delta is None else tuple(delta.shape)}")
+    _check(_core(act).ib_add_cast(_p(residual), _p(delta), _p(out), _p(rows), n_out, width, _stream()), "add_cast")
+
+
+def logit_scale_softcap(logits: torch.Tensor, scale: float, softcap: Optional[float], act_dtype: torch.dtype):
+    """In place on float32 logits: x *= scale, then x = cap * tanh(x / cap) where a cap is given."""
+    _need(logits, "logits", (torch.float32,), 2)
+    if softcap is not None and not softcap > 0:
+        raise KernelError(f"logit_scale_softcap: the cap must be positive, got {softcap}")
+    _check(_core(act_dtype).ib_logit_scale_softcap(_p(logits), logits.numel(), float(scale),
+                                                   float(softcap) if softcap else 0.0, _stream()),
+           "logit_scale_softcap")
 
 
 def silu_gate(gate_up: torch.Tensor, out: torch.Tensor):
@@ -693,13 +736,6 @@ def _gemm_lib():
         lib.ib_gemm_swiglu_tcgen05.restype = c_int
         lib.ib_gemm_tcgen05_error.argtypes = [c_int]
         lib.ib_gemm_tcgen05_error.restype = c_int
-        lib.ib_gemm_tn_streamk.argtypes = [c_void_p, c_long, c_void_p, c_long, c_void_p, c_long, c_int, c_int, c_int,
-                                           c_int, c_void_p, c_void_p, c_int, c_void_p]
-        lib.ib_gemm_tn_streamk.restype = c_int
-        lib.ib_gemm_streamk_workspace_floats.argtypes = [c_int, c_int]
-        lib.ib_gemm_streamk_workspace_floats.restype = c_long
-        lib.ib_gemm_streamk_error.argtypes = [c_int]
-        lib.ib_gemm_streamk_error.restype = c_int
         _GEMM_LIB = lib
     return _GEMM_LIB
 
@@ -771,45 +807,3 @@ SWIGLU_MAX_TOKENS = 32  # rows that the fused gate/up kernel takes
 def gemm_tcgen05_error(reset: bool = True) -> int:
     """0, or the code of the first bounded wait that ran out in a tcgen05 GEMM (synchronises with the device)."""
     return _gemm_lib().ib_gemm_tcgen05_error(int(reset))
-
-
-_STREAMK_WS = {}  # device index -> (partial sums, flags, number of SMs)
-
-
-def _streamk_workspace(device: torch.device, n_tok: int):
-    """The persistent product's workspace on this device: partial sums (grown on demand) and zeroed flags.
-    All launches on a device share it, so they must not overlap (the engine runs on one stream)."""
-    lib = _gemm_lib()
-    idx = device.index if device.index is not None else torch.cuda.current_device()
-    ws = _STREAMK_WS.get(idx)
-    sms = ws[2] if ws else torch.cuda.get_device_properties(idx).multi_processor_count
-    need = lib.ib_gemm_streamk_workspace_floats(n_tok, sms)
-    if ws is None or ws[0].numel() < need:
-        partial = torch.empty((need,), dtype=torch.float32, device=device)
-        flags = ws[1] if ws else torch.zeros((sms,), dtype=torch.int32, device=device)
-        ws = (partial, flags, sms)
-        _STREAMK_WS[idx] = ws
-    return ws
-
-
-def gemm_tn_streamk(x: torch.Tensor, w: torch.Tensor, out: torch.Tensor):
-    """out = x @ w.T by one persistent CTA per SM, each streaming an equal share of W through TMA into
-    tcgen05 MMAs (see csrc/gemm_streamk.cu).  Deterministic for a given shape."""
-    _need(x, "x", (torch.bfloat16,), 2)
-    _need(w, "w", (torch.bfloat16,), 2)
-    _need(out, "out", _W, 2)
-    n, k = x.shape
-    m = w.shape[0]
-    if w.shape[1] != k or out.shape != (n, m):
-        raise KernelError(f"gemm: x {tuple(x.shape)}, w {tuple(w.shape)}, out {tuple(out.shape)}")
-    partial, flags, sms = _streamk_workspace(x.device, n)
-    code = _gemm_lib().ib_gemm_tn_streamk(_p(x), k, _p(w), k, _p(out), m, int(out.dtype == torch.float32), n, m, k,
-                                          _p(partial), _p(flags), sms, _stream())
-    if code == -1:
-        raise KernelError(f"gemm_tn_streamk: K={k} must be a multiple of 8 and the bases 16-byte aligned")
-    _check(code, "gemm_tn_streamk")
-
-
-def gemm_streamk_error(reset: bool = True) -> int:
-    """0, or the code of the first bounded wait that ran out in a persistent product (synchronises)."""
-    return _gemm_lib().ib_gemm_streamk_error(int(reset))

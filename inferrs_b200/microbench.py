@@ -1,6 +1,6 @@
 """Timing of single kernels at given sizes: the commands behind the summaries in ``profiles/``.
 
-    python -m inferrs_b200.microbench gemm --impl streamk --m 8 --n 6144 --k 4096
+    python -m inferrs_b200.microbench gemm --impl tcgen05 --m 8 --n 6144 --k 4096
     python -m inferrs_b200.microbench attention --form decode --batch 8 --context 2048
     python -m inferrs_b200.microbench attention --form prefill --tokens 2048
     python -m inferrs_b200.microbench chain --impl library --m 8 --layers 8
@@ -64,8 +64,7 @@ def gemm(args) -> dict:
     w = (torch.randn(args.n, args.k, device="cuda") * 0.02).to(torch.bfloat16)
     out = torch.empty(args.m, args.n, dtype=torch.bfloat16, device="cuda")
     fn = {"library": lambda: kernels.gemm_tn_bf16(x, w, out),
-          "tcgen05": lambda: kernels.gemm_tn_tcgen05(x, w, out, args.split_k),
-          "streamk": lambda: kernels.gemm_tn_streamk(x, w, out)}[args.impl]
+          "tcgen05": lambda: kernels.gemm_tn_tcgen05(x, w, out, args.split_k)}[args.impl]
     us = _time(fn, args.iters)
     ref = x.float() @ w.float().t()
     err = float((out.float() - ref).abs().max() / ref.abs().max())
@@ -75,44 +74,8 @@ def gemm(args) -> dict:
             "GBps": round(byts / us / 1e3, 1), "TFLOPs": round(flops / us / 1e6, 1), "rel_err": err}
 
 
-ATTENTION_EVENTS = {10: "producer: asks for K", 11: "producer: asks for V", 20: "MMA thread: issues Q K^T",
-                    21: "MMA thread: waits for P", 22: "MMA thread: has P", 23: "MMA thread: has V",
-                    24: "MMA thread: has issued P V", 30: "softmax: waits for S", 32: "softmax: has S",
-                    34: "softmax: S in registers", 36: "softmax: own maximum", 38: "softmax: met its partner",
-                    40: "softmax: P written", 42: "softmax: has the product before", 44: "softmax: added it"}
-
-
-def _attention_events(fn) -> None:
-    """Print when the producer lane, the MMA thread and one softmax thread of the CTA with the most key tiles
-    reached each point of a tile (SM clock cycles), from a build of the kernel that records them."""
-    import ctypes
-    lib = kernels._core(torch.bfloat16)
-    lib.ib_attention_events.argtypes = [ctypes.c_void_p, ctypes.c_int]
-    buf = (ctypes.c_longlong * (64 * 32))()
-    for _ in range(3):
-        fn()
-    torch.cuda.synchronize()
-    lib.ib_attention_events(buf, len(buf))
-    ev = sorted((buf[c * 32 + i], c, i) for c in ATTENTION_EVENTS for i in range(32) if buf[c * 32 + i])
-    if not ev:
-        print("no events were recorded")
-        return
-    t0 = ev[0][0]
-    n_tiles = 1 + max(i for _, _, i in ev)
-    for t, c, i in ev:
-        if n_tiles // 2 <= i < n_tiles // 2 + 2:
-            print(f"{t - t0:8d}  tile {i:2d}  {ATTENTION_EVENTS[c]}")
-    for code in (10, 20, 24, 40, 44):
-        ts = sorted(t for t, c, _ in ev if c == code)
-        print(f"cycles from tile to tile, {ATTENTION_EVENTS[code]}: {[b - a for a, b in zip(ts, ts[1:])]}")
-
-
 def attention(args) -> dict:
     nh, nkv, d, ps = args.heads, args.kv_heads, args.head_dim, args.page_size
-    if args.events:
-        # the build of the kernel library that records the events (another file name: the flags are hashed)
-        from .csrc import build
-        build.LIBRARIES["core_bf16"]["flags"] = build.LIBRARIES["core_bf16"]["flags"] + ["-DIB_ATTN_EVENTS"]
     dev = torch.device("cuda")
     if args.form == "decode":
         lens, new = [args.context] * args.batch, [1] * args.batch
@@ -168,8 +131,6 @@ def attention(args) -> dict:
         t, c = args.tokens, args.context_before
         flops = 4 * nh * d * (t * c + t * (t + 1) // 2)
         extra = {"tokens": args.tokens, "context_before": args.context_before}
-        if args.events and args.impl == "tcgen05":
-            _attention_events(fn)
     us = _time(fn, args.iters)
     return dict({"kernel": f"attention/{args.form}" + (f"/{args.impl}" if args.form == "prefill" else ""), "heads": nh, "kv_heads": nkv, "head_dim": d, "us": round(us, 2),
                  "GBps": round(byts / us / 1e3, 1), "TFLOPs": round(flops / us / 1e6, 1)}, **extra)
@@ -183,8 +144,7 @@ def chain(args) -> dict:
     ws = [[(torch.randn(n, k, device="cuda") * 0.02).to(torch.bfloat16) for n, k in shapes] for _ in range(args.layers)]
     xs = [torch.randn(args.m, k, device="cuda").to(torch.bfloat16) for _, k in shapes]
     outs = [torch.empty(args.m, n, dtype=torch.bfloat16, device="cuda") for n, _ in shapes]
-    fn = {"library": kernels.gemm_tn_bf16, "tcgen05": lambda x, w, o: kernels.gemm_tn_tcgen05(x, w, o, 0),
-          "streamk": kernels.gemm_tn_streamk}[args.impl]
+    fn = {"library": kernels.gemm_tn_bf16, "tcgen05": lambda x, w, o: kernels.gemm_tn_tcgen05(x, w, o, 0)}[args.impl]
 
     def run():
         for layer in ws:
@@ -389,7 +349,7 @@ def main(argv=None) -> int:
                                  formatter_class=argparse.RawDescriptionHelpFormatter)
     sub = ap.add_subparsers(dest="what", required=True)
     g = sub.add_parser("gemm")
-    g.add_argument("--impl", choices=["library", "tcgen05", "streamk", "gated"], default="streamk",
+    g.add_argument("--impl", choices=["library", "tcgen05", "gated"], default="tcgen05",
                    help="gated: both products of a gated feed-forward and the gate in one tcgen05 kernel")
     g.add_argument("--m", type=int, default=8)
     g.add_argument("--n", type=int, default=6144)
@@ -412,11 +372,9 @@ def main(argv=None) -> int:
     a.add_argument("--head-dim", type=int, default=128)
     a.add_argument("--page-size", type=int, default=16)
     a.add_argument("--iters", type=int, default=20)
-    a.add_argument("--events", action="store_true",
-                   help="prefill form, tcgen05 kernel: print when its warps reached each point of a tile")
     a.set_defaults(fn=attention)
     c = sub.add_parser("chain")
-    c.add_argument("--impl", choices=["library", "tcgen05", "streamk"], default="library")
+    c.add_argument("--impl", choices=["library", "tcgen05"], default="library")
     c.add_argument("--m", type=int, default=8)
     c.add_argument("--layers", type=int, default=8)
     c.add_argument("--hidden", type=int, default=4096)

@@ -19,8 +19,8 @@ import math
 
 from ..config.base import register_architecture
 from ..config.qwen3 import Qwen3Config
-from ..parts.spec import (AttentionSpec, GatedDenseSpec, LayerSpec, ModelSpec, NormSpec, PositionSpec,
-                          default_schedule)
+from ..parts.spec import (AttentionSpec, GatedDenseSpec, ModelSpec, NormSpec, PositionSpec, default_schedule,
+                          pre_norm_layer)
 
 ARCHITECTURE = "Qwen3ForCausalLM"
 
@@ -54,13 +54,12 @@ def build_spec(cfg: Qwen3Config) -> ModelSpec:
             down_proj=f"{p}.mlp.down_proj.weight",
             activation="silu",
         )
-        layers.append(LayerSpec(
+        layers.append(pre_norm_layer(
             mixer_norm=NormSpec(size=cfg.hidden_size, eps=cfg.rms_norm_eps, weight=f"{p}.input_layernorm.weight"),
             mixer=attn,
             ffn_norm=NormSpec(size=cfg.hidden_size, eps=cfg.rms_norm_eps,
                               weight=f"{p}.post_attention_layernorm.weight"),
             ffn=ffn,
-            arrangement="pre_norm",
         ))
     return ModelSpec(
         vocab_size=cfg.vocab_size,

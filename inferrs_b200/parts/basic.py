@@ -33,8 +33,39 @@ class RMSNorm:
         kernels.add_rms_norm(residual, delta, self.weight, self.spec.eps, out, rows)
         return out
 
+    def norm(self, x: torch.Tensor) -> torch.Tensor:
+        """The norm alone, on rows in the activation dtype (a norm on a sub-layer's output)."""
+        out = torch.empty_like(x)
+        kernels.rms_norm_rows(x, self.weight, self.spec.eps, out)
+        return out
+
+
+class NoNorm:
+    """No norm: the sub-layer reads (or hands on) the rows as they are.  Still the place where the output of
+    the sub-layer before it is added to the residual stream."""
+
+    graph_safe = True
+
+    @staticmethod
+    def declare(spec) -> List[TensorDecl]:
+        return []
+
+    def __init__(self, spec, weights: Dict[str, torch.Tensor], rt: Runtime):
+        self.spec, self.rt = spec, rt
+
+    def add_norm(self, residual: torch.Tensor, delta: Optional[torch.Tensor],
+                 rows: Optional[torch.Tensor] = None) -> torch.Tensor:
+        n = residual.shape[0] if rows is None else rows.shape[0]
+        out = torch.empty((n, residual.shape[1]), dtype=self.rt.dtype, device=residual.device)
+        kernels.add_cast(residual, delta, out, rows)
+        return out
+
+    def norm(self, x: torch.Tensor) -> torch.Tensor:
+        return x
+
 
 register_norm("rms", RMSNorm)
+register_norm("none", NoNorm)
 
 
 class RotarySplitHalf:

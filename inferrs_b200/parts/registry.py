@@ -19,13 +19,22 @@ norm
     ``declare(spec)``, ``__init__(spec, weights, rt)``,
     ``add_norm(residual, delta, rows=None) -> h``: adds ``delta`` (or nothing) into the float32
     residual in place and returns the normalised rows in the activation dtype; with ``rows``
-    it reads only those rows and writes nothing back.
+    it reads only those rows and writes nothing back.  ``norm(x) -> y``: the norm alone on rows in
+    the activation dtype (used where a description puts a norm on a sub-layer's output).
 position encoding
     ``__init__(spec, rt)``, ``tables() -> (cos, sin, rot_dim)``: float32 ``[max_positions, rot_dim/2]``
     tables that the attention kernels index by position (``rot_dim`` 0: no rotation).
 arrangement
-    ``__init__(spec, mixer_norm, mixer, ffn_norm, ffn)``,
-    ``forward(ctx, cache_id, residual, pending) -> pending``.
+    ``__init__(spec, sublayers)`` with ``spec`` the layer's :class:`~inferrs_b200.parts.spec.LayerSpec` and
+    ``sublayers`` its built sub-layers in order (:class:`~inferrs_b200.parts.blocks.BuiltSubLayer`: ``category``,
+    ``part``, ``norm``, ``post_norm``; ``run(ctx, cache_id, h)`` calls the part the way its category wants),
+    ``forward(ctx, cache_id, residual, pending) -> pending`` (``residual`` float32 ``[rows, width]``, updated in
+    place; ``pending`` is a sub-layer output that has not been added yet, or None), and
+    ``parts() -> iterable`` of every part object the block holds.
+
+Every part may set ``graph_safe = True`` to say that its launches depend only on shapes and device
+memory, never on host-side values of the step; a model whose parts all say so has its steps captured
+into CUDA graphs.  A part without the attribute keeps the model's steps launched one by one.
 """
 from __future__ import annotations
 

@@ -2,7 +2,7 @@
 
 An architecture turns its typed configuration into one :class:`ModelSpec`.
 Nothing below names an architecture: every size and constant is a field, every
-layer has its own mixer and feed-forward description, and the order in which
+layer has its own list of sub-layers (a mixer or a feed-forward with its norms each), and the order in which
 layers run is the ``schedule`` list, which may name a layer twice or let two
 entries use one cache.
 
@@ -93,17 +93,65 @@ class GatedDenseSpec:
 
 
 @dataclass(frozen=True)
-class LayerSpec:
-    """One block: two sub-layers, each with its norm, and how they are arranged.
+class SubLayerSpec:
+    """One sub-layer of a block: a part with what stands before and after it.
 
-    ``arrangement="pre_norm"``: x += mixer(norm(x)); x += feed_forward(norm(x)).
+    ``category`` says which registry the part's ``kind`` is looked up in: ``"mixer"`` (it gets the
+    layer's cache) or ``"feed_forward"``.  ``norm`` is applied to the residual stream before the part
+    (``None``: the part reads the stream as it is); ``post_norm`` to the part's output before it is
+    added to the stream (``None``: it is added as it is).
     """
 
-    mixer_norm: Any
-    mixer: Any
-    ffn_norm: Any
-    ffn: Any
-    arrangement: str = "pre_norm"
+    part: Any
+    category: str
+    norm: Optional[Any] = None
+    post_norm: Optional[Any] = None
+
+
+@dataclass(frozen=True)
+class LayerSpec:
+    """One block: its sub-layers, in order, and how they are arranged around the residual stream.
+
+    ``arrangement="sequential"``: for every sub-layer in turn, x += post_norm(part(norm(x))).  A
+    pre-norm block of a mixer and a feed-forward is two sub-layers with a ``norm`` each
+    (:func:`pre_norm_layer`); a block with four norms gives both a ``post_norm`` too; a block of a
+    mixer alone has one sub-layer.
+    """
+
+    sublayers: Tuple[SubLayerSpec, ...]
+    arrangement: str = "sequential"
+
+    def parts_of(self, category: str) -> Tuple[Any, ...]:
+        return tuple(s.part for s in self.sublayers if s.category == category)
+
+    @property
+    def mixer(self) -> Any:
+        """The layer's mixer description (the first, if it has several; None if it has none)."""
+        return next(iter(self.parts_of("mixer")), None)
+
+    @property
+    def ffn(self) -> Any:
+        """The layer's feed-forward description (the first, if it has several; None if it has none)."""
+        return next(iter(self.parts_of("feed_forward")), None)
+
+    def with_part(self, category: str, part: Any, index: int = 0) -> "LayerSpec":
+        """A copy in which the ``index``-th sub-layer of ``category`` has another part."""
+        seen, subs = 0, []
+        for s in self.sublayers:
+            if s.category == category:
+                if seen == index:
+                    s = SubLayerSpec(part=part, category=category, norm=s.norm, post_norm=s.post_norm)
+                seen += 1
+            subs.append(s)
+        if seen <= index:
+            raise ValueError(f"the layer has {seen} sub-layers of category '{category}', none with index {index}")
+        return LayerSpec(sublayers=tuple(subs), arrangement=self.arrangement)
+
+
+def pre_norm_layer(mixer_norm: Any, mixer: Any, ffn_norm: Any, ffn: Any) -> LayerSpec:
+    """x += mixer(norm(x)); x += feed_forward(norm(x))."""
+    return LayerSpec(sublayers=(SubLayerSpec(part=mixer, category="mixer", norm=mixer_norm),
+                                SubLayerSpec(part=ffn, category="feed_forward", norm=ffn_norm)))
 
 
 @dataclass(frozen=True)
@@ -131,6 +179,11 @@ class ModelSpec:
     # True: the head tensor may be absent, the embedding table is used then.
     lm_head_optional: bool
     max_positions: int
+    # embedding rows are multiplied by this as they are gathered (None: not at all)
+    embedding_scale: Optional[float] = None
+    # logits are multiplied by logit_scale and then squashed to cap * tanh(x / cap) (None: neither)
+    logit_scale: Optional[float] = None
+    logit_softcap: Optional[float] = None
     eos_token_ids: Tuple[int, ...] = ()
     architecture: str = ""
     extra: Tuple[Tuple[str, Any], ...] = field(default_factory=tuple)

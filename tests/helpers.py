@@ -54,5 +54,21 @@ def cut(n: int, sizes: Sequence[int]) -> List[int]:
 
 
 def rel_err(a: torch.Tensor, b: torch.Tensor) -> float:
-    """Largest absolute difference over the largest absolute value of the reference ``b``."""
-    return float((a.double() - b.double()).abs().max() / b.double().abs().max().clamp_min(1e-30))
+    """The worst row's error: for every row (last dimension) the largest absolute difference over the largest
+    absolute value of the reference ``b`` in that row; the largest of these.  One bad row among hundreds, or an
+    error in a row of small values, shows in full."""
+    a, b = a.double(), b.double()
+    if a.shape != b.shape:
+        raise ValueError(f"shapes differ: {tuple(a.shape)} and {tuple(b.shape)}")
+    if a.dim() == 0:
+        a, b = a.reshape(1, 1), b.reshape(1, 1)
+    elif a.dim() == 1:
+        a, b = a.reshape(1, -1), b.reshape(1, -1)
+    a, b = a.reshape(-1, a.shape[-1]), b.reshape(-1, b.shape[-1])
+    if a.numel() == 0:
+        return 0.0
+    if not bool(torch.isfinite(a).all()):
+        return float("inf")
+    diff = (a - b).abs().amax(dim=1)
+    scale = b.abs().amax(dim=1).clamp_min(1e-30)
+    return float((diff / scale).max())

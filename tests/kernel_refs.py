@@ -13,8 +13,31 @@ from typing import Optional
 import torch
 
 
-def embedding_gather(table, ids, out, act_dtype=None):
-    out.copy_(table[ids.long()].float())
+def embedding_gather(table, ids, out, act_dtype=None, scale=1.0):
+    out.copy_(table[ids.long()].float() * scale)
+
+
+def rms_norm_rows(x, weight, eps, out):
+    v = x.float()
+    out.copy_((v / torch.sqrt((v * v).mean(dim=-1, keepdim=True) + eps) * weight.float()).to(out.dtype))
+
+
+def add_cast(residual, delta, out, rows=None):
+    if rows is None:
+        if delta is not None:
+            residual += delta.float()
+        out.copy_(residual.to(out.dtype))
+    else:
+        x = residual[rows.long()]
+        if delta is not None:
+            x = x + delta[rows.long()].float()
+        out.copy_(x.to(out.dtype))
+
+
+def logit_scale_softcap(logits, scale, softcap, act_dtype=None):
+    logits.mul_(scale)
+    if softcap:
+        logits.copy_(softcap * torch.tanh(logits / softcap))
 
 
 def add_rms_norm(residual, delta, weight, eps, out, rows=None):
@@ -75,6 +98,10 @@ def qk_norm_rope_store(qkv, n_heads, n_kv_heads, head_dim, store_kv, q_weight, k
         assert page >= 0, "a row writes into a page that was given back"
         k_pages[page, :, p % page_size, :] = k[r].to(k_pages.dtype)
         v_pages[page, :, p % page_size, :] = v[r].to(v_pages.dtype)
+        if r + 1 == n or int(row_request[r + 1]) != int(row_request[r]):
+            # a request's last row clears the places behind its value in the page (kernels that fetch whole pages
+            # multiply them by a probability of zero)
+            v_pages[page, :, p % page_size + 1:, :] = 0
 
 
 def paged_attention_generic(q, k_pages, v_pages, block_table, row_request, positions, scale, window, out):
@@ -178,4 +205,4 @@ def sample(logits, temperature, top_k, top_p, min_p, uniform, out, act_dtype=Non
         out[r] = int(order[int(hit[0])]) if len(hit) else int(order[-1])
 
 
-_NAMES += ["penalties", "sample"]
+_NAMES += ["penalties", "sample", "rms_norm_rows", "add_cast", "logit_scale_softcap"]

@@ -147,9 +147,9 @@ def decoder_layer(x: torch.Tensor, w: Dict[str, torch.Tensor], layer: int, cfg: 
 
 
 def forward(cfg: dict, w: Dict[str, torch.Tensor], ids: List[int], dtype=torch.float32, store=None,
-            windows: Optional[List[Optional[int]]] = None) -> torch.Tensor:
+            windows: Optional[List[Optional[int]]] = None, last: Optional[int] = None) -> torch.Tensor:
     """Logits [t, vocab] of every position of one sequence (qwen3.rs:398-407; the reference keeps
-    only the last row, attention_utils.rs:382-395)."""
+    only the last row, attention_utils.rs:382-395).  ``last``: only the logits of that many last positions."""
     cfg = dict(cfg)
     cfg.setdefault("head_dim", cfg["hidden_size"] // cfg["num_attention_heads"])
     w = {k: v.to(dtype) for k, v in w.items()}
@@ -159,6 +159,8 @@ def forward(cfg: dict, w: Dict[str, torch.Tensor], ids: List[int], dtype=torch.f
     for layer in range(cfg["num_hidden_layers"]):
         win = windows[layer] if windows is not None else None
         x = decoder_layer(x, w, layer, cfg, cos, sin, store, win)
+    if last is not None:
+        x = x[-last:]
     x = _rnd(rms_norm(x, w["model.norm.weight"], cfg["rms_norm_eps"]), store)
     head = w["lm_head.weight"] if "lm_head.weight" in w else w["model.embed_tokens.weight"]  # qwen3.rs:366-373
     return linear(x, head)

@@ -13,7 +13,7 @@ from inferrs_b200.runtime import Runtime
 pytestmark = pytest.mark.gpu
 
 CONFIGS = {"A": CONFIG_A, "B": CONFIG_B, "C": CONFIG_C, "D": CONFIG_D}
-# float32: the north-star bound.  bfloat16: the plain implementation rounds where the engine stores
+# float32: 1e-4 against the plain implementation.  bfloat16: the plain implementation rounds where the engine stores
 # bfloat16, so what is left is the order of sums and a few roundings that fall differently.
 TOL = {torch.float32: 1e-4, torch.bfloat16: 3e-2}
 _plain_cache = {}
@@ -289,3 +289,59 @@ def test_portions_through_the_kernel_with_two_query_tiles(tmp_path, monkeypatch)
         at2 += 1
     assert kernels.attention_pair_tcgen05_error() == 0
     runner.manager.check_invariants()
+
+
+@pytest.mark.parametrize("name", ["D", "B"])
+def test_a_replayed_step_of_portions_alone_gives_what_the_plain_step_gives_every_time(model_dirs, name):
+    """A captured step that holds prompt portions only launches the kernel for single tokens with nothing to do.
+    Its kernels start before their predecessors have ended (programmatic dependent launch), so a kernel that left
+    without waiting would let its successor read queries and keys that are not written yet.  The same captured
+    step is replayed many times with other tokens; every replay must give what the step launched plainly gives
+    (the same bits in float32; in bfloat16 the library may multiply 100 rows another way than the padded 128)."""
+    dtype = torch.bfloat16 if name == "D" else torch.float32
+    cfg = CONFIGS[name]
+    plain = make_runner(model_dirs[name], dtype, PAGE_SIZE[name], n_pages=64)
+    plain.graphs = plain.portion_graphs = None
+    runner = make_runner(model_dirs[name], dtype, PAGE_SIZE[name], n_pages=64)
+    assert runner.portion_graphs is not None
+    n, want_rows = 100, list(range(60, 100))
+    for i in range(40):
+        toks = random_tokens(n, cfg["vocab_size"], seed=900 + i)
+        plain.admit(i)
+        want = plain.step([StepEntry(i, toks, want_rows)])
+        plain.release(i)
+        runner.admit(i)
+        got = runner.step([StepEntry(i, toks, want_rows)])
+        runner.release(i)
+        if dtype == torch.float32:
+            assert torch.equal(got, want), f"replay {i}"
+        else:
+            assert rel_err(got, want) < 1e-2, f"replay {i}"
+    assert sorted(runner.portion_graphs.captured) == [128]
+    check(got, plain_logits(model_dirs[name], toks, dtype)[60:], dtype, "the last replay")
+
+
+def test_the_positions_of_the_published_checkpoints(tmp_path):
+    """max_position_embeddings as large as the published checkpoints' (40,960): the rotation tables, the block
+    tables of replayed steps (2,560 pages wide) and their descriptions have that size; a request far beyond the
+    sizes of the other tests is decoded and compared with the plain implementation."""
+    from inferrs_b200.weights.random_init import write_random_model
+    cfg = dict(CONFIG_D, max_position_embeddings=40960)
+    model_dir = str(tmp_path / "wide")
+    write_random_model(model_dir, cfg, seed=21, dtype=torch.bfloat16)
+    dtype = torch.bfloat16
+    runner = make_runner(model_dir, dtype, 16, n_pages=2600, max_requests=2)
+    assert runner.graphs.fixed_pages == [2560] and runner.graphs.max_context == 40960
+    n_prompt, n_decode = 2500, 24
+    toks = random_tokens(n_prompt + n_decode, cfg["vocab_size"], seed=5)
+    want = plain_logits(model_dir, toks, dtype)
+    runner.admit("r")
+    at, rows = 0, []
+    for n in (1000, 1000, 500):          # replayed steps of 1,024 and 512 rows
+        out = runner.step([StepEntry("r", toks[at:at + n], [n - 1])])
+        check(out, want[at + n - 1:at + n], dtype, f"the portion that ends at {at + n}")
+        at += n
+    for t in range(n_prompt, n_prompt + n_decode):
+        rows.append(runner.step([StepEntry("r", toks[t:t + 1], [0])]))
+    check(torch.cat(rows), want[n_prompt:], dtype, "decoding at 2,500 tokens with block tables of 2,560 pages")
+    assert sorted(runner.graphs.captured) == [1] and sorted(runner.portion_graphs.captured) == [512, 1024]

@@ -35,6 +35,56 @@ def test_embedding_gather(dtype, wdtype):
 
 
 @pytest.mark.parametrize("dtype", DTYPES)
+def test_embedding_gather_scaled(dtype):
+    from inferrs_b200 import kernels as K
+    table = rand((300, 72), dtype, 0)
+    ids = torch.randint(0, 300, (11,), dtype=torch.int32, device=dev())
+    out = torch.empty((11, 72), dtype=torch.float32, device=dev())
+    K.embedding_gather(table, ids, out, dtype, scale=8.485281)
+    assert torch.equal(out, table[ids.long()].float() * torch.tensor(8.485281, dtype=torch.float32))
+
+
+@pytest.mark.parametrize("dtype", DTYPES)
+@pytest.mark.parametrize("width", [72, 200, 4100])
+def test_rms_norm_rows_and_add_cast(dtype, width):
+    """The norm on a sub-layer's output, and the addition into the residual stream where no norm follows."""
+    from inferrs_b200 import kernels as K
+    n = 13
+    x = rand((n, width), dtype, 1, scale=2.0)
+    w = (1 + 0.1 * rand((width,), torch.float32, 3)).to(dtype)
+    out, ref = torch.empty_like(x), torch.empty_like(x)
+    K.rms_norm_rows(x, w, 1e-5, out)
+    R.rms_norm_rows(x, w, 1e-5, ref)
+    assert rel_err(out, ref) < TOL[dtype]
+    res = rand((n, width), torch.float32, 4)
+    for delta in (x, None):
+        r1, r2 = res.clone(), res.clone()
+        K.add_cast(r1, delta, out)
+        R.add_cast(r2, delta, ref)
+        assert torch.equal(out, ref) and torch.equal(r1, r2)
+    rows = torch.tensor([5, 0, 12], dtype=torch.int32, device=dev())
+    r1 = res.clone()
+    o3, f3 = out[:3].clone(), ref[:3].clone()
+    K.add_cast(r1, x, o3, rows)
+    R.add_cast(res.clone(), x, f3, rows)
+    assert torch.equal(o3, f3) and torch.equal(r1, res)
+
+
+@pytest.mark.parametrize("cap", [None, 30.0])
+def test_logit_scale_softcap(cap):
+    from inferrs_b200 import kernels as K
+    x = rand((5, 1237), torch.float32, 6, scale=40.0)
+    got, ref = x.clone(), x.clone()
+    K.logit_scale_softcap(got, 0.25, cap, torch.float32)
+    R.logit_scale_softcap(ref, 0.25, cap)
+    assert rel_err(got, ref) < 1e-6
+    if cap:
+        assert float(got.abs().max()) <= cap
+    with pytest.raises(K.KernelError):
+        K.logit_scale_softcap(got, 1.0, -1.0, torch.float32)
+
+
+@pytest.mark.parametrize("dtype", DTYPES)
 @pytest.mark.parametrize("n", [1, 37, 1000])
 def test_resolve_tokens(dtype, n):
     """ids[i] < 0 names place -1 - ids[i] of the tokens that an earlier step sampled; other ids stay; a place
@@ -374,66 +424,6 @@ def test_paged_attention_mma_decode_form(nh, nkv, d, ps, window, splits):
     assert rel_err(got, want) < 5e-2, "the far key that stands out was not seen"
 
 
-@pytest.mark.parametrize("n,m,k", [(1, 4096, 4096), (8, 6144, 4096), (17, 300, 136), (64, 517, 96), (33, 128, 64),
-                                   (100, 1000, 512), (300, 384, 256), (16, 4096, 12288), (129, 256, 1024)])
-def test_gemm_tn_tcgen05(n, m, k):
-    from inferrs_b200 import kernels as K
-    x, w = rand((n, k), torch.bfloat16, 70), rand((m, k), torch.bfloat16, 71)
-    ref = x.double() @ w.double().t()
-    for od in (torch.bfloat16, torch.float32):
-        for split in (0, 1, 2, 4, 8):
-            out = torch.full((n, m), float("nan"), dtype=od, device=dev())
-            K.gemm_tn_tcgen05(x, w, out, split)
-            assert K.gemm_tcgen05_error() == 0
-            # float32 sums of up to 12,288 products of magnitude ~1: about 1e-5 of the largest result
-            assert rel_err(out, ref) < (1e-2 if od == torch.bfloat16 else 3e-5), (od, split)
-
-
-@pytest.mark.parametrize("n,inner,k", [(1, 192, 256), (8, 12288, 4096), (5, 200, 136), (16, 64, 64), (3, 1000, 520),
-                                       (17, 328, 192), (32, 1000, 520)])
-def test_gemm_swiglu_tcgen05(n, inner, k):
-    """Both products of a gated feed-forward and the gate in one kernel, against the two-step reference; inner
-    sizes that are no multiple of the 64-row tile, a K that ends inside a 64-wide block."""
-    from inferrs_b200 import kernels as K
-    x = rand((n, k), torch.bfloat16, 41)
-    w = rand((2 * inner, k), torch.bfloat16, 42, scale=k ** -0.5)
-    out = torch.empty((n, inner), dtype=torch.bfloat16, device=dev())
-    K.gemm_swiglu_tcgen05(x, w, out)
-    gu = (x.float() @ w.float().t())
-    g, u = gu[:, :inner].bfloat16().float(), gu[:, inner:].bfloat16().float()
-    want = g / (1.0 + torch.exp(-g)) * u
-    assert K.gemm_tcgen05_error() == 0
-    assert rel_err(out, want) < 1e-2
-    # the same through the dispatcher, and the two-kernel form for more rows than the fused kernel takes
-    out2 = torch.empty_like(out)
-    K.gated_linear(x, w, out2, torch.bfloat16)
-    assert torch.equal(out, out2)
-    xl = rand((40, k), torch.bfloat16, 43)
-    outl = torch.empty((40, inner), dtype=torch.bfloat16, device=dev())
-    K.gated_linear(xl, w, outl, torch.bfloat16)
-    gl = (xl.float() @ w.float().t())
-    g, u = gl[:, :inner].bfloat16().float(), gl[:, inner:].bfloat16().float()
-    assert rel_err(outl, g / (1.0 + torch.exp(-g)) * u) < 1e-2
-
-
-@pytest.mark.parametrize("n,m,k", [(1, 4096, 4096), (8, 6144, 4096), (17, 300, 136), (64, 517, 96), (33, 128, 64),
-                                   (100, 1000, 512), (300, 384, 256), (16, 4096, 12288), (8, 20000, 1024),
-                                   (2, 128, 8192), (500, 4096, 512)])
-def test_gemm_tn_streamk(n, m, k):
-    from inferrs_b200 import kernels as K
-    x, w = rand((n, k), torch.bfloat16, 80), rand((m, k), torch.bfloat16, 81)
-    ref = x.double() @ w.double().t()
-    for od in (torch.bfloat16, torch.float32):
-        outs = []
-        for _ in range(3):   # the flags must be back at zero after every launch
-            out = torch.full((n, m), float("nan"), dtype=od, device=dev())
-            K.gemm_tn_streamk(x, w, out)
-            outs.append(out)
-        assert K.gemm_streamk_error() == 0
-        assert rel_err(outs[0], ref) < (1e-2 if od == torch.bfloat16 else 3e-5), od
-        assert torch.equal(outs[0], outs[1]) and torch.equal(outs[1], outs[2]), "the same shape must give the same bits"
-
-
 @pytest.mark.parametrize("nh,nkv,ps,window", [(8, 2, 16, None), (32, 8, 16, None), (6, 2 * 3, 16, 70), (4, 1, 64, None),
                                               (16, 1, 8, 200), (2, 2, 128, None), (10, 2, 16, None), (6, 2, 32, 90)])
 def test_paged_attention_tcgen05(nh, nkv, ps, window):
@@ -570,3 +560,179 @@ def test_attention_of_a_step_with_portions_and_single_tokens(nh, nkv, ps, window
                               positions[:n_real].contiguous(), scale, window, ref)
     assert rel_err(out[:n_real], ref) < 2e-2
     assert bool((out[n_real:] == 5.0).all()), "rows of no request must be left alone"
+
+
+def _attention_kernels(nh, nkv):
+    """name -> function(q, k_pages, v_pages, table, new, positions, row_request, scale, window, out) for every
+    bfloat16 attention kernel of head size 128 that serves prompt portions, and for single tokens."""
+    from inferrs_b200 import kernels as K
+
+    def prefill(kernel, tokens_per_tile):
+        def run(q, k_pages, v_pages, table, new, positions, row_request, scale, window, out):
+            q_start = torch.tensor([0] + list(torch.tensor(new).cumsum(0)), dtype=torch.int32, device=dev())
+            tile_req, tile_row0, n_tiles = _tiles(new, tokens_per_tile)
+            kernel(q, k_pages, v_pages, table, tile_req, tile_row0, n_tiles, q_start, positions, scale, window, out)
+        return run
+
+    def mma(q, k_pages, v_pages, table, new, positions, row_request, scale, window, out):
+        q_start = torch.tensor([0] + list(torch.tensor(new).cumsum(0)), dtype=torch.int32, device=dev())
+        tile_req, tile_row0, n_tiles = _tiles(new, 64 // (nh // nkv))
+        K.paged_attention_mma(q, k_pages, v_pages, table, tile_req, tile_row0, n_tiles, q_start, positions, scale,
+                              window, out, False)
+
+    def decode(q, k_pages, v_pages, table, new, positions, row_request, scale, window, out):
+        assert all(t == 1 for t in new)
+        K.paged_attention_decode(q, k_pages, v_pages, table, positions, scale, window, out, 6)
+
+    return {"tcgen05": prefill(K.paged_attention_tcgen05, 128 // (nh // nkv)),
+            "pair": prefill(K.paged_attention_pair_tcgen05, K.pair_tile_tokens(nh, nkv)),
+            "mma": mma, "decode": decode, "generic": lambda q, k, v, table, new, positions, row_request, scale, window,
+            out: K.paged_attention_generic(q, k, v, table, row_request, positions, scale, window, out)}
+
+
+def _no_error():
+    from inferrs_b200 import kernels as K
+    assert K.attention_tcgen05_error() == 0 and K.attention_pair_tcgen05_error() == 0 and K.attention_decode_error() == 0
+
+
+@pytest.mark.parametrize("name", ["tcgen05", "pair", "mma", "decode", "generic"])
+@pytest.mark.parametrize("window", [70, 128, 200])
+def test_the_key_just_outside_the_window_is_not_seen(name, window):
+    """The key at pos - window + 1 is the last one inside the window, the key at pos - window the first outside.
+    The outside key is made to stand out so much that it alone would decide the row if it were admitted."""
+    nh, nkv, d, ps, dtype = 8, 2, 128, 16, torch.bfloat16
+    lens = [500, 330, 700]
+    new = [1, 1, 1] if name == "decode" else [40, 1, 333]
+    table, positions, row_request, k_pages, v_pages = _paged_setup(dtype, nkv, d, ps, lens, new, 40)
+    n = sum(new)
+    q = rand((n, nh, d), dtype, 41)
+    scale = d ** -0.5 * 4
+    rows_last = [sum(new[:r + 1]) - 1 for r in range(len(new))]        # each request's last row
+    marked = []
+    for r, row in enumerate(rows_last):
+        outside = lens[r] - 1 - window
+        page, slot = int(table[r, outside // ps]), outside % ps
+        k_pages[page, :, slot, :] = 0
+        k_pages[page, :, slot, 0] = 16.0
+        v_pages[page, :, slot, :] = 100.0                              # it would show at once
+        q[row, :, :] = 0
+        q[row, :, 0] = 16.0
+        marked.append((row, page, slot))
+    out = torch.full((n, nh * d), float("nan"), dtype=dtype, device=dev())
+    ref = torch.empty_like(out)
+    _attention_kernels(nh, nkv)[name](q, k_pages, v_pages, table, new, positions, row_request, scale, window, out)
+    _no_error()
+    R.paged_attention_generic(q, k_pages, v_pages, table, row_request, positions, scale, window, ref)
+    assert rel_err(out, ref) < 2e-2
+    for row, _, _ in marked:
+        assert float(out[row].float().abs().max()) < 10.0, "the key just outside the window was seen"
+    # and one step further in: the same key at the inside edge decides the row
+    out2 = torch.empty_like(out)
+    _attention_kernels(nh, nkv)[name](q, k_pages, v_pages, table, new, positions, row_request, scale, window + 1, out2)
+    for row, _, _ in marked:
+        assert float((out2[row].float() - 100.0).abs().max()) < 2.0, "the key at the inside edge was not seen"
+
+
+@pytest.mark.parametrize("name", ["tcgen05", "pair", "mma", "decode"])
+@pytest.mark.parametrize("window", [None, 90])
+def test_what_an_earlier_owner_left_in_the_pages_does_not_reach_the_output(name, window):
+    """Pages are used again without being cleared.  Everything a request does not own holds NaN here: the pages of
+    no request, the places of its last page behind its last token (keys only: the kernel that writes a request's
+    last value clears the values behind it, which is done here by hand), and, with a window, the pages that the
+    window has passed (their block-table entries are -1).  Every output must be finite and equal the reference."""
+    nh, nkv, d, ps, dtype = 8, 2, 128, 16, torch.bfloat16
+    lens = [300, 17, 200, 65, 1, 700]
+    new = [1] * len(lens) if name == "decode" else [40, 17, 200, 1, 1, 333]
+    table, positions, row_request, k_pages, v_pages = _paged_setup(dtype, nkv, d, ps, lens, new, 50)
+    owned = torch.zeros(k_pages.shape[0], dtype=torch.bool)
+    nan = float("nan")
+    table_h = table.cpu()
+    for r, n_tok in enumerate(lens):
+        n_pg = (n_tok + ps - 1) // ps
+        first = 0
+        if window is not None:
+            first = max(0, n_tok - new[r] - window + 1) // ps          # pages that every query's window has passed
+            for p in range(first):
+                table_h[r, p] = -1
+        for p in range(first, n_pg):
+            owned[int(table_h[r, p])] = True
+        last, used = int(table_h[r, n_pg - 1]), n_tok - (n_pg - 1) * ps
+        k_pages[last, :, used:, :] = nan
+        v_pages[last, :, used:, :] = 0.0
+    k_pages[~owned.to(dev())] = nan
+    v_pages[~owned.to(dev())] = nan
+    table = table_h.to(dev())
+    n = sum(new)
+    q = rand((n, nh, d), dtype, 51)
+    scale = d ** -0.5
+    out = torch.full((n, nh * d), nan, dtype=dtype, device=dev())
+    ref = torch.empty_like(out)
+    _attention_kernels(nh, nkv)[name](q, k_pages, v_pages, table, new, positions, row_request, scale, window, out)
+    _no_error()
+    assert bool(torch.isfinite(out.float()).all()), "something that no request owns reached the output"
+    R.paged_attention_generic(q, k_pages, v_pages, table, row_request, positions, scale, window, ref)
+    assert rel_err(out, ref) < 2e-2
+
+
+def test_the_last_value_of_a_request_clears_the_places_behind_it():
+    """The kernel that writes keys and values: behind the value of a request's last row its page holds zeros
+    afterwards, whatever was there; other pages and the places before it are untouched."""
+    from inferrs_b200 import kernels as K
+    nh, nkv, d, ps = 4, 2, 128, 16
+    for dtype, n_rows in ((torch.bfloat16, [3, 1, 300]), (torch.bfloat16, [3, 1, 20]), (torch.float32, [3, 1, 20])):
+        lens = [35, 64, n_rows[2] + 5]
+        table, positions, row_request, k_pages, v_pages = _paged_setup(dtype, nkv, d, ps, lens, n_rows, 60)
+        k_pages[:], v_pages[:] = float("nan"), float("nan")
+        n = sum(n_rows)
+        qkv = rand((n, (nh + 2 * nkv) * d), dtype, 61)
+        ang = torch.arange(max(lens), dtype=torch.float32)[:, None] * (1.0 / 10000 ** (torch.arange(d // 2) * 2.0 / d))[None]
+        cos, sin = torch.cos(ang).to(dev()), torch.sin(ang).to(dev())
+        q = torch.empty((n, nh, d), dtype=dtype, device=dev())
+        K.qk_norm_rope_store(qkv, nh, nkv, d, True, None, None, 1e-6, cos, sin, d, positions, row_request, table,
+                             k_pages, v_pages, q)
+        for r, n_tok in enumerate(lens):
+            last_page, used = int(table[r, (n_tok - 1) // ps]), (n_tok - 1) % ps + 1
+            assert bool((v_pages[last_page, :, used:, :] == 0).all()), (dtype, r)
+            assert bool(torch.isfinite(v_pages[last_page, :, used - 1, :].float()).all())
+            if used < ps:
+                assert bool(torch.isnan(k_pages[last_page, :, used:, :].float()).all()), "keys are left alone"
+        written = torch.zeros(k_pages.shape[0], dtype=torch.bool)
+        for r, n_tok in enumerate(lens):
+            for p in range((n_tok - n_rows[r]) // ps, (n_tok + ps - 1) // ps):
+                written[int(table[r, p])] = True
+        assert bool(torch.isnan(v_pages[~written.to(dev())].float()).all()), "a page of no row was written to"
+
+
+@pytest.mark.parametrize("name", ["tcgen05", "pair", "decode"])
+@pytest.mark.parametrize("context", [8192, 16384])
+def test_attention_over_long_contexts(name, context):
+    """Thousands of cached keys (two key/value heads): one request with a portion at the end of a long context
+    beside a short one, or single tokens at the end; a key near the start stands out for the last row."""
+    nh, nkv, d, ps, dtype = 8, 2, 128, 16, torch.bfloat16
+    lens = [context, 333, context - 4097]
+    new = [1, 1, 1] if name == "decode" else [200, 70, 1]
+    table, positions, row_request, k_pages, v_pages = _paged_setup(dtype, nkv, d, ps, lens, new, 70)
+    n = sum(new)
+    q = rand((n, nh, d), dtype, 71)
+    far = 3
+    page, slot = int(table[0, far // ps]), far % ps
+    k_pages[page, :, slot, :] = 0
+    k_pages[page, :, slot, 0] = 16.0
+    q[new[0] - 1, :, :] = 0
+    q[new[0] - 1, :, 0] = 16.0
+    scale = d ** -0.5 * 4
+    out = torch.full((n, nh * d), float("nan"), dtype=dtype, device=dev())
+    _attention_kernels(nh, nkv)[name](q, k_pages, v_pages, table, new, positions, row_request, scale, None, out)
+    _no_error()
+    # the reference for the rows that are compared: the first, middle and last rows of every request
+    starts = [0] + list(torch.tensor(new).cumsum(0).tolist())
+    pick = sorted({starts[r] + i for r in range(len(new)) for i in (0, new[r] // 2, new[r] - 1)})
+    idx = torch.tensor(pick, device=dev())
+    ref = torch.empty((len(pick), nh * d), dtype=dtype, device=dev())
+    R.paged_attention_generic(q[idx].contiguous(), k_pages, v_pages, table, row_request[idx].contiguous(),
+                              positions[idx].contiguous(), scale, None, ref)
+    assert bool(torch.isfinite(out.float()).all())
+    assert rel_err(out[idx], ref) < 2e-2
+    got = out[new[0] - 1].view(nh, d).float()
+    want = v_pages[page, :, slot, :].float().repeat_interleave(nh // nkv, dim=0)
+    assert rel_err(got, want) < 5e-2, "the far key that stands out was not seen"

@@ -154,7 +154,7 @@ def run_cut(runner, rid, toks, sizes):
 def test_layers_with_different_mixers_windows_and_a_layer_twice(dtype, cfg):
     spec, _ = spec_from_config(cfg)
     layers = list(spec.layers)
-    layers[1] = dataclasses.replace(layers[1], mixer=dataclasses.replace(layers[1].mixer, window=24))
+    layers[1] = layers[1].with_part("mixer", dataclasses.replace(layers[1].mixer, window=24))
     order = [0, 1, 1] + list(range(2, len(layers)))
     spec = dataclasses.replace(spec, layers=tuple(layers),
                                schedule=tuple(ScheduleEntry(layer=l, cache=i) for i, l in enumerate(order)))
@@ -184,7 +184,7 @@ def test_a_layer_that_reads_another_layers_cache():
     spec, _ = spec_from_config(cfg)
     layers = list(spec.layers)
     reader = dataclasses.replace(layers[1].mixer, own_kv=False, k_proj=None, v_proj=None, k_norm=None)
-    layers[1] = dataclasses.replace(layers[1], mixer=reader)
+    layers[1] = layers[1].with_part("mixer", reader)
     spec = dataclasses.replace(spec, layers=tuple(layers), schedule=(ScheduleEntry(0, 0), ScheduleEntry(1, 0)))
     names = [d.name for d in declared_tensors(spec)]
     assert "model.layers.1.self_attn.k_proj.weight" not in names
@@ -248,7 +248,7 @@ def test_toy_mixer_with_state_is_registered_built_and_stepped(dtype):
     spec, _ = spec_from_config(cfg)
     layers = list(spec.layers)
     toy = ToyEmaSpec(width=cfg["hidden_size"], decay=0.8, proj="model.layers.1.toy.proj.weight")
-    layers[1] = dataclasses.replace(layers[1], mixer=toy)
+    layers[1] = layers[1].with_part("mixer", toy)
     spec = dataclasses.replace(spec, layers=tuple(layers))
     names = [d.name for d in declared_tensors(spec)]
     assert toy.proj in names and "model.layers.1.self_attn.q_proj.weight" not in names
@@ -257,7 +257,7 @@ def test_toy_mixer_with_state_is_registered_built_and_stepped(dtype):
     weights[toy.proj] = (weights[toy.proj].float() * 20).to(dtype)
     runner = ModelRunner(spec, weights, rt, page_size=16, n_pages=32, max_requests=3)
     assert runner.graphs is None, "a part that does not declare graph_safe must keep the step out of CUDA graphs"
-    assert list(runner.storage.states) == [1] and runner.storage.states[1].shape == (3, cfg["hidden_size"])
+    assert list(runner.storage.states) == [1] and runner.storage.states[1].shape == (3 + 1, cfg["hidden_size"])   # one more for padding requests
     assert len(runner.storage.kv) == 1 and runner.storage.kv[0].shape[0] == 1   # only layer 0 has pages
     toks = [random_tokens(n, cfg["vocab_size"], seed=20 + n) for n in (60, 45, 33)]
     tol = 1e-4 if dtype == torch.float32 else 3e-2
@@ -304,7 +304,7 @@ def test_replayed_steps_get_the_description_that_the_general_builder_gives():
     from inferrs_b200.engine.batch import build_context
     spec, _ = spec_from_config(CONFIG_B)
     layers = list(spec.layers)
-    layers[1] = dataclasses.replace(layers[1], mixer=dataclasses.replace(layers[1].mixer, window=24))
+    layers[1] = layers[1].with_part("mixer", dataclasses.replace(layers[1].mixer, window=24))
     spec = dataclasses.replace(spec, layers=tuple(layers))
     rt = Runtime.cuda(torch.float32)
     weights = weights_for(declared_tensors(spec), torch.float32, seed=8)

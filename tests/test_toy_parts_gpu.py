@@ -106,7 +106,7 @@ def test_a_feed_forward_with_routing_is_registered_built_and_stepped():
     spec, _ = spec_from_config(cfg)
     layers = list(spec.layers)
     toy = ToyRoutedSpec(width=cfg["hidden_size"], inner=40, n_experts=3, prefix="model.layers.1.toy_moe")
-    layers[1] = dataclasses.replace(layers[1], ffn=toy)
+    layers[1] = layers[1].with_part("feed_forward", toy)
     spec = dataclasses.replace(spec, layers=tuple(layers))
     names = [d.name for d in declared_tensors(spec)]
     assert f"{toy.prefix}.router.weight" in names and "model.layers.1.mlp.gate_proj.weight" not in names
@@ -173,7 +173,7 @@ def test_another_position_encoding_is_registered_built_and_stepped(dtype, cfg):
     spec, _ = spec_from_config(cfg)
     d = cfg["head_dim"]
     toy = ToyScaledRotarySpec(rot_dim=d // 2, theta=500.0, max_positions=cfg["max_position_embeddings"], factor=4.0)
-    layers = tuple(dataclasses.replace(l, mixer=dataclasses.replace(l.mixer, position=toy)) for l in spec.layers)
+    layers = tuple(l.with_part("mixer", dataclasses.replace(l.mixer, position=toy)) for l in spec.layers)
     spec = dataclasses.replace(spec, layers=layers)
     rt = Runtime.cuda(dtype)
     weights = weights_for(declared_tensors(spec), dtype, seed=14)

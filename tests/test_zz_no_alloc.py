@@ -48,6 +48,15 @@ def test_no_alloc_entry_point_matches_the_regular_one_twice():
     fn, msg = _symbol()
     nh, nkv, d, ps, splits = 32, 8, 128, 16, 5
     stream = torch.cuda.current_stream().cuda_stream
+    # a first call sets the entry point up on this device (it looks the scratch's address up, the kernel's image is
+    # loaded): what is measured below are calls in the state in which a server makes them
+    c = _case(0, [100, 70], nh, nkv, d, ps)
+    warm = torch.empty((2, nh * d), dtype=torch.bfloat16, device="cuda")
+    rc = fn(c["q"].data_ptr(), c["k"].data_ptr(), c["v"].data_ptr(), c["table"].data_ptr(), c["table"].shape[1], ps,
+            c["k"].shape[0], c["rows"].data_ptr(), c["q_start"].data_ptr(), c["positions"].data_ptr(), 2, nh, nkv, d,
+            d ** -0.5, 0, warm.data_ptr(), splits, stream)
+    assert rc == 0, msg(rc).decode()
+    torch.cuda.synchronize()
     for seed, lens in ((1, [700, 33, 64, 1, 129]), (2, [90, 500, 17])):   # two calls in a row, different shapes
         c = _case(seed, lens, nh, nkv, d, ps)
         n = len(lens)
@@ -55,16 +64,19 @@ def test_no_alloc_entry_point_matches_the_regular_one_twice():
         K.paged_attention_mma(c["q"], c["k"], c["v"], c["table"], c["rows"], c["q_start"], n, c["q_start"],
                               c["positions"], d ** -0.5, None, want, True, splits)
         got = torch.full_like(want, float("nan"))
+        torch.cuda.synchronize()
         before = torch.cuda.memory_allocated()
+        free_before = torch.cuda.mem_get_info()[0]      # the device's own count: sees what torch's allocator does not
         rc = fn(c["q"].data_ptr(), c["k"].data_ptr(), c["v"].data_ptr(), c["table"].data_ptr(), c["table"].shape[1],
                 ps, c["k"].shape[0], c["rows"].data_ptr(), c["q_start"].data_ptr(), c["positions"].data_ptr(), n, nh,
                 nkv, d, d ** -0.5, 0, got.data_ptr(), splits, stream)
         assert rc == 0, msg(rc).decode()
         torch.cuda.synchronize()
         assert torch.cuda.memory_allocated() == before
-        diff = (got.float() - want.float()).abs().max().item()
-        assert diff <= 2e-2 * want.float().abs().max().item(), diff
+        assert torch.cuda.mem_get_info()[0] >= free_before, "the call took device memory"
+        # the same kernel with the same number of slices, only the scratch lies elsewhere: the same bits
         assert not torch.isnan(got.float()).any()
+        assert torch.equal(got, want)
 
 
 def test_no_alloc_entry_point_refuses_what_does_not_fit():
