@@ -7,7 +7,12 @@ inferrs/src/bench.rs:21-38 ``bench``).  The model is a local folder (the referen
 ``tokenizer.json`` in the model folder and the ``tokenizers`` library.
 
     python -m inferrs_b200 run MODEL_DIR --prompt-ids 1,2,3 --max-tokens 32 --temperature 0
+    python -m inferrs_b200 run CONFIG.json --random-weights 0 --random-prompt 64 --ignore-eos --max-tokens 32
     python -m inferrs_b200 bench MODEL_DIR --prompt-len 128 --max-tokens 128
+
+Beyond the reference's options: ``--prefill-chunk`` (the most tokens of one prompt in a step), ``--ignore-eos``,
+``--min-p``, ``--random-weights SEED`` (the model argument is then a config.json, or a folder with one, and the
+weights are made on the device), ``--random-prompt LEN`` and ``--prompt-file``.
 """
 from __future__ import annotations
 
@@ -36,14 +41,26 @@ def _shared(ap: argparse.ArgumentParser):
     ap.add_argument("--top-k", type=int, default=50, help="top-k sampling (0 = off)")
     ap.add_argument("--max-tokens", type=int, default=2048, help="max tokens to generate")
     ap.add_argument("--seed", type=int, default=None, help="seed for reproducible sampling")
+    ap.add_argument("--min-p", type=float, default=0.0, help="keep tokens with p >= min_p * p_max (0 = off)")
+    ap.add_argument("--ignore-eos", action="store_true", help="do not stop at end-of-sequence or stop tokens")
+    ap.add_argument("--prefill-chunk", type=int, default=0,
+                    help="most tokens of one prompt in a step (0 = the step's whole budget)")
+    ap.add_argument("--random-weights", type=int, default=None, metavar="SEED",
+                    help="MODEL is a config.json (or a folder with one): weights are random, N(0, 0.02), from this seed")
 
 
 def _engine(args):
     from .engine.engine import Engine
-    return Engine(args.model, dtype=args.dtype, block_size=args.block_size,
-                  num_blocks=args.max_blocks or None, paged_attention=args.paged_attention,
-                  max_batch_size=args.max_batch_size, max_tokens_per_step=args.max_tokens_per_step,
-                  max_seq_len=args.max_seq_len)
+    common = dict(dtype=args.dtype, block_size=args.block_size, num_blocks=args.max_blocks or None,
+                  paged_attention=args.paged_attention, max_batch_size=args.max_batch_size,
+                  max_tokens_per_step=args.max_tokens_per_step, max_seq_len=args.max_seq_len,
+                  prefill_chunk=args.prefill_chunk or None)
+    if args.random_weights is not None:
+        path = os.path.join(args.model, "config.json") if os.path.isdir(args.model) else args.model
+        with open(path, "r", encoding="utf-8") as f:
+            config = json.load(f)
+        return Engine(config=config, random_weights=args.random_weights, **common)
+    return Engine(args.model, **common)
 
 
 def _tokenizer(model_dir: str):
@@ -59,23 +76,39 @@ def _tokenizer(model_dir: str):
 
 def cmd_run(args) -> int:
     from .sampling.params import SamplingParams
-    tok = _tokenizer(args.model)
-    if args.prompt_ids:
+    tok = _tokenizer(args.model) if os.path.isdir(args.model) else None
+    eng = None
+    prompt_text = args.prompt
+    if args.prompt_file is not None:
+        with open(args.prompt_file, "r", encoding="utf-8") as f:
+            content = f.read()
+        if all(t.lstrip("-").isdigit() for t in content.replace(",", " ").split()) and content.strip():
+            args.prompt_ids = content          # a file of token ids
+        else:
+            prompt_text = content
+    if args.random_prompt:
+        import random
+        eng = _engine(args)
+        rng = random.Random(args.seed if args.seed is not None else 0)
+        ids = [rng.randrange(eng.spec.vocab_size) for _ in range(args.random_prompt)]
+        args.prompt_ids = " ".join(map(str, ids))
+    elif args.prompt_ids:
         ids = [int(t) for t in args.prompt_ids.replace(",", " ").split()]
-    elif args.prompt is not None:
+    elif prompt_text is not None:
         if tok is None:
             print("run: a text prompt needs tokenizer.json in the model folder and the tokenizers library; "
                   "use --prompt-ids", file=sys.stderr)
             return 2
-        text = args.prompt if args.system is None else args.system + "\n" + args.prompt
+        text = prompt_text if args.system is None else args.system + "\n" + prompt_text
         ids = tok.encode(text).ids
     else:
-        print("run: give a prompt or --prompt-ids", file=sys.stderr)
+        print("run: give a prompt, --prompt-ids, --prompt-file or --random-prompt", file=sys.stderr)
         return 2
-    eng = _engine(args)
-    sp = SamplingParams(temperature=args.temperature, top_p=args.top_p, top_k=args.top_k,
+    eng = eng or _engine(args)
+    sp = SamplingParams(temperature=args.temperature, top_p=args.top_p, top_k=args.top_k, min_p=args.min_p,
                         repetition_penalty=args.repetition_penalty, repeat_last_n=args.repeat_last_n,
-                        frequency_penalty=args.frequency_penalty, max_tokens=args.max_tokens, seed=args.seed)
+                        frequency_penalty=args.frequency_penalty, max_tokens=args.max_tokens, seed=args.seed,
+                        ignore_eos=args.ignore_eos)
     t0 = time.perf_counter()
     out: List[int] = []
     text = ""
@@ -102,7 +135,7 @@ def cmd_bench(args) -> int:
     from .sampling.params import SamplingParams
     eng = _engine(args)
     prompt = [1 % eng.spec.vocab_size] * args.prompt_len
-    sp = SamplingParams(temperature=args.temperature, top_p=args.top_p, top_k=args.top_k,
+    sp = SamplingParams(temperature=args.temperature, top_p=args.top_p, top_k=args.top_k, min_p=args.min_p,
                         max_tokens=args.max_tokens, seed=args.seed if args.seed is not None else 0, ignore_eos=True)
     prefill, decode, ttft, e2e = [], [], [], []
     for run in range(args.warmup + args.runs):
@@ -143,6 +176,9 @@ def main(argv: Optional[List[str]] = None) -> int:
     _shared(run)
     run.add_argument("prompt", nargs="?", default=None, help="text prompt (needs tokenizer.json)")
     run.add_argument("--prompt-ids", default=None, help="prompt as token ids, separated by commas or spaces")
+    run.add_argument("--prompt-file", default=None, help="file with the prompt: token ids, or text")
+    run.add_argument("--random-prompt", type=int, default=0, metavar="LEN",
+                     help="a prompt of LEN token ids drawn uniformly from the vocabulary (seeded by --seed)")
     run.add_argument("--system", default=None, help="system prompt, put before the prompt")
     run.add_argument("--repetition-penalty", type=float, default=1.1, help="llama.cpp-style; 1.0 = disabled")
     run.add_argument("--repeat-last-n", type=int, default=64, help="window of the penalties; 0 = disabled")

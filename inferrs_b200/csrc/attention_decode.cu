@@ -426,6 +426,12 @@ IB_EXPORT int ib_attention_decode_error(int reset) {
     return v;
 }
 
+// The same word on its way to `out` (pinned host memory) in stream order, without waiting for the device: the
+// caller reads it after an event that it records behind this call.
+IB_EXPORT int ib_attention_decode_error_async(int* out, cudaStream_t stream) {
+    return (int)cudaMemcpyFromSymbolAsync(out, dec::g_error, sizeof(int), 0, cudaMemcpyDeviceToHost, stream);
+}
+
 #else
 
 IB_EXPORT int ib_paged_attention_decode(const void*, const void*, const void*, const int*, int, int, int, const int*, int,
@@ -435,5 +441,7 @@ IB_EXPORT int ib_paged_attention_decode(const void*, const void*, const void*, c
 }
 
 IB_EXPORT int ib_attention_decode_error(int) { return 0; }
+
+IB_EXPORT int ib_attention_decode_error_async(int* out, cudaStream_t) { *out = 0; return 0; }
 
 #endif

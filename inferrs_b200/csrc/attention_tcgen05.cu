@@ -402,6 +402,12 @@ IB_EXPORT int ib_attention_tcgen05_error(int reset) {
     return v;
 }
 
+// The same word on its way to `out` (pinned host memory) in stream order, without waiting for the device: the
+// caller reads it after an event that it records behind this call.
+IB_EXPORT int ib_attention_tcgen05_error_async(int* out, cudaStream_t stream) {
+    return (int)cudaMemcpyFromSymbolAsync(out, fa::g_error, sizeof(int), 0, cudaMemcpyDeviceToHost, stream);
+}
+
 #else  // the float32 build has no tensor-core attention
 
 IB_EXPORT int ib_paged_attention_tcgen05(const void*, const void*, const void*, const int*, int, int, int, const int*,
@@ -411,5 +417,7 @@ IB_EXPORT int ib_paged_attention_tcgen05(const void*, const void*, const void*, 
 }
 
 IB_EXPORT int ib_attention_tcgen05_error(int) { return 0; }
+
+IB_EXPORT int ib_attention_tcgen05_error_async(int* out, cudaStream_t) { *out = 0; return 0; }
 
 #endif

@@ -452,5 +452,11 @@ IB_EXPORT int ib_gemm_tcgen05_error(int reset) {
     return v;
 }
 
+// The same word on its way to `out` (pinned host memory) in stream order, without waiting for the device: the
+// caller reads it after an event that it records behind this call.
+IB_EXPORT int ib_gemm_tcgen05_error_async(int* out, cudaStream_t stream) {
+    return (int)cudaMemcpyFromSymbolAsync(out, tc::g_error, sizeof(int), 0, cudaMemcpyDeviceToHost, stream);
+}
+
 
 #endif

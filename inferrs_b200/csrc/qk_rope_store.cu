@@ -31,6 +31,11 @@ IB_EXPORT int ib_row_fault(int reset) {
     return v;
 }
 
+// The same word on its way to `out` (pinned host memory) in stream order, without waiting for the device.
+IB_EXPORT int ib_row_fault_async(int* out, cudaStream_t stream) {
+    return (int)cudaMemcpyFromSymbolAsync(out, ib_row_fault_word, sizeof(int), 0, cudaMemcpyDeviceToHost, stream);
+}
+
 // A request's last row of the step clears the places behind its value in the value's page.  The attention kernels
 // that fetch whole pages give those places a probability of zero, but zero times what an earlier owner of the
 // page may have left there (an infinity, no number at all) would not be zero.  Keys need no clearing: a score is

@@ -32,22 +32,25 @@ __device__ __forceinline__ unsigned long long global_ns() {
     asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t));
     return t;
 }
-// A wait with a limit of about two seconds: when it runs out, `code` is recorded in *error_word (if that still
-// holds 0) and false comes back; the caller then leaves its loops, lets outstanding copies land and returns.
-// A barrier that has completed already costs one inlined test and no call.
-static __device__ __noinline__ bool mbar_wait_slow(unsigned bar, unsigned parity, int* error_word, int code) {
+// A wait with a limit (about two seconds unless the caller gives another): when it runs out, `code` is recorded in
+// *error_word (if that still holds 0) and false comes back; the caller then leaves its loops, lets outstanding
+// copies land and returns.  A barrier that has completed already costs one inlined test and no call.
+constexpr unsigned long long MBAR_WAIT_LIMIT_NS = 2000000000ull;
+static __device__ __noinline__ bool mbar_wait_slow(unsigned bar, unsigned parity, int* error_word, int code,
+                                                   unsigned long long limit_ns) {
     const unsigned long long t0 = global_ns();
     for (unsigned it = 1;; ++it) {
         if (mbar_try_wait(bar, parity)) return true;
-        if ((it & 1023u) == 0 && global_ns() - t0 > 2000000000ull) {
+        if ((it & 1023u) == 0 && global_ns() - t0 > limit_ns) {
             atomicCAS(error_word, 0, code);
             return false;
         }
     }
 }
-__device__ __forceinline__ bool mbar_wait_bounded(unsigned bar, unsigned parity, int* error_word, int code) {
+__device__ __forceinline__ bool mbar_wait_bounded(unsigned bar, unsigned parity, int* error_word, int code,
+                                                  unsigned long long limit_ns = MBAR_WAIT_LIMIT_NS) {
     if (mbar_try_wait(bar, parity)) return true;
-    return mbar_wait_slow(bar, parity, error_word, code);
+    return mbar_wait_slow(bar, parity, error_word, code, limit_ns);
 }
 
 // ---- bulk tensor copies into shared memory; x is the innermost coordinate (x * element size: a multiple of 16 bytes)

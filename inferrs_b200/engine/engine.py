@@ -17,9 +17,14 @@ from ..runtime import Runtime, parse_dtype
 from ..sampling.params import SamplingParams
 from ..sampling.sampler import Sampler
 from .batch import StepEntry
+from .health import KernelHealth
 from .loading import load_model_dir, random_model
 from .runner import ModelRunner
 from .scheduler import PlannedEntry, Request, Scheduler
+
+
+class KernelFault(RuntimeError):
+    """A kernel reported that it could not do its work (see :mod:`inferrs_b200.engine.health`)."""
 
 
 class Engine:
@@ -57,10 +62,12 @@ class Engine:
             raise ValueError("give a model_dir, or a config dictionary with a random_weights seed")
         self.spec, self.config = spec, cfg
         self.max_seq_len = min(max_seq_len, spec.max_positions) if max_seq_len else spec.max_positions
-        if num_blocks is None:
-            num_blocks = self._blocks_for_fraction(spec, block_size, paged_attention, max_batch_size)
+        # the cache is sized (num_blocks None) once the model stands and the tensors that were fused into others
+        # have been given back: only then does the free memory say what is left
         self.runner = ModelRunner(spec, weights, self.rt, page_size=block_size, n_pages=num_blocks,
-                                  max_requests=max_batch_size, max_context=self.max_seq_len)
+                                  max_requests=max_batch_size, max_context=self.max_seq_len,
+                                  cache_fraction=paged_attention, consume_weights=True)
+        del weights
         self.scheduler = Scheduler(self.runner.manager, max_batch_size, max_tokens_per_step, self.max_seq_len,
                                    spec.eos_token_ids, prefill_chunk,
                                    on_admit=lambda rid, slot: self.runner.storage.clear_slot(slot))
@@ -76,24 +83,12 @@ class Engine:
         self.n_steps_in_vain = 0
         self.n_steps_ahead = 0              # steps launched before the tokens of the step before them were read
         self.n_portion_steps_ahead = 0      # ... of them, steps with prompt portions
-
-    def _blocks_for_fraction(self, spec, block_size, fraction, max_batch_size) -> int:
-        from .model import cache_needs
-        if not 0.0 < fraction <= 1.0:
-            raise ValueError(f"paged_attention must be in (0, 1], got {fraction}")
-        kv_needs, _ = cache_needs(spec)
-        elem = torch.empty((), dtype=self.rt.dtype).element_size()
-        per_page = sum(2 * n.n_kv_heads * n.head_dim * block_size * elem for n in kv_needs.values())
-        if self.rt.device.type != "cuda":
-            raise RuntimeError("num_blocks must be given when the cache is not on a CUDA device")
-        free, _total = torch.cuda.mem_get_info(self.rt.device)
-        blocks = int(free * fraction) // max(per_page, 1)
-        # no request can use more than max_positions tokens: more pages than that per slot are never touched
-        useful = max_batch_size * ((self.max_seq_len + block_size - 1) // block_size)
-        blocks = min(blocks, useful)
-        if blocks < 1:
-            raise RuntimeError("no memory is left for the cache")
-        return blocks
+        # what the kernels report about themselves is looked at every few steps and when a request has ended
+        self.health = KernelHealth(self.rt.dtype) if self.rt.device.type == "cuda" else None
+        self.kernel_errors: List[dict] = []
+        self._unchecked: List[Request] = []  # ended since the last look that found nothing
+        self._checked_up_to = 0              # ... of them, those that ended before the look on its way was asked for
+        self._last_look = 0
 
     # ---- requests -------------------------------------------------------------------
     def add_request(self, prompt: Sequence[int], sampling: Optional[SamplingParams] = None,
@@ -199,9 +194,60 @@ class Engine:
                 return True
         return False
 
+    # ---- what the kernels report about themselves ---------------------------------------
+    def _look_at_kernels(self, wait: bool = False) -> List[Request]:
+        """Read the kernels' error words if they have arrived (``wait``: ask for them now and wait).  A word that is
+        set means that rows of some step since the last clean look were left unwritten: every running request, and
+        every request that ended since that look, ends with reason "error"; the words are cleared.  Returns the
+        requests that ended here."""
+        h = getattr(self, "health", None)
+        if h is None:
+            return []
+        if wait and not h.pending:
+            h.queue()
+            self._checked_up_to = len(self._unchecked)
+        found = h.poll(wait)
+        if found is None:
+            return []
+        if not found:
+            del self._unchecked[:self._checked_up_to]
+            self._checked_up_to = 0
+            return []
+        failed = self.flush() if self._in_flight is not None else []
+        found.update(h.reset())
+        self.kernel_errors.append({"step": self.n_steps, "words": found})
+        for r in list(self.scheduler.running):
+            self.scheduler.abort(r.rid, reason="error")
+            failed.append(r)
+        for r in self._unchecked + failed:
+            r.finish_reason = "error"
+        self._unchecked, self._checked_up_to = [], 0
+        return failed
+
+    def _ask_about_kernels(self, ended: Sequence[Request]):
+        h = getattr(self, "health", None)
+        if h is None:
+            return
+        self._unchecked.extend(ended)
+        if not h.pending and (ended or self.n_steps - self._last_look >= h.every):
+            h.queue()
+            self._checked_up_to = len(self._unchecked)
+            self._last_look = self.n_steps
+
     def step(self) -> List[Request]:
         """Plan, run and sample one step; returns the requests that are known to have finished.  With
-        ``overlap`` the step is launched before the tokens of the one before it are read, where that can be."""
+        ``overlap`` the step is launched before the tokens of the one before it are read, where that can be.
+        A request may end with reason "error": a kernel reported that it left rows unwritten (``stats()`` says
+        which); a request that a call before returned as finished is marked so too if it ended since the last
+        look that found nothing."""
+        failed = self._look_at_kernels()
+        if failed:
+            return failed
+        finished = self._step()
+        self._ask_about_kernels(finished)
+        return finished
+
+    def _step(self) -> List[Request]:
         finished: List[Request] = []
         prev, self._in_flight = self._in_flight, None
         if prev is not None and self._ends_for_sure(prev):
@@ -253,8 +299,15 @@ class Engine:
         while len(done) < len(rids) and self.has_work():
             for r in self.step():
                 done[r.rid] = r
+        for r in self._look_at_kernels(wait=True):      # the device is idle now: this look costs nothing
+            done[r.rid] = r
         out = [done[r] for r in rids]
-        return out if return_requests else [r.output for r in out]
+        if return_requests:
+            return out
+        bad = [r.rid for r in out if r.finish_reason == "error"]
+        if bad:
+            raise KernelFault(f"requests {bad} ended with an error that a kernel reported: {self.kernel_errors[-1]}")
+        return [r.output for r in out]
 
     def stream(self, prompt: Sequence[int], sampling: Optional[SamplingParams] = None):
         """Generated token ids of one prompt, one after the other as the steps bring them (the reference's
@@ -288,4 +341,5 @@ class Engine:
             "free_pages": [p.n_free for p in m.pools],
             "pages": [p.n_pages for p in m.pools],
             "cache_bytes": self.runner.storage.total_bytes(),
+            "kernel_errors": list(getattr(self, "kernel_errors", [])),
         }

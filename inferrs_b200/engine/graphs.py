@@ -124,7 +124,7 @@ class DecodeGraphs:
         bucket = self.bucket_for(len(entries))
         cap = self.captured.get(bucket)
         if cap is None:
-            cap = self._capture(entries, bucket)
+            cap = self._capture(entries, bucket, run=carry is None)
             if carry is None:
                 return self._wanted(cap, entries)
         self._describe(cap, entries, bucket, carry)
@@ -141,7 +141,10 @@ class DecodeGraphs:
             return cap.logits[:0]
         return cap.logits.index_select(0, torch.tensor(wanted, device=cap.logits.device))
 
-    def _capture(self, entries: Sequence[StepEntry], bucket: int) -> _Captured:
+    def _capture(self, entries: Sequence[StepEntry], bucket: int, run: bool = True) -> _Captured:
+        """Capture the step of these entries.  ``run``: also run it for good (one replay); a caller that still has to
+        complete the description on the device replays it itself, and a step must run for good exactly once (a
+        mixer's fixed-size state moves with every run)."""
         r = self.runner
         buffer = torch.zeros((self._buffer_size(bucket),), dtype=torch.int32, device=r.rt.device)
         ctx = self._context(entries, bucket, buffer)
@@ -171,7 +174,8 @@ class DecodeGraphs:
         launches = kernels.launch_count() - n0
         if self.pool is None:
             self.pool = graph.pool()
-        graph.replay()  # the same step again: it rewrites the same keys and gives the captured output its values
+        if run:
+            graph.replay()  # the step for good: it rewrites the same keys and gives the captured output its values
         cap = _Captured(graph, buffer, logits, launches)
         self.captured[bucket] = cap
         return cap
@@ -230,7 +234,7 @@ class PortionGraphs:
         n_wanted = sum(len(e.want) for e in entries)
         cap = self.captured.get(bucket)
         if cap is None:
-            cap = self._capture(entries, bucket)
+            cap = self._capture(entries, bucket, run=carry is None)
             if carry is None:
                 return cap.logits[:n_wanted]
         k = cap.turn
@@ -261,8 +265,8 @@ class PortionGraphs:
         kernels.count_launches(cap.launches)
         return cap.logits[:n_wanted]
 
-    def _capture(self, entries: Sequence[StepEntry], bucket: int) -> _Captured:
-        r = self.runner
+    def _capture(self, entries: Sequence[StepEntry], bucket: int, run: bool = True) -> _Captured:
+        r = self.runner                     # ``run`` as in DecodeGraphs._capture
         if bucket not in self.tile_sizes:
             # once plainly: the attention layers ask the context for their tiles, which tells their sizes (they may
             # depend on how many rows the step has: the plain step says that it stands for the padded one)
@@ -296,7 +300,8 @@ class PortionGraphs:
         launches = kernels.launch_count() - n0
         if self.decode.pool is None:
             self.decode.pool = graph.pool()
-        graph.replay()
+        if run:
+            graph.replay()
         cap = _Captured(graph, buffer, logits, launches)
         self.captured[bucket] = cap
         return cap

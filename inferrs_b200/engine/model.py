@@ -104,14 +104,31 @@ def cache_needs(spec: ModelSpec):
     return kv, states
 
 
+def _layer_tensor_names(layer) -> List[str]:
+    names = []
+    for sub in layer.sublayers:
+        for kind, d in (("norm", sub.norm), (sub.category, sub.part), ("norm", sub.post_norm)):
+            if d is not None:
+                names += [t.name for t in part_class(kind, d).declare(d)]
+    return names
+
+
 class Model:
-    def __init__(self, spec: ModelSpec, weights: Dict[str, torch.Tensor], rt: Runtime):
+    def __init__(self, spec: ModelSpec, weights: Dict[str, torch.Tensor], rt: Runtime, consume: bool = False):
+        """``consume``: a layer's tensors are taken out of ``weights`` as soon as its parts are built (unless a later
+        layer names them too), so that tensors which a part has fused into a new one are given back layer by layer
+        instead of standing twice in memory until the whole model is built."""
         check_schedule(spec)
         self.spec = spec
         self.rt = rt
         self.embedding = weights[spec.embedding]
         self.blocks = []
-        for layer in spec.layers:
+        last_use = {}
+        if consume:
+            for i, layer in enumerate(spec.layers):
+                for name in _layer_tensor_names(layer):
+                    last_use[name] = i
+        for i, layer in enumerate(spec.layers):
             built = []
             for sub in layer.sublayers:
                 _check_category(sub.category)
@@ -123,6 +140,10 @@ class Model:
                 built.append(BuiltSubLayer(sub.category, part_class(sub.category, sub.part)(sub.part, weights, rt),
                                            norm, post))
             self.blocks.append(part_class("arrangement", _Arrangement(layer.arrangement))(layer, built))
+            if consume:
+                for name in _layer_tensor_names(layer):
+                    if last_use[name] == i and name not in (spec.embedding, spec.lm_head):
+                        weights.pop(name, None)
         self.final_norm = part_class("norm", spec.final_norm)(spec.final_norm, weights, rt)
         head = weights.get(spec.lm_head)
         if head is None:

@@ -26,12 +26,23 @@ from .model import Model, cache_needs
 
 class ModelRunner:
     def __init__(self, spec: ModelSpec, weights: Dict[str, torch.Tensor], rt: Runtime, page_size: int,
-                 n_pages: int, max_requests: int, use_graphs: Optional[bool] = None,
-                 max_context: Optional[int] = None, graph_rows: int = 2048):
+                 n_pages: Optional[int], max_requests: int, use_graphs: Optional[bool] = None,
+                 max_context: Optional[int] = None, graph_rows: int = 2048, cache_fraction: float = 0.9,
+                 consume_weights: bool = False):
+        """``n_pages`` None: the cache gets ``cache_fraction`` of the device memory that is free once the model
+        stands (but no more pages than ``max_requests`` requests of ``max_context`` tokens can use).
+        ``consume_weights``: the ``weights`` dictionary is emptied once the model is built; the parts keep what
+        they use, and the tensors that were fused into others (q/k/v, gate/up) are given back before the cache is
+        sized."""
         self.spec = spec
         self.rt = rt
-        self.model = Model(spec, weights, rt)
+        self.model = Model(spec, weights, rt, consume=consume_weights)
         kv_needs, state_needs = cache_needs(spec)
+        if consume_weights:
+            weights.clear()
+        if n_pages is None:
+            n_pages = self._pages_for_fraction(kv_needs, page_size, cache_fraction, max_requests,
+                                               min(max_context or spec.max_positions, spec.max_positions))
         self.storage = CacheStorage(kv_needs, state_needs, page_size, n_pages, max_requests, rt.dtype, rt.device)
         self.manager = CacheManager(self.storage.layouts, page_size, self.storage.n_pages, max_requests)
         self.page_size = page_size
@@ -50,6 +61,26 @@ class ModelRunner:
             self.graphs = DecodeGraphs(self, limit)
             if graph_rows > 0:
                 self.portion_graphs = PortionGraphs(self, self.graphs, graph_rows)
+
+    def _pages_for_fraction(self, kv_needs, page_size: int, fraction: float, max_requests: int, max_context: int) -> int:
+        """Pages that ``fraction`` of the memory that is free right now pays for (the reference sizes its cache as a
+        fraction of memory too, inferrs-models/src/kv_cache.rs:44-65, inferrs/src/engine.rs:944-1000)."""
+        if not 0.0 < fraction <= 1.0:
+            raise ValueError(f"the cache's fraction of free memory must be in (0, 1], got {fraction}")
+        if self.rt.device.type != "cuda":
+            raise RuntimeError("the number of pages must be given when the cache is not on a CUDA device")
+        import gc
+        gc.collect()
+        torch.cuda.empty_cache()        # what the loader and the fusing of tensors have given back
+        elem = torch.empty((), dtype=self.rt.dtype).element_size()
+        per_page = sum(2 * n.n_kv_heads * n.head_dim * page_size * elem for n in kv_needs.values())
+        free, _total = torch.cuda.mem_get_info(self.rt.device)
+        pages = int(free * fraction) // max(per_page, 1)
+        # no request can use more than max_context tokens: more pages than that per slot are never touched
+        pages = min(pages, max_requests * ((max_context + page_size - 1) // page_size))
+        if pages < 1:
+            raise RuntimeError("no memory is left for the cache")
+        return pages
 
     # ---- requests -----------------------------------------------------------
     def admit(self, rid: Hashable) -> int:

@@ -164,7 +164,8 @@ class Scheduler:
         if len(self._by_handle) + 8 > self._cap:
             self._grow(2 * self._cap)
 
-    def abort(self, rid: Hashable) -> Optional[Request]:
+    def abort(self, rid: Hashable, reason: str = "cancelled") -> Optional[Request]:
+        """Take the request out (its pages and slot are free again); it ends with ``reason``."""
         for r in list(self.running) + list(self.waiting):
             if r.rid == rid:
                 was = self._lib.ibh_sched_abort(self._h, r.handle)
@@ -176,7 +177,7 @@ class Scheduler:
                 else:
                     raise SchedulerError(f"request {rid!r}: the native scheduler does not know it")
                 del self._by_handle[r.handle]
-                r.finish_reason = "cancelled"
+                r.finish_reason = reason
                 return r
         return None
 

@@ -51,6 +51,10 @@ _SIGNATURES = {
                                         c_void_p],
     "ib_attention_pair_tcgen05_error": [c_int],
     "ib_row_fault": [c_int],
+    "ib_row_fault_async": [c_void_p, c_void_p],
+    "ib_attention_tcgen05_error_async": [c_void_p, c_void_p],
+    "ib_attention_pair_tcgen05_error_async": [c_void_p, c_void_p],
+    "ib_attention_decode_error_async": [c_void_p, c_void_p],
     "ib_paged_attention_decode": [c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_void_p, c_int, c_int,
                                   c_int, c_int, c_float, c_int, c_void_p, c_int, c_int, c_void_p, c_void_p, c_void_p,
                                   c_void_p, c_void_p, c_void_p],
@@ -736,6 +740,8 @@ def _gemm_lib():
         lib.ib_gemm_swiglu_tcgen05.restype = c_int
         lib.ib_gemm_tcgen05_error.argtypes = [c_int]
         lib.ib_gemm_tcgen05_error.restype = c_int
+        lib.ib_gemm_tcgen05_error_async.argtypes = [c_void_p, c_void_p]
+        lib.ib_gemm_tcgen05_error_async.restype = c_int
         _GEMM_LIB = lib
     return _GEMM_LIB
 
@@ -807,3 +813,48 @@ SWIGLU_MAX_TOKENS = 32  # rows that the fused gate/up kernel takes
 def gemm_tcgen05_error(reset: bool = True) -> int:
     """0, or the code of the first bounded wait that ran out in a tcgen05 GEMM (synchronises with the device)."""
     return _gemm_lib().ib_gemm_tcgen05_error(int(reset))
+
+
+# ---- the kernels' error words, all of them ------------------------------------------------------------------
+# A bounded wait that ran out, or a row whose position lay outside the rotation tables, leaves a code in a word
+# on the device.  The functions above read one word each and wait for the device; these read all of them the way
+# a serving loop wants it: asked for in stream order, read later from pinned memory.
+ERROR_WORDS = ("a row's position outside the rotation tables", "prefill attention (tcgen05)",
+               "prefill attention (two query tiles)", "decode attention", "matrix product (tcgen05)")
+
+
+def error_words_async(host: torch.Tensor, act_dtype: torch.dtype):
+    """Ask for every error word of the kernel libraries, in the order of ``ERROR_WORDS``, to be copied into ``host``
+    (pinned int32, at least ``len(ERROR_WORDS)`` long) behind the work that the current stream holds.  The caller
+    records an event after this call and reads ``host`` once the event has come."""
+    if host.dtype != torch.int32 or host.numel() < len(ERROR_WORDS) or not host.is_pinned():
+        raise KernelError("error_words_async wants a pinned int32 tensor with room for every word")
+    core, stream, at = _core(act_dtype), _stream(), host.data_ptr()
+    calls = [core.ib_row_fault_async, core.ib_attention_tcgen05_error_async,
+             core.ib_attention_pair_tcgen05_error_async, core.ib_attention_decode_error_async]
+    if act_dtype == torch.bfloat16:
+        calls.append(_gemm_lib().ib_gemm_tcgen05_error_async)
+    else:
+        host[len(calls)] = 0
+    for i, fn in enumerate(calls):
+        code = fn(at + 4 * i, stream)
+        if code != 0:
+            raise KernelError(f"error_words_async: CUDA error {code}")
+
+
+def reset_error_words(act_dtype: torch.dtype) -> dict:
+    """Read every error word now (waits for the device), clear them, and put the decode attention's counters back
+    to zero (a wait that ran out may have left a slice uncounted).  Returns {name: code} of the words that were set."""
+    found = {}
+    row = row_fault(act_dtype, reset=True)
+    if row is not None:
+        found[ERROR_WORDS[0]] = row + 1
+    if act_dtype == torch.bfloat16:
+        for name, fn in zip(ERROR_WORDS[1:], (attention_tcgen05_error, attention_pair_tcgen05_error,
+                                              attention_decode_error, gemm_tcgen05_error)):
+            v = fn(True)
+            if v:
+                found[name] = v
+    for counters in _DECODE_COUNTERS.values():
+        counters.zero_()
+    return found

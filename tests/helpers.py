@@ -57,7 +57,7 @@ def rel_err(a: torch.Tensor, b: torch.Tensor) -> float:
     """The worst row's error: for every row (last dimension) the largest absolute difference over the largest
     absolute value of the reference ``b`` in that row; the largest of these.  One bad row among hundreds, or an
     error in a row of small values, shows in full."""
-    a, b = a.double(), b.double()
+    a, b = a.detach().double().cpu(), b.detach().double().cpu()
     if a.shape != b.shape:
         raise ValueError(f"shapes differ: {tuple(a.shape)} and {tuple(b.shape)}")
     if a.dim() == 0:

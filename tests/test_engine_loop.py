@@ -87,6 +87,8 @@ def make_engine(overlap, n_pages, page_size, slots, max_batch, budget, chunk, eo
     eng.overlap = overlap
     eng._in_flight = None
     eng._pinned = []
+    eng.health = None
+    eng.kernel_errors, eng._unchecked, eng._checked_up_to, eng._last_look = [], [], 0, 0
     return eng, manager
 
 
@@ -156,3 +158,66 @@ def test_carried_tokens_are_named_in_the_description():
     assert stage.tolist()[:8] == [-3, 101, 102, 103, 104, -1, 106, 107]
     with pytest.raises(ValueError, match="single token"):
         name_carried_tokens(stage, entries, [-1, 1, -1, -1])
+
+
+class FakeHealth:
+    """Stands in for the reader of the kernels' error words: the look asked for as the ``fail_at``-th one finds a word
+    set, the others find nothing; an answer arrives one poll after it was asked for."""
+
+    def __init__(self, fail_at, every=4):
+        self.every, self.fail_at = every, fail_at
+        self.asked, self.age, self.n_reset, self.pending = 0, 0, 0, False
+
+    def queue(self):
+        assert not self.pending
+        self.pending, self.age = True, 0
+        self.asked += 1
+
+    def poll(self, wait=False):
+        if not self.pending:
+            return None
+        self.age += 1
+        if not wait and self.age < 2:
+            return None
+        self.pending = False
+        return {"decode attention": 2} if self.asked == self.fail_at else {}
+
+    def reset(self):
+        self.n_reset += 1
+        return {}
+
+
+@pytest.mark.parametrize("overlap", [False, True])
+def test_a_word_that_a_kernel_set_ends_the_requests_that_it_may_have_touched(overlap):
+    """The engine asks for the kernels' error words every few steps and when a request ends, and reads the answer
+    when it is there.  When a word is set, the running requests and those that ended since the last look that found
+    nothing end with "error", the words are cleared, every page comes back, and the waiting requests run as if
+    nothing had happened."""
+    eos = ()
+    eng, manager = make_engine(overlap, n_pages=64, page_size=4, slots=3, max_batch=3, budget=16, chunk=None, eos=eos)
+    eng.health = FakeHealth(fail_at=4)
+    params = [SamplingParams(temperature=0.0, max_tokens=n) for n in (3, 40, 40, 9, 12, 5)]
+    prompts = [[(7 * i + j) % VOCAB for j in range(5 + i)] for i in range(len(params))]
+    for i, (p, sp) in enumerate(zip(prompts, params)):
+        eng.add_request(p, sp, rid=i)
+    done, turns = {}, 0
+    while eng.has_work() and turns < 500:
+        for r in eng.step():
+            done[r.rid] = r
+        manager.check_invariants()
+        turns += 1
+    for r in eng.flush():
+        done[r.rid] = r
+    assert sorted(done) == list(range(len(params)))
+    assert eng.health.n_reset == 1 and len(eng.kernel_errors) == 1
+    assert eng.kernel_errors[0]["words"] == {"decode attention": 2}
+    failed = sorted(i for i, r in done.items() if r.finish_reason == "error")
+    assert 1 in failed and 2 in failed, "the requests that were running when the word was found"
+    assert len(failed) < len(params), "requests that came after the words were cleared must run"
+    for i, r in done.items():
+        if r.finish_reason != "error":
+            assert (r.output, r.finish_reason) == plain_generate(prompts[i], params[i], eos), i
+        else:
+            want, _ = plain_generate(prompts[i], params[i], eos)
+            assert r.output == want[:len(r.output)]
+    assert manager.pools[0].n_free == 64 and manager.n_live == 0

@@ -116,3 +116,84 @@ def test_mixed_with_pages_used_again(setup):
     runner.release("a")
     runner.release("b")
     runner.manager.check_invariants()
+
+
+# ---- the sizes that the measured steps have: a prompt of 2,048 tokens in one step, portions of 512 beside a
+# decoding request, decoding at more than 2,048 tokens -------------------------------------------------------
+LONG, LONG_DECODE = 2048, 40
+MID, MID_DECODE = 1100, 8
+
+
+@pytest.fixture(scope="module", params=[torch.float32, torch.bfloat16], ids=["float32", "bfloat16"])
+def long_setup(request):
+    dtype = request.param
+    rt = Runtime.cuda(dtype)
+    spec, weights, _ = random_model(CONFIG, 6, rt)
+    host = {k: v.float().cpu() for k, v in weights.items()}
+    long_toks = random_tokens(LONG + LONG_DECODE, CONFIG["vocab_size"], seed=40)
+    mid_toks = random_tokens(MID + MID_DECODE, CONFIG["vocab_size"], seed=41)
+    store = None if dtype == torch.float32 else dtype
+    want_long = plain_qwen3.forward(CONFIG, host, long_toks, store=store, last=LAST + LONG_DECODE)
+    want_mid = plain_qwen3.forward(CONFIG, host, mid_toks, store=store, last=LAST + MID_DECODE)
+    del host
+    pages = (LONG + LONG_DECODE + 15) // 16 + (MID + MID_DECODE + 15) // 16 + 2
+    runner = ModelRunner(spec, weights, rt, page_size=16, n_pages=pages, max_requests=4)
+    yield dtype, runner, long_toks, mid_toks, want_long, want_mid
+    del runner, weights
+    torch.cuda.empty_cache()
+
+
+def test_the_steps_that_are_measured(long_setup):
+    """A prompt of 2,048 tokens as one step (in bfloat16: a replayed graph of 2,048 rows, the library's products,
+    the rotation kernel for many rows, the attention kernel with two query tiles); then a second request's prompt
+    of 1,100 tokens in portions of 512 beside the first request's decoded tokens; then both decode, the first at
+    more than 2,048 tokens (its keys in several slices)."""
+    from inferrs_b200 import kernels
+    dtype, runner, long_toks, mid_toks, want_long, want_mid = long_setup
+    pair_calls = {"n": 0}
+    original = kernels.paged_attention_pair_tcgen05
+
+    def counted(*a, **k):
+        pair_calls["n"] += 1
+        return original(*a, **k)
+
+    kernels.paged_attention_pair_tcgen05 = counted
+    try:
+        runner.admit("long")
+        got_long = [runner.step([StepEntry("long", long_toks[:LONG], list(range(LONG - LAST, LONG)))])]
+    finally:
+        kernels.paged_attention_pair_tcgen05 = original
+    if dtype == torch.bfloat16:
+        assert pair_calls["n"] > 0, "a step of 2,048 rows was meant to run the kernel with two query tiles"
+        assert 2048 in runner.portion_graphs.captured
+    check(got_long[0], want_long[:LAST], dtype, "the prompt of 2,048 tokens in one step")
+    runner.admit("mid")
+    got_mid, at_long, at_mid = [], LONG, 0
+    for n in (512, 512, MID - 1024):
+        w = [i for i in range(n) if at_mid + i >= MID - LAST]
+        out = runner.step([StepEntry("long", long_toks[at_long:at_long + 1], [0]),
+                           StepEntry("mid", mid_toks[at_mid:at_mid + n], w)])
+        got_long.append(out[:1])
+        if w:
+            got_mid.append(out[1:])
+        at_long += 1
+        at_mid += n
+    while at_long < LONG + LONG_DECODE:
+        entries = [StepEntry("long", long_toks[at_long:at_long + 1], [0])]
+        if at_mid < MID + MID_DECODE:
+            entries.append(StepEntry("mid", mid_toks[at_mid:at_mid + 1], [0]))
+        out = runner.step(entries)
+        got_long.append(out[:1])
+        if len(entries) == 2:
+            got_mid.append(out[1:])
+            at_mid += 1
+        at_long += 1
+    assert at_mid == MID + MID_DECODE
+    check(torch.cat(got_long), want_long, dtype, "the long request: last 32 places of its prompt, then decoded")
+    check(torch.cat(got_mid), want_mid, dtype, "the second request: portions of 512 beside decoded tokens")
+    if dtype == torch.bfloat16:
+        assert kernels.attention_pair_tcgen05_error() == 0 and kernels.attention_tcgen05_error() == 0
+        assert kernels.attention_decode_error() == 0 and kernels.gemm_tcgen05_error() == 0
+    runner.release("long")
+    runner.release("mid")
+    runner.manager.check_invariants()
