@@ -597,7 +597,7 @@ def pair_tile_tokens(n_heads: int, n_kv_heads: int) -> int:
 def tcgen05_pair_attention_supported(dtype: torch.dtype, n_heads: int, n_kv_heads: int, head_dim: int,
                                      page_size: int) -> bool:
     g = n_heads // max(n_kv_heads, 1)
-    return (dtype == torch.bfloat16 and head_dim == 128 and page_size >= 8 and 64 % page_size == 0
+    return (dtype == torch.bfloat16 and head_dim == 128 and page_size >= 8 and 128 % page_size == 0
             and n_heads % n_kv_heads == 0 and 1 <= g <= 128)
 
 
@@ -607,7 +607,8 @@ def paged_attention_pair_tcgen05(q: torch.Tensor, k_pages: torch.Tensor, v_pages
                                  out: torch.Tensor):
     """Attention of prompt portions on tcgen05 tensor cores with two query tiles per CTA that take turns
     (bfloat16, head_dim 128): tile i holds up to ``pair_tile_tokens`` tokens of request tile_req[i] from row
-    tile_row0[i]; the output is accumulated in tensor memory."""
+    tile_row0[i]; the probabilities go to the second product through tensor memory, where the output is
+    accumulated too."""
     bf = (torch.bfloat16,)
     _need(q, "q", bf, 3)
     _need(k_pages, "k_pages", bf, 4)
@@ -622,7 +623,7 @@ def paged_attention_pair_tcgen05(q: torch.Tensor, k_pages: torch.Tensor, v_pages
         raise KernelError(f"paged_attention_pair_tcgen05: q {tuple(q.shape)}, pages {tuple(k_pages.shape)}, "
                           f"out {tuple(out.shape)}")
     if not tcgen05_pair_attention_supported(q.dtype, nh, nkv, d, page_size):
-        raise KernelError(f"paged_attention_pair_tcgen05 takes head_dim 128, a page size of 8..64 that divides 64 and "
+        raise KernelError(f"paged_attention_pair_tcgen05 takes head_dim 128, a page size of 8..128 that divides 128 and "
                           f"a group size of at most 128; got head_dim {d}, page size {page_size}, {nh}/{nkv} heads")
     _check(_core(torch.bfloat16).ib_paged_attention_pair_tcgen05(
         _p(q), _p(k_pages), _p(v_pages), _p(block_table), block_table.shape[1], page_size, n_pages, _p(tile_req),
