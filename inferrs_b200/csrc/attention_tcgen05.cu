@@ -83,8 +83,12 @@ __global__ void __launch_bounds__(THREADS, 1) attention_kernel(const __grid_cons
 
     ib_grid_dependency_sync();
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-    // the last tiles of a prompt see the most keys: they are started first, so that the grid's tail is short
-    const int tile = gridDim.x - 1 - blockIdx.x, kvh = blockIdx.y;
+    // The last tiles of a prompt see the most keys: they are started first, so that the grid's tail is short.  Blocks
+    // are handed out in the order of their index, so the index counts tiles from the last one down and the
+    // key/value heads within each tile (with the heads as a second grid dimension all tiles of head 0, short ones
+    // included, would come before the long tiles of the other heads).
+    const int tile = (int)(gridDim.x / P.n_kv_heads) - 1 - (int)(blockIdx.x / P.n_kv_heads);
+    const int kvh = (int)(blockIdx.x % P.n_kv_heads);
     const int req = P.tile_req[tile], row0 = P.tile_row0[tile];
     if (req < 0) return;                            // a place in a tile list of fixed length that holds no tile
     const int G = P.n_heads / P.n_kv_heads;
@@ -388,7 +392,7 @@ IB_EXPORT int ib_paged_attention_tcgen05(const void* q, const void* k_pages, con
     const size_t smem = 7 * fa::TILE_BYTES + 18 * 8 + 4 * 128 * 4 + fa::SMEM_SLACK;
     static IbDeviceSet configured;   // the attribute is kept per device
     if (const int e = ib_allow_dynamic_smem(configured, fa::attention_kernel, smem)) return e;
-    ib_launch(fa::attention_kernel, dim3(n_tiles, n_kv_heads), fa::THREADS, smem, stream, mq, mk, mv, P);
+    ib_launch(fa::attention_kernel, dim3(n_tiles * n_kv_heads), fa::THREADS, smem, stream, mq, mk, mv, P);
     return ib_launch_status();
 }
 
