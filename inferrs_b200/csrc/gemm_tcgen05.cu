@@ -15,6 +15,15 @@
 // shared memory, one cluster barrier follows, and every owner adds the parts in the order of the CTAs'
 // ranks and stores its rows.  Wider tiles are summed by the cluster's first CTA, which reads the others.
 //
+// Two things can be folded into the read-back of up to 32 tokens, so that the norm between two products needs no
+// kernel of its own (x / sqrt(mean(x^2) + eps) * w is the same as (x * w) scaled by the row's 1 / sqrt(...)):
+//   * the residual stream: y is added to a float32 stream in place, the stream times the weight vector of the norm
+//     that follows is stored as bfloat16 instead of y, and every CTA writes the sums of squares of its share of
+//     the stream's rows to a list of parts ("sink");
+//   * the row scale: x is such a stream-times-weight matrix with its list of parts; the parts are added up in a
+//     fixed order while the weights stream in, and the accumulator is scaled by 1 / sqrt(sum / width + eps) per
+//     token before it is used ("scaled rows").
+//
 // Every wait on an mbarrier is bounded (about two seconds); a wait that runs out records a code in the
 // library's error word, the CTA lets outstanding copies land, frees its tensor memory and returns.
 #include <cuda.h>
@@ -78,8 +87,39 @@ struct Params {
     long ldy;
     int n_tok, n_out, num_kb, y_is_f32;
     int inner;   // gated form: rows of the gate matrix; the up matrix follows it in w
+    // scaled rows (null: x is used as it is): parts of the sums of squares of x's rows [n_in_parts][SSQ_LD]
+    const float* in_ssq;
+    int n_in_parts;
+    float in_eps, in_inv_width;
+    // sink (null: y is stored as it is): the float32 stream [n_tok, n_out] that y is added to, the weight vector
+    // [n_out] that the stream is multiplied by before it is stored in y's place, and where this CTA's part of the
+    // rows' sums of squares goes: [tiles * splits][SSQ_LD]
+    float* residual;
+    long ld_res;
+    const void* sink_w;
+    int sink_w_is_f32;
+    float* out_ssq;
 };
 
+constexpr int SSQ_LD = 32;    // tokens per part of a list of sums of squares (the folded forms take up to 32 tokens)
+
+// What the read-back does with one finished value: scale it by its token's row scale, then either hand it on as it
+// is or add it to the stream (rounded to bfloat16 first, as it is when the product stores it and a norm kernel adds
+// it) and hand on the stream times the norm's weight.  `ssq` gathers the squares of the stream's new values.  The
+// stream's old value and the weight were fetched while the weights streamed in.
+__device__ __forceinline__ float finish_value(const Params& p, float v, int tok, int feature, float inv, float old,
+                                              float w, float& ssq) {
+    v *= inv;
+    if (p.residual == nullptr) return v;
+    const float s = old + __bfloat162float(__float2bfloat16_rn(v));
+    p.residual[(long)tok * p.ld_res + feature] = s;
+    ssq += s * s;
+    return s * w;
+}
+__device__ __forceinline__ float sink_weight(const Params& p, int feature) {
+    return p.sink_w_is_f32 ? reinterpret_cast<const float*>(p.sink_w)[feature]
+                           : __bfloat162float(reinterpret_cast<const __nv_bfloat16*>(p.sink_w)[feature]);
+}
 
 template <int BN, int STAGES, int MODE>
 __global__ void __launch_bounds__(THREADS, (BN <= 64 ? 2 : 1)) gemm_kernel(const __grid_constant__ CUtensorMap map_w,
@@ -94,7 +134,8 @@ __global__ void __launch_bounds__(THREADS, (BN <= 64 ? 2 : 1)) gemm_kernel(const
     unsigned long long* bars = reinterpret_cast<unsigned long long*>(b_tiles + STAGES * B_BYTES);
     const unsigned full0 = smem_u32(bars), empty0 = smem_u32(bars + STAGES), accum = smem_u32(bars + 2 * STAGES);
     unsigned* tmem_slot = reinterpret_cast<unsigned*>(bars + 2 * STAGES + 1);
-    float* recv = reinterpret_cast<float*>(bars + 2 * STAGES + 2);   // [rank of the sender][BN][rows owned], SCATTER only
+    float* fold = reinterpret_cast<float*>(bars + 2 * STAGES + 2);   // [8][32] partial sums, then [32] row scales (folded forms)
+    float* recv = fold + 9 * SSQ_LD;                                  // [rank of the sender][BN][rows owned], SCATTER only
 
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const int tile_f = blockIdx.x, tile_t = blockIdx.y;
@@ -190,6 +231,25 @@ __global__ void __launch_bounds__(THREADS, (BN <= 64 ? 2 : 1)) gemm_kernel(const
         // are rounded to bfloat16 first, as they are when the product and the gate run as two kernels.
         if (warp >= 2) {
             asm volatile("griddepcontrol.wait;" ::: "memory");   // y may still be read by the predecessor
+            // the row scales of scaled rows: their parts are added up in a fixed order while the weights stream in
+            if constexpr (BN <= 32) {
+                const int e = (int)threadIdx.x - 64;   // 0..127 over the four read-back warps
+                if (p.in_ssq != nullptr) {
+                    const int tok = e & 31, grp = e >> 5;
+                    float acc = 0.0f;
+#pragma unroll 8
+                    for (int part = grp; part < p.n_in_parts; part += 4) acc += p.in_ssq[(long)part * SSQ_LD + tok];
+                    fold[grp * SSQ_LD + tok] = acc;
+                    asm volatile("bar.sync 1, 128;" ::: "memory");
+                    if (e < 32)
+                        fold[8 * SSQ_LD + e] = 1.0f / sqrtf((((fold[e] + fold[SSQ_LD + e]) + fold[2 * SSQ_LD + e]) +
+                                                              fold[3 * SSQ_LD + e]) * p.in_inv_width + p.in_eps);
+                } else if (e < 32) {
+                    fold[8 * SSQ_LD + e] = 1.0f;
+                }
+                asm volatile("bar.sync 1, 128;" ::: "memory");
+            }
+            const float* inv_s = fold + 8 * SSQ_LD;
             ok = nkb > 0 ? mbar_wait(accum, 0, 3) : true;
             ok = __all_sync(0xffffffffu, ok);   // one answer per warp: the tensor-memory loads below are warp-wide
             fence_after();
@@ -222,8 +282,9 @@ __global__ void __launch_bounds__(THREADS, (BN <= 64 ? 2 : 1)) gemm_kernel(const
                     for (int j = 0; j < 16; ++j) {
                         const int tok = tile_t * BN + c0 + j;
                         if (tok < p.n_tok && store) {
-                            const float g = __bfloat162float(__float2bfloat16_rn(v[j]));
-                            const float u = __bfloat162float(__float2bfloat16_rn(up_vals[(c0 + j) * 64 + row]));
+                            const float inv = BN <= 32 ? inv_s[c0 + j] : 1.0f;
+                            const float g = __bfloat162float(__float2bfloat16_rn(v[j] * inv));
+                            const float u = __bfloat162float(__float2bfloat16_rn(up_vals[(c0 + j) * 64 + row] * inv));
                             reinterpret_cast<__nv_bfloat16*>(p.y)[(long)tok * p.ldy + feature] =
                                 __float2bfloat16_rn(g / (1.0f + expf(-g)) * u);
                         }
@@ -232,13 +293,45 @@ __global__ void __launch_bounds__(THREADS, (BN <= 64 ? 2 : 1)) gemm_kernel(const
             }
         }
     } else {
+    constexpr int KEEP = BN <= 32 ? BN : 1;        // a sink's old values that a thread keeps (the folded forms only)
+    constexpr int UNROLL = BN <= 32 ? 2 : 1;      // their loops over the tokens are unrolled, so that these stay registers
+    float old_s[KEEP], w_sink = 0.0f;
+#pragma unroll
+    for (int j = 0; j < KEEP; ++j) old_s[j] = 0.0f;
     if (warp >= 2) {
         asm volatile("griddepcontrol.wait;" ::: "memory");   // y may still be read by the predecessor
+        // the row scales of scaled rows: their parts are added up in a fixed order while the weights stream in
+        if constexpr (BN <= 32) {
+            const int e = (int)threadIdx.x - 64;   // 0..127 over the four read-back warps
+            if (p.in_ssq != nullptr) {
+                const int tok = e & 31, grp = e >> 5;
+                float acc = 0.0f;
+#pragma unroll 8
+                for (int part = grp; part < p.n_in_parts; part += 4) acc += p.in_ssq[(long)part * SSQ_LD + tok];
+                fold[grp * SSQ_LD + tok] = acc;
+                asm volatile("bar.sync 1, 128;" ::: "memory");
+                if (e < 32)
+                    fold[8 * SSQ_LD + e] = 1.0f / sqrtf((((fold[e] + fold[SSQ_LD + e]) + fold[2 * SSQ_LD + e]) +
+                                                          fold[3 * SSQ_LD + e]) * p.in_inv_width + p.in_eps);
+            } else if (e < 32) {
+                fold[8 * SSQ_LD + e] = 1.0f;
+            }
+            asm volatile("bar.sync 1, 128;" ::: "memory");
+        }
+        // a sink's stream and weight, for the values that this thread will finish, fetched while the weights stream in
+        if constexpr (BN <= 32) {
+            if (p.residual != nullptr && feature < p.n_out && (splits == 1 || owner == my_rank)) {
+                w_sink = sink_weight(p, feature);
+#pragma unroll
+                for (int j = 0; j < KEEP; ++j)
+                    if (tile_t * BN + j < p.n_tok) old_s[j] = p.residual[(long)(tile_t * BN + j) * p.ld_res + feature];
+            }
+        }
         ok = nkb > 0 ? mbar_wait(accum, 0, 3) : true;
         ok = __all_sync(0xffffffffu, ok);       // one answer per warp: the tensor-memory loads below are warp-wide
         fence_after();
         if (ok) {
-#pragma unroll 1
+#pragma unroll UNROLL
             for (int c0 = 0; c0 < BN; c0 += 16) {
                 float v[16];
                 if (nkb > 0) tmem_ld16(tmem + ((unsigned)(q * 32) << 16) + c0, v);
@@ -262,42 +355,79 @@ __global__ void __launch_bounds__(THREADS, (BN <= 64 ? 2 : 1)) gemm_kernel(const
                 } else if (splits > 1) {
 #pragma unroll
                     for (int j = 0; j < 16; ++j) stage[(c0 + j) * BM + row] = v[j];
-                } else if (feature < p.n_out) {
+                } else {
+                    float ssq[16];
 #pragma unroll
                     for (int j = 0; j < 16; ++j) {
                         const int tok = tile_t * BN + c0 + j;
-                        if (tok < p.n_tok) {
-                            if (p.y_is_f32) reinterpret_cast<float*>(p.y)[(long)tok * p.ldy + feature] = v[j];
-                            else reinterpret_cast<__nv_bfloat16*>(p.y)[(long)tok * p.ldy + feature] = __float2bfloat16_rn(v[j]);
+                        ssq[j] = 0.0f;
+                        if (tok < p.n_tok && feature < p.n_out) {
+                            const float o = BN <= 32 ? finish_value(p, v[j], tok, feature, fold[8 * SSQ_LD + c0 + j],
+                                                                    old_s[(c0 + j) % KEEP], w_sink, ssq[j]) : v[j];
+                            if (p.y_is_f32) reinterpret_cast<float*>(p.y)[(long)tok * p.ldy + feature] = o;
+                            else reinterpret_cast<__nv_bfloat16*>(p.y)[(long)tok * p.ldy + feature] = __float2bfloat16_rn(o);
+                        }
+                    }
+                    if (BN <= 32 && p.residual != nullptr) {   // this warp's part of the rows' sums of squares
+#pragma unroll
+                        for (int j = 0; j < 16; ++j) {
+                            const float t = ib_warp_sum(ssq[j]);
+                            if (lane == 0) fold[q * SSQ_LD + c0 + j] = t;
                         }
                     }
                 }
             }
         }
     }
+    // the sink's list of parts: one part per CTA, the four warps' shares added in a fixed order
+    auto store_ssq_part = [&]() {
+        asm volatile("bar.sync 1, 128;" ::: "memory");
+        const int e = (int)threadIdx.x - 64;
+        if (e < SSQ_LD) {
+            const float t = e < BN ? ((fold[e] + fold[SSQ_LD + e]) + fold[2 * SSQ_LD + e]) + fold[3 * SSQ_LD + e] : 0.0f;
+            p.out_ssq[((long)tile_f * splits + my_rank) * SSQ_LD + e] = t;
+        }
+    };
+    if constexpr (BN <= 32) {
+        if (splits == 1 && p.residual != nullptr && warp >= 2) store_ssq_part();
+    }
     if (splits > 1 && SCATTER) {
         cluster_sync_all();                    // every part of the rows this CTA owns is in its shared memory
-        if (warp >= 2 && owner == my_rank && feature < p.n_out && g_error == 0) {
-#pragma unroll 1
-            for (int c0 = 0; c0 < BN && tile_t * BN + c0 < p.n_tok; c0 += 16) {
-                float sum[16];
+        if (warp >= 2) {
+            const bool mine = owner == my_rank && feature < p.n_out && g_error == 0;
+#pragma unroll UNROLL
+            for (int c0 = 0; c0 < BN; c0 += 16) {
+                if (tile_t * BN + c0 >= p.n_tok) break;
+                float sum[16], ssq[16];
 #pragma unroll
-                for (int j = 0; j < 16; ++j) sum[j] = 0.0f;
-                for (int r = 0; r < splits; ++r) {   // in the order of the ranks, whoever does the adding
-                    const float* part = recv + ((size_t)r * BN + c0) * owned + row_local;
+                for (int j = 0; j < 16; ++j) sum[j] = ssq[j] = 0.0f;
+                if (mine) {
+                    for (int r = 0; r < splits; ++r) {   // in the order of the ranks, whoever does the adding
+                        const float* part = recv + ((size_t)r * BN + c0) * owned + row_local;
 #pragma unroll
-                    for (int j = 0; j < 16; ++j)
-                        if (tile_t * BN + c0 + j < p.n_tok) sum[j] += part[j * owned];
+                        for (int j = 0; j < 16; ++j)
+                            if (tile_t * BN + c0 + j < p.n_tok) sum[j] += part[j * owned];
+                    }
+#pragma unroll
+                    for (int j = 0; j < 16; ++j) {
+                        const int tok = tile_t * BN + c0 + j;
+                        if (tok < p.n_tok) {
+                            const float o = finish_value(p, sum[j], tok, feature, fold[8 * SSQ_LD + c0 + j],
+                                                         old_s[(c0 + j) % KEEP], w_sink, ssq[j]);
+                            if (p.y_is_f32) reinterpret_cast<float*>(p.y)[(long)tok * p.ldy + feature] = o;
+                            else reinterpret_cast<__nv_bfloat16*>(p.y)[(long)tok * p.ldy + feature] = __float2bfloat16_rn(o);
+                        }
+                    }
                 }
+                if (p.residual != nullptr) {   // this warp's part of the rows' sums of squares (its own rows only)
 #pragma unroll
-                for (int j = 0; j < 16; ++j) {
-                    const int tok = tile_t * BN + c0 + j;
-                    if (tok < p.n_tok) {
-                        if (p.y_is_f32) reinterpret_cast<float*>(p.y)[(long)tok * p.ldy + feature] = sum[j];
-                        else reinterpret_cast<__nv_bfloat16*>(p.y)[(long)tok * p.ldy + feature] = __float2bfloat16_rn(sum[j]);
+                    for (int j = 0; j < 16; ++j) {
+                        const float t = ib_warp_sum(ssq[j]);
+                        if (lane == 0) fold[q * SSQ_LD + c0 + j] = t;
                     }
                 }
             }
+            if (p.residual != nullptr) store_ssq_part();
         }
         // nobody touches another CTA's shared memory after the barrier: the CTAs may leave in any order
     } else if (splits > 1) {
@@ -358,8 +488,8 @@ static bool make_map(CUtensorMap* map, const void* base, long rows, long k, long
 
 template <int BN, int STAGES, int MODE = 0>
 static int launch(const CUtensorMap& mw, const CUtensorMap& mx, const Params& p, int splits, cudaStream_t stream) {
-    constexpr size_t smem = (size_t)STAGES * (A_BYTES + BN * BK * 2) + (2 * STAGES + 2) * 8 + 1024 +
-                            (BN <= 32 ? (size_t)BN * BM * 4 : 0);   // + the parts received from the cluster
+    constexpr size_t smem = (size_t)STAGES * (A_BYTES + BN * BK * 2) + (2 * STAGES + 2) * 8 + 1024 + 9 * SSQ_LD * 4 +
+                            (BN <= 32 ? (size_t)BN * BM * 4 : 0);   // + the folded forms' sums + the parts received from the cluster
     static IbDeviceSet configured;   // the attribute is kept per device
     if (const int e = ib_allow_dynamic_smem(configured, gemm_kernel<BN, STAGES, MODE>, smem)) return e;
     cudaLaunchConfig_t cfg = {};
@@ -383,27 +513,47 @@ static int launch(const CUtensorMap& mw, const CUtensorMap& mx, const Params& p,
 
 }  // namespace tc
 
-// x [n_tok, k] (row stride ldx), w [n_out, k] (row stride ldw), both bfloat16; y [n_tok, n_out] bfloat16 or float32.
-// split_k: 0 lets the function choose (1, 2 or 4 CTAs per output tile); 8 is taken for up to 32 tokens (4 stands in beyond).
-IB_EXPORT int ib_gemm_tn_tcgen05(const void* x, long ldx, const void* w, long ldw, void* y, long ldy, int y_is_f32,
-                                 int n_tok, int n_out, int k, int split_k, cudaStream_t stream) {
+// How many CTAs share one output tile when the caller does not say
+static int choose_splits(int n_tok, int n_out, int num_kb, int bn, int split_k) {
+    int splits = split_k;
+    if (splits <= 0) {
+        const long tiles = (long)((n_out + tc::BM - 1) / tc::BM) * ((n_tok + bn - 1) / bn);
+        // few tiles over a long K (the down projection of a decode step): eight parts, of which each CTA has a
+        // larger share on its way before the kernel before it has finished; over a short K eight cost more
+        // in the cluster's summing than they gain
+        splits = tiles >= 120 ? 1 : tiles >= 60 ? 2 : (tiles < 40 && num_kb >= 128) ? 8 : 4;
+    }
+    if (bn == 256) splits = 1;
+    while (splits > 1 && (num_kb + splits - 1) / splits * (splits - 1) >= num_kb) splits >>= 1;  // no empty part
+    if (splits == 8 && bn > 32) splits = 4;               // eight only where the owners sum the parts
+    return splits;
+}
+
+static int bn_for(int n_tok) { return n_tok <= 16 ? 16 : n_tok <= 32 ? 32 : n_tok <= 64 ? 64 : n_tok <= 128 ? 128 : 256; }
+
+// The folded forms (see the head of this file) as the exported functions take them: both optional.
+struct Folded {
+    const float* in_ssq; int n_in_parts; float in_eps; int in_width;          // scaled rows
+    float* residual; long ld_res; const void* sink_w; int sink_w_is_f32; float* out_ssq;   // sink
+};
+
+static int gemm_tn(const void* x, long ldx, const void* w, long ldw, void* y, long ldy, int y_is_f32, int n_tok,
+                   int n_out, int k, int split_k, const Folded& f, cudaStream_t stream) {
     if (n_tok <= 0 || n_out <= 0) return IB_OK;
     if (k <= 0) return IB_ERR_ARGUMENT;
     // TMA wants 16-byte aligned bases and row strides
     if ((k % 8) || (ldx % 8) || (ldw % 8) || ((uintptr_t)x % 16) || ((uintptr_t)w % 16)) return IB_ERR_UNSUPPORTED;
-    const int bn = n_tok <= 16 ? 16 : n_tok <= 32 ? 32 : n_tok <= 64 ? 64 : n_tok <= 128 ? 128 : 256;
+    const int bn = bn_for(n_tok);
+    if ((f.in_ssq != nullptr || f.residual != nullptr) && bn > 32) return IB_ERR_UNSUPPORTED;
+    if (f.residual != nullptr && (f.sink_w == nullptr || f.out_ssq == nullptr || y_is_f32)) return IB_ERR_ARGUMENT;
+    if (f.in_ssq != nullptr && (f.n_in_parts <= 0 || f.in_width <= 0)) return IB_ERR_ARGUMENT;
     tc::Params p;
     p.y = y; p.ldy = ldy; p.n_tok = n_tok; p.n_out = n_out; p.num_kb = (k + tc::BK - 1) / tc::BK; p.y_is_f32 = y_is_f32;
     p.inner = 0;
-    int splits = split_k;
-    if (splits <= 0) {
-        const long tiles = (long)((n_out + tc::BM - 1) / tc::BM) * ((n_tok + bn - 1) / bn);
-        splits = tiles >= 120 ? 1 : tiles >= 60 ? 2 : 4;
-    }
-    if (bn == 256) splits = 1;
-    while (splits > 1 && (p.num_kb + splits - 1) / splits * (splits - 1) >= p.num_kb) splits >>= 1;  // no empty part
+    p.in_ssq = f.in_ssq; p.n_in_parts = f.n_in_parts; p.in_eps = f.in_eps; p.in_inv_width = f.in_width > 0 ? 1.0f / (float)f.in_width : 0.0f;
+    p.residual = f.residual; p.ld_res = f.ld_res; p.sink_w = f.sink_w; p.sink_w_is_f32 = f.sink_w_is_f32; p.out_ssq = f.out_ssq;
+    const int splits = choose_splits(n_tok, n_out, p.num_kb, bn, split_k);
     if (splits != 1 && splits != 2 && splits != 4 && splits != 8) return IB_ERR_ARGUMENT;
-    if (splits == 8 && bn > 32) splits = 4;               // eight only where the owners sum the parts
     CUtensorMap mw, mx;
     if (!tc::make_map(&mw, w, n_out, k, ldw, tc::BM) || !tc::make_map(&mx, x, n_tok, k, ldx, bn)) return IB_ERR_UNSUPPORTED;
     switch (bn) {
@@ -417,21 +567,60 @@ IB_EXPORT int ib_gemm_tn_tcgen05(const void* x, long ldx, const void* w, long ld
     }
 }
 
+// x [n_tok, k] (row stride ldx), w [n_out, k] (row stride ldw), both bfloat16; y [n_tok, n_out] bfloat16 or float32.
+// split_k: 0 lets the function choose (1, 2, 4 or 8 CTAs per output tile); 8 is taken for up to 32 tokens (4 stands in beyond).
+IB_EXPORT int ib_gemm_tn_tcgen05(const void* x, long ldx, const void* w, long ldw, void* y, long ldy, int y_is_f32,
+                                 int n_tok, int n_out, int k, int split_k, cudaStream_t stream) {
+    const Folded none = {nullptr, 0, 0.0f, 0, nullptr, 0, nullptr, 0, nullptr};
+    return gemm_tn(x, ldx, w, ldw, y, ldy, y_is_f32, n_tok, n_out, k, split_k, none, stream);
+}
+
+// The same with the norms around it folded in (up to 32 tokens; y bfloat16).  in_ssq (or null): x holds rows times a
+// norm's weight, and the n_in_parts parts [.., 32] of their sums of squares over in_width elements; the product is
+// scaled by 1 / sqrt(sum / in_width + in_eps) per token.  residual (or null): y is added to this float32 stream
+// [n_tok, n_out] (row stride ld_res) in place, what is stored at y is the stream times sink_w [n_out], and the parts
+// of the new rows' sums of squares go to out_ssq [ib_gemm_tcgen05_ssq_parts(...), 32].
+IB_EXPORT int ib_gemm_tn_tcgen05_folded(const void* x, long ldx, const void* w, long ldw, void* y, long ldy, int n_tok,
+                                        int n_out, int k, int split_k, const float* in_ssq, int n_in_parts, float in_eps,
+                                        int in_width, float* residual, long ld_res, const void* sink_w,
+                                        int sink_w_is_f32, float* out_ssq, cudaStream_t stream) {
+    const Folded f = {in_ssq, n_in_parts, in_eps, in_width, residual, ld_res, sink_w, sink_w_is_f32, out_ssq};
+    return gemm_tn(x, ldx, w, ldw, y, ldy, 0, n_tok, n_out, k, split_k, f, stream);
+}
+
+// Parts that a sink of these sizes writes (one per CTA of the product); negative: the sizes take no sink.
+IB_EXPORT int ib_gemm_tcgen05_ssq_parts(int n_tok, int n_out, int k, int split_k) {
+    if (n_tok <= 0 || n_out <= 0 || k <= 0) return IB_ERR_ARGUMENT;
+    const int bn = bn_for(n_tok);
+    if (bn > 32) return IB_ERR_UNSUPPORTED;
+    return ((n_out + tc::BM - 1) / tc::BM) * choose_splits(n_tok, n_out, (k + tc::BK - 1) / tc::BK, bn, split_k);
+}
+
 // y[t, f] = silu(x[t] . w[f]) * (x[t] . w[inner + f]) for f < inner: the gate and up products of a gated feed-forward
 // and the gate itself in one kernel.  w [2 * inner, k] holds the gate matrix above the up matrix; y [n_tok, inner]
-// bfloat16.  Up to 32 tokens (IB_ERR_UNSUPPORTED beyond; the caller then runs product and gate separately).
-IB_EXPORT int ib_gemm_swiglu_tcgen05(const void* x, long ldx, const void* w, long ldw, void* y, long ldy, int n_tok,
-                                     int inner, int k, cudaStream_t stream) {
+// bfloat16.  Up to 32 tokens (IB_ERR_UNSUPPORTED beyond; the caller then runs product and gate separately).  With
+// in_ssq, x holds scaled rows as above and both products are scaled per token before the gate.
+IB_EXPORT int ib_gemm_swiglu_tcgen05_folded(const void* x, long ldx, const void* w, long ldw, void* y, long ldy, int n_tok,
+                                            int inner, int k, const float* in_ssq, int n_in_parts, float in_eps,
+                                            int in_width, cudaStream_t stream) {
     if (n_tok <= 0 || inner <= 0) return IB_OK;
     if (k <= 0) return IB_ERR_ARGUMENT;
     if ((k % 8) || (ldx % 8) || (ldw % 8) || ((uintptr_t)x % 16) || ((uintptr_t)w % 16) || n_tok > 32) return IB_ERR_UNSUPPORTED;
+    if (in_ssq != nullptr && (n_in_parts <= 0 || in_width <= 0)) return IB_ERR_ARGUMENT;
     const int bn = n_tok <= 16 ? 16 : 32;
     tc::Params p;
     p.y = y; p.ldy = ldy; p.n_tok = n_tok; p.n_out = inner; p.num_kb = (k + tc::BK - 1) / tc::BK; p.y_is_f32 = 0;
     p.inner = inner;
+    p.in_ssq = in_ssq; p.n_in_parts = n_in_parts; p.in_eps = in_eps; p.in_inv_width = in_width > 0 ? 1.0f / (float)in_width : 0.0f;
+    p.residual = nullptr; p.ld_res = 0; p.sink_w = nullptr; p.sink_w_is_f32 = 0; p.out_ssq = nullptr;
     CUtensorMap mw, mx;
     if (!tc::make_map(&mw, w, 2L * inner, k, ldw, 64) || !tc::make_map(&mx, x, n_tok, k, ldx, bn)) return IB_ERR_UNSUPPORTED;
     return bn == 16 ? tc::launch<16, 5, 1>(mw, mx, p, 1, stream) : tc::launch<32, 4, 1>(mw, mx, p, 1, stream);
+}
+
+IB_EXPORT int ib_gemm_swiglu_tcgen05(const void* x, long ldx, const void* w, long ldw, void* y, long ldy, int n_tok,
+                                     int inner, int k, cudaStream_t stream) {
+    return ib_gemm_swiglu_tcgen05_folded(x, ldx, w, ldw, y, ldy, n_tok, inner, k, nullptr, 0, 0.0f, 0, stream);
 }
 
 // 1: later launches may start before the kernel before them in the stream has finished (programmatic dependent

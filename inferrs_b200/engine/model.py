@@ -7,6 +7,7 @@ wants only the last, inferrs-models/src/models/attention_utils.rs:382-395).
 """
 from __future__ import annotations
 
+import inspect
 from typing import Dict, List, Optional
 
 import torch
@@ -144,6 +145,7 @@ class Model:
                 for name in _layer_tensor_names(layer):
                     if last_use[name] == i and name not in (spec.embedding, spec.lm_head):
                         weights.pop(name, None)
+        self._takes_after = ["after" in inspect.signature(b.forward).parameters for b in self.blocks]
         self.final_norm = part_class("norm", spec.final_norm)(spec.final_norm, weights, rt)
         head = weights.get(spec.lm_head)
         if head is None:
@@ -159,9 +161,17 @@ class Model:
         residual = torch.empty((n, self.spec.width), dtype=torch.float32, device=self.rt.device)
         kernels.embedding_gather(self.embedding, ctx.token_ids, residual, self.rt.dtype,
                                  1.0 if self.spec.embedding_scale is None else self.spec.embedding_scale)
-        pending: Optional[torch.Tensor] = None
-        for entry in self.spec.schedule:
-            pending = self.blocks[entry.layer].forward(ctx, entry.cache, residual, pending)
+        pending = None
+        schedule = self.spec.schedule
+        for k, entry in enumerate(schedule):
+            block = self.blocks[entry.layer]
+            # a block that wants to know what runs after it (to fold the norm between into the products around it)
+            # is told; the last block's output goes to the last norm, which reads a choice of rows
+            if k + 1 < len(schedule) and self._takes_after[entry.layer]:
+                after = getattr(self.blocks[schedule[k + 1].layer], "entry", None)
+                pending = block.forward(ctx, entry.cache, residual, pending, after=after() if after else None)
+            else:
+                pending = block.forward(ctx, entry.cache, residual, pending)
         if ctx.logit_rows.shape[0] == 0:
             return torch.empty((0, self.spec.vocab_size), dtype=torch.float32, device=self.rt.device)
         h = self.final_norm.add_norm(residual, pending, rows=ctx.logit_rows)

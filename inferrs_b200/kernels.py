@@ -8,6 +8,7 @@ functions: without a CUDA device, ``nvcc`` or a successful build they raise.
 from __future__ import annotations
 
 import ctypes
+from dataclasses import dataclass
 from typing import Optional
 
 import os
@@ -394,22 +395,79 @@ def gemm_tn_bf16(x: torch.Tensor, w: torch.Tensor, out: torch.Tensor):
         gemm_tn_simt(x, w, out, torch.bfloat16)
 
 
-def linear(x: torch.Tensor, w: torch.Tensor, out: torch.Tensor, act_dtype: torch.dtype):
-    """out = x @ w.T in the precision that ``act_dtype`` and the weight's own dtype ask for."""
+SSQ_LD = 32   # tokens per part of a list of sums of squares (csrc/gemm_tcgen05.cu)
+
+
+@dataclass
+class ScaledRows:
+    """Rows with an RMS norm folded in: ``x`` holds (stream * norm weight) as bfloat16, ``ssq[:n_parts, :rows]`` the
+    parts of the stream's sums of squares per row.  The norm's output is x / sqrt(sum(ssq) / width + eps) per row;
+    a product that reads ``x`` applies that factor to its result instead (see csrc/gemm_tcgen05.cu)."""
+
+    x: torch.Tensor
+    ssq: torch.Tensor
+    n_parts: int
+    eps: float
+    width: int
+
+    @property
+    def shape(self):
+        return self.x.shape
+
+    @property
+    def device(self):
+        return self.x.device
+
+
+@dataclass
+class ResidualSink:
+    """Where a product's result goes when the addition to the residual stream and the norm that follows are folded
+    into its read-back: it is added to ``residual`` (float32, in place) and handed on as :class:`ScaledRows` of the
+    norm with weight ``weight`` and ``eps``."""
+
+    residual: torch.Tensor
+    weight: torch.Tensor
+    eps: float
+
+
+def folded_norm_supported(n_rows: int, act_dtype: torch.dtype, w: torch.Tensor) -> bool:
+    """Whether a product of ``n_rows`` rows with weight ``w`` can take scaled rows or feed a sink: the bfloat16 tcgen05
+    product for a few rows does."""
+    return (act_dtype == torch.bfloat16 and w.dtype == torch.bfloat16 and n_rows <= min(TCGEN05_MAX_TOKENS, SSQ_LD)
+            and w.shape[1] % 8 == 0 and w.data_ptr() % 16 == 0)
+
+
+def linear(x, w: torch.Tensor, out: torch.Tensor, act_dtype: torch.dtype, sink: Optional[ResidualSink] = None):
+    """out = x @ w.T in the precision that ``act_dtype`` and the weight's own dtype ask for.  ``x`` may be
+    :class:`ScaledRows`; with ``sink`` the result is added to the residual stream and ``out`` receives the stream times
+    the next norm's weight: the returned :class:`ScaledRows` (else None) stand for that norm's output."""
+    if isinstance(x, ScaledRows) or sink is not None:
+        rows = x.shape[0]
+        if not folded_norm_supported(rows, act_dtype, w):
+            raise KernelError(f"linear: {rows} rows of {act_dtype} with a {w.dtype} weight cannot take folded norms; "
+                              f"ask folded_norm_supported first")
+        return gemm_tn_tcgen05(x, w, out, sink=sink)
     if act_dtype == torch.float32 or w.dtype == torch.float32:
         gemm_tn_simt(x, w, out, act_dtype)
     elif x.shape[0] <= TCGEN05_MAX_TOKENS and tcgen05_gemm_supported(x, w):
         gemm_tn_tcgen05(x, w, out)
     else:
         gemm_tn_bf16(x, w, out)
+    return None
 
 
-def gated_linear(x: torch.Tensor, w_gate_up: torch.Tensor, out: torch.Tensor, act_dtype: torch.dtype):
+def gated_linear(x, w_gate_up: torch.Tensor, out: torch.Tensor, act_dtype: torch.dtype):
     """out = silu(x @ gate.T) * (x @ up.T), ``w_gate_up`` [2 * inner, k] holding the gate matrix above the up
-    matrix.  A few bfloat16 rows run as one tcgen05 kernel; everything else as the product and the gate kernel."""
+    matrix.  A few bfloat16 rows run as one tcgen05 kernel; everything else as the product and the gate kernel.
+    ``x`` may be :class:`ScaledRows` (a few bfloat16 rows only)."""
     inner = out.shape[1]
     if w_gate_up.shape[0] != 2 * inner:
         raise KernelError(f"gated_linear: weights {tuple(w_gate_up.shape)} do not match out {tuple(out.shape)}")
+    if isinstance(x, ScaledRows):
+        if not folded_norm_supported(x.shape[0], act_dtype, w_gate_up) or x.shape[0] > SWIGLU_MAX_TOKENS:
+            raise KernelError("gated_linear: these rows cannot take a folded norm; ask folded_norm_supported first")
+        gemm_swiglu_tcgen05(x, w_gate_up, out)
+        return
     if act_dtype == torch.bfloat16 and w_gate_up.dtype == torch.bfloat16 \
             and x.shape[0] <= min(TCGEN05_MAX_TOKENS, SWIGLU_MAX_TOKENS) \
             and tcgen05_gemm_supported(x, w_gate_up):
@@ -739,6 +797,15 @@ def _gemm_lib():
         lib.ib_gemm_swiglu_tcgen05.argtypes = [c_void_p, c_long, c_void_p, c_long, c_void_p, c_long, c_int, c_int, c_int,
                                                c_void_p]
         lib.ib_gemm_swiglu_tcgen05.restype = c_int
+        lib.ib_gemm_tn_tcgen05_folded.argtypes = [c_void_p, c_long, c_void_p, c_long, c_void_p, c_long, c_int, c_int, c_int,
+                                                  c_int, c_void_p, c_int, c_float, c_int, c_void_p, c_long, c_void_p,
+                                                  c_int, c_void_p, c_void_p]
+        lib.ib_gemm_tn_tcgen05_folded.restype = c_int
+        lib.ib_gemm_swiglu_tcgen05_folded.argtypes = [c_void_p, c_long, c_void_p, c_long, c_void_p, c_long, c_int, c_int,
+                                                      c_int, c_void_p, c_int, c_float, c_int, c_void_p]
+        lib.ib_gemm_swiglu_tcgen05_folded.restype = c_int
+        lib.ib_gemm_tcgen05_ssq_parts.argtypes = [c_int, c_int, c_int, c_int]
+        lib.ib_gemm_tcgen05_ssq_parts.restype = c_int
         lib.ib_gemm_tcgen05_error.argtypes = [c_int]
         lib.ib_gemm_tcgen05_error.restype = c_int
         lib.ib_gemm_tcgen05_error_async.argtypes = [c_void_p, c_void_p]
@@ -753,34 +820,73 @@ def tcgen05_gemm_supported(x: torch.Tensor, w: torch.Tensor) -> bool:
             and x.data_ptr() % 16 == 0 and w.data_ptr() % 16 == 0)
 
 
-def gemm_tn_tcgen05(x: torch.Tensor, w: torch.Tensor, out: torch.Tensor, split_k: int = 0):
+def _scaled_args(x):
+    if isinstance(x, ScaledRows):
+        _need(x.ssq, "ssq", (torch.float32,), 2)
+        if x.ssq.shape[1] != SSQ_LD or x.ssq.shape[0] < x.n_parts or x.n_parts <= 0:
+            raise KernelError(f"scaled rows: {x.n_parts} parts do not fit a list of shape {tuple(x.ssq.shape)}")
+        return x.x, (_p(x.ssq), int(x.n_parts), float(x.eps), int(x.width))
+    return x, (None, 0, 0.0, 0)
+
+
+def gemm_tn_tcgen05(x, w: torch.Tensor, out: torch.Tensor, split_k: int = 0, sink: Optional[ResidualSink] = None):
     """out = x @ w.T with TMA-fed tcgen05 MMAs: W is the 128-row operand, the tokens are the N dimension.
-    ``split_k`` 0 lets the kernel library choose how many CTAs of a cluster share one output tile."""
-    _need(x, "x", (torch.bfloat16,), 2)
+    ``split_k`` 0 lets the kernel library choose how many CTAs of a cluster share one output tile.  ``x`` may be
+    :class:`ScaledRows` and the result may go to a :class:`ResidualSink` (both: up to 32 rows, bfloat16 out); with a
+    sink the :class:`ScaledRows` that stand for the next norm's output are returned."""
+    xt, scaled = _scaled_args(x)
+    _need(xt, "x", (torch.bfloat16,), 2)
     _need(w, "w", (torch.bfloat16,), 2)
     _need(out, "out", _W, 2)
-    n, k = x.shape
+    n, k = xt.shape
     m = w.shape[0]
     if w.shape[1] != k or out.shape != (n, m):
-        raise KernelError(f"gemm: x {tuple(x.shape)}, w {tuple(w.shape)}, out {tuple(out.shape)}")
-    code = _gemm_lib().ib_gemm_tn_tcgen05(_p(x), k, _p(w), k, _p(out), m, int(out.dtype == torch.float32), n, m, k,
-                                          split_k, _stream())
+        raise KernelError(f"gemm: x {tuple(xt.shape)}, w {tuple(w.shape)}, out {tuple(out.shape)}")
+    lib = _gemm_lib()
+    if scaled[0] is None and sink is None:
+        code = lib.ib_gemm_tn_tcgen05(_p(xt), k, _p(w), k, _p(out), m, int(out.dtype == torch.float32), n, m, k, split_k,
+                                      _stream())
+        if code == -1:
+            raise KernelError(f"gemm_tn_tcgen05: K={k} must be a multiple of 8 and the bases 16-byte aligned")
+        _check(code, "gemm_tn_tcgen05")
+        return None
+    if out.dtype != torch.bfloat16:
+        raise KernelError("gemm_tn_tcgen05: the folded forms store bfloat16")
+    result, sink_args = None, (None, 0, None, 0, None)
+    if sink is not None:
+        _need(sink.residual, "residual", (torch.float32,), 2)
+        _need(sink.weight, "sink weight", _W, 1)
+        if sink.residual.shape != (n, m) or sink.weight.shape[0] != m:
+            raise KernelError(f"gemm: residual {tuple(sink.residual.shape)} and norm weight {tuple(sink.weight.shape)} "
+                              f"do not match the result {(n, m)}")
+        parts = lib.ib_gemm_tcgen05_ssq_parts(n, m, k, split_k)
+        if parts <= 0:
+            raise KernelError(f"gemm_tn_tcgen05: {n} rows take no sink")
+        ssq = torch.empty((parts, SSQ_LD), dtype=torch.float32, device=out.device)
+        sink_args = (_p(sink.residual), m, _p(sink.weight), int(sink.weight.dtype == torch.float32), _p(ssq))
+        result = ScaledRows(out, ssq, parts, float(sink.eps), m)
+    code = lib.ib_gemm_tn_tcgen05_folded(_p(xt), k, _p(w), k, _p(out), m, n, m, k, split_k, *scaled, *sink_args, _stream())
     if code == -1:
-        raise KernelError(f"gemm_tn_tcgen05: K={k} must be a multiple of 8 and the bases 16-byte aligned")
-    _check(code, "gemm_tn_tcgen05")
+        raise KernelError(f"gemm_tn_tcgen05: the folded forms take up to {SSQ_LD} rows, K={k} a multiple of 8 and "
+                          f"16-byte aligned bases")
+    _check(code, "gemm_tn_tcgen05 (folded)")
+    return result
 
 
-def gemm_swiglu_tcgen05(x: torch.Tensor, w_gate_up: torch.Tensor, out: torch.Tensor):
+def gemm_swiglu_tcgen05(x, w_gate_up: torch.Tensor, out: torch.Tensor):
     """out[t, f] = silu(x[t] . w[f]) * (x[t] . w[inner + f]): both products of a gated feed-forward and the gate
-    in one tcgen05 kernel (64 gate rows and the same 64 up rows per tile).  Up to 32 rows of x."""
-    _need(x, "x", (torch.bfloat16,), 2)
+    in one tcgen05 kernel (64 gate rows and the same 64 up rows per tile).  Up to 32 rows of x, which may be
+    :class:`ScaledRows`."""
+    xt, scaled = _scaled_args(x)
+    _need(xt, "x", (torch.bfloat16,), 2)
     _need(w_gate_up, "w_gate_up", (torch.bfloat16,), 2)
     _need(out, "out", (torch.bfloat16,), 2)
-    n, k = x.shape
+    n, k = xt.shape
     inner = out.shape[1]
     if w_gate_up.shape != (2 * inner, k) or out.shape[0] != n:
-        raise KernelError(f"gemm_swiglu: x {tuple(x.shape)}, w {tuple(w_gate_up.shape)}, out {tuple(out.shape)}")
-    code = _gemm_lib().ib_gemm_swiglu_tcgen05(_p(x), k, _p(w_gate_up), k, _p(out), inner, n, inner, k, _stream())
+        raise KernelError(f"gemm_swiglu: x {tuple(xt.shape)}, w {tuple(w_gate_up.shape)}, out {tuple(out.shape)}")
+    code = _gemm_lib().ib_gemm_swiglu_tcgen05_folded(_p(xt), k, _p(w_gate_up), k, _p(out), inner, n, inner, k, *scaled,
+                                                     _stream())
     if code == -1:
         raise KernelError(f"gemm_swiglu_tcgen05: at most 32 rows (got {n}), K={k} a multiple of 8, 16-byte aligned bases")
     _check(code, "gemm_swiglu_tcgen05")

@@ -80,7 +80,15 @@ class Attention:
         if self.rot_dim > spec.head_dim:
             raise ValueError(f"rot_dim {self.rot_dim} exceeds head_dim {spec.head_dim}")
 
-    def forward(self, ctx, cache_id: int, h: torch.Tensor) -> torch.Tensor:
+    # A block may hand this part scaled rows instead of a norm's output, and a sink instead of taking its result, where
+    # both of its products fold norms at the step's number of rows (see SequentialBlock).
+    def takes_scaled_rows(self, n_rows: int) -> bool:
+        return self.qkv.folds_norms(n_rows)
+
+    def feeds_sink(self, n_rows: int) -> bool:
+        return self.o.folds_norms(n_rows)
+
+    def forward(self, ctx, cache_id: int, h, sink=None):
         s = self.spec
         n = h.shape[0]
         qkv = self.qkv(h)
@@ -92,7 +100,7 @@ class Attention:
                                    table, k_pages, v_pages, q)
         out = torch.empty((n, s.n_heads * s.head_dim), dtype=self.rt.dtype, device=h.device)
         kernels.paged_attention(q, k_pages, v_pages, table, ctx, s.scale, s.window, out)
-        return self.o(out)
+        return self.o(out, sink=sink)
 
 
 register_mixer("attention", Attention)

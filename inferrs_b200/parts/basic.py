@@ -26,12 +26,21 @@ class RMSNorm:
         self.rt = rt
         self.weight = weights[spec.weight]
 
-    def add_norm(self, residual: torch.Tensor, delta: Optional[torch.Tensor],
-                 rows: Optional[torch.Tensor] = None) -> torch.Tensor:
+    def add_norm(self, residual: torch.Tensor, delta, rows: Optional[torch.Tensor] = None):
+        if isinstance(delta, kernels.ScaledRows):
+            # the product before has added its result to the residual stream and folded this norm in (it was given
+            # this norm's sink): what it handed on stands for the norm's output
+            if rows is not None:
+                raise ValueError("scaled rows stand for all rows of a step, not for a choice of them")
+            return delta
         n = residual.shape[0] if rows is None else rows.shape[0]
         out = torch.empty((n, self.spec.size), dtype=self.rt.dtype, device=residual.device)
         kernels.add_rms_norm(residual, delta, self.weight, self.spec.eps, out, rows)
         return out
+
+    def sink(self, residual: torch.Tensor) -> "kernels.ResidualSink":
+        """For a product that can fold the addition to the residual stream and this norm into its read-back."""
+        return kernels.ResidualSink(residual, self.weight, self.spec.eps)
 
     def norm(self, x: torch.Tensor) -> torch.Tensor:
         """The norm alone, on rows in the activation dtype (a norm on a sub-layer's output)."""
@@ -135,7 +144,13 @@ class Linear:
         self.rt = rt
         self.n_out, self.n_in = weight.shape
 
-    def __call__(self, x: torch.Tensor, out_dtype: Optional[torch.dtype] = None) -> torch.Tensor:
+    def __call__(self, x, out_dtype: Optional[torch.dtype] = None, sink=None):
+        """``x`` may be :class:`~inferrs_b200.kernels.ScaledRows`; with a ``sink`` the result is added to the residual
+        stream there and the next norm's scaled rows come back instead of the result."""
         out = torch.empty((x.shape[0], self.n_out), dtype=out_dtype or self.rt.dtype, device=x.device)
-        kernels.linear(x, self.weight, out, self.rt.dtype)
-        return out
+        scaled = kernels.linear(x, self.weight, out, self.rt.dtype, sink=sink)
+        return out if sink is None else scaled
+
+    def folds_norms(self, n_rows: int) -> bool:
+        """Whether this product takes scaled rows and feeds a sink at this number of rows."""
+        return kernels.folded_norm_supported(n_rows, self.rt.dtype, self.weight)

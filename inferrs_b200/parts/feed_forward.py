@@ -34,10 +34,16 @@ class GatedDense:
         self.gate_up = Linear(fuse_rows([weights[spec.gate_proj], weights[spec.up_proj]]), rt)
         self.down = Linear(weights[spec.down_proj], rt)
 
-    def forward(self, ctx, h: torch.Tensor) -> torch.Tensor:
+    def takes_scaled_rows(self, n_rows: int) -> bool:
+        return self.gate_up.folds_norms(n_rows) and n_rows <= kernels.SWIGLU_MAX_TOKENS
+
+    def feeds_sink(self, n_rows: int) -> bool:
+        return self.down.folds_norms(n_rows)
+
+    def forward(self, ctx, h, sink=None):
         a = torch.empty((h.shape[0], self.spec.inner), dtype=self.rt.dtype, device=h.device)
         kernels.gated_linear(h, self.gate_up.weight, a, self.rt.dtype)
-        return self.down(a)
+        return self.down(a, sink=sink)
 
 
 register_feed_forward("gated_dense", GatedDense)

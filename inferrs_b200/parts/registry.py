@@ -30,7 +30,14 @@ arrangement
     ``part``, ``norm``, ``post_norm``; ``run(ctx, cache_id, h)`` calls the part the way its category wants),
     ``forward(ctx, cache_id, residual, pending) -> pending`` (``residual`` float32 ``[rows, width]``, updated in
     place; ``pending`` is a sub-layer output that has not been added yet, or None), and
-    ``parts() -> iterable`` of every part object the block holds.
+    ``parts() -> iterable`` of every part object the block holds.  Optional: ``entry() -> BuiltSubLayer`` (the
+    sub-layer that takes what the block before hands on) and a keyword ``after`` of ``forward`` (the next block's
+    entry): with them a block may fold the norm between two products into those products.
+
+Optional for mixers and feed-forwards: ``takes_scaled_rows(n_rows)`` / ``feeds_sink(n_rows)`` and a ``sink`` keyword
+of ``forward``.  A part that has them may be handed :class:`~inferrs_b200.kernels.ScaledRows` in place of its norm's
+output, and a :class:`~inferrs_b200.kernels.ResidualSink` in place of returning its result (see
+:class:`~inferrs_b200.parts.blocks.SequentialBlock`); a part without them never sees either.
 
 Every part may set ``graph_safe = True`` to say that its launches depend only on shapes and device
 memory, never on host-side values of the step; a model whose parts all say so has its steps captured

@@ -137,12 +137,31 @@ def gemm_tn_bf16(x, w, out):
     out.copy_((x.float() @ w.float().t()).to(out.dtype))
 
 
-def linear(x, w, out, act_dtype=None):
-    out.copy_((x.float() @ w.float().t()).to(out.dtype))
+def _unscale(x):
+    """What scaled rows stand for: (stream * weight) / sqrt(sum of squares / width + eps) per row."""
+    ss = x.ssq[:x.n_parts, :x.x.shape[0]].sum(dim=0)
+    return x.x.float() / torch.sqrt(ss / x.width + x.eps)[:, None]
+
+
+def linear(x, w, out, act_dtype=None, sink=None):
+    """With scaled rows and a sink as the product with folded norms defines them (csrc/gemm_tcgen05.cu)."""
+    import inferrs_b200.kernels as K
+    xf = _unscale(x) if isinstance(x, K.ScaledRows) else x.float()
+    y = xf @ w.float().t()
+    if sink is None:
+        out.copy_(y.to(out.dtype))
+        return None
+    sink.residual += y.to(out.dtype).float()
+    out.copy_((sink.residual * sink.weight.float()).to(out.dtype))
+    ssq = torch.zeros((1, K.SSQ_LD), dtype=torch.float32, device=out.device)
+    ssq[0, :out.shape[0]] = (sink.residual * sink.residual).sum(dim=1)
+    return K.ScaledRows(out, ssq, 1, float(sink.eps), out.shape[1])
 
 
 def gated_linear(x, w_gate_up, out, act_dtype=None):
-    gu = (x.float() @ w_gate_up.float().t()).to(out.dtype)
+    import inferrs_b200.kernels as K
+    xf = _unscale(x) if isinstance(x, K.ScaledRows) else x.float()
+    gu = (xf @ w_gate_up.float().t()).to(out.dtype)
     silu_gate(gu, out)
 
 

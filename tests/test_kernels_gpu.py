@@ -736,3 +736,57 @@ def test_attention_over_long_contexts(name, context):
     got = out[new[0] - 1].view(nh, d).float()
     want = v_pages[page, :, slot, :].float().repeat_interleave(nh // nkv, dim=0)
     assert rel_err(got, want) < 5e-2, "the far key that stands out was not seen"
+
+
+@pytest.mark.parametrize("n,m,k", [(1, 4096, 4096), (8, 4096, 12288), (16, 300, 136), (5, 6144, 1024), (13, 384, 64)])
+def test_products_with_folded_norms(n, m, k):
+    """The tcgen05 product for a few rows with the addition to the residual stream and the norm that follows folded
+    into its read-back (a sink), and the products that read what it hands on (scaled rows): against the same
+    arithmetic in plain float32, and against the unfolded kernels (product, then the norm kernel)."""
+    from inferrs_b200 import kernels as K
+    dtype = torch.bfloat16
+    x, w = rand((n, k), dtype, 90), rand((m, k), dtype, 91, scale=0.05)
+    res0 = rand((n, m), torch.float32, 92)
+    wn = (1 + 0.1 * rand((m,), torch.float32, 93)).to(dtype)
+    eps = 1e-5
+    assert K.folded_norm_supported(n, dtype, w)
+    # the sink
+    res, out = res0.clone(), torch.full((n, m), float("nan"), dtype=dtype, device=dev())
+    scaled = K.linear(x, w, out, dtype, sink=K.ResidualSink(res, wn, eps))
+    assert K.gemm_tcgen05_error() == 0
+    assert isinstance(scaled, K.ScaledRows) and scaled.x is out and scaled.width == m
+    res_ref, out_ref = res0.clone(), torch.empty_like(out)
+    scaled_ref = R.linear(x, w, out_ref, dtype, sink=K.ResidualSink(res_ref, wn, eps))
+    assert rel_err(res, res_ref) < 1e-2 and rel_err(out, out_ref) < TOL[dtype]
+    ss = scaled.ssq[:scaled.n_parts, :n].sum(dim=0)
+    assert rel_err(ss, (res.double() ** 2).sum(dim=1).float()) < 1e-5, "the parts must add up to the rows' sums of squares"
+    # ... is what the product and then the norm kernel give
+    y = torch.empty((n, m), dtype=dtype, device=dev())
+    K.linear(x, w, y, dtype)
+    res2, normed = res0.clone(), torch.empty((n, m), dtype=dtype, device=dev())
+    K.add_rms_norm(res2, y, wn, eps, normed)
+    assert torch.equal(res2, res), "the stream must get the same bits either way"
+    assert rel_err(R._unscale(scaled), normed) < TOL[dtype]
+    # scaled rows into a product and into the gated pair of products
+    if m % 8 == 0:
+        w2 = rand((264, m), dtype, 94, scale=0.05)
+        got, ref = torch.empty((n, 264), dtype=dtype, device=dev()), torch.empty((n, 264), dtype=dtype, device=dev())
+        K.linear(scaled, w2, got, dtype)
+        R.linear(scaled, w2, ref, dtype)
+        assert rel_err(got, ref) < TOL[dtype]
+        K.linear(normed, w2, ref, dtype)            # the unfolded way: the norm kernel's output into the product
+        assert rel_err(got, ref) < 2 * TOL[dtype]
+        wg = rand((2 * 192, m), dtype, 95, scale=0.05)
+        got, ref = torch.empty((n, 192), dtype=dtype, device=dev()), torch.empty((n, 192), dtype=dtype, device=dev())
+        K.gated_linear(scaled, wg, got, dtype)
+        R.gated_linear(scaled, wg, ref, dtype)
+        assert rel_err(got, ref) < 2 * TOL[dtype]
+        # a sink fed from scaled rows (both folded forms in one launch)
+        res3, out3 = res0[:, :264].contiguous(), torch.empty((n, 264), dtype=dtype, device=dev())
+        res3_ref, out3_ref = res3.clone(), torch.empty_like(out3)
+        wn3 = wn[:264].contiguous()
+        K.linear(scaled, w2, out3, dtype, sink=K.ResidualSink(res3, wn3, eps))
+        R.linear(scaled, w2, out3_ref, dtype, sink=K.ResidualSink(res3_ref, wn3, eps))
+        assert rel_err(res3, res3_ref) < 1e-2 and rel_err(out3, out3_ref) < 2 * TOL[dtype]
+    assert K.gemm_tcgen05_error() == 0
+    assert not K.folded_norm_supported(40, dtype, w) and not K.folded_norm_supported(n, torch.float32, w.float())
