@@ -345,3 +345,41 @@ def test_the_positions_of_the_published_checkpoints(tmp_path):
         rows.append(runner.step([StepEntry("r", toks[t:t + 1], [0])]))
     check(torch.cat(rows), want[n_prompt:], dtype, "decoding at 2,500 tokens with block tables of 2,560 pages")
     assert sorted(runner.graphs.captured) == [1] and sorted(runner.portion_graphs.captured) == [512, 1024]
+
+
+def test_decode_steps_fold_the_norms_into_the_products(model_dirs, monkeypatch):
+    """In a step of a few rows the addition to the residual stream and the norm between two products run inside the
+    products (head size 128, bfloat16): the norm kernel is then launched for the first layer's first norm and the last
+    norm only, and the logits are those of the same step with every norm as a kernel of its own."""
+    from inferrs_b200 import kernels
+    name, dtype = "D", torch.bfloat16
+    toks = random_tokens(60, CONFIGS[name]["vocab_size"], seed=77)
+    want = plain_logits(model_dirs[name], toks, dtype)
+
+    def decode(fold):
+        if not fold:
+            monkeypatch.setattr(kernels, "folded_norm_supported", lambda *a, **k: False)
+        calls = {"n": 0}
+        original = kernels.add_rms_norm
+
+        def counted(*a, **k):
+            calls["n"] += 1
+            return original(*a, **k)
+
+        monkeypatch.setattr(kernels, "add_rms_norm", counted)
+        runner = make_runner(model_dirs[name], dtype, PAGE_SIZE[name], n_pages=16)
+        runner.graphs = runner.portion_graphs = None          # launched one by one, so that the launches can be counted
+        runner.admit("r")
+        runner.step([StepEntry("r", toks[:40], [])])
+        calls["n"] = 0
+        rows = [runner.step([StepEntry("r", toks[t:t + 1], [0])]) for t in range(40, 60)]
+        monkeypatch.undo()
+        return torch.cat(rows), calls["n"] / 20
+
+    folded, n_folded = decode(True)
+    plain, n_plain = decode(False)
+    layers = CONFIGS[name]["num_hidden_layers"]
+    assert n_plain == 2 * layers + 1 and n_folded == 2, (n_plain, n_folded)
+    check(folded, want[40:], dtype, "folded norms")
+    check(plain, want[40:], dtype, "norm kernels")
+    assert rel_err(folded, plain) < 2e-2
