@@ -40,7 +40,7 @@ _CORE_SOURCES = ["elementwise.cu", "qk_rope_store.cu", "attention_generic.cu", "
 LIBRARIES: Dict[str, dict] = {
     "core_f32": {"sources": _CORE_SOURCES, "flags": ["-DIB_ACT_BF16=0"], "link": []},
     "core_bf16": {"sources": _CORE_SOURCES, "flags": ["-DIB_ACT_BF16=1"], "link": []},
-    "gemm_bf16": {"sources": ["gemm_tcgen05.cu"], "flags": ["-DIB_ACT_BF16=1"], "link": []},
+    "gemm_bf16": {"sources": ["gemm_tcgen05.cu", "gemm_chain.cu"], "flags": ["-DIB_ACT_BF16=1"], "link": []},
     # host code only (the cache's book-keeping and the step description): the C++ compiler alone builds it
     "host_runtime": {"sources": ["host_runtime.cpp"], "flags": [], "link": [], "host": True},
 }

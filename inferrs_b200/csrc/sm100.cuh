@@ -27,6 +27,13 @@ __device__ __forceinline__ bool mbar_try_wait(unsigned bar, unsigned parity) {
                  : "=r"(ok) : "r"(bar), "r"(parity) : "memory");
     return ok != 0;
 }
+// the same question without waiting: try_wait may suspend the thread for a while when the answer is no
+__device__ __forceinline__ bool mbar_test_wait(unsigned bar, unsigned parity) {
+    unsigned ok;
+    asm volatile("{\n\t.reg .pred p;\n\tmbarrier.test_wait.parity.shared::cta.b64 p, [%1], %2;\n\tselp.u32 %0, 1, 0, p;\n\t}"
+                 : "=r"(ok) : "r"(bar), "r"(parity) : "memory");
+    return ok != 0;
+}
 __device__ __forceinline__ unsigned long long global_ns() {
     unsigned long long t;
     asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t));
@@ -38,12 +45,17 @@ __device__ __forceinline__ unsigned long long global_ns() {
 constexpr unsigned long long MBAR_WAIT_LIMIT_NS = 2000000000ull;
 static __device__ __noinline__ bool mbar_wait_slow(unsigned bar, unsigned parity, int* error_word, int code,
                                                    unsigned long long limit_ns) {
-    const unsigned long long t0 = global_ns();
+    unsigned long long t0 = 0;   // the clock is first read after 1,024 tries: reading it costs as much as a short wait
     for (unsigned it = 1;; ++it) {
         if (mbar_try_wait(bar, parity)) return true;
-        if ((it & 1023u) == 0 && global_ns() - t0 > limit_ns) {
-            atomicCAS(error_word, 0, code);
-            return false;
+        if ((it & 1023u) == 0) {
+            const unsigned long long now = global_ns();
+            if (t0 == 0) {
+                t0 = now;
+            } else if (now - t0 > limit_ns) {
+                atomicCAS(error_word, 0, code);
+                return false;
+            }
         }
     }
 }

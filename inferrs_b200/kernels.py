@@ -437,6 +437,108 @@ def folded_norm_supported(n_rows: int, act_dtype: torch.dtype, w: torch.Tensor) 
             and w.shape[1] % 8 == 0 and w.data_ptr() % 16 == 0)
 
 
+# ---- chains of products ---------------------------------------------------------------------------------------
+# In a step of a few rows the products whose norms are folded in follow one another without any other kernel between
+# them: o projection (sink) -> gate/up (scaled rows) -> down (sink) -> the next layer's q/k/v (scaled rows).
+# csrc/gemm_chain.cu runs up to four such products as ONE persistent cooperative kernel whose producers keep streaming
+# the next product's weights while the CTAs meet between two products.  On a B200 it came out a little slower than the
+# products launched one by one under programmatic dependent launch (a meeting of 148 CTAs through global memory costs
+# 5 to 6 us, as much as a kernel's ends), so the parts do not use it; it stands here as a kernel of its own with its
+# tests, for shapes and machines where the balance is another.
+_CHAIN_WS = {}       # device index -> (workspace, counters, number of CTAs)
+
+
+class _ChainProduct(ctypes.Structure):
+    _fields_ = [("x", c_void_p), ("ldx", c_long), ("w", c_void_p), ("ldw", c_long), ("y", c_void_p), ("ldy", c_long),
+                ("n_out", c_int), ("k", c_int), ("gated", c_int),
+                ("in_ssq", c_void_p), ("n_in_parts", c_int), ("in_eps", c_float), ("in_width", c_int),
+                ("residual", c_void_p), ("ld_res", c_long), ("sink_w", c_void_p), ("sink_w_is_f32", c_int),
+                ("out_ssq", c_void_p)]
+
+
+def _chain_workspace(device: torch.device):
+    idx = device.index if device.index is not None else torch.cuda.current_device()
+    ws = _CHAIN_WS.get(idx)
+    if ws is None:
+        lib = _gemm_lib()
+        sms = torch.cuda.get_device_properties(idx).multi_processor_count
+        # (the kernel needs the workspace filled with its "not yet" value and the counters zero, and leaves them so)
+        ws = (torch.full((lib.ib_gemm_chain_workspace_floats(sms),), lib.ib_gemm_chain_workspace_fill(),
+                         dtype=torch.int32, device=device).view(torch.float32),
+              torch.zeros((lib.ib_gemm_chain_max_products() + 1,), dtype=torch.int32, device=device), sms)
+        _CHAIN_WS[idx] = ws
+    return ws
+
+
+class ProductChain:
+    """Up to four products of a few bfloat16 rows (at most 16) that are launched as one kernel by :meth:`launch`.
+
+    ``linear`` and ``gated_linear`` take what the functions of the same names take, ``x`` a tensor or
+    :class:`ScaledRows`; a product's output tensor may be the input of a later product of the chain (that is what the
+    chain is for) and holds nothing before the launch."""
+
+    def __init__(self):
+        self._products = []    # (structure, rows, device, units, what keeps the tensors alive)
+
+    def linear(self, x, w: torch.Tensor, out: torch.Tensor, sink: Optional["ResidualSink"] = None):
+        return self._add(x, w, out, sink, gated=False)
+
+    def gated_linear(self, x, w_gate_up: torch.Tensor, out: torch.Tensor):
+        if w_gate_up.shape[0] != 2 * out.shape[1] or out.shape[1] % 64 != 0:
+            raise KernelError(f"chain: gate/up weights {tuple(w_gate_up.shape)} for out {tuple(out.shape)} "
+                              f"(the inner width must be a multiple of 64)")
+        self._add(x, w_gate_up, out, None, gated=True)
+
+    def _add(self, x, w, out, sink, gated):
+        lib = _gemm_lib()
+        if len(self._products) >= lib.ib_gemm_chain_max_products():
+            raise KernelError(f"chain: at most {lib.ib_gemm_chain_max_products()} products")
+        xt, scaled = _scaled_args(x)
+        _need(xt, "x", (torch.bfloat16,), 2)
+        _need(w, "w", (torch.bfloat16,), 2)
+        _need(out, "out", (torch.bfloat16,), 2)
+        n, k = xt.shape
+        m = out.shape[1]
+        if n > 16 or k % 8 != 0:
+            raise KernelError(f"chain: {n} rows of width {k} (at most 16 rows, a width that is a multiple of 8)")
+        if w.shape != ((2 * m if gated else m), k) or out.shape[0] != n:
+            raise KernelError(f"chain: x {tuple(xt.shape)}, w {tuple(w.shape)}, out {tuple(out.shape)}")
+        if self._products and (self._products[0][1] != n or self._products[0][2] != out.device):
+            raise KernelError("chain: all products have the same rows on the same device")
+        prod = _ChainProduct(x=_p(xt), ldx=k, w=_p(w), ldw=k, y=_p(out), ldy=m, n_out=m, k=k, gated=int(gated),
+                             in_ssq=scaled[0], n_in_parts=scaled[1], in_eps=scaled[2], in_width=scaled[3])
+        result, keep = None, [xt, w, out, x]
+        if sink is not None:
+            _need(sink.residual, "residual", (torch.float32,), 2)
+            _need(sink.weight, "sink weight", _W, 1)
+            if sink.residual.shape != (n, m) or sink.weight.shape[0] != m or gated:
+                raise KernelError(f"chain: residual {tuple(sink.residual.shape)} and norm weight "
+                                  f"{tuple(sink.weight.shape)} do not match the result {(n, m)}")
+            parts = lib.ib_gemm_chain_ssq_parts(m)
+            ssq = torch.empty((parts, SSQ_LD), dtype=torch.float32, device=out.device)
+            prod.residual, prod.ld_res, prod.sink_w = _p(sink.residual), m, _p(sink.weight)
+            prod.sink_w_is_f32, prod.out_ssq = int(sink.weight.dtype == torch.float32), _p(ssq)
+            result = ScaledRows(out, ssq, parts, float(sink.eps), m)
+            keep += [sink.residual, sink.weight, ssq]
+        units = ((m // 64) if gated else (m + 127) // 128) * ((k + 63) // 64)
+        self._products.append((prod, n, out.device, units, keep))
+        return result
+
+    def launch(self):
+        if not self._products:
+            return
+        products, self._products = self._products, []
+        n_tok, device = products[0][1], products[0][2]
+        scratch, counters, sms = _chain_workspace(device)
+        grid = min([sms] + [p[3] for p in products])
+        arr = (_ChainProduct * len(products))(*[p[0] for p in products])
+        code = _gemm_lib().ib_gemm_chain(arr, len(products), n_tok, _p(scratch), _p(counters), grid, _stream())
+        if code == -1:
+            raise KernelError("chain: these sizes are not supported (up to 16 rows, K a multiple of 8, gated widths a "
+                              "multiple of 64)")
+        _check(code, "chain of products")
+
+
 def linear(x, w: torch.Tensor, out: torch.Tensor, act_dtype: torch.dtype, sink: Optional[ResidualSink] = None):
     """out = x @ w.T in the precision that ``act_dtype`` and the weight's own dtype ask for.  ``x`` may be
     :class:`ScaledRows`; with ``sink`` the result is added to the residual stream and ``out`` receives the stream times
@@ -806,6 +908,22 @@ def _gemm_lib():
         lib.ib_gemm_swiglu_tcgen05_folded.restype = c_int
         lib.ib_gemm_tcgen05_ssq_parts.argtypes = [c_int, c_int, c_int, c_int]
         lib.ib_gemm_tcgen05_ssq_parts.restype = c_int
+        lib.ib_gemm_chain.argtypes = [c_void_p, c_int, c_int, c_void_p, c_void_p, c_int, c_void_p]
+        lib.ib_gemm_chain.restype = c_int
+        lib.ib_gemm_chain_workspace_floats.argtypes = [c_int]
+        lib.ib_gemm_chain_workspace_floats.restype = c_long
+        lib.ib_gemm_chain_workspace_fill.argtypes = []
+        lib.ib_gemm_chain_workspace_fill.restype = c_int
+        lib.ib_gemm_chain_max_products.argtypes = []
+        lib.ib_gemm_chain_max_products.restype = c_int
+        lib.ib_gemm_chain_ssq_parts.argtypes = [c_int]
+        lib.ib_gemm_chain_ssq_parts.restype = c_int
+        lib.ib_gemm_chain_set_pdl.argtypes = [c_int]
+        lib.ib_gemm_chain_set_pdl.restype = None
+        lib.ib_gemm_chain_error.argtypes = [c_int]
+        lib.ib_gemm_chain_error.restype = c_int
+        lib.ib_gemm_chain_error_async.argtypes = [c_void_p, c_void_p]
+        lib.ib_gemm_chain_error_async.restype = c_int
         lib.ib_gemm_tcgen05_error.argtypes = [c_int]
         lib.ib_gemm_tcgen05_error.restype = c_int
         lib.ib_gemm_tcgen05_error_async.argtypes = [c_void_p, c_void_p]
@@ -896,6 +1014,7 @@ def gemm_tcgen05_set_pdl(on: bool):
     """Let tcgen05 products start before their predecessor in the stream has finished (they prefetch weights and
     wait for the predecessor before touching anything else).  Only safe among kernels that all wait likewise."""
     _gemm_lib().ib_gemm_tcgen05_set_pdl(int(bool(on)))
+    _gemm_lib().ib_gemm_chain_set_pdl(int(bool(on)))
 
 
 def set_pdl(on: bool, act_dtype: torch.dtype = torch.bfloat16):
@@ -922,12 +1041,18 @@ def gemm_tcgen05_error(reset: bool = True) -> int:
     return _gemm_lib().ib_gemm_tcgen05_error(int(reset))
 
 
+def gemm_chain_error(reset: bool = True) -> int:
+    """0, or the code of the first bounded wait that ran out in a chain of products (synchronises)."""
+    return _gemm_lib().ib_gemm_chain_error(int(reset))
+
+
 # ---- the kernels' error words, all of them ------------------------------------------------------------------
 # A bounded wait that ran out, or a row whose position lay outside the rotation tables, leaves a code in a word
 # on the device.  The functions above read one word each and wait for the device; these read all of them the way
 # a serving loop wants it: asked for in stream order, read later from pinned memory.
 ERROR_WORDS = ("a row's position outside the rotation tables", "prefill attention (tcgen05)",
-               "prefill attention (two query tiles)", "decode attention", "matrix product (tcgen05)")
+               "prefill attention (two query tiles)", "decode attention", "matrix product (tcgen05)",
+               "chain of matrix products")
 
 
 def error_words_async(host: torch.Tensor, act_dtype: torch.dtype):
@@ -940,9 +1065,9 @@ def error_words_async(host: torch.Tensor, act_dtype: torch.dtype):
     calls = [core.ib_row_fault_async, core.ib_attention_tcgen05_error_async,
              core.ib_attention_pair_tcgen05_error_async, core.ib_attention_decode_error_async]
     if act_dtype == torch.bfloat16:
-        calls.append(_gemm_lib().ib_gemm_tcgen05_error_async)
+        calls += [_gemm_lib().ib_gemm_tcgen05_error_async, _gemm_lib().ib_gemm_chain_error_async]
     else:
-        host[len(calls)] = 0
+        host[len(calls):len(ERROR_WORDS)] = 0
     for i, fn in enumerate(calls):
         code = fn(at + 4 * i, stream)
         if code != 0:
@@ -958,7 +1083,7 @@ def reset_error_words(act_dtype: torch.dtype) -> dict:
         found[ERROR_WORDS[0]] = row + 1
     if act_dtype == torch.bfloat16:
         for name, fn in zip(ERROR_WORDS[1:], (attention_tcgen05_error, attention_pair_tcgen05_error,
-                                              attention_decode_error, gemm_tcgen05_error)):
+                                              attention_decode_error, gemm_tcgen05_error, gemm_chain_error)):
             v = fn(True)
             if v:
                 found[name] = v

@@ -144,12 +144,32 @@ def chain(args) -> dict:
     ws = [[(torch.randn(n, k, device="cuda") * 0.02).to(torch.bfloat16) for n, k in shapes] for _ in range(args.layers)]
     xs = [torch.randn(args.m, k, device="cuda").to(torch.bfloat16) for _, k in shapes]
     outs = [torch.empty(args.m, n, dtype=torch.bfloat16, device="cuda") for n, _ in shapes]
-    fn = {"library": kernels.gemm_tn_bf16, "tcgen05": lambda x, w, o: kernels.gemm_tn_tcgen05(x, w, o, 0)}[args.impl]
+    if args.impl in ("folded", "persistent"):
+        # the products as a decode step has them, norms folded in: o projection into the stream, gate and up with
+        # the gate, down into the stream, q/k/v; one kernel each, or all four as one persistent kernel
+        res = torch.randn(args.m, h, device="cuda")
+        norm = [torch.ones(h, dtype=torch.bfloat16, device="cuda") for _ in range(2)]
+        act = torch.empty(args.m, inner, dtype=torch.bfloat16, device="cuda")
+        bf = torch.bfloat16
 
-    def run():
-        for layer in ws:
-            for x, w, o in zip(xs, layer, outs):
-                fn(x, w, o)
+        def run():
+            for w_qkv, w_o, w_gu, w_d in ws:
+                c = kernels.ProductChain() if args.impl == "persistent" else None
+                lin = c.linear if c else (lambda x, w, o, sink=None: kernels.linear(x, w, o, bf, sink=sink))
+                gated = c.gated_linear if c else (lambda x, w, o: kernels.gated_linear(x, w, o, bf))
+                s1 = lin(xs[1], w_o, outs[1], sink=kernels.ResidualSink(res, norm[0], 1e-6))
+                gated(s1, w_gu, act)
+                s2 = lin(act, w_d, outs[3], sink=kernels.ResidualSink(res, norm[1], 1e-6))
+                lin(s2, w_qkv, outs[0])
+                if c:
+                    c.launch()
+    else:
+        fn = {"library": kernels.gemm_tn_bf16, "tcgen05": lambda x, w, o: kernels.gemm_tn_tcgen05(x, w, o, 0)}[args.impl]
+
+        def run():
+            for layer in ws:
+                for x, w, o in zip(xs, layer, outs):
+                    fn(x, w, o)
 
     if args.pdl:
         kernels.gemm_tcgen05_set_pdl(True)
@@ -374,7 +394,8 @@ def main(argv=None) -> int:
     a.add_argument("--iters", type=int, default=20)
     a.set_defaults(fn=attention)
     c = sub.add_parser("chain")
-    c.add_argument("--impl", choices=["library", "tcgen05"], default="library")
+    c.add_argument("--impl", choices=["library", "tcgen05", "folded", "persistent"], default="library",
+                   help="folded: the products with the norms folded in, one kernel each; persistent: the same four as one kernel")
     c.add_argument("--m", type=int, default=8)
     c.add_argument("--layers", type=int, default=8)
     c.add_argument("--hidden", type=int, default=4096)
@@ -382,7 +403,7 @@ def main(argv=None) -> int:
     c.add_argument("--qkv", type=int, default=6144)
     c.add_argument("--attn-out", type=int, default=4096)
     c.add_argument("--iters", type=int, default=10)
-    c.add_argument("--pdl", action="store_true", help="tcgen05 only: programmatic dependent launch between the products")
+    c.add_argument("--pdl", action="store_true", help="programmatic dependent launch between the kernels (not for the library's)")
     c.set_defaults(fn=chain)
     st = sub.add_parser("step")
     st.add_argument("--form", choices=["decode", "prefill"], default="decode")

@@ -60,4 +60,4 @@ def test_the_engine_reads_the_words_in_stream_order():
         assert h.pending
         assert h.poll(wait=True) == {}
         assert h.reset() == {}
-        assert len(kernels.ERROR_WORDS) == 5
+        assert len(kernels.ERROR_WORDS) == 6

@@ -790,3 +790,67 @@ def test_products_with_folded_norms(n, m, k):
         assert rel_err(res3, res3_ref) < 1e-2 and rel_err(out3, out3_ref) < 2 * TOL[dtype]
     assert K.gemm_tcgen05_error() == 0
     assert not K.folded_norm_supported(40, dtype, w) and not K.folded_norm_supported(n, torch.float32, w.float())
+
+
+@pytest.mark.parametrize("n,width,inner,qkv", [(8, 4096, 12288, 6144), (1, 1024, 3072, 4096), (16, 192, 320, 1280), (3, 5120, 1088, 640)])
+def test_a_chain_of_products_is_one_launch_and_gives_what_the_single_products_give(n, width, inner, qkv):
+    """The four products between two attention kernels of a decode step (o projection into the stream, gate and up with
+    the gate, down into the stream, the next layer's q/k/v) as one persistent kernel, against the same products
+    launched one by one; twice in a row (the workspace and the counters must be as they were), with the same bits both
+    times; then shorter chains, one of them fed by a plain tensor."""
+    from inferrs_b200 import kernels as K
+    dtype, eps = torch.bfloat16, 1e-6
+    attn = rand((n, width), dtype, 100)
+    w_o, w_gu = rand((width, width), dtype, 101, scale=0.03), rand((2 * inner, width), dtype, 102, scale=0.03)
+    w_d, w_qkv = rand((width, inner), dtype, 103, scale=0.03), rand((qkv, width), dtype, 104, scale=0.03)
+    n1 = (1 + 0.1 * rand((width,), torch.float32, 105)).to(dtype)
+    n2 = (1 + 0.1 * rand((width,), torch.float32, 106)).to(dtype)
+    res0 = rand((n, width), torch.float32, 107)
+
+    def run(chained, products=4):
+        res = res0.clone()
+        o = torch.empty((n, width), dtype=dtype, device=dev())
+        a = torch.empty((n, inner), dtype=dtype, device=dev())
+        d = torch.empty((n, width), dtype=dtype, device=dev())
+        q = torch.full((n, qkv), float("nan"), dtype=dtype, device=dev())
+        chain = K.ProductChain() if chained else None
+        linear = chain.linear if chained else (lambda x, w, out, sink=None: K.linear(x, w, out, dtype, sink=sink))
+        gated = chain.gated_linear if chained else (lambda x, w, out: K.gated_linear(x, w, out, dtype))
+        before = K.launch_count()
+        s1 = linear(attn, w_o, o, sink=K.ResidualSink(res, n1, eps))
+        gated(s1, w_gu, a)
+        if products > 2:
+            s2 = linear(a, w_d, d, sink=K.ResidualSink(res, n2, eps))
+            linear(s2, w_qkv, q)
+        if chained:
+            chain.launch()
+        launches = K.launch_count() - before
+        torch.cuda.synchronize()
+        return res, q, a, launches
+
+    res_c, q_c, a_c, launches = run(True)
+    assert launches == 1 and K.gemm_chain_error() == 0
+    res_c2, q_c2, a_c2, _ = run(True)
+    assert torch.equal(res_c, res_c2) and torch.equal(q_c, q_c2) and torch.equal(a_c, a_c2)
+    res_s, q_s, a_s, launches = run(False)
+    assert launches == 4
+    assert K.gemm_chain_error() == 0 and K.gemm_tcgen05_error() == 0
+    assert rel_err(a_c, a_s) < 2e-2 and rel_err(res_c, res_s) < 1e-2
+    assert not torch.isnan(q_c.float()).any()
+    assert rel_err(q_c, q_s) < 2e-2
+    res_c, _, a_c, launches = run(True, products=2)
+    res_s, _, a_s, _ = run(False, products=2)
+    assert launches == 1 and K.gemm_chain_error() == 0
+    assert rel_err(a_c, a_s) < 2e-2 and rel_err(res_c, res_s) < 1e-2
+    # one product alone, from a plain tensor, and what a chain refuses
+    chain = K.ProductChain()
+    y = torch.empty((n, qkv), dtype=dtype, device=dev())
+    assert chain.linear(attn, w_qkv, y) is None
+    chain.launch()
+    y_s = torch.empty_like(y)
+    K.linear(attn, w_qkv, y_s, dtype)
+    assert K.gemm_chain_error() == 0 and rel_err(y, y_s) < 2e-2
+    with pytest.raises(K.KernelError):
+        chain.linear(attn[:, :width - 8], w_qkv, y)
+    with pytest.raises(K.KernelError):
+        K.ProductChain().linear(rand((17, width), dtype, 108), w_qkv, torch.empty((17, qkv), dtype=dtype, device=dev()))
