@@ -197,3 +197,54 @@ def test_the_steps_that_are_measured(long_setup):
     runner.release("long")
     runner.release("mid")
     runner.manager.check_invariants()
+
+
+# ---- the layer sizes of the other two checkpoints that are measured: Qwen3-0.6B (a narrow stream, two query heads per
+# key/value head, tied embeddings) and Qwen3-32B (eight query heads per key/value head, a wide feed-forward) ----------
+OTHER_SHAPES = {
+    "0.6b": dict(hidden_size=1024, num_attention_heads=16, num_key_value_heads=8, head_dim=128, intermediate_size=3072,
+                 tie_word_embeddings=True, num_hidden_layers=2),
+    "32b": dict(hidden_size=5120, num_attention_heads=64, num_key_value_heads=8, head_dim=128, intermediate_size=25600,
+                tie_word_embeddings=False, num_hidden_layers=1),
+}
+
+
+@pytest.mark.parametrize("shape", sorted(OTHER_SHAPES))
+def test_the_other_checkpoints_layer_sizes(shape):
+    """bfloat16, the whole vocabulary: a prompt of 300 tokens in two portions (the second beside another request's
+    first), then both requests decode eight tokens side by side; the last 32 places of the first prompt and every
+    decoded place against the plain implementation."""
+    dtype = torch.bfloat16
+    config = dict(CONFIG, **OTHER_SHAPES[shape])
+    rt = Runtime.cuda(dtype)
+    spec, weights, _ = random_model(config, 9, rt)
+    host = {k: v.float().cpu() for k, v in weights.items()}
+    n_a, n_b, n_dec = 300, 70, 8
+    a = random_tokens(n_a + n_dec, config["vocab_size"], seed=50)
+    b = random_tokens(n_b + n_dec, config["vocab_size"], seed=51)
+    want_a = plain_qwen3.forward(config, host, a, store=dtype, last=LAST + n_dec)
+    want_b = plain_qwen3.forward(config, host, b, store=dtype, last=n_dec + 1)
+    del host
+    runner = ModelRunner(spec, weights, rt, page_size=16, n_pages=(n_a + n_b + 2 * n_dec) // 16 + 4, max_requests=4)
+    runner.admit("a")
+    runner.admit("b")
+    runner.step([StepEntry("a", a[:200], [])])
+    got_a = []
+    out = runner.step([StepEntry("a", a[200:n_a], list(range(n_a - 200 - LAST, n_a - 200))),
+                       StepEntry("b", b[:n_b], [n_b - 1])])
+    got_a.append(out[:LAST])
+    got_b = [out[LAST:]]
+    for i in range(n_dec):
+        out = runner.step([StepEntry("a", a[n_a + i:n_a + i + 1], [0]), StepEntry("b", b[n_b + i:n_b + i + 1], [0])])
+        got_a.append(out[:1])
+        got_b.append(out[1:])
+    check(torch.cat(got_a), want_a, dtype, f"{shape}: the first request")
+    check(torch.cat(got_b), want_b, dtype, f"{shape}: the second request")
+    from inferrs_b200 import kernels
+    assert kernels.attention_decode_error() == 0 and kernels.gemm_tcgen05_error() == 0
+    assert kernels.attention_tcgen05_error() == 0 and kernels.attention_pair_tcgen05_error() == 0
+    runner.release("a")
+    runner.release("b")
+    runner.manager.check_invariants()
+    del runner, weights
+    torch.cuda.empty_cache()
