@@ -48,7 +48,7 @@ template <typename WT>
 __global__ void qk_norm_rope_store_kernel(
     const act_t* __restrict__ qkv, int row_stride, int n_heads, int n_kv_heads, int head_dim, int store_kv,
     const WT* __restrict__ q_weight, const WT* __restrict__ k_weight, float eps,
-    const float* __restrict__ cos_table, const float* __restrict__ sin_table, int rot_dim, int table_rows,
+    const float* __restrict__ cos_table, const float* __restrict__ sin_table, int rot_dim, int interleaved, int table_rows,
     const int* __restrict__ positions, const int* __restrict__ row_request,
     const int* __restrict__ block_table, int max_pages, int page_size, int n_pages,
     act_t* __restrict__ k_pages, act_t* __restrict__ v_pages, act_t* __restrict__ q_out) {
@@ -110,11 +110,13 @@ __global__ void qk_norm_rope_store_kernel(
         __syncwarp();
         const float* c = cos_table + (long)pos * half;
         const float* s = sin_table + (long)pos * half;
+        // element i of the first half turns with element i + rot_dim / 2, or (interleaved) element 2i with 2i + 1
         for (int j = lane; j < d; j += 32) {
             float o;
-            if (j < half) o = sh[j] * c[j] - sh[j + half] * s[j];
-            else if (j < rot_dim) o = sh[j - half] * s[j - half] + sh[j] * c[j - half];
-            else o = sh[j];
+            if (j >= rot_dim) o = sh[j];
+            else if (interleaved) o = (j & 1) ? sh[j - 1] * s[j >> 1] + sh[j] * c[j >> 1] : sh[j] * c[j >> 1] - sh[j + 1] * s[j >> 1];
+            else if (j < half) o = sh[j] * c[j] - sh[j + half] * s[j];
+            else o = sh[j - half] * s[j - half] + sh[j] * c[j - half];
             dst[j] = ib_from_float<act_t>(o);
         }
         __syncwarp();  // sh is overwritten by this warp's next head
@@ -340,7 +342,7 @@ __global__ void qk_norm_rope_store_d128_wide_kernel(
 IB_EXPORT int ib_qk_norm_rope_store(const void* qkv, int row_stride, int n_rows, int n_heads, int n_kv_heads,
                                     int head_dim, int store_kv, const void* q_weight, const void* k_weight,
                                     int weight_is_f32, float eps, const float* cos_table, const float* sin_table,
-                                    int rot_dim, int table_rows, const int* positions, const int* row_request,
+                                    int rot_dim, int interleaved, int table_rows, const int* positions, const int* row_request,
                                     const int* block_table, int max_pages, int page_size, int n_pages,
                                     void* k_pages, void* v_pages, void* q_out, cudaStream_t stream) {
     if (n_rows <= 0) return IB_OK;
@@ -352,7 +354,7 @@ IB_EXPORT int ib_qk_norm_rope_store(const void* qkv, int row_stride, int n_rows,
     const int heads_total = n_heads + (store_kv ? 2 * n_kv_heads : 0);
     const dim3 grid(n_rows, (heads_total + QRS_WARPS - 1) / QRS_WARPS);
 #if IB_ACT_BF16
-    if (head_dim == 128 && rot_dim == 128 && (row_stride % 4) == 0 && ((uintptr_t)qkv % 8) == 0 &&
+    if (head_dim == 128 && rot_dim == 128 && !interleaved && (row_stride % 4) == 0 && ((uintptr_t)qkv % 8) == 0 &&
         ((uintptr_t)cos_table % 16) == 0 && ((uintptr_t)sin_table % 16) == 0) {
 #define IB_LAUNCH_D128(WT, HPW)                                                                                    \
     ib_launch(qk_norm_rope_store_d128_kernel<WT, HPW>, dim3(n_rows, (heads_total + QRS_WARPS * HPW - 1) / (QRS_WARPS * HPW)), \
@@ -387,12 +389,12 @@ IB_EXPORT int ib_qk_norm_rope_store(const void* qkv, int row_stride, int n_rows,
     if (weight_is_f32)
         ib_launch(qk_norm_rope_store_kernel<float>, grid, 32 * QRS_WARPS, smem, stream,
             (const act_t*)qkv, row_stride, n_heads, n_kv_heads, head_dim, store_kv, (const float*)q_weight,
-            (const float*)k_weight, eps, cos_table, sin_table, rot_dim, table_rows, positions, row_request, block_table,
+            (const float*)k_weight, eps, cos_table, sin_table, rot_dim, interleaved, table_rows, positions, row_request, block_table,
             max_pages, page_size, n_pages, (act_t*)k_pages, (act_t*)v_pages, (act_t*)q_out);
     else
         ib_launch(qk_norm_rope_store_kernel<__nv_bfloat16>, grid, 32 * QRS_WARPS, smem, stream,
             (const act_t*)qkv, row_stride, n_heads, n_kv_heads, head_dim, store_kv, (const __nv_bfloat16*)q_weight,
-            (const __nv_bfloat16*)k_weight, eps, cos_table, sin_table, rot_dim, table_rows, positions, row_request,
+            (const __nv_bfloat16*)k_weight, eps, cos_table, sin_table, rot_dim, interleaved, table_rows, positions, row_request,
             block_table,
             max_pages, page_size, n_pages, (act_t*)k_pages, (act_t*)v_pages, (act_t*)q_out);
     return ib_launch_status();

@@ -34,7 +34,7 @@ _SIGNATURES = {
     "ib_silu_gate": [c_void_p, c_void_p, c_int, c_int, c_void_p],
     "ib_act_to_float": [c_void_p, c_void_p, c_long, c_void_p],
     "ib_qk_norm_rope_store": [c_void_p, c_int, c_int, c_int, c_int, c_int, c_int, c_void_p, c_void_p, c_int, c_float,
-                              c_void_p, c_void_p, c_int, c_int, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int,
+                              c_void_p, c_void_p, c_int, c_int, c_int, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int,
                               c_void_p, c_void_p, c_void_p, c_void_p],
     "ib_paged_attention_generic": [c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_void_p, c_void_p,
                                    c_int, c_int, c_int, c_int, c_float, c_int, c_void_p, c_void_p],
@@ -249,8 +249,10 @@ def qk_norm_rope_store(qkv: torch.Tensor, n_heads: int, n_kv_heads: int, head_di
                        q_weight: Optional[torch.Tensor], k_weight: Optional[torch.Tensor], eps: float,
                        cos: Optional[torch.Tensor], sin: Optional[torch.Tensor], rot_dim: int,
                        positions: torch.Tensor, row_request: torch.Tensor, block_table: Optional[torch.Tensor],
-                       k_pages: Optional[torch.Tensor], v_pages: Optional[torch.Tensor], q_out: torch.Tensor):
-    """Per-head norm of q and k, rotation by position, q to ``q_out``, k and v into their pages.
+                       k_pages: Optional[torch.Tensor], v_pages: Optional[torch.Tensor], q_out: torch.Tensor,
+                       interleaved: bool = False):
+    """Per-head norm of q and k, rotation by position, q to ``q_out``, k and v into their pages.  Element ``i`` of
+    a head's first ``rot_dim / 2`` turns with element ``i + rot_dim / 2``; ``interleaved``: element ``2i`` with ``2i + 1``.
 
     qkv [N, (n_heads + 2 n_kv_heads) * d] (queries only when ``store_kv`` is False);
     pages [n_pages, n_kv_heads, page_size, d]; block_table int32 [R, max_pages].
@@ -294,7 +296,7 @@ def qk_norm_rope_store(qkv: torch.Tensor, n_heads: int, n_kv_heads: int, head_di
     _check(_core(act).ib_qk_norm_rope_store(
         _p(qkv), cols, n, n_heads, n_kv_heads, head_dim, int(store_kv), _p(q_weight), _p(k_weight),
         int(wdt == torch.float32), float(eps), _p(cos) if rot_dim else None, _p(sin) if rot_dim else None, rot_dim,
-        table_rows, _p(positions), _p(row_request), _p(block_table) if store_kv else None, max_pages, page_size,
+        int(bool(interleaved)), table_rows, _p(positions), _p(row_request), _p(block_table) if store_kv else None, max_pages, page_size,
         n_pages, _p(k_pages) if store_kv else None, _p(v_pages) if store_kv else None, _p(q_out), _stream()),
         "qk_norm_rope_store")
 

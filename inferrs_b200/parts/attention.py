@@ -76,7 +76,9 @@ class Attention:
         if self.q_weight is not None and self.k_weight is not None and self.q_weight.dtype != self.k_weight.dtype:
             self.q_weight, self.k_weight = self.q_weight.float(), self.k_weight.float()
         self.eps = (spec.q_norm or spec.k_norm).eps if (spec.q_norm or spec.k_norm) else 0.0
-        self.cos, self.sin, self.rot_dim = build_position(spec.position, rt).tables()
+        position = build_position(spec.position, rt)
+        self.cos, self.sin, self.rot_dim = position.tables()
+        self.interleaved = bool(getattr(position, "interleaved", False))   # which elements of a head turn together
         if self.rot_dim > spec.head_dim:
             raise ValueError(f"rot_dim {self.rot_dim} exceeds head_dim {spec.head_dim}")
 
@@ -97,7 +99,7 @@ class Attention:
         q = torch.empty((n, s.n_heads, s.head_dim), dtype=self.rt.dtype, device=h.device)
         kernels.qk_norm_rope_store(qkv, s.n_heads, s.n_kv_heads, s.head_dim, s.own_kv, self.q_weight, self.k_weight,
                                    self.eps, self.cos, self.sin, self.rot_dim, ctx.positions, ctx.row_request,
-                                   table, k_pages, v_pages, q)
+                                   table, k_pages, v_pages, q, interleaved=self.interleaved)
         out = torch.empty((n, s.n_heads * s.head_dim), dtype=self.rt.dtype, device=h.device)
         kernels.paged_attention(q, k_pages, v_pages, table, ctx, s.scale, s.window, out)
         return self.o(out, sink=sink)

@@ -100,6 +100,12 @@ class RotarySplitHalf:
         return self.cos, self.sin, self.spec.rot_dim
 
 
+class RotaryInterleaved(RotarySplitHalf):
+    """The same tables; element 2i of a head is rotated with element 2i + 1."""
+
+    interleaved = True
+
+
 class NoPosition:
     def __init__(self, spec: PositionSpec, rt: Runtime):
         self.spec = spec
@@ -109,6 +115,7 @@ class NoPosition:
 
 
 register_position("rotary_split_half", RotarySplitHalf)
+register_position("rotary_interleaved", RotaryInterleaved)
 register_position("none", NoPosition)
 
 

@@ -23,7 +23,8 @@ norm
     the activation dtype (used where a description puts a norm on a sub-layer's output).
 position encoding
     ``__init__(spec, rt)``, ``tables() -> (cos, sin, rot_dim)``: float32 ``[max_positions, rot_dim/2]``
-    tables that the attention kernels index by position (``rot_dim`` 0: no rotation).
+    tables that the rotation kernel indexes by position (``rot_dim`` 0: no rotation).  Optional attribute
+    ``interleaved = True``: element ``2i`` of a head turns with ``2i + 1`` instead of ``i`` with ``i + rot_dim/2``.
 arrangement
     ``__init__(spec, sublayers)`` with ``spec`` the layer's :class:`~inferrs_b200.parts.spec.LayerSpec` and
     ``sublayers`` its built sub-layers in order (:class:`~inferrs_b200.parts.blocks.BuiltSubLayer`: ``category``,

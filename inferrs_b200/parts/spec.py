@@ -43,6 +43,7 @@ class PositionSpec:
     """Rotation of the first ``rot_dim`` elements of each head by position.
 
     ``kind="rotary_split_half"`` pairs element ``i`` with ``i + rot_dim/2``;
+    ``kind="rotary_interleaved"`` pairs element ``2i`` with ``2i + 1``;
     ``kind="none"`` leaves heads as they are.
     """
 

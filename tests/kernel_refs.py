@@ -63,16 +63,21 @@ def _rms(x, w, eps):
     return x / torch.sqrt((x * x).mean(dim=-1, keepdim=True) + eps) * w.float()
 
 
-def _rotate(x, cos, sin, rot_dim):
+def _rotate(x, cos, sin, rot_dim, interleaved=False):
     # x [rows, heads, d]; cos/sin [rows, rot_dim/2]
     half = rot_dim // 2
+    if interleaved:
+        x1, x2, rest = x[..., 0:rot_dim:2], x[..., 1:rot_dim:2], x[..., rot_dim:]
+        c, s = cos[:, None, :], sin[:, None, :]
+        turned = torch.stack([x1 * c - x2 * s, x1 * s + x2 * c], dim=-1).flatten(-2)
+        return torch.cat([turned, rest], dim=-1)
     x1, x2, rest = x[..., :half], x[..., half:rot_dim], x[..., rot_dim:]
     c, s = cos[:, None, :], sin[:, None, :]
     return torch.cat([x1 * c - x2 * s, x1 * s + x2 * c, rest], dim=-1)
 
 
 def qk_norm_rope_store(qkv, n_heads, n_kv_heads, head_dim, store_kv, q_weight, k_weight, eps, cos, sin, rot_dim,
-                       positions, row_request, block_table, k_pages, v_pages, q_out):
+                       positions, row_request, block_table, k_pages, v_pages, q_out, interleaved=False):
     n = qkv.shape[0]
     d = head_dim
     x = qkv.float()
@@ -81,7 +86,7 @@ def qk_norm_rope_store(qkv, n_heads, n_kv_heads, head_dim, store_kv, q_weight, k
     if q_weight is not None:
         q = _rms(q, q_weight, eps)
     if rot_dim:
-        q = _rotate(q, cos[pos], sin[pos], rot_dim)
+        q = _rotate(q, cos[pos], sin[pos], rot_dim, interleaved)
     q_out.copy_(q.to(q_out.dtype))
     if not store_kv:
         return
@@ -90,7 +95,7 @@ def qk_norm_rope_store(qkv, n_heads, n_kv_heads, head_dim, store_kv, q_weight, k
     if k_weight is not None:
         k = _rms(k, k_weight, eps)
     if rot_dim:
-        k = _rotate(k, cos[pos], sin[pos], rot_dim)
+        k = _rotate(k, cos[pos], sin[pos], rot_dim, interleaved)
     page_size = k_pages.shape[2]
     for r in range(n):
         p = int(positions[r])

@@ -188,6 +188,32 @@ def _paged_setup(dtype, n_kv, d, page_size, lens, new, seed, n_pages=None):
 
 
 @pytest.mark.parametrize("dtype", DTYPES)
+@pytest.mark.parametrize("nh,nkv,d,rot,ps", [(6, 3, 48, 48, 8), (4, 4, 16, 8, 4), (8, 2, 128, 128, 16), (5, 1, 128, 64, 16)])
+def test_qk_norm_rope_store_with_neighbours_turning_together(dtype, nh, nkv, d, rot, ps):
+    """The other pairing: element 2i of a head turns with element 2i + 1 (head size 128 too, which has kernels of its
+    own for the pairing by halves only)."""
+    from inferrs_b200 import kernels as K
+    lens, new = [21, 9, 40], [5, 9, 1]
+    table, positions, row_request, k_pages, v_pages = _paged_setup(dtype, nkv, d, ps, lens, new, 17)
+    n = sum(new)
+    qkv = rand((n, (nh + 2 * nkv) * d), dtype, 18)
+    wq = (1 + 0.1 * rand((d,), torch.float32, 19)).to(dtype)
+    wk = (1 + 0.1 * rand((d,), torch.float32, 20)).to(dtype)
+    ang = torch.arange(64, dtype=torch.float32)[:, None] * (1.0 / 10000 ** (torch.arange(rot // 2) * 2.0 / rot))[None]
+    cos, sin = torch.cos(ang).to(dev()), torch.sin(ang).to(dev())
+    k1, v1, k2, v2 = k_pages.clone(), v_pages.clone(), k_pages.clone(), v_pages.clone()
+    q1 = torch.empty((n, nh, d), dtype=dtype, device=dev())
+    q2, q3 = torch.empty_like(q1), torch.empty_like(q1)
+    K.qk_norm_rope_store(qkv, nh, nkv, d, True, wq, wk, 1e-5, cos, sin, rot, positions, row_request, table, k1, v1, q1,
+                         interleaved=True)
+    R.qk_norm_rope_store(qkv, nh, nkv, d, True, wq, wk, 1e-5, cos, sin, rot, positions, row_request, table, k2, v2, q2,
+                         interleaved=True)
+    assert rel_err(q1, q2) < TOL[dtype] and rel_err(k1, k2) < TOL[dtype] and torch.equal(v1, v2)
+    R.qk_norm_rope_store(qkv, nh, nkv, d, True, wq, wk, 1e-5, cos, sin, rot, positions, row_request, table, k2, v2, q3)
+    assert rel_err(q1, q3) > 10 * TOL[dtype], "the two pairings were meant to differ"
+
+
+@pytest.mark.parametrize("dtype", DTYPES)
 @pytest.mark.parametrize("nh,nkv,d,rot,ps", [(6, 3, 48, 48, 8), (4, 4, 16, 8, 4), (8, 2, 128, 128, 16), (3, 1, 80, 0, 16)])
 def test_qk_norm_rope_store(dtype, nh, nkv, d, rot, ps):
     from inferrs_b200 import kernels as K

@@ -161,18 +161,30 @@ class ToyScaledRotary:
         return self.cos, self.sin, self.rot_dim
 
 
-def plain_partial_rope(x, cos, sin, rot_dim):
+class ToyInterleavedRotary(ToyScaledRotary):
+    """The same tables, but element 2i of a head turns with element 2i + 1 (the attribute is all it takes)."""
+    interleaved = True
+
+
+def plain_partial_rope(x, cos, sin, rot_dim, interleaved=False):
+    if interleaved:
+        x1, x2, rest = x[..., 0:rot_dim:2], x[..., 1:rot_dim:2], x[..., rot_dim:]
+        turned = torch.stack([x1 * cos - x2 * sin, x1 * sin + x2 * cos], dim=-1).flatten(-2)
+        return torch.cat([turned, rest], dim=-1)
     half = rot_dim // 2
     x1, x2, rest = x[..., :half], x[..., half:rot_dim], x[..., rot_dim:]
     return torch.cat([x1 * cos - x2 * sin, x1 * sin + x2 * cos, rest], dim=-1)
 
 
+@pytest.mark.parametrize("interleaved", [False, True], ids=["halves", "interleaved"])
 @pytest.mark.parametrize("dtype,cfg", [(torch.float32, CONFIG_B), (torch.bfloat16, CONFIG_C)])
-def test_another_position_encoding_is_registered_built_and_stepped(dtype, cfg):
+def test_another_position_encoding_is_registered_built_and_stepped(dtype, cfg, interleaved):
     register_position("toy_scaled_rotary", ToyScaledRotary, replace=True)
+    register_position("toy_interleaved_rotary", ToyInterleavedRotary, replace=True)
     spec, _ = spec_from_config(cfg)
     d = cfg["head_dim"]
-    toy = ToyScaledRotarySpec(rot_dim=d // 2, theta=500.0, max_positions=cfg["max_position_embeddings"], factor=4.0)
+    toy = ToyScaledRotarySpec(rot_dim=d // 2, theta=500.0, max_positions=cfg["max_position_embeddings"], factor=4.0,
+                              kind="toy_interleaved_rotary" if interleaved else "toy_scaled_rotary")
     layers = tuple(l.with_part("mixer", dataclasses.replace(l.mixer, position=toy)) for l in spec.layers)
     spec = dataclasses.replace(spec, layers=layers)
     rt = Runtime.cuda(dtype)
@@ -195,8 +207,8 @@ def test_another_position_encoding_is_registered_built_and_stepped(dtype, cfg):
         q = rnd(P.linear(h, w[f"{p}.self_attn.q_proj.weight"])).reshape(t, nh, d).transpose(0, 1)
         k = rnd(P.linear(h, w[f"{p}.self_attn.k_proj.weight"])).reshape(t, nkv, d).transpose(0, 1)
         v = rnd(P.linear(h, w[f"{p}.self_attn.v_proj.weight"])).reshape(t, nkv, d).transpose(0, 1)
-        q = rnd(plain_partial_rope(P.rms_norm(q, w[f"{p}.self_attn.q_norm.weight"], eps), cos, sin, toy.rot_dim))
-        k = rnd(plain_partial_rope(P.rms_norm(k, w[f"{p}.self_attn.k_norm.weight"], eps), cos, sin, toy.rot_dim))
+        q = rnd(plain_partial_rope(P.rms_norm(q, w[f"{p}.self_attn.q_norm.weight"], eps), cos, sin, toy.rot_dim, interleaved))
+        k = rnd(plain_partial_rope(P.rms_norm(k, w[f"{p}.self_attn.k_norm.weight"], eps), cos, sin, toy.rot_dim, interleaved))
         o = rnd(P.causal_attention(q, k, v, 1.0 / math.sqrt(d)))
         x = x + rnd(P.linear(o, w[f"{p}.self_attn.o_proj.weight"]))
         h = rnd(P.rms_norm(x, w[f"{p}.post_attention_layernorm.weight"], eps))
