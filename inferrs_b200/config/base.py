@@ -12,7 +12,7 @@ from __future__ import annotations
 import json
 import os
 from dataclasses import dataclass
-from typing import Any, Callable, Dict, List, Optional
+from typing import Any, Callable, Dict, List, Optional, Tuple
 
 
 class ConfigError(ValueError):
@@ -130,3 +130,29 @@ def resolve_architecture(raw: RawConfig) -> Architecture:
         f"{raw.source}: unsupported model architecture (architectures={names!r}, model_type={mt!r}); "
         f"registered: {registered_architectures()}"
     )
+
+
+def generation_eos_ids(model_dir: str, vocab_size: int) -> Tuple[int, ...]:
+    """The ``eos_token_id`` (one id or a list) of ``generation_config.json`` in a model folder; () if there is no such
+    file or no such key.  Checkpoints name there the ids that end a turn beside config.json's own end-of-text id.  (The
+    reference takes its stop ids from the tokenizer's files, inferrs/src/tokenizer.rs:329-353; this engine reads no
+    tokenizer, so the two JSON files and the request's own list are where stop ids come from.)"""
+    path = os.path.join(model_dir, "generation_config.json")
+    if not os.path.isfile(path):
+        return ()
+    with open(path, "r", encoding="utf-8") as f:
+        try:
+            values = json.load(f)
+        except json.JSONDecodeError as e:
+            raise ConfigError(f"{path}: not valid JSON: {e}") from e
+    v = values.get("eos_token_id") if isinstance(values, dict) else None
+    if v is None:
+        return ()
+    ids = [v] if isinstance(v, int) and not isinstance(v, bool) else v
+    if not isinstance(ids, list) or any(isinstance(t, bool) or not isinstance(t, int) for t in ids):
+        raise ConfigError(f"{path}: eos_token_id must be an integer or a list of integers, got {v!r}")
+    for t in ids:
+        if not 0 <= t < vocab_size:
+            raise ConfigError(f"{path}: eos_token_id {t} is outside the vocabulary of {vocab_size}")
+    return tuple(ids)
+

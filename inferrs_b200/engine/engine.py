@@ -13,6 +13,7 @@ from typing import Dict, Hashable, List, Optional, Sequence, Union
 
 import torch
 
+from ..config.base import generation_eos_ids
 from ..runtime import Runtime, parse_dtype
 from ..sampling.params import SamplingParams
 from ..sampling.sampler import Sampler
@@ -61,6 +62,11 @@ class Engine:
         else:
             raise ValueError("give a model_dir, or a config dictionary with a random_weights seed")
         self.spec, self.config = spec, cfg
+        # what ends a request by itself: config.json's ids and, from a model folder, generation_config.json's
+        eos = tuple(spec.eos_token_ids)
+        if model_dir is not None:
+            eos += tuple(t for t in generation_eos_ids(model_dir, spec.vocab_size) if t not in eos)
+        self.eos_token_ids = eos
         self.max_seq_len = min(max_seq_len, spec.max_positions) if max_seq_len else spec.max_positions
         # the cache is sized (num_blocks None) once the model stands and the tensors that were fused into others
         # have been given back: only then does the free memory say what is left
@@ -69,7 +75,7 @@ class Engine:
                                   cache_fraction=paged_attention, consume_weights=True)
         del weights
         self.scheduler = Scheduler(self.runner.manager, max_batch_size, max_tokens_per_step, self.max_seq_len,
-                                   spec.eos_token_ids, prefill_chunk,
+                                   self.eos_token_ids, prefill_chunk,
                                    on_admit=lambda rid, slot: self.runner.storage.clear_slot(slot))
         self.sampler = Sampler(self.rt.device, self.rt.dtype)
         self._ids = itertools.count()

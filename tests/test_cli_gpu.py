@@ -74,3 +74,27 @@ def test_the_cache_is_sized_from_the_memory_that_is_free_once_the_model_stands()
     assert len(out[0]) == 4
     del eng
     torch.cuda.empty_cache()
+
+
+def test_generation_config_in_the_model_folder_ends_requests(tmp_path):
+    """A model folder whose generation_config.json names an id that ends a turn: generation through the entry point
+    stops there, although config.json does not name it."""
+    from inferrs_b200 import Engine, SamplingParams
+    from inferrs_b200.weights.random_init import write_random_model
+    cfg = {k: v for k, v in CONFIG_D.items() if k != "eos_token_id"}
+    folder = str(tmp_path / "model")
+    write_random_model(folder, cfg, seed=12, dtype=torch.float32)
+    prompt = random_tokens(30, cfg["vocab_size"], seed=2)
+    kw = dict(dtype="f32", block_size=16, num_blocks=16, max_batch_size=2)
+    def params(**more):     # sampled, so that the tokens differ from one another; seeded, so that they come again
+        return SamplingParams(temperature=1.5, seed=5, max_tokens=10, **more)
+
+    free = Engine(folder, **kw).generate([prompt], params())[0]
+    assert len(free) == 10
+    stop_at = next(i for i in range(2, 10) if free[i] not in free[:i])     # a token that has not come before
+    with open(os.path.join(folder, "generation_config.json"), "w") as f:
+        json.dump({"eos_token_id": [free[stop_at], cfg["vocab_size"] - 1], "temperature": 0.6}, f)
+    eng = Engine(folder, **kw)
+    assert free[stop_at] in eng.eos_token_ids
+    assert eng.generate([prompt], params())[0] == free[:stop_at + 1]
+    assert eng.generate([prompt], params(ignore_eos=True))[0] == free

@@ -144,3 +144,19 @@ def test_sharded_files_later_wins(tmp_path):
     write_safetensors(os.path.join(d, "model-00002-of-00002.safetensors"), [(n, tensors[n]) for n in names[8:]])
     w = load_weights(d, _decls(CONFIG_A), torch.bfloat16)
     assert all(torch.equal(w[n], tensors[n]) for n in names)
+
+
+def test_generation_config_names_more_ids_that_end_a_request(tmp_path):
+    from inferrs_b200.config.base import ConfigError, generation_eos_ids
+    d = str(tmp_path)
+    assert generation_eos_ids(d, 100) == ()                       # no such file
+    (tmp_path / "generation_config.json").write_text('{"temperature": 0.6}')
+    assert generation_eos_ids(d, 100) == ()                       # no such key
+    (tmp_path / "generation_config.json").write_text('{"eos_token_id": 7}')
+    assert generation_eos_ids(d, 100) == (7,)
+    (tmp_path / "generation_config.json").write_text('{"eos_token_id": [7, 45]}')
+    assert generation_eos_ids(d, 100) == (7, 45)
+    for bad in ('{"eos_token_id": [7, 100]}', '{"eos_token_id": "7"}', '{"eos_token_id": [true]}', '{"eos_token_id": '):
+        (tmp_path / "generation_config.json").write_text(bad)
+        with pytest.raises(ConfigError):
+            generation_eos_ids(d, 100)
