@@ -9,6 +9,9 @@ inferrs/src/bench.rs:21-38 ``bench``).  The model is a local folder (the referen
     python -m inferrs_b200 run MODEL_DIR --prompt-ids 1,2,3 --max-tokens 32 --temperature 0
     python -m inferrs_b200 run CONFIG.json --random-weights 0 --random-prompt 64 --ignore-eos --max-tokens 32
     python -m inferrs_b200 bench MODEL_DIR --prompt-len 128 --max-tokens 128
+    python -m inferrs_b200 replay --model MODEL_DIR --dtype bfloat16 --out DIR --max-tokens 256 < steps.jsonl
+
+(``replay`` is the trace replay program, ``bin/trace_run``, under this command's roof: ``engine/trace.py``.)
 
 Beyond the reference's options: ``--prefill-chunk`` (the most tokens of one prompt in a step), ``--ignore-eos``,
 ``--min-p``, ``--random-weights SEED`` (the model argument is then a config.json, or a folder with one, and the
@@ -169,6 +172,11 @@ def cmd_bench(args) -> int:
 
 
 def main(argv: Optional[List[str]] = None) -> int:
+    argv = list(sys.argv[1:] if argv is None else argv)
+    if argv[:1] == ["replay"]:
+        # the trace replay program under this command's roof: the same options as bin/trace_run, steps on standard input
+        from .engine.trace import main as replay
+        return replay(argv[1:])
     ap = argparse.ArgumentParser(prog="inferrs_b200", description=__doc__,
                                  formatter_class=argparse.RawDescriptionHelpFormatter)
     sub = ap.add_subparsers(dest="command", required=True)

@@ -104,3 +104,20 @@ def test_a_step_that_does_not_fit_ends_the_replay_with_a_status(model_dirs, tmp_
     assert out.split("\n")[0] == "done 0" and "done 1" not in out
     assert "trace_run: step 1:" in err and "Traceback" not in err
     assert sorted(os.listdir(out_dir)) == ["0.f32"]
+
+
+def test_the_replay_subcommand_is_the_same_program(model_dirs, tmp_path):
+    """``python -m inferrs_b200 replay`` takes the options and the steps of ``bin/trace_run`` and writes the same bytes."""
+    toks = random_tokens(24, CONFIG_A["vocab_size"], seed=3)
+    steps = [{"step": 0, "entries": [{"id": "a", "tokens": toks[:17], "want": [16]}], "end": []},
+             {"step": 1, "entries": [{"id": "a", "tokens": toks[17:], "want": [0, 6]}], "end": ["a"]}]
+    one, two = str(tmp_path / "one"), str(tmp_path / "two")
+    replay(model_dirs["A"], "float32", steps, one, max_tokens=64)
+    p = subprocess.run([sys.executable, "-m", "inferrs_b200", "replay", "--model", model_dirs["A"], "--dtype", "float32",
+                        "--out", two, "--max-tokens", "64"], input="".join(json.dumps(s) + "\n" for s in steps),
+                       capture_output=True, text=True, timeout=300, cwd=ROOT)
+    assert p.returncode == 0, p.stderr[-500:]
+    assert p.stdout.split() == ["done", "0", "done", "1"]
+    for name in ("0.f32", "1.f32"):
+        with open(os.path.join(one, name), "rb") as a, open(os.path.join(two, name), "rb") as b:
+            assert a.read() == b.read()
