@@ -98,3 +98,27 @@ def test_generation_config_in_the_model_folder_ends_requests(tmp_path):
     assert free[stop_at] in eng.eos_token_ids
     assert eng.generate([prompt], params())[0] == free[:stop_at + 1]
     assert eng.generate([prompt], params(ignore_eos=True))[0] == free
+
+
+def test_a_seed_gives_the_same_weights_on_the_host_and_on_the_device(tmp_path):
+    """A model folder written from a seed and a model made on the device from the same seed are the same model: the
+    engine gives the same logits either way, bit for bit."""
+    from inferrs_b200 import Engine
+    from inferrs_b200.engine.batch import StepEntry
+    from inferrs_b200.parts.spec import TensorDecl
+    from inferrs_b200.weights.random_init import random_tensor, write_random_model
+    for init in ("normal", "norm"):
+        decl = TensorDecl("a.weight", (300, 129), init=init)
+        host = random_tensor(decl, 0, 11, torch.float32)
+        device = random_tensor(decl, 0, 11, torch.float32, torch.device("cuda"))
+        assert torch.equal(host, device.cpu())
+    folder = str(tmp_path / "model")
+    write_random_model(folder, CONFIG_D, seed=21, dtype=torch.bfloat16)
+    toks = random_tokens(40, CONFIG_D["vocab_size"], seed=6)
+    kw = dict(dtype="bf16", block_size=16, num_blocks=16, max_batch_size=2)
+    logits = []
+    for eng in (Engine(folder, **kw), Engine(config=CONFIG_D, random_weights=21, **kw)):
+        eng.runner.admit("a")
+        logits.append(eng.runner.step([StepEntry("a", toks, list(range(len(toks))))]).clone())
+        eng.runner.release("a")
+    assert torch.equal(logits[0], logits[1])

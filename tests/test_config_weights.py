@@ -131,6 +131,21 @@ def test_random_weights_are_seeded(tmp_path):
     assert abs(float(w["model.embed_tokens.weight"].std()) - 0.02) < 0.002
     n = w["model.layers.0.input_layernorm.weight"]
     assert 0.9 <= float(n.min()) and float(n.max()) <= 1.1 and float(n.std()) > 0.01
+    # a value depends on the seed, the tensor's name and the element's index only: not on the tensor's place in the
+    # declaration, and not on how many elements are made at a time
+    from inferrs_b200.parts.spec import TensorDecl
+    from inferrs_b200.weights import random_init
+    decl = TensorDecl("some.weight", (37, 53))
+    one = random_init.random_tensor(decl, 0, 9, torch.float32)
+    assert torch.equal(one, random_init.random_tensor(decl, 5, 9, torch.float32))
+    whole = random_init._CHUNK
+    try:
+        random_init._CHUNK = 100
+        assert torch.equal(one, random_init.random_tensor(decl, 0, 9, torch.float32))
+    finally:
+        random_init._CHUNK = whole
+    other = random_init.random_tensor(TensorDecl("some.other.weight", (37, 53)), 0, 9, torch.float32)
+    assert abs(float((one * other).mean()) / float(one.std() * other.std())) < 0.1
 
 
 def test_sharded_files_later_wins(tmp_path):
