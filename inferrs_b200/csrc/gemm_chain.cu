@@ -122,9 +122,9 @@ __global__ void __launch_bounds__(THREADS, 1) chain_kernel(const __grid_constant
     const unsigned full0 = smem_u32(bars), empty0 = smem_u32(bars + STAGES);
     const unsigned accf0 = smem_u32(bars + 2 * STAGES), acce0 = smem_u32(bars + 2 * STAGES + 2);
     unsigned* tmem_slot = reinterpret_cast<unsigned*>(bars + 2 * STAGES + 4);
-    float* fold = reinterpret_cast<float*>(bars + 2 * STAGES + 5);
+    float* fold = reinterpret_cast<float*>(bars + 2 * STAGES + 5);   // [4][SSQ_LD] partial sums, [SSQ_LD] row scales
     float* own_head = fold + 5 * SSQ_LD;      // this CTA's own slice of the tile it finishes last, [token][row]
-    float* own_whole = own_head + SLOT;       // a tile that this CTA computes alone   // [4][SSQ_LD] partial sums, [SSQ_LD] row scales
+    float* own_whole = own_head + SLOT;       // a tile that this CTA computes alone
 
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const int cta = blockIdx.x, grid = gridDim.x;

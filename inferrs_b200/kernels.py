@@ -1045,7 +1045,10 @@ def gemm_tcgen05_error(reset: bool = True) -> int:
 
 def gemm_chain_error(reset: bool = True) -> int:
     """0, or the code of the first bounded wait that ran out in a chain of products (synchronises)."""
-    return _gemm_lib().ib_gemm_chain_error(int(reset))
+    code = _gemm_lib().ib_gemm_chain_error(int(reset))
+    if code != 0 and reset:
+        _CHAIN_WS.clear()    # a chain that gave up may have left marks in its workspace: the next chain gets a fresh one
+    return code
 
 
 # ---- the kernels' error words, all of them ------------------------------------------------------------------
