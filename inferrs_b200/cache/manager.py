@@ -80,7 +80,7 @@ def host_library():
             "ibh_cache_check": [p, ctypes.c_char_p, i],
             "ibh_cache_fit_in_order": [p, i, p, p, p],
             "ibh_describe_decode": [p, i, p, p, i, p, i, i, p, i, p],
-            "ibh_describe_step": [p, i, p, p, p, p, p, i, i, i, p, i, p, p, i, i, p, i, p],
+            "ibh_describe_step": [p, i, p, p, p, p, p, i, i, i, p, i, p, p, i, i, i, p, i, p],
             "ibh_sched_add": [p, l, i, i, i, p, i], "ibh_sched_abort": [p, l],
             "ibh_sched_plan": [p, i, i, p, p, p, p, p, p, p, p, p],
             "ibh_sched_advance": [p, i, p, p, p], "ibh_sched_deliver": [p, i, p, p, p],
@@ -300,10 +300,11 @@ class CacheManager:
 
     def describe_step(self, rids: Sequence[Hashable], tokens: Sequence[Sequence[int]], wants: Sequence[Sequence[int]],
                       pad_rows: int, pad_requests: int, pad_wanted: int, fixed_pages: Sequence[int],
-                      tile_sizes: Sequence[tuple], vocab_size: int, max_positions: int, out_ptr: int, cap: int):
+                      tile_sizes: Sequence[tuple], tile_pad: int, vocab_size: int, max_positions: int, out_ptr: int,
+                      cap: int):
         """The same for a step of any portions, padded to ``pad_rows`` rows, ``pad_requests`` requests and
         ``pad_wanted`` wanted places, with a tile list of fixed length for every (tokens per tile, portions only)
-        pair: the layout of ``build_context(..., pad_rows=...)``.  Returns (numbers written, 0) or (a negative
+        pair (room for ``pad_rows // tokens + tile_pad`` tiles): the layout of ``build_context(..., pad_rows=...)``.  Returns (numbers written, 0) or (a negative
         refusal, index of the entry it is about)."""
         import numpy as np
         n = len(rids)
@@ -322,5 +323,5 @@ class CacheManager:
         bad = ctypes.c_int(0)
         code = self._lib.ibh_describe_step(self._h, n, handles, n_tok, flat.ctypes.data, n_want, flat_w.ctypes.data,
                                            pad_rows, pad_requests, pad_wanted, pages, k, tile_tokens, tile_portions,
-                                           vocab_size, max_positions, out_ptr, cap, ctypes.byref(bad))
+                                           tile_pad, vocab_size, max_positions, out_ptr, cap, ctypes.byref(bad))
         return code, bad.value

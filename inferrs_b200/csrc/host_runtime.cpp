@@ -376,15 +376,19 @@ IBH_EXPORT int ibh_describe_decode(void* h, int n, const int64_t* rids, const in
 // Request i brings n_tok[i] tokens (concatenated in `tokens`) and wants the logits at n_want[i] of its places
 // (concatenated in `wants`).  The rows that fill the step up belong to one more request without pages, at position
 // 0; the requests after it are empty.  -1 marks table entries, tiles and single-token places that are not there.
-// A tile size with tile_portions[k] != 0 leaves the single-token requests out.  The pages for the step's tokens are
-// reserved already.  Returns the count of numbers written, or an error with the offending entry in *bad.
+// A tile size with tile_portions[k] != 0 leaves the single-token requests out.  A tile list has room for
+// pad_rows / tile_tokens[k] + tile_pad tiles (tile_pad: the most requests that may bring tiles); the tiles stand at its
+// end, the one that sees the fewest keys first (the attention kernels start at the end: the longest tile first, the
+// places without a tile last).  The pages for the step's tokens are reserved already.  Returns the count of numbers
+// written, or an error with the offending entry in *bad.
 IBH_EXPORT int ibh_describe_step(void* h, int n, const int64_t* rids, const int* n_tok, const int* tokens,
                                  const int* n_want, const int* wants, int pad_rows, int pad_requests, int pad_wanted,
                                  const int* fixed_pages, int n_tile_sizes, const int* tile_tokens,
-                                 const int* tile_portions, int vocab_size, int max_positions, int* out, int cap,
-                                 int* bad) {
+                                 const int* tile_portions, int tile_pad, int vocab_size, int max_positions, int* out,
+                                 int cap, int* bad) {
     Cache* c = static_cast<Cache*>(h);
-    if (n <= 0 || n + 1 > pad_requests || out == nullptr || pad_rows <= 0 || pad_wanted < 0) return ERR_ARGUMENT;
+    if (n <= 0 || n + 1 > pad_requests || out == nullptr || pad_rows <= 0 || pad_wanted < 0 || tile_pad < 0)
+        return ERR_ARGUMENT;
     const int n_groups = (int)c->pools.size();
     auto round4 = [](int v) { return (v + 3) / 4 * 4; };
     int total_rows = 0, total_want = 0;
@@ -404,7 +408,7 @@ IBH_EXPORT int ibh_describe_step(void* h, int n, const int64_t* rids, const int*
     std::vector<int> t_max(n_tile_sizes);
     for (int k = 0; k < n_tile_sizes; ++k) {
         if (tile_tokens[k] <= 0) return ERR_ARGUMENT;
-        t_max[k] = pad_rows / tile_tokens[k] + pad_requests;
+        t_max[k] = pad_rows / tile_tokens[k] + tile_pad;
         part(t_max[k]);
         part(t_max[k]);
     }
@@ -431,7 +435,8 @@ IBH_EXPORT int ibh_describe_step(void* h, int n, const int64_t* rids, const int*
     for (int j = 0; j < pad_requests; ++j) single_rows[j] = single_reqs[j] = -1;
     for (int j = 0; j < pad_requests; ++j) slots[j] = c->max_requests;   // the slot that no request ever gets
 
-    std::vector<int> n_tiles(n_tile_sizes, 0);
+    struct Tile { int last_pos, req, row0; };
+    std::vector<std::vector<Tile>> tiles(n_tile_sizes);
     int row = 0, tok_at = 0, want_at = 0, n_logit = 0, n_single = 0;
     for (int i = 0; i < n; ++i) {
         if (bad != nullptr) *bad = i;
@@ -463,10 +468,10 @@ IBH_EXPORT int ibh_describe_step(void* h, int n, const int64_t* rids, const int*
         for (int k = 0; k < n_tile_sizes; ++k) {
             if (tile_portions[k] && t == 1) continue;
             for (int s0 = 0; s0 < t; s0 += tile_tokens[k]) {
-                out[off[tiles_at + 2 * k] + n_tiles[k]] = i;
-                out[off[tiles_at + 2 * k + 1] + n_tiles[k]] = row + s0;
-                ++n_tiles[k];
+                const int s1 = s0 + tile_tokens[k] < t ? s0 + tile_tokens[k] : t;
+                tiles[k].push_back({r->n_tokens + s1 - 1, i, row + s0});
             }
+            if ((int)tiles[k].size() > t_max[k]) return ERR_ARGUMENT;   // more requests bring tiles than tile_pad allows
         }
         if (t == 1) {
             single_rows[n_single] = row;
@@ -476,6 +481,14 @@ IBH_EXPORT int ibh_describe_step(void* h, int n, const int64_t* rids, const int*
         row += t;
         tok_at += t;
         want_at += n_want[i];
+    }
+    for (int k = 0; k < n_tile_sizes; ++k) {
+        std::stable_sort(tiles[k].begin(), tiles[k].end(), [](const Tile& a, const Tile& b) { return a.last_pos < b.last_pos; });
+        const int first = t_max[k] - (int)tiles[k].size();
+        for (size_t j = 0; j < tiles[k].size(); ++j) {
+            out[off[tiles_at + 2 * k] + first + (int)j] = tiles[k][j].req;
+            out[off[tiles_at + 2 * k + 1] + first + (int)j] = tiles[k][j].row0;
+        }
     }
     // the request that takes the rows that fill the step up, then the empty ones
     const int extra = pad_rows - row;

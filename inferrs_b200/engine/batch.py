@@ -70,15 +70,11 @@ class StepContext:
         (:meth:`single_rows` has those).  Made once per step and tile size, on first use."""
         key = ("attention_tiles", tokens_per_tile, portions_only)
         if key not in self.extra:
-            req, row0, at = [], [], 0
-            for r, n in enumerate(self.q_lens):
-                if not (portions_only and n == 1):
-                    for s in range(0, n, tokens_per_tile):
-                        req.append(r)
-                        row0.append(at + s)
-                at += n
-            both = torch.from_numpy(np.asarray([req, row0], dtype=np.int32).reshape(2, -1)).to(self.token_ids.device)
-            self.extra[key] = (both[0], both[1], len(req))
+            tiles = sorted_tiles(self.q_lens, [k - n for k, n in zip(self.kv_lens, self.q_lens)], tokens_per_tile,
+                                 portions_only)
+            both = torch.from_numpy(np.asarray([[t[1] for t in tiles], [t[2] for t in tiles]],
+                                               dtype=np.int32).reshape(2, -1)).to(self.token_ids.device)
+            self.extra[key] = (both[0], both[1], len(tiles))
         return self.extra[key]
 
     def single_rows(self):
@@ -100,11 +96,27 @@ class BatchError(ValueError):
     pass
 
 
+def sorted_tiles(q_lens: Sequence[int], starts: Sequence[int], tokens_per_tile: int, portions_only: bool):
+    """The step's rows cut into tiles of at most ``tokens_per_tile`` tokens of one request each, as
+    (position of the tile's last token, request, first row); ``starts[r]`` is the position of request r's first token
+    of the step.  The tile that sees the fewest keys comes first: the attention kernels start at the end of the list,
+    with the longest tile, so that the grid's tail is short."""
+    tiles, at = [], 0
+    for r, n in enumerate(q_lens):
+        if not (portions_only and n == 1):
+            for s in range(0, n, tokens_per_tile):
+                tiles.append((starts[r] + min(s + tokens_per_tile, n) - 1, r, at + s))
+        at += n
+    tiles.sort(key=lambda t: t[0])      # stable: tiles that see as many keys keep their order
+    return tiles
+
+
 def build_context(entries: Sequence[StepEntry], manager: CacheManager, storage: CacheStorage, vocab_size: int,
                   max_positions: int, device: torch.device, fixed_pages: Optional[Sequence[int]] = None,
                   pad_to: Optional[int] = None, into: Optional[torch.Tensor] = None,
                   pad_rows: Optional[int] = None, pad_requests: Optional[int] = None,
-                  pad_wanted: Optional[int] = None, tile_sizes: Sequence[int] = ()) -> StepContext:
+                  pad_wanted: Optional[int] = None, tile_sizes: Sequence[int] = (),
+                  tile_pad: Optional[int] = None) -> StepContext:
     """Check the entries and lay their rows out.  Pages must already be reserved in ``manager``.
 
     ``fixed_pages[g]`` pads group g's block table to that many columns, ``pad_to`` pads a step of
@@ -117,8 +129,11 @@ def build_context(entries: Sequence[StepEntry], manager: CacheManager, storage: 
     ``pad_rows`` does the same for a step of any portions: the rows are padded to ``pad_rows`` (the
     added rows belong to one padding request without pages), the requests to ``pad_requests``, the
     wanted places to ``pad_wanted`` (row 0 stands in), and for every (number of tokens, portions
-    only) pair in ``tile_sizes`` the list of attention tiles is laid out with a fixed length, -1
-    marking the places that hold no tile; so is the list of the requests that bring a single token.
+    only) pair in ``tile_sizes`` the list of attention tiles is laid out with a fixed length
+    (``pad_rows // tokens + tile_pad``; ``tile_pad``, the most requests that may bring tiles, is
+    ``pad_requests`` if not given), the tiles at its end in the order of :func:`sorted_tiles` and -1
+    marking the places before them that hold no tile; the list of the requests that bring a single
+    token has ``pad_requests`` places.
     """
     if not entries:
         raise BatchError("a step needs at least one entry")
@@ -171,17 +186,15 @@ def build_context(entries: Sequence[StepEntry], manager: CacheManager, storage: 
             raise BatchError(f"{n_rows_real} rows, {n_real} requests and {len(logit_rows)} wanted places do not fit "
                              f"the fixed step of {pad_rows} rows, {pad_requests} requests, {pad_wanted} places")
         for tpt, portions_only in tile_sizes:   # the tiles of the real requests; the padding request gets none
-            t_max = pad_rows // tpt + pad_requests
+            t_max = pad_rows // tpt + (pad_requests if tile_pad is None else tile_pad)
             req = np.full(t_max, -1, dtype=np.int32)
             row0 = np.zeros(t_max, dtype=np.int32)
-            k = 0
-            for r in range(n_real):
-                if portions_only and q_lens[r] == 1:
-                    continue
-                for s0 in range(0, q_lens[r], tpt):
-                    req[k] = r
-                    row0[k] = q_start[r] + s0
-                    k += 1
+            tiles = sorted_tiles(q_lens[:n_real], [k - n for k, n in zip(kv_lens, q_lens)], tpt, portions_only)
+            if len(tiles) > t_max:
+                raise BatchError(f"{len(tiles)} attention tiles of {tpt} tokens do not fit the fixed list of {t_max}")
+            first = t_max - len(tiles)
+            for k, (_, r, r0) in enumerate(tiles):
+                req[first + k], row0[first + k] = r, r0
             tiles_fixed[(tpt, portions_only)] = (req, row0, t_max)
         single = np.full((2, pad_requests), -1, dtype=np.int32)   # rows and requests of the single tokens
         k = 0

@@ -187,7 +187,10 @@ class PortionGraphs:
     Such a step is padded to a fixed shape: its rows to the next of a few row counts (the added rows belong to
     one padding request without pages: they write nothing to the cache and nobody reads what they compute), its
     requests to the most the cache admits plus that one, its wanted places to as many.  The attention kernels
-    get their tiles from a list of fixed length in the description, in which -1 marks a place without a tile.
+    get their tiles from a list of fixed length in the description, in which -1 marks a place without a tile.  A place
+    without a tile still costs the launch of a CTA, and a list with room for every request that the cache admits
+    would have hundreds of them; so there is a captured step for each of a few numbers of requests that may bring
+    tiles (``TILE_PADS``), and a step is replayed by the smallest one that holds it.
     What the host pays per step is then the description and one graph launch instead of a dozen launches per
     layer; for small models and short portions that is the difference between a step bound by the host and one
     bound by the GPU.  The first step of every row count runs once plainly (which also tells which tile sizes
@@ -195,6 +198,7 @@ class PortionGraphs:
     """
 
     ROW_BUCKETS = (32, 64, 128, 256, 512, 1024, 2048, 4096)
+    TILE_PADS = (8,)                 # ... and as many requests as the cache admits
 
     def __init__(self, runner, decode: DecodeGraphs, max_rows: int):
         self.runner = runner
@@ -204,7 +208,8 @@ class PortionGraphs:
         self.n_requests = runner.manager.max_requests + 1
         self.n_wanted = max(self.n_requests, 64)   # wanted places that a captured step provides
         self.buckets = [b for b in self.ROW_BUCKETS if b <= max(max_rows, self.ROW_BUCKETS[0])]
-        self.captured: Dict[int, _Captured] = {}
+        self.tile_pads = [t for t in self.TILE_PADS if t < self.n_requests] + [self.n_requests]
+        self.captured: Dict[int, Dict[int, _Captured]] = {}      # row count -> requests that may bring tiles -> step
         # per row count: the (tokens per tile, portions only) pairs that the attention layers ask for at that size
         self.tile_sizes: Dict[int, list] = {}
 
@@ -218,11 +223,21 @@ class PortionGraphs:
         return (self.bucket_for(n_rows) is not None and len(entries) < self.n_requests and n_wanted <= self.n_wanted
                 and all(m.n_tokens(e.rid) + len(e.tokens) <= self.max_context for e in entries))
 
-    def _build(self, entries, bucket, device, into=None) -> StepContext:
+    def tile_pad_for(self, entries: Sequence[StepEntry], bucket: int) -> int:
+        """The smallest provided number of requests with tiles that holds this step's: the requests that bring more
+        than one token, or all of them if some attention layer cuts single tokens into tiles too."""
+        sizes = self.tile_sizes.get(bucket)
+        if sizes is not None and all(portions_only for _, portions_only in sizes):
+            n = sum(len(e.tokens) > 1 for e in entries)
+        else:
+            n = len(entries)
+        return next(t for t in self.tile_pads if t >= n)
+
+    def _build(self, entries, bucket, tile_pad, device, into=None) -> StepContext:
         r = self.runner
         ctx = build_context(entries, r.manager, r.storage, r.spec.vocab_size, r.spec.max_positions, device,
                             fixed_pages=self.fixed_pages, into=into, pad_rows=bucket, pad_requests=self.n_requests,
-                            pad_wanted=self.n_wanted, tile_sizes=self.tile_sizes[bucket])
+                            pad_wanted=self.n_wanted, tile_sizes=self.tile_sizes[bucket], tile_pad=tile_pad)
         ctx.max_kv_len = self.max_context
         return ctx
 
@@ -232,9 +247,11 @@ class PortionGraphs:
         n_rows = sum(len(e.tokens) for e in entries)
         bucket = self.bucket_for(n_rows)
         n_wanted = sum(len(e.want) for e in entries)
-        cap = self.captured.get(bucket)
+        self._learn_tile_sizes(entries, bucket)
+        tile_pad = self.tile_pad_for(entries, bucket)
+        cap = self.captured.get(bucket, {}).get(tile_pad)
         if cap is None:
-            cap = self._capture(entries, bucket, run=carry is None)
+            cap = self._capture(entries, bucket, tile_pad, run=carry is None)
             if carry is None:
                 return cap.logits[:n_wanted]
         k = cap.turn
@@ -245,13 +262,13 @@ class PortionGraphs:
         try:
             code, _ = r.manager.describe_step(
                 [e.rid for e in entries], [e.tokens for e in entries], [e.want for e in entries], bucket,
-                self.n_requests, self.n_wanted, self.fixed_pages, self.tile_sizes[bucket], r.spec.vocab_size,
+                self.n_requests, self.n_wanted, self.fixed_pages, self.tile_sizes[bucket], tile_pad, r.spec.vocab_size,
                 r.spec.max_positions, stage.data_ptr(), stage.numel())
         except (TypeError, ValueError, OverflowError):
             code = -1
         if code < 0:
             # something is wrong with an entry: the general builder says what (or builds it, if it can)
-            host = self._build(entries, bucket, torch.device("cpu")).extra["host"]
+            host = self._build(entries, bucket, tile_pad, torch.device("cpu")).extra["host"]
             stage.numpy()[:host.size] = host
         if carry is not None:
             name_carried_tokens(stage, entries, carry[1])
@@ -265,8 +282,8 @@ class PortionGraphs:
         kernels.count_launches(cap.launches)
         return cap.logits[:n_wanted]
 
-    def _capture(self, entries: Sequence[StepEntry], bucket: int, run: bool = True) -> _Captured:
-        r = self.runner                     # ``run`` as in DecodeGraphs._capture
+    def _learn_tile_sizes(self, entries: Sequence[StepEntry], bucket: int):
+        r = self.runner
         if bucket not in self.tile_sizes:
             # once plainly: the attention layers ask the context for their tiles, which tells their sizes (they may
             # depend on how many rows the step has: the plain step says that it stands for the padded one)
@@ -277,9 +294,12 @@ class PortionGraphs:
             r.storage.restore_states(saved)
             self.tile_sizes[bucket] = sorted(k[1:] for k in plain.extra
                                              if isinstance(k, tuple) and k[0] == "attention_tiles")
-        size = self._build(entries, bucket, torch.device("cpu")).extra["host"].size
+
+    def _capture(self, entries: Sequence[StepEntry], bucket: int, tile_pad: int, run: bool = True) -> _Captured:
+        r = self.runner                     # ``run`` as in DecodeGraphs._capture
+        size = self._build(entries, bucket, tile_pad, torch.device("cpu")).extra["host"].size
         buffer = torch.zeros((size + 16,), dtype=torch.int32, device=r.rt.device)
-        ctx = self._build(entries, bucket, r.rt.device, into=buffer)
+        ctx = self._build(entries, bucket, tile_pad, r.rt.device, into=buffer)
         saved = r.storage.snapshot_states()
         r.model.forward(ctx)
         r.storage.restore_states(saved)
@@ -303,5 +323,5 @@ class PortionGraphs:
         if run:
             graph.replay()
         cap = _Captured(graph, buffer, logits, launches)
-        self.captured[bucket] = cap
+        self.captured.setdefault(bucket, {})[tile_pad] = cap
         return cap

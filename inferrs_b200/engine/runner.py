@@ -122,21 +122,32 @@ class ModelRunner:
                 for rid in rids:
                     self.release(rid)
         if self.portion_graphs is not None and batch_sizes is None:
-            # the steps with prompt portions too: one stand-in request with as many tokens as each row count has
+            # the steps with prompt portions too, for every row count and every number of requests that may bring
+            # attention tiles: stand-in requests of two tokens each and one that takes the rest of the rows
             pg = self.portion_graphs
             for rows in pg.buckets:
                 n = min(rows, pg.max_context - 1)
-                if rows in pg.captured or pg.bucket_for(n) != rows:
+                if pg.bucket_for(n) != rows:
                     continue
-                rid = ("warm-up", "rows", rows)
-                self.admit(rid)
-                try:
-                    if self.manager.can_reserve({rid: n}):
-                        self.manager.reserve({rid: n})
-                        pg.run([StepEntry(rid, [0] * n, [n - 1])])
-                        done.append(-rows)
-                finally:
-                    self.release(rid)
+                for k, tile_pad in enumerate(pg.tile_pads):
+                    n_small = 0 if k == 0 else pg.tile_pads[k - 1]       # more requests than the pad below holds
+                    if tile_pad in pg.captured.get(rows, {}) or n_small + 1 >= pg.n_requests or n - 2 * n_small < 2:
+                        continue
+                    counts = [2] * n_small + [n - 2 * n_small]
+                    rids = [("warm-up", "rows", rows, i) for i in range(len(counts))]
+                    wants = dict(zip(rids, counts))
+                    for rid in rids:
+                        self.admit(rid)
+                    try:
+                        if self.manager.can_reserve(wants):
+                            self.manager.reserve(wants)
+                            pg.run([StepEntry(rid, [0] * c, [c - 1] if i + 1 == len(rids) else [])
+                                    for i, (rid, c) in enumerate(zip(rids, counts))])
+                            if -rows not in done:
+                                done.append(-rows)
+                    finally:
+                        for rid in rids:
+                            self.release(rid)
         return done
 
     # ---- the step -----------------------------------------------------------

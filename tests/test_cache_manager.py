@@ -246,17 +246,34 @@ def test_native_description_of_a_padded_step_equals_the_general_builders(seed):
         wants = [sorted(rng.sample(range(n), rng.randint(0, min(n, 3)))) for n in counts]
         rows = 64 if sum(counts) <= 64 else 256
         out = np.full(8192, 12345, dtype=np.int32)
-        code, _ = m.describe_step(chosen, tokens, wants, rows, 7, 20, fixed, tile_sizes, vocab, max_pos,
+        # room in the tile lists for as many requests as the step has, for one more, or for every request
+        tile_pad = rng.choice([len(chosen), len(chosen) + 1, 7])
+        code, _ = m.describe_step(chosen, tokens, wants, rows, 7, 20, fixed, tile_sizes, tile_pad, vocab, max_pos,
                                   out.ctypes.data, out.size)
         ctx = build_context([StepEntry(rid, t, w) for rid, t, w in zip(chosen, tokens, wants)], m, None, vocab, max_pos,
                             torch.device("cpu"), fixed_pages=fixed, pad_rows=rows, pad_requests=7, pad_wanted=20,
-                            tile_sizes=tile_sizes)
+                            tile_sizes=tile_sizes, tile_pad=tile_pad)
         host = ctx.extra["host"]
         assert code == host.size, (code, host.size)
         assert np.array_equal(out[:code], host)
+        # the tiles stand at the end of their list, the one that sees the fewest keys first
+        for (tpt, portions_only) in tile_sizes:
+            req, row0, n_tiles = ctx.attention_tiles(tpt, portions_only)
+            req, row0 = req.tolist(), row0.tolist()
+            real = [k for k in range(n_tiles) if req[k] >= 0]
+            assert real == list(range(n_tiles - len(real), n_tiles))
+            last = [ctx.positions[min(row0[k] + tpt, ctx.q_start[req[k] + 1]) - 1].item() for k in real]
+            assert last == sorted(last)
+            want_tiles = sum((n + tpt - 1) // tpt for n in counts if not (portions_only and n == 1))
+            assert len(real) == want_tiles
         for rid, n in zip(chosen, counts):
             m.commit(rid, n)
     m.reserve({0: 2})
     out = np.zeros(8192, dtype=np.int32)
-    assert m.describe_step([0], [[1, vocab]], [[0]], 64, 7, 20, fixed, tile_sizes, vocab, max_pos, out.ctypes.data, out.size)[0] < 0
-    assert m.describe_step([0], [[1, 2]], [[2]], 64, 7, 20, fixed, tile_sizes, vocab, max_pos, out.ctypes.data, out.size)[0] < 0
+    assert m.describe_step([0], [[1, vocab]], [[0]], 64, 7, 20, fixed, tile_sizes, 7, vocab, max_pos, out.ctypes.data, out.size)[0] < 0
+    assert m.describe_step([0], [[1, 2]], [[2]], 64, 7, 20, fixed, tile_sizes, 7, vocab, max_pos, out.ctypes.data, out.size)[0] < 0
+    # more requests with tiles than the lists have room for beyond rows / tokens: refused by both
+    m.reserve({1: 2, 2: 2})
+    many = ([0, 1, 2], [[1, 2], [3, 4], [5, 6]], [[0], [0], [0]])
+    if all(po for _, po in tile_sizes):
+        assert m.describe_step(*many, 64, 7, 20, fixed, tile_sizes, 0, vocab, max_pos, out.ctypes.data, out.size)[0] < 0
