@@ -383,3 +383,43 @@ def test_decode_steps_fold_the_norms_into_the_products(model_dirs, monkeypatch):
     check(folded, want[40:], dtype, "folded norms")
     check(plain, want[40:], dtype, "norm kernels")
     assert rel_err(folded, plain) < 2e-2
+
+
+def test_steps_of_many_short_prompts_take_the_longer_tile_list(model_dirs):
+    """A captured step with prompt portions exists for up to eight requests that bring attention tiles and for as many
+    as the cache admits: twelve short prompts in one step, beside a longer one and a decoding request, are replayed by
+    the second and give what the plain implementation gives; a step of three prompts afterwards takes the first."""
+    name, dtype = "B", torch.float32
+    cfg = CONFIGS[name]
+    runner = make_runner(model_dirs[name], dtype, PAGE_SIZE[name], n_pages=96, max_requests=16)
+    pg = runner.portion_graphs
+    assert pg is not None and pg.tile_pads == [8, 17]
+    lens = [5, 2, 9, 3, 17, 2, 6, 4, 11, 2, 7, 3]
+    prompts = [random_tokens(n, cfg["vocab_size"], seed=300 + i) for i, n in enumerate(lens)]
+    long_one = random_tokens(40, cfg["vocab_size"], seed=299)
+    decoding = random_tokens(21, cfg["vocab_size"], seed=298)
+    runner.admit("d")
+    runner.step([StepEntry("d", decoding[:20], [])])
+    entries = [StepEntry("d", decoding[20:], [0]), StepEntry("long", long_one, [39])]
+    entries += [StepEntry(i, p, [len(p) - 1]) for i, p in enumerate(prompts)]
+    for e in entries[1:]:
+        runner.admit(e.rid)
+    out = runner.step(entries)
+    rows = sum(len(e.tokens) for e in entries)
+    bucket = pg.bucket_for(rows)
+    assert sorted(pg.captured[bucket]) == [17], "thirteen requests bring tiles: the list for eight does not hold them"
+    check(out[0:1], plain_logits(model_dirs[name], decoding, dtype)[20:], dtype, "the decoding request")
+    check(out[1:2], plain_logits(model_dirs[name], long_one, dtype)[39:], dtype, "the longer prompt")
+    for i, p in enumerate(prompts):
+        check(out[2 + i:3 + i], plain_logits(model_dirs[name], p, dtype)[-1:], dtype, f"short prompt {i}")
+    for e in entries:
+        runner.release(e.rid)
+    few = [random_tokens(n, cfg["vocab_size"], seed=400 + n) for n in (30, 41, 37)]
+    for i, p in enumerate(few):
+        runner.admit(("few", i))
+    out = runner.step([StepEntry(("few", i), p, [len(p) - 1]) for i, p in enumerate(few)])
+    assert bucket == pg.bucket_for(sum(map(len, few))) and sorted(pg.captured[bucket]) == [8, 17]
+    for i, p in enumerate(few):
+        check(out[i:i + 1], plain_logits(model_dirs[name], p, dtype)[-1:], dtype, f"one of three prompts, {i}")
+        runner.release(("few", i))
+    runner.manager.check_invariants()
