@@ -9,6 +9,7 @@
     python -m inferrs_b200.microbench workload --shape 0.6b --requests 256 --prompt-min 16 --prompt-max 1024
     python -m inferrs_b200.microbench workload --shape 32b --requests 8 --prompt-min 8192 --prompt-max 8192 \
         --max-context 16384
+    python -m inferrs_b200.microbench workload --shape 0.6b --requests 256 --profile-steps 4 --skip-steps 10
 
 Every case is timed with CUDA events after warm-up; between timed launches a buffer larger than the
 L2 cache is written, so each launch starts cold.  One JSON line per case.
@@ -335,6 +336,8 @@ def workload(args) -> dict:
     for n in lens:
         eng.add_request(torch.randint(0, args.vocab, (n,), generator=g).tolist(), sp)
     torch.cuda.synchronize()
+    if args.profile_steps:
+        return _profile_steps(eng, args)
     t0 = time.perf_counter()
     first_decode = None
     steps = mixed = 0
@@ -362,6 +365,46 @@ def workload(args) -> dict:
         out["prompt_tokens_per_s_until_then"] = round(sum(lens) / (first_decode - t0), 1)
         out["decode_tokens_per_s_after"] = round(args.requests * (steps - mixed - 1) / max(t1 - first_decode, 1e-9), 1)
     return out
+
+
+def _profile_steps(eng, args) -> dict:
+    """``--skip-steps`` steps of the workload unrecorded, then ``--profile-steps`` steps under the profiler: per kernel how
+    far it moved the end of the step on the device ("adds": kernels started early under programmatic dependent launch
+    overlap, so their own durations would count time twice) and how often it ran.  Times under the profiler are a few
+    percent longer than without it."""
+    from torch.profiler import ProfilerActivity, profile
+    kinds = []
+    for _ in range(args.skip_steps):
+        if eng.has_work():
+            eng.step()
+    torch.cuda.synchronize()
+    n = 0
+    with profile(activities=[ProfilerActivity.CUDA]) as prof:
+        while n < args.profile_steps and eng.has_work():
+            waiting = len(eng.scheduler.waiting) + sum(r.n_pending > 1 for r in eng.scheduler.running)
+            kinds.append("portions" if waiting else "decode")
+            eng.step()
+            n += 1
+        torch.cuda.synchronize()
+    events = sorted((e for e in prof.events() if e.device_type == torch.autograd.DeviceType.CUDA),
+                    key=lambda e: e.time_range.start)
+    adds, count, end = {}, {}, None
+    for e in events:
+        st, en = e.time_range.start, e.time_range.end
+        add = en - st if end is None else (en - max(end, st) if en > end else 0.0)
+        gap = 0.0 if end is None else max(0.0, st - end)
+        end = en if end is None else max(end, en)
+        name = e.name.split("(")[0][:64]
+        adds[name] = adds.get(name, 0.0) + add
+        count[name] = count.get(name, 0) + 1
+        key = "(idle between kernels)" if gap < 200.0 else "(idle between steps)"
+        adds[key] = adds.get(key, 0.0) + gap
+    top = sorted(adds.items(), key=lambda kv: -kv[1])[:14]
+    while eng.has_work():       # let the requests end, so that the engine's books close
+        eng.step()
+    return {"kernel": "workload steps", "shape": args.shape, "steps": n, "with_prompt_portions": kinds.count("portions"),
+            "us_per_step": round(sum(adds.values()) / max(n, 1), 1),
+            "adds_us_per_step": {k: [round(v / max(n, 1), 1), round(count.get(k, 0) / max(n, 1), 1)] for k, v in top}}
 
 
 def main(argv=None) -> int:
@@ -437,6 +480,9 @@ def main(argv=None) -> int:
     wl.add_argument("--page-size", type=int, default=16)
     wl.add_argument("--cache-share", type=float, default=1.0,
                     help="pages as a share of what all requests need at once (less: requests are preempted)")
+    wl.add_argument("--profile-steps", type=int, default=0,
+                    help="instead of timing the workload: record this many steps and print what every kernel adds")
+    wl.add_argument("--skip-steps", type=int, default=10, help="... after this many unrecorded steps")
     wl.set_defaults(fn=workload)
     args = ap.parse_args(argv)
     print(json.dumps(args.fn(args)))
