@@ -135,6 +135,39 @@ def test_long_decode(model_dirs, name, dtype):
     check(torch.cat(rows), want, dtype, "long decode")
 
 
+@pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
+@pytest.mark.parametrize("name", ["A", "B", "C", "D"])
+def test_the_first_tokens_of_a_sequence(model_dirs, name, dtype):
+    """From an empty cache, one token a step: position 0 alone, the first page while it fills, the first step over a
+    page's edge; then a second request that starts beside the first one's decoding with portions of one, two and three
+    tokens.  Every position against the plain implementation."""
+    cfg = CONFIGS[name]
+    n = 2 * PAGE_SIZE[name] + 3
+    toks = random_tokens(n, cfg["vocab_size"], seed=61)
+    other = random_tokens(6, cfg["vocab_size"], seed=62)
+    want, want_other = plain_logits(model_dirs[name], toks, dtype), plain_logits(model_dirs[name], other, dtype)
+    runner = make_runner(model_dirs[name], dtype, PAGE_SIZE[name], n_pages=8)
+    runner.admit("r")
+    rows, rows_other, at = [], [], 0
+    for t in range(n):
+        entries = [StepEntry("r", toks[t:t + 1], [0])]
+        if t in (4, 5, 6):                                      # the other request's first tokens: 1, then 2, then 3
+            if t == 4:
+                runner.admit("o")
+            k = t - 3
+            entries.append(StepEntry("o", other[at:at + k], list(range(k))))
+            at += k
+        out = runner.step(entries)
+        rows.append(out[:1])
+        if len(entries) == 2:
+            rows_other.append(out[1:])
+    check(torch.cat(rows), want, dtype, "one token a step from an empty cache")
+    check(torch.cat(rows_other), want_other, dtype, "a request that starts with portions of 1, 2 and 3 tokens")
+    runner.release("r")
+    runner.release("o")
+    runner.manager.check_invariants()
+
+
 @pytest.mark.parametrize("name,dtype", [("B", torch.float32), ("C", torch.bfloat16), ("D", torch.bfloat16),
                                         ("D", torch.float32)])
 def test_steps_with_portions_are_replayed_graphs(model_dirs, name, dtype):
