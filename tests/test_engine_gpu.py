@@ -456,3 +456,43 @@ def test_steps_of_many_short_prompts_take_the_longer_tile_list(model_dirs):
         check(out[i:i + 1], plain_logits(model_dirs[name], p, dtype)[-1:], dtype, f"one of three prompts, {i}")
         runner.release(("few", i))
     runner.manager.check_invariants()
+
+
+@pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
+@pytest.mark.parametrize("heads,kv_heads,head_dim,width,inner,vocab,page", [
+    (5, 5, 48, 88, 120, 263, 8), (7, 1, 80, 136, 72, 149, 16), (9, 3, 112, 104, 152, 211, 4), (3, 1, 144, 56, 200, 331, 16),
+    (2, 2, 256, 72, 88, 97, 16), (12, 4, 96, 200, 136, 401, 8)])
+def test_head_sizes_in_steps_of_sixteen_and_odd_numbers_of_heads(tmp_path, dtype, heads, kv_heads, head_dim, width, inner,
+                                                                 vocab, page):
+    """Sizes that no kernel written for head size 64, 128 or 256 and groups of a power of two takes for granted: the
+    dispatch has to find a kernel for each or say clearly that there is none; what runs must agree with the plain
+    implementation, whole and cut into portions and single tokens beside another request."""
+    from inferrs_b200.weights.random_init import write_random_model
+    cfg = dict(CONFIG_A, num_hidden_layers=2, hidden_size=width, num_attention_heads=heads, num_key_value_heads=kv_heads,
+               head_dim=head_dim, intermediate_size=inner, vocab_size=vocab, rms_norm_eps=3e-6, rope_theta=30000.0)
+    folder = write_random_model(str(tmp_path / "m"), cfg, seed=heads * 100 + head_dim, dtype=torch.bfloat16)
+    toks = random_tokens(70, vocab, seed=head_dim)
+    other = random_tokens(23, vocab, seed=head_dim + 1)
+    want, want_other = plain_logits(folder, toks, dtype), plain_logits(folder, other, dtype)
+    runner = make_runner(folder, dtype, page, n_pages=(70 + 23) // page + 6)
+    runner.admit("w")
+    check(runner.step([StepEntry("w", toks, list(range(70)))]), want, dtype, "whole")
+    runner.release("w")
+    runner.admit("a")
+    runner.admit("b")
+    rows_a, rows_b, at, bt = [], [], 0, 0
+    for n, m in ((9, 0), (2, 11), (31, 1), (1, 1), (1, 7), (17, 1), (1, 2), (8, 0)):
+        entries = [StepEntry("a", toks[at:at + n], list(range(n)))]
+        if m:
+            entries.append(StepEntry("b", other[bt:bt + m], list(range(m))))
+        out = runner.step(entries)
+        rows_a.append(out[:n])
+        if m:
+            rows_b.append(out[n:])
+        at, bt = at + n, bt + m
+    assert at == 70 and bt == 23
+    check(torch.cat(rows_a), want, dtype, "portions and single tokens")
+    check(torch.cat(rows_b), want_other, dtype, "the request beside it")
+    runner.release("a")
+    runner.release("b")
+    runner.manager.check_invariants()
