@@ -24,6 +24,10 @@
 //     fixed order while the weights stream in, and the accumulator is scaled by 1 / sqrt(sum / width + eps) per
 //     token before it is used ("scaled rows").
 //
+// A tile may cover fewer rows of W than the MMA's 128 (the TMA box is lower; the accumulator's other rows are never
+// stored): the host lowers the tiles of a product whose CTAs number between one and two per SM until every SM has
+// two, because such a product ends when its fullest SM does (see tile_rows_for).
+//
 // Every wait on an mbarrier is bounded (about two seconds); a wait that runs out records a code in the
 // library's error word, the CTA lets outstanding copies land, frees its tensor memory and returns.
 #include <cuda.h>
@@ -87,6 +91,7 @@ struct Params {
     long ldy;
     int n_tok, n_out, num_kb, y_is_f32;
     int inner;   // gated form: rows of the gate matrix; the up matrix follows it in w
+    int tile_rows;   // rows of W that a tile covers (gated form: of each of the two matrices); the MMA's other rows are not used
     // scaled rows (null: x is used as it is): parts of the sums of squares of x's rows [n_in_parts][SSQ_LD]
     const float* in_ssq;
     int n_in_parts;
@@ -170,19 +175,21 @@ __global__ void __launch_bounds__(THREADS, (BN <= 64 ? 2 : 1)) gemm_kernel(const
         if (lane == 0 && nkb > 0) {
             // the weights are read once: their lines are the first to leave the L2 cache again
             const unsigned long long pol = policy_evict_first();
+            // what a stage receives: the boxes of W are tile_rows high, whatever the MMA's height
+            const unsigned stage_bytes = (unsigned)((MODE == 1 ? 2 : 1) * p.tile_rows * BK * 2 + B_BYTES);
             auto load_w = [&](int i, int s) {   // k-block i of this CTA's part into stage s
                 const unsigned dst = smem_u32(a_tiles + s * A_BYTES);
                 if (MODE == 1) {   // 64 rows of the gate matrix above the same 64 rows of the up matrix
-                    tma_load_2d_hint(dst, &map_w, (kb0 + i) * BK, tile_f * 64, full0 + 8 * s, pol);
-                    tma_load_2d_hint(dst + A_BYTES / 2, &map_w, (kb0 + i) * BK, p.inner + tile_f * 64, full0 + 8 * s, pol);
+                    tma_load_2d_hint(dst, &map_w, (kb0 + i) * BK, tile_f * p.tile_rows, full0 + 8 * s, pol);
+                    tma_load_2d_hint(dst + A_BYTES / 2, &map_w, (kb0 + i) * BK, p.inner + tile_f * p.tile_rows, full0 + 8 * s, pol);
                 } else {
-                    tma_load_2d_hint(dst, &map_w, (kb0 + i) * BK, tile_f * BM, full0 + 8 * s, pol);
+                    tma_load_2d_hint(dst, &map_w, (kb0 + i) * BK, tile_f * p.tile_rows, full0 + 8 * s, pol);
                 }
             };
             // the first ring of weight tiles is on its way before the predecessor's results are waited for
             const int head = nkb < STAGES ? nkb : STAGES;
             for (int i = 0; i < head; ++i) {
-                mbar_expect_tx(full0 + 8 * i, A_BYTES + B_BYTES);
+                mbar_expect_tx(full0 + 8 * i, stage_bytes);
                 load_w(i, i);
             }
             asm volatile("griddepcontrol.wait;" ::: "memory");
@@ -191,7 +198,7 @@ __global__ void __launch_bounds__(THREADS, (BN <= 64 ? 2 : 1)) gemm_kernel(const
             for (int i = head; i < nkb; ++i) {
                 const int s = i % STAGES;
                 if (!mbar_wait(empty0 + 8 * s, ((i / STAGES) - 1) & 1, 1)) { ok = false; break; }
-                mbar_expect_tx(full0 + 8 * s, A_BYTES + B_BYTES);
+                mbar_expect_tx(full0 + 8 * s, stage_bytes);
                 load_w(i, s);
                 tma_load_2d(smem_u32(b_tiles + s * B_BYTES), &map_x, (kb0 + i) * BK, tile_t * BN, full0 + 8 * s);
             }
@@ -217,11 +224,14 @@ __global__ void __launch_bounds__(THREADS, (BN <= 64 ? 2 : 1)) gemm_kernel(const
 
     const int q = warp & 3;                    // the quarter of the 128 lanes that this warp may read
     const int row = q * 32 + lane;
-    const int feature = MODE == 1 ? tile_f * 64 + (row & 63) : tile_f * BM + row;
+    // a tile may cover fewer rows of W than the MMA has (the host spreads a product's rows evenly over the SMs):
+    // the accumulator's other rows hold what the stage's unwritten rows happened to contain and are never stored
+    const int feature = MODE == 1 ? tile_f * p.tile_rows + (row & 63) : tile_f * p.tile_rows + row;
+    const bool feature_ok = (MODE == 1 ? (row & 63) : row) < p.tile_rows && feature < p.n_out;
     float* stage = reinterpret_cast<float*>(smem);  // [BN][BM] partial sums for the cluster reduction (stages are idle by then)
     if (splits > 1 && SCATTER) cluster_wait();
     const unsigned my_rank = splits > 1 ? cluster_rank() : 0;
-    const int owned = BM / splits;             // SCATTER: rows of the tile that each CTA of the cluster sums and stores
+    const int owned = p.tile_rows / splits;    // SCATTER: rows of the tile that each CTA of the cluster sums and stores
     const unsigned owner = (unsigned)(row / owned);   // per lane: with eight CTAs a warp's rows have two owners
     const int row_local = row - (int)owner * owned;
     if constexpr (MODE == 1) {
@@ -269,7 +279,7 @@ __global__ void __launch_bounds__(THREADS, (BN <= 64 ? 2 : 1)) gemm_kernel(const
             }
             asm volatile("bar.sync 1, 128;" ::: "memory");   // the four epilogue warps
             if (ok && q < 2) {                  // whole warps: the tensor-memory load below is warp-wide
-                const bool store = feature < p.n_out && g_error == 0;
+                const bool store = feature_ok && g_error == 0;
 #pragma unroll 1
                 for (int c0 = 0; c0 < BN && tile_t * BN + c0 < p.n_tok; c0 += 16) {
                     float v[16];
@@ -320,7 +330,7 @@ __global__ void __launch_bounds__(THREADS, (BN <= 64 ? 2 : 1)) gemm_kernel(const
         }
         // a sink's stream and weight, for the values that this thread will finish, fetched while the weights stream in
         if constexpr (BN <= 32) {
-            if (p.residual != nullptr && feature < p.n_out && (splits == 1 || owner == my_rank)) {
+            if (p.residual != nullptr && feature_ok && (splits == 1 || owner == my_rank)) {
                 w_sink = sink_weight(p, feature);
 #pragma unroll
                 for (int j = 0; j < KEEP; ++j)
@@ -341,7 +351,7 @@ __global__ void __launch_bounds__(THREADS, (BN <= 64 ? 2 : 1)) gemm_kernel(const
                 }
                 if (splits > 1 && SCATTER) {
                     // this warp's 32 rows go to the CTA that owns them (which may be this one)
-                    if (tile_t * BN + c0 < p.n_tok) {
+                    if (tile_t * BN + c0 < p.n_tok && row < p.tile_rows) {
                         float* slot = recv + ((size_t)my_rank * BN + c0) * owned + row_local;
                         if (owner == my_rank) {
 #pragma unroll
@@ -361,7 +371,7 @@ __global__ void __launch_bounds__(THREADS, (BN <= 64 ? 2 : 1)) gemm_kernel(const
                     for (int j = 0; j < 16; ++j) {
                         const int tok = tile_t * BN + c0 + j;
                         ssq[j] = 0.0f;
-                        if (tok < p.n_tok && feature < p.n_out) {
+                        if (tok < p.n_tok && feature_ok) {
                             const float o = BN <= 32 ? finish_value(p, v[j], tok, feature, fold[8 * SSQ_LD + c0 + j],
                                                                     old_s[(c0 + j) % KEEP], w_sink, ssq[j]) : v[j];
                             if (p.y_is_f32) reinterpret_cast<float*>(p.y)[(long)tok * p.ldy + feature] = o;
@@ -394,7 +404,7 @@ __global__ void __launch_bounds__(THREADS, (BN <= 64 ? 2 : 1)) gemm_kernel(const
     if (splits > 1 && SCATTER) {
         cluster_sync_all();                    // every part of the rows this CTA owns is in its shared memory
         if (warp >= 2) {
-            const bool mine = owner == my_rank && feature < p.n_out && g_error == 0;
+            const bool mine = owner == my_rank && feature_ok && g_error == 0;
 #pragma unroll UNROLL
             for (int c0 = 0; c0 < BN; c0 += 16) {
                 if (tile_t * BN + c0 >= p.n_tok) break;
@@ -432,7 +442,7 @@ __global__ void __launch_bounds__(THREADS, (BN <= 64 ? 2 : 1)) gemm_kernel(const
         // nobody touches another CTA's shared memory after the barrier: the CTAs may leave in any order
     } else if (splits > 1) {
         cluster_sync_all();                    // every CTA's partial sums are in its shared memory
-        if (warp >= 2 && my_rank == 0 && feature < p.n_out && g_error == 0) {
+        if (warp >= 2 && my_rank == 0 && feature_ok && g_error == 0) {
 #pragma unroll 1
             for (int c0 = 0; c0 < BN && tile_t * BN + c0 < p.n_tok; c0 += 16) {
                 float sum[16];
@@ -486,15 +496,66 @@ static bool make_map(CUtensorMap* map, const void* base, long rows, long k, long
                CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) == CUDA_SUCCESS;
 }
 
+template <int BN, int STAGES>
+constexpr size_t smem_bytes() {
+    return (size_t)STAGES * (A_BYTES + BN * BK * 2) + (2 * STAGES + 2) * 8 + 1024 + 9 * SSQ_LD * 4 +
+           (BN <= 32 ? (size_t)BN * BM * 4 : 0);   // + the folded forms' sums + the parts received from the cluster
+}
+
+template <int BN, int STAGES, int MODE>
+static int allow_smem() {
+    static IbDeviceSet configured;   // the attribute is kept per device
+    return ib_allow_dynamic_smem(configured, gemm_kernel<BN, STAGES, MODE>, smem_bytes<BN, STAGES>());
+}
+
+// A kernel with this file's block size, two CTAs per SM and no tensor memory; it is never launched.  The driver's
+// occupancy query answers "one CTA per SM" for every kernel that allocates tensor memory, although two CTAs of the
+// kernels above run on an SM (each takes 32 or 64 of the 512 columns, and a profile of the 192 CTAs of a gated
+// product counts 7.7 active warps per SM: two CTAs on 44 SMs, one on the rest).  So the query is put to this kernel
+// with the same shared memory instead.
+__global__ void __launch_bounds__(THREADS, 2) occupancy_stand_in(float* p) {
+    extern __shared__ float stand_in_smem[];
+    stand_in_smem[threadIdx.x] = p[threadIdx.x];
+    __syncthreads();
+    p[threadIdx.x] = stand_in_smem[THREADS - 1 - threadIdx.x];
+}
+
+// CTAs with `smem` bytes of shared memory (two fit on an SM) that the GPU holds at a time when they come in clusters
+// of `splits`; 0: not known.  With clusters it is fewer than twice the SMs, because a cluster wants its SMs in one
+// part of the chip: 284 in clusters of four and 264 in clusters of eight on a B200 with 148 SMs.
+static int resident_ctas(size_t smem, int splits) {
+    static int cached[64][9] = {};
+    int dev = 0;
+    if (splits < 1 || splits > 8 || cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= 64) return 0;
+    if (cached[dev][splits] == 0) {
+        cached[dev][splits] = -1;
+        if (cudaFuncSetAttribute(occupancy_stand_in, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem) == cudaSuccess) {
+            cudaLaunchConfig_t cfg = {};
+            cfg.gridDim = dim3(1, 1, splits);
+            cfg.blockDim = dim3(THREADS);
+            cfg.dynamicSmemBytes = smem;
+            cudaLaunchAttribute attr[1];
+            attr[0].id = cudaLaunchAttributeClusterDimension;
+            attr[0].val.clusterDim.x = 1;
+            attr[0].val.clusterDim.y = 1;
+            attr[0].val.clusterDim.z = splits;
+            cfg.attrs = attr;
+            cfg.numAttrs = 1;
+            int clusters = 0;
+            if (cudaOccupancyMaxActiveClusters(&clusters, occupancy_stand_in, &cfg) == cudaSuccess && clusters > 0)
+                cached[dev][splits] = clusters * splits;
+        }
+        (void)cudaGetLastError();
+    }
+    return cached[dev][splits] > 0 ? cached[dev][splits] : 0;
+}
+
 template <int BN, int STAGES, int MODE = 0>
 static int launch(const CUtensorMap& mw, const CUtensorMap& mx, const Params& p, int splits, cudaStream_t stream) {
-    constexpr size_t smem = (size_t)STAGES * (A_BYTES + BN * BK * 2) + (2 * STAGES + 2) * 8 + 1024 + 9 * SSQ_LD * 4 +
-                            (BN <= 32 ? (size_t)BN * BM * 4 : 0);   // + the folded forms' sums + the parts received from the cluster
-    static IbDeviceSet configured;   // the attribute is kept per device
-    if (const int e = ib_allow_dynamic_smem(configured, gemm_kernel<BN, STAGES, MODE>, smem)) return e;
+    constexpr size_t smem = smem_bytes<BN, STAGES>();
+    if (const int e = allow_smem<BN, STAGES, MODE>()) return e;
     cudaLaunchConfig_t cfg = {};
-    const int rows_per_tile = MODE == 1 ? 64 : BM;
-    cfg.gridDim = dim3((p.n_out + rows_per_tile - 1) / rows_per_tile, (p.n_tok + BN - 1) / BN, splits);
+    cfg.gridDim = dim3((p.n_out + p.tile_rows - 1) / p.tile_rows, (p.n_tok + BN - 1) / BN, splits);
     cfg.blockDim = dim3(THREADS);
     cfg.dynamicSmemBytes = smem;
     cfg.stream = stream;
@@ -529,6 +590,39 @@ static int choose_splits(int n_tok, int n_out, int num_kb, int bn, int split_k) 
     return splits;
 }
 
+static int g_even_tiles = 1;   // host: see ib_gemm_tcgen05_set_even_tiles
+
+static int sm_count() {
+    static int sms[64] = {};
+    int dev = 0;
+    if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= 64) return 148;
+    if (sms[dev] == 0 && cudaDeviceGetAttribute(&sms[dev], cudaDevAttrMultiProcessorCount, dev) != cudaSuccess) sms[dev] = 148;
+    return sms[dev];
+}
+
+// Rows of W per tile.  A product whose CTAs all fit on the GPU at once, but are more than the SMs, streams its weights
+// unevenly: 192 tiles leave 44 SMs with two CTAs and 104 with one, and the product ends when the 44 do.  The tiles
+// of such a product are made lower than the MMA (which then computes rows that nobody stores) until there are as
+// many CTAs as the GPU holds.  `full` is the MMA's share of rows per tile: 128, or 64 of each matrix in the gated
+// form; `resident` what resident_ctas() says for the kernel that will run.
+static int tile_rows_for(int n_out, int splits, int full, int resident) {
+    if (!g_even_tiles || resident <= 0) return full;
+    const long ctas_full = (long)((n_out + full - 1) / full) * splits;
+    if (ctas_full > resident || ctas_full <= sm_count()) return full;   // several waves anyway, or one CTA per SM at most   // several waves anyway, or one CTA per SM at most
+    const int tiles_wanted = resident / splits;
+    int rows = (n_out + tiles_wanted - 1) / tiles_wanted;
+    rows = (rows + 7) / 8 * 8;                              // a few CTAs fewer than fit: the next kernel's first ones find room
+    rows = (rows + splits - 1) / splits * splits;           // the owners of a cluster take equal shares
+    return rows < full ? rows : full;
+}
+
+// what resident_ctas() says for the kernel that a product of bn tokens per tile runs (up to 64 tokens: beyond, a
+// product has one CTA per SM and tiles as high as the MMA).  The three kernels' shared memory differs by a few KB and
+// two of each fit on an SM, so the largest stands for all.
+static int resident_for(int bn, int splits) {
+    return bn <= 64 ? tc::resident_ctas(tc::smem_bytes<16, 5>(), splits) : 0;
+}
+
 static int bn_for(int n_tok) { return n_tok <= 16 ? 16 : n_tok <= 32 ? 32 : n_tok <= 64 ? 64 : n_tok <= 128 ? 128 : 256; }
 
 // The folded forms (see the head of this file) as the exported functions take them: both optional.
@@ -554,8 +648,9 @@ static int gemm_tn(const void* x, long ldx, const void* w, long ldw, void* y, lo
     p.residual = f.residual; p.ld_res = f.ld_res; p.sink_w = f.sink_w; p.sink_w_is_f32 = f.sink_w_is_f32; p.out_ssq = f.out_ssq;
     const int splits = choose_splits(n_tok, n_out, p.num_kb, bn, split_k);
     if (splits != 1 && splits != 2 && splits != 4 && splits != 8) return IB_ERR_ARGUMENT;
+    p.tile_rows = tile_rows_for(n_out, splits, tc::BM, resident_for(bn, splits));
     CUtensorMap mw, mx;
-    if (!tc::make_map(&mw, w, n_out, k, ldw, tc::BM) || !tc::make_map(&mx, x, n_tok, k, ldx, bn)) return IB_ERR_UNSUPPORTED;
+    if (!tc::make_map(&mw, w, n_out, k, ldw, p.tile_rows) || !tc::make_map(&mx, x, n_tok, k, ldx, bn)) return IB_ERR_UNSUPPORTED;
     switch (bn) {
         // up to 64 tokens: two CTAs per SM with half the ring each, so that tile counts between one and two
         // per SM still run as one wave in which every CTA gets the same share of the memory bandwidth
@@ -593,7 +688,9 @@ IB_EXPORT int ib_gemm_tcgen05_ssq_parts(int n_tok, int n_out, int k, int split_k
     if (n_tok <= 0 || n_out <= 0 || k <= 0) return IB_ERR_ARGUMENT;
     const int bn = bn_for(n_tok);
     if (bn > 32) return IB_ERR_UNSUPPORTED;
-    return ((n_out + tc::BM - 1) / tc::BM) * choose_splits(n_tok, n_out, (k + tc::BK - 1) / tc::BK, bn, split_k);
+    const int splits = choose_splits(n_tok, n_out, (k + tc::BK - 1) / tc::BK, bn, split_k);
+    const int rows = tile_rows_for(n_out, splits, tc::BM, resident_for(bn, splits));
+    return ((n_out + rows - 1) / rows) * splits;
 }
 
 // y[t, f] = silu(x[t] . w[f]) * (x[t] . w[inner + f]) for f < inner: the gate and up products of a gated feed-forward
@@ -613,8 +710,9 @@ IB_EXPORT int ib_gemm_swiglu_tcgen05_folded(const void* x, long ldx, const void*
     p.inner = inner;
     p.in_ssq = in_ssq; p.n_in_parts = n_in_parts; p.in_eps = in_eps; p.in_inv_width = in_width > 0 ? 1.0f / (float)in_width : 0.0f;
     p.residual = nullptr; p.ld_res = 0; p.sink_w = nullptr; p.sink_w_is_f32 = 0; p.out_ssq = nullptr;
+    p.tile_rows = tile_rows_for(inner, 1, 64, resident_for(bn, 1));
     CUtensorMap mw, mx;
-    if (!tc::make_map(&mw, w, 2L * inner, k, ldw, 64) || !tc::make_map(&mx, x, n_tok, k, ldx, bn)) return IB_ERR_UNSUPPORTED;
+    if (!tc::make_map(&mw, w, 2L * inner, k, ldw, p.tile_rows) || !tc::make_map(&mx, x, n_tok, k, ldx, bn)) return IB_ERR_UNSUPPORTED;
     return bn == 16 ? tc::launch<16, 5, 1>(mw, mx, p, 1, stream) : tc::launch<32, 4, 1>(mw, mx, p, 1, stream);
 }
 
@@ -628,6 +726,24 @@ IB_EXPORT int ib_gemm_swiglu_tcgen05(const void* x, long ldx, const void* w, lon
 // kernel that runs between two such launches must itself call griddepcontrol.wait before its first access to
 // memory that another kernel writes.  0 (default): plain stream order.
 IB_EXPORT void ib_gemm_tcgen05_set_pdl(int on) { tc::g_pdl = on; }
+
+// 1 (default): a product whose CTAs all run at once gets tiles of such a height that every SM has the same number
+// of them; 0: every tile is as high as the MMA.  The number of parts that a sink writes follows the setting, so it
+// is set before the lists of parts are sized.
+IB_EXPORT void ib_gemm_tcgen05_set_even_tiles(int on) { g_even_tiles = on; }
+
+// What the choice of a product's tiles rests on: the CTAs that the GPU holds at a time of the kernel that a product of
+// n_tok tokens runs (gated: the gate/up form), in clusters of `splits`; and the rows of W per tile that follow.
+IB_EXPORT int ib_gemm_tcgen05_resident_ctas(int n_tok, int gated, int splits) {
+    return resident_for(gated ? (n_tok <= 16 ? 16 : 32) : bn_for(n_tok), splits);
+}
+IB_EXPORT int ib_gemm_tcgen05_tile_rows(int n_tok, int n_out, int k, int split_k, int gated) {
+    if (n_tok <= 0 || n_out <= 0 || k <= 0) return IB_ERR_ARGUMENT;
+    if (gated) return tile_rows_for(n_out, 1, 64, resident_for(n_tok <= 16 ? 16 : 32, 1));
+    const int bn = bn_for(n_tok);
+    const int splits = choose_splits(n_tok, n_out, (k + tc::BK - 1) / tc::BK, bn, split_k);
+    return tile_rows_for(n_out, splits, tc::BM, resident_for(bn, splits));
+}
 
 // The error word of the kernels above: 0, or the code of the first wait that ran out (1 producer, 2 MMA
 // issuer, 3 epilogue).  Reading it synchronises with the device; `reset` clears it.

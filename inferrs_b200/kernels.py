@@ -995,7 +995,7 @@ def gemm_tn_tcgen05(x, w: torch.Tensor, out: torch.Tensor, split_k: int = 0, sin
 
 def gemm_swiglu_tcgen05(x, w_gate_up: torch.Tensor, out: torch.Tensor):
     """out[t, f] = silu(x[t] . w[f]) * (x[t] . w[inner + f]): both products of a gated feed-forward and the gate
-    in one tcgen05 kernel (64 gate rows and the same 64 up rows per tile).  Up to 32 rows of x, which may be
+    in one tcgen05 kernel (up to 64 gate rows and the same up rows per tile).  Up to 32 rows of x, which may be
     :class:`ScaledRows`."""
     xt, scaled = _scaled_args(x)
     _need(xt, "x", (torch.bfloat16,), 2)
@@ -1017,6 +1017,24 @@ def gemm_tcgen05_set_pdl(on: bool):
     wait for the predecessor before touching anything else).  Only safe among kernels that all wait likewise."""
     _gemm_lib().ib_gemm_tcgen05_set_pdl(int(bool(on)))
     _gemm_lib().ib_gemm_chain_set_pdl(int(bool(on)))
+
+
+def gemm_tcgen05_set_even_tiles(on: bool):
+    """Whether a tcgen05 product whose CTAs all run at once cuts its tiles lower than the MMA so that every SM gets
+    the same number of them (default) or keeps every tile at the MMA's height."""
+    lib = _gemm_lib()
+    lib.ib_gemm_tcgen05_set_even_tiles.argtypes = [c_int]
+    lib.ib_gemm_tcgen05_set_even_tiles.restype = None
+    lib.ib_gemm_tcgen05_set_even_tiles(int(bool(on)))
+
+
+def gemm_tcgen05_tile_rows(n_rows: int, n_out: int, k: int, split_k: int = 0, gated: bool = False) -> int:
+    """Rows of the weight matrix per tile (of each of the two matrices in the gated form) that a tcgen05 product of
+    these sizes takes: the MMA's 128 (64), or fewer where that spreads the product evenly over the SMs."""
+    lib = _gemm_lib()
+    lib.ib_gemm_tcgen05_tile_rows.argtypes = [c_int, c_int, c_int, c_int, c_int]
+    lib.ib_gemm_tcgen05_tile_rows.restype = c_int
+    return int(lib.ib_gemm_tcgen05_tile_rows(n_rows, n_out, k, split_k, int(gated)))
 
 
 def set_pdl(on: bool, act_dtype: torch.dtype = torch.bfloat16):

@@ -410,6 +410,9 @@ def _profile_steps(eng, args) -> dict:
 def main(argv=None) -> int:
     ap = argparse.ArgumentParser(prog="inferrs_b200.microbench", description=__doc__,
                                  formatter_class=argparse.RawDescriptionHelpFormatter)
+    ap.add_argument("--full-tiles", action="store_true",
+                    help="tcgen05 products keep every tile at the MMA's height instead of spreading their rows "
+                         "evenly over the SMs")
     sub = ap.add_subparsers(dest="what", required=True)
     g = sub.add_parser("gemm")
     g.add_argument("--impl", choices=["library", "tcgen05", "gated"], default="tcgen05",
@@ -485,6 +488,8 @@ def main(argv=None) -> int:
     wl.add_argument("--skip-steps", type=int, default=10, help="... after this many unrecorded steps")
     wl.set_defaults(fn=workload)
     args = ap.parse_args(argv)
+    if args.full_tiles:
+        kernels.gemm_tcgen05_set_even_tiles(False)
     print(json.dumps(args.fn(args)))
     return 0
 

@@ -818,6 +818,78 @@ def test_products_with_folded_norms(n, m, k):
     assert not K.folded_norm_supported(40, dtype, w) and not K.folded_norm_supported(n, torch.float32, w.float())
 
 
+@pytest.mark.parametrize("n,m,k,split_k", [(5, 20000, 72, 0), (20, 10000, 136, 0), (8, 6100, 1024, 0), (3, 3000, 8192, 0),
+                                           (40, 6100, 256, 0), (12, 5000, 512, 4)])
+def test_products_with_tiles_lower_than_the_mma(n, m, k, split_k):
+    """A product whose CTAs number between one and two per SM gets tiles of fewer rows than the MMA has, so that
+    every SM holds two CTAs: the rows that the MMA computes beyond a tile are never stored, the last tile ends in
+    the middle of a box, the owners of a cluster share a tile that is no power of two high.  Plain, with a sink and
+    from scaled rows, against float32 and, bit for bit, against the same kernels with tiles of the MMA's height."""
+    from inferrs_b200 import kernels as K
+    dtype, eps = torch.bfloat16, 1e-6
+    rows = K.gemm_tcgen05_tile_rows(n, m, k, split_k)
+    assert 0 < rows < 128, "these sizes are meant to take lowered tiles"
+    x, w = rand((n, k), dtype, 120), rand((m, k), dtype, 121, scale=0.05)
+
+    def run():
+        out = torch.full((n, m), float("nan"), dtype=dtype, device=dev())
+        K.gemm_tn_tcgen05(x, w, out, split_k)
+        if n > 32:
+            return out, None, None, None
+        res = rand((n, m), torch.float32, 122)
+        wn = (1 + 0.1 * rand((m,), torch.float32, 123)).to(dtype)
+        handed = torch.full((n, m), float("nan"), dtype=dtype, device=dev())
+        scaled = K.gemm_tn_tcgen05(x, w, handed, split_k, sink=K.ResidualSink(res, wn, eps))
+        w2 = rand((136, m), dtype, 124, scale=0.05)
+        nxt = torch.empty((n, 136), dtype=dtype, device=dev())
+        K.gemm_tn_tcgen05(scaled, w2, nxt) if m % 8 == 0 else None
+        return out, res, handed, (scaled.ssq[:scaled.n_parts, :n].sum(dim=0), nxt)
+
+    out, res, handed, rest = run()
+    assert K.gemm_tcgen05_error() == 0
+    ref = x.float() @ w.float().t()
+    assert bool(torch.isfinite(out.float()).all()) and rel_err(out, ref) < TOL[dtype]
+    if res is not None:
+        res_ref = rand((n, m), torch.float32, 122) + ref.to(dtype).float()
+        assert rel_err(res, res_ref) < 1e-2
+        assert rel_err(rest[0], (res.double() ** 2).sum(dim=1).float()) < 1e-5
+    K.gemm_tcgen05_set_even_tiles(False)
+    try:
+        assert K.gemm_tcgen05_tile_rows(n, m, k, split_k) == 128
+        out_full, res_full, handed_full, rest_full = run()
+    finally:
+        K.gemm_tcgen05_set_even_tiles(True)
+    assert torch.equal(out, out_full)
+    if res is not None:
+        assert torch.equal(res, res_full) and torch.equal(handed, handed_full)
+        if m % 8 == 0:
+            assert rel_err(rest[1], rest_full[1]) < 1e-2   # the parts of the sums of squares are cut elsewhere
+
+
+@pytest.mark.parametrize("n,inner,k", [(7, 10000, 136), (24, 12288, 512), (1, 15000, 64)])
+def test_gated_products_with_tiles_lower_than_the_mma(n, inner, k):
+    """The gate/up form with fewer than 64 rows of each matrix per tile: the gate box of the last tile reaches into
+    the up matrix and the up box beyond the matrix, and neither is stored."""
+    from inferrs_b200 import kernels as K
+    dtype = torch.bfloat16
+    assert 0 < K.gemm_tcgen05_tile_rows(n, inner, k, 0, gated=True) < 64, "these sizes are meant to take lowered tiles"
+    x, w = rand((n, k), dtype, 130), rand((2 * inner, k), dtype, 131, scale=0.08)
+    out = torch.full((n, inner), float("nan"), dtype=dtype, device=dev())
+    K.gemm_swiglu_tcgen05(x, w, out)
+    assert K.gemm_tcgen05_error() == 0
+    g = (x.float() @ w[:inner].float().t()).to(dtype).float()
+    u = (x.float() @ w[inner:].float().t()).to(dtype).float()
+    ref = torch.nn.functional.silu(g) * u
+    assert bool(torch.isfinite(out.float()).all()) and rel_err(out, ref) < 2 * TOL[dtype]
+    K.gemm_tcgen05_set_even_tiles(False)
+    try:
+        full = torch.empty_like(out)
+        K.gemm_swiglu_tcgen05(x, w, full)
+    finally:
+        K.gemm_tcgen05_set_even_tiles(True)
+    assert torch.equal(out, full)
+
+
 @pytest.mark.parametrize("n,width,inner,qkv", [(8, 4096, 12288, 6144), (1, 1024, 3072, 4096), (16, 192, 320, 1280), (3, 5120, 1088, 640)])
 def test_a_chain_of_products_is_one_launch_and_gives_what_the_single_products_give(n, width, inner, qkv):
     """The four products between two attention kernels of a decode step (o projection into the stream, gate and up with
