@@ -179,7 +179,7 @@ __global__ void __launch_bounds__(THREADS, (BN <= 64 ? 2 : 1)) gemm_kernel(const
             const unsigned stage_bytes = (unsigned)((MODE == 1 ? 2 : 1) * p.tile_rows * BK * 2 + B_BYTES);
             auto load_w = [&](int i, int s) {   // k-block i of this CTA's part into stage s
                 const unsigned dst = smem_u32(a_tiles + s * A_BYTES);
-                if (MODE == 1) {   // 64 rows of the gate matrix above the same 64 rows of the up matrix
+                if (MODE == 1) {   // up to 64 rows of the gate matrix, and the same rows of the up matrix 64 rows below them in the stage
                     tma_load_2d_hint(dst, &map_w, (kb0 + i) * BK, tile_f * p.tile_rows, full0 + 8 * s, pol);
                     tma_load_2d_hint(dst + A_BYTES / 2, &map_w, (kb0 + i) * BK, p.inner + tile_f * p.tile_rows, full0 + 8 * s, pol);
                 } else {
