@@ -647,18 +647,33 @@ def tma_decode_attention_supported(dtype: torch.dtype, n_heads: int, n_kv_heads:
 DECODE_RESIDENT_CTAS = 296  # two CTAs of the decode attention kernel fit on each of the 148 SMs
 
 
-def decode_max_splits(n_requests: int, n_kv_heads: int, max_kv_len: int) -> int:
-    """Upper bound of the slices per request that the decode kernel's grid provides (the kernel itself uses no more
-    than the request's real length gives four tiles to).  Few requests: as many slices as still run as one wave
-    of resident CTAs, because a CTA's fixed start-up cost is paid once per wave.  More (request, head group)
-    pairs than resident CTAs: one slice each; measured at 2,048 keys, 32 and 64 requests take 64 and 108 us
-    with one slice against 81 and 134 us with four."""
+def decode_slices(n_requests: int, n_kv_heads: int, max_kv_len: int):
+    """(max_splits, min_tiles) for :func:`paged_attention_decode`: the slices per request that the decode kernel's
+    grid provides, and how the kernel picks a request's slices from its real length.
+
+    Few requests: as many slices as still run as one wave of resident CTAs, because a CTA's fixed start-up cost
+    is paid once per wave; a request uses as many as leave each slice four tiles.  Between one and one and a half
+    waves of (request, head group) pairs the second wave would be nearly empty and as long as the first: three or two
+    slices make four or three nearly full waves of shorter CTAs (measured at 2,048 keys: 40 requests 88 us against
+    99 with one slice, 48 requests 92 against 99; inside a step of 48 requests of 8,192 keys 347 us per layer against
+    400).  More pairs: one slice (at 2,048 keys 64 requests take 102 us with one slice and 115 to 123 with two to
+    four; 64 requests of 8,192 keys in four slices, which would fill seven waves, take 438 us per layer inside a step
+    against 421 with one)."""
     tiles = max(1, (max_kv_len + MMA_KEYS - 1) // MMA_KEYS)
     pairs = max(1, n_requests * n_kv_heads)
     most = max(1, (tiles + 3) // 4)
-    if pairs <= DECODE_RESIDENT_CTAS:
-        return max(1, min(most, DECODE_RESIDENT_CTAS // pairs))
-    return 1
+    room = DECODE_RESIDENT_CTAS
+    if pairs <= room:
+        return max(1, min(most, room // pairs)), 4
+    if pairs * 3 <= 4 * room:
+        return min(most, 3), 4
+    if pairs * 2 <= 3 * room:
+        return min(most, 2), 4
+    return 1, 4
+
+
+def decode_max_splits(n_requests: int, n_kv_heads: int, max_kv_len: int) -> int:
+    return decode_slices(n_requests, n_kv_heads, max_kv_len)[0]
 
 
 def paged_attention_decode(q: torch.Tensor, k_pages: torch.Tensor, v_pages: torch.Tensor, block_table: torch.Tensor,
@@ -668,7 +683,8 @@ def paged_attention_decode(q: torch.Tensor, k_pages: torch.Tensor, v_pages: torc
     """Attention of one new token per request (row r = request r) over its pages: TMA-fed key/value tiles, split
     over the keys, merged by the slice that finishes last (bfloat16, head_dim 128).  With ``rows`` and ``reqs``
     (int32, equally long) only the rows named are worked on, row ``rows[i]`` being a single token of request
-    ``reqs[i]``; a negative row is skipped.  The other rows of ``out`` are left alone."""
+    ``reqs[i]``; a negative row is skipped.  The other rows of ``out`` are left alone.  A request is cut into as
+    many slices as leave each ``min_tiles`` tiles of 64 keys (at most ``max_splits``)."""
     bf = (torch.bfloat16,)
     _need(q, "q", bf, 3)
     _need(k_pages, "k_pages", bf, 4)
@@ -824,8 +840,9 @@ def paged_attention(q: torch.Tensor, k_pages: torch.Tensor, v_pages: torch.Tenso
     prefill_kernel = paged_attention_pair_tcgen05 if pair else paged_attention_tcgen05
     prefill_tokens = pair_tokens if pair else TC_ROWS // (nh // nkv)
     if ctx.decode_only and tma_decode_attention_supported(q.dtype, nh, nkv, d, page_size):
-        paged_attention_decode(q, k_pages, v_pages, block_table, ctx.positions, scale, window, out,
-                               decode_max_splits(ctx.n_requests, nkv, ctx.max_kv_len))
+        max_splits, min_tiles = decode_slices(ctx.n_requests, nkv, ctx.max_kv_len)
+        paged_attention_decode(q, k_pages, v_pages, block_table, ctx.positions, scale, window, out, max_splits,
+                               min_tiles=min_tiles)
     elif ctx.decode_only:
         # one row per request: the rows are the tiles
         splits = decode_splits(ctx.n_requests, nkv, ctx.max_kv_len)
@@ -837,8 +854,9 @@ def paged_attention(q: torch.Tensor, k_pages: torch.Tensor, v_pages: torch.Tenso
         # of the prefill kernel would hold one token of 32), the portions to the prefill kernel
         rows, reqs, n_single = ctx.single_rows()
         if n_single > 0:
-            paged_attention_decode(q, k_pages, v_pages, block_table, ctx.positions, scale, window, out,
-                                   decode_max_splits(n_single, nkv, ctx.max_kv_len), rows, reqs)
+            max_splits, min_tiles = decode_slices(n_single, nkv, ctx.max_kv_len)
+            paged_attention_decode(q, k_pages, v_pages, block_table, ctx.positions, scale, window, out, max_splits,
+                                   rows, reqs, min_tiles=min_tiles)
         tile_req, tile_row0, n_tiles = ctx.attention_tiles(prefill_tokens, portions_only=True)
         if n_tiles > 0:
             prefill_kernel(q, k_pages, v_pages, block_table, tile_req, tile_row0, n_tiles, ctx.q_start,

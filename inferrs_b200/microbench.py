@@ -106,9 +106,10 @@ def attention(args) -> dict:
             fn = lambda: kernels.paged_attention_mma(q, k_pages, v_pages, table, row_request, q_start, n, q_start,  # noqa: E731
                                                      positions, scale, None, out, True, splits)
         else:
-            splits = args.splits or kernels.decode_max_splits(args.batch, nkv, args.max_context or args.context)
+            splits, min_tiles = kernels.decode_slices(args.batch, nkv, args.max_context or args.context)
+            splits, min_tiles = args.splits or splits, args.min_tiles or min_tiles
             fn = lambda: kernels.paged_attention_decode(q, k_pages, v_pages, table, positions, scale, None, out,  # noqa: E731
-                                                        splits, min_tiles=args.min_tiles)
+                                                        splits, min_tiles=min_tiles)
         byts = 2 * 2 * sum(lens) * nkv * d
         flops = 4 * nh * d * sum(lens)
         extra = {"batch": args.batch, "context": args.context, "splits": splits}
@@ -431,7 +432,7 @@ def main(argv=None) -> int:
     a.add_argument("--tokens", type=int, default=2048)
     a.add_argument("--context-before", type=int, default=0)
     a.add_argument("--splits", type=int, default=0)
-    a.add_argument("--min-tiles", type=int, default=4, help="decode form: fewest 64-key tiles per slice")
+    a.add_argument("--min-tiles", type=int, default=0, help="decode form: fewest 64-key tiles per slice (0: as the engine chooses)")
     a.add_argument("--max-context", type=int, default=0, help="decode form: the context that the grid is sized for")
     a.add_argument("--heads", type=int, default=32)
     a.add_argument("--kv-heads", type=int, default=8)

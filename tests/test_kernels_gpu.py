@@ -534,14 +534,28 @@ def test_paged_attention_decode(nh, nkv, ps, window, max_splits):
     ref = torch.empty((n, nh * d), dtype=dtype, device=dev())
     scale = d ** -0.5 * 4
     R.paged_attention_generic(q, k_pages, v_pages, table, row_request, positions, scale, window, ref)
-    for _ in range(2):   # the counters must be back at zero after a launch
+    for min_tiles in (4, 4, 9):   # twice the same: the counters must be back at zero after a launch
         out = torch.full((n, nh * d), float("nan"), dtype=dtype, device=dev())
-        K.paged_attention_decode(q, k_pages, v_pages, table, positions, scale, window, out, max_splits)
+        K.paged_attention_decode(q, k_pages, v_pages, table, positions, scale, window, out, max_splits,
+                                 min_tiles=min_tiles)
         assert K.attention_decode_error() == 0
         assert rel_err(out, ref) < 2e-2
     got = out[5].view(nh, d).float()
     want = v_pages[page, :, slot, :].float().repeat_interleave(nh // nkv, dim=0)
     assert rel_err(got, want) < 5e-2, "the far key that stands out was not seen"
+
+
+def test_how_the_decode_kernel_is_cut_follows_the_waves_of_ctas():
+    """Host arithmetic only: the slices per request for numbers of (request, head group) pairs around one and two
+    waves of resident CTAs."""
+    from inferrs_b200 import kernels as K
+    room = K.DECODE_RESIDENT_CTAS
+    assert K.decode_slices(1, 8, 4096) == (16, 4) and K.decode_slices(8, 8, 4096) == (room // 64, 4)
+    assert K.decode_slices(37, 8, 4096) == (1, 4), "one wave: one slice"
+    assert K.decode_slices(40, 8, 4096) == (3, 4) and K.decode_slices(52, 8, 4096) == (2, 4)
+    assert K.decode_slices(64, 8, 4096) == (1, 4) and K.decode_slices(64, 8, 40960) == (1, 4), "nearly two waves: one slice"
+    assert K.decode_slices(256, 8, 40960) == (1, 4)
+    assert K.decode_max_splits(48, 8, 16384) == 3
 
 
 @pytest.mark.parametrize("nh,nkv,ps,window", [(8, 2, 16, None), (32, 8, 16, 300)])
