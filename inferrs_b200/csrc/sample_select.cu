@@ -6,19 +6,30 @@
 // p >= min_p * p_max, renormalise, walk the kept list until the cumulative probability
 // passes the random number u.  No list is sorted here.  With e_i = exp(z_i - z_max) every
 // question the walk asks ("how much mass lies before rank r", "which rank holds mass t")
-// is answered by a radix descent over the bits of e_i: four passes of 256 buckets, each
+// is answered by a radix descent over the bits of e_i: four levels of 256 buckets, each
 // bucket holding a count and a mass.  Masses are 64-bit integers (e * 2^40), so sums do
 // not depend on the order of additions and a row's token does not depend on the batch.
 //
-// One block per row.  Rows with temperature < 1e-5 take the largest logit.
+// How the work is laid out (a vocabulary of 150,000 and a handful of rows would otherwise
+// keep a handful of SMs busy for milliseconds):
+//   * a row is taken by a cluster of 1, 2, 4 or 8 CTAs, each with its own stretch of the
+//     vocabulary; after every pass each CTA adds up all CTAs' bucket tables through
+//     distributed shared memory and comes to the same decision as the others;
+//   * e_i is computed once, in the pass that also fills the first level's table, and kept in a
+//     float32 scratch row; that table serves all descents (top-k, top-p, the final walk), and
+//     the later levels only look at the scratch row's bits;
+//   * a warp adds its 32 elements to a table of its own: lanes with the same bucket are found
+//     with a ballot and summed with a warp reduction, so no atomic operation is needed.
 #include "common.cuh"
 
 #define SMP_THREADS 1024
+#define SMP_WARPS (SMP_THREADS / 32)
 #define SMP_FIXED 1099511627776.0f  // 2^40
+#define SMP_MAX_CLUSTER 8
 
 typedef unsigned long long u64;
 
-__device__ __noinline__ float smp_elem(float logit, float temperature, float zmax) {
+__device__ __forceinline__ float smp_elem(float logit, float temperature, float zmax) {
     const float z = logit / temperature;
     if (!(z == z)) return 0.0f;
     return expf(z - zmax);
@@ -26,43 +37,169 @@ __device__ __noinline__ float smp_elem(float logit, float temperature, float zma
 
 __device__ __forceinline__ u64 smp_fixed(float e) { return __float2ull_rz(e * SMP_FIXED); }
 
-__device__ __forceinline__ u64 smp_block_sum_u64(u64 v, u64* sh /* 32 */) {
-    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
-#pragma unroll
-    for (int o = 16; o > 0; o >>= 1) v += __shfl_xor_sync(0xffffffffu, v, o);
-    __syncthreads();
-    if (lane == 0) sh[warp] = v;
-    __syncthreads();
-    u64 r = lane < (blockDim.x >> 5) ? sh[lane] : 0ull;
-#pragma unroll
-    for (int o = 16; o > 0; o >>= 1) r += __shfl_xor_sync(0xffffffffu, r, o);
+// ---- the cluster -------------------------------------------------------------------------------------------
+__device__ __forceinline__ unsigned smp_cluster_rank() {
+    unsigned r;
+    asm volatile("mov.u32 %0, %%cluster_ctarank;" : "=r"(r));
     return r;
 }
+__device__ __forceinline__ unsigned smp_cluster_size() {
+    unsigned r;
+    asm volatile("mov.u32 %0, %%cluster_nctarank;" : "=r"(r));
+    return r;
+}
+__device__ __forceinline__ void smp_cluster_sync() {
+    asm volatile("barrier.cluster.arrive.release.aligned;\n\tbarrier.cluster.wait.acquire.aligned;" ::: "memory");
+}
+template <typename T>
+__device__ __forceinline__ T smp_remote(const T* local, unsigned rank) {   // the same variable in another CTA of the cluster
+    const unsigned addr = (unsigned)__cvta_generic_to_shared(local);
+    unsigned remote;
+    asm volatile("mapa.shared::cluster.u32 %0, %1, %2;" : "=r"(remote) : "r"(addr), "r"(rank));
+    T v;
+    if constexpr (sizeof(T) == 8) {
+        unsigned long long raw;
+        asm volatile("ld.shared::cluster.u64 %0, [%1];" : "=l"(raw) : "r"(remote) : "memory");
+        v = *reinterpret_cast<T*>(&raw);
+    } else {
+        unsigned raw;
+        asm volatile("ld.shared::cluster.u32 %0, [%1];" : "=r"(raw) : "r"(remote) : "memory");
+        v = *reinterpret_cast<T*>(&raw);
+    }
+    return v;
+}
+
+// What a CTA shows the others of its cluster: two copies, used in turn, so that one cluster barrier per exchange is
+// enough (a CTA may fill the next copy while a slower one still reads the last).
+struct SmpBoard {
+    unsigned int cnt[256];
+    u64 mass[256];
+    u64 sums[2];        // two numbers of a plain sum (min-p's count and mass; the matches of the last scan)
+    float best;         // largest logit of this CTA's stretch, and its lowest index
+    int best_at;
+};
 
 struct SmpShared {
-    unsigned int cnt[256];
+    SmpBoard board[2];
+    unsigned int cnt0[256];   // the first level's table of the whole row
+    u64 mass0[256];
+    unsigned int cnt[256];    // the table of the whole row after the last pass
     u64 mass[256];
     u64 red[32];
     float fred[32];
     int ired[32];
-    // result of a descent step, written by thread 0
-    int found;
-    int bucket;
-    unsigned int cnt_above;
-    u64 mass_above;
-    unsigned int c_tau;
     int scan[SMP_THREADS];
+    // a descent step's answer, written by thread 0
+    int found, bucket;
+    unsigned int cnt_above, c_tau;
+    u64 mass_above;
 };
+
+struct SmpCtx {
+    SmpShared* sh;
+    unsigned int* warp_cnt;   // [SMP_WARPS][256], dynamic shared memory
+    u64* warp_mass;           // [SMP_WARPS][256]
+    unsigned rank, size;
+    int turn;                 // which copy of the board the next exchange uses
+    int lo, hi;               // this CTA's stretch of the vocabulary
+};
+
+// one element per lane into the warp's own table: lanes with the same bucket are summed first
+__device__ __forceinline__ void smp_warp_add(unsigned int* wc, u64* wm, bool active, int bucket, u64 mass) {
+    const int lane = threadIdx.x & 31;
+    unsigned todo = __ballot_sync(0xffffffffu, active);
+    while (todo) {
+        const int leader = __ffs(todo) - 1;
+        const int lb = __shfl_sync(0xffffffffu, bucket, leader);
+        const bool mine = active && bucket == lb;
+        const unsigned grp = __ballot_sync(0xffffffffu, mine);
+        // a mass is below 2^41: twenty low bits and twenty-one high bits, each summed over 32 lanes in 32 bits
+        const unsigned lo = __reduce_add_sync(0xffffffffu, mine ? (unsigned)(mass & 0xFFFFFu) : 0u);
+        const unsigned hi = __reduce_add_sync(0xffffffffu, mine ? (unsigned)(mass >> 20) : 0u);
+        if (lane == leader) {
+            wc[lb] += (unsigned)__popc(grp);
+            wm[lb] += ((u64)hi << 20) + lo;
+        }
+        todo &= ~grp;
+    }
+    __syncwarp();   // the next call's leader may be another lane with the same bucket
+}
+
+__device__ __forceinline__ void smp_clear_warp_tables(const SmpCtx& c) {
+    for (int i = threadIdx.x; i < SMP_WARPS * 256; i += SMP_THREADS) { c.warp_cnt[i] = 0; c.warp_mass[i] = 0; }
+    __syncthreads();
+}
+
+// the warps' tables -> this CTA's board -> the row's table in sh->cnt / sh->mass of every CTA of the cluster
+__device__ void smp_merge_tables(SmpCtx& c) {
+    SmpShared* sh = c.sh;
+    __syncthreads();
+    SmpBoard* board = &sh->board[c.turn];
+    for (int b = threadIdx.x; b < 256; b += SMP_THREADS) {
+        unsigned int n = 0;
+        u64 m = 0;
+        for (int w = 0; w < SMP_WARPS; ++w) { n += c.warp_cnt[w * 256 + b]; m += c.warp_mass[w * 256 + b]; }
+        board->cnt[b] = n;
+        board->mass[b] = m;
+    }
+    if (c.size > 1) smp_cluster_sync(); else __syncthreads();
+    for (int b = threadIdx.x; b < 256; b += SMP_THREADS) {
+        unsigned int n = 0;
+        u64 m = 0;
+        for (unsigned r = 0; r < c.size; ++r) {
+            n += c.size > 1 ? smp_remote(&board->cnt[b], r) : board->cnt[b];
+            m += c.size > 1 ? smp_remote(&board->mass[b], r) : board->mass[b];
+        }
+        sh->cnt[b] = n;
+        sh->mass[b] = m;
+    }
+    c.turn ^= 1;
+    __syncthreads();
+}
+
+// two numbers summed over the block and then over the cluster; every thread gets both sums
+__device__ void smp_sum2(SmpCtx& c, u64 a, u64 b, u64* a_out, u64* b_out) {
+    SmpShared* sh = c.sh;
+    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) { a += __shfl_xor_sync(0xffffffffu, a, o); b += __shfl_xor_sync(0xffffffffu, b, o); }
+    __syncthreads();
+    if (lane == 0) sh->red[warp] = a;
+    __syncthreads();
+    u64 ta = 0;
+    if (threadIdx.x == 0) for (int w = 0; w < SMP_WARPS; ++w) ta += sh->red[w];
+    __syncthreads();
+    if (lane == 0) sh->red[warp] = b;
+    __syncthreads();
+    SmpBoard* board = &sh->board[c.turn];
+    if (threadIdx.x == 0) {
+        u64 tb = 0;
+        for (int w = 0; w < SMP_WARPS; ++w) tb += sh->red[w];
+        board->sums[0] = ta;
+        board->sums[1] = tb;
+    }
+    if (c.size > 1) smp_cluster_sync(); else __syncthreads();
+    u64 sa = 0, sb = 0;
+    for (unsigned r = 0; r < c.size; ++r) {
+        sa += c.size > 1 ? smp_remote(&board->sums[0], r) : board->sums[0];
+        sb += c.size > 1 ? smp_remote(&board->sums[1], r) : board->sums[1];
+    }
+    c.turn ^= 1;
+    *a_out = sa;
+    *b_out = sb;
+    __syncthreads();
+}
 
 enum { SMP_COUNT_GE = 0, SMP_MASS_GE = 1, SMP_MASS_GT = 2 };
 
 // Walk the sorted order (descending e) until the condition holds:
 //   COUNT_GE: rank + 1 >= goal;  MASS_GE: mass up to and including the element >= goal;  MASS_GT: > goal.
 // Returns the element's key `tau`, the count and mass of elements with key > tau, and how many share tau.
-// found == 0: the condition never holds (the goal exceeds the totals).
-__device__ void smp_descend(const float* __restrict__ row, int vocab, float temperature, float zmax, int mode,
-                            u64 goal, SmpShared* sh, unsigned int* tau_out, unsigned int* cnt_above_out,
-                            u64* mass_above_out, unsigned int* c_tau_out, int* found_out) {
+// found == 0: the condition never holds (the goal exceeds the totals).  The first level reads the table that the
+// pass over the logits made; the others make theirs from the bits of the scratch row.
+__device__ void smp_descend(SmpCtx& c, const float* __restrict__ e_row, int mode, u64 goal, unsigned int* tau_out,
+                            unsigned int* cnt_above_out, u64* mass_above_out, unsigned int* c_tau_out, int* found_out) {
+    SmpShared* sh = c.sh;
     unsigned int prefix = 0, prefix_mask = 0;
     unsigned int cnt_above = 0;
     u64 mass_above = 0;
@@ -70,46 +207,44 @@ __device__ void smp_descend(const float* __restrict__ row, int vocab, float temp
     int found = 1;
     for (int level = 0; level < 4 && found; ++level) {
         const int shift = 24 - 8 * level;
-        for (int b = threadIdx.x; b < 256; b += blockDim.x) { sh->cnt[b] = 0; sh->mass[b] = 0; }
-        __syncthreads();
-        int cur = -1;
-        unsigned int cur_cnt = 0;
-        u64 cur_mass = 0;
-        for (int i = threadIdx.x; i < vocab; i += blockDim.x) {
-            const float e = smp_elem(row[i], temperature, zmax);
-            const unsigned int key = __float_as_uint(e);
-            if ((key & prefix_mask) != prefix) continue;
-            const int b = (key >> shift) & 255;
-            if (b != cur) {
-                if (cur >= 0) { atomicAdd(&sh->cnt[cur], cur_cnt); atomicAdd(&sh->mass[cur], cur_mass); }
-                cur = b; cur_cnt = 0; cur_mass = 0;
+        const unsigned int* cnt = sh->cnt0;
+        const u64* mass = sh->mass0;
+        if (level > 0) {
+            smp_clear_warp_tables(c);
+            unsigned int* wc = c.warp_cnt + (threadIdx.x >> 5) * 256;
+            u64* wm = c.warp_mass + (threadIdx.x >> 5) * 256;
+            for (int i0 = c.lo; i0 < c.hi; i0 += SMP_THREADS) {   // the same number of rounds for every lane of a warp
+                const int i = i0 + threadIdx.x;
+                const float e = i < c.hi ? e_row[i] : 0.0f;
+                const unsigned int key = __float_as_uint(e);
+                const bool active = i < c.hi && (key & prefix_mask) == prefix;
+                if (__any_sync(0xffffffffu, active)) smp_warp_add(wc, wm, active, (key >> shift) & 255, smp_fixed(e));
             }
-            cur_cnt += 1;
-            cur_mass += smp_fixed(e);
+            smp_merge_tables(c);
+            cnt = sh->cnt;
+            mass = sh->mass;
         }
-        if (cur >= 0) { atomicAdd(&sh->cnt[cur], cur_cnt); atomicAdd(&sh->mass[cur], cur_mass); }
-        __syncthreads();
         if (threadIdx.x == 0) {
-            unsigned int c = cnt_above;
+            unsigned int n = cnt_above;
             u64 m = mass_above;
             int hit = -1;
             for (int b = 255; b >= 0; --b) {
-                const unsigned int cb = sh->cnt[b];
+                const unsigned int cb = cnt[b];
                 if (cb == 0) continue;
-                const u64 mb = sh->mass[b];
+                const u64 mb = mass[b];
                 bool ok;
-                if (mode == SMP_COUNT_GE) ok = (u64)c + cb >= goal;
+                if (mode == SMP_COUNT_GE) ok = (u64)n + cb >= goal;
                 else if (mode == SMP_MASS_GE) ok = m + mb >= goal;
                 else ok = m + mb > goal;
                 if (ok) { hit = b; break; }
-                c += cb;
+                n += cb;
                 m += mb;
             }
             sh->found = hit >= 0;
             sh->bucket = hit;
-            sh->cnt_above = c;
+            sh->cnt_above = n;
             sh->mass_above = m;
-            sh->c_tau = hit >= 0 ? sh->cnt[hit] : 0;
+            sh->c_tau = hit >= 0 ? cnt[hit] : 0;
         }
         __syncthreads();
         found = sh->found;
@@ -132,18 +267,30 @@ __device__ void smp_descend(const float* __restrict__ row, int vocab, float temp
 __global__ void __launch_bounds__(SMP_THREADS) sample_kernel(
     const float* __restrict__ logits, long ld, int vocab, const float* __restrict__ temperature,
     const int* __restrict__ top_k, const float* __restrict__ top_p, const float* __restrict__ min_p,
-    const float* __restrict__ uniform, int* __restrict__ out) {
+    const float* __restrict__ uniform, float* __restrict__ scratch, int* __restrict__ out) {
     __shared__ SmpShared sh;
+    extern __shared__ __align__(16) unsigned char smp_dynamic[];
     ib_grid_dependency_sync();
-    const int r = blockIdx.x;
+    SmpCtx c;
+    c.sh = &sh;
+    c.warp_mass = reinterpret_cast<u64*>(smp_dynamic);
+    c.warp_cnt = reinterpret_cast<unsigned int*>(smp_dynamic + (size_t)SMP_WARPS * 256 * sizeof(u64));
+    c.size = smp_cluster_size();
+    c.rank = smp_cluster_rank();
+    c.turn = 0;
+    const int r = blockIdx.x / c.size;
+    const int stretch = (vocab + (int)c.size - 1) / (int)c.size;
+    c.lo = min(vocab, (int)c.rank * stretch);
+    c.hi = min(vocab, c.lo + stretch);
     const float* row = logits + (long)r * ld;
+    float* e_row = scratch + (long)r * vocab;
     const float T = temperature[r];
     const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
 
     // largest logit and its lowest index (greedy answer, and z_max for the softmax)
     float bv = -INFINITY;
     int bi = 0x7fffffff;
-    for (int i = threadIdx.x; i < vocab; i += blockDim.x) {
+    for (int i = c.lo + threadIdx.x; i < c.hi; i += SMP_THREADS) {
         const float v = row[i];
         if (v == v && (v > bv || bi == 0x7fffffff)) { bv = v; bi = i; }
     }
@@ -156,30 +303,63 @@ __global__ void __launch_bounds__(SMP_THREADS) sample_kernel(
     if (lane == 0) { sh.fred[warp] = bv; sh.ired[warp] = bi; }
     __syncthreads();
     if (warp == 0) {
-        bv = lane < (blockDim.x >> 5) ? sh.fred[lane] : -INFINITY;
-        bi = lane < (blockDim.x >> 5) ? sh.ired[lane] : 0x7fffffff;
+        bv = sh.fred[lane];
+        bi = sh.ired[lane];
 #pragma unroll
         for (int o = 16; o > 0; o >>= 1) {
             const float ov = __shfl_xor_sync(0xffffffffu, bv, o);
             const int oi = __shfl_xor_sync(0xffffffffu, bi, o);
             if (ov > bv || (ov == bv && oi < bi)) { bv = ov; bi = oi; }
         }
-        if (lane == 0) { sh.fred[0] = bv; sh.ired[0] = bi == 0x7fffffff ? 0 : bi; }
+        if (lane == 0) { sh.board[c.turn].best = bv; sh.board[c.turn].best_at = bi; }
     }
-    __syncthreads();
-    const float lmax = sh.fred[0];
-    const int imax = sh.ired[0];
+    if (c.size > 1) smp_cluster_sync(); else __syncthreads();
+    float lmax = -INFINITY;
+    int imax = 0x7fffffff;
+    for (unsigned k = 0; k < c.size; ++k) {   // the same answer in every CTA
+        const float ov = c.size > 1 ? smp_remote(&sh.board[c.turn].best, k) : sh.board[c.turn].best;
+        const int oi = c.size > 1 ? smp_remote(&sh.board[c.turn].best_at, k) : sh.board[c.turn].best_at;
+        if (ov > lmax || (ov == lmax && oi < imax)) { lmax = ov; imax = oi; }
+    }
+    if (imax == 0x7fffffff) imax = 0;
+    c.turn ^= 1;
     __syncthreads();
     if (T < 1e-5f || !(lmax > -INFINITY)) {
-        if (threadIdx.x == 0) out[r] = imax;
+        if (threadIdx.x == 0 && c.rank == 0) out[r] = imax;
+        // a CTA's board may still be read by the others: nobody leaves before everybody has read
+        if (c.size > 1) smp_cluster_sync();
         return;
     }
     const float zmax = lmax / T;
 
-    // total mass
+    // e_i into the scratch row, and the first level's table (which holds the total mass too)
+    smp_clear_warp_tables(c);
+    {
+        unsigned int* wc = c.warp_cnt + warp * 256;
+        u64* wm = c.warp_mass + warp * 256;
+        for (int i0 = c.lo; i0 < c.hi; i0 += SMP_THREADS) {
+            const int i = i0 + threadIdx.x;
+            const bool active = i < c.hi;
+            const float e = active ? smp_elem(row[i], T, zmax) : 0.0f;
+            if (active) e_row[i] = e;
+            smp_warp_add(wc, wm, active, (int)(__float_as_uint(e) >> 24), smp_fixed(e));
+        }
+    }
+    __syncthreads();   // this CTA's stretch of the scratch row is read by other threads from here on
+    smp_merge_tables(c);
     u64 part = 0;
-    for (int i = threadIdx.x; i < vocab; i += blockDim.x) part += smp_fixed(smp_elem(row[i], T, zmax));
-    const u64 total = smp_block_sum_u64(part, sh.red);
+    for (int b = threadIdx.x; b < 256; b += SMP_THREADS) {
+        sh.cnt0[b] = sh.cnt[b];
+        sh.mass0[b] = sh.mass[b];
+    }
+    __syncthreads();
+    if (threadIdx.x == 0) {
+        for (int b = 0; b < 256; ++b) part += sh.mass0[b];
+        sh.red[0] = part;
+    }
+    __syncthreads();
+    const u64 total = sh.red[0];
+    __syncthreads();
 
     unsigned int keep_cnt = vocab;
     u64 keep_mass = total;
@@ -188,7 +368,7 @@ __global__ void __launch_bounds__(SMP_THREADS) sample_kernel(
     int found;
     const int k = top_k[r];
     if (k > 0 && k < vocab) {
-        smp_descend(row, vocab, T, zmax, SMP_COUNT_GE, (u64)k, &sh, &tau, &ca, &ma, &ct, &found);
+        smp_descend(c, e_row, SMP_COUNT_GE, (u64)k, &tau, &ca, &ma, &ct, &found);
         if (found) {
             keep_cnt = k;
             keep_mass = ma + (u64)(k - ca) * smp_fixed(__uint_as_float(tau));
@@ -197,7 +377,7 @@ __global__ void __launch_bounds__(SMP_THREADS) sample_kernel(
     const float tp = top_p[r];
     if (tp < 1.0f) {
         const u64 goal = (u64)((double)tp * (double)total);
-        smp_descend(row, vocab, T, zmax, SMP_MASS_GE, goal, &sh, &tau, &ca, &ma, &ct, &found);
+        smp_descend(c, e_row, SMP_MASS_GE, goal, &tau, &ca, &ma, &ct, &found);
         if (found) {
             const u64 pm = smp_fixed(__uint_as_float(tau));
             u64 n = 1;
@@ -210,23 +390,23 @@ __global__ void __launch_bounds__(SMP_THREADS) sample_kernel(
     const float mp = min_p[r];
     if (mp > 0.0f) {
         // e_max is 1, so "p >= min_p * p_max" is "e >= min_p"
-        unsigned int c = 0;
-        u64 m = 0;
-        for (int i = threadIdx.x; i < vocab; i += blockDim.x) {
-            const float e = smp_elem(row[i], T, zmax);
-            if (e >= mp) { c += 1; m += smp_fixed(e); }
+        u64 n = 0, m = 0;
+        for (int i = c.lo + threadIdx.x; i < c.hi; i += SMP_THREADS) {
+            const float e = e_row[i];
+            if (e >= mp) { n += 1; m += smp_fixed(e); }
         }
-        const u64 cm = smp_block_sum_u64((u64)c, sh.red);
-        const u64 mm = smp_block_sum_u64(m, sh.red);
+        u64 cm, mm;
+        smp_sum2(c, n, m, &cm, &mm);
         if (cm > 0 && cm < keep_cnt) { keep_cnt = (unsigned int)cm; keep_mass = mm; }
     }
 
     // the element of the kept list whose interval of cumulative mass holds u * keep_mass
     u64 target = (u64)((double)uniform[r] * (double)keep_mass);
     if (keep_mass > 0 && target >= keep_mass) target = keep_mass - 1;
-    smp_descend(row, vocab, T, zmax, SMP_MASS_GT, target, &sh, &tau, &ca, &ma, &ct, &found);
+    smp_descend(c, e_row, SMP_MASS_GT, target, &tau, &ca, &ma, &ct, &found);
     if (!found) {  // no mass at all: the most probable token
-        if (threadIdx.x == 0) out[r] = imax;
+        if (threadIdx.x == 0 && c.rank == 0) out[r] = imax;
+        if (c.size > 1) smp_cluster_sync();
         return;
     }
     const u64 pm = smp_fixed(__uint_as_float(tau));
@@ -234,36 +414,70 @@ __global__ void __launch_bounds__(SMP_THREADS) sample_kernel(
     if (n >= ct) n = ct - 1;
     if (ca + n >= keep_cnt) n = keep_cnt > ca ? keep_cnt - 1 - ca : 0;
 
-    // the n-th token, in order of token id, whose key is tau
-    const int chunk = (vocab + blockDim.x - 1) / blockDim.x;
-    const int i0 = threadIdx.x * chunk, i1 = min(vocab, i0 + chunk);
+    // the n-th token, in order of token id, whose key is tau: every thread counts a stretch of its own, the stretches
+    // before it (in its CTA, and in the CTAs with lower ranks) tell it where its matches stand
+    const int chunk = (c.hi - c.lo + SMP_THREADS - 1) / SMP_THREADS;
+    const int i0 = min(c.hi, c.lo + (int)threadIdx.x * chunk), i1 = min(c.hi, i0 + chunk);
     int mine = 0;
-    for (int i = i0; i < i1; ++i) mine += (__float_as_uint(smp_elem(row[i], T, zmax)) == tau);
+    for (int i = i0; i < i1; ++i) mine += (__float_as_uint(e_row[i]) == tau);
     sh.scan[threadIdx.x] = mine;
     __syncthreads();
+    SmpBoard* board = &sh.board[c.turn];
     if (threadIdx.x == 0) {
         int run = 0;
-        for (int t = 0; t < blockDim.x; ++t) { const int c = sh.scan[t]; sh.scan[t] = run; run += c; }
+        for (int t = 0; t < SMP_THREADS; ++t) { const int v = sh.scan[t]; sh.scan[t] = run; run += v; }
+        board->sums[0] = (u64)run;
     }
-    __syncthreads();
-    const int before = sh.scan[threadIdx.x];
-    if ((u64)before <= n && n < (u64)before + mine) {
-        int seen = before;
+    if (c.size > 1) smp_cluster_sync(); else __syncthreads();
+    u64 before = (u64)sh.scan[threadIdx.x];
+    for (unsigned k2 = 0; k2 < c.rank; ++k2) before += smp_remote(&board->sums[0], k2);
+    if (before <= n && n < before + (u64)mine) {
+        u64 seen = before;
         for (int i = i0; i < i1; ++i) {
-            if (__float_as_uint(smp_elem(row[i], T, zmax)) == tau) {
-                if ((u64)seen == n) { out[r] = i; break; }
+            if (__float_as_uint(e_row[i]) == tau) {
+                if (seen == n) { out[r] = i; break; }
                 ++seen;
             }
         }
     }
+    if (c.size > 1) smp_cluster_sync();   // nobody leaves while its board may still be read
 }
 
+// How many CTAs take a row: as many as still give every CTA an SM (the kernel keeps an SM to itself), up to eight.
+static int smp_cluster_for(int n_rows) {
+    int sms = 148, dev = 0;
+    if (cudaGetDevice(&dev) == cudaSuccess) cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev);
+    int size = 1;
+    while (size < SMP_MAX_CLUSTER && (long)n_rows * size * 2 <= sms) size *= 2;
+    return size;
+}
+
+// scratch: float32 [n_rows, vocab] (e_i of every row).  cluster: CTAs per row (1, 2, 4 or 8), 0 lets the function choose.
 IB_EXPORT int ib_sample(const float* logits, long ld, int n_rows, int vocab, const float* temperature,
-                        const int* top_k, const float* top_p, const float* min_p, const float* uniform, int* out,
-                        cudaStream_t stream) {
+                        const int* top_k, const float* top_p, const float* min_p, const float* uniform, float* scratch,
+                        int cluster, int* out, cudaStream_t stream) {
     if (n_rows <= 0) return IB_OK;
-    if (vocab <= 0) return IB_ERR_ARGUMENT;
-    sample_kernel<<<n_rows, SMP_THREADS, 0, stream>>>(logits, ld, vocab, temperature, top_k, top_p, min_p, uniform,
-                                                      out);
-    return ib_launch_status();
+    if (vocab <= 0 || scratch == nullptr) return IB_ERR_ARGUMENT;
+    if (cluster == 0) cluster = smp_cluster_for(n_rows);
+    if (cluster != 1 && cluster != 2 && cluster != 4 && cluster != 8) return IB_ERR_ARGUMENT;
+    const size_t smem = (size_t)SMP_WARPS * 256 * (sizeof(u64) + sizeof(unsigned int));
+    static IbDeviceSet configured;   // the attribute is kept per device
+    if (const int e = ib_allow_dynamic_smem(configured, sample_kernel, smem)) return e;
+    cudaLaunchConfig_t cfg = {};
+    cfg.gridDim = dim3((unsigned)n_rows * cluster);
+    cfg.blockDim = dim3(SMP_THREADS);
+    cfg.dynamicSmemBytes = smem;
+    cfg.stream = stream;
+    cudaLaunchAttribute attr[2];
+    attr[0].id = cudaLaunchAttributeClusterDimension;
+    attr[0].val.clusterDim.x = cluster;
+    attr[0].val.clusterDim.y = 1;
+    attr[0].val.clusterDim.z = 1;
+    attr[1].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    attr[1].val.programmaticStreamSerializationAllowed = 1;
+    cfg.attrs = attr;
+    cfg.numAttrs = ib_pdl_enabled ? 2 : 1;
+    const cudaError_t e = cudaLaunchKernelEx(&cfg, sample_kernel, logits, ld, vocab, temperature, top_k, top_p, min_p,
+                                             uniform, scratch, out);
+    return e == cudaSuccess ? ib_launch_status() : (int)e;
 }

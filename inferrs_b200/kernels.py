@@ -64,7 +64,7 @@ _SIGNATURES = {
     "ib_penalties": [c_void_p, c_long, c_int, c_int, c_void_p, c_int, c_void_p, c_void_p, c_void_p, c_void_p,
                      c_void_p],
     "ib_sample": [c_void_p, c_long, c_int, c_int, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p,
-                  c_void_p],
+                  c_int, c_void_p, c_void_p],
 }
 
 _LIBS = {}
@@ -891,9 +891,11 @@ def penalties(logits: torch.Tensor, prev: torch.Tensor, n_prev: torch.Tensor, re
 
 
 def sample(logits: torch.Tensor, temperature: torch.Tensor, top_k: torch.Tensor, top_p: torch.Tensor,
-           min_p: torch.Tensor, uniform: torch.Tensor, out: torch.Tensor, act_dtype: torch.dtype = torch.float32):
+           min_p: torch.Tensor, uniform: torch.Tensor, out: torch.Tensor, act_dtype: torch.dtype = torch.float32,
+           cluster: int = 0):
     """One token per row of float32 logits [R, V]: largest logit where temperature < 1e-5, else
-    temperature, top-k, top-p, min-p and the inverse-CDF walk with the row's random number ``uniform``."""
+    temperature, top-k, top-p, min-p and the inverse-CDF walk with the row's random number ``uniform``.
+    ``cluster``: CTAs that share a row (1, 2, 4 or 8; 0 lets the kernel library choose by the number of rows)."""
     _need(logits, "logits", (torch.float32,), 2)
     r = logits.shape[0]
     for name, t, dt in (("temperature", temperature, torch.float32), ("top_k", top_k, torch.int32),
@@ -902,8 +904,10 @@ def sample(logits: torch.Tensor, temperature: torch.Tensor, top_k: torch.Tensor,
         _need(t, name, (dt,), 1)
         if t.shape[0] != r:
             raise KernelError(f"sample: {name} has {t.shape[0]} entries for {r} rows")
+    scratch = torch.empty((r, logits.shape[1]), dtype=torch.float32, device=logits.device)
     _check(_core(act_dtype).ib_sample(_p(logits), logits.shape[1], r, logits.shape[1], _p(temperature), _p(top_k),
-                                      _p(top_p), _p(min_p), _p(uniform), _p(out), _stream()), "sample")
+                                      _p(top_p), _p(min_p), _p(uniform), _p(scratch), int(cluster), _p(out), _stream()),
+           "sample")
 
 
 _GEMM_LIB = None

@@ -201,7 +201,7 @@ def penalties(logits, prev, n_prev, repetition, frequency, presence, act_dtype=N
             logits[r, t] = v
 
 
-def sample(logits, temperature, top_k, top_p, min_p, uniform, out, act_dtype=None):
+def sample(logits, temperature, top_k, top_p, min_p, uniform, out, act_dtype=None, cluster=0):
     for r in range(logits.shape[0]):
         t = float(temperature[r])
         if t < 1e-5:

@@ -41,6 +41,39 @@ def test_sample_kernel_matches_plain_sampler(vocab, opts):
     assert got == want
 
 
+@pytest.mark.parametrize("vocab", [263, 5000, 151936])
+def test_a_row_shared_by_one_to_eight_ctas_gives_the_same_token(vocab):
+    """The selection kernel cuts a row's vocabulary over a cluster of CTAs when there are few rows: whatever the
+    cluster, every row gets the token that the plain selection gives (rows with every option, equal probabilities,
+    a row of one value, greedy rows)."""
+    import kernel_refs as R
+    from inferrs_b200 import kernels as K
+    rows = 10
+    logits = _logits(rows, vocab, seed=11).cuda()
+    logits[3, 10] = logits[3, 200] = logits[3].max() + 1.0
+    logits[4, :] = 0.25                                        # all equal: the walk counts token ids
+    temperature = torch.tensor([0.8, 0.7, 1.3, 1.0, 1.0, 0.0, 0.7, 2.0, 0.7, 0.5]).cuda()
+    top_k = torch.tensor([0, 50, 0, 7, 0, 50, 1, 0, 1000, 3], dtype=torch.int32).cuda()
+    top_p = torch.tensor([1.0, 0.9, 0.6, 1.0, 1.0, 0.9, 1.0, 0.999, 0.5, 1.0]).cuda()
+    min_p = torch.tensor([0.0, 0.0, 0.0, 0.2, 0.0, 0.0, 0.0, 0.0, 0.01, 0.0]).cuda()
+    # rows that walk the whole of a large vocabulary are left out of the comparison with the plain selection: far
+    # down the tail the kernel's fixed-point masses and the plain float64 sums part (see plain_sampler's docstring)
+    exact = [r for r in range(rows) if vocab < 1000 or r not in (0, 7)]
+    for draw in (0.0, 0.37, 0.999999):
+        uniform = torch.full((rows,), draw).cuda()
+        want = torch.empty(rows, dtype=torch.int32, device="cuda")
+        R.sample(logits, temperature, top_k, top_p, min_p, uniform, want)
+        alone = torch.full((rows,), -1, dtype=torch.int32, device="cuda")
+        K.sample(logits, temperature, top_k, top_p, min_p, uniform, alone, cluster=1)
+        assert [alone.tolist()[r] for r in exact] == [want.tolist()[r] for r in exact], f"draw {draw}"
+        for cluster in (2, 4, 8, 0):
+            got = torch.full((rows,), -1, dtype=torch.int32, device="cuda")
+            K.sample(logits, temperature, top_k, top_p, min_p, uniform, got, cluster=cluster)
+            assert got.tolist() == alone.tolist(), f"cluster {cluster}, draw {draw}"
+    with pytest.raises(K.KernelError):
+        K.sample(logits, temperature, top_k, top_p, min_p, uniform, got, cluster=3)
+
+
 def test_penalties_and_mixed_rows():
     from inferrs_b200.sampling.sampler import Sampler
     vocab, rows = 2000, 6
