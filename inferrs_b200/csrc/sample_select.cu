@@ -18,14 +18,16 @@
 //   * e_i is computed once, in the pass that also fills the first level's table, and kept in a
 //     float32 scratch row; that table serves all descents (top-k, top-p, the final walk), and
 //     the later levels only look at the scratch row's bits;
-//   * a warp adds its 32 elements to a table of its own: lanes with the same bucket are found
-//     with a ballot and summed with a warp reduction, so no atomic operation is needed.
+//   * a warp adds its 32 elements to a table of its own: lanes that share a bucket are found
+//     with a ballot and summed with a warp reduction, so that atomic operations are left for
+//     lanes whose bucket no other lane has.
 #include "common.cuh"
 
 #define SMP_THREADS 1024
 #define SMP_WARPS (SMP_THREADS / 32)
 #define SMP_FIXED 1099511627776.0f  // 2^40
 #define SMP_MAX_CLUSTER 8
+#define SMP_UNROLL 4                   // loads that a thread has on their way in the passes over a row
 
 typedef unsigned long long u64;
 
@@ -104,11 +106,15 @@ struct SmpCtx {
     int lo, hi;               // this CTA's stretch of the vocabulary
 };
 
-// one element per lane into the warp's own table: lanes with the same bucket are summed first
+// One element per lane into the warp's own table.  Where most lanes share a bucket or two (the first level: e's
+// exponents; a row of equal logits at every level) those lanes are found with a ballot and summed with a warp
+// reduction; what is left after two such rounds (lanes with buckets of their own: the later levels, where the bits
+// are a mantissa's) goes in with shared-memory atomics, which then meet no other lane.
 __device__ __forceinline__ void smp_warp_add(unsigned int* wc, u64* wm, bool active, int bucket, u64 mass) {
     const int lane = threadIdx.x & 31;
     unsigned todo = __ballot_sync(0xffffffffu, active);
-    while (todo) {
+#pragma unroll 1
+    for (int round = 0; round < 2 && todo; ++round) {
         const int leader = __ffs(todo) - 1;
         const int lb = __shfl_sync(0xffffffffu, bucket, leader);
         const bool mine = active && bucket == lb;
@@ -120,9 +126,15 @@ __device__ __forceinline__ void smp_warp_add(unsigned int* wc, u64* wm, bool act
             wc[lb] += (unsigned)__popc(grp);
             wm[lb] += ((u64)hi << 20) + lo;
         }
+        active = active && !mine;
         todo &= ~grp;
     }
-    __syncwarp();   // the next call's leader may be another lane with the same bucket
+    __syncwarp();   // the leaders' plain additions are done before anybody's atomic ones, and before the next call
+    if (active) {
+        atomicAdd(&wc[bucket], 1u);
+        atomicAdd(&wm[bucket], mass);
+    }
+    __syncwarp();
 }
 
 __device__ __forceinline__ void smp_clear_warp_tables(const SmpCtx& c) {
@@ -213,38 +225,73 @@ __device__ void smp_descend(SmpCtx& c, const float* __restrict__ e_row, int mode
             smp_clear_warp_tables(c);
             unsigned int* wc = c.warp_cnt + (threadIdx.x >> 5) * 256;
             u64* wm = c.warp_mass + (threadIdx.x >> 5) * 256;
-            for (int i0 = c.lo; i0 < c.hi; i0 += SMP_THREADS) {   // the same number of rounds for every lane of a warp
-                const int i = i0 + threadIdx.x;
-                const float e = i < c.hi ? e_row[i] : 0.0f;
-                const unsigned int key = __float_as_uint(e);
-                const bool active = i < c.hi && (key & prefix_mask) == prefix;
-                if (__any_sync(0xffffffffu, active)) smp_warp_add(wc, wm, active, (key >> shift) & 255, smp_fixed(e));
+            // the same number of rounds for every lane of a warp; four loads on their way per lane
+            for (int i0 = c.lo; i0 < c.hi; i0 += SMP_UNROLL * SMP_THREADS) {
+                float e[SMP_UNROLL];
+#pragma unroll
+                for (int u = 0; u < SMP_UNROLL; ++u) {
+                    const int i = i0 + u * SMP_THREADS + threadIdx.x;
+                    e[u] = i < c.hi ? e_row[i] : 0.0f;
+                }
+#pragma unroll
+                for (int u = 0; u < SMP_UNROLL; ++u) {
+                    const int i = i0 + u * SMP_THREADS + threadIdx.x;
+                    const unsigned int key = __float_as_uint(e[u]);
+                    const bool active = i < c.hi && (key & prefix_mask) == prefix;
+                    if (__any_sync(0xffffffffu, active)) smp_warp_add(wc, wm, active, (key >> shift) & 255, smp_fixed(e[u]));
+                }
             }
             smp_merge_tables(c);
             cnt = sh->cnt;
             mass = sh->mass;
         }
-        if (threadIdx.x == 0) {
-            unsigned int n = cnt_above;
-            u64 m = mass_above;
+        if (threadIdx.x < 32) {
+            // lane l looks at buckets 255 - 8 l down to 248 - 8 l; what lies before them comes from a scan over the lanes
+            const int lane = threadIdx.x;
+            unsigned int n_loc[8], n_sum = 0;
+            u64 m_loc[8], m_sum = 0;
+#pragma unroll
+            for (int j = 0; j < 8; ++j) {
+                const int b = 255 - (8 * lane + j);
+                n_loc[j] = cnt[b];
+                m_loc[j] = mass[b];
+                n_sum += n_loc[j];
+                m_sum += m_loc[j];
+            }
+            unsigned int n_inc = n_sum;
+            u64 m_inc = m_sum;
+#pragma unroll
+            for (int o = 1; o < 32; o <<= 1) {
+                const unsigned int tn = __shfl_up_sync(0xffffffffu, n_inc, o);
+                const u64 tm = __shfl_up_sync(0xffffffffu, m_inc, o);
+                if (lane >= o) { n_inc += tn; m_inc += tm; }
+            }
+            unsigned int n = cnt_above + (n_inc - n_sum);
+            u64 m = mass_above + (m_inc - m_sum);
             int hit = -1;
-            for (int b = 255; b >= 0; --b) {
-                const unsigned int cb = cnt[b];
-                if (cb == 0) continue;
-                const u64 mb = mass[b];
+            unsigned int hit_cnt = 0;
+#pragma unroll
+            for (int j = 0; j < 8; ++j) {
+                const unsigned int cb = n_loc[j];
+                if (hit >= 0 || cb == 0) continue;
                 bool ok;
                 if (mode == SMP_COUNT_GE) ok = (u64)n + cb >= goal;
-                else if (mode == SMP_MASS_GE) ok = m + mb >= goal;
-                else ok = m + mb > goal;
-                if (ok) { hit = b; break; }
-                n += cb;
-                m += mb;
+                else if (mode == SMP_MASS_GE) ok = m + m_loc[j] >= goal;
+                else ok = m + m_loc[j] > goal;
+                if (ok) { hit = 255 - (8 * lane + j); hit_cnt = cb; }
+                else { n += cb; m += m_loc[j]; }
             }
-            sh->found = hit >= 0;
-            sh->bucket = hit;
-            sh->cnt_above = n;
-            sh->mass_above = m;
-            sh->c_tau = hit >= 0 ? cnt[hit] : 0;
+            // the sums grow from lane to lane, so the first lane with a hit holds the first bucket with one
+            const unsigned who = __ballot_sync(0xffffffffu, hit >= 0);
+            if (who == 0) {
+                if (lane == 0) { sh->found = 0; sh->bucket = -1; sh->c_tau = 0; }
+            } else if (lane == __ffs(who) - 1) {
+                sh->found = 1;
+                sh->bucket = hit;
+                sh->cnt_above = n;
+                sh->mass_above = m;
+                sh->c_tau = hit_cnt;
+            }
         }
         __syncthreads();
         found = sh->found;
@@ -337,12 +384,21 @@ __global__ void __launch_bounds__(SMP_THREADS) sample_kernel(
     {
         unsigned int* wc = c.warp_cnt + warp * 256;
         u64* wm = c.warp_mass + warp * 256;
-        for (int i0 = c.lo; i0 < c.hi; i0 += SMP_THREADS) {
-            const int i = i0 + threadIdx.x;
-            const bool active = i < c.hi;
-            const float e = active ? smp_elem(row[i], T, zmax) : 0.0f;
-            if (active) e_row[i] = e;
-            smp_warp_add(wc, wm, active, (int)(__float_as_uint(e) >> 24), smp_fixed(e));
+        for (int i0 = c.lo; i0 < c.hi; i0 += SMP_UNROLL * SMP_THREADS) {
+            float v[SMP_UNROLL];
+#pragma unroll
+            for (int u = 0; u < SMP_UNROLL; ++u) {
+                const int i = i0 + u * SMP_THREADS + threadIdx.x;
+                v[u] = i < c.hi ? row[i] : 0.0f;
+            }
+#pragma unroll
+            for (int u = 0; u < SMP_UNROLL; ++u) {
+                const int i = i0 + u * SMP_THREADS + threadIdx.x;
+                const bool active = i < c.hi;
+                const float e = active ? smp_elem(v[u], T, zmax) : 0.0f;
+                if (active) e_row[i] = e;
+                smp_warp_add(wc, wm, active, (int)(__float_as_uint(e) >> 24), smp_fixed(e));
+            }
         }
     }
     __syncthreads();   // this CTA's stretch of the scratch row is read by other threads from here on
@@ -353,9 +409,11 @@ __global__ void __launch_bounds__(SMP_THREADS) sample_kernel(
         sh.mass0[b] = sh.mass[b];
     }
     __syncthreads();
-    if (threadIdx.x == 0) {
-        for (int b = 0; b < 256; ++b) part += sh.mass0[b];
-        sh.red[0] = part;
+    if (threadIdx.x < 32) {
+        for (int b = threadIdx.x; b < 256; b += 32) part += sh.mass0[b];
+#pragma unroll
+        for (int o = 16; o > 0; o >>= 1) part += __shfl_xor_sync(0xffffffffu, part, o);
+        if (threadIdx.x == 0) sh.red[0] = part;
     }
     __syncthreads();
     const u64 total = sh.red[0];
@@ -420,16 +478,28 @@ __global__ void __launch_bounds__(SMP_THREADS) sample_kernel(
     const int i0 = min(c.hi, c.lo + (int)threadIdx.x * chunk), i1 = min(c.hi, i0 + chunk);
     int mine = 0;
     for (int i = i0; i < i1; ++i) mine += (__float_as_uint(e_row[i]) == tau);
-    sh.scan[threadIdx.x] = mine;
+    int upto = mine;                       // matches of this warp's lanes up to and including this one
+#pragma unroll
+    for (int o = 1; o < 32; o <<= 1) {
+        const int t = __shfl_up_sync(0xffffffffu, upto, o);
+        if (lane >= o) upto += t;
+    }
+    if (lane == 31) sh.ired[warp] = upto;
     __syncthreads();
     SmpBoard* board = &sh.board[c.turn];
-    if (threadIdx.x == 0) {
-        int run = 0;
-        for (int t = 0; t < SMP_THREADS; ++t) { const int v = sh.scan[t]; sh.scan[t] = run; run += v; }
-        board->sums[0] = (u64)run;
+    if (warp == 0) {                       // the warps' totals: each warp's start, and the CTA's total
+        const int mine_w = sh.ired[lane];
+        int upto_w = mine_w;
+#pragma unroll
+        for (int o = 1; o < 32; o <<= 1) {
+            const int t = __shfl_up_sync(0xffffffffu, upto_w, o);
+            if (lane >= o) upto_w += t;
+        }
+        sh.scan[lane] = upto_w - mine_w;
+        if (lane == 31) board->sums[0] = (u64)upto_w;
     }
     if (c.size > 1) smp_cluster_sync(); else __syncthreads();
-    u64 before = (u64)sh.scan[threadIdx.x];
+    u64 before = (u64)(sh.scan[warp] + upto - mine);
     for (unsigned k2 = 0; k2 < c.rank; ++k2) before += smp_remote(&board->sums[0], k2);
     if (before <= n && n < before + (u64)mine) {
         u64 seen = before;
