@@ -147,13 +147,11 @@ class Engine:
         ids = host = event = None
         if sampling:
             pending = [int(s >= 0) for _, s in sampling]
-            pending_ids = None
-            if any(pending) and any(e.request.params.has_penalty for e, _ in sampling):
-                index = torch.tensor([max(s, 0) for _, s in sampling], dtype=torch.int64, device=self.rt.device)
-                pending_ids = before[1].index_select(0, index)
+            # a pending token is looked up on the device, where the step before left it
+            pending_from = (before[1], [max(s, 0) for _, s in sampling]) if any(pending) else None
             ids = self.sampler.sample(logits, [e.request.params for e, _ in sampling],
                                       [e.request.seed for e, _ in sampling], [e.request for e, _ in sampling],
-                                      pending, pending_ids)
+                                      pending, pending_from=pending_from)
             if self.overlap and ids.device.type == "cuda":
                 # the token ids start their way to pinned memory now; an event says when they are there
                 host = self._pinned.pop() if self._pinned else \

@@ -76,3 +76,26 @@ def uniform_for(seed: int, step: int) -> float:
     x ^= (x << 17) & _M64
     u = ((x * 0x2545F4914F6CDD1D) & _M64) >> 32
     return u / 4294967296.0
+
+
+def uniforms_for(seeds, steps):
+    """:func:`uniform_for` for many (seed, step) pairs at once, with the same bits: 64-bit arithmetic that wraps
+    around, in numpy.  Returns float32 [n]."""
+    import numpy as np
+
+    def splitmix(x):
+        x = (x ^ (x >> np.uint64(30))) * np.uint64(0xBF58476D1CE4E5B9)
+        x = (x ^ (x >> np.uint64(27))) * np.uint64(0x94D049BB133111EB)
+        return x ^ (x >> np.uint64(31))
+
+    with np.errstate(over="ignore"):
+        golden = np.uint64(0x9E3779B97F4A7C15)
+        x = splitmix(np.array([int(s) & _M64 for s in seeds], dtype=np.uint64) + golden)
+        x = splitmix(x + (np.array([int(n) + 1 for n in steps], dtype=np.uint64) * golden))
+        x = np.where(x == 0, np.uint64(0x1234567890ABCDEF), x)
+        x ^= x << np.uint64(13)
+        x ^= x >> np.uint64(7)
+        x ^= x << np.uint64(17)
+        u = (x * np.uint64(0x2545F4914F6CDD1D)) >> np.uint64(32)
+    return (u.astype(np.float64) / 4294967296.0).astype(np.float32)
+

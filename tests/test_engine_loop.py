@@ -54,7 +54,7 @@ class FakeRunner:
 
 
 class FakeSampler:
-    def sample(self, logits, params, seeds, histories, pending=0, pending_ids=None):
+    def sample(self, logits, params, seeds, histories, pending=0, pending_ids=None, pending_from=None):
         return torch.tensor([next_token(int(h)) for h in logits], dtype=torch.int32)
 
 
