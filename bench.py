@@ -8,7 +8,8 @@ Prints one JSON line.  A "step" is one decode step of the batch (default 8 reque
 timed with CUDA events (``ms_per_step_sd``: the spread of five equal parts of them); ``e2e`` is the same
 through ``Engine.step``'s own loop with host token ids in and out; ``prefill`` is a 2,048-token prompt in one
 step; ``roofline`` compares the bytes a decode step must read with the measured copy bandwidth; ``points``
-holds decode rates at batch 1 and 64 with their fractions of that bandwidth, the batch-8 rate with the positions
+holds decode rates at batch 1 and 64 with their fractions of that bandwidth, the end-to-end rate with the command
+line's default sampling instead of greedy choice (``e2e_b8_sampled``), the batch-8 rate with the positions
 of the published checkpoints (40,960: block tables and descriptions ten times as wide), and the two other
 workloads that the baseline names (Qwen3-0.6B shape, 256 requests at once; Qwen3-32B shape, 8 requests of
 8,192 tokens in portions of 2,048), each through the engine's own scheduler.
@@ -260,34 +261,38 @@ def main() -> int:
     frac = hbm_frac(args.batch, ms, ctx_mid)
 
     # end to end: the engine's own loop, host token ids in, host token ids out, every step
-    sp = SamplingParams.greedy(max_tokens=args.steps + args.warmup + 16, ignore_eos=True)  # none ends inside the timed loop
-    for _ in range(args.batch):
-        eng.add_request(prompt(), sp)
-    reqs = list(eng.scheduler.waiting)
-    while any(not r.output for r in reqs):
-        eng.step()
-    for _ in range(args.warmup):
-        eng.step()
-    torch.cuda.synchronize()
-    e2e_parts, n_e2e = [], 0
-    n_loop = args.steps - 1
-    edges = [round(k * n_loop / 5) for k in range(6)]
-    t0 = time.perf_counter()
-    for k in range(5):
-        tk = time.perf_counter()
-        done = 0
-        for _ in range(edges[k + 1] - edges[k]):
-            if not eng.has_work():
-                break
+    def end_to_end(sp):
+        for _ in range(args.batch):
+            eng.add_request(prompt(), sp)
+        reqs = list(eng.scheduler.waiting)
+        while any(not r.output for r in reqs):
             eng.step()
-            done += 1
+        for _ in range(args.warmup):
+            eng.step()
         torch.cuda.synchronize()
-        if done:
-            e2e_parts.append((time.perf_counter() - tk) * 1e3 / done)
-        n_e2e += done
-    e2e_ms = (time.perf_counter() - t0) * 1e3 / max(n_e2e, 1)
-    while eng.has_work():
-        eng.step()
+        parts_ms, n_done = [], 0
+        n_loop = args.steps - 1
+        edges = [round(k * n_loop / 5) for k in range(6)]
+        t0 = time.perf_counter()
+        for k in range(5):
+            tk = time.perf_counter()
+            done = 0
+            for _ in range(edges[k + 1] - edges[k]):
+                if not eng.has_work():
+                    break
+                eng.step()
+                done += 1
+            torch.cuda.synchronize()
+            if done:
+                parts_ms.append((time.perf_counter() - tk) * 1e3 / done)
+            n_done += done
+        ms_step = (time.perf_counter() - t0) * 1e3 / max(n_done, 1)
+        while eng.has_work():
+            eng.step()
+        return ms_step, parts_ms
+
+    n_new = args.steps + args.warmup + 16          # no request ends inside the timed loop
+    e2e_ms, e2e_parts = end_to_end(SamplingParams.greedy(max_tokens=n_new, ignore_eos=True))
     # the step's description as it is copied from pinned host memory: the replayed graph's whole fixed buffer
     graphs = eng.runner.graphs
     meta_ints = graphs.captured[graphs.bucket_for(args.batch)].buffer.numel() if graphs is not None else 0
@@ -313,6 +318,9 @@ def main() -> int:
     }
 
     if not args.no_points:
+        # the same loop with the sampling that the command line starts with (temperature 0.7, top-k 50, top-p 0.9,
+        # repetition penalty 1.1 over the last 64 tokens)
+        sampled_ms, _ = end_to_end(SamplingParams(max_tokens=n_new, ignore_eos=True, seed=1))
         # prefill: one 2,048-token prompt in one step
         runner = eng.runner
         times = []
@@ -347,6 +355,7 @@ def main() -> int:
             points[f"decode_b{b}"] = round(b * 1e3 / ms_b, 1)
             points[f"decode_b{b}_ms_sd"] = round(sd_b, 4)
             points[f"decode_b{b}_frac"] = round(hbm_frac(b, ms_b, PROMPT_LEN + 4 + n_b / 2), 4)
+        points[f"e2e_b{args.batch}_sampled"] = round(args.batch * 1e3 / sampled_ms, 1)
         out["points"] = points
     del eng
     gc.collect()
