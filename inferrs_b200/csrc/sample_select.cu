@@ -533,21 +533,26 @@ IB_EXPORT int ib_sample(const float* logits, long ld, int n_rows, int vocab, con
     const size_t smem = (size_t)SMP_WARPS * 256 * (sizeof(u64) + sizeof(unsigned int));
     static IbDeviceSet configured;   // the attribute is kept per device
     if (const int e = ib_allow_dynamic_smem(configured, sample_kernel, smem)) return e;
-    cudaLaunchConfig_t cfg = {};
-    cfg.gridDim = dim3((unsigned)n_rows * cluster);
-    cfg.blockDim = dim3(SMP_THREADS);
-    cfg.dynamicSmemBytes = smem;
-    cfg.stream = stream;
-    cudaLaunchAttribute attr[2];
-    attr[0].id = cudaLaunchAttributeClusterDimension;
-    attr[0].val.clusterDim.x = cluster;
-    attr[0].val.clusterDim.y = 1;
-    attr[0].val.clusterDim.z = 1;
-    attr[1].id = cudaLaunchAttributeProgrammaticStreamSerialization;
-    attr[1].val.programmaticStreamSerializationAllowed = 1;
-    cfg.attrs = attr;
-    cfg.numAttrs = ib_pdl_enabled ? 2 : 1;
-    const cudaError_t e = cudaLaunchKernelEx(&cfg, sample_kernel, logits, ld, vocab, temperature, top_k, top_p, min_p,
-                                             uniform, scratch, out);
+    cudaError_t e = cudaSuccess;
+    for (;; cluster = 1) {   // a cluster that the device cannot place (a partitioned GPU) is tried again as single CTAs
+        cudaLaunchConfig_t cfg = {};
+        cfg.gridDim = dim3((unsigned)n_rows * cluster);
+        cfg.blockDim = dim3(SMP_THREADS);
+        cfg.dynamicSmemBytes = smem;
+        cfg.stream = stream;
+        cudaLaunchAttribute attr[2];
+        attr[0].id = cudaLaunchAttributeClusterDimension;
+        attr[0].val.clusterDim.x = cluster;
+        attr[0].val.clusterDim.y = 1;
+        attr[0].val.clusterDim.z = 1;
+        attr[1].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+        attr[1].val.programmaticStreamSerializationAllowed = 1;
+        cfg.attrs = attr;
+        cfg.numAttrs = ib_pdl_enabled ? 2 : 1;
+        e = cudaLaunchKernelEx(&cfg, sample_kernel, logits, ld, vocab, temperature, top_k, top_p, min_p, uniform,
+                               scratch, out);
+        if (e == cudaSuccess || cluster == 1) break;
+        (void)cudaGetLastError();
+    }
     return e == cudaSuccess ? ib_launch_status() : (int)e;
 }
