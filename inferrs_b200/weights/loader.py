@@ -123,11 +123,15 @@ def load_weights(model_dir: str, decls: Iterable[TensorDecl], dtype: torch.dtype
                 owner[name] = f
         names = check_declared(model_dir, decls, present)
         out: Dict[str, torch.Tensor] = {}
+        # for another device the bytes go there straight from the mapped file (the copy is done when .to() returns)
+        elsewhere = device is not None and torch.device(device).type != "cpu"
+        t = None
         for name in names:
-            t = convert_for(owner[name].read(name), present[name].dtype, dtype)
+            t = convert_for(owner[name].read(name, private=not elsewhere), present[name].dtype, dtype)
             if device is not None:
                 t = t.to(device)
             out[name] = t
+        del t
         return out
     finally:
         for f in files:

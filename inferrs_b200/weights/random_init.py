@@ -23,7 +23,7 @@ import torch
 
 from ..config.base import RawConfig, resolve_architecture
 from ..parts.spec import TensorDecl
-from .safetensors_io import write_safetensors
+from .safetensors_io import write_safetensors_streamed
 
 NORMAL_STD = 0.02
 NORM_SPREAD = 0.1
@@ -112,12 +112,14 @@ def random_weights(decls: Iterable[TensorDecl], seed: int, dtype: torch.dtype,
 
 
 def write_random_model(model_dir: str, config: dict, seed: int, dtype: torch.dtype = torch.bfloat16,
-                       tied: Optional[bool] = None) -> str:
+                       tied: Optional[bool] = None, device: Optional[torch.device] = None) -> str:
     """Write ``config.json`` and ``model.safetensors`` for ``config`` into ``model_dir``.
 
     ``tied``: leave the optional head tensor out (True) or write it (False);
     by default it is left out exactly when config.json says
-    ``tie_word_embeddings: true``.
+    ``tie_word_embeddings: true``.  The tensors are made one at a time, on ``device`` (by default the GPU if there
+    is one: the same bits as on the host, a hundred times as fast), and written as they come, so the folder of a
+    model larger than the host's memory can be written.
     """
     from .. import models  # noqa: F401  (registers the architectures)
     from ..engine.model import declared_tensors  # late: engine imports weights
@@ -128,11 +130,17 @@ def write_random_model(model_dir: str, config: dict, seed: int, dtype: torch.dty
     spec = arch.build_spec(cfg)
     if tied is None:
         tied = bool(config.get("tie_word_embeddings", False))
-    decls = declared_tensors(spec)
-    weights = random_weights(decls, seed, dtype, skip_optional=tied)
+    if device is None:
+        device = torch.device("cuda") if torch.cuda.is_available() else torch.device("cpu")
+    entries, seen = [], set()
+    for i, d in enumerate(declared_tensors(spec)):
+        if d.name in seen or (d.optional and tied):
+            continue
+        seen.add(d.name)
+        entries.append((d.name, tuple(d.shape), dtype, (lambda d=d, i=i: random_tensor(d, i, seed, dtype, device))))
     os.makedirs(model_dir, exist_ok=True)
     with open(os.path.join(model_dir, "config.json"), "w", encoding="utf-8") as f:
         json.dump(config, f, indent=1)
-    write_safetensors(os.path.join(model_dir, "model.safetensors"), weights.items(),
-                      metadata={"format": "pt", "seed": str(seed)})
+    write_safetensors_streamed(os.path.join(model_dir, "model.safetensors"), entries,
+                               metadata={"format": "pt", "seed": str(seed)})
     return model_dir

@@ -12,6 +12,7 @@ import json
 import mmap
 import os
 import struct
+import warnings
 from dataclasses import dataclass
 from typing import Dict, Iterable, List, Tuple
 
@@ -83,15 +84,22 @@ class SafetensorsFile:
             self.info[name] = TensorInfo(name, dtype, shape, b, e, path)
         self._mm = mmap.mmap(self._f.fileno(), 0, access=mmap.ACCESS_READ) if size > 0 else None
 
-    def read(self, name: str) -> torch.Tensor:
-        """The tensor, in its stored dtype, as a private copy on the CPU."""
+    def read(self, name: str, private: bool = True) -> torch.Tensor:
+        """The tensor, in its stored dtype, on the CPU: a private copy, or (``private=False``) a read-only view of
+        the mapped file for a caller that copies it elsewhere at once and drops the view before the file is
+        closed."""
         ti = self.info[name]
         tdt, ndt, _ = _DTYPES[ti.dtype]
         n = 1
         for s in ti.shape:
             n *= s
         arr = np.frombuffer(self._mm, dtype=ndt, count=n, offset=self._data_start + ti.begin)
-        t = torch.from_numpy(arr.copy())
+        if private:
+            t = torch.from_numpy(arr.copy())
+        else:
+            with warnings.catch_warnings():
+                warnings.simplefilter("ignore")       # torch warns that the array cannot be written to: nobody writes
+                t = torch.from_numpy(arr)
         if tdt == torch.bfloat16:
             t = t.view(torch.bfloat16)
         elif tdt == torch.bool:
@@ -100,38 +108,63 @@ class SafetensorsFile:
 
     def close(self):
         if self._mm is not None:
-            self._mm.close()
+            try:
+                self._mm.close()
+            except BufferError:      # a view from read(private=False) is still alive: the mapping goes when it does
+                pass
             self._mm = None
         self._f.close()
 
 
-def write_safetensors(path: str, tensors: Iterable[Tuple[str, torch.Tensor]], metadata: Dict[str, str] = None):
-    """Write tensors in the order given; the data section starts on an 8-byte boundary."""
+def _raw_bytes(name: str, t: torch.Tensor) -> bytes:
+    if t.dtype not in _TORCH_TO_NAME:
+        raise SafetensorsError(f"cannot store tensor '{name}' of dtype {t.dtype}")
+    t = t.detach().to("cpu").contiguous()
+    if t.dtype == torch.bfloat16:
+        return t.view(torch.int16).numpy().tobytes()
+    if t.dtype == torch.bool:
+        return t.to(torch.uint8).numpy().tobytes()
+    return t.numpy().tobytes()
+
+
+def write_safetensors_streamed(path: str, entries, metadata: Dict[str, str] = None):
+    """Write tensors that are made one at a time: ``entries`` is a list of (name, shape, dtype, make), where
+    ``make()`` returns the tensor when its turn has come.  Only one tensor is held at a time, so a model larger
+    than the host's memory can be written.  The data section starts on an 8-byte boundary."""
     header: Dict[str, dict] = {}
     if metadata:
         header["__metadata__"] = {str(k): str(v) for k, v in metadata.items()}
-    blobs: List[bytes] = []
     offset = 0
-    for name, t in tensors:
-        if t.dtype not in _TORCH_TO_NAME:
-            raise SafetensorsError(f"cannot store tensor '{name}' of dtype {t.dtype}")
-        t = t.detach().to("cpu").contiguous()
-        if t.dtype == torch.bfloat16:
-            raw = t.view(torch.int16).numpy().tobytes()
-        elif t.dtype == torch.bool:
-            raw = t.to(torch.uint8).numpy().tobytes()
-        else:
-            raw = t.numpy().tobytes()
-        header[name] = {"dtype": _TORCH_TO_NAME[t.dtype], "shape": list(t.shape),
-                        "data_offsets": [offset, offset + len(raw)]}
-        blobs.append(raw)
-        offset += len(raw)
+    for name, shape, dtype, _ in entries:
+        if dtype not in _TORCH_TO_NAME:
+            raise SafetensorsError(f"cannot store tensor '{name}' of dtype {dtype}")
+        n = 1
+        for d in shape:
+            n *= int(d)
+        size = n * _DTYPES[_TORCH_TO_NAME[dtype]][2]
+        header[name] = {"dtype": _TORCH_TO_NAME[dtype], "shape": [int(d) for d in shape],
+                        "data_offsets": [offset, offset + size]}
+        offset += size
     hjson = json.dumps(header, separators=(",", ":")).encode("utf-8")
     hjson += b" " * ((8 - len(hjson) % 8) % 8)
     tmp = path + ".tmp"
     with open(tmp, "wb") as f:
         f.write(struct.pack("<Q", len(hjson)))
         f.write(hjson)
-        for raw in blobs:
+        for name, shape, dtype, make in entries:
+            t = make()
+            if tuple(t.shape) != tuple(shape) or t.dtype != dtype:
+                raise SafetensorsError(f"tensor '{name}' was announced as {dtype} {tuple(shape)} and came as "
+                                       f"{t.dtype} {tuple(t.shape)}")
+            raw = _raw_bytes(name, t)
+            lo, hi = header[name]["data_offsets"]
+            if len(raw) != hi - lo:
+                raise SafetensorsError(f"tensor '{name}': {len(raw)} bytes where {hi - lo} were announced")
             f.write(raw)
     os.replace(tmp, path)
+
+
+def write_safetensors(path: str, tensors: Iterable[Tuple[str, torch.Tensor]], metadata: Dict[str, str] = None):
+    """Write tensors in the order given; the data section starts on an 8-byte boundary."""
+    entries = [(name, tuple(t.shape), t.dtype, (lambda t=t: t)) for name, t in tensors]
+    write_safetensors_streamed(path, entries, metadata)

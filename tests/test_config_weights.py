@@ -175,3 +175,28 @@ def test_generation_config_names_more_ids_that_end_a_request(tmp_path):
         (tmp_path / "generation_config.json").write_text(bad)
         with pytest.raises(ConfigError):
             generation_eos_ids(d, 100)
+
+
+def test_tensors_written_one_at_a_time_and_read_as_views(tmp_path):
+    """The writer that makes tensors as their turn comes writes the same file as the one that is handed all of them,
+    and refuses a tensor that is not what was announced; a view of the mapped file reads the same values as a copy."""
+    from inferrs_b200.weights.safetensors_io import SafetensorsError, write_safetensors_streamed
+    g = torch.Generator().manual_seed(3)
+    tensors = {"a": torch.randn((5, 7), generator=g).to(torch.bfloat16), "b": torch.arange(12, dtype=torch.int32).view(3, 4),
+               "c": torch.randn((9,), generator=g)}
+    whole, streamed = str(tmp_path / "whole.safetensors"), str(tmp_path / "streamed.safetensors")
+    write_safetensors(whole, tensors.items(), metadata={"k": "v"})
+    made = []
+    entries = [(n, tuple(t.shape), t.dtype, (lambda n=n, t=t: made.append(n) or t)) for n, t in tensors.items()]
+    write_safetensors_streamed(streamed, entries, metadata={"k": "v"})
+    assert made == ["a", "b", "c"]
+    assert open(whole, "rb").read() == open(streamed, "rb").read()
+    f = SafetensorsFile(streamed)
+    for n, t in tensors.items():
+        view = f.read(n, private=False)
+        assert torch.equal(view, t) and torch.equal(f.read(n), t)
+        del view
+    f.close()
+    with pytest.raises(SafetensorsError, match="announced"):
+        write_safetensors_streamed(streamed, [("a", (5, 8), torch.bfloat16, lambda: tensors["a"])])
+
