@@ -10,6 +10,7 @@
     python -m inferrs_b200.microbench workload --shape 32b --requests 8 --prompt-min 8192 --prompt-max 8192 \
         --max-context 16384
     python -m inferrs_b200.microbench workload --shape 0.6b --requests 256 --profile-steps 4 --skip-steps 10
+    python -m inferrs_b200.microbench sample --rows 8 --top-k 50 --top-p 0.9
 
 Every case is timed with CUDA events after warm-up; between timed launches a buffer larger than the
 L2 cache is written, so each launch starts cold.  One JSON line per case.
@@ -408,6 +409,22 @@ def _profile_steps(eng, args) -> dict:
             "adds_us_per_step": {k: [round(v / max(n, 1), 1), round(count.get(k, 0) / max(n, 1), 1)] for k, v in top}}
 
 
+def sample(args) -> dict:
+    """The selection kernel alone: one token per row of float32 logits [rows, vocab]."""
+    dev = torch.device("cuda")
+    g = torch.Generator(device="cuda").manual_seed(0)
+    logits = torch.randn((args.rows, args.vocab), device=dev, generator=g) * 3.0
+    t = torch.full((args.rows,), args.temperature, device=dev)
+    tk = torch.full((args.rows,), args.top_k, dtype=torch.int32, device=dev)
+    tp = torch.full((args.rows,), args.top_p, device=dev)
+    mp = torch.full((args.rows,), args.min_p, device=dev)
+    u = torch.rand((args.rows,), device=dev, generator=g)
+    out = torch.empty((args.rows,), dtype=torch.int32, device=dev)
+    us = _time(lambda: kernels.sample(logits, t, tk, tp, mp, u, out, torch.bfloat16, cluster=args.cluster), args.iters)
+    return {"kernel": "sample", "rows": args.rows, "vocab": args.vocab, "temperature": args.temperature,
+            "top_k": args.top_k, "top_p": args.top_p, "min_p": args.min_p, "cluster": args.cluster, "us": round(us, 1)}
+
+
 def main(argv=None) -> int:
     ap = argparse.ArgumentParser(prog="inferrs_b200.microbench", description=__doc__,
                                  formatter_class=argparse.RawDescriptionHelpFormatter)
@@ -470,6 +487,17 @@ def main(argv=None) -> int:
     st.add_argument("--iters", type=int, default=64)
     st.add_argument("--trace", action="store_true", help="print when every kernel of one step started and ended")
     st.set_defaults(fn=step)
+    sm = sub.add_parser("sample")
+    sm.add_argument("--rows", type=int, default=8)
+    sm.add_argument("--vocab", type=int, default=151936)
+    sm.add_argument("--temperature", type=float, default=0.7)
+    sm.add_argument("--top-k", type=int, default=50)
+    sm.add_argument("--top-p", type=float, default=0.9)
+    sm.add_argument("--min-p", type=float, default=0.0)
+    sm.add_argument("--cluster", type=int, default=0, help="CTAs per row (1, 2, 4, 8); 0 lets the library choose")
+    sm.add_argument("--iters", type=int, default=20)
+    sm.set_defaults(fn=sample)
+
     wl = sub.add_parser("workload")
     wl.add_argument("--shape", choices=sorted(SHAPES), default="0.6b")
     wl.add_argument("--layers", type=int, default=0, help="fewer layers than the shape has, for quick runs")
