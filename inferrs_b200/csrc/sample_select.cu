@@ -350,8 +350,8 @@ __global__ void __launch_bounds__(SMP_THREADS) sample_kernel(
     if (lane == 0) { sh.fred[warp] = bv; sh.ired[warp] = bi; }
     __syncthreads();
     if (warp == 0) {
-        bv = sh.fred[lane];
-        bi = sh.ired[lane];
+        bv = lane < SMP_WARPS ? sh.fred[lane] : -INFINITY;
+        bi = lane < SMP_WARPS ? sh.ired[lane] : 0x7fffffff;
 #pragma unroll
         for (int o = 16; o > 0; o >>= 1) {
             const float ov = __shfl_xor_sync(0xffffffffu, bv, o);
@@ -488,7 +488,7 @@ __global__ void __launch_bounds__(SMP_THREADS) sample_kernel(
     __syncthreads();
     SmpBoard* board = &sh.board[c.turn];
     if (warp == 0) {                       // the warps' totals: each warp's start, and the CTA's total
-        const int mine_w = sh.ired[lane];
+        const int mine_w = lane < SMP_WARPS ? sh.ired[lane] : 0;
         int upto_w = mine_w;
 #pragma unroll
         for (int o = 1; o < 32; o <<= 1) {
