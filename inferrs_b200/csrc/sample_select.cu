@@ -106,15 +106,16 @@ struct SmpCtx {
     int lo, hi;               // this CTA's stretch of the vocabulary
 };
 
-// One element per lane into the warp's own table.  Where most lanes share a bucket or two (the first level: e's
-// exponents; a row of equal logits at every level) those lanes are found with a ballot and summed with a warp
-// reduction; what is left after two such rounds (lanes with buckets of their own: the later levels, where the bits
-// are a mantissa's) goes in with shared-memory atomics, which then meet no other lane.
+// One element per lane into the warp's own table.  The lanes that share the first active lane's bucket (at the
+// first level, where the buckets are e's exponents, often most of the warp; in a row of equal logits all of it, at
+// every level) are found with a ballot and summed with a warp reduction; the others go in with shared-memory
+// atomics, which then meet few lanes with the same bucket.  (Measured on 148 rows of random logits: 455 us with one
+// such round, 477 with two, 678 with as many as there are buckets, 425 with none; on 148 rows of equal logits 716 us
+// with one round and 4,005 with none.)
 __device__ __forceinline__ void smp_warp_add(unsigned int* wc, u64* wm, bool active, int bucket, u64 mass) {
     const int lane = threadIdx.x & 31;
-    unsigned todo = __ballot_sync(0xffffffffu, active);
-#pragma unroll 1
-    for (int round = 0; round < 2 && todo; ++round) {
+    const unsigned todo = __ballot_sync(0xffffffffu, active);
+    if (todo) {
         const int leader = __ffs(todo) - 1;
         const int lb = __shfl_sync(0xffffffffu, bucket, leader);
         const bool mine = active && bucket == lb;
@@ -127,9 +128,8 @@ __device__ __forceinline__ void smp_warp_add(unsigned int* wc, u64* wm, bool act
             wm[lb] += ((u64)hi << 20) + lo;
         }
         active = active && !mine;
-        todo &= ~grp;
     }
-    __syncwarp();   // the leaders' plain additions are done before anybody's atomic ones, and before the next call
+    __syncwarp();   // the leader's plain additions are done before anybody's atomic ones, and before the next call
     if (active) {
         atomicAdd(&wc[bucket], 1u);
         atomicAdd(&wm[bucket], mass);
