@@ -315,8 +315,8 @@ SHAPES = {
 
 def workload(args) -> dict:
     """Requests through the engine's own scheduler, host token ids in and out, timed by the wall clock:
-    ``--requests`` prompts with lengths uniform in [--prompt-min, --prompt-max], ``--max-tokens`` greedy tokens
-    each, all added at once (continuous batching with prompts cut into portions of ``--prefill-chunk``)."""
+    ``--requests`` prompts with lengths uniform in [--prompt-min, --prompt-max], ``--max-tokens`` greedy (or, with
+    ``--sampled``, sampled) tokens each, all added at once (continuous batching with prompts cut into portions of ``--prefill-chunk``)."""
     import time
 
     from .engine.engine import Engine
@@ -334,7 +334,8 @@ def workload(args) -> dict:
     eng.warm_up()
     g = torch.Generator().manual_seed(7)
     lens = torch.randint(args.prompt_min, args.prompt_max + 1, (args.requests,), generator=g).tolist()
-    sp = SamplingParams.greedy(max_tokens=args.max_tokens, ignore_eos=True)
+    sp = SamplingParams(max_tokens=args.max_tokens, ignore_eos=True, seed=1) if args.sampled \
+        else SamplingParams.greedy(max_tokens=args.max_tokens, ignore_eos=True)
     for n in lens:
         eng.add_request(torch.randint(0, args.vocab, (n,), generator=g).tolist(), sp)
     torch.cuda.synchronize()
@@ -512,6 +513,9 @@ def main(argv=None) -> int:
     wl.add_argument("--page-size", type=int, default=16)
     wl.add_argument("--cache-share", type=float, default=1.0,
                     help="pages as a share of what all requests need at once (less: requests are preempted)")
+    wl.add_argument("--sampled", action="store_true",
+                    help="the command line's default sampling (temperature 0.7, top-k 50, top-p 0.9, repetition "
+                         "penalty 1.1) instead of greedy choice")
     wl.add_argument("--profile-steps", type=int, default=0,
                     help="instead of timing the workload: record this many steps and print what every kernel adds")
     wl.add_argument("--skip-steps", type=int, default=10, help="... after this many unrecorded steps")
