@@ -27,6 +27,7 @@
 #define SMP_WARPS (SMP_THREADS / 32)
 #define SMP_FIXED 1099511627776.0f  // 2^40
 #define SMP_MAX_CLUSTER 8
+#define SMP_LIST 2048                  // most elements that the list after top-k may hold (over all CTAs of a row)
 #define SMP_UNROLL 4                   // loads that a thread has on their way in the passes over a row
 
 typedef unsigned long long u64;
@@ -91,6 +92,11 @@ struct SmpShared {
     float fred[32];
     int ired[32];
     int scan[SMP_THREADS];
+    // the elements that survive top-k (those with a key above the k-th's, and all that share it): the head of the
+    // sorted order, as far as this CTA's stretch holds it
+    unsigned int list_key[SMP_LIST];
+    int list_at[SMP_LIST];
+    int list_n;
     // a descent step's answer, written by thread 0
     int found, bucket;
     unsigned int cnt_above, c_tau;
@@ -169,6 +175,31 @@ __device__ void smp_merge_tables(SmpCtx& c) {
     __syncthreads();
 }
 
+// The same for a table that the threads have added to this CTA's board directly (the few elements of the list, with
+// atomics): clear_board before, exchange_board after.
+__device__ void smp_clear_board(SmpCtx& c) {
+    SmpBoard* board = &c.sh->board[c.turn];
+    for (int b = threadIdx.x; b < 256; b += SMP_THREADS) { board->cnt[b] = 0; board->mass[b] = 0; }
+    __syncthreads();
+}
+__device__ void smp_exchange_board(SmpCtx& c) {
+    SmpShared* sh = c.sh;
+    SmpBoard* board = &sh->board[c.turn];
+    if (c.size > 1) smp_cluster_sync(); else __syncthreads();
+    for (int b = threadIdx.x; b < 256; b += SMP_THREADS) {
+        unsigned int n = 0;
+        u64 m = 0;
+        for (unsigned r = 0; r < c.size; ++r) {
+            n += c.size > 1 ? smp_remote(&board->cnt[b], r) : board->cnt[b];
+            m += c.size > 1 ? smp_remote(&board->mass[b], r) : board->mass[b];
+        }
+        sh->cnt[b] = n;
+        sh->mass[b] = m;
+    }
+    c.turn ^= 1;
+    __syncthreads();
+}
+
 // two numbers summed over the block and then over the cluster; every thread gets both sums
 __device__ void smp_sum2(SmpCtx& c, u64 a, u64 b, u64* a_out, u64* b_out) {
     SmpShared* sh = c.sh;
@@ -209,8 +240,11 @@ enum { SMP_COUNT_GE = 0, SMP_MASS_GE = 1, SMP_MASS_GT = 2 };
 // Returns the element's key `tau`, the count and mass of elements with key > tau, and how many share tau.
 // found == 0: the condition never holds (the goal exceeds the totals).  The first level reads the table that the
 // pass over the logits made; the others make theirs from the bits of the scratch row.
-__device__ void smp_descend(SmpCtx& c, const float* __restrict__ e_row, int mode, u64 goal, unsigned int* tau_out,
-                            unsigned int* cnt_above_out, u64* mass_above_out, unsigned int* c_tau_out, int* found_out) {
+// With `from_list` the elements are those of the list in shared memory instead of the row's (the list is the head of
+// the sorted order, so whatever holds at a rank inside it is found there as in the row), at every level.
+__device__ void smp_descend(SmpCtx& c, const float* __restrict__ e_row, bool from_list, int mode, u64 goal,
+                            unsigned int* tau_out, unsigned int* cnt_above_out, u64* mass_above_out,
+                            unsigned int* c_tau_out, int* found_out) {
     SmpShared* sh = c.sh;
     unsigned int prefix = 0, prefix_mask = 0;
     unsigned int cnt_above = 0;
@@ -221,7 +255,20 @@ __device__ void smp_descend(SmpCtx& c, const float* __restrict__ e_row, int mode
         const int shift = 24 - 8 * level;
         const unsigned int* cnt = sh->cnt0;
         const u64* mass = sh->mass0;
-        if (level > 0) {
+        if (from_list) {
+            smp_clear_board(c);
+            SmpBoard* board = &sh->board[c.turn];
+            for (int j = threadIdx.x; j < sh->list_n; j += SMP_THREADS) {
+                const unsigned int key = sh->list_key[j];
+                if ((key & prefix_mask) == prefix) {
+                    atomicAdd(&board->cnt[(key >> shift) & 255], 1u);
+                    atomicAdd(&board->mass[(key >> shift) & 255], smp_fixed(__uint_as_float(key)));
+                }
+            }
+            smp_exchange_board(c);
+            cnt = sh->cnt;
+            mass = sh->mass;
+        } else if (level > 0) {
             smp_clear_warp_tables(c);
             unsigned int* wc = c.warp_cnt + (threadIdx.x >> 5) * 256;
             u64* wm = c.warp_mass + (threadIdx.x >> 5) * 256;
@@ -424,34 +471,73 @@ __global__ void __launch_bounds__(SMP_THREADS) sample_kernel(
     unsigned int tau, ca, ct;
     u64 ma;
     int found;
+    // With top-k on, the elements that can still be chosen (those above the k-th, and all that share its key) are
+    // few.  They are gathered into shared memory once; the top-p cut, min-p, the draw and the look-up of the drawn
+    // token then go over this list, which is the head of the sorted order, instead of over the row.
+    bool listed = false;
     const int k = top_k[r];
     if (k > 0 && k < vocab) {
-        smp_descend(c, e_row, SMP_COUNT_GE, (u64)k, &tau, &ca, &ma, &ct, &found);
+        smp_descend(c, e_row, false, SMP_COUNT_GE, (u64)k, &tau, &ca, &ma, &ct, &found);
         if (found) {
             keep_cnt = k;
             keep_mass = ma + (u64)(k - ca) * smp_fixed(__uint_as_float(tau));
+            if ((u64)ca + ct <= SMP_LIST) {
+                if (threadIdx.x == 0) sh.list_n = 0;
+                __syncthreads();
+                for (int i0 = c.lo; i0 < c.hi; i0 += SMP_UNROLL * SMP_THREADS) {
+                    float e[SMP_UNROLL];
+#pragma unroll
+                    for (int u = 0; u < SMP_UNROLL; ++u) {
+                        const int i = i0 + u * SMP_THREADS + threadIdx.x;
+                        e[u] = i < c.hi ? e_row[i] : 0.0f;
+                    }
+#pragma unroll
+                    for (int u = 0; u < SMP_UNROLL; ++u) {
+                        const int i = i0 + u * SMP_THREADS + threadIdx.x;
+                        const unsigned int key = __float_as_uint(e[u]);   // e >= 0: the bits order as the values do
+                        if (i < c.hi && key >= tau) {
+                            const int at = atomicAdd(&sh.list_n, 1);
+                            sh.list_key[at] = key;
+                            sh.list_at[at] = i;
+                        }
+                    }
+                }
+                __syncthreads();
+                listed = true;
+            }
         }
     }
     const float tp = top_p[r];
     if (tp < 1.0f) {
         const u64 goal = (u64)((double)tp * (double)total);
-        smp_descend(c, e_row, SMP_MASS_GE, goal, &tau, &ca, &ma, &ct, &found);
-        if (found) {
-            const u64 pm = smp_fixed(__uint_as_float(tau));
-            u64 n = 1;
-            if (pm > 0 && goal > ma) n = (goal - ma + pm - 1) / pm;
-            if (n < 1) n = 1;
-            if (n > ct) n = ct;
-            if (ca + n < keep_cnt) { keep_cnt = ca + (unsigned int)n; keep_mass = ma + n * pm; }
+        // with the list: a goal beyond the mass of the first k is reached behind them, where the cut changes nothing
+        if (!listed || goal <= keep_mass) {
+            smp_descend(c, e_row, listed, SMP_MASS_GE, goal, &tau, &ca, &ma, &ct, &found);
+            if (found) {
+                const u64 pm = smp_fixed(__uint_as_float(tau));
+                u64 n = 1;
+                if (pm > 0 && goal > ma) n = (goal - ma + pm - 1) / pm;
+                if (n < 1) n = 1;
+                if (n > ct) n = ct;
+                if (ca + n < keep_cnt) { keep_cnt = ca + (unsigned int)n; keep_mass = ma + n * pm; }
+            }
         }
     }
     const float mp = min_p[r];
     if (mp > 0.0f) {
-        // e_max is 1, so "p >= min_p * p_max" is "e >= min_p"
+        // e_max is 1, so "p >= min_p * p_max" is "e >= min_p".  Over the list the count is the row's whenever it is
+        // below keep_cnt (then some listed element fails, and with it every element behind the list).
         u64 n = 0, m = 0;
-        for (int i = c.lo + threadIdx.x; i < c.hi; i += SMP_THREADS) {
-            const float e = e_row[i];
-            if (e >= mp) { n += 1; m += smp_fixed(e); }
+        if (listed) {
+            for (int j = threadIdx.x; j < sh.list_n; j += SMP_THREADS) {
+                const float e = __uint_as_float(sh.list_key[j]);
+                if (e >= mp) { n += 1; m += smp_fixed(e); }
+            }
+        } else {
+            for (int i = c.lo + threadIdx.x; i < c.hi; i += SMP_THREADS) {
+                const float e = e_row[i];
+                if (e >= mp) { n += 1; m += smp_fixed(e); }
+            }
         }
         u64 cm, mm;
         smp_sum2(c, n, m, &cm, &mm);
@@ -461,7 +547,7 @@ __global__ void __launch_bounds__(SMP_THREADS) sample_kernel(
     // the element of the kept list whose interval of cumulative mass holds u * keep_mass
     u64 target = (u64)((double)uniform[r] * (double)keep_mass);
     if (keep_mass > 0 && target >= keep_mass) target = keep_mass - 1;
-    smp_descend(c, e_row, SMP_MASS_GT, target, &tau, &ca, &ma, &ct, &found);
+    smp_descend(c, e_row, listed, SMP_MASS_GT, target, &tau, &ca, &ma, &ct, &found);
     if (!found) {  // no mass at all: the most probable token
         if (threadIdx.x == 0 && c.rank == 0) out[r] = imax;
         if (c.size > 1) smp_cluster_sync();
@@ -472,8 +558,35 @@ __global__ void __launch_bounds__(SMP_THREADS) sample_kernel(
     if (n >= ct) n = ct - 1;
     if (ca + n >= keep_cnt) n = keep_cnt > ca ? keep_cnt - 1 - ca : 0;
 
-    // the n-th token, in order of token id, whose key is tau: every thread counts a stretch of its own, the stretches
-    // before it (in its CTA, and in the CTAs with lower ranks) tell it where its matches stand
+    // the n-th token, in order of token id, whose key is tau
+    SmpBoard* board = &sh.board[c.turn];
+    if (listed) {
+        // this CTA's matches, and those of the CTAs with lower ranks (whose token ids are all lower)
+        int mine = 0;
+        for (int j = threadIdx.x; j < sh.list_n; j += SMP_THREADS) mine += (sh.list_key[j] == tau);
+        mine = (int)ib_warp_sum((float)mine);           // at most 2,048: exact in float32
+        if (lane == 0) sh.ired[warp] = mine;
+        __syncthreads();
+        if (threadIdx.x == 0) {
+            int all = 0;
+            for (int w = 0; w < SMP_WARPS; ++w) all += sh.ired[w];
+            board->sums[0] = (u64)all;
+        }
+        if (c.size > 1) smp_cluster_sync(); else __syncthreads();
+        u64 before = 0;
+        for (unsigned k2 = 0; k2 < c.rank; ++k2) before += smp_remote(&board->sums[0], k2);
+        for (int j = threadIdx.x; j < sh.list_n; j += SMP_THREADS) {
+            if (sh.list_key[j] != tau) continue;
+            const int at = sh.list_at[j];
+            u64 place = before;                         // matches with a lower token id
+            for (int j2 = 0; j2 < sh.list_n; ++j2) place += (sh.list_key[j2] == tau && sh.list_at[j2] < at);
+            if (place == n) out[r] = at;
+        }
+        if (c.size > 1) smp_cluster_sync();   // nobody leaves while its board may still be read
+        return;
+    }
+    // over the row: every thread counts a stretch of its own, the stretches before it (in its CTA, and in the CTAs
+    // with lower ranks) tell it where its matches stand
     const int chunk = (c.hi - c.lo + SMP_THREADS - 1) / SMP_THREADS;
     const int i0 = min(c.hi, c.lo + (int)threadIdx.x * chunk), i1 = min(c.hi, i0 + chunk);
     int mine = 0;
@@ -486,7 +599,6 @@ __global__ void __launch_bounds__(SMP_THREADS) sample_kernel(
     }
     if (lane == 31) sh.ired[warp] = upto;
     __syncthreads();
-    SmpBoard* board = &sh.board[c.turn];
     if (warp == 0) {                       // the warps' totals: each warp's start, and the CTA's total
         const int mine_w = lane < SMP_WARPS ? sh.ired[lane] : 0;
         int upto_w = mine_w;

@@ -45,7 +45,7 @@ def test_sample_kernel_matches_plain_sampler(vocab, opts):
 def test_a_row_shared_by_one_to_eight_ctas_gives_the_same_token(vocab):
     """The selection kernel cuts a row's vocabulary over a cluster of CTAs when there are few rows: whatever the
     cluster, every row gets the token that the plain selection gives (rows with every option, equal probabilities,
-    a row of one value, greedy rows)."""
+    a row of one value, greedy rows; top-k with few survivors, which the kernel keeps as a list, and with many)."""
     import kernel_refs as R
     from inferrs_b200 import kernels as K
     rows = 10
@@ -53,7 +53,8 @@ def test_a_row_shared_by_one_to_eight_ctas_gives_the_same_token(vocab):
     logits[3, 10] = logits[3, 200] = logits[3].max() + 1.0
     logits[4, :] = 0.25                                        # all equal: the walk counts token ids
     temperature = torch.tensor([0.8, 0.7, 1.3, 1.0, 1.0, 0.0, 0.7, 2.0, 0.7, 0.5]).cuda()
-    top_k = torch.tensor([0, 50, 0, 7, 0, 50, 1, 0, 1000, 3], dtype=torch.int32).cuda()
+    # (1,000 survivors of top-k are few enough for the kernel's list in shared memory, 3,000 are not)
+    top_k = torch.tensor([0, 50, 3000, 7, 0, 50, 1, 0, 1000, 3], dtype=torch.int32).cuda()
     top_p = torch.tensor([1.0, 0.9, 0.6, 1.0, 1.0, 0.9, 1.0, 0.999, 0.5, 1.0]).cuda()
     min_p = torch.tensor([0.0, 0.0, 0.0, 0.2, 0.0, 0.0, 0.0, 0.0, 0.01, 0.0]).cuda()
     # rows that walk the whole of a large vocabulary are left out of the comparison with the plain selection: far
