@@ -21,6 +21,9 @@
 //   * a warp adds its 32 elements to a table of its own: lanes that share a bucket are found
 //     with a ballot and summed with a warp reduction, so that atomic operations are left for
 //     lanes whose bucket no other lane has.
+//   * with top-k on, what can still be chosen after it (the elements above the k-th and all that
+//     share its key: the head of the sorted order) is gathered into shared memory once, and the
+//     top-p cut, min-p, the draw and the look-up of the drawn token go over that list.
 #include "common.cuh"
 
 #define SMP_THREADS 1024
